@@ -1,0 +1,73 @@
+"""ctypes binding of the C ABI declared in include/agention_b200.h.
+
+Loading fails loudly when libagention_b200.so is missing or cannot be loaded:
+there is no Python or CPU substitute for the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libagention_b200.so"
+
+AGN_OK, AGN_EINVAL, AGN_EUNSUPPORTED_DTYPE, AGN_ECUDA, AGN_EOOB_ID, AGN_ENOMEM, AGN_ETIMEOUT = range(7)
+AGN_F32, AGN_F16, AGN_Q8_0, AGN_Q4_K, AGN_Q6_K, AGN_BF16 = 0, 1, 8, 12, 14, 30
+AGN_ROPE_NEOX, AGN_ROPE_NORMAL = 0, 1
+
+_vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
+_pp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes); must list every AGN_API symbol of the header
+SIGNATURES = {
+    "agn_ctx_create": (_i32, [_i32, _pp]),
+    "agn_ctx_destroy": (_i32, [_vp]),
+    "agn_backend_name": (C.c_char_p, []),
+    "agn_last_error": (C.c_char_p, [_vp]),
+    "agn_status_string": (C.c_char_p, [_i32]),
+    "agn_ctx_set_stream": (_i32, [_vp, _vp]),
+    "agn_ctx_get_stream": (_i32, [_vp, _pp]),
+    "agn_ctx_launch_count": (C.c_uint64, [_vp]),
+    "agn_malloc": (_i32, [_vp, _sz, _pp]),
+    "agn_free": (_i32, [_vp, _vp]),
+    "agn_host_alloc": (_i32, [_vp, _sz, _pp]),
+    "agn_host_free": (_i32, [_vp, _vp]),
+    "agn_memcpy_h2d": (_i32, [_vp, _vp, _vp, _sz]),
+    "agn_memcpy_d2h": (_i32, [_vp, _vp, _vp, _sz]),
+    "agn_memset": (_i32, [_vp, _vp, C.c_int, _sz]),
+    "agn_sync": (_i32, [_vp]),
+    "agn_event_create": (_i32, [_vp, _pp]),
+    "agn_event_record": (_i32, [_vp, _vp]),
+    "agn_event_elapsed_ms": (_i32, [_vp, _vp, _vp, C.POINTER(C.c_float)]),
+    "agn_event_destroy": (_i32, [_vp, _vp]),
+    "agn_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "agn_add_residual_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "agn_rope_f32": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),
+    "agn_rope_qk_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),
+    "agn_qk_norm_rope_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _f32, _i32, _vp, _i32, _f32, _f32, _i32]),
+    "agn_qk_norm_rope_qk_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32,
+                                       _f32, _f32, _i32]),
+    "agn_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
+    "agn_softmax_rows_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32]),
+    "agn_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
+    "agn_type_size": (_sz, [_i32, _sz]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """dlopen the CUDA library and type every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m agention_infer_b200.build` "
+            "(there is no fallback implementation)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,254 @@
+"""Host-side mirror of the reference's GPU operator surface over the C ABI.
+
+`CudaBackend` carries the same operator names and argument meaning as the
+reference's `WgpuBackend::launch_*` family (src/ops/wgpu_backend/resident.rs:187-443)
+and `WeightMap::dequant_row` (src/model/mod.rs:343-348), extended from one token
+vector per call to T token rows per call.  It is a thin ctypes layer: every method
+is one call into libagention_b200.so; nothing is computed in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import numpy as np
+
+from . import _abi
+from ._abi import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q4_K, AGN_Q6_K, AGN_Q8_0,  # noqa: F401
+                   AGN_ROPE_NEOX, AGN_ROPE_NORMAL)
+
+
+class BackendError(RuntimeError):
+    """`GgufError::BackendError` (src/error.rs:37-38) plus the ABI status code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[agn status {status}] {message}")
+        self.status = status
+
+
+class DeviceBuffer:
+    """A device allocation owned by a backend (the role of a cubecl `Handle`)."""
+
+    def __init__(self, backend: "CudaBackend", ptr: int, nbytes: int):
+        self.backend, self.ptr, self.nbytes = backend, ptr, nbytes
+
+    def data_ptr(self) -> int:
+        return self.ptr
+
+    def free(self) -> None:
+        if self.ptr:
+            self.backend._free(self.ptr)
+            self.ptr = 0
+
+    def __del__(self):  # best effort
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _ptr(obj) -> Optional[int]:
+    if obj is None:
+        return None
+    if isinstance(obj, int):
+        return obj
+    return int(obj.data_ptr())  # DeviceBuffer or torch CUDA tensor
+
+
+class CudaBackend:
+    """One GPU, one stream.  Replaces `create_backend(BackendPreference::Cuda)`
+    (src/ops/backend_select.rs:60-108), whose Cuda arm silently falls back to CPU."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _abi.load()
+        ctx = C.c_void_p()
+        st = self._lib.agn_ctx_create(device, C.byref(ctx))
+        if st != _abi.AGN_OK:
+            raise BackendError(st, f"no usable CUDA device {device} (this backend has no CPU fallback)")
+        self._ctx = ctx
+        self.device = device
+
+    # ------------------------------------------------------------ plumbing
+    def close(self) -> None:
+        if getattr(self, "_ctx", None):
+            self._lib.agn_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st: int) -> None:
+        if st != _abi.AGN_OK:
+            raise BackendError(st, self._lib.agn_last_error(self._ctx).decode())
+
+    def name(self) -> str:
+        """`Backend::name` (src/ops/mod.rs:99)."""
+        return self._lib.agn_backend_name().decode()
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.agn_ctx_launch_count(self._ctx))
+
+    def set_stream(self, cuda_stream: Optional[int]) -> None:
+        self._check(self._lib.agn_ctx_set_stream(self._ctx, cuda_stream))
+
+    def stream(self) -> int:
+        p = C.c_void_p()
+        self._check(self._lib.agn_ctx_get_stream(self._ctx, C.byref(p)))
+        return p.value or 0
+
+    def sync(self) -> None:
+        self._check(self._lib.agn_sync(self._ctx))
+
+    def empty(self, nbytes: int) -> DeviceBuffer:
+        """`client.empty(bytes)` (src/ops/wgpu_backend/resident.rs:195)."""
+        p = C.c_void_p()
+        self._check(self._lib.agn_malloc(self._ctx, nbytes, C.byref(p)))
+        return DeviceBuffer(self, p.value or 0, nbytes)
+
+    def _free(self, ptr: int) -> None:
+        if getattr(self, "_ctx", None):
+            self._lib.agn_free(self._ctx, ptr)
+
+    def upload(self, arr: np.ndarray) -> DeviceBuffer:
+        """`upload_act` / `create_from_slice` (src/ops/wgpu_backend/resident.rs:673-690)."""
+        arr = np.ascontiguousarray(arr)
+        buf = self.empty(max(arr.nbytes, 1))
+        self.copy_h2d(buf, arr)
+        self.sync()  # pageable source: make the copy complete before `arr` can change
+        return buf
+
+    def copy_h2d(self, dst, src: np.ndarray, nbytes: Optional[int] = None) -> None:
+        n = src.nbytes if nbytes is None else nbytes
+        self._check(self._lib.agn_memcpy_h2d(self._ctx, _ptr(dst), src.ctypes.data, n))
+
+    def copy_d2h(self, dst: np.ndarray, src, nbytes: Optional[int] = None) -> None:
+        n = dst.nbytes if nbytes is None else nbytes
+        self._check(self._lib.agn_memcpy_d2h(self._ctx, dst.ctypes.data, _ptr(src), n))
+
+    def read(self, buf, dtype, shape) -> np.ndarray:
+        """`read_handle` (src/ops/wgpu_backend/resident.rs:696-699): copy back and sync."""
+        out = np.empty(shape, dtype=dtype)
+        self.copy_d2h(out, buf)
+        self.sync()
+        return out
+
+    def pinned(self, shape, dtype) -> np.ndarray:
+        """A page-locked host array (freed with `free_pinned`)."""
+        nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        self._check(self._lib.agn_host_alloc(self._ctx, max(nbytes, 1), C.byref(p)))
+        raw = (C.c_uint8 * max(nbytes, 1)).from_address(p.value)
+        arr = np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+        self._pinned = getattr(self, "_pinned", {})
+        self._pinned[arr.ctypes.data] = p.value
+        return arr
+
+    def free_pinned(self, arr: np.ndarray) -> None:
+        p = getattr(self, "_pinned", {}).pop(arr.ctypes.data, None)
+        if p:
+            self._check(self._lib.agn_host_free(self._ctx, p))
+
+    # ---------------------------------------------------------- GPU timing
+    def event(self) -> int:
+        e = C.c_void_p()
+        self._check(self._lib.agn_event_create(self._ctx, C.byref(e)))
+        return e.value
+
+    def record(self, ev: int) -> None:
+        self._check(self._lib.agn_event_record(self._ctx, ev))
+
+    def elapsed_ms(self, start: int, stop: int) -> float:
+        ms = C.c_float()
+        self._check(self._lib.agn_event_elapsed_ms(self._ctx, start, stop, C.byref(ms)))
+        return float(ms.value)
+
+    def destroy_event(self, ev: int) -> None:
+        self._check(self._lib.agn_event_destroy(self._ctx, ev))
+
+    # ------------------------------------------------------------ layer ops
+    def launch_rms_norm(self, x, w, T: int, H: int, eps: float, out=None):
+        """`launch_rms_norm(x, weight, len, eps) -> Handle` (resident.rs:213-235) over T rows."""
+        if out is None:
+            out = self.empty(4 * T * H)
+        self._check(self._lib.agn_rms_norm_f32(self._ctx, _ptr(x), _ptr(w), _ptr(out), T, H, eps))
+        return out
+
+    def launch_add_residual_rms_norm(self, x, delta, w, T: int, H: int, eps: float, new_x=None, normed=None) -> Tuple:
+        """`launch_add_residual_rms_norm(..) -> (new_x, normed)` (resident.rs:240-266)."""
+        if new_x is None:
+            new_x = self.empty(4 * T * H)
+        if normed is None:
+            normed = self.empty(4 * T * H)
+        self._check(self._lib.agn_add_residual_rms_norm_f32(self._ctx, _ptr(x), _ptr(delta), _ptr(w), _ptr(new_x),
+                                                            _ptr(normed), T, H, eps))
+        return new_x, normed
+
+    def launch_rope(self, x, T: int, n_heads: int, head_dim: int, n_rot: int, pos, theta: float,
+                    freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX, pos_start: int = 0) -> None:
+        """`launch_rope(handle, n_heads, head_dim, n_rot, pos, theta)` in place (resident.rs:326-353).
+        `pos` is a device int32 array [T], or None for positions pos_start + t."""
+        self._check(self._lib.agn_rope_f32(self._ctx, _ptr(x), T, n_heads, head_dim, n_rot, _ptr(pos), pos_start,
+                                           theta, freq_scale, layout))
+
+    def launch_rope_qk(self, q, k, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, n_rot: int, pos,
+                       theta: float, freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX, pos_start: int = 0) -> None:
+        """CPU `rope(q, k, pos)` (src/model/llama/cpu_path.rs:99-133): both buffers, one launch."""
+        self._check(self._lib.agn_rope_qk_f32(self._ctx, _ptr(q), _ptr(k), T, n_q_heads, n_kv_heads, head_dim, n_rot,
+                                              _ptr(pos), pos_start, theta, freq_scale, layout))
+
+    def launch_qk_norm_rope(self, x, w, T: int, n_heads: int, head_dim: int, eps: float, n_rot: int, pos,
+                            theta: float, freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX,
+                            pos_start: int = 0) -> None:
+        """`launch_qk_norm_rope(handle, weight, n_heads, head_dim, eps, n_rot, pos, theta)` (resident.rs:414-443)."""
+        self._check(self._lib.agn_qk_norm_rope_f32(self._ctx, _ptr(x), _ptr(w), T, n_heads, head_dim, eps, n_rot,
+                                                   _ptr(pos), pos_start, theta, freq_scale, layout))
+
+    def launch_qk_norm_rope_qk(self, q, k, wq, wk, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, eps: float,
+                               n_rot: int, pos, theta: float, freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX,
+                               pos_start: int = 0) -> None:
+        """Per-position QK-norm -> RoPE of both Q and K (cpu_path.rs:896-906), one launch."""
+        self._check(self._lib.agn_qk_norm_rope_qk_f32(self._ctx, _ptr(q), _ptr(k), _ptr(wq), _ptr(wk), T, n_q_heads,
+                                                      n_kv_heads, head_dim, eps, n_rot, _ptr(pos), pos_start, theta,
+                                                      freq_scale, layout))
+
+    def launch_silu_mul(self, gate, up, n: int, out=None):
+        """`launch_silu_mul(gate, up, len) -> Handle` (resident.rs:187-209)."""
+        if out is None:
+            out = self.empty(4 * n)
+        self._check(self._lib.agn_silu_mul_f32(self._ctx, _ptr(gate), _ptr(up), _ptr(out), n))
+        return out
+
+    def launch_softmax_rows(self, scores, n_rows: int, row_len: int, out=None, row_stride: Optional[int] = None,
+                            n_valid=None, causal_period: int = 0, causal_offset: int = 0):
+        """Softmax step of `launch_attention` (resident.rs:551-565) / cpu_path.rs:175-183, normalised."""
+        if row_stride is None:
+            row_stride = row_len
+        if out is None:
+            out = self.empty(4 * n_rows * row_stride)
+        self._check(self._lib.agn_softmax_rows_f32(self._ctx, _ptr(scores), _ptr(out), n_rows, row_len, row_stride,
+                                                   _ptr(n_valid), causal_period, causal_offset))
+        return out
+
+    def get_rows(self, dtype: int, table, table_bytes: int, n_rows: int, row_len: int, ids, T: int, out=None):
+        """Embedding loop `dequant_row(token_embd, token)` for T tokens (cpu_path.rs:865-868)."""
+        if out is None:
+            out = self.empty(4 * T * row_len)
+        self._check(self._lib.agn_get_rows_f32(self._ctx, dtype, _ptr(table), table_bytes, n_rows, row_len, _ptr(ids),
+                                               T, _ptr(out)))
+        return out
+
+    def dequant_row(self, dtype: int, table, table_bytes: int, n_rows: int, row_len: int, row: int) -> np.ndarray:
+        """`WeightMap::dequant_row(name, row) -> Vec<f32>` (src/model/mod.rs:343-348) on the GPU.
+        An out-of-range row raises, as the reference returns Err (src/quant/mod.rs:116-120)."""
+        ids = self.upload(np.array([row], dtype=np.uint32))
+        out = self.get_rows(dtype, table, table_bytes, n_rows, row_len, ids, 1)
+        return self.read(out, np.float32, (row_len,))
+
+    @staticmethod
+    def type_size(dtype: int, n: int) -> int:
+        """`GgmlType::type_size` (src/types.rs:164-168)."""
+        return int(_abi.load().agn_type_size(dtype, n))

@@ -1,0 +1,98 @@
+// Shared internals of libagention_b200: context struct, error plumbing, device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <mutex>
+#include <string>
+
+#include "agention_b200.h"
+
+// Device-side error bits kernels may OR into agn_ctx::d_flags[0].
+#define AGN_FLAG_OOB_ID 1u
+#define AGN_FLAG_TIMEOUT 2u
+
+#define AGN_ROPE_CACHE_SLOTS 16
+#define AGN_ROPE_MAX_HALF 512  // n_rot <= 1024
+
+struct agn_rope_slot {
+    uint32_t theta_bits;
+    int32_t n_rot;
+    bool used;
+};
+
+struct agn_ctx {
+    int device;
+    int sm_count;
+    cudaStream_t own_stream;
+    cudaStream_t stream;        // own_stream or an adopted one
+    uint32_t *d_flags;          // [4] device error bits
+    uint32_t *h_flags;          // pinned mirror
+    float *d_rope_denom;        // [AGN_ROPE_CACHE_SLOTS][AGN_ROPE_MAX_HALF]
+    float *h_rope_denom;        // pinned staging, same shape
+    agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
+    int rope_next;
+    bool flags_dirty;           // a kernel that can raise a flag ran since the last sync
+    uint64_t launches;
+    std::string last_error;
+};
+
+struct agn_event {
+    cudaEvent_t ev;
+};
+
+int32_t agn_fail(agn_ctx *ctx, int32_t status, const char *fmt, ...);
+
+// Device pointer to the powf(theta, 2d/n_rot) table, d < n_rot/2 (built on the host
+// with libm the first time a (theta, n_rot) pair is seen).
+int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d_table);
+
+#define AGN_CHECK_CTX(ctx) \
+    do {                   \
+        if (!(ctx)) return AGN_EINVAL; \
+    } while (0)
+
+#define AGN_CUDA(ctx, call)                                                            \
+    do {                                                                               \
+        cudaError_t _e = (call);                                                       \
+        if (_e != cudaSuccess)                                                         \
+            return agn_fail((ctx), AGN_ECUDA, "%s failed: %s (%s:%d)", #call,          \
+                            cudaGetErrorString(_e), __FILE__, __LINE__);               \
+    } while (0)
+
+// After a kernel launch: count it and surface launch-configuration errors.
+#define AGN_LAUNCHED(ctx, name)                                                        \
+    do {                                                                               \
+        (ctx)->launches++;                                                             \
+        cudaError_t _e = cudaPeekAtLastError();                                        \
+        if (_e != cudaSuccess) {                                                       \
+            (void)cudaGetLastError();                                                  \
+            return agn_fail((ctx), AGN_ECUDA, "launch of %s failed: %s", name,         \
+                            cudaGetErrorString(_e));                                   \
+        }                                                                              \
+    } while (0)
+
+static inline bool agn_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float agn_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float agn_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Streaming (read-once / write-once) 128-bit accesses: keep them from displacing
+// reusable lines (weights, tables) in L1/L2.
+__device__ __forceinline__ float4 agn_ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void agn_st_stream(float4 *p, float4 v) { __stcs(p, v); }
+
+#endif  // __CUDACC__

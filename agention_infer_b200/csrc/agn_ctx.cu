@@ -1,0 +1,282 @@
+// Context, memory, stream, events and the RoPE denominator cache of libagention_b200.
+#include <math.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include "agn_common.cuh"
+
+int32_t agn_fail(agn_ctx *ctx, int32_t status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->last_error = buf;
+    return status;
+}
+
+extern "C" {
+
+const char *agn_backend_name(void) { return "cuda-sm100a"; }
+
+const char *agn_status_string(int32_t s) {
+    switch (s) {
+    case AGN_OK: return "ok";
+    case AGN_EINVAL: return "invalid argument";
+    case AGN_EUNSUPPORTED_DTYPE: return "unsupported tensor type";
+    case AGN_ECUDA: return "CUDA error";
+    case AGN_EOOB_ID: return "row index out of range";
+    case AGN_ENOMEM: return "out of memory";
+    case AGN_ETIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+    }
+}
+
+int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
+    if (!out) return AGN_EINVAL;
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || device < 0 || device >= n) {
+        (void)cudaGetLastError();
+        return AGN_ECUDA;  // no device: never fall back to a CPU path
+    }
+    agn_ctx *ctx = new agn_ctx();
+    ctx->device = device;
+    ctx->launches = 0;
+    ctx->rope_next = 0;
+    ctx->flags_dirty = false;
+    ctx->d_flags = nullptr;
+    ctx->h_flags = nullptr;
+    ctx->d_rope_denom = nullptr;
+    ctx->h_rope_denom = nullptr;
+    ctx->own_stream = nullptr;
+    memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
+    const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
+    bool ok = cudaSetDevice(device) == cudaSuccess &&
+              cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaMalloc(&ctx->d_flags, 4 * sizeof(uint32_t)) == cudaSuccess &&
+              cudaMemset(ctx->d_flags, 0, 4 * sizeof(uint32_t)) == cudaSuccess &&
+              cudaHostAlloc(&ctx->h_flags, 4 * sizeof(uint32_t), cudaHostAllocDefault) == cudaSuccess &&
+              cudaMalloc(&ctx->d_rope_denom, rope_bytes) == cudaSuccess &&
+              cudaHostAlloc(&ctx->h_rope_denom, rope_bytes, cudaHostAllocDefault) == cudaSuccess;
+    if (!ok) {
+        (void)cudaGetLastError();
+        agn_ctx_destroy(ctx);
+        return AGN_ECUDA;
+    }
+    ctx->stream = ctx->own_stream;
+    *out = ctx;
+    return AGN_OK;
+}
+
+int32_t agn_ctx_destroy(agn_ctx *ctx) {
+    if (!ctx) return AGN_EINVAL;
+    cudaSetDevice(ctx->device);
+    if (ctx->own_stream) {
+        cudaStreamSynchronize(ctx->own_stream);
+        cudaStreamDestroy(ctx->own_stream);
+    }
+    if (ctx->d_flags) cudaFree(ctx->d_flags);
+    if (ctx->h_flags) cudaFreeHost(ctx->h_flags);
+    if (ctx->d_rope_denom) cudaFree(ctx->d_rope_denom);
+    if (ctx->h_rope_denom) cudaFreeHost(ctx->h_rope_denom);
+    (void)cudaGetLastError();
+    delete ctx;
+    return AGN_OK;
+}
+
+const char *agn_last_error(agn_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int32_t agn_ctx_set_stream(agn_ctx *ctx, void *cuda_stream) {
+    AGN_CHECK_CTX(ctx);
+    ctx->stream = cuda_stream ? reinterpret_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+    return AGN_OK;
+}
+
+int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream) {
+    AGN_CHECK_CTX(ctx);
+    if (!cuda_stream) return agn_fail(ctx, AGN_EINVAL, "agn_ctx_get_stream: null out pointer");
+    *cuda_stream = reinterpret_cast<void *>(ctx->stream);
+    return AGN_OK;
+}
+
+uint64_t agn_ctx_launch_count(agn_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t agn_malloc(agn_ctx *ctx, size_t bytes, void **dptr) {
+    AGN_CHECK_CTX(ctx);
+    if (!dptr) return agn_fail(ctx, AGN_EINVAL, "agn_malloc: null out pointer");
+    *dptr = nullptr;
+    if (bytes == 0) return AGN_OK;
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaError_t e = cudaMalloc(dptr, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        return agn_fail(ctx, AGN_ENOMEM, "agn_malloc: %zu bytes not available on device %d", bytes, ctx->device);
+    }
+    AGN_CUDA(ctx, e);
+    return AGN_OK;
+}
+
+int32_t agn_free(agn_ctx *ctx, void *dptr) {
+    AGN_CHECK_CTX(ctx);
+    if (!dptr) return AGN_OK;
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    AGN_CUDA(ctx, cudaFree(dptr));
+    return AGN_OK;
+}
+
+int32_t agn_host_alloc(agn_ctx *ctx, size_t bytes, void **hptr) {
+    AGN_CHECK_CTX(ctx);
+    if (!hptr) return agn_fail(ctx, AGN_EINVAL, "agn_host_alloc: null out pointer");
+    *hptr = nullptr;
+    if (bytes == 0) return AGN_OK;
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaError_t e = cudaHostAlloc(hptr, bytes, cudaHostAllocDefault);
+    if (e == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        return agn_fail(ctx, AGN_ENOMEM, "agn_host_alloc: %zu pinned bytes not available", bytes);
+    }
+    AGN_CUDA(ctx, e);
+    return AGN_OK;
+}
+
+int32_t agn_host_free(agn_ctx *ctx, void *hptr) {
+    AGN_CHECK_CTX(ctx);
+    if (!hptr) return AGN_OK;
+    AGN_CUDA(ctx, cudaFreeHost(hptr));
+    return AGN_OK;
+}
+
+int32_t agn_memcpy_h2d(agn_ctx *ctx, void *dst, const void *src, size_t bytes) {
+    AGN_CHECK_CTX(ctx);
+    if (bytes == 0) return AGN_OK;
+    if (!dst || !src) return agn_fail(ctx, AGN_EINVAL, "agn_memcpy_h2d: null pointer");
+    AGN_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return AGN_OK;
+}
+
+int32_t agn_memcpy_d2h(agn_ctx *ctx, void *dst, const void *src, size_t bytes) {
+    AGN_CHECK_CTX(ctx);
+    if (bytes == 0) return AGN_OK;
+    if (!dst || !src) return agn_fail(ctx, AGN_EINVAL, "agn_memcpy_d2h: null pointer");
+    AGN_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return AGN_OK;
+}
+
+int32_t agn_memset(agn_ctx *ctx, void *dst, int value, size_t bytes) {
+    AGN_CHECK_CTX(ctx);
+    if (bytes == 0) return AGN_OK;
+    if (!dst) return agn_fail(ctx, AGN_EINVAL, "agn_memset: null pointer");
+    AGN_CUDA(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream));
+    return AGN_OK;
+}
+
+int32_t agn_sync(agn_ctx *ctx) {
+    AGN_CHECK_CTX(ctx);
+    if (ctx->flags_dirty) {
+        AGN_CUDA(ctx, cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    AGN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->flags_dirty) {
+        ctx->flags_dirty = false;
+        uint32_t f = ctx->h_flags[0];
+        if (f) {
+            AGN_CUDA(ctx, cudaMemsetAsync(ctx->d_flags, 0, sizeof(uint32_t), ctx->stream));
+            AGN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            if (f & AGN_FLAG_TIMEOUT)
+                return agn_fail(ctx, AGN_ETIMEOUT, "a staging wait in a kernel gave up; outputs of that launch are invalid");
+            return agn_fail(ctx, AGN_EOOB_ID, "get_rows: row index out of range (those output rows are zero)");
+        }
+    }
+    return AGN_OK;
+}
+
+int32_t agn_event_create(agn_ctx *ctx, agn_event **ev) {
+    AGN_CHECK_CTX(ctx);
+    if (!ev) return agn_fail(ctx, AGN_EINVAL, "agn_event_create: null out pointer");
+    agn_event *e = new agn_event();
+    cudaError_t ce = cudaEventCreate(&e->ev);
+    if (ce != cudaSuccess) {
+        delete e;
+        AGN_CUDA(ctx, ce);
+    }
+    *ev = e;
+    return AGN_OK;
+}
+
+int32_t agn_event_record(agn_ctx *ctx, agn_event *ev) {
+    AGN_CHECK_CTX(ctx);
+    if (!ev) return agn_fail(ctx, AGN_EINVAL, "agn_event_record: null event");
+    AGN_CUDA(ctx, cudaEventRecord(ev->ev, ctx->stream));
+    return AGN_OK;
+}
+
+int32_t agn_event_elapsed_ms(agn_ctx *ctx, agn_event *start, agn_event *stop, float *ms) {
+    AGN_CHECK_CTX(ctx);
+    if (!start || !stop || !ms) return agn_fail(ctx, AGN_EINVAL, "agn_event_elapsed_ms: null argument");
+    AGN_CUDA(ctx, cudaEventSynchronize(stop->ev));
+    AGN_CUDA(ctx, cudaEventElapsedTime(ms, start->ev, stop->ev));
+    return AGN_OK;
+}
+
+int32_t agn_event_destroy(agn_ctx *ctx, agn_event *ev) {
+    AGN_CHECK_CTX(ctx);
+    if (!ev) return AGN_OK;
+    cudaEventDestroy(ev->ev);
+    delete ev;
+    return AGN_OK;
+}
+
+size_t agn_type_size(int32_t dtype, size_t n) {
+    // GgmlType::block_size / block_bytes / type_size, src/types.rs:88-168
+    size_t bs, bb;
+    switch (dtype) {
+    case AGN_F32: bs = 1; bb = 4; break;
+    case AGN_F16: case AGN_BF16: bs = 1; bb = 2; break;
+    case AGN_Q8_0: bs = 32; bb = 34; break;
+    case AGN_Q4_K: bs = 256; bb = 144; break;
+    case AGN_Q6_K: bs = 256; bb = 210; break;
+    default: return 0;
+    }
+    return ((n + bs - 1) / bs) * bb;
+}
+
+}  // extern "C"
+
+// The reference builds its sin/cos table from
+//   freq = pos as f32 * freq_scale / theta.powf(2.0 * d as f32 / n_rot as f32)
+// (src/model/llama/cpu_path.rs:107-112, :474-479).  Device powf differs from libm's by
+// an ulp now and then, which at pos ~ 3e4 moves the angle by ~1e-3 rad.  The powf values
+// are therefore produced here, once per (theta, n_rot), by the host libm, and the kernel
+// only performs the IEEE multiply and divide.
+int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d_table) {
+    const int half = n_rot / 2;
+    if (half < 1 || half > AGN_ROPE_MAX_HALF)
+        return agn_fail(ctx, AGN_EINVAL, "rope: n_rot=%d outside [2, %d]", n_rot, 2 * AGN_ROPE_MAX_HALF);
+    uint32_t bits;
+    memcpy(&bits, &theta, 4);
+    for (int s = 0; s < AGN_ROPE_CACHE_SLOTS; s++) {
+        const agn_rope_slot &sl = ctx->rope_slots[s];
+        if (sl.used && sl.theta_bits == bits && sl.n_rot == n_rot) {
+            *d_table = ctx->d_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
+            return AGN_OK;
+        }
+    }
+    const int s = ctx->rope_next;
+    ctx->rope_next = (ctx->rope_next + 1) % AGN_ROPE_CACHE_SLOTS;
+    float *h = ctx->h_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
+    float *d = ctx->d_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
+    if (ctx->rope_slots[s].used) {
+        // The pinned staging slot may still be the source of an in-flight copy.
+        AGN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    for (int i = 0; i < half; i++) h[i] = powf(theta, 2.0f * (float)i / (float)n_rot);
+    AGN_CUDA(ctx, cudaMemcpyAsync(d, h, sizeof(float) * half, cudaMemcpyHostToDevice, ctx->stream));
+    ctx->rope_slots[s].used = true;
+    ctx->rope_slots[s].theta_bits = bits;
+    ctx->rope_slots[s].n_rot = n_rot;
+    *d_table = d;
+    return AGN_OK;
+}

@@ -1,0 +1,241 @@
+// Embedding get_rows with inline dequantisation (Q8_0 / Q4_K / Q6_K / F16 / BF16 / F32).
+//
+// Reference: `quant::dequant_row` + `row_view` (src/quant/mod.rs:30-47, :97-135) and the
+// codecs `dequant_q8_0` (src/quant/q8_0.rs:14-51), `get_scale_min_k4` + `dequant_q4_k`
+// (src/quant/q4_k.rs:26-91), `quads` + `dequant_q6_k` (src/quant/q6_k.rs:25-77), called once
+// per token by the embedding loop (src/model/llama/cpu_path.rs:865-868).  The reference
+// has no GPU get_rows (it dequantises on the CPU and uploads the row per token).
+//
+// Bit-exact contract: the codecs are integer unpacking followed by one to three f32
+// operations; every one of them is spelled with __fmul_rn / __fsub_rn so nothing is
+// contracted into an FMA, and f16 -> f32 is the exact widening.
+//
+// Data movement: one CTA per token.  The quantised row (2-3.4 KB) is staged into shared
+// memory with 16-byte cp.async copies — Q8_0 (34 B) and Q6_K (210 B) blocks are only
+// 2-byte aligned, so they cannot be read with wide loads directly — then decoded from
+// shared memory four outputs per thread and written with coalesced 128-bit streaming
+// stores.  Traffic is dominated by the f32 output (4*row_len bytes vs <= 1.06*row_len in).
+#include <cuda_fp16.h>
+
+#include "agn_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+__device__ __forceinline__ uint16_t ld_u16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+__device__ __forceinline__ uint32_t ld_u32_2(const uint8_t *p) {  // 4 bytes from a 2-byte aligned address
+    return (uint32_t)ld_u16(p) | ((uint32_t)ld_u16(p + 2) << 16);
+}
+
+// Four consecutive outputs starting at element e0 (a multiple of 4) of a staged row.
+template <int DTYPE>
+__device__ __forceinline__ float4 decode4(const uint8_t *row, int e0);
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_Q8_0>(const uint8_t *row, int e0) {
+    const uint8_t *blk = row + (e0 >> 5) * 34;
+    const float d = f16_bits_to_f32(ld_u16(blk));
+    const uint32_t q = ld_u32_2(blk + 2 + (e0 & 31));
+    float4 o;
+    o.x = __fmul_rn(d, (float)(int8_t)(q & 0xff));
+    o.y = __fmul_rn(d, (float)(int8_t)((q >> 8) & 0xff));
+    o.z = __fmul_rn(d, (float)(int8_t)((q >> 16) & 0xff));
+    o.w = __fmul_rn(d, (float)(int8_t)(q >> 24));
+    return o;
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_Q4_K>(const uint8_t *row, int e0) {
+    const uint8_t *blk = row + (e0 >> 8) * 144;  // 144 = 9*16: blocks stay 16-byte aligned
+    const int r = e0 & 255;
+    const int g = r >> 6;          // 64-value group
+    const int hi = (r >> 5) & 1;   // second 32 of the group = high nibbles
+    const int l = r & 31;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
+    const uint8_t *sc = blk + 4;
+    const int j = 2 * g + hi;
+    uint32_t s, m;
+    if (j < 4) {
+        s = sc[j] & 63;
+        m = sc[j + 4] & 63;
+    } else {
+        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
+        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+    }
+    const float dd = __fmul_rn(d, (float)s);
+    const float mm = __fmul_rn(dmin, (float)m);
+    uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l);
+    q >>= 4 * hi;
+    float4 o;
+    o.x = __fsub_rn(__fmul_rn(dd, (float)(q & 0xF)), mm);
+    o.y = __fsub_rn(__fmul_rn(dd, (float)((q >> 8) & 0xF)), mm);
+    o.z = __fsub_rn(__fmul_rn(dd, (float)((q >> 16) & 0xF)), mm);
+    o.w = __fsub_rn(__fmul_rn(dd, (float)((q >> 24) & 0xF)), mm);
+    return o;
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_Q6_K>(const uint8_t *row, int e0) {
+    const uint8_t *blk = row + (e0 >> 8) * 210;
+    const int r = e0 & 255;
+    const int h = r >> 7;         // 128-value half
+    const int c = (r >> 5) & 3;   // which of the four 32-value quadrants of the half
+    const int l = r & 31;
+    const uint32_t ql = ld_u32_2(blk + h * 64 + (c & 1) * 32 + l) >> (4 * (c >> 1));
+    const uint32_t qh = ld_u32_2(blk + 128 + h * 32 + l) >> (2 * c);
+    const float sc = (float)(int8_t)blk[192 + 8 * h + (l >> 4) + 2 * c];
+    const float d = f16_bits_to_f32(ld_u16(blk + 208));
+    const float ds = __fmul_rn(d, sc);
+    float4 o;
+    o.x = __fmul_rn(ds, (float)((int)((ql & 0xF) | ((qh & 3) << 4)) - 32));
+    o.y = __fmul_rn(ds, (float)((int)(((ql >> 8) & 0xF) | (((qh >> 8) & 3) << 4)) - 32));
+    o.z = __fmul_rn(ds, (float)((int)(((ql >> 16) & 0xF) | (((qh >> 16) & 3) << 4)) - 32));
+    o.w = __fmul_rn(ds, (float)((int)(((ql >> 24) & 0xF) | (((qh >> 24) & 3) << 4)) - 32));
+    return o;
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_F16>(const uint8_t *row, int e0) {
+    const uint8_t *p = row + 2 * e0;
+    return make_float4(f16_bits_to_f32(ld_u16(p)), f16_bits_to_f32(ld_u16(p + 2)), f16_bits_to_f32(ld_u16(p + 4)),
+                       f16_bits_to_f32(ld_u16(p + 6)));
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_BF16>(const uint8_t *row, int e0) {
+    const uint8_t *p = row + 2 * e0;
+    return make_float4(__uint_as_float((uint32_t)ld_u16(p) << 16), __uint_as_float((uint32_t)ld_u16(p + 2) << 16),
+                       __uint_as_float((uint32_t)ld_u16(p + 4) << 16), __uint_as_float((uint32_t)ld_u16(p + 6) << 16));
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_F32>(const uint8_t *row, int e0) {
+    const uint8_t *p = row + 4 * e0;
+    return make_float4(__uint_as_float(ld_u32_2(p)), __uint_as_float(ld_u32_2(p + 4)), __uint_as_float(ld_u32_2(p + 8)),
+                       __uint_as_float(ld_u32_2(p + 12)));
+}
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <int DTYPE, bool VEC_OUT>
+__global__ void __launch_bounds__(256)
+get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
+                const uint32_t *__restrict__ ids, float *__restrict__ out, uint32_t *flags) {
+    extern __shared__ __align__(16) uint8_t stage[];
+    const int64_t t = blockIdx.x;
+    const uint32_t id = ids[t];
+    float *o_row = out + t * (int64_t)row_len;
+    const int n4 = (row_len + 3) >> 2;
+    if ((int64_t)id >= n_rows) {
+        // "row index out of range": zero row + error flag, never a trap
+        for (int j = threadIdx.x; j < row_len; j += blockDim.x) o_row[j] = 0.0f;
+        if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_OOB_ID);
+        return;
+    }
+    const size_t start = (size_t)id * (size_t)row_bytes;
+    const size_t a0 = start & ~(size_t)15;
+    const int lead = (int)(start - a0);
+    const int n16 = (lead + row_bytes + 15) >> 4;
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) {
+        const size_t off = a0 + 16 * (size_t)c;
+        if (off + 16 <= table_bytes) {
+            cp_async16(stage + 16 * c, table + off);
+        } else {
+            // last chunk of the table: copy only the bytes that exist
+            for (int b = 0; b < 16; b++) stage[16 * c + b] = off + b < table_bytes ? table[off + b] : 0;
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    const uint8_t *row = stage + lead;
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+        // a partial last block is fully present in the table (type_size rounds up to whole
+        // blocks), so decoding 4 values is always in bounds; only the store is clipped
+        const float4 v = decode4<DTYPE>(row, 4 * j);
+        if (VEC_OUT) {
+            agn_st_stream(reinterpret_cast<float4 *>(o_row) + j, v);
+        } else {
+            const int e = 4 * j;
+            if (e < row_len) o_row[e] = v.x;
+            if (e + 1 < row_len) o_row[e + 1] = v.y;
+            if (e + 2 < row_len) o_row[e + 2] = v.z;
+            if (e + 3 < row_len) o_row[e + 3] = v.w;
+        }
+    }
+}
+
+template <int DTYPE>
+void launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
+                     size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, float *out) {
+    if (vec)
+        get_rows_kernel<DTYPE, true><<<grid, threads, smem, ctx->stream>>>(table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+    else
+        get_rows_kernel<DTYPE, false><<<grid, threads, smem, ctx->stream>>>(table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+}
+
+}  // namespace
+
+extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows,
+                                    int64_t row_len, const uint32_t *ids, int64_t T, float *out) {
+    AGN_CHECK_CTX(ctx);
+    const size_t row_bytes = agn_type_size(dtype, (size_t)(row_len > 0 ? row_len : 0));
+    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_F16 && dtype != AGN_BF16 && dtype != AGN_F32)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "get_rows: dequantization not implemented for ggml type %d", dtype);
+    if (T < 0 || n_rows < 0 || row_len <= 0)
+        return agn_fail(ctx, AGN_EINVAL, "get_rows: T=%lld n_rows=%lld row_len=%lld", (long long)T, (long long)n_rows, (long long)row_len);
+    if (T == 0) return AGN_OK;
+    if (!table || !ids || !out) return agn_fail(ctx, AGN_EINVAL, "get_rows: null pointer");
+    if (!agn_aligned16(table)) return agn_fail(ctx, AGN_EINVAL, "get_rows: table must be 16-byte aligned");
+    if ((size_t)n_rows * row_bytes > table_bytes)
+        return agn_fail(ctx, AGN_EINVAL, "get_rows: tensor rows extend beyond the data (need %zu bytes, have %zu)",
+                        (size_t)n_rows * row_bytes, table_bytes);
+    if (row_bytes + 32 > 200 * 1024) return agn_fail(ctx, AGN_EINVAL, "get_rows: row of %zu bytes exceeds the staging buffer", row_bytes);
+    if (T > 0x7fffffffLL || row_len > 0x3fffffffLL) return agn_fail(ctx, AGN_EINVAL, "get_rows: T or row_len too large");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool vec = row_len % 4 == 0 && agn_aligned16(out);
+    const int n4 = (int)((row_len + 3) / 4);
+    int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
+    if (threads < 64) threads = 64;
+    if (threads > 256) threads = 256;
+    const size_t smem = ((row_bytes + 15) / 16 + 2) * 16;
+    const uint8_t *tb = static_cast<const uint8_t *>(table);
+    if (smem > 48 * 1024) {
+        // opt in to large dynamic shared memory for very long rows
+        cudaError_t e = cudaSuccess;
+#define AGN_GR_ATTR(DT)                                                                                               \
+    e = cudaFuncSetAttribute(get_rows_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    if (e == cudaSuccess)                                                                                              \
+        e = cudaFuncSetAttribute(get_rows_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        switch (dtype) {
+        case AGN_Q8_0: AGN_GR_ATTR(AGN_Q8_0) break;
+        case AGN_Q4_K: AGN_GR_ATTR(AGN_Q4_K) break;
+        case AGN_Q6_K: AGN_GR_ATTR(AGN_Q6_K) break;
+        case AGN_F16: AGN_GR_ATTR(AGN_F16) break;
+        case AGN_BF16: AGN_GR_ATTR(AGN_BF16) break;
+        default: AGN_GR_ATTR(AGN_F32) break;
+        }
+#undef AGN_GR_ATTR
+        AGN_CUDA(ctx, e);
+    }
+    const unsigned grid = (unsigned)T;
+    const int rl = (int)row_len, rb = (int)row_bytes;
+    switch (dtype) {
+    case AGN_Q8_0: launch_get_rows<AGN_Q8_0>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q4_K: launch_get_rows<AGN_Q4_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q6_K: launch_get_rows<AGN_Q6_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_F16: launch_get_rows<AGN_F16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_BF16: launch_get_rows<AGN_BF16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    default: launch_get_rows<AGN_F32>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    }
+    ctx->flags_dirty = true;
+    AGN_LAUNCHED(ctx, "get_rows");
+    return AGN_OK;
+}

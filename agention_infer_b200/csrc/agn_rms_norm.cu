@@ -1,0 +1,157 @@
+// RMSNorm and fused residual-add + RMSNorm over T token rows.
+//
+// Reference (src/model/llama/cpu_path.rs:67-74):
+//   sum_sq = sum_i x[i]^2 ; rms = sqrt(sum_sq / n + eps) ; out[i] = (w[i] * x[i]) / rms
+// and `launch_add_residual_rms_norm` (src/ops/wgpu_backend/resident.rs:240-266).
+//
+// 8 algorithmic bytes per element (16 for the residual form): bound by HBM.  One CTA owns
+// one row and keeps it in registers between the sum-of-squares pass and the scaling pass,
+// so x is read from HBM exactly once: thread i holds float4 number i + k*blockDim, k < VPT
+// (coalesced 128-bit loads, all VPT issued before the first use).  The statistic is reduced
+// by warp shuffles, then across warps through shared memory in a fixed order, which makes
+// the result independent of scheduling.
+#include "agn_common.cuh"
+
+namespace {
+
+// Sum over the CTA; every thread returns the same value.
+__device__ __forceinline__ float block_sum(float v, float *smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = agn_warp_sum(v);
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < nwarps; w++) total += smem[w];
+    __syncthreads();  // smem is reused by the next call
+    return total;
+}
+
+template <int VPT, bool RESIDUAL>
+__global__ void __launch_bounds__(1024)
+rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ delta,
+                     const float4 *__restrict__ w, float4 *__restrict__ new_x,
+                     float4 *__restrict__ out, int n4, float n_f, float eps) {
+    __shared__ float red[32];
+    const int64_t row = (int64_t)blockIdx.x * n4;
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) v[k] = agn_ld_stream(x + row + i);
+        else v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (RESIDUAL) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) {
+                const float4 d = agn_ld_stream(delta + row + i);
+                v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+                agn_st_stream(new_x + row + i, v[k]);
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) {
+            const float4 ww = __ldg(w + i);
+            float4 o;
+            o.x = ww.x * v[k].x / rms;
+            o.y = ww.y * v[k].y / rms;
+            o.z = ww.z * v[k].z / rms;
+            o.w = ww.w * v[k].w / rms;
+            agn_st_stream(out + row + i, o);
+        }
+    }
+}
+
+// Any H, any alignment, rows too long for registers: two passes over the row, the second
+// one served by L2 for rows that fit there.
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(1024)
+rms_norm_rows_generic_kernel(const float *__restrict__ x, const float *__restrict__ delta,
+                             const float *__restrict__ w, float *__restrict__ new_x,
+                             float *__restrict__ out, int64_t H, float eps) {
+    __shared__ float red[32];
+    const int64_t row = (int64_t)blockIdx.x * H;
+    float ss = 0.0f;
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[row + i];
+        if (RESIDUAL) {
+            v += delta[row + i];
+            new_x[row + i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rms = sqrtf(ss / (float)H + eps);
+    const float *src = RESIDUAL ? new_x : x;
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[row + i] = w[i] * src[row + i] / rms;
+}
+
+template <int VPT, bool RESIDUAL>
+void launch_vec(agn_ctx *ctx, const float *x, const float *delta, const float *w, float *new_x,
+                float *out, int64_t T, int n4, float eps, int threads) {
+    rms_norm_rows_kernel<VPT, RESIDUAL><<<(unsigned)T, threads, 0, ctx->stream>>>(
+        reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
+        reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
+        reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
+}
+
+template <bool RESIDUAL>
+int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, const float *w,
+                          float *new_x, float *out, int64_t T, int64_t H, float eps, const char *name) {
+    if (T < 0 || H <= 0) return agn_fail(ctx, AGN_EINVAL, "%s: T=%lld H=%lld", name, (long long)T, (long long)H);
+    if (T == 0) return AGN_OK;
+    if (!x || !w || !out || (RESIDUAL && (!delta || !new_x)))
+        return agn_fail(ctx, AGN_EINVAL, "%s: null pointer", name);
+    if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "%s: T too large", name);
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool vec_ok = (H % 4 == 0) && agn_aligned16(x) && agn_aligned16(w) && agn_aligned16(out) &&
+                        (!RESIDUAL || (agn_aligned16(delta) && agn_aligned16(new_x))) && H <= 32768;
+    if (vec_ok) {
+        const int n4 = (int)(H / 4);
+        // Pick the smallest VPT in {1,2,4,8} that keeps the CTA at <= 256 threads when
+        // possible: more rows resident per SM and more loads in flight per thread.
+        int vpt = 1;
+        while (vpt < 8 && (n4 + vpt - 1) / vpt > 256) vpt *= 2;
+        int threads = (n4 + vpt - 1) / vpt;
+        threads = ((threads + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        switch (vpt) {
+        case 1: launch_vec<1, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
+        case 2: launch_vec<2, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
+        case 4: launch_vec<4, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
+        default: launch_vec<8, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
+        }
+        AGN_LAUNCHED(ctx, name);
+    } else {
+        int threads = H >= 1024 ? 256 : (int)(((H + 31) / 32) * 32);
+        if (threads > 256) threads = 256;
+        rms_norm_rows_generic_kernel<RESIDUAL><<<(unsigned)T, threads, 0, ctx->stream>>>(x, delta, w, new_x, out, H, eps);
+        AGN_LAUNCHED(ctx, name);
+    }
+    return AGN_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t agn_rms_norm_f32(agn_ctx *ctx, const float *x, const float *w, float *out,
+                                    int64_t T, int64_t H, float eps) {
+    AGN_CHECK_CTX(ctx);
+    return rms_norm_dispatch<false>(ctx, x, nullptr, w, nullptr, out, T, H, eps, "rms_norm");
+}
+
+extern "C" int32_t agn_add_residual_rms_norm_f32(agn_ctx *ctx, const float *x, const float *delta,
+                                                 const float *w, float *new_x, float *normed,
+                                                 int64_t T, int64_t H, float eps) {
+    AGN_CHECK_CTX(ctx);
+    return rms_norm_dispatch<true>(ctx, x, delta, w, new_x, normed, T, H, eps, "add_residual_rms_norm");
+}

@@ -1,0 +1,215 @@
+// Row softmax with a per-row valid length (causal attention scores, router logits).
+//
+// Reference: the softmax step of `attention_into` (src/model/llama/cpu_path.rs:175-183):
+//   max = fold(-inf, f32::max) over s[0..n) ; s = exp(s - max) ; sum = sum(s) ; s = s / sum
+// with n = pos + 1: causality is a row LENGTH, entries past n are never touched.  Here
+// those entries of the output are written as 0 so the full [n_rows, row_len] matrix is
+// defined.  GPU twin: `attention_softmax` (src/ops/kernels_wgpu.rs:795-864).
+//
+// Bound by HBM: reads only the valid prefix of each row, writes the full row, the row
+// stays in registers between the three passes (max, exp+sum, divide).
+//   - rows up to 1024 entries: one warp per row, statistics by warp shuffles only;
+//   - rows up to 32768 entries: one CTA per row, shuffles + a shared-memory combine;
+//   - anything else (odd lengths, unaligned, longer): three passes over global memory.
+#include <math.h>
+
+#include "agn_common.cuh"
+
+namespace {
+
+struct SoftmaxArgs {
+    const float *in;
+    float *out;
+    const int32_t *n_valid;
+    int64_t n_rows, row_len, row_stride;
+    int causal_period, causal_offset;
+};
+
+__device__ __forceinline__ int64_t valid_len(const SoftmaxArgs &a, int64_t r) {
+    int64_t nv;
+    if (a.n_valid) nv = a.n_valid[r];
+    else if (a.causal_period > 0) nv = (int64_t)a.causal_offset + (r % a.causal_period) + 1;
+    else nv = a.row_len;
+    if (nv > a.row_len) nv = a.row_len;
+    if (nv < 0) nv = 0;
+    return nv;
+}
+
+__device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
+
+// Load float4 number i of a row whose first nv entries are valid; the rest reads as -inf.
+__device__ __forceinline__ float4 load_masked(const float4 *row, int i, int nv) {
+    float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    const int e = 4 * i;
+    if (e < nv) {
+        v = agn_ld_stream(row + i);
+        if (e + 1 >= nv) v.y = -INFINITY;
+        if (e + 2 >= nv) v.z = -INFINITY;
+        if (e + 3 >= nv) v.w = -INFINITY;
+    }
+    return v;
+}
+
+__device__ __forceinline__ float4 exp4(float4 v, float m, int e, int nv) {
+    float4 o;
+    o.x = e < nv ? expf(v.x - m) : 0.0f;
+    o.y = e + 1 < nv ? expf(v.y - m) : 0.0f;
+    o.z = e + 2 < nv ? expf(v.z - m) : 0.0f;
+    o.w = e + 3 < nv ? expf(v.w - m) : 0.0f;
+    return o;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256)
+softmax_warp_rows_kernel(const SoftmaxArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= a.n_rows) return;  // whole warp leaves together
+    const int nv = (int)valid_len(a, r);
+    const int n4 = (int)(a.row_len >> 2);
+    const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
+    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    float4 v[VPL];
+#pragma unroll
+    for (int k = 0; k < VPL; k++) v[k] = load_masked(in, lane + 32 * k, nv);
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPL; k++) m = fmaxf(m, max4(v[k]));
+    m = agn_warp_max(m);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPL; k++) {
+        v[k] = exp4(v[k], m, 4 * (lane + 32 * k), nv);
+        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    sum = agn_warp_sum(sum);
+#pragma unroll
+    for (int k = 0; k < VPL; k++) {
+        const int i = lane + 32 * k;
+        if (i < n4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (4 * i < nv) {
+                o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum;
+            }
+            agn_st_stream(out + i, o);
+        }
+    }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(1024)
+softmax_block_rows_kernel(const SoftmaxArgs a) {
+    __shared__ float red[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int64_t r = blockIdx.x;
+    const int nv = (int)valid_len(a, r);
+    const int n4 = (int)(a.row_len >> 2);
+    const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
+    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) v[k] = load_masked(in, threadIdx.x + k * blockDim.x, nv);
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    m = agn_warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        v[k] = exp4(v[k], m, 4 * (threadIdx.x + k * blockDim.x), nv);
+        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    sum = agn_warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = 0.0f;
+    for (int w = 0; w < nwarps; w++) sum += red[w];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < n4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (4 * i < nv) {
+                o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum;
+            }
+            agn_st_stream(out + i, o);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+softmax_generic_rows_kernel(const SoftmaxArgs a) {
+    __shared__ float red[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int64_t r = blockIdx.x;
+    const int64_t nv = valid_len(a, r);
+    const float *in = a.in + r * a.row_stride;
+    float *out = a.out + r * a.row_stride;
+    float m = -INFINITY;
+    for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) m = fmaxf(m, in[i]);
+    m = agn_warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
+        const float e = expf(in[i] - m);
+        out[i] = e;  // in may alias out: element i is only ever touched by this thread
+        sum += e;
+    }
+    sum = agn_warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    sum = 0.0f;
+    for (int w = 0; w < nwarps; w++) sum += red[w];
+    for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) out[i] = i < nv ? out[i] / sum : 0.0f;
+}
+
+}  // namespace
+
+extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, int64_t n_rows, int64_t row_len,
+                                        int64_t row_stride, const int32_t *n_valid, int32_t causal_period,
+                                        int32_t causal_offset) {
+    AGN_CHECK_CTX(ctx);
+    if (n_rows < 0 || row_len < 0 || row_stride < row_len || causal_period < 0 || causal_offset < 0)
+        return agn_fail(ctx, AGN_EINVAL, "softmax_rows: n_rows=%lld row_len=%lld row_stride=%lld period=%d offset=%d",
+                        (long long)n_rows, (long long)row_len, (long long)row_stride, causal_period, causal_offset);
+    if (n_rows == 0 || row_len == 0) return AGN_OK;
+    if (!in || !out) return agn_fail(ctx, AGN_EINVAL, "softmax_rows: null pointer");
+    if (n_rows > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "softmax_rows: n_rows too large");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    SoftmaxArgs a;
+    a.in = in; a.out = out; a.n_valid = n_valid; a.n_rows = n_rows; a.row_len = row_len; a.row_stride = row_stride;
+    a.causal_period = causal_period; a.causal_offset = causal_offset;
+    const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned16(out);
+    const int64_t n4 = row_len / 4;
+    if (vec_ok && n4 <= 256) {
+        const int warps = 8;
+        const unsigned grid = (unsigned)((n_rows + warps - 1) / warps);
+        if (n4 <= 32) softmax_warp_rows_kernel<1><<<grid, 32 * warps, 0, ctx->stream>>>(a);
+        else if (n4 <= 64) softmax_warp_rows_kernel<2><<<grid, 32 * warps, 0, ctx->stream>>>(a);
+        else if (n4 <= 128) softmax_warp_rows_kernel<4><<<grid, 32 * warps, 0, ctx->stream>>>(a);
+        else softmax_warp_rows_kernel<8><<<grid, 32 * warps, 0, ctx->stream>>>(a);
+        AGN_LAUNCHED(ctx, "softmax_warp_rows");
+    } else if (vec_ok && n4 <= 8192) {
+        int vpt = 2;
+        while (vpt < 8 && (n4 + vpt - 1) / vpt > 512) vpt *= 2;
+        int threads = (int)((n4 + vpt - 1) / vpt);
+        threads = ((threads + 31) / 32) * 32;
+        if (vpt == 2) softmax_block_rows_kernel<2><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
+        else if (vpt == 4) softmax_block_rows_kernel<4><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
+        else softmax_block_rows_kernel<8><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
+        AGN_LAUNCHED(ctx, "softmax_block_rows");
+    } else {
+        softmax_generic_rows_kernel<<<(unsigned)n_rows, 256, 0, ctx->stream>>>(a);
+        AGN_LAUNCHED(ctx, "softmax_generic_rows");
+    }
+    return AGN_OK;
+}

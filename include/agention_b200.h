@@ -1,0 +1,193 @@
+/*
+ * agention_b200 — C ABI of the CUDA (sm_100a) layer-op backend for the gguf-rs
+ * engine (LaurentZuijdwijk/agention-infer).
+ *
+ * This is the boundary a Rust `CudaBackend` binds with `extern "C"`: plain
+ * pointers and sizes, int32 status codes, no exceptions, no C++ or torch types.
+ * Every op works on T token rows at once (row-major, token-major f32, the
+ * layout `run_batch` uses, src/model/llama/cpu_path.rs:854-862); T = 1 with a
+ * scalar position reproduces the reference's per-token call.
+ *
+ * All device pointers are plain CUDA device addresses owned by the caller.
+ * Ops are asynchronous on the context's stream and never allocate; only
+ * agn_sync / agn_memcpy_d2h(+sync) block.  Calls on one context must be
+ * serialised by the caller (the reference's `forward` is not re-entrant either,
+ * src/model/llama/mod.rs:340-343); contexts on different GPUs are independent.
+ *
+ * There is no CPU fallback anywhere behind this ABI: a call either runs the
+ * CUDA kernel or returns an error status.
+ */
+#ifndef AGENTION_B200_H
+#define AGENTION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define AGN_API
+#else
+#define AGN_API __attribute__((visibility("default")))
+#endif
+
+/* ------------------------------------------------------------------ status */
+
+/* Replaces `Result<T, GgufError>` / `GgufError::BackendError(String)`
+ * (src/error.rs:3-42); the message is read with agn_last_error. */
+typedef enum agn_status {
+    AGN_OK = 0,
+    AGN_EINVAL = 1,            /* bad argument (null, size, alignment, n_rot > head_dim ...) */
+    AGN_EUNSUPPORTED_DTYPE = 2,/* quant type without a kernel ("dequantization not yet
+                                  implemented for ..", src/quant/mod.rs:43-45) */
+    AGN_ECUDA = 3,             /* a CUDA runtime call failed */
+    AGN_EOOB_ID = 4,           /* get_rows met a row index >= n_rows ("row index .. out of
+                                  range", src/quant/mod.rs:116-120); that output row is zero */
+    AGN_ENOMEM = 5,            /* device or pinned allocation failed */
+    AGN_ETIMEOUT = 6           /* a bounded device-side wait gave up (staging barrier) */
+} agn_status;
+
+/* GgmlType discriminants accepted by agn_get_rows_f32 (src/types.rs:9-46). */
+typedef enum agn_dtype {
+    AGN_F32 = 0,
+    AGN_F16 = 1,
+    AGN_Q8_0 = 8,
+    AGN_Q4_K = 12,
+    AGN_Q6_K = 14,
+    AGN_BF16 = 30
+} agn_dtype;
+
+/* Pairing of rotated dims: NeoX (d, d + n_rot/2) is what the reference does
+ * (src/model/llama/cpu_path.rs:114-132); NORMAL pairs (2d, 2d+1). */
+typedef enum agn_rope_layout { AGN_ROPE_NEOX = 0, AGN_ROPE_NORMAL = 1 } agn_rope_layout;
+
+typedef struct agn_ctx agn_ctx;     /* one device + one stream; replaces WgpuBackend's
+                                       ComputeClient (src/ops/wgpu_backend/mod.rs) */
+typedef struct agn_event agn_event; /* device timestamp on the context's stream */
+
+/* ----------------------------------------------------------- context, memory */
+
+/* Replaces `create_backend(BackendPreference::Cuda)` whose Cuda arm falls back to
+ * CPU today (src/ops/backend_select.rs:84-95).  Fails with AGN_ECUDA when the
+ * device is absent; never falls back. */
+AGN_API int32_t agn_ctx_create(int32_t device, agn_ctx **out);
+AGN_API int32_t agn_ctx_destroy(agn_ctx *ctx);
+/* `Backend::name` (src/ops/mod.rs:99): "cuda-sm100a". */
+AGN_API const char *agn_backend_name(void);
+AGN_API const char *agn_last_error(agn_ctx *ctx);
+AGN_API const char *agn_status_string(int32_t status);
+/* Use an existing cudaStream_t (e.g. the host framework's) instead of the
+ * context's own; pass NULL to return to the own stream. */
+AGN_API int32_t agn_ctx_set_stream(agn_ctx *ctx, void *cuda_stream);
+AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
+/* Number of kernels this context has launched so far. */
+AGN_API uint64_t agn_ctx_launch_count(agn_ctx *ctx);
+
+/* `client.empty(bytes)` / `client.create_from_slice` / `read_one_unchecked`
+ * (src/ops/wgpu_backend/resident.rs:195,673-700). Copies are stream-ordered;
+ * host memory from agn_host_alloc is pinned so they are truly asynchronous. */
+AGN_API int32_t agn_malloc(agn_ctx *ctx, size_t bytes, void **dptr);
+AGN_API int32_t agn_free(agn_ctx *ctx, void *dptr);
+AGN_API int32_t agn_host_alloc(agn_ctx *ctx, size_t bytes, void **hptr);
+AGN_API int32_t agn_host_free(agn_ctx *ctx, void *hptr);
+AGN_API int32_t agn_memcpy_h2d(agn_ctx *ctx, void *dst, const void *src, size_t bytes);
+AGN_API int32_t agn_memcpy_d2h(agn_ctx *ctx, void *dst, const void *src, size_t bytes);
+AGN_API int32_t agn_memset(agn_ctx *ctx, void *dst, int value, size_t bytes);
+/* Blocks until the stream is idle; also reports (once) AGN_EOOB_ID / AGN_ETIMEOUT
+ * raised by kernels since the last sync.  Replaces the sync implied by
+ * `read_handle` (src/ops/wgpu_backend/resident.rs:696-699). */
+AGN_API int32_t agn_sync(agn_ctx *ctx);
+
+/* GPU-time tracing; replaces the host-side `trace::Timer` around each launch_*
+ * (src/ops/trace.rs:148-219), which times only the enqueue. */
+AGN_API int32_t agn_event_create(agn_ctx *ctx, agn_event **ev);
+AGN_API int32_t agn_event_record(agn_ctx *ctx, agn_event *ev);
+AGN_API int32_t agn_event_elapsed_ms(agn_ctx *ctx, agn_event *start, agn_event *stop, float *ms);
+AGN_API int32_t agn_event_destroy(agn_ctx *ctx, agn_event *ev);
+
+/* ---------------------------------------------------------------- layer ops */
+
+/* `LlamaModel::rms_norm_into` (src/model/llama/cpu_path.rs:67-74) over T rows;
+ * GPU twin `WgpuBackend::launch_rms_norm` (src/ops/wgpu_backend/resident.rs:213-235).
+ * out[t,i] = (w[i] * x[t,i]) / sqrt(sum_i x[t,i]^2 / H + eps).  out may alias x. */
+AGN_API int32_t agn_rms_norm_f32(agn_ctx *ctx, const float *x, const float *w, float *out,
+                                 int64_t T, int64_t H, float eps);
+
+/* `launch_add_residual_rms_norm` (src/ops/wgpu_backend/resident.rs:240-266); CPU
+ * equivalent = residual loop cpu_path.rs:785-787 followed by rms_norm_into :790.
+ * new_x = x + delta; normed = rms_norm(new_x, w).  new_x may alias x. */
+AGN_API int32_t agn_add_residual_rms_norm_f32(agn_ctx *ctx, const float *x, const float *delta,
+                                              const float *w, float *new_x, float *normed,
+                                              int64_t T, int64_t H, float eps);
+
+/* `LlamaModel::rope` / `rope_partial` (src/model/llama/cpu_path.rs:99-133,461-496),
+ * GPU twin `launch_rope` (src/ops/wgpu_backend/resident.rs:326-353), in place on
+ * x [T, n_heads*head_dim].  Token t rotates with position pos[t] (device int32
+ * array) or, when pos is NULL, pos_start + t (cpu_path.rs:897).
+ * angle(d) = (pos * freq_scale) / powf(theta, 2d/n_rot); the powf table is built
+ * once per (theta, n_rot) on the host with libm and cached in the context, so the
+ * angle is bit-identical to the CPU path's. */
+AGN_API int32_t agn_rope_f32(agn_ctx *ctx, float *x, int64_t T, int32_t n_heads,
+                             int32_t head_dim, int32_t n_rot, const int32_t *pos,
+                             int32_t pos_start, float theta, float freq_scale,
+                             int32_t layout);
+/* Same, Q and K in one launch as the CPU `rope(q, k, pos)` does. */
+AGN_API int32_t agn_rope_qk_f32(agn_ctx *ctx, float *q, float *k, int64_t T, int32_t n_q_heads,
+                                int32_t n_kv_heads, int32_t head_dim, int32_t n_rot,
+                                const int32_t *pos, int32_t pos_start, float theta,
+                                float freq_scale, int32_t layout);
+
+/* Fused norm->rope: `launch_qk_norm_rope` (src/ops/wgpu_backend/resident.rs:414-443);
+ * CPU = `qk_norm` (cpu_path.rs:78-93) then `rope` (:99-133) per token (:896-906).
+ * w is [head_dim], shared by all heads.  In place. */
+AGN_API int32_t agn_qk_norm_rope_f32(agn_ctx *ctx, float *x, const float *w, int64_t T,
+                                     int32_t n_heads, int32_t head_dim, float eps,
+                                     int32_t n_rot, const int32_t *pos, int32_t pos_start,
+                                     float theta, float freq_scale, int32_t layout);
+/* Q (weights wq) and K (weights wk) in one launch. */
+AGN_API int32_t agn_qk_norm_rope_qk_f32(agn_ctx *ctx, float *q, float *k, const float *wq,
+                                        const float *wk, int64_t T, int32_t n_q_heads,
+                                        int32_t n_kv_heads, int32_t head_dim, float eps,
+                                        int32_t n_rot, const int32_t *pos, int32_t pos_start,
+                                        float theta, float freq_scale, int32_t layout);
+
+/* Fused gate·up -> SiLU·mul: `launch_silu_mul` (src/ops/wgpu_backend/resident.rs:187-209);
+ * CPU cpu_path.rs:228-229 and :975-978.  out[i] = gate[i] / (1 + exp(-gate[i])) * up[i].
+ * out may alias gate (the CPU batch path writes into gate). */
+AGN_API int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float *up, float *out,
+                                 int64_t n);
+
+/* Row softmax: the softmax step of `attention_into` (src/model/llama/cpu_path.rs:175-183),
+ * GPU twin `attention_softmax` (src/ops/kernels_wgpu.rs:795-864).  Row r of
+ * in/out [n_rows, row_stride] is normalised over its first nv(r) entries and the
+ * entries nv(r)..row_len-1 of out are set to 0:
+ *   n_valid != NULL        : nv(r) = n_valid[r]            (device int32 array)
+ *   else causal_period > 0 : nv(r) = causal_offset + (r % causal_period) + 1
+ *   else                   : nv(r) = row_len
+ * (causality is a row length in the reference, never a -inf mask).  out may alias in. */
+AGN_API int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, int64_t n_rows,
+                                     int64_t row_len, int64_t row_stride,
+                                     const int32_t *n_valid, int32_t causal_period,
+                                     int32_t causal_offset);
+
+/* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
+ * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
+ * -> dequant_q8_0 / dequant_q4_k / dequant_q6_k (src/quant/q8_0.rs:14-51,
+ * q4_k.rs:37-91, q6_k.rs:34-77), looped over tokens as cpu_path.rs:865-868 does.
+ * table: n_rows rows of type_size(dtype, row_len) bytes each, 16-byte aligned;
+ * table_bytes = readable bytes at table; ids: device u32 [T]; out: [T, row_len] f32.
+ * Bit-exact with the CPU codecs.  An id >= n_rows zero-fills its row and makes the
+ * next agn_sync return AGN_EOOB_ID. */
+AGN_API int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table,
+                                 size_t table_bytes, int64_t n_rows, int64_t row_len,
+                                 const uint32_t *ids, int64_t T, float *out);
+
+/* `GgmlType::type_size` (src/types.rs:164-168); 0 for a dtype without a kernel. */
+AGN_API size_t agn_type_size(int32_t dtype, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AGENTION_B200_H */

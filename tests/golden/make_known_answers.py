@@ -1,0 +1,82 @@
+"""Writes tests/golden/reference_known_answers.json: the input/expected pairs of the
+reference's own unit tests for the quant codecs and the RoPE scale helper, transcribed from
+the cited test bodies (the reference is Rust and cannot be run here, so its tests are read
+as data).  Run: python tests/golden/make_known_answers.py
+"""
+import json
+from pathlib import Path
+
+import numpy as np
+
+
+def f16_bytes(v: float) -> list:
+    return list(np.array([v], dtype=np.float16).view(np.uint8))
+
+
+def q8_block(scale: float, vals) -> list:
+    return [int(b) for b in f16_bytes(scale)] + [int(np.uint8(np.int8(v))) for v in vals]
+
+
+cases = {}
+
+# src/quant/q8_0.rs:110-126  test_dequant_q8_0_single_block
+vals = [(i % 5) - 2 for i in range(32)]
+cases["q8_0_single_block"] = {
+    "cite": "src/quant/q8_0.rs:110-126", "data": q8_block(2.0, vals), "n": 32,
+    "expected": [2.0 * v for v in vals], "tol": 1e-6}
+
+# src/quant/q8_0.rs:129-148  test_dequant_q8_0_partial_block
+data = q8_block(1.0, list(range(32))) + q8_block(1.0, [42] + [0] * 31)
+cases["q8_0_partial_block"] = {
+    "cite": "src/quant/q8_0.rs:129-148", "data": data, "n": 33, "expected_len": 33,
+    "expected_at": {"32": 42.0}}
+
+# src/quant/q8_0.rs:151-170  test_dot_q8_0_matches_dequant (inputs only; the assertion is dot == dequant.x)
+data = []
+for b in range(3):
+    data += q8_block(0.75, [((i + b) % 7) - 3 for i in range(32)])
+cases["q8_0_three_blocks"] = {"cite": "src/quant/q8_0.rs:151-170", "data": data, "n": 70}
+
+# src/quant/q4_k.rs:229-241  test_get_scale_min_k4
+cases["q4_k_scale_min"] = {
+    "cite": "src/quant/q4_k.rs:229-241",
+    "cases": [
+        {"scales": [10, 20, 30, 40, 50, 60, 70, 80, 0, 0, 0, 0],
+         "expect": {"0": [10, 50], "1": [20, 60], "2": [30, 6], "3": [40, 16]}},
+        {"scales": [0xC0, 0x80, 0x40, 0x00, 0x00, 0x00, 0x00, 0x00, 0x3F, 0x2F, 0x1F, 0x0F],
+         "expect": {"4": [0x3F, 3], "5": [0x2F, 2]}},
+    ]}
+
+# src/quant/q4_k.rs:244-259  test_dot_q4_k_matches_dequant (block inputs)
+scales = [10, 20, 30, 40, 50, 60, 70, 80, 0x3F, 0x2F, 0x1F, 0x0F]
+quants = [(i * 13) & 0xFF for i in range(128)]
+cases["q4_k_block"] = {
+    "cite": "src/quant/q4_k.rs:244-259",
+    "data": [int(b) for b in f16_bytes(0.05)] + [int(b) for b in f16_bytes(-0.01)] + scales + quants, "n": 256}
+
+# src/quant/q6_k.rs:148-164  test_dot_q6_k_matches_dequant (block inputs)
+ql = [(i * 37) & 0xFF for i in range(128)]
+qh = [((i * 53) + 1) & 0xFF for i in range(64)]
+sc = [int(np.uint8(np.int8(i - 6))) for i in range(16)]
+cases["q6_k_block"] = {
+    "cite": "src/quant/q6_k.rs:148-164", "data": ql + qh + sc + [int(b) for b in f16_bytes(0.02)], "n": 256}
+
+# src/quant/mod.rs:176-205  f32 / f16 / bf16 rows
+cases["f32_row"] = {"cite": "src/quant/mod.rs:176-185",
+                    "data": [int(b) for b in np.array([1.0, 2.0, -3.5], dtype="<f4").view(np.uint8)], "n": 3,
+                    "expected": [1.0, 2.0, -3.5], "tol": 0.0}
+cases["f16_row"] = {"cite": "src/quant/mod.rs:187-196",
+                    "data": [int(b) for b in np.array([1.5, -2.25], dtype="<f2").view(np.uint8)], "n": 2,
+                    "expected": [1.5, -2.25], "tol": 1e-3}
+cases["bf16_row"] = {"cite": "src/quant/mod.rs:198-205", "data": [0x80, 0x3F, 0x00, 0xC0], "n": 2,
+                     "expected": [1.0, -2.0], "tol": 1e-3}
+
+# src/model/llama/cpu_path.rs:1034-1060  compute_rope_freq_scale
+cases["rope_freq_scale"] = {
+    "cite": "src/model/llama/cpu_path.rs:1034-1060",
+    "cases": [[None, None, 1.0], ["none", 8.0, 1.0], ["", 8.0, 1.0], ["linear", 4.0, 0.25], ["linear", 2.0, 0.5],
+              ["linear", None, 1.0], ["yarn", 4.0, None]]}
+
+out = Path(__file__).with_name("reference_known_answers.json")
+out.write_text(json.dumps(cases, indent=1) + "\n")
+print("wrote", out)

@@ -1,0 +1,107 @@
+"""Independent numpy statements of the quant codecs and float ops, used to cross-check the
+C oracle (a second restatement written from the block-layout descriptions in
+src/quant/q8_0.rs:1-7, q4_k.rs:1-16, q6_k.rs:1-15 and from the GPU kernels' second statement
+of the same layouts, src/ops/kernels_wgpu.rs:1380-1410, :1655-1701)."""
+import numpy as np
+
+
+def f16(bits_u8_pairs: np.ndarray) -> np.ndarray:
+    """[..., 2] uint8 little-endian -> f32 (exact widening)."""
+    return np.ascontiguousarray(bits_u8_pairs).view(np.float16)[..., 0].astype(np.float32)
+
+
+def dequant_q8_0(data: np.ndarray, n: int) -> np.ndarray:
+    nb = (n + 31) // 32
+    blk = np.ascontiguousarray(data[: nb * 34]).reshape(nb, 34)
+    d = f16(blk[:, 0:2])
+    q = blk[:, 2:].view(np.int8).astype(np.float32)
+    return (d[:, None] * q).reshape(-1)[:n]
+
+
+def scale_min_k4(scales: np.ndarray):
+    """[nb, 12] uint8 -> (sc [nb, 8], m [nb, 8]) uint8."""
+    s = scales.astype(np.uint8)
+    sc = np.empty(s.shape[:-1] + (8,), dtype=np.uint8)
+    m = np.empty_like(sc)
+    sc[..., :4] = s[..., 0:4] & 63
+    m[..., :4] = s[..., 4:8] & 63
+    sc[..., 4:] = (s[..., 8:12] & 0xF) | ((s[..., 0:4] >> 6) << 4)
+    m[..., 4:] = (s[..., 8:12] >> 4) | ((s[..., 4:8] >> 6) << 4)
+    return sc, m
+
+
+def dequant_q4_k(data: np.ndarray, n: int) -> np.ndarray:
+    nb = (n + 255) // 256
+    blk = np.ascontiguousarray(data[: nb * 144]).reshape(nb, 144)
+    d, dmin = f16(blk[:, 0:2]), f16(blk[:, 2:4])
+    sc, m = scale_min_k4(blk[:, 4:16])
+    qs = blk[:, 16:].reshape(nb, 4, 32)
+    lo = (qs & 0xF).astype(np.float32)
+    hi = (qs >> 4).astype(np.float32)
+    q = np.stack([lo, hi], axis=2).reshape(nb, 8, 32)  # group g: low run then high run
+    dd = (d[:, None] * sc.astype(np.float32)).astype(np.float32)
+    mm = (dmin[:, None] * m.astype(np.float32)).astype(np.float32)
+    out = (dd[:, :, None] * q).astype(np.float32) - mm[:, :, None]
+    return out.astype(np.float32).reshape(-1)[:n]
+
+
+def dequant_q6_k(data: np.ndarray, n: int) -> np.ndarray:
+    nb = (n + 255) // 256
+    blk = np.ascontiguousarray(data[: nb * 210]).reshape(nb, 210)
+    ql = blk[:, 0:128].reshape(nb, 2, 2, 32)      # [half][first/second 32][l]
+    qh = blk[:, 128:192].reshape(nb, 2, 32)
+    sc = blk[:, 192:208].view(np.int8).astype(np.float32).reshape(nb, 2, 8)
+    d = f16(blk[:, 208:210])
+    q = np.empty((nb, 2, 4, 32), dtype=np.int32)
+    q[:, :, 0] = (ql[:, :, 0] & 0xF) | (((qh >> 0) & 3) << 4)
+    q[:, :, 1] = (ql[:, :, 1] & 0xF) | (((qh >> 2) & 3) << 4)
+    q[:, :, 2] = (ql[:, :, 0] >> 4) | (((qh >> 4) & 3) << 4)
+    q[:, :, 3] = (ql[:, :, 1] >> 4) | (((qh >> 6) & 3) << 4)
+    q -= 32
+    l = np.arange(32)
+    c = np.arange(4)
+    sidx = (l[None, :] // 16) + 2 * c[:, None]           # [4, 32] scale index inside the half
+    s = sc[:, :, sidx]                                    # [nb, 2, 4, 32]
+    ds = (d[:, None, None, None] * s).astype(np.float32)
+    return (ds * q.astype(np.float32)).astype(np.float32).reshape(-1)[:n]
+
+
+def rms_norm64(x, w, eps):
+    x64 = x.astype(np.float64)
+    rms = np.sqrt((x64 * x64).mean(axis=-1, keepdims=True) + eps)
+    return w.astype(np.float64) * x64 / rms
+
+
+def rope64(x, n_heads, head_dim, n_rot, pos, theta, freq_scale=1.0, layout=0):
+    T = x.shape[0]
+    xr = x.astype(np.float64).reshape(T, n_heads, head_dim).copy()
+    half = n_rot // 2
+    d = np.arange(half, dtype=np.float64)
+    ang = (pos.astype(np.float64)[:, None] * freq_scale) / np.power(float(theta), 2.0 * d / n_rot)
+    c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+    if layout == 0:
+        x0, x1 = xr[:, :, :half].copy(), xr[:, :, half:n_rot].copy()
+        xr[:, :, :half] = x0 * c - x1 * s
+        xr[:, :, half:n_rot] = x0 * s + x1 * c
+    else:
+        x0, x1 = xr[:, :, 0:n_rot:2].copy(), xr[:, :, 1:n_rot:2].copy()
+        xr[:, :, 0:n_rot:2] = x0 * c - x1 * s
+        xr[:, :, 1:n_rot:2] = x0 * s + x1 * c
+    return xr.reshape(T, n_heads * head_dim)
+
+
+def softmax64(s, n_valid=None):
+    s64 = s.astype(np.float64)
+    rows = s64.reshape(-1, s64.shape[-1])
+    out = np.zeros_like(rows)
+    for r in range(rows.shape[0]):
+        nv = rows.shape[1] if n_valid is None else int(n_valid[r])
+        if nv > 0:
+            e = np.exp(rows[r, :nv] - rows[r, :nv].max())
+            out[r, :nv] = e / e.sum()
+    return out.reshape(s.shape)
+
+
+def silu_mul64(g, u):
+    g64 = g.astype(np.float64)
+    return g64 / (1.0 + np.exp(-g64)) * u.astype(np.float64)
