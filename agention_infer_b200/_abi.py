@@ -49,6 +49,8 @@ SIGNATURES = {
     "agn_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_softmax_rows_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32]),
     "agn_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
+    "agn_router_top2_f32": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
     "agn_type_size": (_sz, [_i32, _sz]),
 }
 

@@ -241,6 +241,30 @@ class CudaBackend:
                                                T, _ptr(out)))
         return out
 
+    def router_top2(self, logits, T: int, n_experts: int, idx=None, w=None):
+        """MoE router: softmax + top-2 per token (docs/08-moe-routing.md:27-33). Returns (idx [T,2] i32, w [T,2] f32)."""
+        if idx is None:
+            idx = self.empty(8 * max(T, 1))
+        if w is None:
+            w = self.empty(8 * max(T, 1))
+        self._check(self._lib.agn_router_top2_f32(self._ctx, _ptr(logits), T, n_experts, _ptr(idx), _ptr(w)))
+        return idx, w
+
+    def gather_rows_by_expert(self, x, idx, T: int, H: int, n_experts: int, out=None, offsets=None, src_token=None,
+                              src_slot=None):
+        """Expert-sorted copy of the hidden rows: returns (out [2T,H], offsets [E+1], src_token [2T], src_slot [2T])."""
+        if out is None:
+            out = self.empty(8 * max(T, 1) * H)
+        if offsets is None:
+            offsets = self.empty(4 * (n_experts + 1))
+        if src_token is None:
+            src_token = self.empty(8 * max(T, 1))
+        if src_slot is None:
+            src_slot = self.empty(8 * max(T, 1))
+        self._check(self._lib.agn_gather_rows_by_expert_f32(self._ctx, _ptr(x), _ptr(idx), T, H, n_experts, _ptr(out),
+                                                            _ptr(offsets), _ptr(src_token), _ptr(src_slot)))
+        return out, offsets, src_token, src_slot
+
     def dequant_row(self, dtype: int, table, table_bytes: int, n_rows: int, row_len: int, row: int) -> np.ndarray:
         """`WeightMap::dequant_row(name, row) -> Vec<f32>` (src/model/mod.rs:343-348) on the GPU.
         An out-of-range row raises, as the reference returns Err (src/quant/mod.rs:116-120)."""

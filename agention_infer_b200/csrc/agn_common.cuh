@@ -16,6 +16,7 @@
 
 #define AGN_ROPE_CACHE_SLOTS 16
 #define AGN_ROPE_MAX_HALF 512  // n_rot <= 1024
+#define AGN_SCRATCH_BYTES (1u << 20)
 
 struct agn_rope_slot {
     uint32_t theta_bits;
@@ -32,6 +33,8 @@ struct agn_ctx {
     uint32_t *h_flags;          // pinned mirror
     float *d_rope_denom;        // [AGN_ROPE_CACHE_SLOTS][AGN_ROPE_MAX_HALF]
     float *h_rope_denom;        // pinned staging, same shape
+    void *d_scratch;            // workspace for ops that need one (gather_rows_by_expert)
+    size_t scratch_bytes;
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync

@@ -51,6 +51,8 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->d_rope_denom = nullptr;
     ctx->h_rope_denom = nullptr;
     ctx->own_stream = nullptr;
+    ctx->d_scratch = nullptr;
+    ctx->scratch_bytes = 0;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -60,12 +62,14 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
               cudaMemset(ctx->d_flags, 0, 4 * sizeof(uint32_t)) == cudaSuccess &&
               cudaHostAlloc(&ctx->h_flags, 4 * sizeof(uint32_t), cudaHostAllocDefault) == cudaSuccess &&
               cudaMalloc(&ctx->d_rope_denom, rope_bytes) == cudaSuccess &&
+              cudaMalloc(&ctx->d_scratch, AGN_SCRATCH_BYTES) == cudaSuccess &&
               cudaHostAlloc(&ctx->h_rope_denom, rope_bytes, cudaHostAllocDefault) == cudaSuccess;
     if (!ok) {
         (void)cudaGetLastError();
         agn_ctx_destroy(ctx);
         return AGN_ECUDA;
     }
+    ctx->scratch_bytes = AGN_SCRATCH_BYTES;
     ctx->stream = ctx->own_stream;
     *out = ctx;
     return AGN_OK;
@@ -82,6 +86,7 @@ int32_t agn_ctx_destroy(agn_ctx *ctx) {
     if (ctx->h_flags) cudaFreeHost(ctx->h_flags);
     if (ctx->d_rope_denom) cudaFree(ctx->d_rope_denom);
     if (ctx->h_rope_denom) cudaFreeHost(ctx->h_rope_denom);
+    if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     (void)cudaGetLastError();
     delete ctx;
     return AGN_OK;

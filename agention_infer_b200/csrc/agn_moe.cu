@@ -1,0 +1,203 @@
+// MoE routing ops for token rows: router softmax + top-2, and the stable gather of the
+// hidden rows by expert that feeds the per-expert SwiGLU.
+//
+// The reference does not implement an MoE forward pass; the semantics follow its design
+// notes (docs/08-moe-routing.md:27-33, docs/05-inference-pipeline.md:271-317):
+//   probs = softmax(router logits) ; pick the top-k experts ; weights = their probabilities,
+//   not renormalised.
+// Selection compares the logits (softmax is monotonic, so this is top-k by probability
+// without depending on exp rounding); ties go to the lower expert index.
+//
+// gather_rows_by_expert is a stable counting sort of the 2T (token, slot) pairs by expert
+// (order inside an expert: ascending token, slot 0 before slot 1) followed by a row copy:
+//   1. count   : per chunk of 1024 pairs, a histogram over experts      -> scratch
+//   2. scan    : exclusive scan over (expert, chunk)                    -> scratch, offsets
+//   3. place   : stable rank of each pair inside its chunk (warp match + warp prefix)
+//   4. gather  : out[dst] = x[src_token[dst]], 128-bit streaming copies (bound by HBM:
+//                8 bytes per gathered element)
+#include <math.h>
+
+#include "agn_common.cuh"
+
+namespace {
+
+constexpr int CHUNK = 1024;  // pairs per CTA in count/place
+constexpr int MAX_EXPERTS = 64;
+
+__global__ void __launch_bounds__(256)
+router_top2_kernel(const float *__restrict__ logits, int64_t T, int E, int32_t *__restrict__ idx, float *__restrict__ w) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const float *l = logits + t * E;
+    // softmax statistics in the reference's order: max by left fold, then sequential sum
+    float m = -INFINITY;
+    for (int e = 0; e < E; e++) m = fmaxf(m, l[e]);
+    float sum = 0.0f;
+    for (int e = 0; e < E; e++) sum += expf(l[e] - m);
+    int b0 = 0;
+    for (int e = 1; e < E; e++)
+        if (l[e] > l[b0]) b0 = e;
+    int b1 = -1;
+    for (int e = 0; e < E; e++) {
+        if (e == b0) continue;
+        if (b1 < 0 || l[e] > l[b1]) b1 = e;
+    }
+    idx[2 * t] = b0;
+    idx[2 * t + 1] = b1;
+    w[2 * t] = expf(l[b0] - m) / sum;
+    w[2 * t + 1] = b1 >= 0 ? expf(l[b1] - m) / sum : 0.0f;
+}
+
+__global__ void __launch_bounds__(CHUNK)
+expert_count_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, int32_t *__restrict__ chunk_counts,
+                    uint32_t *flags) {
+    __shared__ int cnt[MAX_EXPERTS];
+    if (threadIdx.x < MAX_EXPERTS) cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const int64_t i = (int64_t)blockIdx.x * CHUNK + threadIdx.x;
+    if (i < n_pairs) {
+        const int e = idx[i];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+        else atomicOr(flags, AGN_FLAG_OOB_ID);
+    }
+    __syncthreads();
+    if (threadIdx.x < E) chunk_counts[(int64_t)blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
+}
+
+// One CTA.  chunk_counts[c][e] -> exclusive position of (e, c) in expert-major order.
+__global__ void __launch_bounds__(MAX_EXPERTS)
+expert_scan_kernel(int32_t *__restrict__ chunk_counts, int n_chunks, int E, int32_t *__restrict__ offsets) {
+    __shared__ int total[MAX_EXPERTS + 1];
+    const int e = threadIdx.x;
+    if (e < E) {
+        int run = 0;
+        for (int c = 0; c < n_chunks; c++) {
+            const int v = chunk_counts[(int64_t)c * E + e];
+            chunk_counts[(int64_t)c * E + e] = run;
+            run += v;
+        }
+        total[e] = run;
+    }
+    __syncthreads();
+    if (e == 0) {
+        int run = 0;
+        for (int k = 0; k < E; k++) {
+            const int v = total[k];
+            total[k] = run;
+            offsets[k] = run;
+            run += v;
+        }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    if (e < E)
+        for (int c = 0; c < n_chunks; c++) chunk_counts[(int64_t)c * E + e] += total[e];
+}
+
+__global__ void __launch_bounds__(CHUNK)
+expert_place_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, const int32_t *__restrict__ chunk_base,
+                    int32_t *__restrict__ src_token, int32_t *__restrict__ src_slot) {
+    __shared__ int warp_cnt[CHUNK / 32][MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < (CHUNK / 32) * MAX_EXPERTS; k += blockDim.x) (&warp_cnt[0][0])[k] = 0;
+    __syncthreads();
+    const int64_t i = (int64_t)blockIdx.x * CHUNK + threadIdx.x;
+    int e = -1;
+    if (i < n_pairs) {
+        e = idx[i];
+        if (e < 0 || e >= E) e = -1;
+    }
+    // lanes of this warp holding the same expert; the rank inside the warp keeps lane order
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_cnt[warp][e] = __popc(same);
+    __syncthreads();
+    if (e >= 0) {
+        int before = 0;
+        for (int w = 0; w < warp; w++) before += warp_cnt[w][e];
+        const int dst = chunk_base[(int64_t)blockIdx.x * E + e] + before + rank_in_warp;
+        src_token[dst] = (int32_t)(i >> 1);
+        src_slot[dst] = (int32_t)(i & 1);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const float *__restrict__ x, const int32_t *__restrict__ src_token, int64_t n_out, int64_t T,
+                   int64_t H, float *__restrict__ out, int vec) {
+    const int64_t r = blockIdx.x;
+    const int64_t t = src_token[r];
+    if (t < 0 || t >= T) return;
+    if (vec) {
+        const float4 *s = reinterpret_cast<const float4 *>(x + t * H);
+        float4 *d = reinterpret_cast<float4 *>(out + r * H);
+        for (int i = threadIdx.x; i < (int)(H >> 2); i += blockDim.x) agn_st_stream(d + i, __ldg(s + i));
+    } else {
+        for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[r * H + i] = x[t * H + i];
+    }
+}
+
+}  // namespace
+
+size_t agn_gather_scratch_bytes(int64_t T, int32_t n_experts) {
+    const int64_t n_chunks = (2 * T + CHUNK - 1) / CHUNK;
+    return (size_t)n_chunks * (size_t)n_experts * sizeof(int32_t);
+}
+
+// Shared by the context-workspace entry point and any caller that brings its own scratch.
+int32_t agn_gather_rows_by_expert_impl(agn_ctx *ctx, const float *x, const int32_t *idx, int64_t T, int64_t H,
+                                       int32_t n_experts, float *out, int32_t *offsets, int32_t *src_token,
+                                       int32_t *src_slot, int32_t *scratch) {
+    const int64_t n_pairs = 2 * T;
+    const int n_chunks = (int)((n_pairs + CHUNK - 1) / CHUNK);
+    // pairs with an out-of-range expert are skipped by `place`; mark their slots as empty
+    AGN_CUDA(ctx, cudaMemsetAsync(src_token, 0xFF, sizeof(int32_t) * (size_t)n_pairs, ctx->stream));
+    expert_count_kernel<<<n_chunks, CHUNK, 0, ctx->stream>>>(idx, n_pairs, n_experts, scratch, ctx->d_flags);
+    AGN_LAUNCHED(ctx, "expert_count");
+    expert_scan_kernel<<<1, MAX_EXPERTS, 0, ctx->stream>>>(scratch, n_chunks, n_experts, offsets);
+    AGN_LAUNCHED(ctx, "expert_scan");
+    expert_place_kernel<<<n_chunks, CHUNK, 0, ctx->stream>>>(idx, n_pairs, n_experts, scratch, src_token, src_slot);
+    AGN_LAUNCHED(ctx, "expert_place");
+    const int vec = (H % 4 == 0 && agn_aligned16(x) && agn_aligned16(out)) ? 1 : 0;
+    gather_rows_kernel<<<(unsigned)n_pairs, 256, 0, ctx->stream>>>(x, src_token, n_pairs, T, H, out, vec);
+    AGN_LAUNCHED(ctx, "gather_rows");
+    ctx->flags_dirty = true;
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_router_top2_f32(agn_ctx *ctx, const float *logits, int64_t T, int32_t n_experts, int32_t *idx,
+                                       float *w) {
+    AGN_CHECK_CTX(ctx);
+    if (T < 0 || n_experts < 2 || n_experts > 1024)
+        return agn_fail(ctx, AGN_EINVAL, "router_top2: T=%lld n_experts=%d (need 2..1024)", (long long)T, n_experts);
+    if (T == 0) return AGN_OK;
+    if (!logits || !idx || !w) return agn_fail(ctx, AGN_EINVAL, "router_top2: null pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int64_t blocks = (T + 255) / 256;
+    if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "router_top2: T too large");
+    router_top2_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(logits, T, n_experts, idx, w);
+    AGN_LAUNCHED(ctx, "router_top2");
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, const int32_t *idx, int64_t T, int64_t H,
+                                                 int32_t n_experts, float *out, int32_t *offsets, int32_t *src_token,
+                                                 int32_t *src_slot) {
+    AGN_CHECK_CTX(ctx);
+    if (T < 0 || H <= 0 || n_experts < 1 || n_experts > MAX_EXPERTS)
+        return agn_fail(ctx, AGN_EINVAL, "gather_rows_by_expert: T=%lld H=%lld n_experts=%d (need 1..%d)", (long long)T,
+                        (long long)H, n_experts, MAX_EXPERTS);
+    if (!offsets) return agn_fail(ctx, AGN_EINVAL, "gather_rows_by_expert: null offsets");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (T == 0) {
+        AGN_CUDA(ctx, cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (n_experts + 1), ctx->stream));
+        return AGN_OK;
+    }
+    if (!x || !idx || !out || !src_token || !src_slot) return agn_fail(ctx, AGN_EINVAL, "gather_rows_by_expert: null pointer");
+    if (2 * T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "gather_rows_by_expert: T too large");
+    const size_t need = agn_gather_scratch_bytes(T, n_experts);
+    if (need > ctx->scratch_bytes)
+        return agn_fail(ctx, AGN_EINVAL, "gather_rows_by_expert: needs %zu bytes of workspace, the context holds %zu", need,
+                        ctx->scratch_bytes);
+    return agn_gather_rows_by_expert_impl(ctx, x, idx, T, H, n_experts, out, offsets, src_token, src_slot,
+                                          static_cast<int32_t *>(ctx->d_scratch));
+}

@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Layer-op hot-path benchmark: tokens/s and HBM GB/s of the CUDA backend, one JSON line.
+
+  python bench.py --gpus N --steps K --warmup W            # our CUDA arm (default)
+  python bench.py --impl reference --gpus N --steps K ...  # the CPU restatement of the reference
+  torchrun --nproc-per-node N bench.py --gpus N ...        # one rank per GPU
+
+A step is one pass of the hot path over one batch of token rows of the Qwen2.5-7B-shaped
+prefill configuration (T=4096 rows per GPU): quantised-embedding get_rows (Q4_K), RMSNorm,
+NeoX RoPE on Q and K, the fused per-head norm->RoPE, and the fused SiLU*mul.  Rows shard
+across ranks with no data-path collective (weak scaling: T rows per GPU).
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "layer_op_tokens_per_s"
+UNIT = "tokens/s"
+NSETS = 4  # rotating buffer sets: every timed launch reads inputs that are not in L2
+
+
+# --------------------------------------------------------------------------- helpers
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes(cfg, T):
+    """Bytes each op must move for T token rows (f32 activations, read + write)."""
+    from agention_infer_b200 import CudaBackend
+    H, hd, nq, nkv, I = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
+    row_bytes = CudaBackend.type_size(cfg.embd_dtype, H)
+    rope = 8 * T * (nq + nkv) * hd + 4 * T + 2 * cfg.n_rot
+    return {
+        "get_rows": T * row_bytes + 4 * T * H + 4 * T,
+        "rms_norm": 8 * T * H + 4 * H,
+        "rope_qk": rope,
+        "qk_norm_rope_qk": rope + 8 * hd,
+        "silu_mul": 12 * T * I,
+    }
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the GPU is under load."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(device_index), f"--query-gpu={self.Q}",
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons, power = [], [], set(), []
+        for r in rows:
+            if len(r) < 8:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1])); power.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": float(max(power))}
+
+
+# ------------------------------------------------------------------- CPU (reference) arm
+
+def cpu_step(orc, cfg, data, rows, threads):
+    """One pass of the hot path over `rows` token rows on the host, oracle code."""
+    T = rows
+    orc.get_rows(cfg.embd_dtype, data["table"], cfg.vocab, cfg.hidden, data["ids"][:T], threads)
+    orc.rms_norm_rows(data["x"][:T], data["w"], cfg.eps, threads)
+    orc.rope_rows(data["q"][:T], cfg.n_q_heads, cfg.head_dim, cfg.n_rot, data["pos"][:T], cfg.theta, 1.0, 0, threads)
+    orc.rope_rows(data["k"][:T], cfg.n_kv_heads, cfg.head_dim, cfg.n_rot, data["pos"][:T], cfg.theta, 1.0, 0, threads)
+    orc.qk_norm_rope_rows(data["q"][:T], data["wq"], cfg.n_q_heads, cfg.head_dim, cfg.eps, cfg.n_rot, data["pos"][:T],
+                          cfg.theta, 1.0, 0, threads)
+    orc.qk_norm_rope_rows(data["k"][:T], data["wk"], cfg.n_kv_heads, cfg.head_dim, cfg.eps, cfg.n_rot,
+                          data["pos"][:T], cfg.theta, 1.0, 0, threads)
+    orc.silu_mul(data["gate"][:T], data["up"][:T], threads)
+
+
+def host_data(cfg, T, vocab_rows=None):
+    """Seeded host inputs of one batch.  A reduced number of table rows keeps the CPU arm's
+    set-up short; ids are drawn inside it."""
+    from agention_infer_b200 import synth
+    vocab = cfg.vocab if vocab_rows is None else vocab_rows
+    i = cfg.index
+    d = {
+        "table": synth.quant_table(cfg.embd_dtype, vocab, cfg.hidden, cfg_index=i),
+        "ids": synth.token_ids(i, T, vocab),
+        "x": synth.activations(i, "x", (T, cfg.hidden)),
+        "w": synth.norm_weight(i, "w", cfg.hidden),
+        "q": synth.activations(i, "q", (T, cfg.n_q_heads * cfg.head_dim)),
+        "k": synth.activations(i, "k", (T, cfg.n_kv_heads * cfg.head_dim)),
+        "wq": synth.norm_weight(i, "wq", cfg.head_dim),
+        "wk": synth.norm_weight(i, "wk", cfg.head_dim),
+        "pos": synth.positions(i, T, cfg.random_pos),
+        "gate": synth.activations(i, "gate", (T, cfg.ffn)),
+        "up": synth.activations(i, "up", (T, cfg.ffn)),
+    }
+    return d, vocab
+
+
+def time_cpu(orc, cfg, data, rows, threads, reps):
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_step(orc, cfg, data, rows, threads)
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+def run_reference(args, cfg):
+    """The reference's CPU implementation of the path (C restatement; the Rust original cannot
+    be built here), all host threads, on a bounded row sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    threads = orc.max_threads()
+    rows = min(cfg.T, 1024)
+    data, vocab = host_data(cfg, rows, vocab_rows=min(cfg.vocab, 16384))
+
+    c = dataclasses.replace(cfg, vocab=vocab)  # same config with the reduced table
+    t1 = time_cpu(orc, c, data, rows, threads, 1)
+    budget = 120.0
+    while rows > 64 and t1 * (args.steps + args.warmup) > budget:
+        rows //= 2
+        t1 = time_cpu(orc, c, data, rows, threads, 1)
+    for _ in range(args.warmup):
+        cpu_step(orc, c, data, rows, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(orc, c, data, rows, threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = rows / dt
+    sample = f"{rows} of {cfg.T} token rows per step, table of {vocab} rows, OpenMP over rows"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens_per_step": rows, "hidden": cfg.hidden, "ffn": cfg.ffn,
+                   "embedding": "Q4_K", "ops": ["get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------- CUDA arm
+
+def run_ours(args, cfg):
+    import torch
+    import torch.distributed as dist
+
+    from agention_infer_b200 import CudaBackend, sharding, synth
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    be = CudaBackend(local)
+    # One explicit (non-default) stream for everything: torch's allocations and events and our
+    # kernels.  (A null handle would select the backend's own stream, which torch events on
+    # the default stream do not see.)
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
+    be.set_stream(stream.cuda_stream)
+    assert be.stream() == stream.cuda_stream
+
+    T, H, hd, nq, nkv, I = cfg.T, cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
+    ab = algorithmic_bytes(cfg, T)
+    table_h = synth.quant_table(cfg.embd_dtype, cfg.vocab, H, cfg_index=cfg.index)
+    table = torch.from_numpy(table_h).to(dev)
+    table_bytes = table_h.nbytes
+    w = torch.from_numpy(synth.norm_weight(cfg.index, "w", H)).to(dev)
+    wq = torch.from_numpy(synth.norm_weight(cfg.index, "wq", hd)).to(dev)
+    wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
+    pos = torch.from_numpy(synth.positions(cfg.index, T, cfg.random_pos)).to(dev)
+    gen = torch.Generator(device=dev); gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index + rank)
+    sets = []
+    for s in range(NSETS):
+        ids = torch.from_numpy(synth.token_ids(cfg.index, T, cfg.vocab, salt=1 + rank * NSETS + s).astype(np.int32)).to(dev)
+        sets.append({
+            "ids": ids, "emb": torch.empty(T, H, device=dev),
+            "x": torch.randn(T, H, device=dev, generator=gen), "xn": torch.empty(T, H, device=dev),
+            "q": torch.randn(T, nq * hd, device=dev, generator=gen), "k": torch.randn(T, nkv * hd, device=dev, generator=gen),
+            "q2": torch.randn(T, nq * hd, device=dev, generator=gen), "k2": torch.randn(T, nkv * hd, device=dev, generator=gen),
+            "gate": torch.randn(T, I, device=dev, generator=gen), "up": torch.randn(T, I, device=dev, generator=gen),
+            "act": torch.empty(T, I, device=dev),
+        })
+
+    ops = {
+        "get_rows": lambda b: be.get_rows(cfg.embd_dtype, table, table_bytes, cfg.vocab, H, b["ids"], T, out=b["emb"]),
+        "rms_norm": lambda b: be.launch_rms_norm(b["x"], w, T, H, cfg.eps, out=b["xn"]),
+        "rope_qk": lambda b: be.launch_rope_qk(b["q"], b["k"], T, nq, nkv, hd, cfg.n_rot, pos, cfg.theta),
+        "qk_norm_rope_qk": lambda b: be.launch_qk_norm_rope_qk(b["q2"], b["k2"], wq, wk, T, nq, nkv, hd, cfg.eps,
+                                                               cfg.n_rot, pos, cfg.theta),
+        "silu_mul": lambda b: be.launch_silu_mul(b["gate"], b["up"], T * I, out=b["act"]),
+    }
+    order = list(ops)
+
+    def step(i, silu_events=None):
+        b = sets[i % NSETS]
+        for name in order:
+            if silu_events is not None and name == "silu_mul":
+                e0, e1 = silu_events
+                e0.record(stream); ops[name](b); e1.record(stream)
+            else:
+                ops[name](b)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+
+    # ---- timed region: exactly K steps, device time, max over ranks
+    silu_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = be.launch_count
+    start.record(stream)
+    for i in range(args.steps):
+        step(i, silu_ev[i])
+    stop.record(stream)
+    barrier()
+    launches = be.launch_count - n0
+    elapsed_ms = sharding.max_over_ranks(start.elapsed_time(stop))
+    silu_ms = float(np.mean([a.elapsed_time(b) for a, b in silu_ev]))
+    ms_per_step = elapsed_ms / args.steps
+    value = world * T / (ms_per_step * 1e-3)
+
+    # ---- per-op device time, each op alone, rotating buffer sets (inputs never L2-resident)
+    per_op = {}
+    reps = 40
+    for name in order:
+        for i in range(4):
+            ops[name](sets[i % NSETS])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(reps):
+            ops[name](sets[i % NSETS])
+        b.record(stream)
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / reps
+        per_op[name] = {"us": round(us, 2), "gbs": round(ab[name] / (us * 1e-6) / 1e9, 1)}
+    clocks = sampler.stop() if sampler else None
+
+    # ---- end to end through the public API with HOST buffers: pinned inputs -> device ->
+    #      ops -> pinned outputs, every step, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        b0 = sets[0]
+        names_in = ["ids", "x", "q", "k", "q2", "k2", "gate", "up"]
+        names_out = ["emb", "xn", "q", "k", "q2", "k2", "act"]
+        host_in = {n: b0[n].cpu().pin_memory() for n in names_in}
+        host_out = {n: torch.empty_like(b0[n], device="cpu").pin_memory() for n in names_out}
+        h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+        d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+
+        def e2e_step():
+            for n in names_in:
+                be.copy_h2d(b0[n], host_in[n].numpy())
+            for name in order:
+                ops[name](b0)
+            for n in names_out:
+                be.copy_d2h(host_out[n].numpy(), b0[n])
+
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record(stream)
+        barrier()
+        e2e_ms = sharding.max_over_ranks(a.elapsed_time(b)) / e2e_steps
+        e2e = {"value": world * T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms, "steps": e2e_steps}
+
+    # ---- verification gather (the only collective): per-rank checksums of one op's output
+    be.sync()
+    chk = sharding.gather_objects(sharding.checksum(sets[0]["xn"][:8].cpu().numpy()))
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        achieved = ab["silu_mul"] / (silu_ms * 1e-3) / 1e9
+        step_bytes = sum(ab.values())
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg.name, "tokens_per_gpu": T, "hidden": H, "head_dim": hd, "q_heads": nq,
+                       "kv_heads": nkv, "ffn": I, "embedding": "Q4_K 152064x3584", "ops": order,
+                       "parallelism": f"token rows sharded over {world} GPU(s), no data-path collective",
+                       "l2": f"inputs larger than L2: {NSETS} rotating buffer sets, {step_bytes / 1e9:.2f} GB per step"},
+            "hbm_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9 * world,
+            "hbm_frac_of_measured_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+            "roofline": {"kernel": "silu_mul_vec4_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_src} (of measured copy bandwidth)"
+                         if peak_src == "measured" else "fallback", "traffic": None,
+                         "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
+            "ops": per_op, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+            "verification": {"ranks": len(chk)},
+        }
+        traffic = ROOT / "profiles" / "silu_mul_traffic.json"
+        if traffic.exists():
+            try:
+                tj = json.loads(traffic.read_text())
+                out["roofline"]["traffic"] = tj["dram_bytes_per_element"] * T * I
+            except Exception:
+                pass
+        if world == 1 and not args.no_cpu:
+            out["cpu_baseline"] = cpu_baseline(cfg)
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    be.close()
+
+
+def cpu_baseline(cfg):
+    """The oracle timed on this box's host cores on a bounded sample of the workload."""
+    from oracle import oracle as orc
+    threads = orc.max_threads()
+    rows = min(cfg.T, 1024)
+    data, vocab = host_data(cfg, rows, vocab_rows=min(cfg.vocab, 16384))
+
+    c = dataclasses.replace(cfg, vocab=vocab)
+    cpu_step(orc, c, data, rows, threads)
+    t_all = time_cpu(orc, c, data, rows, threads, 5)
+    t_one = time_cpu(orc, c, data, rows, 1, 2)
+    return {"value": rows / t_all, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{rows} of {cfg.T} token rows, table of {vocab} rows, best of 5, OpenMP over rows",
+            "single_thread_value": rows / t_one}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 200; 5 for --impl reference)")
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tokens", type=int, default=None,
+                    help="token rows per GPU (default: the configuration's 4096); smaller values are for profiling")
+    args = ap.parse_args()
+    from agention_infer_b200 import synth
+    cfg = synth.CONFIGS["c2"]
+    if args.tokens:
+        cfg = dataclasses.replace(cfg, T=args.tokens, name=f"{cfg.name} (rows overridden to {args.tokens})")
+    if args.steps is None:
+        args.steps = 5 if args.impl == "reference" else 200
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world == 1 and args.gpus > 1:
+            # not under torchrun: relaunch one rank per GPU
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", "29517", __file__, *sys.argv[1:]]
+            sys.exit(subprocess.call(cmd))
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

@@ -79,7 +79,9 @@ AGN_API const char *agn_backend_name(void);
 AGN_API const char *agn_last_error(agn_ctx *ctx);
 AGN_API const char *agn_status_string(int32_t status);
 /* Use an existing cudaStream_t (e.g. the host framework's) instead of the
- * context's own; pass NULL to return to the own stream. */
+ * context's own; pass NULL to return to the own stream.  (NULL therefore does not
+ * mean CUDA's legacy default stream; pass cudaStreamLegacy / cudaStreamPerThread
+ * explicitly for those.) */
 AGN_API int32_t agn_ctx_set_stream(agn_ctx *ctx, void *cuda_stream);
 AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
 /* Number of kernels this context has launched so far. */
@@ -183,6 +185,27 @@ AGN_API int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, 
 AGN_API int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table,
                                  size_t table_bytes, int64_t n_rows, int64_t row_len,
                                  const uint32_t *ids, int64_t T, float *out);
+
+/* MoE router: softmax over the n_experts logits of each token and top-2 selection.  The
+ * reference has no MoE forward pass; the semantics follow its design notes
+ * (docs/08-moe-routing.md:27-33): weights are the softmax probabilities of the two picks,
+ * not renormalised; ties go to the lower expert index.  logits [T, n_experts] f32;
+ * idx [T, 2] int32; w [T, 2] f32. */
+AGN_API int32_t agn_router_top2_f32(agn_ctx *ctx, const float *logits, int64_t T, int32_t n_experts,
+                                    int32_t *idx, float *w);
+
+/* Gather of the hidden rows by expert, the step that feeds the per-expert SwiGLU
+ * (docs/05-inference-pipeline.md:271-317; not implemented by the reference).  Stable
+ * counting sort of the 2T (token, slot) pairs of idx [T, 2] by expert — inside an expert:
+ * ascending token, slot 0 before slot 1 — then out[r, :] = x[src_token[r], :].
+ * x [T, H]; out [2T, H]; offsets int32 [n_experts + 1] (rows of expert e are
+ * offsets[e] .. offsets[e+1]); src_token, src_slot int32 [2T].  All device pointers.
+ * Uses the context's workspace; n_experts <= 64.  An expert index outside
+ * [0, n_experts) drops that pair and makes the next agn_sync return AGN_EOOB_ID. */
+AGN_API int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, const int32_t *idx,
+                                              int64_t T, int64_t H, int32_t n_experts, float *out,
+                                              int32_t *offsets, int32_t *src_token,
+                                              int32_t *src_slot);
 
 /* `GgmlType::type_size` (src/types.rs:164-168); 0 for a dtype without a kernel. */
 AGN_API size_t agn_type_size(int32_t dtype, size_t n);

@@ -386,13 +386,15 @@ void orc_router_top2(const float *logits, size_t T, size_t n_experts, int32_t *i
     for (size_t t = 0; t < T; t++) {
         memcpy(p, logits + t * n_experts, n_experts * sizeof(float));
         orc_softmax(p, n_experts);
+        /* softmax is monotonic: rank by logit so that exp rounding cannot reorder picks */
+        const float *l = logits + t * n_experts;
         int b0 = 0;
         for (size_t e = 1; e < n_experts; e++)
-            if (p[e] > p[b0]) b0 = (int)e;
+            if (l[e] > l[b0]) b0 = (int)e;
         int b1 = -1;
         for (size_t e = 0; e < n_experts; e++) {
             if ((int)e == b0) continue;
-            if (b1 < 0 || p[e] > p[b1]) b1 = (int)e;
+            if (b1 < 0 || l[e] > l[b1]) b1 = (int)e;
         }
         idx[2 * t] = b0;
         idx[2 * t + 1] = b1;
