@@ -14,16 +14,15 @@
 // (head, d) thread; at 6 TB/s that alone would saturate the SM's issue slots).
 //
 // Fast path (rope_heads_kernel): a group of W lanes owns one head, the head lives in
-// registers (VPL float4 per lane), each group has SLOTS heads in flight so that every
-// lane has SLOTS*VPL 128-bit loads outstanding before the first use.  The norm statistic
-// is a shuffle reduction inside the group; the NeoX partner is fetched with one
-// shuffle-xor (or is in the same lane for head_dim 256).  The intermediate normalised
-// head never leaves registers.
+// registers (VPL float4 per lane, float4 number lane + W*l), each group has 2 or 4 heads
+// in flight so that every lane has 8 or more 128-bit loads outstanding before the first
+// use.  W is chosen so that the NeoX partner of a float4 is another register of the same
+// lane (head_dim 128: W=8, VPL=4, partner two registers on), which needs no shuffle; the
+// norm statistic is a log2(W)-step shuffle reduction inside the group.  The intermediate
+// normalised head never leaves registers.
 #include "agn_common.cuh"
 
 namespace {
-
-constexpr int SLOTS = 4;
 
 struct RopeArgs {
     float *q;
@@ -57,57 +56,69 @@ __device__ __forceinline__ void fill_sincos(const RopeArgs &a, float *s_cos, flo
     }
 }
 
-template <int W, int VPL, int LAYOUT, bool NORM>
-__global__ void __launch_bounds__(512)
+// How the rotated pairs map onto the registers of a lane (float4 number i = lane + W*l):
+enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
+       MODE_NEOX_K1 = 1,  // NeoX, n_rot/8 == W   : partner float4 is register l+1 of the same lane
+       MODE_NEOX_K2 = 2,  // NeoX, n_rot/8 == 2*W : partner float4 is register l+2 of the same lane
+       MODE_NEOX_SHFL = 3 // NeoX, n_rot/8 < W (power of two): partner is register 0 of lane ^ (n_rot/8)
+};
+
+template <int W, int VPL, int MODE, bool NORM>
+__global__ void __launch_bounds__(256)
 rope_heads_kernel(const RopeArgs a) {
-    extern __shared__ __align__(16) float smem[];
+    constexpr int NS = VPL == 4 ? 2 : 4;  // head rows in flight per lane group
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int half = a.n_rot >> 1;
-    float *s_cos = smem;
-    float *s_sin = smem + a.tpc * half;
-    fill_sincos(a, s_cos, s_sin, half);
+    const int n_heads = a.n_q + a.n_kv;
+    const int rows = a.tpc * n_heads;  // head rows of this CTA
+    // shared memory: row pointers | row meta (token in CTA, is-K flag) | cos | sin
+    float **s_ptr = reinterpret_cast<float **>(smem_raw);
+    int *s_meta = reinterpret_cast<int *>(smem_raw + (size_t)rows * 8);
+    float *s_cos = reinterpret_cast<float *>(smem_raw + (((size_t)rows * 12 + 15) & ~(size_t)15));
+    float *s_sin = s_cos + a.tpc * half;
+    const int64_t t0 = (int64_t)blockIdx.x * a.tpc;
+
+    // one integer division per head row per CTA, instead of one per lane and slot
+    for (int hr = threadIdx.x; hr < rows; hr += blockDim.x) {
+        const int tt = hr / n_heads, h = hr - tt * n_heads;
+        const int64_t t = t0 + tt;
+        float *p = nullptr;
+        if (t < a.T)
+            p = h < a.n_q ? a.q + (t * a.n_q + h) * (int64_t)a.head_dim
+                          : a.k + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
+        s_ptr[hr] = p;
+        s_meta[hr] = tt | (h < a.n_q ? 0 : 1 << 16);
+    }
     __syncthreads();
 
     const int lane = threadIdx.x & (W - 1);
     const int group = threadIdx.x / W;
     const int n_groups = blockDim.x / W;
-    const int n_heads = a.n_q + a.n_kv;
-    const int rows = a.tpc * n_heads;  // head rows of this CTA
     const int hd4 = a.head_dim >> 2;
-    const int hq = half >> 2;  // float4 per half (NeoX), n_rot/8
-    const int64_t t0 = (int64_t)blockIdx.x * a.tpc;
+    const int hq = half >> 2;  // float4 per rotated half (NeoX): n_rot/8
 
-    for (int base = 0; base < rows; base += n_groups * SLOTS) {
-        float4 v[SLOTS][VPL];
-        float *ptr[SLOTS];
-        const float *wptr[SLOTS];
-        int tok[SLOTS];
+    for (int base = 0; base < rows; base += n_groups * NS) {
+        float4 v[NS][VPL];
+        float4 *ptr[NS];
+        int meta[NS];
 #pragma unroll
-        for (int s = 0; s < SLOTS; s++) {
+        for (int s = 0; s < NS; s++) {
             const int hr = base + group + s * n_groups;
-            const int tt = hr / n_heads, h = hr - tt * n_heads;
-            const int64_t t = t0 + tt;
-            const bool on = hr < rows && t < a.T;
-            tok[s] = tt;
-            ptr[s] = nullptr;
-            wptr[s] = nullptr;
-            if (on) {
-                if (h < a.n_q) {
-                    ptr[s] = a.q + (t * a.n_q + h) * (int64_t)a.head_dim;
-                    wptr[s] = a.wq;
-                } else {
-                    ptr[s] = a.k + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
-                    wptr[s] = a.wk;
-                }
-            }
+            ptr[s] = hr < rows ? reinterpret_cast<float4 *>(s_ptr[hr]) : nullptr;
+            meta[s] = hr < rows ? s_meta[hr] : 0;
 #pragma unroll
             for (int l = 0; l < VPL; l++) {
                 const int i = lane + W * l;
-                v[s][l] = (on && i < hd4) ? agn_ld_stream(reinterpret_cast<const float4 *>(ptr[s]) + i)
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[s][l] = (ptr[s] && i < hd4) ? agn_ld_stream(ptr[s] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
+        if (base == 0) {
+            // The sin/cos table is built while the HBM loads issued above are in flight.
+            fill_sincos(a, s_cos, s_sin, half);
+            __syncthreads();
+        }
 #pragma unroll
-        for (int s = 0; s < SLOTS; s++) {
+        for (int s = 0; s < NS; s++) {
             if (NORM) {
                 float ss = 0.0f;
 #pragma unroll
@@ -115,70 +126,71 @@ rope_heads_kernel(const RopeArgs a) {
                     ss += v[s][l].x * v[s][l].x + v[s][l].y * v[s][l].y + v[s][l].z * v[s][l].z + v[s][l].w * v[s][l].w;
 #pragma unroll
                 for (int o = W / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float rms = sqrtf(ss / (float)a.head_dim + a.eps);
+                // (w*x)/rms of the CPU path, evaluated as (w*x)*(1/rms): one IEEE division per
+                // head instead of one per element; differs from the CPU order by <= 1 ulp
+                const float inv = 1.0f / sqrtf(ss / (float)a.head_dim + a.eps);
+                const float4 *wv = reinterpret_cast<const float4 *>((meta[s] >> 16) ? a.wk : a.wq);
 #pragma unroll
                 for (int l = 0; l < VPL; l++) {
                     const int i = lane + W * l;
                     if (ptr[s] && i < hd4) {
-                        const float4 ww = __ldg(reinterpret_cast<const float4 *>(wptr[s]) + i);
-                        v[s][l].x = ww.x * v[s][l].x / rms;
-                        v[s][l].y = ww.y * v[s][l].y / rms;
-                        v[s][l].z = ww.z * v[s][l].z / rms;
-                        v[s][l].w = ww.w * v[s][l].w / rms;
+                        const float4 ww = __ldg(wv + i);
+                        v[s][l].x = ww.x * v[s][l].x * inv;
+                        v[s][l].y = ww.y * v[s][l].y * inv;
+                        v[s][l].z = ww.z * v[s][l].z * inv;
+                        v[s][l].w = ww.w * v[s][l].w * inv;
                     }
                 }
             }
-            const float *c_tab = s_cos + tok[s] * half;
-            const float *s_tab = s_sin + tok[s] * half;
-            if (LAYOUT == AGN_ROPE_NEOX) {
-                if (VPL > 1 && hq == (W * VPL) / 2) {
-                    // full rotation of a head wider than one float4 per lane: the partner
-                    // float4 sits in the same lane, VPL/2 registers further on
+            const float *c_tab = s_cos + (meta[s] & 0xffff) * half;
+            const float *s_tab = s_sin + (meta[s] & 0xffff) * half;
+            if (MODE == MODE_NEOX_K1 || MODE == MODE_NEOX_K2) {
+                constexpr int K = MODE == MODE_NEOX_K2 ? 2 : 1;
 #pragma unroll
-                    for (int l = 0; l < VPL / 2; l++) {
+                for (int l = 0; l < K; l++) {
+                    if (l + K < VPL && ptr[s]) {
                         const int i = lane + W * l;
-                        if (ptr[s]) {
-                            const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
-                            const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
-                            const float4 x0 = v[s][l], x1 = v[s][l + VPL / 2];
-                            v[s][l].x = x0.x * c.x - x1.x * sn.x;
-                            v[s][l].y = x0.y * c.y - x1.y * sn.y;
-                            v[s][l].z = x0.z * c.z - x1.z * sn.z;
-                            v[s][l].w = x0.w * c.w - x1.w * sn.w;
-                            v[s][l + VPL / 2].x = x0.x * sn.x + x1.x * c.x;
-                            v[s][l + VPL / 2].y = x0.y * sn.y + x1.y * c.y;
-                            v[s][l + VPL / 2].z = x0.z * sn.z + x1.z * c.z;
-                            v[s][l + VPL / 2].w = x0.w * sn.w + x1.w * c.w;
-                        }
-                    }
-                } else {
-                    // hq is a power of two below W: the partner float4 is in lane ^ hq
-                    const float4 mine = v[s][0];
-                    float4 oth;
-                    oth.x = __shfl_xor_sync(0xffffffffu, mine.x, hq);
-                    oth.y = __shfl_xor_sync(0xffffffffu, mine.y, hq);
-                    oth.z = __shfl_xor_sync(0xffffffffu, mine.z, hq);
-                    oth.w = __shfl_xor_sync(0xffffffffu, mine.w, hq);
-                    if (ptr[s] && lane < 2 * hq) {
-                        const bool low = lane < hq;
-                        const int i = low ? lane : lane - hq;
                         const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
                         const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
-                        if (low) {  // x0 = mine, x1 = oth
-                            v[s][0].x = mine.x * c.x - oth.x * sn.x;
-                            v[s][0].y = mine.y * c.y - oth.y * sn.y;
-                            v[s][0].z = mine.z * c.z - oth.z * sn.z;
-                            v[s][0].w = mine.w * c.w - oth.w * sn.w;
-                        } else {  // x0 = oth, x1 = mine
-                            v[s][0].x = oth.x * sn.x + mine.x * c.x;
-                            v[s][0].y = oth.y * sn.y + mine.y * c.y;
-                            v[s][0].z = oth.z * sn.z + mine.z * c.z;
-                            v[s][0].w = oth.w * sn.w + mine.w * c.w;
-                        }
+                        const float4 x0 = v[s][l], x1 = v[s][(l + K) % VPL];
+                        float4 y0, y1;
+                        y0.x = x0.x * c.x - x1.x * sn.x;
+                        y0.y = x0.y * c.y - x1.y * sn.y;
+                        y0.z = x0.z * c.z - x1.z * sn.z;
+                        y0.w = x0.w * c.w - x1.w * sn.w;
+                        y1.x = x0.x * sn.x + x1.x * c.x;
+                        y1.y = x0.y * sn.y + x1.y * c.y;
+                        y1.z = x0.z * sn.z + x1.z * c.z;
+                        y1.w = x0.w * sn.w + x1.w * c.w;
+                        v[s][l] = y0;
+                        v[s][(l + K) % VPL] = y1;
+                    }
+                }
+            } else if (MODE == MODE_NEOX_SHFL) {
+                const float4 mine = v[s][0];
+                float4 oth;
+                oth.x = __shfl_xor_sync(0xffffffffu, mine.x, hq);
+                oth.y = __shfl_xor_sync(0xffffffffu, mine.y, hq);
+                oth.z = __shfl_xor_sync(0xffffffffu, mine.z, hq);
+                oth.w = __shfl_xor_sync(0xffffffffu, mine.w, hq);
+                if (ptr[s] && lane < 2 * hq) {
+                    const bool low = lane < hq;
+                    const int i = low ? lane : lane - hq;
+                    const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
+                    const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
+                    if (low) {  // x0 = mine, x1 = oth
+                        v[s][0].x = mine.x * c.x - oth.x * sn.x;
+                        v[s][0].y = mine.y * c.y - oth.y * sn.y;
+                        v[s][0].z = mine.z * c.z - oth.z * sn.z;
+                        v[s][0].w = mine.w * c.w - oth.w * sn.w;
+                    } else {  // x0 = oth, x1 = mine
+                        v[s][0].x = oth.x * sn.x + mine.x * c.x;
+                        v[s][0].y = oth.y * sn.y + mine.y * c.y;
+                        v[s][0].z = oth.z * sn.z + mine.z * c.z;
+                        v[s][0].w = oth.w * sn.w + mine.w * c.w;
                     }
                 }
             } else {
-                // pairs (2p, 2p+1): both members are in the same float4
 #pragma unroll
                 for (int l = 0; l < VPL; l++) {
                     const int i = lane + W * l;
@@ -198,7 +210,7 @@ rope_heads_kernel(const RopeArgs a) {
                 const int i = lane + W * l;
                 // dims past n_rot are untouched by rope: skip the store unless normalised
                 const bool touched = NORM || 4 * i < a.n_rot;
-                if (ptr[s] && i < hd4 && touched) agn_st_stream(reinterpret_cast<float4 *>(ptr[s]) + i, v[s][l]);
+                if (ptr[s] && i < hd4 && touched) agn_st_stream(ptr[s] + i, v[s][l]);
             }
         }
     }
@@ -252,15 +264,25 @@ rope_heads_generic_kernel(const RopeArgs a) {
     }
 }
 
+template <int W, int VPL, int MODE>
+void launch_fast3(const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem, cudaStream_t st) {
+    if (norm) rope_heads_kernel<W, VPL, MODE, true><<<grid, threads, smem, st>>>(a);
+    else rope_heads_kernel<W, VPL, MODE, false><<<grid, threads, smem, st>>>(a);
+}
+
 template <int W, int VPL>
-void launch_fast(const RopeArgs &a, bool norm, int layout, unsigned grid, int threads, size_t smem, cudaStream_t st) {
-    if (layout == AGN_ROPE_NEOX) {
-        if (norm) rope_heads_kernel<W, VPL, AGN_ROPE_NEOX, true><<<grid, threads, smem, st>>>(a);
-        else rope_heads_kernel<W, VPL, AGN_ROPE_NEOX, false><<<grid, threads, smem, st>>>(a);
-    } else {
-        if (norm) rope_heads_kernel<W, VPL, AGN_ROPE_NORMAL, true><<<grid, threads, smem, st>>>(a);
-        else rope_heads_kernel<W, VPL, AGN_ROPE_NORMAL, false><<<grid, threads, smem, st>>>(a);
+bool launch_fast(const RopeArgs &a, bool norm, int mode, unsigned grid, int threads, size_t smem, cudaStream_t st) {
+    switch (mode) {
+    case MODE_NORMAL: launch_fast3<W, VPL, MODE_NORMAL>(a, norm, grid, threads, smem, st); return true;
+    case MODE_NEOX_SHFL: launch_fast3<W, VPL, MODE_NEOX_SHFL>(a, norm, grid, threads, smem, st); return true;
+    case MODE_NEOX_K1:
+        if constexpr (VPL >= 2) { launch_fast3<W, VPL, MODE_NEOX_K1>(a, norm, grid, threads, smem, st); return true; }
+        return false;
+    case MODE_NEOX_K2:
+        if constexpr (VPL >= 4) { launch_fast3<W, VPL, MODE_NEOX_K2>(a, norm, grid, threads, smem, st); return true; }
+        return false;
     }
+    return false;
 }
 
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -294,19 +316,33 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
     const int n_heads = n_q + n_kv;
     const int hd4 = head_dim / 4;
 
-    // register fast path?
-    int W = 8;
-    while (W < 32 && W < hd4) W *= 2;
-    const int VPL = (hd4 + W - 1) / W;
+    // Register fast path: a group of W lanes owns a head of W*VPL float4 (or fewer, with idle
+    // lanes).  Prefer many registers per lane (VPL 4) so that the NeoX partner of a float4
+    // is in the same lane and the per-head bookkeeping is amortised over more data.
+    int W = 0, VPL = 0, mode = -1;
     const int hq = half / 4;
-    bool fast = head_dim % 4 == 0 && (VPL == 1 || VPL == 2 || VPL == 4) && (n_q == 0 || agn_aligned16(q)) &&
-                (n_kv == 0 || agn_aligned16(k)) &&
+    bool fast = head_dim % 4 == 0 && (n_q == 0 || agn_aligned16(q)) && (n_kv == 0 || agn_aligned16(k)) &&
                 (!norm || ((n_q == 0 || agn_aligned16(wq)) && (n_kv == 0 || agn_aligned16(wk))));
-    if (fast && n_rot > 0) {
-        if (layout == AGN_ROPE_NEOX)
-            fast = half % 4 == 0 && ((VPL > 1 && hq == (W * VPL) / 2) || (is_pow2(hq) && hq < W));
-        else
-            fast = n_rot % 4 == 0;
+    if (fast) {
+        static const int shapes[7][2] = {{8, 4}, {16, 4}, {32, 4}, {8, 2}, {8, 1}, {32, 2}, {32, 1}};
+        bool found = false;
+        for (int pass = 0; pass < 2 && !found; pass++) {
+            for (int c = 0; c < 7 && !found; c++) {
+                const int w = shapes[c][0], v = shapes[c][1];
+                const bool exact = w * v == hd4;
+                if (pass == 0 ? !exact : !(w == 32 && w * v >= hd4 && w * (v / 2) < hd4)) continue;
+                int m = -1;
+                if (n_rot == 0 || layout == AGN_ROPE_NORMAL) {
+                    if (n_rot % 4 == 0) m = MODE_NORMAL;
+                } else if (half % 4 == 0) {
+                    if (hq == w && v >= 2) m = MODE_NEOX_K1;
+                    else if (hq == 2 * w && v >= 4) m = MODE_NEOX_K2;
+                    else if (is_pow2(hq) && 2 * hq <= w) m = MODE_NEOX_SHFL;
+                }
+                if (m >= 0) { W = w; VPL = v; mode = m; found = true; }
+            }
+        }
+        fast = found;
     }
     if (fast) {
         // tokens per CTA: aim at 32 head rows per CTA, keep the sin/cos table small
@@ -316,17 +352,22 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
         if ((int64_t)tpc > T) tpc = (int)T;
         a.tpc = tpc;
         const int rows = tpc * n_heads;
-        int groups = (rows + SLOTS - 1) / SLOTS;
+        const int ns = VPL == 4 ? 2 : 4;
+        int groups = (rows + ns - 1) / ns;
         int threads = groups * W;
         threads = ((threads + 31) / 32) * 32;
-        if (threads > 512) threads = 512;
+        if (threads > 256) threads = 256;
         const unsigned grid = (unsigned)((T + tpc - 1) / tpc);
-        const size_t smem = sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
-        if (W == 8) launch_fast<8, 1>(a, norm, layout, grid, threads, smem, ctx->stream);
-        else if (W == 16) launch_fast<16, 1>(a, norm, layout, grid, threads, smem, ctx->stream);
-        else if (VPL == 1) launch_fast<32, 1>(a, norm, layout, grid, threads, smem, ctx->stream);
-        else if (VPL == 2) launch_fast<32, 2>(a, norm, layout, grid, threads, smem, ctx->stream);
-        else launch_fast<32, 4>(a, norm, layout, grid, threads, smem, ctx->stream);
+        const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
+        bool ok = false;
+        if (W == 8 && VPL == 4) ok = launch_fast<8, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 16 && VPL == 4) ok = launch_fast<16, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 32 && VPL == 4) ok = launch_fast<32, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 8 && VPL == 2) ok = launch_fast<8, 2>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 8 && VPL == 1) ok = launch_fast<8, 1>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 32 && VPL == 2) ok = launch_fast<32, 2>(a, norm, mode, grid, threads, smem, ctx->stream);
+        else if (W == 32 && VPL == 1) ok = launch_fast<32, 1>(a, norm, mode, grid, threads, smem, ctx->stream);
+        if (!ok) return agn_fail(ctx, AGN_EINVAL, "%s: internal dispatch error (W=%d VPL=%d mode=%d)", name, W, VPL, mode);
         AGN_LAUNCHED(ctx, name);
     } else {
         int threads = n_heads >= 8 ? 256 : 32 * n_heads;

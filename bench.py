@@ -294,6 +294,23 @@ def run_ours(args, cfg):
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1e3 / reps
         per_op[name] = {"us": round(us, 2), "gbs": round(ab[name] / (us * 1e-6) / 1e9, 1)}
+        # calibration: a plain device copy (torch copy_, what the measured peak was taken with)
+        # moving the same number of bytes, timed the same way: the speed of light at this size
+        n_el = ab[name] // 8
+        srcs = [torch.empty(n_el, device=dev) for _ in range(NSETS)]
+        dsts = [torch.empty(n_el, device=dev) for _ in range(NSETS)]
+        for i in range(4):
+            dsts[i % NSETS].copy_(srcs[i % NSETS])
+        torch.cuda.synchronize()
+        a.record(stream)
+        for i in range(reps):
+            dsts[i % NSETS].copy_(srcs[i % NSETS])
+        b.record(stream)
+        torch.cuda.synchronize()
+        cus = a.elapsed_time(b) * 1e3 / reps
+        per_op[name]["copy_same_bytes_us"] = round(cus, 2)
+        per_op[name]["frac_of_copy_same_bytes"] = round(cus / us, 3)
+        del srcs, dsts
     clocks = sampler.stop() if sampler else None
 
     # ---- end to end through the public API with HOST buffers: pinned inputs -> device ->
