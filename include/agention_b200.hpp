@@ -1,0 +1,166 @@
+// C++ host-side mirror of the reference's GPU operator surface over the C ABI.
+//
+// `agn::CudaBackend` has the method names and argument meaning of the reference's
+// `WgpuBackend::launch_*` family (src/ops/wgpu_backend/resident.rs:187-443), extended from
+// one token vector per call to T token rows per call, plus `dequant_row`
+// (`WeightMap::dequant_row`, src/model/mod.rs:343-348).  Header-only; link libagention_b200.so.
+// Errors (the reference's `GgufError::BackendError`, src/error.rs:37-38) are thrown as
+// `agn::BackendError`.  There is no CPU fallback: construction throws without a CUDA device.
+#pragma once
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "agention_b200.h"
+
+namespace agn {
+
+class BackendError : public std::runtime_error {
+  public:
+    BackendError(int32_t status, const std::string &msg) : std::runtime_error(msg), status(status) {}
+    int32_t status;
+};
+
+class CudaBackend;
+
+// A device allocation owned by a backend (the role of a cubecl `Handle`).
+class DeviceBuffer {
+  public:
+    DeviceBuffer() = default;
+    DeviceBuffer(agn_ctx *ctx, void *p, size_t n) : ctx_(ctx), ptr_(p), bytes_(n) {}
+    DeviceBuffer(const DeviceBuffer &) = delete;
+    DeviceBuffer &operator=(const DeviceBuffer &) = delete;
+    DeviceBuffer(DeviceBuffer &&o) noexcept { *this = std::move(o); }
+    DeviceBuffer &operator=(DeviceBuffer &&o) noexcept {
+        if (this != &o) {
+            release();
+            ctx_ = o.ctx_; ptr_ = o.ptr_; bytes_ = o.bytes_;
+            o.ptr_ = nullptr; o.bytes_ = 0;
+        }
+        return *this;
+    }
+    ~DeviceBuffer() { release(); }
+    template <typename T> T *as() const { return static_cast<T *>(ptr_); }
+    void *ptr() const { return ptr_; }
+    size_t bytes() const { return bytes_; }
+
+  private:
+    void release() {
+        if (ptr_) agn_free(ctx_, ptr_);
+        ptr_ = nullptr;
+    }
+    agn_ctx *ctx_ = nullptr;
+    void *ptr_ = nullptr;
+    size_t bytes_ = 0;
+};
+
+class CudaBackend {
+  public:
+    // `create_backend(BackendPreference::Cuda)` (src/ops/backend_select.rs:60-108), without the CPU fallback.
+    explicit CudaBackend(int device = 0) {
+        const int32_t st = agn_ctx_create(device, &ctx_);
+        if (st != AGN_OK) throw BackendError(st, std::string("no usable CUDA device: ") + agn_status_string(st));
+    }
+    CudaBackend(const CudaBackend &) = delete;
+    CudaBackend &operator=(const CudaBackend &) = delete;
+    ~CudaBackend() { if (ctx_) agn_ctx_destroy(ctx_); }
+
+    const char *name() const { return agn_backend_name(); }  // Backend::name, src/ops/mod.rs:99
+    agn_ctx *ctx() const { return ctx_; }
+    uint64_t launch_count() const { return agn_ctx_launch_count(ctx_); }
+    void sync() { check(agn_sync(ctx_)); }
+
+    DeviceBuffer empty(size_t bytes) {  // client.empty, resident.rs:195
+        void *p = nullptr;
+        check(agn_malloc(ctx_, bytes ? bytes : 1, &p));
+        return DeviceBuffer(ctx_, p, bytes);
+    }
+    template <typename T> DeviceBuffer upload(const std::vector<T> &host) {  // upload_act, resident.rs:673-690
+        DeviceBuffer b = empty(host.size() * sizeof(T));
+        check(agn_memcpy_h2d(ctx_, b.ptr(), host.data(), host.size() * sizeof(T)));
+        sync();
+        return b;
+    }
+    template <typename T> std::vector<T> read(const DeviceBuffer &b, size_t count) {  // read_handle, resident.rs:696-699
+        std::vector<T> host(count);
+        check(agn_memcpy_d2h(ctx_, host.data(), b.ptr(), count * sizeof(T)));
+        sync();
+        return host;
+    }
+
+    // launch_rms_norm(x, weight, len, eps) -> Handle   (resident.rs:213-235), T rows
+    DeviceBuffer launch_rms_norm(const float *x, const float *w, int64_t T, int64_t H, float eps) {
+        DeviceBuffer out = empty(sizeof(float) * T * H);
+        check(agn_rms_norm_f32(ctx_, x, w, out.as<float>(), T, H, eps));
+        return out;
+    }
+    // launch_add_residual_rms_norm(..) -> (new_x, normed)   (resident.rs:240-266)
+    std::pair<DeviceBuffer, DeviceBuffer> launch_add_residual_rms_norm(const float *x, const float *delta, const float *w,
+                                                                        int64_t T, int64_t H, float eps) {
+        DeviceBuffer nx = empty(sizeof(float) * T * H), nm = empty(sizeof(float) * T * H);
+        check(agn_add_residual_rms_norm_f32(ctx_, x, delta, w, nx.as<float>(), nm.as<float>(), T, H, eps));
+        return {std::move(nx), std::move(nm)};
+    }
+    // launch_rope(handle, n_heads, head_dim, n_rot, pos, theta) in place   (resident.rs:326-353)
+    void launch_rope(float *x, int64_t T, int n_heads, int head_dim, int n_rot, const int32_t *pos, int pos_start,
+                     float theta, float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {
+        check(agn_rope_f32(ctx_, x, T, n_heads, head_dim, n_rot, pos, pos_start, theta, freq_scale, layout));
+    }
+    // CPU rope(q, k, pos)   (src/model/llama/cpu_path.rs:99-133): both buffers, one launch
+    void launch_rope_qk(float *q, float *k, int64_t T, int n_q, int n_kv, int head_dim, int n_rot, const int32_t *pos,
+                        int pos_start, float theta, float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {
+        check(agn_rope_qk_f32(ctx_, q, k, T, n_q, n_kv, head_dim, n_rot, pos, pos_start, theta, freq_scale, layout));
+    }
+    // launch_qk_norm_rope(handle, weight, n_heads, head_dim, eps, n_rot, pos, theta)   (resident.rs:414-443)
+    void launch_qk_norm_rope(float *x, const float *w, int64_t T, int n_heads, int head_dim, float eps, int n_rot,
+                             const int32_t *pos, int pos_start, float theta, float freq_scale = 1.0f,
+                             int layout = AGN_ROPE_NEOX) {
+        check(agn_qk_norm_rope_f32(ctx_, x, w, T, n_heads, head_dim, eps, n_rot, pos, pos_start, theta, freq_scale, layout));
+    }
+    void launch_qk_norm_rope_qk(float *q, float *k, const float *wq, const float *wk, int64_t T, int n_q, int n_kv,
+                                int head_dim, float eps, int n_rot, const int32_t *pos, int pos_start, float theta,
+                                float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {
+        check(agn_qk_norm_rope_qk_f32(ctx_, q, k, wq, wk, T, n_q, n_kv, head_dim, eps, n_rot, pos, pos_start, theta,
+                                      freq_scale, layout));
+    }
+    // launch_silu_mul(gate, up, len) -> Handle   (resident.rs:187-209)
+    DeviceBuffer launch_silu_mul(const float *gate, const float *up, int64_t n) {
+        DeviceBuffer out = empty(sizeof(float) * n);
+        check(agn_silu_mul_f32(ctx_, gate, up, out.as<float>(), n));
+        return out;
+    }
+    // softmax step of launch_attention   (resident.rs:551-565; cpu_path.rs:175-183), normalised
+    DeviceBuffer launch_softmax_rows(const float *scores, int64_t n_rows, int64_t row_len, const int32_t *n_valid,
+                                     int causal_period = 0, int causal_offset = 0) {
+        DeviceBuffer out = empty(sizeof(float) * n_rows * row_len);
+        check(agn_softmax_rows_f32(ctx_, scores, out.as<float>(), n_rows, row_len, row_len, n_valid, causal_period,
+                                   causal_offset));
+        return out;
+    }
+    // embedding loop of run_batch   (cpu_path.rs:865-868)
+    DeviceBuffer get_rows(int dtype, const void *table, size_t table_bytes, int64_t n_rows, int64_t row_len,
+                          const uint32_t *ids, int64_t T) {
+        DeviceBuffer out = empty(sizeof(float) * T * row_len);
+        check(agn_get_rows_f32(ctx_, dtype, table, table_bytes, n_rows, row_len, ids, T, out.as<float>()));
+        return out;
+    }
+    // WeightMap::dequant_row(name, row) -> Result<Vec<f32>>   (src/model/mod.rs:343-348)
+    std::vector<float> dequant_row(int dtype, const void *table, size_t table_bytes, int64_t n_rows, int64_t row_len,
+                                   uint32_t row) {
+        DeviceBuffer id = upload(std::vector<uint32_t>{row});
+        DeviceBuffer out = get_rows(dtype, table, table_bytes, n_rows, row_len, id.as<uint32_t>(), 1);
+        return read<float>(out, (size_t)row_len);  // sync inside throws on an out-of-range row
+    }
+
+    void check(int32_t st) const {
+        if (st != AGN_OK) throw BackendError(st, agn_last_error(ctx_));
+    }
+
+  private:
+    agn_ctx *ctx_ = nullptr;
+};
+
+}  // namespace agn

@@ -1,0 +1,133 @@
+// C++ host test of the drop-in boundary: drives agn::CudaBackend (include/agention_b200.hpp)
+// the way the reference's model code drives WgpuBackend::launch_*, and checks every result
+// against the CPU oracle (oracle/cpu_ref.h, the checker only).  Exit code 0 = all parity
+// checks passed.  Built and run by tests/test_gpu_cpp_host.py.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <random>
+#include <vector>
+
+#include "agention_b200.hpp"
+#include "cpu_ref.h"
+
+static int failures = 0;
+
+static double rel_to_row_scale(const std::vector<float> &got, const std::vector<float> &ref, size_t row_len) {
+    double worst = 0.0;
+    for (size_t r = 0; r * row_len < ref.size(); r++) {
+        double scale = 1e-30;
+        for (size_t i = 0; i < row_len; i++) scale = std::fmax(scale, std::fabs((double)ref[r * row_len + i]));
+        for (size_t i = 0; i < row_len; i++)
+            worst = std::fmax(worst, std::fabs((double)got[r * row_len + i] - (double)ref[r * row_len + i]) / scale);
+    }
+    return worst;
+}
+
+static void expect(bool ok, const char *what, double v = 0.0) {
+    std::printf("%-28s %s (%.3g)\n", what, ok ? "ok" : "FAIL", v);
+    if (!ok) failures++;
+}
+
+int main() {
+    const double TOL = 1e-5;
+    const int64_t T = 48, H = 3584, hd = 128, nq = 28, nkv = 4, I = 4096, vocab = 512;
+    std::mt19937 rng(20261125);
+    std::normal_distribution<float> N01(0.f, 1.f);
+    auto randn = [&](size_t n) { std::vector<float> v(n); for (auto &x : v) x = N01(rng); return v; };
+    auto weight = [&](size_t n) { std::vector<float> v(n); for (auto &x : v) x = 1.f + 0.02f * N01(rng); return v; };
+
+    agn::CudaBackend be(0);
+    std::printf("backend: %s\n", be.name());
+
+    {  // rms_norm
+        auto x = randn(T * H), w = weight(H);
+        std::vector<float> ref(T * H);
+        orc_rms_norm_rows(x.data(), w.data(), ref.data(), T, H, 1e-6f, 1);
+        auto dx = be.upload(x), dw = be.upload(w);
+        auto out = be.launch_rms_norm(dx.as<float>(), dw.as<float>(), T, H, 1e-6f);
+        double e = rel_to_row_scale(be.read<float>(out, T * H), ref, H);
+        expect(e <= TOL, "launch_rms_norm", e);
+    }
+    {  // rope on Q and K, then fused norm->rope
+        auto q = randn(T * nq * hd), k = randn(T * nkv * hd), wq = weight(hd);
+        std::vector<int32_t> pos(T);
+        for (int64_t t = 0; t < T; t++) pos[t] = (int32_t)((t * 7919) % 32768);
+        auto rq = q, rk = k;
+        orc_rope_rows(rq.data(), T, nq, hd, hd, pos.data(), 1e6f, 1.f, ORC_ROPE_NEOX, 1);
+        orc_rope_rows(rk.data(), T, nkv, hd, hd, pos.data(), 1e6f, 1.f, ORC_ROPE_NEOX, 1);
+        auto dq = be.upload(q), dk = be.upload(k);
+        auto dp = be.upload(pos);
+        be.launch_rope_qk(dq.as<float>(), dk.as<float>(), T, nq, nkv, hd, hd, dp.as<int32_t>(), 0, 1e6f);
+        double e = std::fmax(rel_to_row_scale(be.read<float>(dq, q.size()), rq, nq * hd),
+                             rel_to_row_scale(be.read<float>(dk, k.size()), rk, nkv * hd));
+        expect(e <= TOL, "launch_rope_qk", e);
+        auto rn = q;
+        orc_qk_norm_rope_rows(rn.data(), wq.data(), T, nq, hd, 1e-6f, hd, pos.data(), 1e6f, 1.f, ORC_ROPE_NEOX, 1);
+        auto dn = be.upload(q);
+        auto dwq = be.upload(wq);
+        be.launch_qk_norm_rope(dn.as<float>(), dwq.as<float>(), T, nq, hd, 1e-6f, hd, dp.as<int32_t>(), 0, 1e6f);
+        e = rel_to_row_scale(be.read<float>(dn, q.size()), rn, nq * hd);
+        expect(e <= TOL, "launch_qk_norm_rope", e);
+    }
+    {  // silu*mul
+        auto g = randn(T * I), u = randn(T * I);
+        std::vector<float> ref(T * I);
+        orc_silu_mul(g.data(), u.data(), ref.data(), T * I, 1);
+        auto dg = be.upload(g), du = be.upload(u);
+        auto out = be.launch_silu_mul(dg.as<float>(), du.as<float>(), T * I);
+        double e = rel_to_row_scale(be.read<float>(out, T * I), ref, I);
+        expect(e <= TOL, "launch_silu_mul", e);
+    }
+    {  // causal softmax
+        const int64_t L = 256, R = 2 * L;
+        auto s = randn(R * L);
+        for (auto &x : s) x *= 2.f;
+        std::vector<int32_t> nv(R);
+        for (int64_t r = 0; r < R; r++) nv[r] = (int32_t)(r % L) + 1;
+        std::vector<float> ref(R * L);
+        orc_softmax_rows(s.data(), ref.data(), R, L, L, nv.data(), 1);
+        auto ds = be.upload(s);
+        auto out = be.launch_softmax_rows(ds.as<float>(), R, L, nullptr, (int)L, 0);
+        double e = rel_to_row_scale(be.read<float>(out, R * L), ref, L);
+        expect(e <= TOL, "launch_softmax_rows", e);
+    }
+    for (int dtype : {AGN_Q8_0, AGN_Q4_K, AGN_Q6_K}) {  // get_rows, bit-exact
+        const size_t rb = agn_type_size(dtype, H);
+        std::vector<uint8_t> table(vocab * rb);
+        for (auto &b : table) b = (uint8_t)(rng() & 0xff);
+        // keep the f16 scales finite: clear the top exponent bit of every 16-bit word that is a scale
+        const size_t bb = dtype == AGN_Q8_0 ? 34 : dtype == AGN_Q4_K ? 144 : 210;
+        for (size_t off = 0; off + bb <= table.size(); off += bb) {
+            if (dtype == AGN_Q8_0) table[off + 1] &= 0x3f;
+            if (dtype == AGN_Q4_K) { table[off + 1] &= 0x3f; table[off + 3] &= 0x3f; }
+            if (dtype == AGN_Q6_K) table[off + 209] &= 0x3f;
+        }
+        std::vector<uint32_t> ids(T);
+        for (auto &i : ids) i = rng() % vocab;
+        std::vector<float> ref(T * H);
+        int rc = orc_get_rows(dtype, table.data(), table.size(), vocab, H, ids.data(), T, ref.data(), 1);
+        auto dt = be.upload(table);
+        auto di = be.upload(ids);
+        auto out = be.get_rows(dtype, dt.ptr(), table.size(), vocab, H, di.as<uint32_t>(), T);
+        auto got = be.read<float>(out, T * H);
+        expect(rc == ORC_OK && std::memcmp(got.data(), ref.data(), got.size() * sizeof(float)) == 0,
+               dtype == AGN_Q8_0 ? "get_rows Q8_0 (bit-exact)" : dtype == AGN_Q4_K ? "get_rows Q4_K (bit-exact)" : "get_rows Q6_K (bit-exact)");
+        if (dtype == AGN_Q8_0) {
+            bool threw = false;
+            try { be.dequant_row(dtype, dt.ptr(), table.size(), vocab, H, (uint32_t)vocab); }
+            catch (const agn::BackendError &e) { threw = e.status == AGN_EOOB_ID; }
+            expect(threw, "dequant_row out of range");
+        }
+    }
+    {  // error behaviour: bad argument -> status + message, context still usable
+        bool threw = false;
+        auto d = be.empty(512);
+        try { be.launch_rope(d.as<float>(), 1, 1, 128, 130, nullptr, 0, 1e4f); }
+        catch (const agn::BackendError &e) { threw = e.status == AGN_EINVAL && std::strstr(e.what(), "n_rot") != nullptr; }
+        expect(threw, "EINVAL on n_rot > head_dim");
+        be.sync();
+    }
+    std::printf("kernels launched: %llu, failures: %d\n", (unsigned long long)be.launch_count(), failures);
+    return failures ? 1 : 0;
+}
