@@ -60,6 +60,15 @@ def algorithmic_bytes(cfg, T):
     }
 
 
+def silu_traffic_bytes(n_elements):
+    """DRAM bytes of one silu_mul launch, scaled from the ncu capture summarised in
+    profiles/silu_mul_vec4_qwen7b_rows1024.md (19,398,656 elements: dram read 155.2 MB = 8.00 B per
+    element, i.e. no re-reads; of the 4 B per element written, ~40 MB were still dirty in L2 when the
+    kernel ended).  Reads and writes scale with the element count; the dirty remainder does not."""
+    dirty_left = 40.5e6
+    return 8.0 * n_elements + max(4.0 * n_elements - dirty_left, 0.0)
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples while the GPU is under load."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -372,13 +381,7 @@ def run_ours(args, cfg):
             "ops": per_op, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk)},
         }
-        traffic = ROOT / "profiles" / "silu_mul_traffic.json"
-        if traffic.exists():
-            try:
-                tj = json.loads(traffic.read_text())
-                out["roofline"]["traffic"] = tj["dram_bytes_per_element"] * T * I
-            except Exception:
-                pass
+        out["roofline"]["traffic"] = silu_traffic_bytes(T * I)
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline(cfg)
         print(json.dumps(out))
