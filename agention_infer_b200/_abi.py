@@ -51,6 +51,8 @@ SIGNATURES = {
     "agn_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_router_top2_f32": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "agn_gather_rows_by_expert_noalloc_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, C.c_char_p,
+                                                     _sz]),
     "agn_type_size": (_sz, [_i32, _sz]),
 }
 

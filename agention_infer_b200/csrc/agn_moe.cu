@@ -16,6 +16,7 @@
 //   4. gather  : out[dst] = x[src_token[dst]], 128-bit streaming copies (bound by HBM:
 //                8 bytes per gathered element)
 #include <math.h>
+#include <stdarg.h>
 
 #include "agn_common.cuh"
 
@@ -200,4 +201,115 @@ extern "C" int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, c
                         ctx->scratch_bytes);
     return agn_gather_rows_by_expert_impl(ctx, x, idx, T, H, n_experts, out, offsets, src_token, src_slot,
                                           static_cast<int32_t *>(ctx->d_scratch));
+}
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of gather_rows_by_expert.
+//
+// Who needs it: a host that has handed the whole GPU to its own arena (an inference server
+// that sizes its KV cache to all free memory has nothing left for cudaMalloc to give out),
+// and a host that must not allocate inside its serving loop because cudaMalloc / cudaFree
+// stall every stream of the device.  Such a host cannot create an agn_ctx either: context
+// creation allocates the workspace this op normally uses.  This entry point therefore takes
+// no context and gets its scratch from a fixed array that is part of the loaded library.
+//
+// The array lives in every GPU that loads the library, from load until exit; its size is the
+// limit of the problem size (see AGN_NOALLOC_SCRATCH_BYTES).  All calls share it: it still
+// holds the previous call's counts when the next call starts, and two calls that run on the
+// GPU at the same time (different streams, no event between them) overwrite each other.
+#define AGN_NOALLOC_SCRATCH_BYTES (256 * 1024)
+#define AGN_NOALLOC_HEADER_BYTES 256  // word 0: "an expert index was out of range" flag
+static __device__ __align__(256) unsigned char g_noalloc_scratch[AGN_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mutex;
+void *g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES] = {};
+
+int32_t noalloc_fail(char *err, size_t err_len, int32_t status, const char *fmt, ...) {
+    if (err && err_len) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, err_len, fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+}  // namespace
+
+extern "C" int32_t agn_gather_rows_by_expert_noalloc_f32(void *cuda_stream, const float *x, const int32_t *idx, int64_t T,
+                                                         int64_t H, int32_t n_experts, float *out, int32_t *offsets,
+                                                         int32_t *src_token, int32_t *src_slot, char *err, size_t err_len) {
+    if (err && err_len) err[0] = '\0';
+    if (T < 0 || H <= 0 || n_experts < 1 || n_experts > MAX_EXPERTS)
+        return noalloc_fail(err, err_len, AGN_EINVAL, "gather_rows_by_expert_noalloc: T=%lld H=%lld n_experts=%d (need 1..%d)",
+                            (long long)T, (long long)H, n_experts, MAX_EXPERTS);
+    if (!offsets || (T > 0 && (!x || !idx || !out || !src_token || !src_slot)))
+        return noalloc_fail(err, err_len, AGN_EINVAL, "gather_rows_by_expert_noalloc: null pointer");
+    if (2 * T > 0x7fffffffLL) return noalloc_fail(err, err_len, AGN_EINVAL, "gather_rows_by_expert_noalloc: T too large");
+    const int64_t n_pairs = 2 * T;
+    const int64_t n_chunks = (n_pairs + CHUNK - 1) / CHUNK;
+    const size_t need = AGN_NOALLOC_HEADER_BYTES + (size_t)n_chunks * (size_t)n_experts * sizeof(int32_t);
+    if (need > AGN_NOALLOC_SCRATCH_BYTES)
+        return noalloc_fail(err, err_len, AGN_EINVAL,
+                            "gather_rows_by_expert_noalloc: T=%lld with %d experts needs %zu bytes of scratch, the built-in "
+                            "array holds %d (limit: ceil(2T/1024)*n_experts <= %d); use agn_gather_rows_by_expert_f32",
+                            (long long)T, n_experts, need, AGN_NOALLOC_SCRATCH_BYTES,
+                            (AGN_NOALLOC_SCRATCH_BYTES - AGN_NOALLOC_HEADER_BYTES) / 4);
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        (void)cudaGetLastError();
+        return noalloc_fail(err, err_len, AGN_ECUDA, "gather_rows_by_expert_noalloc: no current CUDA device (%s)",
+                            cudaGetErrorString(e));
+    }
+    // Set-up, once per device, with that device current: in host code the array's name is
+    // only a handle; the address kernels can use comes from cudaGetSymbolAddress.
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_dev_ptr[dev]) {
+            void *p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) {
+                (void)cudaGetLastError();
+                return noalloc_fail(err, err_len, AGN_ECUDA, "gather_rows_by_expert_noalloc: cudaGetSymbolAddress failed: %s",
+                                    cudaGetErrorString(e));
+            }
+            g_noalloc_dev_ptr[dev] = p;
+        }
+        scratch = g_noalloc_dev_ptr[dev];
+    }
+#define NOALLOC_CUDA(call)                                                                                              \
+    do {                                                                                                                \
+        cudaError_t _e = (call);                                                                                        \
+        if (_e != cudaSuccess) {                                                                                        \
+            (void)cudaGetLastError();                                                                                   \
+            return noalloc_fail(err, err_len, AGN_ECUDA, "gather_rows_by_expert_noalloc: %s failed: %s", #call,         \
+                                cudaGetErrorString(_e));                                                                \
+        }                                                                                                               \
+    } while (0)
+    if (T == 0) {
+        NOALLOC_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * (n_experts + 1), stream));
+        return AGN_OK;
+    }
+    uint32_t *flags = static_cast<uint32_t *>(scratch);
+    int32_t *counts = reinterpret_cast<int32_t *>(static_cast<unsigned char *>(scratch) + AGN_NOALLOC_HEADER_BYTES);
+    // What must start clean: the flag word (left over from an earlier call) and the slots of
+    // dropped pairs.  The counts need no clearing: the count kernel overwrites every entry
+    // that the scan and place kernels of this call read.
+    NOALLOC_CUDA(cudaMemsetAsync(flags, 0, AGN_NOALLOC_HEADER_BYTES, stream));
+    NOALLOC_CUDA(cudaMemsetAsync(src_token, 0xFF, sizeof(int32_t) * (size_t)n_pairs, stream));
+    expert_count_kernel<<<(unsigned)n_chunks, CHUNK, 0, stream>>>(idx, n_pairs, n_experts, counts, flags);
+    NOALLOC_CUDA(cudaPeekAtLastError());
+    expert_scan_kernel<<<1, MAX_EXPERTS, 0, stream>>>(counts, (int)n_chunks, n_experts, offsets);
+    NOALLOC_CUDA(cudaPeekAtLastError());
+    expert_place_kernel<<<(unsigned)n_chunks, CHUNK, 0, stream>>>(idx, n_pairs, n_experts, counts, src_token, src_slot);
+    NOALLOC_CUDA(cudaPeekAtLastError());
+    const int vec = (H % 4 == 0 && agn_aligned16(x) && agn_aligned16(out)) ? 1 : 0;
+    gather_rows_kernel<<<(unsigned)n_pairs, 256, 0, stream>>>(x, src_token, n_pairs, T, H, out, vec);
+    NOALLOC_CUDA(cudaPeekAtLastError());
+#undef NOALLOC_CUDA
+    return AGN_OK;
 }

@@ -207,6 +207,33 @@ AGN_API int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, cons
                                               int32_t *offsets, int32_t *src_token,
                                               int32_t *src_slot);
 
+/* Allocation-free variant of agn_gather_rows_by_expert_f32.  It has no counterpart in the
+ * reference.  It exists for hosts that cannot allocate device memory: one that has given the
+ * whole GPU to its own arena (nothing is left for cudaMalloc), or one that must not allocate
+ * in its serving loop because cudaMalloc / cudaFree stall all streams of the device.  Such a
+ * host cannot create an agn_ctx either (that allocates), so this call takes no context: it
+ * works on the CURRENT device, on `cuda_stream` (a cudaStream_t; NULL = the legacy default
+ * stream), and its scratch is a 256 KiB array built into the library and resident on every
+ * GPU that loads it until the process exits.  It calls no cudaMalloc, cudaFree or allocating
+ * library routine.
+ *   - Limit: 256 + ceil(2T / 1024) * n_experts * 4 bytes must fit in 256 KiB (8 experts:
+ *     T <= 4,189,184); larger problems are rejected with AGN_EINVAL and a message in `err`.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) and keeps it; make that first call outside any stream capture.
+ *   - All calls share the array and it keeps the previous call's contents; the call itself
+ *     clears what has to start at zero.  Two calls whose kernels can overlap on the GPU
+ *     (different streams without an event between them) race on it: serialise them.
+ *   - An expert index outside [0, n_experts) drops that pair: offsets[n_experts] is then
+ *     smaller than 2T and the unused tail of src_token is -1 (no status is raised, because
+ *     reading a flag back would need a synchronisation).
+ * Arguments and results are otherwise those of agn_gather_rows_by_expert_f32.  `err` (may be
+ * NULL) receives a message of at most err_len bytes when the status is not AGN_OK. */
+AGN_API int32_t agn_gather_rows_by_expert_noalloc_f32(void *cuda_stream, const float *x,
+                                                      const int32_t *idx, int64_t T, int64_t H,
+                                                      int32_t n_experts, float *out, int32_t *offsets,
+                                                      int32_t *src_token, int32_t *src_slot,
+                                                      char *err, size_t err_len);
+
 /* `GgmlType::type_size` (src/types.rs:164-168); 0 for a dtype without a kernel. */
 AGN_API size_t agn_type_size(int32_t dtype, size_t n);
 
