@@ -272,6 +272,56 @@ class CudaBackend:
         out = self.get_rows(dtype, table, table_bytes, n_rows, row_len, ids, 1)
         return self.read(out, np.float32, (row_len,))
 
+    # ------------------------------------------------- host-slice ops (activations in host memory)
+    # The arrays must stay alive and unmodified until sync(); pinned arrays (pinned()) make the
+    # transfers asynchronous.  Weights / tables are device buffers.
+    @staticmethod
+    def _h(a: np.ndarray, dtype) -> int:
+        if a.dtype != dtype or not a.flags["C_CONTIGUOUS"]:
+            raise ValueError(f"host array must be C-contiguous {np.dtype(dtype).name}")
+        return a.ctypes.data
+
+    def rms_norm_into(self, x: np.ndarray, w_dev, out: np.ndarray, eps: float) -> None:
+        """`rms_norm_into(x, weight, out)` (src/model/llama/cpu_path.rs:67-74) over the rows of host x [T, H]."""
+        T, H = x.shape
+        self._check(self._lib.agn_host_rms_norm_f32(self._ctx, self._h(x, np.float32), _ptr(w_dev),
+                                                    self._h(out, np.float32), T, H, eps))
+
+    def silu_mul_into(self, gate: np.ndarray, up: np.ndarray, out: np.ndarray) -> None:
+        """The batched silu-combine loop (cpu_path.rs:975-978) on host arrays; out may be gate."""
+        self._check(self._lib.agn_host_silu_mul_f32(self._ctx, self._h(gate, np.float32), self._h(up, np.float32),
+                                                    self._h(out, np.float32), gate.size))
+
+    def rope_host(self, q: np.ndarray, k: np.ndarray, n_q_heads: int, n_kv_heads: int, head_dim: int, n_rot: int,
+                  pos: Optional[np.ndarray], theta: float, freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX,
+                  pos_start: int = 0, wq_dev=None, wk_dev=None, eps: float = 0.0) -> None:
+        """`rope(q, k, pos)` per token (cpu_path.rs:896-906), in place on host q [T, nq*hd], k [T, nkv*hd];
+        with wq_dev / wk_dev the per-head QK-norm runs first (fused)."""
+        T = q.shape[0]
+        pp = None if pos is None else self._h(pos, np.int32)
+        if wq_dev is None and wk_dev is None:
+            st = self._lib.agn_host_rope_qk_f32(self._ctx, self._h(q, np.float32), self._h(k, np.float32), T, n_q_heads,
+                                                n_kv_heads, head_dim, n_rot, pp, pos_start, theta, freq_scale, layout)
+        else:
+            st = self._lib.agn_host_qk_norm_rope_qk_f32(self._ctx, self._h(q, np.float32), self._h(k, np.float32),
+                                                        _ptr(wq_dev), _ptr(wk_dev), T, n_q_heads, n_kv_heads, head_dim,
+                                                        eps, n_rot, pp, pos_start, theta, freq_scale, layout)
+        self._check(st)
+
+    def softmax_rows_into(self, scores: np.ndarray, out: np.ndarray, n_valid: Optional[np.ndarray] = None,
+                          causal_period: int = 0, causal_offset: int = 0) -> None:
+        """Row softmax (cpu_path.rs:175-183) on host rows [n_rows, row_len]."""
+        rows = scores.reshape(-1, scores.shape[-1])
+        nv = None if n_valid is None else self._h(n_valid, np.int32)
+        self._check(self._lib.agn_host_softmax_rows_f32(self._ctx, self._h(scores, np.float32), self._h(out, np.float32),
+                                                        rows.shape[0], rows.shape[1], nv, causal_period, causal_offset))
+
+    def get_rows_into(self, dtype: int, table_dev, table_bytes: int, n_rows: int, row_len: int, ids: np.ndarray,
+                      out: np.ndarray) -> None:
+        """The embedding loop (cpu_path.rs:865-868): host ids [T] -> host out [T, row_len]."""
+        self._check(self._lib.agn_host_get_rows_f32(self._ctx, dtype, _ptr(table_dev), table_bytes, n_rows, row_len,
+                                                    self._h(ids, np.uint32), ids.size, self._h(out, np.float32)))
+
     @staticmethod
     def type_size(dtype: int, n: int) -> int:
         """`GgmlType::type_size` (src/types.rs:164-168)."""

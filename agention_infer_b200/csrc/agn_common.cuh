@@ -18,6 +18,8 @@
 #define AGN_ROPE_MAX_HALF 512  // n_rot <= 1024
 #define AGN_SCRATCH_BYTES (1u << 20)
 
+struct agn_host_pipe;  // staging ring of the host-slice entry points (agn_host_ops.cu)
+
 struct agn_rope_slot {
     uint32_t theta_bits;
     int32_t n_rot;
@@ -35,6 +37,7 @@ struct agn_ctx {
     float *h_rope_denom;        // pinned staging, same shape
     void *d_scratch;            // workspace for ops that need one (gather_rows_by_expert)
     size_t scratch_bytes;
+    agn_host_pipe *host_pipe;   // created by the first host-slice call
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync
@@ -47,6 +50,7 @@ struct agn_event {
 };
 
 int32_t agn_fail(agn_ctx *ctx, int32_t status, const char *fmt, ...);
+void agn_host_pipe_destroy(agn_ctx *ctx);
 
 // Device pointer to the powf(theta, 2d/n_rot) table, d < n_rot/2 (built on the host
 // with libm the first time a (theta, n_rot) pair is seen).

@@ -53,6 +53,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->own_stream = nullptr;
     ctx->d_scratch = nullptr;
     ctx->scratch_bytes = 0;
+    ctx->host_pipe = nullptr;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -78,6 +79,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
 int32_t agn_ctx_destroy(agn_ctx *ctx) {
     if (!ctx) return AGN_EINVAL;
     cudaSetDevice(ctx->device);
+    agn_host_pipe_destroy(ctx);
     if (ctx->own_stream) {
         cudaStreamSynchronize(ctx->own_stream);
         cudaStreamDestroy(ctx->own_stream);

@@ -207,6 +207,41 @@ AGN_API int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, cons
                                               int32_t *offsets, int32_t *src_token,
                                               int32_t *src_slot);
 
+/* ------------------------------------------------------- host-slice entry points
+ * The same ops for callers whose activations live in HOST memory, as the reference's CPU
+ * path does (`rms_norm_into(x: &[f32], w, out: &mut [f32])`, src/model/llama/cpu_path.rs:67;
+ * `rope(q, k, pos)` :99; silu·mul :975-978; embedding loop :865-868).  `*_host` arguments are
+ * host pointers (pinned memory from agn_host_alloc makes the copies asynchronous), `*_dev`
+ * arguments are device pointers to weights / the embedding table, uploaded once.  Rows are
+ * streamed through a ring of device staging slots on three streams (upload, kernel,
+ * download) so both directions of the PCIe link stay busy.  The ring (96 MiB of device
+ * memory) is created by the first host-slice call on a context.  Calls return after
+ * enqueueing; host outputs are valid after agn_sync, and host inputs must not be modified
+ * before it.  Arguments otherwise as in the device-pointer entry points. */
+AGN_API int32_t agn_host_rms_norm_f32(agn_ctx *ctx, const float *x_host, const float *w_dev,
+                                      float *out_host, int64_t T, int64_t H, float eps);
+AGN_API int32_t agn_host_silu_mul_f32(agn_ctx *ctx, const float *gate_host, const float *up_host,
+                                      float *out_host, int64_t n);
+/* In place on q_host / k_host; pos_host may be NULL (positions pos_start + t). */
+AGN_API int32_t agn_host_rope_qk_f32(agn_ctx *ctx, float *q_host, float *k_host, int64_t T,
+                                     int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                     int32_t n_rot, const int32_t *pos_host, int32_t pos_start,
+                                     float theta, float freq_scale, int32_t layout);
+AGN_API int32_t agn_host_qk_norm_rope_qk_f32(agn_ctx *ctx, float *q_host, float *k_host,
+                                             const float *wq_dev, const float *wk_dev, int64_t T,
+                                             int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                             float eps, int32_t n_rot, const int32_t *pos_host,
+                                             int32_t pos_start, float theta, float freq_scale,
+                                             int32_t layout);
+/* Dense rows (row_stride == row_len). */
+AGN_API int32_t agn_host_softmax_rows_f32(agn_ctx *ctx, const float *in_host, float *out_host,
+                                          int64_t n_rows, int64_t row_len,
+                                          const int32_t *n_valid_host, int32_t causal_period,
+                                          int32_t causal_offset);
+AGN_API int32_t agn_host_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table_dev,
+                                      size_t table_bytes, int64_t n_rows, int64_t row_len,
+                                      const uint32_t *ids_host, int64_t T, float *out_host);
+
 /* Allocation-free variant of agn_gather_rows_by_expert_f32.  It has no counterpart in the
  * reference.  It exists for hosts that cannot allocate device memory: one that has given the
  * whole GPU to its own arena (nothing is left for cudaMalloc), or one that must not allocate
