@@ -92,6 +92,9 @@ class CudaBackend:
     def launch_count(self) -> int:
         return int(self._lib.agn_ctx_launch_count(self._ctx))
 
+    def set_option(self, name: str, value: int) -> None:
+        self._check(self._lib.agn_ctx_set_option(self._ctx, name.encode(), value))
+
     def set_stream(self, cuda_stream: Optional[int]) -> None:
         self._check(self._lib.agn_ctx_set_stream(self._ctx, cuda_stream))
 

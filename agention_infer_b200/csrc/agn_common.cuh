@@ -38,6 +38,7 @@ struct agn_ctx {
     void *d_scratch;            // workspace for ops that need one (gather_rows_by_expert)
     size_t scratch_bytes;
     agn_host_pipe *host_pipe;   // created by the first host-slice call
+    bool pdl;                   // launch kernels with programmatic stream serialization
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync
@@ -84,6 +85,30 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
 static inline bool agn_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  Every kernel of this library starts with
+// agn_pdl_prologue(): it lets the next kernel in the stream be scheduled onto SMs as this
+// grid's CTAs retire (hiding its launch latency), and it blocks until the previous grid has
+// completed and flushed its writes, before the first global access of this one.
+__device__ __forceinline__ void agn_pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline void agn_launch(agn_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in AGN_LAUNCHED
+}
 
 __device__ __forceinline__ float agn_warp_sum(float v) {
 #pragma unroll

@@ -54,6 +54,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->d_scratch = nullptr;
     ctx->scratch_bytes = 0;
     ctx->host_pipe = nullptr;
+    ctx->pdl = true;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -110,6 +111,16 @@ int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream) {
 }
 
 uint64_t agn_ctx_launch_count(agn_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
+    AGN_CHECK_CTX(ctx);
+    if (!name) return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: null name");
+    if (strcmp(name, "pdl") == 0) {
+        ctx->pdl = value != 0;
+        return AGN_OK;
+    }
+    return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: unknown option '%s'", name);
+}
 
 int32_t agn_malloc(agn_ctx *ctx, size_t bytes, void **dptr) {
     AGN_CHECK_CTX(ctx);

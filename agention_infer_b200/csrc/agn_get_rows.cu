@@ -129,6 +129,7 @@ template <int DTYPE, bool VEC_OUT>
 __global__ void __launch_bounds__(256)
 get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
                 const uint32_t *__restrict__ ids, float *__restrict__ out, uint32_t *flags) {
+    agn_pdl_prologue();
     extern __shared__ __align__(16) uint8_t stage[];
     const int64_t t = blockIdx.x;
     const uint32_t id = ids[t];
@@ -176,9 +177,9 @@ template <int DTYPE>
 void launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
                      size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, float *out) {
     if (vec)
-        get_rows_kernel<DTYPE, true><<<grid, threads, smem, ctx->stream>>>(table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
     else
-        get_rows_kernel<DTYPE, false><<<grid, threads, smem, ctx->stream>>>(table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
 }
 
 }  // namespace

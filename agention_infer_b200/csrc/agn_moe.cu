@@ -27,6 +27,7 @@ constexpr int MAX_EXPERTS = 64;
 
 __global__ void __launch_bounds__(256)
 router_top2_kernel(const float *__restrict__ logits, int64_t T, int E, int32_t *__restrict__ idx, float *__restrict__ w) {
+    agn_pdl_prologue();
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     const float *l = logits + t * E;
@@ -52,6 +53,7 @@ router_top2_kernel(const float *__restrict__ logits, int64_t T, int E, int32_t *
 __global__ void __launch_bounds__(CHUNK)
 expert_count_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, int32_t *__restrict__ chunk_counts,
                     uint32_t *flags) {
+    agn_pdl_prologue();
     __shared__ int cnt[MAX_EXPERTS];
     if (threadIdx.x < MAX_EXPERTS) cnt[threadIdx.x] = 0;
     __syncthreads();
@@ -68,6 +70,7 @@ expert_count_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, int
 // One CTA.  chunk_counts[c][e] -> exclusive position of (e, c) in expert-major order.
 __global__ void __launch_bounds__(MAX_EXPERTS)
 expert_scan_kernel(int32_t *__restrict__ chunk_counts, int n_chunks, int E, int32_t *__restrict__ offsets) {
+    agn_pdl_prologue();
     __shared__ int total[MAX_EXPERTS + 1];
     const int e = threadIdx.x;
     if (e < E) {
@@ -98,6 +101,7 @@ expert_scan_kernel(int32_t *__restrict__ chunk_counts, int n_chunks, int E, int3
 __global__ void __launch_bounds__(CHUNK)
 expert_place_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, const int32_t *__restrict__ chunk_base,
                     int32_t *__restrict__ src_token, int32_t *__restrict__ src_slot) {
+    agn_pdl_prologue();
     __shared__ int warp_cnt[CHUNK / 32][MAX_EXPERTS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < (CHUNK / 32) * MAX_EXPERTS; k += blockDim.x) (&warp_cnt[0][0])[k] = 0;
@@ -125,6 +129,7 @@ expert_place_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, con
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float *__restrict__ x, const int32_t *__restrict__ src_token, int64_t n_out, int64_t T,
                    int64_t H, float *__restrict__ out, int vec) {
+    agn_pdl_prologue();
     const int64_t r = blockIdx.x;
     const int64_t t = src_token[r];
     if (t < 0 || t >= T) return;
@@ -152,14 +157,14 @@ int32_t agn_gather_rows_by_expert_impl(agn_ctx *ctx, const float *x, const int32
     const int n_chunks = (int)((n_pairs + CHUNK - 1) / CHUNK);
     // pairs with an out-of-range expert are skipped by `place`; mark their slots as empty
     AGN_CUDA(ctx, cudaMemsetAsync(src_token, 0xFF, sizeof(int32_t) * (size_t)n_pairs, ctx->stream));
-    expert_count_kernel<<<n_chunks, CHUNK, 0, ctx->stream>>>(idx, n_pairs, n_experts, scratch, ctx->d_flags);
+    agn_launch(ctx, expert_count_kernel, dim3(n_chunks), dim3(CHUNK), 0, idx, n_pairs, n_experts, scratch, ctx->d_flags);
     AGN_LAUNCHED(ctx, "expert_count");
-    expert_scan_kernel<<<1, MAX_EXPERTS, 0, ctx->stream>>>(scratch, n_chunks, n_experts, offsets);
+    agn_launch(ctx, expert_scan_kernel, dim3(1), dim3(MAX_EXPERTS), 0, scratch, n_chunks, n_experts, offsets);
     AGN_LAUNCHED(ctx, "expert_scan");
-    expert_place_kernel<<<n_chunks, CHUNK, 0, ctx->stream>>>(idx, n_pairs, n_experts, scratch, src_token, src_slot);
+    agn_launch(ctx, expert_place_kernel, dim3(n_chunks), dim3(CHUNK), 0, idx, n_pairs, n_experts, scratch, src_token, src_slot);
     AGN_LAUNCHED(ctx, "expert_place");
     const int vec = (H % 4 == 0 && agn_aligned16(x) && agn_aligned16(out)) ? 1 : 0;
-    gather_rows_kernel<<<(unsigned)n_pairs, 256, 0, ctx->stream>>>(x, src_token, n_pairs, T, H, out, vec);
+    agn_launch(ctx, gather_rows_kernel, dim3((unsigned)n_pairs), dim3(256), 0, x, src_token, n_pairs, T, H, out, vec);
     AGN_LAUNCHED(ctx, "gather_rows");
     ctx->flags_dirty = true;
     return AGN_OK;
@@ -175,7 +180,7 @@ extern "C" int32_t agn_router_top2_f32(agn_ctx *ctx, const float *logits, int64_
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     const int64_t blocks = (T + 255) / 256;
     if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "router_top2: T too large");
-    router_top2_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(logits, T, n_experts, idx, w);
+    agn_launch(ctx, router_top2_kernel, dim3((unsigned)blocks), dim3(256), 0, logits, T, n_experts, idx, w);
     AGN_LAUNCHED(ctx, "router_top2");
     return AGN_OK;
 }

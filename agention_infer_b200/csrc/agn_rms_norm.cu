@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(1024)
 rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ delta,
                      const float4 *__restrict__ w, float4 *__restrict__ new_x,
                      float4 *__restrict__ out, int n4, float n_f, float eps) {
+    agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * n4;
     float4 v[VPT];
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(1024)
 rms_norm_rows_generic_kernel(const float *__restrict__ x, const float *__restrict__ delta,
                              const float *__restrict__ w, float *__restrict__ new_x,
                              float *__restrict__ out, int64_t H, float eps) {
+    agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * H;
     float ss = 0.0f;
@@ -99,7 +101,7 @@ rms_norm_rows_generic_kernel(const float *__restrict__ x, const float *__restric
 template <int VPT, bool RESIDUAL>
 void launch_vec(agn_ctx *ctx, const float *x, const float *delta, const float *w, float *new_x,
                 float *out, int64_t T, int n4, float eps, int threads) {
-    rms_norm_rows_kernel<VPT, RESIDUAL><<<(unsigned)T, threads, 0, ctx->stream>>>(
+    agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL>, dim3((unsigned)T), dim3(threads), 0, 
         reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
         reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
         reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
@@ -135,7 +137,7 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, cons
     } else {
         int threads = H >= 1024 ? 256 : (int)(((H + 31) / 32) * 32);
         if (threads > 256) threads = 256;
-        rms_norm_rows_generic_kernel<RESIDUAL><<<(unsigned)T, threads, 0, ctx->stream>>>(x, delta, w, new_x, out, H, eps);
+        agn_launch(ctx, rms_norm_rows_generic_kernel<RESIDUAL>, dim3((unsigned)T), dim3(threads), 0, x, delta, w, new_x, out, H, eps);
         AGN_LAUNCHED(ctx, name);
     }
     return AGN_OK;

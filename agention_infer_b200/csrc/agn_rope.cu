@@ -66,6 +66,7 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
 template <int W, int VPL, int MODE, bool NORM>
 __global__ void __launch_bounds__(256)
 rope_heads_kernel(const RopeArgs a) {
+    agn_pdl_prologue();
     constexpr int NS = VPL == 4 ? 2 : 4;  // head rows in flight per lane group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int half = a.n_rot >> 1;
@@ -221,6 +222,7 @@ rope_heads_kernel(const RopeArgs a) {
 template <int LAYOUT, bool NORM>
 __global__ void __launch_bounds__(256)
 rope_heads_generic_kernel(const RopeArgs a) {
+    agn_pdl_prologue();
     extern __shared__ __align__(16) float smem[];
     const int half = a.n_rot >> 1;
     float *s_cos = smem;
@@ -265,21 +267,21 @@ rope_heads_generic_kernel(const RopeArgs a) {
 }
 
 template <int W, int VPL, int MODE>
-void launch_fast3(const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem, cudaStream_t st) {
-    if (norm) rope_heads_kernel<W, VPL, MODE, true><<<grid, threads, smem, st>>>(a);
-    else rope_heads_kernel<W, VPL, MODE, false><<<grid, threads, smem, st>>>(a);
+void launch_fast3(agn_ctx *ctx, const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem) {
+    if (norm) agn_launch(ctx, rope_heads_kernel<W, VPL, MODE, true>, dim3(grid), dim3(threads), smem, a);
+    else agn_launch(ctx, rope_heads_kernel<W, VPL, MODE, false>, dim3(grid), dim3(threads), smem, a);
 }
 
 template <int W, int VPL>
-bool launch_fast(const RopeArgs &a, bool norm, int mode, unsigned grid, int threads, size_t smem, cudaStream_t st) {
+bool launch_fast(agn_ctx *ctx, const RopeArgs &a, bool norm, int mode, unsigned grid, int threads, size_t smem) {
     switch (mode) {
-    case MODE_NORMAL: launch_fast3<W, VPL, MODE_NORMAL>(a, norm, grid, threads, smem, st); return true;
-    case MODE_NEOX_SHFL: launch_fast3<W, VPL, MODE_NEOX_SHFL>(a, norm, grid, threads, smem, st); return true;
+    case MODE_NORMAL: launch_fast3<W, VPL, MODE_NORMAL>(ctx, a, norm, grid, threads, smem); return true;
+    case MODE_NEOX_SHFL: launch_fast3<W, VPL, MODE_NEOX_SHFL>(ctx, a, norm, grid, threads, smem); return true;
     case MODE_NEOX_K1:
-        if constexpr (VPL >= 2) { launch_fast3<W, VPL, MODE_NEOX_K1>(a, norm, grid, threads, smem, st); return true; }
+        if constexpr (VPL >= 2) { launch_fast3<W, VPL, MODE_NEOX_K1>(ctx, a, norm, grid, threads, smem); return true; }
         return false;
     case MODE_NEOX_K2:
-        if constexpr (VPL >= 4) { launch_fast3<W, VPL, MODE_NEOX_K2>(a, norm, grid, threads, smem, st); return true; }
+        if constexpr (VPL >= 4) { launch_fast3<W, VPL, MODE_NEOX_K2>(ctx, a, norm, grid, threads, smem); return true; }
         return false;
     }
     return false;
@@ -360,24 +362,24 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
         const unsigned grid = (unsigned)((T + tpc - 1) / tpc);
         const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
         bool ok = false;
-        if (W == 8 && VPL == 4) ok = launch_fast<8, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 16 && VPL == 4) ok = launch_fast<16, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 32 && VPL == 4) ok = launch_fast<32, 4>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 8 && VPL == 2) ok = launch_fast<8, 2>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 8 && VPL == 1) ok = launch_fast<8, 1>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 32 && VPL == 2) ok = launch_fast<32, 2>(a, norm, mode, grid, threads, smem, ctx->stream);
-        else if (W == 32 && VPL == 1) ok = launch_fast<32, 1>(a, norm, mode, grid, threads, smem, ctx->stream);
+        if (W == 8 && VPL == 4) ok = launch_fast<8, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 16 && VPL == 4) ok = launch_fast<16, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 4) ok = launch_fast<32, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 8 && VPL == 2) ok = launch_fast<8, 2>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 8 && VPL == 1) ok = launch_fast<8, 1>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 2) ok = launch_fast<32, 2>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 1) ok = launch_fast<32, 1>(ctx, a, norm, mode, grid, threads, smem);
         if (!ok) return agn_fail(ctx, AGN_EINVAL, "%s: internal dispatch error (W=%d VPL=%d mode=%d)", name, W, VPL, mode);
         AGN_LAUNCHED(ctx, name);
     } else {
         int threads = n_heads >= 8 ? 256 : 32 * n_heads;
         const size_t smem = sizeof(float) * 2 * (size_t)(half > 0 ? half : 1);
         if (layout == AGN_ROPE_NEOX) {
-            if (norm) rope_heads_generic_kernel<AGN_ROPE_NEOX, true><<<(unsigned)T, threads, smem, ctx->stream>>>(a);
-            else rope_heads_generic_kernel<AGN_ROPE_NEOX, false><<<(unsigned)T, threads, smem, ctx->stream>>>(a);
+            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NEOX, true>, dim3((unsigned)T), dim3(threads), smem, a);
+            else agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NEOX, false>, dim3((unsigned)T), dim3(threads), smem, a);
         } else {
-            if (norm) rope_heads_generic_kernel<AGN_ROPE_NORMAL, true><<<(unsigned)T, threads, smem, ctx->stream>>>(a);
-            else rope_heads_generic_kernel<AGN_ROPE_NORMAL, false><<<(unsigned)T, threads, smem, ctx->stream>>>(a);
+            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NORMAL, true>, dim3((unsigned)T), dim3(threads), smem, a);
+            else agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NORMAL, false>, dim3((unsigned)T), dim3(threads), smem, a);
         }
         AGN_LAUNCHED(ctx, name);
     }

@@ -29,6 +29,7 @@ template <int UNROLL>
 __global__ void __launch_bounds__(256)
 silu_mul_vec4_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ up,
                      float4 *__restrict__ out, int64_t n4) {
+    agn_pdl_prologue();
     const int64_t tile = (int64_t)blockIdx.x * (UNROLL * blockDim.x);
     float4 g[UNROLL], u[UNROLL];
 #pragma unroll
@@ -49,6 +50,7 @@ silu_mul_vec4_kernel(const float4 *__restrict__ gate, const float4 *__restrict__
 // Tail (n % 4 elements) and unaligned buffers.
 __global__ void silu_mul_scalar_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                                        float *__restrict__ out, int64_t begin, int64_t n) {
+    agn_pdl_prologue();
     const int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = silu_mul1(gate[i], up[i]);
 }
@@ -69,7 +71,7 @@ extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float
             const int64_t per_cta = (int64_t)THREADS * UNROLL;
             const int64_t blocks = (n4 + per_cta - 1) / per_cta;
             if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: n too large");
-            silu_mul_vec4_kernel<UNROLL><<<(unsigned)blocks, THREADS, 0, ctx->stream>>>(
+            agn_launch(ctx, silu_mul_vec4_kernel<UNROLL>, dim3((unsigned)blocks), dim3(THREADS), 0, 
                 reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(up),
                 reinterpret_cast<float4 *>(out), n4);
             AGN_LAUNCHED(ctx, "silu_mul_vec4");
@@ -80,7 +82,7 @@ extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float
         const int64_t rest = n - done;
         const int64_t blocks = (rest + THREADS - 1) / THREADS;
         if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: unaligned n too large");
-        silu_mul_scalar_kernel<<<(unsigned)blocks, THREADS, 0, ctx->stream>>>(gate, up, out, done, n);
+        agn_launch(ctx, silu_mul_scalar_kernel, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, done, n);
         AGN_LAUNCHED(ctx, "silu_mul_scalar");
     }
     return AGN_OK;

@@ -62,6 +62,7 @@ __device__ __forceinline__ float4 exp4(float4 v, float m, int e, int nv) {
 template <int VPL>
 __global__ void __launch_bounds__(256)
 softmax_warp_rows_kernel(const SoftmaxArgs a) {
+    agn_pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= a.n_rows) return;  // whole warp leaves together
@@ -99,6 +100,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
 template <int VPT>
 __global__ void __launch_bounds__(1024)
 softmax_block_rows_kernel(const SoftmaxArgs a) {
+    agn_pdl_prologue();
     __shared__ float red[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int64_t r = blockIdx.x;
@@ -144,6 +146,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
 
 __global__ void __launch_bounds__(256)
 softmax_generic_rows_kernel(const SoftmaxArgs a) {
+    agn_pdl_prologue();
     __shared__ float red[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int64_t r = blockIdx.x;
@@ -193,22 +196,22 @@ extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *ou
     if (vec_ok && n4 <= 256) {
         const int warps = 8;
         const unsigned grid = (unsigned)((n_rows + warps - 1) / warps);
-        if (n4 <= 32) softmax_warp_rows_kernel<1><<<grid, 32 * warps, 0, ctx->stream>>>(a);
-        else if (n4 <= 64) softmax_warp_rows_kernel<2><<<grid, 32 * warps, 0, ctx->stream>>>(a);
-        else if (n4 <= 128) softmax_warp_rows_kernel<4><<<grid, 32 * warps, 0, ctx->stream>>>(a);
-        else softmax_warp_rows_kernel<8><<<grid, 32 * warps, 0, ctx->stream>>>(a);
+        if (n4 <= 32) agn_launch(ctx, softmax_warp_rows_kernel<1>, dim3(grid), dim3(32 * warps), 0, a);
+        else if (n4 <= 64) agn_launch(ctx, softmax_warp_rows_kernel<2>, dim3(grid), dim3(32 * warps), 0, a);
+        else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<4>, dim3(grid), dim3(32 * warps), 0, a);
+        else agn_launch(ctx, softmax_warp_rows_kernel<8>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
     } else if (vec_ok && n4 <= 8192) {
         int vpt = 2;
         while (vpt < 8 && (n4 + vpt - 1) / vpt > 512) vpt *= 2;
         int threads = (int)((n4 + vpt - 1) / vpt);
         threads = ((threads + 31) / 32) * 32;
-        if (vpt == 2) softmax_block_rows_kernel<2><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
-        else if (vpt == 4) softmax_block_rows_kernel<4><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
-        else softmax_block_rows_kernel<8><<<(unsigned)n_rows, threads, 0, ctx->stream>>>(a);
+        if (vpt == 2) agn_launch(ctx, softmax_block_rows_kernel<2>, dim3((unsigned)n_rows), dim3(threads), 0, a);
+        else if (vpt == 4) agn_launch(ctx, softmax_block_rows_kernel<4>, dim3((unsigned)n_rows), dim3(threads), 0, a);
+        else agn_launch(ctx, softmax_block_rows_kernel<8>, dim3((unsigned)n_rows), dim3(threads), 0, a);
         AGN_LAUNCHED(ctx, "softmax_block_rows");
     } else {
-        softmax_generic_rows_kernel<<<(unsigned)n_rows, 256, 0, ctx->stream>>>(a);
+        agn_launch(ctx, softmax_generic_rows_kernel, dim3((unsigned)n_rows), dim3(256), 0, a);
         AGN_LAUNCHED(ctx, "softmax_generic_rows");
     }
     return AGN_OK;

@@ -236,6 +236,8 @@ def run_ours(args, cfg):
     assert stream.cuda_stream != 0
     be.set_stream(stream.cuda_stream)
     assert be.stream() == stream.cuda_stream
+    if args.no_pdl:
+        be.set_option("pdl", 0)
 
     T, H, hd, nq, nkv, I = cfg.T, cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
     ab = algorithmic_bytes(cfg, T)
@@ -445,6 +447,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (for comparison)")
     ap.add_argument("--tokens", type=int, default=None,
                     help="token rows per GPU (default: the configuration's 4096); smaller values are for profiling")
     args = ap.parse_args()

@@ -84,6 +84,10 @@ AGN_API const char *agn_status_string(int32_t status);
  * explicitly for those.) */
 AGN_API int32_t agn_ctx_set_stream(agn_ctx *ctx, void *cuda_stream);
 AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
+/* Options.  "pdl" (default 1): launch kernels with programmatic stream serialization, so
+ * that a kernel's launch latency overlaps the tail of the previous kernel of the stream
+ * (every kernel still waits for the previous one to complete before its first access). */
+AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value);
 /* Number of kernels this context has launched so far. */
 AGN_API uint64_t agn_ctx_launch_count(agn_ctx *ctx);
 
