@@ -39,6 +39,9 @@ struct agn_ctx {
     size_t scratch_bytes;
     agn_host_pipe *host_pipe;   // created by the first host-slice call
     bool pdl;                   // launch kernels with programmatic stream serialization
+    int tune_rms_vpt;           // 0 = automatic; 1/2/4/8 float4 per thread in rms_norm
+    int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
+    int tune_get_rows_threads;  // 0 = automatic
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync

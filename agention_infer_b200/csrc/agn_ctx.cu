@@ -55,6 +55,9 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->scratch_bytes = 0;
     ctx->host_pipe = nullptr;
     ctx->pdl = true;
+    ctx->tune_rms_vpt = 0;
+    ctx->tune_rms_recip = 1;
+    ctx->tune_get_rows_threads = 0;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -117,6 +120,18 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     if (!name) return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: null name");
     if (strcmp(name, "pdl") == 0) {
         ctx->pdl = value != 0;
+        return AGN_OK;
+    }
+    if (strcmp(name, "rms_vpt") == 0) {
+        ctx->tune_rms_vpt = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "get_rows_threads") == 0) {
+        ctx->tune_get_rows_threads = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "rms_recip") == 0) {
+        ctx->tune_rms_recip = value != 0;
         return AGN_OK;
     }
     return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: unknown option '%s'", name);

@@ -203,9 +203,12 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     const bool vec = row_len % 4 == 0 && agn_aligned16(out);
     const int n4 = (int)((row_len + 3) / 4);
-    int threads = ((n4 + 3) / 4 + 31) / 32 * 32;
+    // small CTAs (8 float4 per thread): more rows resident per SM hides the id -> row -> decode
+    // latency chain better than wide CTAs do (measured: 128 threads beat 224 by 15% at H=3584)
+    int threads = ((n4 + 7) / 8 + 31) / 32 * 32;
     if (threads < 64) threads = 64;
     if (threads > 256) threads = 256;
+    if (ctx->tune_get_rows_threads >= 32 && ctx->tune_get_rows_threads <= 256) threads = ctx->tune_get_rows_threads & ~31;
     const size_t smem = ((row_bytes + 15) / 16 + 2) * 16;
     const uint8_t *tb = static_cast<const uint8_t *>(table);
     if (smem > 48 * 1024) {

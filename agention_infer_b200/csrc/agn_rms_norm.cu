@@ -27,7 +27,7 @@ __device__ __forceinline__ float block_sum(float v, float *smem) {
     return total;
 }
 
-template <int VPT, bool RESIDUAL>
+template <int VPT, bool RESIDUAL, bool RECIP>
 __global__ void __launch_bounds__(1024)
 rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ delta,
                      const float4 *__restrict__ w, float4 *__restrict__ new_x,
@@ -58,16 +58,24 @@ rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ de
     for (int k = 0; k < VPT; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
     ss = block_sum(ss, red);
     const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps
+    const float inv = 1.0f / rms;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < n4) {
             const float4 ww = __ldg(w + i);
             float4 o;
-            o.x = ww.x * v[k].x / rms;
-            o.y = ww.y * v[k].y / rms;
-            o.z = ww.z * v[k].z / rms;
-            o.w = ww.w * v[k].w / rms;
+            if (RECIP) {
+                o.x = ww.x * v[k].x * inv;
+                o.y = ww.y * v[k].y * inv;
+                o.z = ww.z * v[k].z * inv;
+                o.w = ww.w * v[k].w * inv;
+            } else {
+                o.x = ww.x * v[k].x / rms;
+                o.y = ww.y * v[k].y / rms;
+                o.z = ww.z * v[k].z / rms;
+                o.w = ww.w * v[k].w / rms;
+            }
             agn_st_stream(out + row + i, o);
         }
     }
@@ -101,7 +109,13 @@ rms_norm_rows_generic_kernel(const float *__restrict__ x, const float *__restric
 template <int VPT, bool RESIDUAL>
 void launch_vec(agn_ctx *ctx, const float *x, const float *delta, const float *w, float *new_x,
                 float *out, int64_t T, int n4, float eps, int threads) {
-    agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL>, dim3((unsigned)T), dim3(threads), 0, 
+    if (ctx->tune_rms_recip)
+        agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL, true>, dim3((unsigned)T), dim3(threads), 0,
+                   reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
+                   reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
+                   reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
+    else
+    agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL, false>, dim3((unsigned)T), dim3(threads), 0, 
         reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
         reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
         reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
@@ -124,6 +138,10 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, cons
         // possible: more rows resident per SM and more loads in flight per thread.
         int vpt = 1;
         while (vpt < 8 && (n4 + vpt - 1) / vpt > 256) vpt *= 2;
+        if (ctx->tune_rms_vpt == 1 || ctx->tune_rms_vpt == 2 || ctx->tune_rms_vpt == 4 || ctx->tune_rms_vpt == 8) {
+            vpt = ctx->tune_rms_vpt;
+            while (vpt < 8 && (n4 + vpt - 1) / vpt > 1024) vpt *= 2;
+        }
         int threads = (n4 + vpt - 1) / vpt;
         threads = ((threads + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;

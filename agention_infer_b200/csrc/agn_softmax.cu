@@ -84,13 +84,14 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
         sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     }
     sum = agn_warp_sum(sum);
+    const float inv = 1.0f / sum;  // s / sum of the CPU path as s * (1/sum): <= 1 ulp apart
 #pragma unroll
     for (int k = 0; k < VPL; k++) {
         const int i = lane + 32 * k;
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) {
-                o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum;
+                o.x = v[k].x * inv; o.y = v[k].y * inv; o.z = v[k].z * inv; o.w = v[k].w * inv;
             }
             agn_st_stream(out + i, o);
         }
@@ -131,13 +132,14 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     __syncthreads();
     sum = 0.0f;
     for (int w = 0; w < nwarps; w++) sum += red[w];
+    const float inv = 1.0f / sum;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) {
-                o.x = v[k].x / sum; o.y = v[k].y / sum; o.z = v[k].z / sum; o.w = v[k].w / sum;
+                o.x = v[k].x * inv; o.y = v[k].y * inv; o.z = v[k].z * inv; o.w = v[k].w * inv;
             }
             agn_st_stream(out + i, o);
         }
