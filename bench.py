@@ -45,21 +45,6 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-def algorithmic_bytes(cfg, T):
-    """Bytes each op must move for T token rows (f32 activations, read + write)."""
-    from agention_infer_b200 import CudaBackend
-    H, hd, nq, nkv, I = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
-    row_bytes = CudaBackend.type_size(cfg.embd_dtype, H)
-    rope = 8 * T * (nq + nkv) * hd + 4 * T + 2 * cfg.n_rot
-    return {
-        "get_rows": T * row_bytes + 4 * T * H + 4 * T,
-        "rms_norm": 8 * T * H + 4 * H,
-        "rope_qk": rope,
-        "qk_norm_rope_qk": rope + 8 * hd,
-        "silu_mul": 12 * T * I,
-    }
-
-
 def silu_traffic_bytes(n_elements):
     """DRAM bytes of one silu_mul launch, scaled from the ncu capture summarised in
     profiles/silu_mul_vec4_qwen7b_rows1024.md (19,398,656 elements: dram read 155.2 MB = 8.00 B per
@@ -126,28 +111,55 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": float(max(power))}
 
 
+# ---------------------------------------------------------------------------- workloads
+
+WORKLOADS = {
+    # name: (config key, ops of one step, scaling)
+    "c2": ("c2", ["get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul"], "weak"),
+    "c1": ("c1", ["get_rows", "rms_norm", "rope_qk", "silu_mul", "softmax"], "weak"),
+    "c4": ("c4", ["get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul"], "strong"),
+    "c5": ("c5", ["get_rows", "rms_norm", "rope_qk", "router_top2", "gather_rows_by_expert", "silu_mul"], "strong"),
+}
+DTYPE_NAMES = {8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}
+
+
+def op_bytes(cfg, T, ops):
+    """Algorithmic bytes of each op of a step for T token rows (f32 activations, read + write)."""
+    from agention_infer_b200 import CudaBackend
+    H, hd, nq, nkv, I = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
+    rope = 8 * T * (nq + nkv) * hd + 4 * T + 2 * cfg.n_rot
+    L = T  # c1: causal scores [nq, T, T]
+    table = {
+        "get_rows": T * CudaBackend.type_size(cfg.embd_dtype, H) + 4 * T * H + 4 * T,
+        "rms_norm": 8 * T * H + 4 * H,
+        "rope_qk": rope,
+        "qk_norm_rope_qk": rope + 8 * hd,
+        "silu_mul": 12 * T * I * (2 if cfg.n_experts else 1),  # MoE: 2T routed rows
+        "softmax": 4 * (nq * L * (L + 1) // 2 + nq * L * L),
+        "router_top2": 4 * T * max(cfg.n_experts, 1) + 16 * T,
+        "gather_rows_by_expert": 2 * 2 * T * H * 4,
+    }
+    return {k: table[k] for k in ops}
+
+
 # ------------------------------------------------------------------- CPU (reference) arm
 
-def cpu_step(orc, cfg, data, rows, threads):
-    """One pass of the hot path over `rows` token rows on the host, oracle code."""
-    T = rows
-    orc.get_rows(cfg.embd_dtype, data["table"], cfg.vocab, cfg.hidden, data["ids"][:T], threads)
-    orc.rms_norm_rows(data["x"][:T], data["w"], cfg.eps, threads)
-    orc.rope_rows(data["q"][:T], cfg.n_q_heads, cfg.head_dim, cfg.n_rot, data["pos"][:T], cfg.theta, 1.0, 0, threads)
-    orc.rope_rows(data["k"][:T], cfg.n_kv_heads, cfg.head_dim, cfg.n_rot, data["pos"][:T], cfg.theta, 1.0, 0, threads)
-    orc.qk_norm_rope_rows(data["q"][:T], data["wq"], cfg.n_q_heads, cfg.head_dim, cfg.eps, cfg.n_rot, data["pos"][:T],
-                          cfg.theta, 1.0, 0, threads)
-    orc.qk_norm_rope_rows(data["k"][:T], data["wk"], cfg.n_kv_heads, cfg.head_dim, cfg.eps, cfg.n_rot,
-                          data["pos"][:T], cfg.theta, 1.0, 0, threads)
-    orc.silu_mul(data["gate"][:T], data["up"][:T], threads)
+def host_threads():
+    """All host threads this process may use (torchrun exports OMP_NUM_THREADS=1, so the OpenMP
+    default is not it)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
-def host_data(cfg, T, vocab_rows=None):
+def host_data(cfg, T, ops, vocab_rows=None):
     """Seeded host inputs of one batch.  A reduced number of table rows keeps the CPU arm's
     set-up short; ids are drawn inside it."""
     from agention_infer_b200 import synth
     vocab = cfg.vocab if vocab_rows is None else vocab_rows
     i = cfg.index
+    R = 2 * T if cfg.n_experts else T
     d = {
         "table": synth.quant_table(cfg.embd_dtype, vocab, cfg.hidden, cfg_index=i),
         "ids": synth.token_ids(i, T, vocab),
@@ -158,66 +170,113 @@ def host_data(cfg, T, vocab_rows=None):
         "wq": synth.norm_weight(i, "wq", cfg.head_dim),
         "wk": synth.norm_weight(i, "wk", cfg.head_dim),
         "pos": synth.positions(i, T, cfg.random_pos),
-        "gate": synth.activations(i, "gate", (T, cfg.ffn)),
-        "up": synth.activations(i, "up", (T, cfg.ffn)),
+        "gate": synth.activations(i, "gate", (R, cfg.ffn)),
+        "up": synth.activations(i, "up", (R, cfg.ffn)),
     }
+    if "softmax" in ops:
+        d["scores"] = synth.causal_scores(i, cfg.n_q_heads, T)
+        d["nv"] = np.tile(np.arange(1, T + 1, dtype=np.int32), cfg.n_q_heads)
+    if cfg.n_experts:
+        d["logits"] = synth.activations(i, "logits", (T, cfg.n_experts))
     return d, vocab
 
 
-def time_cpu(orc, cfg, data, rows, threads, reps):
+def cpu_step(orc, cfg, d, T, ops, threads):
+    """One pass of the hot path over T token rows on the host, oracle code."""
+    for op in ops:
+        if op == "get_rows":
+            orc.get_rows(cfg.embd_dtype, d["table"], cfg.vocab, cfg.hidden, d["ids"][:T], threads)
+        elif op == "rms_norm":
+            orc.rms_norm_rows(d["x"][:T], d["w"], cfg.eps, threads)
+        elif op == "rope_qk":
+            orc.rope_rows(d["q"][:T], cfg.n_q_heads, cfg.head_dim, cfg.n_rot, d["pos"][:T], cfg.theta, 1.0, 0, threads)
+            orc.rope_rows(d["k"][:T], cfg.n_kv_heads, cfg.head_dim, cfg.n_rot, d["pos"][:T], cfg.theta, 1.0, 0, threads)
+        elif op == "qk_norm_rope_qk":
+            orc.qk_norm_rope_rows(d["q"][:T], d["wq"], cfg.n_q_heads, cfg.head_dim, cfg.eps, cfg.n_rot, d["pos"][:T],
+                                  cfg.theta, 1.0, 0, threads)
+            orc.qk_norm_rope_rows(d["k"][:T], d["wk"], cfg.n_kv_heads, cfg.head_dim, cfg.eps, cfg.n_rot, d["pos"][:T],
+                                  cfg.theta, 1.0, 0, threads)
+        elif op == "silu_mul":
+            R = 2 * T if cfg.n_experts else T
+            orc.silu_mul(d["gate"][:R], d["up"][:R], threads)
+        elif op == "softmax":
+            orc.softmax_rows(d["scores"], d["nv"], threads)
+        elif op == "router_top2":
+            d["idx"], _ = orc.router_top2(d["logits"][:T])
+        elif op == "gather_rows_by_expert":
+            orc.gather_rows_by_expert(d["x"][:T], d["idx"], cfg.n_experts)
+
+
+def time_cpu(orc, cfg, data, rows, ops, threads, reps):
     best = float("inf")
     for _ in range(reps):
         t0 = time.perf_counter()
-        cpu_step(orc, cfg, data, rows, threads)
+        cpu_step(orc, cfg, data, rows, ops, threads)
         best = min(best, time.perf_counter() - t0)
     return best
 
 
-def run_reference(args, cfg):
+def cpu_sample(cfg, ops):
+    """Bounded sample of the workload for the host arm: at most 1024 token rows (all 512 for
+    the causal-softmax configuration, whose scores need whole heads) and a 16384-row table."""
+    from oracle import oracle as orc
+    rows = cfg.T if "softmax" in ops else min(cfg.T, 1024)
+    data, vocab = host_data(cfg, rows, ops, vocab_rows=min(cfg.vocab, 16384))
+    return orc, rows, data, dataclasses.replace(cfg, vocab=vocab, T=rows), vocab
+
+
+def run_reference(args, cfg, ops, wl):
     """The reference's CPU implementation of the path (C restatement; the Rust original cannot
     be built here), all host threads, on a bounded row sample of the same workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle as orc
-    threads = orc.max_threads()
-    rows = min(cfg.T, 1024)
-    data, vocab = host_data(cfg, rows, vocab_rows=min(cfg.vocab, 16384))
-
-    c = dataclasses.replace(cfg, vocab=vocab)  # same config with the reduced table
-    t1 = time_cpu(orc, c, data, rows, threads, 1)
+    orc, rows, data, c, vocab = cpu_sample(cfg, ops)
+    threads = host_threads()
+    t1 = time_cpu(orc, c, data, rows, ops, threads, 1)
     budget = 120.0
-    while rows > 64 and t1 * (args.steps + args.warmup) > budget:
+    while rows > 64 and "softmax" not in ops and t1 * (args.steps + args.warmup) > budget:
         rows //= 2
-        t1 = time_cpu(orc, c, data, rows, threads, 1)
+        t1 = time_cpu(orc, c, data, rows, ops, threads, 1)
     for _ in range(args.warmup):
-        cpu_step(orc, c, data, rows, threads)
+        cpu_step(orc, c, data, rows, ops, threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step(orc, c, data, rows, threads)
+        cpu_step(orc, c, data, rows, ops, threads)
     dt = (time.perf_counter() - t0) / args.steps
     value = rows / dt
     sample = f"{rows} of {cfg.T} token rows per step, table of {vocab} rows, OpenMP over rows"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": WORKLOADS[wl][2], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": cfg.name, "tokens_per_step": rows, "hidden": cfg.hidden, "ffn": cfg.ffn,
-                   "embedding": "Q4_K", "ops": ["get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul"]},
+                   "embedding": DTYPE_NAMES[cfg.embd_dtype], "ops": ops},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
+def cpu_baseline(cfg, ops):
+    """The oracle timed on this box's host cores on a bounded sample of the workload."""
+    orc, rows, data, c, vocab = cpu_sample(cfg, ops)
+    threads = host_threads()
+    cpu_step(orc, c, data, rows, ops, threads)
+    t_all = time_cpu(orc, c, data, rows, ops, threads, 5)
+    t_one = time_cpu(orc, c, data, rows, ops, 1, 2)
+    return {"value": rows / t_all, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{rows} of {cfg.T} token rows, table of {vocab} rows, best of 5, OpenMP over rows",
+            "single_thread_value": rows / t_one}
+
+
 # ------------------------------------------------------------------------- CUDA arm
 
-def run_ours(args, cfg):
+def setup_cuda(args):
     import torch
     import torch.distributed as dist
 
-    from agention_infer_b200 import CudaBackend, sharding, synth
-
+    from agention_infer_b200 import CudaBackend
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -238,9 +297,24 @@ def run_ours(args, cfg):
     assert be.stream() == stream.cuda_stream
     if args.no_pdl:
         be.set_option("pdl", 0)
+    return torch, dist, be, dev, stream, sampler, rank, world, local
 
-    T, H, hd, nq, nkv, I = cfg.T, cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
-    ab = algorithmic_bytes(cfg, T)
+
+def run_ours(args, cfg, ops_list, wl):
+    from agention_infer_b200 import sharding, synth
+    torch, dist, be, dev, stream, sampler, rank, world, local = setup_cuda(args)
+    scaling = WORKLOADS[wl][2]
+    if scaling == "strong":  # the configuration's rows are split over the ranks
+        r0, r1 = sharding.shard_rows(cfg.T, rank, world)
+        T = r1 - r0
+    else:                    # every rank runs the configuration's rows
+        T = cfg.T
+    T_total = cfg.T if scaling == "strong" else world * cfg.T
+    H, hd, nq, nkv, I, E = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn, cfg.n_experts
+    R = 2 * T if E else T  # rows of the SwiGLU operands (MoE: routed rows)
+    ab = op_bytes(cfg, T, ops_list)
+    step_bytes = sum(ab.values())
+    nsets = NSETS if step_bytes < 4e9 else 2
     table_h = synth.quant_table(cfg.embd_dtype, cfg.vocab, H, cfg_index=cfg.index)
     table = torch.from_numpy(table_h).to(dev)
     table_bytes = table_h.nbytes
@@ -249,30 +323,43 @@ def run_ours(args, cfg):
     wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
     pos = torch.from_numpy(synth.positions(cfg.index, T, cfg.random_pos)).to(dev)
     gen = torch.Generator(device=dev); gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index + rank)
+    rn = lambda *shape: torch.randn(*shape, device=dev, generator=gen)
     sets = []
-    for s in range(NSETS):
+    for s in range(nsets):
         ids = torch.from_numpy(synth.token_ids(cfg.index, T, cfg.vocab, salt=1 + rank * NSETS + s).astype(np.int32)).to(dev)
-        sets.append({
-            "ids": ids, "emb": torch.empty(T, H, device=dev),
-            "x": torch.randn(T, H, device=dev, generator=gen), "xn": torch.empty(T, H, device=dev),
-            "q": torch.randn(T, nq * hd, device=dev, generator=gen), "k": torch.randn(T, nkv * hd, device=dev, generator=gen),
-            "q2": torch.randn(T, nq * hd, device=dev, generator=gen), "k2": torch.randn(T, nkv * hd, device=dev, generator=gen),
-            "gate": torch.randn(T, I, device=dev, generator=gen), "up": torch.randn(T, I, device=dev, generator=gen),
-            "act": torch.empty(T, I, device=dev),
-        })
+        b = {"ids": ids, "emb": torch.empty(T, H, device=dev), "x": rn(T, H), "xn": torch.empty(T, H, device=dev),
+             "q": rn(T, nq * hd), "k": rn(T, nkv * hd), "gate": rn(R, I), "up": rn(R, I),
+             "act": torch.empty(R, I, device=dev)}
+        if "qk_norm_rope_qk" in ops_list:
+            b.update(q2=rn(T, nq * hd), k2=rn(T, nkv * hd))
+        if "softmax" in ops_list:
+            b.update(scores=rn(nq, T, T) * 2.0, probs=torch.empty(nq, T, T, device=dev))
+        if E:
+            b.update(logits=rn(T, E), ridx=torch.empty(T, 2, dtype=torch.int32, device=dev),
+                     rw=torch.empty(T, 2, device=dev), gx=torch.empty(2 * T, H, device=dev),
+                     goff=torch.empty(E + 1, dtype=torch.int32, device=dev),
+                     gtok=torch.empty(2 * T, dtype=torch.int32, device=dev),
+                     gslot=torch.empty(2 * T, dtype=torch.int32, device=dev))
+        sets.append(b)
 
-    ops = {
+    all_ops = {
         "get_rows": lambda b: be.get_rows(cfg.embd_dtype, table, table_bytes, cfg.vocab, H, b["ids"], T, out=b["emb"]),
         "rms_norm": lambda b: be.launch_rms_norm(b["x"], w, T, H, cfg.eps, out=b["xn"]),
         "rope_qk": lambda b: be.launch_rope_qk(b["q"], b["k"], T, nq, nkv, hd, cfg.n_rot, pos, cfg.theta),
         "qk_norm_rope_qk": lambda b: be.launch_qk_norm_rope_qk(b["q2"], b["k2"], wq, wk, T, nq, nkv, hd, cfg.eps,
                                                                cfg.n_rot, pos, cfg.theta),
-        "silu_mul": lambda b: be.launch_silu_mul(b["gate"], b["up"], T * I, out=b["act"]),
+        "silu_mul": lambda b: be.launch_silu_mul(b["gate"], b["up"], R * I, out=b["act"]),
+        "softmax": lambda b: be.launch_softmax_rows(b["scores"], nq * T, T, out=b["probs"], causal_period=T),
+        "router_top2": lambda b: be.router_top2(b["logits"], T, E, idx=b["ridx"], w=b["rw"]),
+        "gather_rows_by_expert": lambda b: be.gather_rows_by_expert(b["x"], b["ridx"], T, H, E, out=b["gx"],
+                                                                    offsets=b["goff"], src_token=b["gtok"],
+                                                                    src_slot=b["gslot"]),
     }
+    ops = {k: all_ops[k] for k in ops_list}
     order = list(ops)
 
     def step(i, silu_events=None):
-        b = sets[i % NSETS]
+        b = sets[i % nsets]
         for name in order:
             if silu_events is not None and name == "silu_mul":
                 e0, e1 = silu_events
@@ -291,8 +378,8 @@ def run_ours(args, cfg):
         sampler.mark_load(True)
     t_w = time.perf_counter()
     n_warm = 0
-    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_w < 0.6:
-        for _ in range(10):
+    while n_warm < max(args.warmup, 3) or time.perf_counter() - t_w < args.warm_seconds:
+        for _ in range(5):
             step(n_warm); n_warm += 1
         torch.cuda.synchronize()
     barrier()
@@ -310,34 +397,34 @@ def run_ours(args, cfg):
     elapsed_ms = sharding.max_over_ranks(start.elapsed_time(stop))
     silu_ms = float(np.mean([a.elapsed_time(b) for a, b in silu_ev]))
     ms_per_step = elapsed_ms / args.steps
-    value = world * T / (ms_per_step * 1e-3)
+    value = T_total / (ms_per_step * 1e-3)
 
     # ---- per-op device time, each op alone, rotating buffer sets (inputs never L2-resident)
     per_op = {}
-    reps = 40
+    reps = 40 if step_bytes < 4e9 else 10
     for name in order:
         for i in range(4):
-            ops[name](sets[i % NSETS])
+            ops[name](sets[i % nsets])
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
         for i in range(reps):
-            ops[name](sets[i % NSETS])
+            ops[name](sets[i % nsets])
         b.record(stream)
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1e3 / reps
         per_op[name] = {"us": round(us, 2), "gbs": round(ab[name] / (us * 1e-6) / 1e9, 1)}
         # calibration: a plain device copy (torch copy_, what the measured peak was taken with)
         # moving the same number of bytes, timed the same way: the speed of light at this size
-        n_el = ab[name] // 8
-        srcs = [torch.empty(n_el, device=dev) for _ in range(NSETS)]
-        dsts = [torch.empty(n_el, device=dev) for _ in range(NSETS)]
+        n_el = max(ab[name] // 8, 1)
+        srcs = [torch.empty(n_el, device=dev) for _ in range(nsets)]
+        dsts = [torch.empty(n_el, device=dev) for _ in range(nsets)]
         for i in range(4):
-            dsts[i % NSETS].copy_(srcs[i % NSETS])
+            dsts[i % nsets].copy_(srcs[i % nsets])
         torch.cuda.synchronize()
         a.record(stream)
         for i in range(reps):
-            dsts[i % NSETS].copy_(srcs[i % NSETS])
+            dsts[i % nsets].copy_(srcs[i % nsets])
         b.record(stream)
         torch.cuda.synchronize()
         cus = a.elapsed_time(b) * 1e3 / reps
@@ -348,31 +435,40 @@ def run_ours(args, cfg):
         sampler.mark_load(False)
     clocks = sampler.stop() if sampler else None
 
-    # ---- end to end through the public API with HOST buffers: pinned inputs -> device ->
-    #      ops -> pinned outputs, every step, copies inside the timed region
+    # ---- end to end through the public host-slice API: pinned host arrays in, pinned host
+    #      arrays out, every step, copies inside the timed region
     e2e = None
-    if not args.no_e2e:
+    e2e_ops = [o for o in order if o in ("get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul", "softmax")]
+    if not args.no_e2e and e2e_ops == order and step_bytes < 4e9:  # (the 16 GB configuration would pin 17 GB of host memory)
         b0 = sets[0]
-        names_in = ["ids", "x", "q", "k", "q2", "k2", "gate", "up"]
-        names_out = ["emb", "xn", "act"]  # q, k, q2, k2 are rotated in place in their host arrays
+        needs = {"get_rows": (["ids"], ["emb"]), "rms_norm": (["x"], ["xn"]), "rope_qk": (["q", "k"], []),
+                 "qk_norm_rope_qk": (["q2", "k2"], []), "silu_mul": (["gate", "up"], ["act"]),
+                 "softmax": (["scores"], ["probs"])}
+        names_in = [n for o in order for n in needs[o][0]]
+        names_out = [n for o in order for n in needs[o][1]]
+        inplace = [n for n in names_in if n in ("q", "k", "q2", "k2")]  # rotated in place in their host arrays
         host_in = {n: b0[n].cpu().pin_memory() for n in names_in}
         host_out = {n: torch.empty_like(b0[n], device="cpu").pin_memory() for n in names_out}
         h2d = sum(t.numel() * t.element_size() for t in host_in.values())
-        d2h = sum(t.numel() * t.element_size() for t in host_out.values()) + sum(
-            host_in[n].numel() * 4 for n in ("q", "k", "q2", "k2"))
-
+        d2h = sum(t.numel() * t.element_size() for t in host_out.values()) + sum(host_in[n].numel() * 4 for n in inplace)
         hin = {n: t.numpy() for n, t in host_in.items()}
         hout = {n: t.numpy() for n, t in host_out.items()}
-        hin["ids"] = hin["ids"].view(np.uint32)
+        if "ids" in hin:
+            hin["ids"] = hin["ids"].view(np.uint32)
+        pos_h = None if not cfg.random_pos else synth.positions(cfg.index, T, True)
+        host_ops = {
+            "get_rows": lambda: be.get_rows_into(cfg.embd_dtype, table, table_bytes, cfg.vocab, H, hin["ids"], hout["emb"]),
+            "rms_norm": lambda: be.rms_norm_into(hin["x"], w, hout["xn"], cfg.eps),
+            "rope_qk": lambda: be.rope_host(hin["q"], hin["k"], nq, nkv, hd, cfg.n_rot, pos_h, cfg.theta),
+            "qk_norm_rope_qk": lambda: be.rope_host(hin["q2"], hin["k2"], nq, nkv, hd, cfg.n_rot, pos_h, cfg.theta,
+                                                    wq_dev=wq, wk_dev=wk, eps=cfg.eps),
+            "silu_mul": lambda: be.silu_mul_into(hin["gate"], hin["up"], hout["act"]),
+            "softmax": lambda: be.softmax_rows_into(hin["scores"], hout["probs"], causal_period=T),
+        }
 
         def e2e_step():
-            # the host-slice entry points: pinned host arrays in, pinned host arrays out, rows
-            # streamed through the library's staging ring (upload / kernel / download overlapped)
-            be.get_rows_into(cfg.embd_dtype, table, table_bytes, cfg.vocab, H, hin["ids"], hout["emb"])
-            be.rms_norm_into(hin["x"], w, hout["xn"], cfg.eps)
-            be.rope_host(hin["q"], hin["k"], nq, nkv, hd, cfg.n_rot, None, cfg.theta)
-            be.rope_host(hin["q2"], hin["k2"], nq, nkv, hd, cfg.n_rot, None, cfg.theta, wq_dev=wq, wk_dev=wk, eps=cfg.eps)
-            be.silu_mul_into(hin["gate"], hin["up"], hout["act"])
+            for o in order:
+                host_ops[o]()
             be.sync()  # the step's results are read on the host
 
         e2e_steps = max(3, min(args.steps, 10))
@@ -386,8 +482,9 @@ def run_ours(args, cfg):
         b.record(stream)
         barrier()
         e2e_ms = sharding.max_over_ranks(a.elapsed_time(b)) / e2e_steps
-        e2e = {"value": world * T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms, "steps": e2e_steps}
+        e2e = {"value": T_total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "api": "host-slice entry points (agn_host_*), pinned host arrays, 3-stream staging ring"}
 
     # ---- verification gather (the only collective): per-rank checksums of one op's output
     be.sync()
@@ -396,47 +493,100 @@ def run_ours(args, cfg):
     if rank == 0:
         peak, peak_src = measured_peaks()
         achieved = ab["silu_mul"] / (silu_ms * 1e-3) / 1e9
-        step_bytes = sum(ab.values())
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cfg.name, "tokens_per_gpu": T, "hidden": H, "head_dim": hd, "q_heads": nq,
-                       "kv_heads": nkv, "ffn": I, "embedding": "Q4_K 152064x3584", "ops": order,
+            "config": {"workload": cfg.name, "tokens_per_gpu": T, "tokens_total": T_total, "hidden": H, "head_dim": hd,
+                       "q_heads": nq, "kv_heads": nkv, "ffn": I,
+                       "embedding": f"{DTYPE_NAMES[cfg.embd_dtype]} {cfg.vocab}x{H}", "ops": order,
                        "parallelism": f"token rows sharded over {world} GPU(s), no data-path collective",
-                       "l2": f"inputs larger than L2: {NSETS} rotating buffer sets, {step_bytes / 1e9:.2f} GB per step"},
+                       "l2": f"inputs larger than L2: {nsets} rotating buffer sets, {step_bytes / 1e9:.2f} GB per step"},
             "hbm_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9 * world,
             "hbm_frac_of_measured_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
             "roofline": {"kernel": "silu_mul_vec4_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_src} (of measured copy bandwidth)"
-                         if peak_src == "measured" else "fallback", "traffic": None,
+                         "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": "of measured (copy bandwidth, MEASURED_PEAKS.json)" if peak_src == "measured"
+                         else "of fallback", "traffic": silu_traffic_bytes(R * I),
                          "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
             "ops": per_op, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk)},
         }
-        out["roofline"]["traffic"] = silu_traffic_bytes(T * I)
         if world == 1 and not args.no_cpu:
-            out["cpu_baseline"] = cpu_baseline(cfg)
+            out["cpu_baseline"] = cpu_baseline(cfg, order)
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
     be.close()
 
 
-def cpu_baseline(cfg):
-    """The oracle timed on this box's host cores on a bounded sample of the workload."""
-    from oracle import oracle as orc
-    threads = orc.max_threads()
-    rows = min(cfg.T, 1024)
-    data, vocab = host_data(cfg, rows, vocab_rows=min(cfg.vocab, 16384))
+def run_decode_sweep(args):
+    """Decode-shaped latency sweep (Qwen2.5-7B shapes): for T in {1, 8, 32, 64} tokens per step with
+    random positions, the fused norm->rope and SiLU*mul kernels run back to back for 28 layers.
+    Timed as plain stream launches and as one CUDA graph replay."""
+    from agention_infer_b200 import synth
+    torch, dist, be, dev, stream, sampler, rank, world, local = setup_cuda(args)
+    cfg = synth.CONFIGS["c3"]
+    H, hd, nq, nkv, I, layers = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn, 28
+    wq = torch.from_numpy(synth.norm_weight(cfg.index, "wq", hd)).to(dev)
+    wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
+    gen = torch.Generator(device=dev); gen.manual_seed(synth.BASE_SEED + 3000 + rank)
+    sweep = []
+    if sampler:
+        sampler.mark_load(True)
+    for T in (1, 8, 32, 64):
+        pos = torch.from_numpy(synth.positions(cfg.index, T, True)).to(dev)
+        # one buffer set per layer: 28 layers of activations are distinct memory, as in the engine
+        L = [{"q": torch.randn(T, nq * hd, device=dev, generator=gen), "k": torch.randn(T, nkv * hd, device=dev, generator=gen),
+              "gate": torch.randn(T, I, device=dev, generator=gen), "up": torch.randn(T, I, device=dev, generator=gen),
+              "act": torch.empty(T, I, device=dev)} for _ in range(layers)]
 
-    c = dataclasses.replace(cfg, vocab=vocab)
-    cpu_step(orc, c, data, rows, threads)
-    t_all = time_cpu(orc, c, data, rows, threads, 5)
-    t_one = time_cpu(orc, c, data, rows, 1, 2)
-    return {"value": rows / t_all, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{rows} of {cfg.T} token rows, table of {vocab} rows, best of 5, OpenMP over rows",
-            "single_thread_value": rows / t_one}
+        def chain():
+            for b in L:
+                be.launch_qk_norm_rope_qk(b["q"], b["k"], wq, wk, T, nq, nkv, hd, cfg.eps, cfg.n_rot, pos, cfg.theta)
+                be.launch_silu_mul(b["gate"], b["up"], T * I, out=b["act"])
+
+        for _ in range(5):
+            chain()
+        torch.cuda.synchronize()
+        reps = max(args.steps, 20)
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            chain()
+        b_.record(stream); torch.cuda.synchronize()
+        us_plain = a.elapsed_time(b_) * 1e3 / reps
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            chain()
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+        a.record(stream)
+        for _ in range(reps):
+            g.replay()
+        b_.record(stream); torch.cuda.synchronize()
+        us_graph = a.elapsed_time(b_) * 1e3 / reps
+        bytes_chain = layers * (8 * T * (nq + nkv) * hd + 12 * T * I)
+        sweep.append({"T": T, "layers": layers, "launches": 2 * layers, "us_plain": round(us_plain, 2),
+                      "us_graph": round(us_graph, 2), "us_per_layer_graph": round(us_graph / layers, 3),
+                      "gbs_graph": round(bytes_chain / (us_graph * 1e-6) / 1e9, 1),
+                      "tokens_per_s_graph": round(T / (us_graph * 1e-6), 1)})
+    if sampler:
+        sampler.mark_load(False)
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        best = sweep[-1]
+        print(json.dumps({
+            "metric": "decode_layer_chain_tokens_per_s", "value": best["tokens_per_s_graph"], "unit": UNIT, "n_gpus": world,
+            "steps": max(args.steps, 20), "warmup": 5, "ms_per_step": best["us_graph"] / 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg.name, "chain": "28 x (qk_norm_rope_qk + silu_mul)", "hidden": H, "ffn": I,
+                       "positions": "random in [0, 32768)", "timing": "CUDA graph replay vs plain launches"},
+            "sweep": sweep, "clocks": clocks, "gpu_launches": 2 * layers * max(args.steps, 20), "e2e": None}))
+    if world > 1:
+        dist.destroy_process_group()
+    be.close()
 
 
 def main():
@@ -445,28 +595,40 @@ def main():
     ap.add_argument("--steps", type=int, default=None, help="timed steps (default 200; 5 for --impl reference)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=list(WORKLOADS) + ["c3"], default="c2",
+                    help="c2 (default, the headline): Qwen2.5-7B-shaped prefill, T=4096 rows per GPU; c1: Llama-3.2-1B "
+                         "shapes incl. causal softmax; c3: decode latency sweep; c4: T=65536 Llama-3-8B-shaped rows "
+                         "split over the GPUs; c5: Mixtral-shaped MoE routing ops")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (for comparison)")
+    ap.add_argument("--warm-seconds", type=float, default=0.6,
+                    help="minimum duration of the warm-up (0 for profiling runs)")
     ap.add_argument("--tokens", type=int, default=None,
-                    help="token rows per GPU (default: the configuration's 4096); smaller values are for profiling")
+                    help="token rows (default: the configuration's); smaller values are for profiling")
     args = ap.parse_args()
     from agention_infer_b200 import synth
-    cfg = synth.CONFIGS["c2"]
+    if args.steps is None:
+        args.steps = 5 if args.impl == "reference" else (200 if args.workload in ("c1", "c2", "c3") else 20)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "ours" and world == 1 and args.gpus > 1:
+        # not under torchrun: relaunch one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29517", __file__, *sys.argv[1:]]
+        sys.exit(subprocess.call(cmd))
+    if args.workload == "c3":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the decode latency sweep has no host arm"}))
+            return
+        return run_decode_sweep(args)
+    key, ops, _ = WORKLOADS[args.workload]
+    cfg = synth.CONFIGS[key]
     if args.tokens:
         cfg = dataclasses.replace(cfg, T=args.tokens, name=f"{cfg.name} (rows overridden to {args.tokens})")
-    if args.steps is None:
-        args.steps = 5 if args.impl == "reference" else 200
     if args.impl == "reference":
-        run_reference(args, cfg)
+        run_reference(args, cfg, ops, args.workload)
     else:
-        world = int(os.environ.get("WORLD_SIZE", "1"))
-        if world == 1 and args.gpus > 1:
-            # not under torchrun: relaunch one rank per GPU
-            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
-                   "--master-addr", "127.0.0.1", "--master-port", "29517", __file__, *sys.argv[1:]]
-            sys.exit(subprocess.call(cmd))
-        run_ours(args, cfg)
+        run_ours(args, cfg, ops, args.workload)
 
 
 if __name__ == "__main__":
