@@ -47,10 +47,10 @@ def measured_peaks():
 
 def silu_traffic_bytes(n_elements):
     """DRAM bytes of one silu_mul launch, scaled from the ncu capture summarised in
-    profiles/silu_mul_vec4_qwen7b_rows1024.md (19,398,656 elements: dram read 155.2 MB = 8.00 B per
-    element, i.e. no re-reads; of the 4 B per element written, ~40 MB were still dirty in L2 when the
-    kernel ended).  Reads and writes scale with the element count; the dirty remainder does not."""
-    dirty_left = 40.5e6
+    profiles/hot_kernels_qwen7b_rows2048.md (38,797,312 elements: dram read 310.4 MB = 8.00 B per
+    element, i.e. no re-reads; of the 155.2 MB written, 43.5 MB were still dirty in L2 when the kernel
+    ended).  Reads and writes scale with the element count; the dirty remainder does not."""
+    dirty_left = 43.5e6
     return 8.0 * n_elements + max(4.0 * n_elements - dirty_left, 0.0)
 
 
