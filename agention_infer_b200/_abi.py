@@ -12,6 +12,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libagention_b200.so"
 
 AGN_OK, AGN_EINVAL, AGN_EUNSUPPORTED_DTYPE, AGN_ECUDA, AGN_EOOB_ID, AGN_ENOMEM, AGN_ETIMEOUT = range(7)
 AGN_F32, AGN_F16, AGN_Q8_0, AGN_Q4_K, AGN_Q6_K, AGN_BF16 = 0, 1, 8, 12, 14, 30
+AGN_Q5_0, AGN_Q5_K = 6, 13
 AGN_ROPE_NEOX, AGN_ROPE_NORMAL = 0, 1
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
@@ -27,6 +28,7 @@ SIGNATURES = {
     "agn_ctx_set_stream": (_i32, [_vp, _vp]),
     "agn_ctx_get_stream": (_i32, [_vp, _pp]),
     "agn_ctx_launch_count": (C.c_uint64, [_vp]),
+    "agn_launch_noop": (_i32, [_vp]),
     "agn_ctx_set_option": (_i32, [_vp, C.c_char_p, _i64]),
     "agn_malloc": (_i32, [_vp, _sz, _pp]),
     "agn_free": (_i32, [_vp, _vp]),
@@ -50,6 +52,9 @@ SIGNATURES = {
     "agn_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_softmax_rows_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32]),
     "agn_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
+    "agn_kv_write_f32": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32, _i64]),
+    "agn_kv_read_f32": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "agn_kv_bytes_per_token": (_i64, [_i32, _i64]),
     "agn_router_top2_f32": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
     "agn_host_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),

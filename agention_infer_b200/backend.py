@@ -92,6 +92,10 @@ class CudaBackend:
     def launch_count(self) -> int:
         return int(self._lib.agn_ctx_launch_count(self._ctx))
 
+    def launch_noop(self) -> None:
+        """One empty kernel (the launch-latency floor)."""
+        self._check(self._lib.agn_launch_noop(self._ctx))
+
     def set_option(self, name: str, value: int) -> None:
         self._check(self._lib.agn_ctx_set_option(self._ctx, name.encode(), value))
 
@@ -243,6 +247,26 @@ class CudaBackend:
         self._check(self._lib.agn_get_rows_f32(self._ctx, dtype, _ptr(table), table_bytes, n_rows, row_len, _ptr(ids),
                                                T, _ptr(out)))
         return out
+
+    def kv_bytes_per_token(self, kv_dtype: int, head_dim_kv: int) -> int:
+        """`KvDtype::bytes_per_token` (src/model/mod.rs:550-556)."""
+        return int(self._lib.agn_kv_bytes_per_token(kv_dtype, head_dim_kv))
+
+    def kv_write(self, kv_dtype: int, k, v, k_cache, v_cache, T: int, head_dim_kv: int, pos, max_seq_len: int,
+                 pos_start: int = 0) -> None:
+        """`KvCache::write_range(layer, pos_start, k, v)` (src/model/mod.rs:660-672): pack T tokens into the cache."""
+        self._check(self._lib.agn_kv_write_f32(self._ctx, kv_dtype, _ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), T,
+                                               head_dim_kv, _ptr(pos), pos_start, max_seq_len))
+
+    def kv_read(self, kv_dtype: int, k_cache, v_cache, n_pos: int, head_dim_kv: int, k_out=None, v_out=None):
+        """`KvCache::read_up_to(layer, pos)` (src/model/mod.rs:678-697) with n_pos = pos + 1."""
+        if k_out is None:
+            k_out = self.empty(4 * n_pos * head_dim_kv)
+        if v_out is None:
+            v_out = self.empty(4 * n_pos * head_dim_kv)
+        self._check(self._lib.agn_kv_read_f32(self._ctx, kv_dtype, _ptr(k_cache), _ptr(v_cache), n_pos, head_dim_kv,
+                                              _ptr(k_out), _ptr(v_out)))
+        return k_out, v_out
 
     def router_top2(self, logits, T: int, n_experts: int, idx=None, w=None):
         """MoE router: softmax + top-2 per token (docs/08-moe-routing.md:27-33). Returns (idx [T,2] i32, w [T,2] f32)."""

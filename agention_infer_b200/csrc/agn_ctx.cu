@@ -269,6 +269,8 @@ size_t agn_type_size(int32_t dtype, size_t n) {
     case AGN_F32: bs = 1; bb = 4; break;
     case AGN_F16: case AGN_BF16: bs = 1; bb = 2; break;
     case AGN_Q8_0: bs = 32; bb = 34; break;
+    case AGN_Q5_0: bs = 32; bb = 22; break;
+    case AGN_Q5_K: bs = 256; bb = 176; break;
     case AGN_Q4_K: bs = 256; bb = 144; break;
     case AGN_Q6_K: bs = 256; bb = 210; break;
     default: return 0;
@@ -277,6 +279,20 @@ size_t agn_type_size(int32_t dtype, size_t n) {
 }
 
 }  // extern "C"
+
+namespace {
+__global__ void noop_kernel() { agn_pdl_prologue(); }
+}  // namespace
+
+// One empty kernel on the context's stream: the launch-latency floor that the decode-shaped
+// (launch-bound) measurements are compared with.
+extern "C" int32_t agn_launch_noop(agn_ctx *ctx) {
+    AGN_CHECK_CTX(ctx);
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    agn_launch(ctx, noop_kernel, dim3(1), dim3(32), 0);
+    AGN_LAUNCHED(ctx, "noop");
+    return AGN_OK;
+}
 
 // The reference builds its sin/cos table from
 //   freq = pos as f32 * freq_scale / theta.powf(2.0 * d as f32 / n_rot as f32)

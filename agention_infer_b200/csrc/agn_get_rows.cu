@@ -1,4 +1,4 @@
-// Embedding get_rows with inline dequantisation (Q8_0 / Q4_K / Q6_K / F16 / BF16 / F32).
+// Embedding get_rows with inline dequantisation (Q8_0 / Q4_K / Q6_K / Q5_K / Q5_0 / F16 / BF16 / F32).
 //
 // Reference: `quant::dequant_row` + `row_view` (src/quant/mod.rs:30-47, :97-135) and the
 // codecs `dequant_q8_0` (src/quant/q8_0.rs:14-51), `get_scale_min_k4` + `dequant_q4_k`
@@ -73,6 +73,57 @@ __device__ __forceinline__ float4 decode4<AGN_Q4_K>(const uint8_t *row, int e0) 
     o.y = __fsub_rn(__fmul_rn(dd, (float)((q >> 8) & 0xF)), mm);
     o.z = __fsub_rn(__fmul_rn(dd, (float)((q >> 16) & 0xF)), mm);
     o.w = __fsub_rn(__fmul_rn(dd, (float)((q >> 24) & 0xF)), mm);
+    return o;
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_Q5_K>(const uint8_t *row, int e0) {
+    // src/quant/q5_k.rs:43-103: Q4_K's scales plus a fifth bit per value in qh[32]
+    const uint8_t *blk = row + (e0 >> 8) * 176;  // 176 = 11*16: blocks stay 16-byte aligned
+    const int r = e0 & 255;
+    const int g = r >> 6;
+    const int hi = (r >> 5) & 1;
+    const int l = r & 31;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
+    const uint8_t *sc = blk + 4;
+    const int j = 2 * g + hi;
+    uint32_t s, m;
+    if (j < 4) {
+        s = sc[j] & 63;
+        m = sc[j + 4] & 63;
+    } else {
+        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
+        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+    }
+    const float dd = __fmul_rn(d, (float)s);
+    const float mm = __fmul_rn(dmin, (float)m);
+    const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 16 + l) >> j;  // bit j of each byte
+    const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * g + l) >> (4 * hi);
+    float4 o;
+    o.x = __fsub_rn(__fmul_rn(dd, (float)((q & 0xF) + ((qh & 1) << 4))), mm);
+    o.y = __fsub_rn(__fmul_rn(dd, (float)(((q >> 8) & 0xF) + (((qh >> 8) & 1) << 4))), mm);
+    o.z = __fsub_rn(__fmul_rn(dd, (float)(((q >> 16) & 0xF) + (((qh >> 16) & 1) << 4))), mm);
+    o.w = __fsub_rn(__fmul_rn(dd, (float)(((q >> 24) & 0xF) + (((qh >> 24) & 1) << 4))), mm);
+    return o;
+}
+
+template <>
+__device__ __forceinline__ float4 decode4<AGN_Q5_0>(const uint8_t *row, int e0) {
+    // src/quant/q5_0.rs:20-62: f16 d, 32 high bits, 16 bytes of nibbles; value = (q - 16) * d
+    const uint8_t *blk = row + (e0 >> 5) * 22;
+    const int i0 = e0 & 31;
+    const int hi = i0 >> 4;  // outputs 16..31 take the high nibbles and qh bits 16..31
+    const int j = i0 & 15;
+    const float d = f16_bits_to_f32(ld_u16(blk));
+    const uint32_t qh = ld_u32_2(blk + 2) >> (j + 16 * hi);
+    const uint32_t q = ld_u32_2(blk + 6 + j) >> (4 * hi);
+    float4 o;
+    o.x = __fmul_rn((float)((int)((q & 0xF) | ((qh & 1) << 4)) - 16), d);
+    o.y = __fmul_rn((float)((int)(((q >> 8) & 0xF) | (((qh >> 1) & 1) << 4)) - 16), d);
+    o.z = __fmul_rn((float)((int)(((q >> 16) & 0xF) | (((qh >> 2) & 1) << 4)) - 16), d);
+    o.w = __fmul_rn((float)((int)(((q >> 24) & 0xF) | (((qh >> 3) & 1) << 4)) - 16), d);
     return o;
 }
 
@@ -188,7 +239,7 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
                                     int64_t row_len, const uint32_t *ids, int64_t T, float *out) {
     AGN_CHECK_CTX(ctx);
     const size_t row_bytes = agn_type_size(dtype, (size_t)(row_len > 0 ? row_len : 0));
-    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_F16 && dtype != AGN_BF16 && dtype != AGN_F32)
+    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_Q5_K && dtype != AGN_Q5_0 && dtype != AGN_F16 && dtype != AGN_BF16 && dtype != AGN_F32)
         return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "get_rows: dequantization not implemented for ggml type %d", dtype);
     if (T < 0 || n_rows < 0 || row_len <= 0)
         return agn_fail(ctx, AGN_EINVAL, "get_rows: T=%lld n_rows=%lld row_len=%lld", (long long)T, (long long)n_rows, (long long)row_len);
@@ -222,6 +273,8 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
         case AGN_Q8_0: AGN_GR_ATTR(AGN_Q8_0) break;
         case AGN_Q4_K: AGN_GR_ATTR(AGN_Q4_K) break;
         case AGN_Q6_K: AGN_GR_ATTR(AGN_Q6_K) break;
+        case AGN_Q5_K: AGN_GR_ATTR(AGN_Q5_K) break;
+        case AGN_Q5_0: AGN_GR_ATTR(AGN_Q5_0) break;
         case AGN_F16: AGN_GR_ATTR(AGN_F16) break;
         case AGN_BF16: AGN_GR_ATTR(AGN_BF16) break;
         default: AGN_GR_ATTR(AGN_F32) break;
@@ -235,6 +288,8 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
     case AGN_Q8_0: launch_get_rows<AGN_Q8_0>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q4_K: launch_get_rows<AGN_Q4_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q6_K: launch_get_rows<AGN_Q6_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_K: launch_get_rows<AGN_Q5_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_0: launch_get_rows<AGN_Q5_0>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_F16: launch_get_rows<AGN_F16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_BF16: launch_get_rows<AGN_BF16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     default: launch_get_rows<AGN_F32>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;

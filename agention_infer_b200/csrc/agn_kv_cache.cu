@@ -1,0 +1,181 @@
+// KV-cache write (pack) and read (unpack) for f16 and Q8_0 storage.
+//
+// Reference: `KvDtype::pack` / `unpack` (src/model/mod.rs:567-604), `KvCache::write`,
+// `write_range` (:648-672) and `read_up_to` (:678-697); GPU twins `kv_cache_write` /
+// `kv_cache_write_q8_0` (src/ops/kernels_wgpu.rs:566-698).  A cache holds, per layer,
+// max_seq_len token slots of bytes_per_token = 2*hd (f16) or ceil(hd/32)*34 (Q8_0) bytes,
+// hd = n_kv_heads * head_dim.
+//
+//   f16  : half::f16::from_f32 (round to nearest even) per element
+//   Q8_0 : per 32 values: amax = max |v| ; scale = amax > 0 ? amax / 127 : 1 ;
+//          store f16(scale) ; q = clamp(round(v / scale), -127, 127)   (round half away,
+//          dividing by the f32 scale, not by the stored f16 one)
+//
+// Integer / byte outputs: bit-exact with the CPU code (IEEE division and f16 conversion
+// spelled with __fdiv_rn / __float2half_rn).  Bound by HBM: 4 B read + 2 or 1.06 B written
+// per element; eight lanes own one 32-value block (coalesced 128-bit loads, amax by three
+// shuffles).
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "agn_common.cuh"
+
+namespace {
+
+struct KvArgs {
+    const float *k, *v;
+    unsigned char *k_cache, *v_cache;
+    const int32_t *pos;
+    int64_t T, hd, max_seq;
+    int pos_start;
+    int bytes_per_token;
+    uint32_t *flags;
+};
+
+__device__ __forceinline__ int64_t kv_slot(const KvArgs &a, int64_t t) {
+    const int64_t p = a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t;
+    return (p >= 0 && p < a.max_seq) ? p : -1;
+}
+
+// grid.x covers (token, block-of-32) pairs, 8 lanes each; blockIdx.y = 0 (K) or 1 (V)
+__global__ void __launch_bounds__(256)
+kv_write_q8_0_kernel(const KvArgs a) {
+    agn_pdl_prologue();
+    const int lane8 = threadIdx.x & 7;
+    const int64_t nblk = (a.hd + 31) >> 5;
+    const int64_t unit = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // (token, block)
+    const bool on = unit < a.T * nblk;
+    const int64_t t = on ? unit / nblk : 0;
+    const int64_t b = on ? unit - t * nblk : 0;
+    const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd + b * 32;
+    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
+    const int e0 = lane8 * 4;
+    const int64_t left = a.hd - b * 32;  // elements of this (possibly partial) block
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (on) {
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (e0 + i < left) x[i] = src[e0 + i];
+    }
+    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!on) return;
+    const int64_t slot = kv_slot(a, t);
+    if (slot < 0) {
+        if (lane8 == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+        return;
+    }
+    const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    unsigned char *blk = cache + slot * a.bytes_per_token + b * 34;
+    if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (e0 + i < left) {
+            float q = roundf(__fdiv_rn(x[i], scale));
+            q = fminf(fmaxf(q, -127.0f), 127.0f);
+            blk[2 + e0 + i] = (unsigned char)(signed char)(int)q;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+kv_write_f16_kernel(const KvArgs a) {
+    agn_pdl_prologue();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.T * a.hd) return;
+    const int64_t t = i / a.hd, d = i - t * a.hd;
+    const int64_t slot = kv_slot(a, t);
+    if (slot < 0) {
+        if (d == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+        return;
+    }
+    const float *src = blockIdx.y ? a.v : a.k;
+    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
+    reinterpret_cast<uint16_t *>(cache + slot * a.bytes_per_token)[d] = __half_as_ushort(__float2half_rn(src[i]));
+}
+
+// read positions [0, n_pos): one thread per element
+__global__ void __launch_bounds__(256)
+kv_read_kernel(const unsigned char *__restrict__ k_cache, const unsigned char *__restrict__ v_cache, int64_t n_pos, int64_t hd,
+               int bytes_per_token, int q8, float *__restrict__ k_out, float *__restrict__ v_out) {
+    agn_pdl_prologue();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pos * hd) return;
+    const int64_t p = i / hd, d = i - p * hd;
+    const unsigned char *tok = (blockIdx.y ? v_cache : k_cache) + p * bytes_per_token;
+    float val;
+    if (q8) {
+        const unsigned char *blk = tok + (d >> 5) * 34;
+        const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
+        val = __fmul_rn((float)(signed char)blk[2 + (d & 31)], scale);
+    } else {
+        val = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t *>(tok)[d]));
+    }
+    (blockIdx.y ? v_out : k_out)[i] = val;
+}
+
+int kv_bytes_per_token(int32_t dtype, int64_t hd) {
+    if (dtype == AGN_F16) return (int)(hd * 2);
+    if (dtype == AGN_Q8_0) return (int)(((hd + 31) / 32) * 34);
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int64_t agn_kv_bytes_per_token(int32_t kv_dtype, int64_t head_dim_kv) {
+    return head_dim_kv > 0 ? kv_bytes_per_token(kv_dtype, head_dim_kv) : 0;
+}
+
+extern "C" int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float *k, const float *v, void *k_cache,
+                                    void *v_cache, int64_t T, int64_t head_dim_kv, const int32_t *pos, int32_t pos_start,
+                                    int64_t max_seq_len) {
+    AGN_CHECK_CTX(ctx);
+    const int bpt = head_dim_kv > 0 ? kv_bytes_per_token(kv_dtype, head_dim_kv) : 0;
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_write: KV dtype %d is neither f16 (1) nor q8_0 (8)", kv_dtype);
+    if (T < 0 || head_dim_kv <= 0 || max_seq_len <= 0)
+        return agn_fail(ctx, AGN_EINVAL, "kv_write: T=%lld head_dim_kv=%lld max_seq_len=%lld", (long long)T,
+                        (long long)head_dim_kv, (long long)max_seq_len);
+    if (T == 0) return AGN_OK;
+    if (!k || !v || !k_cache || !v_cache) return agn_fail(ctx, AGN_EINVAL, "kv_write: null pointer");
+    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 1)
+        return agn_fail(ctx, AGN_EINVAL, "kv_write: caches must be 2-byte aligned");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    KvArgs a;
+    a.k = k; a.v = v; a.k_cache = static_cast<unsigned char *>(k_cache); a.v_cache = static_cast<unsigned char *>(v_cache);
+    a.pos = pos; a.T = T; a.hd = head_dim_kv; a.max_seq = max_seq_len; a.pos_start = pos_start; a.bytes_per_token = bpt;
+    a.flags = ctx->d_flags;
+    if (kv_dtype == AGN_Q8_0) {
+        const int64_t units = T * ((head_dim_kv + 31) / 32);
+        const int64_t blocks = (units * 8 + 255) / 256;
+        if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
+        agn_launch(ctx, kv_write_q8_0_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, a);
+    } else {
+        const int64_t blocks = (T * head_dim_kv + 255) / 256;
+        if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
+        agn_launch(ctx, kv_write_f16_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, a);
+    }
+    ctx->flags_dirty = true;
+    AGN_LAUNCHED(ctx, "kv_write");
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k_cache, const void *v_cache, int64_t n_pos,
+                                   int64_t head_dim_kv, float *k_out, float *v_out) {
+    AGN_CHECK_CTX(ctx);
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_read: KV dtype %d is neither f16 (1) nor q8_0 (8)", kv_dtype);
+    if (n_pos < 0 || head_dim_kv <= 0)
+        return agn_fail(ctx, AGN_EINVAL, "kv_read: n_pos=%lld head_dim_kv=%lld", (long long)n_pos, (long long)head_dim_kv);
+    if (n_pos == 0) return AGN_OK;
+    if (!k_cache || !v_cache || !k_out || !v_out) return agn_fail(ctx, AGN_EINVAL, "kv_read: null pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int64_t blocks = (n_pos * head_dim_kv + 255) / 256;
+    if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_read: too many positions");
+    agn_launch(ctx, kv_read_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, static_cast<const unsigned char *>(k_cache),
+               static_cast<const unsigned char *>(v_cache), n_pos, head_dim_kv, kv_bytes_per_token(kv_dtype, head_dim_kv),
+               kv_dtype == AGN_Q8_0 ? 1 : 0, k_out, v_out);
+    AGN_LAUNCHED(ctx, "kv_read");
+    return AGN_OK;
+}

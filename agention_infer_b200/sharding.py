@@ -65,6 +65,34 @@ def max_over_ranks(value: float, group=None) -> float:
     return float(t.item())
 
 
+class RankFailure(RuntimeError):
+    """Some ranks did not reach a rendezvous in time; `.missing` lists them."""
+
+    def __init__(self, tag: str, missing):
+        super().__init__(f"ranks {sorted(missing)} did not reach '{tag}' in time")
+        self.missing = sorted(missing)
+
+
+def rendezvous(store, tag: str, rank: int, world: int, timeout_s: float = 30.0, poll_s: float = 0.05) -> None:
+    """Host-side liveness check between steps: every rank posts a key in the key-value store
+    and waits, with a limit, for the keys of all the others.  A rank that has died or hangs on
+    the host is reported by name (RankFailure) instead of blocking the next collective.  It
+    runs with no kernel or collective in flight, so no GPU work is ever abandoned."""
+    import time
+    store.set(f"{tag}/{rank}", b"1")
+    deadline = time.monotonic() + timeout_s
+    missing = set(range(world)) - {rank}
+    while missing:
+        for r in list(missing):
+            if store.check([f"{tag}/{r}"]):
+                missing.discard(r)
+        if not missing:
+            break
+        if time.monotonic() > deadline:
+            raise RankFailure(tag, missing)
+        time.sleep(poll_s)
+
+
 def gather_objects(obj, group=None) -> list:
     """All ranks' small Python objects (checksums, parity figures), in rank order."""
     import torch.distributed as dist

@@ -12,7 +12,7 @@ from typing import Optional
 
 import numpy as np
 
-from ._abi import AGN_Q4_K, AGN_Q6_K, AGN_Q8_0
+from ._abi import AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0
 
 BASE_SEED = 20261125
 STREAMS = {name: i for i, name in enumerate(
@@ -104,6 +104,15 @@ def quant_table(dtype: int, n_rows: int, row_len: int, cfg_index: int = 0, salt:
         t = r.integers(0, 256, size=(nb, 144), dtype=np.uint8)
         t[:, 0:2] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
         t[:, 2:4] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
+    elif dtype == AGN_Q5_K:  # f16 d, dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes
+        nb = n_rows * ((row_len + 255) // 256)
+        t = r.integers(0, 256, size=(nb, 176), dtype=np.uint8)
+        t[:, 0:2] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
+        t[:, 2:4] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
+    elif dtype == AGN_Q5_0:  # f16 d, 4 bytes of high bits, 16 nibble bytes
+        nb = n_rows * ((row_len + 31) // 32)
+        t = r.integers(0, 256, size=(nb, 22), dtype=np.uint8)
+        t[:, 0:2] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
     elif dtype == AGN_Q6_K:
         nb = n_rows * ((row_len + 255) // 256)
         t = r.integers(0, 256, size=(nb, 210), dtype=np.uint8)

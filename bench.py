@@ -536,6 +536,29 @@ def run_decode_sweep(args):
     sweep = []
     if sampler:
         sampler.mark_load(True)
+
+    def timed(fn, reps):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b_.record(stream); torch.cuda.synchronize()
+        return a.elapsed_time(b_) * 1e3 / reps
+
+    # the floor: the same number of empty kernels, as plain launches and as a graph
+    def noops():
+        for _ in range(2 * layers):
+            be.launch_noop()
+    for _ in range(3):
+        noops()
+    torch.cuda.synchronize()
+    floor_plain = timed(noops, 20)
+    g0 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g0, stream=stream):
+        noops()
+    for _ in range(3):
+        g0.replay()
+    floor_graph = timed(g0.replay, 50)
     for T in (1, 8, 32, 64):
         pos = torch.from_numpy(synth.positions(cfg.index, T, True)).to(dev)
         # one buffer set per layer: 28 layers of activations are distinct memory, as in the engine
@@ -585,6 +608,8 @@ def run_decode_sweep(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": cfg.name, "chain": "28 x (qk_norm_rope_qk + silu_mul)", "hidden": H, "ffn": I,
                        "positions": "random in [0, 32768)", "timing": "CUDA graph replay vs plain launches"},
+            "launch_floor": {"kernels": 2 * layers, "us_plain": round(floor_plain, 2), "us_graph": round(floor_graph, 2),
+                             "what": "the same number of empty kernels"},
             "sweep": sweep, "clocks": clocks, "gpu_launches": 2 * layers * max(args.steps, 20), "e2e": None}))
     if world > 1:
         dist.destroy_process_group()

@@ -53,8 +53,10 @@ typedef enum agn_status {
 typedef enum agn_dtype {
     AGN_F32 = 0,
     AGN_F16 = 1,
+    AGN_Q5_0 = 6,
     AGN_Q8_0 = 8,
     AGN_Q4_K = 12,
+    AGN_Q5_K = 13,
     AGN_Q6_K = 14,
     AGN_BF16 = 30
 } agn_dtype;
@@ -88,6 +90,10 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
  * that a kernel's launch latency overlaps the tail of the previous kernel of the stream
  * (every kernel still waits for the previous one to complete before its first access). */
 AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value);
+/* Launches one empty kernel: the per-launch floor for launch-bound (decode-shaped) timings,
+ * the counterpart of the reference's "dispatch floor" probe
+ * (docs/PERFORMANCE_RECOMMENDATIONS.md:829). */
+AGN_API int32_t agn_launch_noop(agn_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 AGN_API uint64_t agn_ctx_launch_count(agn_ctx *ctx);
 
@@ -181,7 +187,8 @@ AGN_API int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, 
 /* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
  * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
  * -> dequant_q8_0 / dequant_q4_k / dequant_q6_k (src/quant/q8_0.rs:14-51,
- * q4_k.rs:37-91, q6_k.rs:34-77), looped over tokens as cpu_path.rs:865-868 does.
+ * q4_k.rs:37-91, q6_k.rs:34-77), also dequant_q5_k (q5_k.rs:43-103) and dequant_q5_0
+ * (q5_0.rs:20-62), looped over tokens as cpu_path.rs:865-868 does.
  * table: n_rows rows of type_size(dtype, row_len) bytes each, 16-byte aligned;
  * table_bytes = readable bytes at table; ids: device u32 [T]; out: [T, row_len] f32.
  * Bit-exact with the CPU codecs.  An id >= n_rows zero-fills its row and makes the
@@ -189,6 +196,24 @@ AGN_API int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, 
 AGN_API int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table,
                                  size_t table_bytes, int64_t n_rows, int64_t row_len,
                                  const uint32_t *ids, int64_t T, float *out);
+
+/* KV-cache write: `KvCache::write` / `write_range` (src/model/mod.rs:648-672) with
+ * `KvDtype::pack` (:567-585); GPU twins `kv_cache_write` / `kv_cache_write_q8_0`
+ * (src/ops/kernels_wgpu.rs:566-698).  kv_dtype is AGN_F16 or AGN_Q8_0 (`KvDtype`, :536-539).
+ * k, v: [T, head_dim_kv] f32 (head_dim_kv = n_kv_heads * head_dim); k_cache, v_cache: one
+ * layer's [max_seq_len, agn_kv_bytes_per_token] bytes.  Token t goes to slot pos[t] (device
+ * int32) or pos_start + t.  Bit-exact with the CPU pack.  A slot outside [0, max_seq_len)
+ * is skipped and makes the next agn_sync return AGN_EOOB_ID. */
+AGN_API int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float *k, const float *v,
+                                 void *k_cache, void *v_cache, int64_t T, int64_t head_dim_kv,
+                                 const int32_t *pos, int32_t pos_start, int64_t max_seq_len);
+/* `KvCache::read_up_to` (src/model/mod.rs:678-697) with `KvDtype::unpack` (:587-604):
+ * dequantises slots [0, n_pos) into k_out, v_out [n_pos, head_dim_kv] f32. */
+AGN_API int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k_cache,
+                                const void *v_cache, int64_t n_pos, int64_t head_dim_kv,
+                                float *k_out, float *v_out);
+/* `KvDtype::bytes_per_token` (src/model/mod.rs:550-556); 0 for an unknown dtype. */
+AGN_API int64_t agn_kv_bytes_per_token(int32_t kv_dtype, int64_t head_dim_kv);
 
 /* MoE router: softmax over the n_experts logits of each token and top-2 selection.  The
  * reference has no MoE forward pass; the semantics follow its design notes

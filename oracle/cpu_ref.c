@@ -20,8 +20,8 @@
 size_t orc_block_size(int dtype) {
     switch (dtype) {
     case ORC_F32: case ORC_F16: case ORC_BF16: return 1;
-    case ORC_Q8_0: return 32;
-    case ORC_Q4_K: case ORC_Q6_K: return 256;
+    case ORC_Q8_0: case ORC_Q5_0: return 32;
+    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -32,6 +32,8 @@ size_t orc_block_bytes(int dtype) {
     case ORC_F32: return 4;
     case ORC_F16: case ORC_BF16: return 2;
     case ORC_Q8_0: return 34;
+    case ORC_Q5_0: return 22;
+    case ORC_Q5_K: return 176;
     case ORC_Q4_K: return 144;
     case ORC_Q6_K: return 210;
     default: return 0;
@@ -282,6 +284,66 @@ int orc_dequant_q4_k(const uint8_t *data, size_t data_len, size_t n, float *out)
     return ORC_OK;
 }
 
+/* src/quant/q5_k.rs:43-103 */
+int orc_dequant_q5_k(const uint8_t *data, size_t data_len, size_t n, float *out) {
+    size_t n_blocks = (n + 255) / 256;
+    if (data_len < n_blocks * 176) return ORC_ESHORT;
+    for (size_t b = 0; b < n_blocks; b++) {
+        const uint8_t *blk = data + b * 176;
+        float d = orc_f16_to_f32(rd_u16(blk));
+        float dmin = orc_f16_to_f32(rd_u16(blk + 2));
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        float tmp[256];
+        size_t is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (size_t j = 0; j < 256; j += 64) {
+            const uint8_t *q = qs + j / 2;
+            uint8_t sc, m;
+            orc_get_scale_min_k4(is, scales, &sc, &m);
+            float d1 = d * (float)sc;
+            float m1 = dmin * (float)m;
+            orc_get_scale_min_k4(is + 1, scales, &sc, &m);
+            float d2 = d * (float)sc;
+            float m2 = dmin * (float)m;
+            for (size_t l = 0; l < 32; l++)
+                tmp[j + l] = d1 * (float)((q[l] & 0x0F) + ((qh[l] & u1) ? 16 : 0)) - m1;
+            for (size_t l = 0; l < 32; l++)
+                tmp[j + 32 + l] = d2 * (float)((q[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - m2;
+            is += 2;
+            u1 <<= 2;
+            u2 <<= 2;
+        }
+        size_t base = b * 256;
+        size_t cnt = n - base < 256 ? n - base : 256;
+        memcpy(out + base, tmp, cnt * sizeof(float));
+    }
+    return ORC_OK;
+}
+
+/* src/quant/q5_0.rs:20-62 */
+int orc_dequant_q5_0(const uint8_t *data, size_t data_len, size_t n, float *out) {
+    size_t n_blocks = (n + 31) / 32;
+    if (data_len < n_blocks * 22) return ORC_ESHORT;
+    for (size_t b = 0; b < n_blocks; b++) {
+        const uint8_t *blk = data + b * 22;
+        float d = orc_f16_to_f32(rd_u16(blk));
+        uint32_t qh = (uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24);
+        const uint8_t *qs = blk + 6;
+        float tmp[32];
+        for (size_t j = 0; j < 16; j++) {
+            uint8_t xh0 = (uint8_t)((qh >> j) & 1), xh1 = (uint8_t)((qh >> (j + 16)) & 1);
+            int x0 = (int)((qs[j] & 0x0F) | (xh0 << 4)) - 16;
+            int x1 = (int)((qs[j] >> 4) | (xh1 << 4)) - 16;
+            tmp[j] = (float)x0 * d;
+            tmp[j + 16] = (float)x1 * d;
+        }
+        size_t base = b * 32;
+        size_t cnt = n - base < 32 ? n - base : 32;
+        memcpy(out + base, tmp, cnt * sizeof(float));
+    }
+    return ORC_OK;
+}
+
 /* src/quant/q6_k.rs:25-77 */
 int orc_dequant_q6_k(const uint8_t *data, size_t data_len, size_t n, float *out) {
     size_t n_blocks = (n + 255) / 256;
@@ -356,6 +418,8 @@ int orc_dequant_row(int dtype, const uint8_t *data, size_t data_len, size_t byte
     case ORC_BF16: return orc_dequant_bf16(p, avail, row_len, out);
     case ORC_Q8_0: return orc_dequant_q8_0(p, avail, row_len, out);
     case ORC_Q4_K: return orc_dequant_q4_k(p, avail, row_len, out);
+    case ORC_Q5_K: return orc_dequant_q5_k(p, avail, row_len, out);
+    case ORC_Q5_0: return orc_dequant_q5_0(p, avail, row_len, out);
     case ORC_Q6_K: return orc_dequant_q6_k(p, avail, row_len, out);
     default: return ORC_EDTYPE;
     }
@@ -376,6 +440,90 @@ int orc_get_rows(int dtype, const uint8_t *table, size_t table_len, size_t n_voc
         }
     }
     return bad ? ORC_EROW : ORC_OK;
+}
+
+/* ------------------------------------------------------------- KV cache -- */
+
+static uint16_t f32_to_f16_bits(float f) { /* half::f16::from_f32: round to nearest even */
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t exp = (x >> 23) & 0xFFu;
+    uint32_t man = x & 0x7FFFFFu;
+    if (exp == 0xFF) return (uint16_t)(sign | 0x7C00u | (man ? (0x200u | (man >> 13)) : 0));
+    int32_t e = (int32_t)exp - 127 + 15;
+    if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        man |= 0x800000u;
+        uint32_t shift = (uint32_t)(14 - e);
+        uint32_t half_man = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1), halfway = 1u << (shift - 1);
+        if (rem > halfway || (rem == halfway && (half_man & 1))) half_man++;
+        return (uint16_t)(sign | half_man);
+    }
+    uint32_t half = ((uint32_t)e << 10) | (man >> 13);
+    uint32_t rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) half++;
+    return (uint16_t)(sign | half);
+}
+
+size_t orc_kv_bytes_per_token(int dtype, size_t hd) { /* src/model/mod.rs:550-556 */
+    if (dtype == ORC_F16) return hd * 2;
+    if (dtype == ORC_Q8_0) return ((hd + 31) / 32) * 34;
+    return 0;
+}
+
+/* KvDtype::pack, src/model/mod.rs:567-585 */
+void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out) {
+    if (dtype == ORC_F16) {
+        for (size_t i = 0; i < n; i++) {
+            uint16_t h = f32_to_f16_bits(x[i]);
+            out[2 * i] = (uint8_t)(h & 0xFF);
+            out[2 * i + 1] = (uint8_t)(h >> 8);
+        }
+        return;
+    }
+    for (size_t b = 0; b * 32 < n; b++) {
+        const float *blk = x + b * 32;
+        size_t cnt = n - b * 32 < 32 ? n - b * 32 : 32;
+        uint8_t *o = out + b * 34;
+        float amax = 0.0f;
+        for (size_t i = 0; i < cnt; i++) amax = fmaxf(amax, fabsf(blk[i]));
+        float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        uint16_t h = f32_to_f16_bits(scale);
+        o[0] = (uint8_t)(h & 0xFF);
+        o[1] = (uint8_t)(h >> 8);
+        for (size_t i = 0; i < cnt; i++) {
+            float q = roundf(blk[i] / scale);
+            q = q < -127.0f ? -127.0f : (q > 127.0f ? 127.0f : q);
+            o[2 + i] = (uint8_t)(int8_t)q;
+        }
+    }
+}
+
+/* KvDtype::unpack, src/model/mod.rs:587-604 */
+void orc_kv_unpack(int dtype, const uint8_t *bytes, size_t n, float *out) {
+    if (dtype == ORC_F16) {
+        for (size_t i = 0; i < n; i++) out[i] = orc_f16_to_f32(rd_u16(bytes + 2 * i));
+        return;
+    }
+    for (size_t i = 0; i < n; i++) {
+        const uint8_t *blk = bytes + (i / 32) * 34;
+        out[i] = (float)(int8_t)blk[2 + i % 32] * orc_f16_to_f32(rd_u16(blk));
+    }
+}
+
+/* KvCache::write_range, src/model/mod.rs:660-672: token t -> slot pos[t] */
+void orc_kv_write_rows(int dtype, const float *x, size_t T, size_t hd, const int32_t *pos, uint8_t *cache) {
+    size_t bpt = orc_kv_bytes_per_token(dtype, hd);
+    for (size_t t = 0; t < T; t++) orc_kv_pack(dtype, x + t * hd, hd, cache + (size_t)pos[t] * bpt);
+}
+
+/* KvCache::read_up_to, src/model/mod.rs:678-697 */
+void orc_kv_read(int dtype, const uint8_t *cache, size_t n_pos, size_t hd, float *out) {
+    size_t bpt = orc_kv_bytes_per_token(dtype, hd);
+    for (size_t p = 0; p < n_pos; p++) orc_kv_unpack(dtype, cache + p * bpt, hd, out + p * hd);
 }
 
 /* ------------------------------------------------------------------ MoE -- */

@@ -39,8 +39,10 @@ extern "C" {
 enum {
     ORC_F32 = 0,
     ORC_F16 = 1,
+    ORC_Q5_0 = 6,
     ORC_Q8_0 = 8,
     ORC_Q4_K = 12,
+    ORC_Q5_K = 13,
     ORC_Q6_K = 14,
     ORC_BF16 = 30
 };
@@ -111,6 +113,9 @@ void orc_get_scale_min_k4(size_t j, const uint8_t *scales, uint8_t *sc, uint8_t 
 int orc_dequant_q8_0(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_q4_k(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_q6_k(const uint8_t *data, size_t data_len, size_t n, float *out);
+/* src/quant/q5_k.rs:43-103, src/quant/q5_0.rs:20-62 */
+int orc_dequant_q5_k(const uint8_t *data, size_t data_len, size_t n, float *out);
+int orc_dequant_q5_0(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_f32(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_f16(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_bf16(const uint8_t *data, size_t data_len, size_t n, float *out);
@@ -124,6 +129,15 @@ int orc_dequant_row(int dtype, const uint8_t *data, size_t data_len, size_t byte
  * zero row and make the call return ORC_EROW (after finishing the others). */
 int orc_get_rows(int dtype, const uint8_t *table, size_t table_len, size_t n_vocab,
                  size_t row_len, const uint32_t *ids, size_t T, float *out, int threads);
+
+/* KV cache: KvDtype::bytes_per_token / pack / unpack (src/model/mod.rs:550-604),
+ * KvCache::write_range (:660-672), read_up_to (:678-697); dtype ORC_F16 or ORC_Q8_0.
+ * Parity unpinned: the reference has no test for them. */
+size_t orc_kv_bytes_per_token(int dtype, size_t hd);
+void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out);
+void orc_kv_unpack(int dtype, const uint8_t *bytes, size_t n, float *out);
+void orc_kv_write_rows(int dtype, const float *x, size_t T, size_t hd, const int32_t *pos, uint8_t *cache);
+void orc_kv_read(int dtype, const uint8_t *cache, size_t n_pos, size_t hd, float *out);
 
 /* MoE router (docs/08-moe-routing.md:27-33; not implemented by the reference):
  * probs = softmax(logits row); pick the 2 largest (ties -> lower index);

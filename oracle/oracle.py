@@ -15,6 +15,7 @@ HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
+Q5_0, Q5_K = 6, 13
 NEOX, NORMAL = 0, 1
 OK, ESHORT, EROW, EDTYPE = 0, 1, 2, 3
 
@@ -49,10 +50,14 @@ def lib() -> C.CDLL:
             "orc_silu_mul": (None, [_vp, _vp, _vp, _sz, _i]),
             "orc_get_scale_min_k4": (None, [_sz, _vp, _vp, _vp]),
             "orc_dequant_q8_0": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_q4_k": (_i, [_vp, _sz, _sz, _vp]),
+            "orc_dequant_q5_k": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_q5_0": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_q6_k": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_f32": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_f16": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_bf16": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_row": (_i, [_i, _vp, _sz, _sz, _sz, _sz, _sz, _vp]),
             "orc_get_rows": (_i, [_i, _vp, _sz, _sz, _sz, _vp, _sz, _vp, _i]),
+            "orc_kv_bytes_per_token": (_sz, [_i, _sz]),
+            "orc_kv_write_rows": (None, [_i, _vp, _sz, _sz, _vp, _vp]),
+            "orc_kv_read": (None, [_i, _vp, _sz, _sz, _vp]),
             "orc_router_top2": (None, [_vp, _sz, _sz, _vp, _vp]),
             "orc_gather_rows_by_expert": (None, [_vp, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _vp]),
             "orc_max_threads": (_i, []),
@@ -156,7 +161,7 @@ def get_scale_min_k4(j: int, scales) -> tuple:
     return int(sc.value), int(m.value)
 
 
-_DEQ = {Q8_0: "orc_dequant_q8_0", Q4_K: "orc_dequant_q4_k", Q6_K: "orc_dequant_q6_k", F32: "orc_dequant_f32",
+_DEQ = {Q5_0: "orc_dequant_q5_0", Q5_K: "orc_dequant_q5_k", Q8_0: "orc_dequant_q8_0", Q4_K: "orc_dequant_q4_k", Q6_K: "orc_dequant_q6_k", F32: "orc_dequant_f32",
         F16: "orc_dequant_f16", BF16: "orc_dequant_bf16"}
 
 
@@ -181,6 +186,24 @@ def get_rows(dtype: int, table, n_vocab: int, row_len: int, ids, threads: int = 
     out = np.empty((ids.size, row_len), dtype=np.float32)
     st = lib().orc_get_rows(dtype, _p(t), t.size, n_vocab, row_len, _p(ids), ids.size, _p(out), threads)
     return int(st), out
+
+
+def kv_bytes_per_token(dtype: int, hd: int) -> int:
+    return int(lib().orc_kv_bytes_per_token(dtype, hd))
+
+
+def kv_write_rows(dtype: int, x, pos, cache: np.ndarray) -> None:
+    """Packs the rows of x [T, hd] into the slots pos[t] of cache [max_seq, bytes_per_token] (uint8, in place)."""
+    x = _f32(x)
+    pos = np.ascontiguousarray(pos, dtype=np.int32)
+    T, hd = x.shape
+    lib().orc_kv_write_rows(dtype, _p(x), T, hd, _p(pos), _p(cache))
+
+
+def kv_read(dtype: int, cache: np.ndarray, n_pos: int, hd: int) -> np.ndarray:
+    out = np.empty((n_pos, hd), dtype=np.float32)
+    lib().orc_kv_read(dtype, _p(cache), n_pos, hd, _p(out))
+    return out
 
 
 def router_top2(logits):

@@ -61,6 +61,45 @@ sc = [int(np.uint8(np.int8(i - 6))) for i in range(16)]
 cases["q6_k_block"] = {
     "cite": "src/quant/q6_k.rs:148-164", "data": ql + qh + sc + [int(b) for b in f16_bytes(0.02)], "n": 256}
 
+# src/quant/q5_0.rs:89-125  roundtrip_single_block / high_bit_extremes (packer of q5_0.rs:68-87)
+def q5_0_block(scale, values):
+    qh = 0
+    qs = [0] * 16
+    for j in range(16):
+        v0, v1 = values[j] + 16, values[j + 16] + 16
+        if (v0 >> 4) & 1:
+            qh |= 1 << j
+        if (v1 >> 4) & 1:
+            qh |= 1 << (j + 16)
+        qs[j] = (v0 & 0x0F) | ((v1 & 0x0F) << 4)
+    return [int(b) for b in f16_bytes(scale)] + [(qh >> (8 * i)) & 0xFF for i in range(4)] + qs
+
+
+vals = [(i % 32) - 16 for i in range(32)]
+cases["q5_0_roundtrip"] = {"cite": "src/quant/q5_0.rs:89-107", "data": q5_0_block(0.5, vals), "n": 32,
+                           "expected": [0.5 * v for v in vals], "tol": 1e-4}
+vals = [0] * 32
+vals[0], vals[16], vals[1] = 15, -16, -1
+cases["q5_0_high_bit_extremes"] = {"cite": "src/quant/q5_0.rs:109-125", "data": q5_0_block(1.0, vals), "n": 32,
+                                   "expected_at": {"0": 15.0, "16": -16.0, "1": -1.0}}
+
+
+# src/quant/q5_k.rs:348-392  range / zero-scale / dot-vs-dequant blocks (d, dmin, scales[12], qh[32], qs[128])
+def q5_k_block(d, dmin, scales, qh, qs):
+    return [int(b) for b in f16_bytes(d)] + [int(b) for b in f16_bytes(dmin)] + list(scales) + list(qh) + list(qs)
+
+
+cases["q5_k_range"] = {"cite": "src/quant/q5_k.rs:348-363",
+                       "data": q5_k_block(1.0, 0.0, [0xFF] * 4 + [0] * 4 + [0x0F] * 4, [0xFF] * 32, [0xFF] * 128),
+                       "n": 256, "expected_all": 63.0 * 31.0, "tol": 1.0}
+cases["q5_k_zero_scale"] = {"cite": "src/quant/q5_k.rs:365-373",
+                            "data": q5_k_block(1.0, 0.0, [0] * 12, [0] * 32, [0] * 128), "n": 256,
+                            "expected_all": 0.0, "tol": 0.0}
+cases["q5_k_block"] = {"cite": "src/quant/q5_k.rs:375-392",
+                       "data": q5_k_block(0.05, -0.01, [10, 20, 30, 40, 50, 60, 70, 80, 0x3F, 0x2F, 0x1F, 0x0F],
+                                          [((i * 29) + 3) & 0xFF for i in range(32)],
+                                          [(i * 13) & 0xFF for i in range(128)]), "n": 256}
+
 # src/quant/mod.rs:176-205  f32 / f16 / bf16 rows
 cases["f32_row"] = {"cite": "src/quant/mod.rs:176-185",
                     "data": [int(b) for b in np.array([1.0, 2.0, -3.5], dtype="<f4").view(np.uint8)], "n": 3,

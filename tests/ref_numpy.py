@@ -45,6 +45,39 @@ def dequant_q4_k(data: np.ndarray, n: int) -> np.ndarray:
     return out.astype(np.float32).reshape(-1)[:n]
 
 
+def dequant_q5_k(data: np.ndarray, n: int) -> np.ndarray:
+    nb = (n + 255) // 256
+    blk = np.ascontiguousarray(data[: nb * 176]).reshape(nb, 176)
+    d, dmin = f16(blk[:, 0:2]), f16(blk[:, 2:4])
+    sc, m = scale_min_k4(blk[:, 4:16])
+    qh = blk[:, 16:48]                                   # [nb, 32]
+    qs = blk[:, 48:].reshape(nb, 4, 32)
+    sub = np.arange(8)
+    hbit = ((qh[:, None, :] >> sub[None, :, None]) & 1).astype(np.uint8) * 16   # sub-block s uses bit s
+    lo = (qs & 0xF)
+    hi = (qs >> 4)
+    q = np.stack([lo, hi], axis=2).reshape(nb, 8, 32) + hbit
+    dd = (d[:, None] * sc.astype(np.float32)).astype(np.float32)
+    mm = (dmin[:, None] * m.astype(np.float32)).astype(np.float32)
+    out = (dd[:, :, None] * q.astype(np.float32)).astype(np.float32) - mm[:, :, None]
+    return out.astype(np.float32).reshape(-1)[:n]
+
+
+def dequant_q5_0(data: np.ndarray, n: int) -> np.ndarray:
+    nb = (n + 31) // 32
+    blk = np.ascontiguousarray(data[: nb * 22]).reshape(nb, 22)
+    d = f16(blk[:, 0:2])
+    qh = np.ascontiguousarray(blk[:, 2:6]).view("<u4")[:, 0]
+    qs = blk[:, 6:]
+    j = np.arange(16)
+    b0 = ((qh[:, None] >> j[None, :]) & 1).astype(np.int32)
+    b1 = ((qh[:, None] >> (j[None, :] + 16)) & 1).astype(np.int32)
+    x0 = ((qs & 0xF).astype(np.int32) | (b0 << 4)) - 16
+    x1 = ((qs >> 4).astype(np.int32) | (b1 << 4)) - 16
+    x = np.concatenate([x0, x1], axis=1).astype(np.float32)
+    return (x * d[:, None]).astype(np.float32).reshape(-1)[:n]
+
+
 def dequant_q6_k(data: np.ndarray, n: int) -> np.ndarray:
     nb = (n + 255) // 256
     blk = np.ascontiguousarray(data[: nb * 210]).reshape(nb, 210)

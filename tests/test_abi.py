@@ -43,7 +43,9 @@ def test_type_size_matches_reference_table(lib):  # src/types.rs:88-168
     assert lib.agn_type_size(_abi.AGN_Q6_K, 4096) == 3360
     assert lib.agn_type_size(_abi.AGN_Q8_0, 33) == 68
     assert lib.agn_type_size(_abi.AGN_BF16, 5) == 10
-    assert lib.agn_type_size(13, 256) == 0  # Q5_K: no kernel
+    assert lib.agn_type_size(_abi.AGN_Q5_K, 512) == 352
+    assert lib.agn_type_size(_abi.AGN_Q5_0, 64) == 44
+    assert lib.agn_type_size(10, 256) == 0  # Q2_K: no kernel
 
 
 def test_status_strings_and_name(lib):

@@ -4,7 +4,7 @@ same seeded inputs.  get_rows is bit-exact; the float ops are within 1e-5 of the
 import numpy as np
 import pytest
 
-from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q4_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
+from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
                                  AGN_ROPE_NORMAL, BackendError, synth)
 from oracle import oracle as orc
 
@@ -149,6 +149,16 @@ def test_qk_norm_rope_qk_one_launch(backend):
     assert rel(backend.read(dk, np.float32, k.shape), rk) <= TOL
 
 
+def test_qk_norm_alone_is_the_fused_op_without_rotation(backend):
+    # `qk_norm` (src/model/llama/cpu_path.rs:78-93) without rope: n_rot = 0
+    T, nh, hd = 50, 8, 128
+    x = synth.activations(3, "q", (T, nh * hd)); w = synth.norm_weight(3, "wq", hd)
+    ref = orc.rms_norm_rows(x.reshape(T * nh, hd), w, 1e-6).reshape(T, nh * hd)
+    dx = backend.upload(x)
+    backend.launch_qk_norm_rope(dx, backend.upload(w), T, nh, hd, 1e-6, 0, None, 1e6)
+    assert rel(backend.read(dx, np.float32, x.shape), ref) <= TOL
+
+
 def test_rope_rejects_bad_arguments(backend):
     dx = backend.empty(4 * 128)
     for n_rot in (130, 63, -2):
@@ -244,6 +254,8 @@ def test_softmax_decode_shape_with_offset_and_stride(backend):
     (AGN_Q8_0, 128256, 2048, 512), (AGN_Q4_K, 152064, 3584, 4096), (AGN_Q6_K, 16384, 4096, 2048),
     (AGN_Q4_K, 32000, 4096, 512), (AGN_Q8_0, 100, 96, 33), (AGN_Q8_0, 64, 33, 17), (AGN_Q6_K, 50, 768, 50),
     (AGN_Q6_K, 20, 300, 9), (AGN_Q4_K, 20, 300, 9), (AGN_Q4_K, 7, 256, 1), (AGN_Q8_0, 1, 32, 5),
+    (AGN_Q5_K, 32000, 4096, 2048), (AGN_Q5_K, 20, 300, 9), (AGN_Q5_0, 4096, 2048, 1024), (AGN_Q5_0, 64, 33, 17),
+    (AGN_Q5_0, 10, 96, 33),
 ])
 def test_get_rows_bit_exact(backend, dtype, vocab, row_len, T):
     table = synth.quant_table(dtype, vocab, row_len, cfg_index=2)
@@ -295,8 +307,8 @@ def test_get_rows_argument_errors(backend):
     t = backend.empty(4096)
     ids = backend.upload(np.zeros(1, np.uint32))
     o = backend.empty(4 * 256)
-    with pytest.raises(BackendError) as e:  # Q5_K has no kernel: "not yet implemented" in the reference too
-        backend.get_rows(13, t, 4096, 1, 256, ids, 1, out=o)
+    with pytest.raises(BackendError) as e:  # Q3_K has no codec: "dequantization not yet implemented" in the reference too
+        backend.get_rows(11, t, 4096, 1, 256, ids, 1, out=o)
     assert e.value.status == 2
     with pytest.raises(BackendError) as e:  # rows extend beyond the data section
         backend.get_rows(AGN_Q4_K, t, 100, 1, 256, ids, 1, out=o)

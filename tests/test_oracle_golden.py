@@ -42,7 +42,25 @@ def test_get_scale_min_k4_known_answers():  # src/quant/q4_k.rs:229-241
             assert orc.get_scale_min_k4(int(j), case["scales"]) == tuple(exp)
 
 
+def test_q5_0_reference_vectors():  # src/quant/q5_0.rs:89-125
+    c = KA["q5_0_roundtrip"]
+    st, out = orc.dequant(orc.Q5_0, _data("q5_0_roundtrip"), 32)
+    assert st == orc.OK and np.max(np.abs(out - np.array(c["expected"], dtype=np.float32))) < c["tol"]
+    st, out = orc.dequant(orc.Q5_0, _data("q5_0_high_bit_extremes"), 32)
+    for i, v in KA["q5_0_high_bit_extremes"]["expected_at"].items():
+        assert out[int(i)] == v
+
+
+def test_q5_k_reference_vectors():  # src/quant/q5_k.rs:348-373
+    for name in ("q5_k_range", "q5_k_zero_scale"):
+        c = KA[name]
+        st, out = orc.dequant(orc.Q5_K, _data(name), 256)
+        assert st == orc.OK and np.all(np.abs(out - c["expected_all"]) <= c["tol"])
+
+
 @pytest.mark.parametrize("name,dtype,fn", [("q8_0_three_blocks", orc.Q8_0, rn.dequant_q8_0),
+                                           ("q5_k_block", orc.Q5_K, rn.dequant_q5_k),
+                                           ("q5_0_roundtrip", orc.Q5_0, rn.dequant_q5_0),
                                            ("q4_k_block", orc.Q4_K, rn.dequant_q4_k),
                                            ("q6_k_block", orc.Q6_K, rn.dequant_q6_k)])
 def test_reference_test_blocks_match_numpy_statement(name, dtype, fn):
@@ -100,6 +118,7 @@ def test_f16_widening_is_exact_for_every_bit_pattern():
 
 
 @pytest.mark.parametrize("dtype,fn,blk", [(orc.Q8_0, rn.dequant_q8_0, 34 / 32), (orc.Q4_K, rn.dequant_q4_k, 144 / 256),
+                                          (orc.Q5_K, rn.dequant_q5_k, 176 / 256), (orc.Q5_0, rn.dequant_q5_0, 22 / 32),
                                           (orc.Q6_K, rn.dequant_q6_k, 210 / 256)])
 def test_random_blocks_match_numpy_statement_bitwise(dtype, fn, blk):
     from agention_infer_b200 import synth

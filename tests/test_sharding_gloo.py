@@ -72,3 +72,39 @@ def test_two_ranks_sharded_equals_unsharded():
     for rank, slowest, sums, whole in res:
         assert slowest == 10.0 + world - 1
         assert sharding.combine_checksums(sums) == whole
+
+
+def _liveness_worker(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    import datetime
+
+    import torch.distributed as dist
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30))
+    sharding.rendezvous(store, "step0", rank, world, timeout_s=20)
+    if rank == 2:
+        q.put((rank, "left"))  # this rank leaves between steps (host-side failure, nothing in flight)
+        return
+    try:
+        sharding.rendezvous(store, "step1", rank, world, timeout_s=1.5)
+        q.put((rank, "no failure seen"))
+    except sharding.RankFailure as e:
+        q.put((rank, e.missing))
+    if rank == 0:
+        import time
+        time.sleep(1.0)  # keep the store alive until the others have polled it
+
+
+def test_a_rank_that_leaves_between_steps_is_named_by_the_others():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_liveness_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res[2] == "left"
+    assert res[0] == [2] and res[1] == [2]
