@@ -58,6 +58,9 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_rms_vpt = 0;
     ctx->tune_rms_recip = 1;
     ctx->tune_get_rows_threads = 0;
+    ctx->tune_get_rows_tma = 1;
+    ctx->tune_silu_unroll = 4;
+    ctx->tune_silu_threads = 256;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -124,6 +127,18 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     }
     if (strcmp(name, "rms_vpt") == 0) {
         ctx->tune_rms_vpt = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "silu_unroll") == 0 && (value == 2 || value == 4 || value == 8)) {
+        ctx->tune_silu_unroll = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "silu_threads") == 0 && (value == 128 || value == 256 || value == 512)) {
+        ctx->tune_silu_threads = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "get_rows_tma") == 0) {
+        ctx->tune_get_rows_tma = value != 0;
         return AGN_OK;
     }
     if (strcmp(name, "get_rows_threads") == 0) {

@@ -10,11 +10,12 @@
 // operations; every one of them is spelled with __fmul_rn / __fsub_rn so nothing is
 // contracted into an FMA, and f16 -> f32 is the exact widening.
 //
-// Data movement: one CTA per token.  The quantised row (2-3.4 KB) is staged into shared
-// memory with 16-byte cp.async copies — Q8_0 (34 B) and Q6_K (210 B) blocks are only
-// 2-byte aligned, so they cannot be read with wide loads directly — then decoded from
-// shared memory four outputs per thread and written with coalesced 128-bit streaming
-// stores.  Traffic is dominated by the f32 output (4*row_len bytes vs <= 1.06*row_len in).
+// Data movement: one small CTA per token.  The quantised row (2-3.4 KB) is staged into
+// shared memory by one bulk asynchronous copy (TMA `cp.async.bulk`, completed on an mbarrier
+// with a bounded wait; 16-byte cp.async copies for the last bytes of the table or when the
+// option "get_rows_tma" is 0) — Q8_0 (34 B) and Q6_K (210 B) blocks are only 2-byte aligned,
+// so they cannot be read with wide loads directly — then decoded from shared memory four
+// outputs per thread and written with coalesced 128-bit streaming stores.  Traffic is dominated by the f32 output (4*row_len bytes vs <= 1.06*row_len in).
 #include <cuda_fp16.h>
 
 #include "agn_common.cuh"
@@ -176,12 +177,51 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
-template <int DTYPE, bool VEC_OUT>
+// --- staging of the quantised row into shared memory ---------------------------------------
+// Preferred: one bulk asynchronous copy (TMA, `cp.async.bulk` into this CTA's own shared memory) issued by one
+// thread and completed on an mbarrier; it needs 16-byte aligned source, destination and size,
+// which holds whenever the 16-byte rounded row lies inside the table.  Otherwise (the last
+// bytes of the table) 16-byte cp.async copies with a byte-wise tail.
+constexpr int MBAR_SPIN_LIMIT = 1 << 22;  // bounded wait: a few hundred ms at most, then an error flag
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(d),
+                 "l"(gmem_src), "r"(bytes), "r"(b)
+                 : "memory");
+}
+// true once the phase with the given parity has completed; gives up after MBAR_SPIN_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+    for (int it = 0; it < MBAR_SPIN_LIMIT; it++) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done)
+                     : "r"(b), "r"(parity)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+template <int DTYPE, bool VEC_OUT, bool TMA>
 __global__ void __launch_bounds__(256)
 get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
                 const uint32_t *__restrict__ ids, float *__restrict__ out, uint32_t *flags) {
+    extern __shared__ __align__(128) uint8_t stage[];
+    __shared__ __align__(8) uint64_t bar;
+    if (TMA) {
+        if (threadIdx.x == 0) mbar_init(&bar, 1);
+        __syncthreads();  // barrier initialised before anyone polls it (runs ahead of the dependency wait)
+    }
     agn_pdl_prologue();
-    extern __shared__ __align__(16) uint8_t stage[];
     const int64_t t = blockIdx.x;
     const uint32_t id = ids[t];
     float *o_row = out + t * (int64_t)row_len;
@@ -196,17 +236,28 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     const size_t a0 = start & ~(size_t)15;
     const int lead = (int)(start - a0);
     const int n16 = (lead + row_bytes + 15) >> 4;
-    for (int c = threadIdx.x; c < n16; c += blockDim.x) {
-        const size_t off = a0 + 16 * (size_t)c;
-        if (off + 16 <= table_bytes) {
-            cp_async16(stage + 16 * c, table + off);
-        } else {
-            // last chunk of the table: copy only the bytes that exist
-            for (int b = 0; b < 16; b++) stage[16 * c + b] = off + b < table_bytes ? table[off + b] : 0;
+    const bool bulk = TMA && a0 + 16 * (size_t)n16 <= table_bytes;  // same answer in every thread of the CTA
+    if (bulk) {
+        if (threadIdx.x == 0) bulk_load(stage, table + a0, 16u * (uint32_t)n16, &bar);
+        if (!mbar_wait(&bar, 0)) {
+            // the copy may still be writing shared memory: wait once more, bounded, before leaving
+            if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_TIMEOUT);
+            (void)mbar_wait(&bar, 0);
+            return;
         }
+    } else {
+        for (int c = threadIdx.x; c < n16; c += blockDim.x) {
+            const size_t off = a0 + 16 * (size_t)c;
+            if (off + 16 <= table_bytes) {
+                cp_async16(stage + 16 * c, table + off);
+            } else {
+                // last chunk of the table: copy only the bytes that exist
+                for (int b = 0; b < 16; b++) stage[16 * c + b] = off + b < table_bytes ? table[off + b] : 0;
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
     }
-    cp_async_wait_all();
-    __syncthreads();
     const uint8_t *row = stage + lead;
     for (int j = threadIdx.x; j < n4; j += blockDim.x) {
         // a partial last block is fully present in the table (type_size rounds up to whole
@@ -227,10 +278,15 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
 template <int DTYPE>
 void launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
                      size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, float *out) {
-    if (vec)
-        agn_launch(ctx, get_rows_kernel<DTYPE, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+    const bool tma = ctx->tune_get_rows_tma != 0;
+    if (vec && tma)
+        agn_launch(ctx, get_rows_kernel<DTYPE, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+    else if (vec)
+        agn_launch(ctx, get_rows_kernel<DTYPE, true, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+    else if (tma)
+        agn_launch(ctx, get_rows_kernel<DTYPE, false, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
     else
-        agn_launch(ctx, get_rows_kernel<DTYPE, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, false, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
 }
 
 }  // namespace
@@ -266,9 +322,13 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
         // opt in to large dynamic shared memory for very long rows
         cudaError_t e = cudaSuccess;
 #define AGN_GR_ATTR(DT)                                                                                               \
-    e = cudaFuncSetAttribute(get_rows_kernel<DT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    e = cudaFuncSetAttribute(get_rows_kernel<DT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e == cudaSuccess)                                                                                              \
-        e = cudaFuncSetAttribute(get_rows_kernel<DT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(get_rows_kernel<DT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess)                                                                                              \
+        e = cudaFuncSetAttribute(get_rows_kernel<DT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess)                                                                                              \
+        e = cudaFuncSetAttribute(get_rows_kernel<DT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         switch (dtype) {
         case AGN_Q8_0: AGN_GR_ATTR(AGN_Q8_0) break;
         case AGN_Q4_K: AGN_GR_ATTR(AGN_Q4_K) break;

@@ -26,7 +26,7 @@ __device__ __forceinline__ float4 silu_mul4(float4 g, float4 u) {
 // Each CTA owns a contiguous tile of UNROLL * blockDim float4; a thread issues all of its
 // 2*UNROLL loads before the first use so that UNROLL*32 B per thread are in flight.
 template <int UNROLL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 silu_mul_vec4_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ up,
                      float4 *__restrict__ out, int64_t n4) {
     agn_pdl_prologue();
@@ -63,7 +63,7 @@ extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float
     if (n == 0) return AGN_OK;
     if (!gate || !up || !out) return agn_fail(ctx, AGN_EINVAL, "silu_mul: null pointer");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
-    constexpr int THREADS = 256, UNROLL = 4;
+    const int THREADS = ctx->tune_silu_threads, UNROLL = ctx->tune_silu_unroll;
     int64_t done = 0;
     if (agn_aligned16(gate) && agn_aligned16(up) && agn_aligned16(out)) {
         const int64_t n4 = n / 4;
@@ -71,9 +71,11 @@ extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float
             const int64_t per_cta = (int64_t)THREADS * UNROLL;
             const int64_t blocks = (n4 + per_cta - 1) / per_cta;
             if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: n too large");
-            agn_launch(ctx, silu_mul_vec4_kernel<UNROLL>, dim3((unsigned)blocks), dim3(THREADS), 0, 
-                reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(up),
-                reinterpret_cast<float4 *>(out), n4);
+            const float4 *g4 = reinterpret_cast<const float4 *>(gate), *u4 = reinterpret_cast<const float4 *>(up);
+            float4 *o4 = reinterpret_cast<float4 *>(out);
+            if (UNROLL == 2) agn_launch(ctx, silu_mul_vec4_kernel<2>, dim3((unsigned)blocks), dim3(THREADS), 0, g4, u4, o4, n4);
+            else if (UNROLL == 8) agn_launch(ctx, silu_mul_vec4_kernel<8>, dim3((unsigned)blocks), dim3(THREADS), 0, g4, u4, o4, n4);
+            else agn_launch(ctx, silu_mul_vec4_kernel<4>, dim3((unsigned)blocks), dim3(THREADS), 0, g4, u4, o4, n4);
             AGN_LAUNCHED(ctx, "silu_mul_vec4");
         }
         done = n4 * 4;

@@ -363,7 +363,9 @@ def run_ours(args, cfg, ops_list, wl):
     def step(i, silu_events=None):
         b = sets[i % nsets]
         for name in order:
-            if silu_events is not None and name == "silu_mul":
+            # events around the dominant kernel on every 4th step only: an event between two
+            # kernels breaks their programmatic overlap, so sampling keeps the timed region honest
+            if silu_events is not None and name == "silu_mul" and i % 4 == 0:
                 e0, e1 = silu_events
                 e0.record(stream); ops[name](b); e1.record(stream)
             else:
@@ -397,7 +399,7 @@ def run_ours(args, cfg, ops_list, wl):
     barrier()
     launches = be.launch_count - n0
     elapsed_ms = sharding.max_over_ranks(start.elapsed_time(stop))
-    silu_ms = float(np.mean([a.elapsed_time(b) for a, b in silu_ev]))
+    silu_ms = float(np.mean([a.elapsed_time(b) for i, (a, b) in enumerate(silu_ev) if i % 4 == 0]))
     ms_per_step = elapsed_ms / args.steps
     value = T_total / (ms_per_step * 1e-3)
 

@@ -269,6 +269,25 @@ def test_get_rows_bit_exact(backend, dtype, vocab, row_len, T):
     assert np.array_equal(bits(got), bits(ref))
 
 
+@pytest.mark.parametrize("dtype,vocab,row_len,T", [(AGN_Q4_K, 4096, 3584, 2048), (AGN_Q8_0, 300, 96, 300),
+                                                   (AGN_Q6_K, 128, 768, 128), (AGN_Q5_0, 64, 33, 64), (AGN_Q6_K, 50, 4096, 50)])
+def test_get_rows_both_staging_paths_bit_exact(backend, dtype, vocab, row_len, T):
+    # default staging is one bulk asynchronous copy (TMA, cp.async.bulk + mbarrier) per row, with
+    # rows that start off a 16-byte boundary and the last row of the table (which falls back to
+    # cp.async); with the option off every row is staged by 16-byte cp.async copies
+    table = synth.quant_table(dtype, vocab, row_len, cfg_index=3)
+    ids = synth.token_ids(3, T, vocab); ids[0], ids[-1] = vocab - 1, 0
+    st, ref = orc.get_rows(dtype, table, vocab, row_len, ids, THREADS)
+    dt, di = backend.upload(table), backend.upload(ids)
+    got_tma = backend.read(backend.get_rows(dtype, dt, table.nbytes, vocab, row_len, di, T), np.float32, (T, row_len))
+    backend.set_option("get_rows_tma", 0)
+    try:
+        got_cp = backend.read(backend.get_rows(dtype, dt, table.nbytes, vocab, row_len, di, T), np.float32, (T, row_len))
+    finally:
+        backend.set_option("get_rows_tma", 1)
+    assert st == orc.OK and np.array_equal(bits(got_tma), bits(ref)) and np.array_equal(bits(got_cp), bits(ref))
+
+
 @pytest.mark.parametrize("dtype,np_dtype", [(AGN_F32, np.float32), (AGN_F16, np.float16), (AGN_BF16, None)])
 def test_get_rows_plain_types(backend, dtype, np_dtype):
     vocab, row_len, T = 40, 72, 25
