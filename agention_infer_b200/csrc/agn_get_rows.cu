@@ -169,6 +169,100 @@ __device__ __forceinline__ float4 decode4<AGN_F32>(const uint8_t *row, int e0) {
                        __uint_as_float(ld_u32_2(p + 12)));
 }
 
+// Eight outputs per call: two float4 at elements ea and eb of the row.  For the K-quants the
+// two float4 are the low- and the high-nibble values of the same four quant bytes, so the
+// bytes, the super-block scales and (Q5_K, Q6_K) the high-bit word are loaded and unpacked
+// once for both; eight consecutive units still write 128 contiguous bytes per float4.
+template <int DTYPE>
+__device__ __forceinline__ void decode8(const uint8_t *row, int u, int row_len, int &ea, float4 &va, int &eb, float4 &vb) {
+    ea = 8 * u;
+    eb = 8 * u + 4;
+    va = decode4<DTYPE>(row, ea);
+    vb = eb < row_len ? decode4<DTYPE>(row, eb) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__device__ __forceinline__ void k4_scale_min(const uint8_t *sc, int j, uint32_t &s, uint32_t &m) {
+    if (j < 4) {
+        s = sc[j] & 63;
+        m = sc[j + 4] & 63;
+    } else {
+        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
+        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode8<AGN_Q4_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
+    const uint8_t *blk = row + (u >> 5) * 144;
+    const int r = u & 31, g = r >> 3, l = (r & 7) * 4;
+    ea = (u >> 5) * 256 + 64 * g + l;
+    eb = ea + 32;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
+    uint32_t s0, m0, s1, m1;
+    k4_scale_min(blk + 4, 2 * g, s0, m0);
+    k4_scale_min(blk + 4, 2 * g + 1, s1, m1);
+    const float d1 = __fmul_rn(d, (float)s0), mm1 = __fmul_rn(dmin, (float)m0);
+    const float d2 = __fmul_rn(d, (float)s1), mm2 = __fmul_rn(dmin, (float)m1);
+    const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l);
+    va.x = __fsub_rn(__fmul_rn(d1, (float)(q & 0xF)), mm1);
+    va.y = __fsub_rn(__fmul_rn(d1, (float)((q >> 8) & 0xF)), mm1);
+    va.z = __fsub_rn(__fmul_rn(d1, (float)((q >> 16) & 0xF)), mm1);
+    va.w = __fsub_rn(__fmul_rn(d1, (float)((q >> 24) & 0xF)), mm1);
+    vb.x = __fsub_rn(__fmul_rn(d2, (float)((q >> 4) & 0xF)), mm2);
+    vb.y = __fsub_rn(__fmul_rn(d2, (float)((q >> 12) & 0xF)), mm2);
+    vb.z = __fsub_rn(__fmul_rn(d2, (float)((q >> 20) & 0xF)), mm2);
+    vb.w = __fsub_rn(__fmul_rn(d2, (float)(q >> 28)), mm2);
+}
+
+template <>
+__device__ __forceinline__ void decode8<AGN_Q5_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
+    const uint8_t *blk = row + (u >> 5) * 176;
+    const int r = u & 31, g = r >> 3, l = (r & 7) * 4;
+    ea = (u >> 5) * 256 + 64 * g + l;
+    eb = ea + 32;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
+    uint32_t s0, m0, s1, m1;
+    k4_scale_min(blk + 4, 2 * g, s0, m0);
+    k4_scale_min(blk + 4, 2 * g + 1, s1, m1);
+    const float d1 = __fmul_rn(d, (float)s0), mm1 = __fmul_rn(dmin, (float)m0);
+    const float d2 = __fmul_rn(d, (float)s1), mm2 = __fmul_rn(dmin, (float)m1);
+    const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 16 + l) >> (2 * g);  // bit 0: low run, bit 1: high run
+    const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * g + l);
+    va.x = __fsub_rn(__fmul_rn(d1, (float)((q & 0xF) + ((qh & 1) << 4))), mm1);
+    va.y = __fsub_rn(__fmul_rn(d1, (float)(((q >> 8) & 0xF) + (((qh >> 8) & 1) << 4))), mm1);
+    va.z = __fsub_rn(__fmul_rn(d1, (float)(((q >> 16) & 0xF) + (((qh >> 16) & 1) << 4))), mm1);
+    va.w = __fsub_rn(__fmul_rn(d1, (float)(((q >> 24) & 0xF) + (((qh >> 24) & 1) << 4))), mm1);
+    vb.x = __fsub_rn(__fmul_rn(d2, (float)(((q >> 4) & 0xF) + (((qh >> 1) & 1) << 4))), mm2);
+    vb.y = __fsub_rn(__fmul_rn(d2, (float)(((q >> 12) & 0xF) + (((qh >> 9) & 1) << 4))), mm2);
+    vb.z = __fsub_rn(__fmul_rn(d2, (float)(((q >> 20) & 0xF) + (((qh >> 17) & 1) << 4))), mm2);
+    vb.w = __fsub_rn(__fmul_rn(d2, (float)((q >> 28) + (((qh >> 25) & 1) << 4))), mm2);
+}
+
+template <>
+__device__ __forceinline__ void decode8<AGN_Q6_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
+    const uint8_t *blk = row + (u >> 5) * 210;
+    const int r = u & 31, h = r >> 4, cp = (r >> 3) & 1, l = (r & 7) * 4;
+    ea = (u >> 5) * 256 + 128 * h + 32 * cp + l;  // quadrant cp: low nibbles
+    eb = ea + 64;                                 // quadrant cp + 2: high nibbles of the same bytes
+    const uint32_t ql = ld_u32_2(blk + h * 64 + cp * 32 + l);
+    const uint32_t qh = ld_u32_2(blk + 128 + h * 32 + l) >> (2 * cp);
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * h + (l >> 4) + 2 * cp);
+    const float d = f16_bits_to_f32(ld_u16(blk + 208));
+    const float da = __fmul_rn(d, (float)sc[0]), db = __fmul_rn(d, (float)sc[4]);
+    va.x = __fmul_rn(da, (float)((int)((ql & 0xF) | ((qh & 3) << 4)) - 32));
+    va.y = __fmul_rn(da, (float)((int)(((ql >> 8) & 0xF) | (((qh >> 8) & 3) << 4)) - 32));
+    va.z = __fmul_rn(da, (float)((int)(((ql >> 16) & 0xF) | (((qh >> 16) & 3) << 4)) - 32));
+    va.w = __fmul_rn(da, (float)((int)(((ql >> 24) & 0xF) | (((qh >> 24) & 3) << 4)) - 32));
+    vb.x = __fmul_rn(db, (float)((int)(((ql >> 4) & 0xF) | (((qh >> 4) & 3) << 4)) - 32));
+    vb.y = __fmul_rn(db, (float)((int)(((ql >> 12) & 0xF) | (((qh >> 12) & 3) << 4)) - 32));
+    vb.z = __fmul_rn(db, (float)((int)(((ql >> 20) & 0xF) | (((qh >> 20) & 3) << 4)) - 32));
+    vb.w = __fmul_rn(db, (float)((int)((ql >> 28) | (((qh >> 28) & 3) << 4)) - 32));
+}
+
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
@@ -225,7 +319,6 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     const int64_t t = blockIdx.x;
     const uint32_t id = ids[t];
     float *o_row = out + t * (int64_t)row_len;
-    const int n4 = (row_len + 3) >> 2;
     if ((int64_t)id >= n_rows) {
         // "row index out of range": zero row + error flag, never a trap
         for (int j = threadIdx.x; j < row_len; j += blockDim.x) o_row[j] = 0.0f;
@@ -259,18 +352,25 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
         __syncthreads();
     }
     const uint8_t *row = stage + lead;
-    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
-        // a partial last block is fully present in the table (type_size rounds up to whole
-        // blocks), so decoding 4 values is always in bounds; only the store is clipped
-        const float4 v = decode4<DTYPE>(row, 4 * j);
+    // a partial last block is fully present in the table (type_size rounds up to whole blocks),
+    // so decoding past row_len inside it stays in bounds; only the stores are clipped
+    // K-quant units are numbered per 256-value super-block (32 units each, not in element order)
+    constexpr bool K_QUANT = DTYPE == AGN_Q4_K || DTYPE == AGN_Q5_K || DTYPE == AGN_Q6_K;
+    const int n8 = K_QUANT ? ((row_len + 255) >> 8) * 32 : (row_len + 7) >> 3;
+    for (int u = threadIdx.x; u < n8; u += blockDim.x) {
+        int ea, eb;
+        float4 va, vb;
+        decode8<DTYPE>(row, u, row_len, ea, va, eb, vb);
         if (VEC_OUT) {
-            agn_st_stream(reinterpret_cast<float4 *>(o_row) + j, v);
+            if (ea < row_len) agn_st_stream(reinterpret_cast<float4 *>(o_row + ea), va);
+            if (eb < row_len) agn_st_stream(reinterpret_cast<float4 *>(o_row + eb), vb);
         } else {
-            const int e = 4 * j;
-            if (e < row_len) o_row[e] = v.x;
-            if (e + 1 < row_len) o_row[e + 1] = v.y;
-            if (e + 2 < row_len) o_row[e + 2] = v.z;
-            if (e + 3 < row_len) o_row[e + 3] = v.w;
+            const float a[4] = {va.x, va.y, va.z, va.w}, b[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (ea + i < row_len) o_row[ea + i] = a[i];
+                if (eb + i < row_len) o_row[eb + i] = b[i];
+            }
         }
     }
 }
@@ -312,7 +412,7 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
     const int n4 = (int)((row_len + 3) / 4);
     // small CTAs (8 float4 per thread): more rows resident per SM hides the id -> row -> decode
     // latency chain better than wide CTAs do (measured: 128 threads beat 224 by 15% at H=3584)
-    int threads = ((n4 + 7) / 8 + 31) / 32 * 32;
+    int threads = ((n4 + 7) / 8 + 31) / 32 * 32;  // four 8-value units per thread
     if (threads < 64) threads = 64;
     if (threads > 256) threads = 256;
     if (ctx->tune_get_rows_threads >= 32 && ctx->tune_get_rows_threads <= 256) threads = ctx->tune_get_rows_threads & ~31;
