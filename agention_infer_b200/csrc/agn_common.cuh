@@ -96,9 +96,11 @@ static inline bool agn_aligned16(const void *p) { return (reinterpret_cast<uintp
 // agn_pdl_prologue(): it lets the next kernel in the stream be scheduled onto SMs as this
 // grid's CTAs retire (hiding its launch latency), and it blocks until the previous grid has
 // completed and flushed its writes, before the first global access of this one.
+__device__ __forceinline__ void agn_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void agn_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void agn_pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    agn_pdl_launch_dependents();
+    agn_pdl_wait();
 }
 
 template <typename... KArgs, typename... Args>

@@ -66,7 +66,7 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
 template <int W, int VPL, int MODE, bool NORM>
 __global__ void __launch_bounds__(256)
 rope_heads_kernel(const RopeArgs a) {
-    agn_pdl_prologue();
+    agn_pdl_launch_dependents();
     constexpr int NS = VPL == 4 ? 2 : 4;  // head rows in flight per lane group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int half = a.n_rot >> 1;
@@ -91,6 +91,9 @@ rope_heads_kernel(const RopeArgs a) {
         s_meta[hr] = tt | (h < a.n_q ? 0 : 1 << 16);
     }
     __syncthreads();
+    // everything above used kernel parameters and shared memory only; global memory (which the
+    // previous kernel of the stream may still be writing) is touched from here on
+    agn_pdl_wait();
 
     const int lane = threadIdx.x & (W - 1);
     const int group = threadIdx.x / W;
