@@ -29,6 +29,10 @@ SIGNATURES = {
     "agn_ctx_get_stream": (_i32, [_vp, _pp]),
     "agn_ctx_launch_count": (C.c_uint64, [_vp]),
     "agn_launch_noop": (_i32, [_vp]),
+    "agn_graph_begin": (_i32, [_vp]),
+    "agn_graph_end": (_i32, [_vp, _pp]),
+    "agn_graph_launch": (_i32, [_vp, _vp]),
+    "agn_graph_destroy": (_i32, [_vp, _vp]),
     "agn_ctx_set_option": (_i32, [_vp, C.c_char_p, _i64]),
     "agn_malloc": (_i32, [_vp, _sz, _pp]),
     "agn_free": (_i32, [_vp, _vp]),

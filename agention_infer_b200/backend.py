@@ -92,6 +92,21 @@ class CudaBackend:
     def launch_count(self) -> int:
         return int(self._lib.agn_ctx_launch_count(self._ctx))
 
+    def graph_begin(self) -> None:
+        """Start recording the ops enqueued on this backend into a CUDA graph."""
+        self._check(self._lib.agn_graph_begin(self._ctx))
+
+    def graph_end(self) -> int:
+        g = C.c_void_p()
+        self._check(self._lib.agn_graph_end(self._ctx, C.byref(g)))
+        return g.value
+
+    def graph_launch(self, graph: int) -> None:
+        self._check(self._lib.agn_graph_launch(self._ctx, graph))
+
+    def graph_destroy(self, graph: int) -> None:
+        self._check(self._lib.agn_graph_destroy(self._ctx, graph))
+
     def launch_noop(self) -> None:
         """One empty kernel (the launch-latency floor)."""
         self._check(self._lib.agn_launch_noop(self._ctx))

@@ -39,6 +39,8 @@ struct agn_ctx {
     size_t scratch_bytes;
     agn_host_pipe *host_pipe;   // created by the first host-slice call
     bool pdl;                   // launch kernels with programmatic stream serialization
+    bool capturing;             // between agn_graph_begin and agn_graph_end
+    uint64_t capture_launches0;
     int tune_rms_vpt;           // 0 = automatic; 1/2/4/8 float4 per thread in rms_norm
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic

@@ -55,6 +55,8 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->scratch_bytes = 0;
     ctx->host_pipe = nullptr;
     ctx->pdl = true;
+    ctx->capturing = false;
+    ctx->capture_launches0 = 0;
     ctx->tune_rms_vpt = 0;
     ctx->tune_rms_recip = 1;
     ctx->tune_get_rows_threads = 0;
@@ -157,6 +159,7 @@ int32_t agn_malloc(agn_ctx *ctx, size_t bytes, void **dptr) {
     if (!dptr) return agn_fail(ctx, AGN_EINVAL, "agn_malloc: null out pointer");
     *dptr = nullptr;
     if (bytes == 0) return AGN_OK;
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_malloc: allocation would invalidate the open graph capture");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaError_t e = cudaMalloc(dptr, bytes);
     if (e == cudaErrorMemoryAllocation) {
@@ -170,6 +173,7 @@ int32_t agn_malloc(agn_ctx *ctx, size_t bytes, void **dptr) {
 int32_t agn_free(agn_ctx *ctx, void *dptr) {
     AGN_CHECK_CTX(ctx);
     if (!dptr) return AGN_OK;
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_free: freeing would invalidate the open graph capture");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaFree(dptr));
     return AGN_OK;
@@ -180,6 +184,7 @@ int32_t agn_host_alloc(agn_ctx *ctx, size_t bytes, void **hptr) {
     if (!hptr) return agn_fail(ctx, AGN_EINVAL, "agn_host_alloc: null out pointer");
     *hptr = nullptr;
     if (bytes == 0) return AGN_OK;
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_host_alloc: allocation would invalidate the open graph capture");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaError_t e = cudaHostAlloc(hptr, bytes, cudaHostAllocDefault);
     if (e == cudaErrorMemoryAllocation) {
@@ -223,6 +228,7 @@ int32_t agn_memset(agn_ctx *ctx, void *dst, int value, size_t bytes) {
 
 int32_t agn_sync(agn_ctx *ctx) {
     AGN_CHECK_CTX(ctx);
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_sync: not allowed while a graph capture is open");
     if (ctx->flags_dirty) {
         AGN_CUDA(ctx, cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     }
@@ -298,6 +304,66 @@ size_t agn_type_size(int32_t dtype, size_t n) {
 namespace {
 __global__ void noop_kernel() { agn_pdl_prologue(); }
 }  // namespace
+
+struct agn_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;  // kernels recorded, added to the launch count at every replay
+};
+
+// Records every op enqueued on the context's stream between begin and end into a CUDA graph
+// instead of running it.  The decode loop (a fixed chain of small kernels per token) is
+// launch-bound from any host language; one graph replay costs a fraction of a microsecond
+// per kernel.  The RoPE table of a (theta, n_rot) pair must already exist (run the chain
+// once before capturing it); agn_sync and memory allocation are not allowed inside.
+extern "C" int32_t agn_graph_begin(agn_ctx *ctx) {
+    AGN_CHECK_CTX(ctx);
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_graph_begin: a capture is already open");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    AGN_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    ctx->capture_launches0 = ctx->launches;
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_graph_end(agn_ctx *ctx, agn_graph **out) {
+    AGN_CHECK_CTX(ctx);
+    if (!out) return agn_fail(ctx, AGN_EINVAL, "agn_graph_end: null out pointer");
+    *out = nullptr;
+    if (!ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_graph_end: no capture is open");
+    ctx->capturing = false;
+    agn_graph *g = new agn_graph();
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        if (g->graph) cudaGraphDestroy(g->graph);
+        delete g;
+        (void)cudaGetLastError();
+        return agn_fail(ctx, AGN_ECUDA, "agn_graph_end: %s", cudaGetErrorString(e));
+    }
+    g->kernels = ctx->launches - ctx->capture_launches0;
+    ctx->launches = ctx->capture_launches0;  // nothing ran yet
+    *out = g;
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_graph_launch(agn_ctx *ctx, agn_graph *g) {
+    AGN_CHECK_CTX(ctx);
+    if (!g || !g->exec) return agn_fail(ctx, AGN_EINVAL, "agn_graph_launch: null graph");
+    AGN_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    ctx->launches += g->kernels;
+    return AGN_OK;
+}
+
+extern "C" int32_t agn_graph_destroy(agn_ctx *ctx, agn_graph *g) {
+    AGN_CHECK_CTX(ctx);
+    if (!g) return AGN_OK;
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    (void)cudaGetLastError();
+    return AGN_OK;
+}
 
 // One empty kernel on the context's stream: the launch-latency floor that the decode-shaped
 // (launch-bound) measurements are compared with.

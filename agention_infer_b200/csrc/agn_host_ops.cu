@@ -93,6 +93,7 @@ template <class F>
 int32_t run_pipelined(agn_ctx *ctx, const char *name, int64_t n_rows, const HostBuf *bufs, int nb, F launch,
                       int64_t chunk_multiple = 1) {
     if (n_rows == 0) return AGN_OK;
+    if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "%s: host-slice ops cannot be recorded into a graph", name);
     agn_host_pipe *p = nullptr;
     int32_t rc = get_pipe(ctx, &p);
     if (rc != AGN_OK) return rc;

@@ -576,12 +576,11 @@ def run_decode_sweep(args):
         noops()
     torch.cuda.synchronize()
     floor_plain = timed(noops, 20)
-    g0 = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g0, stream=stream):
-        noops()
+    be.graph_begin(); noops(); g0 = be.graph_end()
     for _ in range(3):
-        g0.replay()
-    floor_graph = timed(g0.replay, 50)
+        be.graph_launch(g0)
+    floor_graph = timed(lambda: be.graph_launch(g0), 50)
+    be.graph_destroy(g0)
     for T in (1, 8, 32, 64):
         pos = torch.from_numpy(synth.positions(cfg.index, T, True)).to(dev)
         # one buffer set per layer: 28 layers of activations are distinct memory, as in the engine
@@ -604,17 +603,16 @@ def run_decode_sweep(args):
             chain()
         b_.record(stream); torch.cuda.synchronize()
         us_plain = a.elapsed_time(b_) * 1e3 / reps
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
-            chain()
+        be.graph_begin(); chain(); g = be.graph_end()  # recorded through the library's own graph entry points
         for _ in range(5):
-            g.replay()
+            be.graph_launch(g)
         torch.cuda.synchronize()
         a.record(stream)
         for _ in range(reps):
-            g.replay()
+            be.graph_launch(g)
         b_.record(stream); torch.cuda.synchronize()
         us_graph = a.elapsed_time(b_) * 1e3 / reps
+        be.graph_destroy(g)
         bytes_chain = layers * (8 * T * (nq + nkv) * hd + 12 * T * I)
         sweep.append({"T": T, "layers": layers, "launches": 2 * layers, "us_plain": round(us_plain, 2),
                       "us_graph": round(us_graph, 2), "us_per_layer_graph": round(us_graph / layers, 3),

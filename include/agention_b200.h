@@ -68,6 +68,7 @@ typedef enum agn_rope_layout { AGN_ROPE_NEOX = 0, AGN_ROPE_NORMAL = 1 } agn_rope
 typedef struct agn_ctx agn_ctx;     /* one device + one stream; replaces WgpuBackend's
                                        ComputeClient (src/ops/wgpu_backend/mod.rs) */
 typedef struct agn_event agn_event; /* device timestamp on the context's stream */
+typedef struct agn_graph agn_graph; /* a recorded chain of ops, replayed with one launch */
 
 /* ----------------------------------------------------------- context, memory */
 
@@ -118,6 +119,18 @@ AGN_API int32_t agn_event_create(agn_ctx *ctx, agn_event **ev);
 AGN_API int32_t agn_event_record(agn_ctx *ctx, agn_event *ev);
 AGN_API int32_t agn_event_elapsed_ms(agn_ctx *ctx, agn_event *start, agn_event *stop, float *ms);
 AGN_API int32_t agn_event_destroy(agn_ctx *ctx, agn_event *ev);
+
+/* CUDA graphs for launch-bound chains (the decode loop: a fixed sequence of small kernels
+ * per token).  Ops enqueued between begin and end are recorded, not run; agn_graph_launch
+ * replays them on the context's stream for a fraction of a microsecond per kernel.  The
+ * reference's counterpart is its queue of asynchronous launches with one final readback
+ * (src/model/llama/gpu_resident.rs:427-697).  Run the chain once before capturing it (the
+ * RoPE table of a (theta, n_rot) pair is built on first use); agn_sync, allocation and the
+ * host-slice entry points are not allowed inside a capture. */
+AGN_API int32_t agn_graph_begin(agn_ctx *ctx);
+AGN_API int32_t agn_graph_end(agn_ctx *ctx, agn_graph **out);
+AGN_API int32_t agn_graph_launch(agn_ctx *ctx, agn_graph *graph);
+AGN_API int32_t agn_graph_destroy(agn_ctx *ctx, agn_graph *graph);
 
 /* ---------------------------------------------------------------- layer ops */
 
