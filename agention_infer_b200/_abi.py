@@ -61,6 +61,13 @@ SIGNATURES = {
     "agn_kv_bytes_per_token": (_i64, [_i32, _i64]),
     "agn_router_top2_f32": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "agn_silu_mul_f16": (_i32, [_vp, _vp, _vp, _vp, _i64]),
+    "agn_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "agn_add_residual_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "agn_rope_qk_f16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),
+    "agn_qk_norm_rope_qk_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32, _f32,
+                                       _f32, _i32]),
+    "agn_get_rows_f16": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_host_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_host_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_host_rope_qk_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),

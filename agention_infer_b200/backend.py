@@ -314,6 +314,43 @@ class CudaBackend:
         out = self.get_rows(dtype, table, table_bytes, n_rows, row_len, ids, 1)
         return self.read(out, np.float32, (row_len,))
 
+    # ------------------------------------------------- f16 activation storage (the reference's `Act = f16`)
+    def launch_silu_mul_f16(self, gate, up, n: int, out=None):
+        if out is None:
+            out = self.empty(2 * n)
+        self._check(self._lib.agn_silu_mul_f16(self._ctx, _ptr(gate), _ptr(up), _ptr(out), n))
+        return out
+
+    def launch_rms_norm_f16(self, x, w, T: int, H: int, eps: float, out=None):
+        if out is None:
+            out = self.empty(2 * T * H)
+        self._check(self._lib.agn_rms_norm_f16(self._ctx, _ptr(x), _ptr(w), _ptr(out), T, H, eps))
+        return out
+
+    def launch_add_residual_rms_norm_f16(self, x, delta, w, T: int, H: int, eps: float, new_x=None, normed=None):
+        if new_x is None:
+            new_x = self.empty(2 * T * H)
+        if normed is None:
+            normed = self.empty(2 * T * H)
+        self._check(self._lib.agn_add_residual_rms_norm_f16(self._ctx, _ptr(x), _ptr(delta), _ptr(w), _ptr(new_x),
+                                                            _ptr(normed), T, H, eps))
+        return new_x, normed
+
+    def launch_qk_norm_rope_qk_f16(self, q, k, wq, wk, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, eps: float,
+                                   n_rot: int, pos, theta: float, freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX,
+                                   pos_start: int = 0) -> None:
+        """f16 q/k in place; wq = wk = None is rope without the norm; k = None with n_kv_heads = 0 is one buffer."""
+        self._check(self._lib.agn_qk_norm_rope_qk_f16(self._ctx, _ptr(q), _ptr(k), _ptr(wq), _ptr(wk), T, n_q_heads,
+                                                      n_kv_heads, head_dim, eps, n_rot, _ptr(pos), pos_start, theta,
+                                                      freq_scale, layout))
+
+    def get_rows_f16(self, dtype: int, table, table_bytes: int, n_rows: int, row_len: int, ids, T: int, out=None):
+        if out is None:
+            out = self.empty(2 * T * row_len)
+        self._check(self._lib.agn_get_rows_f16(self._ctx, dtype, _ptr(table), table_bytes, n_rows, row_len, _ptr(ids), T,
+                                               _ptr(out)))
+        return out
+
     # ------------------------------------------------- host-slice ops (activations in host memory)
     # The arrays must stay alive and unmodified until sync(); pinned arrays (pinned()) make the
     # transfers asynchronous.  Weights / tables are device buffers.

@@ -91,6 +91,7 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
     } while (0)
 
 static inline bool agn_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool agn_aligned(const void *p, int a) { return (reinterpret_cast<uintptr_t>(p) & (uintptr_t)(a - 1)) == 0; }
 
 #ifdef __CUDACC__
 
@@ -131,6 +132,42 @@ __device__ __forceinline__ float agn_warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// Activation storage.  The kernels compute in f32; activations are stored as f32 or, like the
+// reference's default `Act` type (src/ops/mod.rs:36-45), as f16 (converted with round to
+// nearest even on store, `Act::cast_from`).  ActVec<T> moves four consecutive activations:
+// one 128-bit access for f32, one 64-bit access for f16.
+template <typename T> struct ActVec;
+template <> struct ActVec<float> {
+    static constexpr int ALIGN = 16;
+    static __device__ __forceinline__ float4 load(const float *p, int64_t vec) {
+        return __ldcs(reinterpret_cast<const float4 *>(p) + vec);
+    }
+    static __device__ __forceinline__ void store(float *p, int64_t vec, float4 v) {
+        __stcs(reinterpret_cast<float4 *>(p) + vec, v);
+    }
+    static __device__ __forceinline__ float load1(const float *p, int64_t i) { return p[i]; }
+    static __device__ __forceinline__ void store1(float *p, int64_t i, float v) { p[i] = v; }
+};
+#include <cuda_fp16.h>
+template <> struct ActVec<__half> {
+    static constexpr int ALIGN = 8;
+    static __device__ __forceinline__ float4 load(const __half *p, int64_t vec) {
+        const uint2 r = __ldcs(reinterpret_cast<const uint2 *>(p) + vec);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__half *p, int64_t vec, float4 v) {
+        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<const uint32_t *>(&a);
+        r.y = *reinterpret_cast<const uint32_t *>(&b);
+        __stcs(reinterpret_cast<uint2 *>(p) + vec, r);
+    }
+    static __device__ __forceinline__ float load1(const __half *p, int64_t i) { return __half2float(p[i]); }
+    static __device__ __forceinline__ void store1(__half *p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+};
 
 // Streaming (read-once / write-once) 128-bit accesses: keep them from displacing
 // reusable lines (weights, tables) in L1/L2.

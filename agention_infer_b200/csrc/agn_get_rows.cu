@@ -28,7 +28,8 @@ __device__ __forceinline__ uint32_t ld_u32_2(const uint8_t *p) {  // 4 bytes fro
     return (uint32_t)ld_u16(p) | ((uint32_t)ld_u16(p + 2) << 16);
 }
 
-// Four consecutive outputs starting at element e0 (a multiple of 4) of a staged row.
+// Four consecutive outputs starting at element e0 (a multiple of 4) of a staged row (the
+// formats whose blocks decode in element order; the K-quants have decode8 below).
 template <int DTYPE>
 __device__ __forceinline__ float4 decode4(const uint8_t *row, int e0);
 
@@ -42,71 +43,6 @@ __device__ __forceinline__ float4 decode4<AGN_Q8_0>(const uint8_t *row, int e0) 
     o.y = __fmul_rn(d, (float)(int8_t)((q >> 8) & 0xff));
     o.z = __fmul_rn(d, (float)(int8_t)((q >> 16) & 0xff));
     o.w = __fmul_rn(d, (float)(int8_t)(q >> 24));
-    return o;
-}
-
-template <>
-__device__ __forceinline__ float4 decode4<AGN_Q4_K>(const uint8_t *row, int e0) {
-    const uint8_t *blk = row + (e0 >> 8) * 144;  // 144 = 9*16: blocks stay 16-byte aligned
-    const int r = e0 & 255;
-    const int g = r >> 6;          // 64-value group
-    const int hi = (r >> 5) & 1;   // second 32 of the group = high nibbles
-    const int l = r & 31;
-    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
-    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
-    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
-    const uint8_t *sc = blk + 4;
-    const int j = 2 * g + hi;
-    uint32_t s, m;
-    if (j < 4) {
-        s = sc[j] & 63;
-        m = sc[j + 4] & 63;
-    } else {
-        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
-        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
-    }
-    const float dd = __fmul_rn(d, (float)s);
-    const float mm = __fmul_rn(dmin, (float)m);
-    uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l);
-    q >>= 4 * hi;
-    float4 o;
-    o.x = __fsub_rn(__fmul_rn(dd, (float)(q & 0xF)), mm);
-    o.y = __fsub_rn(__fmul_rn(dd, (float)((q >> 8) & 0xF)), mm);
-    o.z = __fsub_rn(__fmul_rn(dd, (float)((q >> 16) & 0xF)), mm);
-    o.w = __fsub_rn(__fmul_rn(dd, (float)((q >> 24) & 0xF)), mm);
-    return o;
-}
-
-template <>
-__device__ __forceinline__ float4 decode4<AGN_Q5_K>(const uint8_t *row, int e0) {
-    // src/quant/q5_k.rs:43-103: Q4_K's scales plus a fifth bit per value in qh[32]
-    const uint8_t *blk = row + (e0 >> 8) * 176;  // 176 = 11*16: blocks stay 16-byte aligned
-    const int r = e0 & 255;
-    const int g = r >> 6;
-    const int hi = (r >> 5) & 1;
-    const int l = r & 31;
-    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
-    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
-    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
-    const uint8_t *sc = blk + 4;
-    const int j = 2 * g + hi;
-    uint32_t s, m;
-    if (j < 4) {
-        s = sc[j] & 63;
-        m = sc[j + 4] & 63;
-    } else {
-        s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4);
-        m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
-    }
-    const float dd = __fmul_rn(d, (float)s);
-    const float mm = __fmul_rn(dmin, (float)m);
-    const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 16 + l) >> j;  // bit j of each byte
-    const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * g + l) >> (4 * hi);
-    float4 o;
-    o.x = __fsub_rn(__fmul_rn(dd, (float)((q & 0xF) + ((qh & 1) << 4))), mm);
-    o.y = __fsub_rn(__fmul_rn(dd, (float)(((q >> 8) & 0xF) + (((qh >> 8) & 1) << 4))), mm);
-    o.z = __fsub_rn(__fmul_rn(dd, (float)(((q >> 16) & 0xF) + (((qh >> 16) & 1) << 4))), mm);
-    o.w = __fsub_rn(__fmul_rn(dd, (float)(((q >> 24) & 0xF) + (((qh >> 24) & 1) << 4))), mm);
     return o;
 }
 
@@ -125,26 +61,6 @@ __device__ __forceinline__ float4 decode4<AGN_Q5_0>(const uint8_t *row, int e0) 
     o.y = __fmul_rn((float)((int)(((q >> 8) & 0xF) | (((qh >> 1) & 1) << 4)) - 16), d);
     o.z = __fmul_rn((float)((int)(((q >> 16) & 0xF) | (((qh >> 2) & 1) << 4)) - 16), d);
     o.w = __fmul_rn((float)((int)(((q >> 24) & 0xF) | (((qh >> 3) & 1) << 4)) - 16), d);
-    return o;
-}
-
-template <>
-__device__ __forceinline__ float4 decode4<AGN_Q6_K>(const uint8_t *row, int e0) {
-    const uint8_t *blk = row + (e0 >> 8) * 210;
-    const int r = e0 & 255;
-    const int h = r >> 7;         // 128-value half
-    const int c = (r >> 5) & 3;   // which of the four 32-value quadrants of the half
-    const int l = r & 31;
-    const uint32_t ql = ld_u32_2(blk + h * 64 + (c & 1) * 32 + l) >> (4 * (c >> 1));
-    const uint32_t qh = ld_u32_2(blk + 128 + h * 32 + l) >> (2 * c);
-    const float sc = (float)(int8_t)blk[192 + 8 * h + (l >> 4) + 2 * c];
-    const float d = f16_bits_to_f32(ld_u16(blk + 208));
-    const float ds = __fmul_rn(d, sc);
-    float4 o;
-    o.x = __fmul_rn(ds, (float)((int)((ql & 0xF) | ((qh & 3) << 4)) - 32));
-    o.y = __fmul_rn(ds, (float)((int)(((ql >> 8) & 0xF) | (((qh >> 8) & 3) << 4)) - 32));
-    o.z = __fmul_rn(ds, (float)((int)(((ql >> 16) & 0xF) | (((qh >> 16) & 3) << 4)) - 32));
-    o.w = __fmul_rn(ds, (float)((int)(((ql >> 24) & 0xF) | (((qh >> 24) & 3) << 4)) - 32));
     return o;
 }
 
@@ -305,10 +221,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
-template <int DTYPE, bool VEC_OUT, bool TMA>
+template <int DTYPE, typename OUT, bool VEC_OUT, bool TMA>
 __global__ void __launch_bounds__(256)
 get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
-                const uint32_t *__restrict__ ids, float *__restrict__ out, uint32_t *flags) {
+                const uint32_t *__restrict__ ids, OUT *__restrict__ out, uint32_t *flags) {
     extern __shared__ __align__(128) uint8_t stage[];
     __shared__ __align__(8) uint64_t bar;
     if (TMA) {
@@ -318,10 +234,10 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     agn_pdl_prologue();
     const int64_t t = blockIdx.x;
     const uint32_t id = ids[t];
-    float *o_row = out + t * (int64_t)row_len;
+    OUT *o_row = out + t * (int64_t)row_len;
     if ((int64_t)id >= n_rows) {
         // "row index out of range": zero row + error flag, never a trap
-        for (int j = threadIdx.x; j < row_len; j += blockDim.x) o_row[j] = 0.0f;
+        for (int j = threadIdx.x; j < row_len; j += blockDim.x) ActVec<OUT>::store1(o_row, j, 0.0f);
         if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_OOB_ID);
         return;
     }
@@ -362,40 +278,48 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
         float4 va, vb;
         decode8<DTYPE>(row, u, row_len, ea, va, eb, vb);
         if (VEC_OUT) {
-            if (ea < row_len) agn_st_stream(reinterpret_cast<float4 *>(o_row + ea), va);
-            if (eb < row_len) agn_st_stream(reinterpret_cast<float4 *>(o_row + eb), vb);
+            if (ea < row_len) ActVec<OUT>::store(o_row, ea >> 2, va);
+            if (eb < row_len) ActVec<OUT>::store(o_row, eb >> 2, vb);
         } else {
             const float a[4] = {va.x, va.y, va.z, va.w}, b[4] = {vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                if (ea + i < row_len) o_row[ea + i] = a[i];
-                if (eb + i < row_len) o_row[eb + i] = b[i];
+                if (ea + i < row_len) ActVec<OUT>::store1(o_row, ea + i, a[i]);
+                if (eb + i < row_len) ActVec<OUT>::store1(o_row, eb + i, b[i]);
             }
         }
     }
 }
 
-template <int DTYPE>
-void launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
-                     size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, float *out) {
+template <int DTYPE, typename OUT>
+cudaError_t launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
+                            size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, OUT *out) {
+    cudaError_t e = cudaSuccess;
+    if (smem > 48 * 1024) {  // opt in to large dynamic shared memory for very long rows
+        e = cudaFuncSetAttribute(get_rows_kernel<DTYPE, OUT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(get_rows_kernel<DTYPE, OUT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(get_rows_kernel<DTYPE, OUT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(get_rows_kernel<DTYPE, OUT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
     const bool tma = ctx->tune_get_rows_tma != 0;
     if (vec && tma)
-        agn_launch(ctx, get_rows_kernel<DTYPE, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
     else if (vec)
-        agn_launch(ctx, get_rows_kernel<DTYPE, true, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
     else if (tma)
-        agn_launch(ctx, get_rows_kernel<DTYPE, false, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
     else
-        agn_launch(ctx, get_rows_kernel<DTYPE, false, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+    return cudaSuccess;
 }
 
-}  // namespace
-
-extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows,
-                                    int64_t row_len, const uint32_t *ids, int64_t T, float *out) {
-    AGN_CHECK_CTX(ctx);
+template <typename OUT>
+int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows, int64_t row_len,
+                          const uint32_t *ids, int64_t T, OUT *out) {
     const size_t row_bytes = agn_type_size(dtype, (size_t)(row_len > 0 ? row_len : 0));
-    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_Q5_K && dtype != AGN_Q5_0 && dtype != AGN_F16 && dtype != AGN_BF16 && dtype != AGN_F32)
+    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_Q5_K && dtype != AGN_Q5_0 && dtype != AGN_F16 &&
+        dtype != AGN_BF16 && dtype != AGN_F32)
         return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "get_rows: dequantization not implemented for ggml type %d", dtype);
     if (T < 0 || n_rows < 0 || row_len <= 0)
         return agn_fail(ctx, AGN_EINVAL, "get_rows: T=%lld n_rows=%lld row_len=%lld", (long long)T, (long long)n_rows, (long long)row_len);
@@ -408,7 +332,7 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
     if (row_bytes + 32 > 200 * 1024) return agn_fail(ctx, AGN_EINVAL, "get_rows: row of %zu bytes exceeds the staging buffer", row_bytes);
     if (T > 0x7fffffffLL || row_len > 0x3fffffffLL) return agn_fail(ctx, AGN_EINVAL, "get_rows: T or row_len too large");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const bool vec = row_len % 4 == 0 && agn_aligned16(out);
+    const bool vec = row_len % 4 == 0 && agn_aligned(out, ActVec<OUT>::ALIGN);
     const int n4 = (int)((row_len + 3) / 4);
     // small CTAs (8 float4 per thread): more rows resident per SM hides the id -> row -> decode
     // latency chain better than wide CTAs do (measured: 128 threads beat 224 by 15% at H=3584)
@@ -418,43 +342,37 @@ extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *tab
     if (ctx->tune_get_rows_threads >= 32 && ctx->tune_get_rows_threads <= 256) threads = ctx->tune_get_rows_threads & ~31;
     const size_t smem = ((row_bytes + 15) / 16 + 2) * 16;
     const uint8_t *tb = static_cast<const uint8_t *>(table);
-    if (smem > 48 * 1024) {
-        // opt in to large dynamic shared memory for very long rows
-        cudaError_t e = cudaSuccess;
-#define AGN_GR_ATTR(DT)                                                                                               \
-    e = cudaFuncSetAttribute(get_rows_kernel<DT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess)                                                                                              \
-        e = cudaFuncSetAttribute(get_rows_kernel<DT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess)                                                                                              \
-        e = cudaFuncSetAttribute(get_rows_kernel<DT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess)                                                                                              \
-        e = cudaFuncSetAttribute(get_rows_kernel<DT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        switch (dtype) {
-        case AGN_Q8_0: AGN_GR_ATTR(AGN_Q8_0) break;
-        case AGN_Q4_K: AGN_GR_ATTR(AGN_Q4_K) break;
-        case AGN_Q6_K: AGN_GR_ATTR(AGN_Q6_K) break;
-        case AGN_Q5_K: AGN_GR_ATTR(AGN_Q5_K) break;
-        case AGN_Q5_0: AGN_GR_ATTR(AGN_Q5_0) break;
-        case AGN_F16: AGN_GR_ATTR(AGN_F16) break;
-        case AGN_BF16: AGN_GR_ATTR(AGN_BF16) break;
-        default: AGN_GR_ATTR(AGN_F32) break;
-        }
-#undef AGN_GR_ATTR
-        AGN_CUDA(ctx, e);
-    }
     const unsigned grid = (unsigned)T;
     const int rl = (int)row_len, rb = (int)row_bytes;
+    cudaError_t e;
     switch (dtype) {
-    case AGN_Q8_0: launch_get_rows<AGN_Q8_0>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q4_K: launch_get_rows<AGN_Q4_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q6_K: launch_get_rows<AGN_Q6_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q5_K: launch_get_rows<AGN_Q5_K>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q5_0: launch_get_rows<AGN_Q5_0>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_F16: launch_get_rows<AGN_F16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_BF16: launch_get_rows<AGN_BF16>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    default: launch_get_rows<AGN_F32>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q8_0: e = launch_get_rows<AGN_Q8_0, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q4_K: e = launch_get_rows<AGN_Q4_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q6_K: e = launch_get_rows<AGN_Q6_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_K: e = launch_get_rows<AGN_Q5_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_0: e = launch_get_rows<AGN_Q5_0, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_F16: e = launch_get_rows<AGN_F16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_BF16: e = launch_get_rows<AGN_BF16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    default: e = launch_get_rows<AGN_F32, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     }
+    AGN_CUDA(ctx, e);
     ctx->flags_dirty = true;
     AGN_LAUNCHED(ctx, "get_rows");
     return AGN_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows,
+                                    int64_t row_len, const uint32_t *ids, int64_t T, float *out) {
+    AGN_CHECK_CTX(ctx);
+    return get_rows_dispatch<float>(ctx, dtype, table, table_bytes, n_rows, row_len, ids, T, out);
+}
+
+// Output stored as f16 (round to nearest even): the embedding row as the reference uploads
+// it with `Act = f16` (`act_encode`, src/ops/mod.rs:47-60, after the CPU `dequant_row`).
+extern "C" int32_t agn_get_rows_f16(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows,
+                                    int64_t row_len, const uint32_t *ids, int64_t T, void *out) {
+    AGN_CHECK_CTX(ctx);
+    return get_rows_dispatch<__half>(ctx, dtype, table, table_bytes, n_rows, row_len, ids, T, static_cast<__half *>(out));
 }

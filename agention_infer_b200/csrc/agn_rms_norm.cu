@@ -27,19 +27,18 @@ __device__ __forceinline__ float block_sum(float v, float *smem) {
     return total;
 }
 
-template <int VPT, bool RESIDUAL, bool RECIP>
+template <typename T, int VPT, bool RESIDUAL, bool RECIP>
 __global__ void __launch_bounds__(1024)
-rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ delta,
-                     const float4 *__restrict__ w, float4 *__restrict__ new_x,
-                     float4 *__restrict__ out, int n4, float n_f, float eps) {
+rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float4 *__restrict__ w,
+                     T *__restrict__ new_x, T *__restrict__ out, int n4, float n_f, float eps) {
     agn_pdl_prologue();
     __shared__ float red[32];
-    const int64_t row = (int64_t)blockIdx.x * n4;
+    const int64_t row = (int64_t)blockIdx.x * n4;  // in vectors of four activations
     float4 v[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
-        if (i < n4) v[k] = agn_ld_stream(x + row + i);
+        if (i < n4) v[k] = ActVec<T>::load(x, row + i);
         else v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (RESIDUAL) {
@@ -47,9 +46,15 @@ rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ de
         for (int k = 0; k < VPT; k++) {
             const int i = threadIdx.x + k * blockDim.x;
             if (i < n4) {
-                const float4 d = agn_ld_stream(delta + row + i);
+                const float4 d = ActVec<T>::load(delta, row + i);
                 v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
-                agn_st_stream(new_x + row + i, v[k]);
+                ActVec<T>::store(new_x, row + i, v[k]);
+                if (sizeof(T) == 2) {
+                    // the reference's f16 kernel normalises the STORED new_x (re-read after the
+                    // cast, src/ops/kernels_wgpu.rs:139,159): round through f16 here as well
+                    v[k].x = __half2float(__float2half_rn(v[k].x)); v[k].y = __half2float(__float2half_rn(v[k].y));
+                    v[k].z = __half2float(__float2half_rn(v[k].z)); v[k].w = __half2float(__float2half_rn(v[k].w));
+                }
             }
         }
     }
@@ -76,62 +81,60 @@ rms_norm_rows_kernel(const float4 *__restrict__ x, const float4 *__restrict__ de
                 o.z = ww.z * v[k].z / rms;
                 o.w = ww.w * v[k].w / rms;
             }
-            agn_st_stream(out + row + i, o);
+            ActVec<T>::store(out, row + i, o);
         }
     }
 }
 
 // Any H, any alignment, rows too long for registers: two passes over the row, the second
 // one served by L2 for rows that fit there.
-template <bool RESIDUAL>
+template <typename T, bool RESIDUAL>
 __global__ void __launch_bounds__(1024)
-rms_norm_rows_generic_kernel(const float *__restrict__ x, const float *__restrict__ delta,
-                             const float *__restrict__ w, float *__restrict__ new_x,
-                             float *__restrict__ out, int64_t H, float eps) {
+rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float *__restrict__ w,
+                             T *__restrict__ new_x, T *__restrict__ out, int64_t H, float eps) {
     agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * H;
     float ss = 0.0f;
     for (int64_t i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = x[row + i];
+        float v = ActVec<T>::load1(x, row + i);
         if (RESIDUAL) {
-            v += delta[row + i];
-            new_x[row + i] = v;
+            v += ActVec<T>::load1(delta, row + i);
+            ActVec<T>::store1(new_x, row + i, v);
+            v = ActVec<T>::load1(new_x, row + i);
         }
         ss += v * v;
     }
     ss = block_sum(ss, red);
-    const float rms = sqrtf(ss / (float)H + eps);
-    const float *src = RESIDUAL ? new_x : x;
-    for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[row + i] = w[i] * src[row + i] / rms;
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    const T *src = RESIDUAL ? new_x : x;
+    for (int64_t i = threadIdx.x; i < H; i += blockDim.x)
+        ActVec<T>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
 }
 
-template <int VPT, bool RESIDUAL>
-void launch_vec(agn_ctx *ctx, const float *x, const float *delta, const float *w, float *new_x,
-                float *out, int64_t T, int n4, float eps, int threads) {
+template <typename T, int VPT, bool RESIDUAL>
+void launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, T *out, int64_t T_rows, int n4,
+                float eps, int threads) {
+    const float4 *w4 = reinterpret_cast<const float4 *>(w);
     if (ctx->tune_rms_recip)
-        agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL, true>, dim3((unsigned)T), dim3(threads), 0,
-                   reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
-                   reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
-                   reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
+        agn_launch(ctx, rms_norm_rows_kernel<T, VPT, RESIDUAL, true>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
+                   new_x, out, n4, (float)(n4 * 4), eps);
     else
-    agn_launch(ctx, rms_norm_rows_kernel<VPT, RESIDUAL, false>, dim3((unsigned)T), dim3(threads), 0, 
-        reinterpret_cast<const float4 *>(x), reinterpret_cast<const float4 *>(delta),
-        reinterpret_cast<const float4 *>(w), reinterpret_cast<float4 *>(new_x),
-        reinterpret_cast<float4 *>(out), n4, (float)(n4 * 4), eps);
+        agn_launch(ctx, rms_norm_rows_kernel<T, VPT, RESIDUAL, false>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
+                   new_x, out, n4, (float)(n4 * 4), eps);
 }
 
-template <bool RESIDUAL>
-int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, const float *w,
-                          float *new_x, float *out, int64_t T, int64_t H, float eps, const char *name) {
-    if (T < 0 || H <= 0) return agn_fail(ctx, AGN_EINVAL, "%s: T=%lld H=%lld", name, (long long)T, (long long)H);
-    if (T == 0) return AGN_OK;
-    if (!x || !w || !out || (RESIDUAL && (!delta || !new_x)))
-        return agn_fail(ctx, AGN_EINVAL, "%s: null pointer", name);
-    if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "%s: T too large", name);
+template <typename T, bool RESIDUAL>
+int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, T *out, int64_t T_rows,
+                          int64_t H, float eps, const char *name) {
+    if (T_rows < 0 || H <= 0) return agn_fail(ctx, AGN_EINVAL, "%s: T=%lld H=%lld", name, (long long)T_rows, (long long)H);
+    if (T_rows == 0) return AGN_OK;
+    if (!x || !w || !out || (RESIDUAL && (!delta || !new_x))) return agn_fail(ctx, AGN_EINVAL, "%s: null pointer", name);
+    if (T_rows > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "%s: T too large", name);
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const bool vec_ok = (H % 4 == 0) && agn_aligned16(x) && agn_aligned16(w) && agn_aligned16(out) &&
-                        (!RESIDUAL || (agn_aligned16(delta) && agn_aligned16(new_x))) && H <= 32768;
+    constexpr int A = ActVec<T>::ALIGN;
+    const bool vec_ok = (H % 4 == 0) && agn_aligned(x, A) && agn_aligned16(w) && agn_aligned(out, A) &&
+                        (!RESIDUAL || (agn_aligned(delta, A) && agn_aligned(new_x, A))) && H <= 32768;
     if (vec_ok) {
         const int n4 = (int)(H / 4);
         // Pick the smallest VPT in {1,2,4,8} that keeps the CTA at <= 256 threads when
@@ -146,16 +149,17 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, cons
         threads = ((threads + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         switch (vpt) {
-        case 1: launch_vec<1, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
-        case 2: launch_vec<2, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
-        case 4: launch_vec<4, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
-        default: launch_vec<8, RESIDUAL>(ctx, x, delta, w, new_x, out, T, n4, eps, threads); break;
+        case 1: launch_vec<T, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 2: launch_vec<T, 2, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 4: launch_vec<T, 4, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        default: launch_vec<T, 8, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
         }
         AGN_LAUNCHED(ctx, name);
     } else {
         int threads = H >= 1024 ? 256 : (int)(((H + 31) / 32) * 32);
         if (threads > 256) threads = 256;
-        agn_launch(ctx, rms_norm_rows_generic_kernel<RESIDUAL>, dim3((unsigned)T), dim3(threads), 0, x, delta, w, new_x, out, H, eps);
+        agn_launch(ctx, rms_norm_rows_generic_kernel<T, RESIDUAL>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w, new_x,
+                   out, H, eps);
         AGN_LAUNCHED(ctx, name);
     }
     return AGN_OK;
@@ -166,12 +170,28 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const float *x, const float *delta, cons
 extern "C" int32_t agn_rms_norm_f32(agn_ctx *ctx, const float *x, const float *w, float *out,
                                     int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<false>(ctx, x, nullptr, w, nullptr, out, T, H, eps, "rms_norm");
+    return rms_norm_dispatch<float, false>(ctx, x, nullptr, w, nullptr, out, T, H, eps, "rms_norm");
 }
 
 extern "C" int32_t agn_add_residual_rms_norm_f32(agn_ctx *ctx, const float *x, const float *delta,
                                                  const float *w, float *new_x, float *normed,
                                                  int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<true>(ctx, x, delta, w, new_x, normed, T, H, eps, "add_residual_rms_norm");
+    return rms_norm_dispatch<float, true>(ctx, x, delta, w, new_x, normed, T, H, eps, "add_residual_rms_norm");
+}
+
+// f16 activation storage (the reference's `Act = f16`, src/ops/kernels_wgpu.rs:79-163): x, delta,
+// new_x and the output are f16, the weight is f32, the arithmetic is f32.
+extern "C" int32_t agn_rms_norm_f16(agn_ctx *ctx, const void *x, const float *w, void *out, int64_t T, int64_t H, float eps) {
+    AGN_CHECK_CTX(ctx);
+    return rms_norm_dispatch<__half, false>(ctx, static_cast<const __half *>(x), nullptr, w, nullptr, static_cast<__half *>(out),
+                                            T, H, eps, "rms_norm_f16");
+}
+
+extern "C" int32_t agn_add_residual_rms_norm_f16(agn_ctx *ctx, const void *x, const void *delta, const float *w, void *new_x,
+                                                 void *normed, int64_t T, int64_t H, float eps) {
+    AGN_CHECK_CTX(ctx);
+    return rms_norm_dispatch<__half, true>(ctx, static_cast<const __half *>(x), static_cast<const __half *>(delta), w,
+                                           static_cast<__half *>(new_x), static_cast<__half *>(normed), T, H, eps,
+                                           "add_residual_rms_norm_f16");
 }

@@ -25,8 +25,8 @@
 namespace {
 
 struct RopeArgs {
-    float *q;
-    float *k;
+    void *q;  // activations: float or __half, see the kernels' template parameter T
+    void *k;
     const float *wq;
     const float *wk;
     const int32_t *pos;
@@ -37,6 +37,12 @@ struct RopeArgs {
     int tpc;  // tokens per CTA
     float freq_scale, eps;
 };
+
+// With f16 storage the reference's fused kernel writes the normalised head to the f16 buffer
+// and reads it back for the rotation (src/ops/kernels_wgpu.rs:296-316): the value that is
+// rotated has been rounded to f16.  Keep that rounding (the data itself stays in registers).
+template <typename T> __device__ __forceinline__ float act_round(float v) { return v; }
+template <> __device__ __forceinline__ float act_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
 
 // (cos, sin) of every (token of this CTA, d < half) into shared memory.
 __device__ __forceinline__ void fill_sincos(const RopeArgs &a, float *s_cos, float *s_sin, int half) {
@@ -63,7 +69,7 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
        MODE_NEOX_SHFL = 3 // NeoX, n_rot/8 < W (power of two): partner is register 0 of lane ^ (n_rot/8)
 };
 
-template <int W, int VPL, int MODE, bool NORM>
+template <typename T, int W, int VPL, int MODE, bool NORM>
 __global__ void __launch_bounds__(256)
 rope_heads_kernel(const RopeArgs a) {
     agn_pdl_launch_dependents();
@@ -73,7 +79,7 @@ rope_heads_kernel(const RopeArgs a) {
     const int n_heads = a.n_q + a.n_kv;
     const int rows = a.tpc * n_heads;  // head rows of this CTA
     // shared memory: row pointers | row meta (token in CTA, is-K flag) | cos | sin
-    float **s_ptr = reinterpret_cast<float **>(smem_raw);
+    T **s_ptr = reinterpret_cast<T **>(smem_raw);
     int *s_meta = reinterpret_cast<int *>(smem_raw + (size_t)rows * 8);
     float *s_cos = reinterpret_cast<float *>(smem_raw + (((size_t)rows * 12 + 15) & ~(size_t)15));
     float *s_sin = s_cos + a.tpc * half;
@@ -83,10 +89,10 @@ rope_heads_kernel(const RopeArgs a) {
     for (int hr = threadIdx.x; hr < rows; hr += blockDim.x) {
         const int tt = hr / n_heads, h = hr - tt * n_heads;
         const int64_t t = t0 + tt;
-        float *p = nullptr;
+        T *p = nullptr;
         if (t < a.T)
-            p = h < a.n_q ? a.q + (t * a.n_q + h) * (int64_t)a.head_dim
-                          : a.k + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
+            p = h < a.n_q ? static_cast<T *>(a.q) + (t * a.n_q + h) * (int64_t)a.head_dim
+                          : static_cast<T *>(a.k) + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
         s_ptr[hr] = p;
         s_meta[hr] = tt | (h < a.n_q ? 0 : 1 << 16);
     }
@@ -103,17 +109,17 @@ rope_heads_kernel(const RopeArgs a) {
 
     for (int base = 0; base < rows; base += n_groups * NS) {
         float4 v[NS][VPL];
-        float4 *ptr[NS];
+        T *ptr[NS];
         int meta[NS];
 #pragma unroll
         for (int s = 0; s < NS; s++) {
             const int hr = base + group + s * n_groups;
-            ptr[s] = hr < rows ? reinterpret_cast<float4 *>(s_ptr[hr]) : nullptr;
+            ptr[s] = hr < rows ? s_ptr[hr] : nullptr;
             meta[s] = hr < rows ? s_meta[hr] : 0;
 #pragma unroll
             for (int l = 0; l < VPL; l++) {
                 const int i = lane + W * l;
-                v[s][l] = (ptr[s] && i < hd4) ? agn_ld_stream(ptr[s] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[s][l] = (ptr[s] && i < hd4) ? ActVec<T>::load(ptr[s], i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
         if (base == 0) {
@@ -139,10 +145,10 @@ rope_heads_kernel(const RopeArgs a) {
                     const int i = lane + W * l;
                     if (ptr[s] && i < hd4) {
                         const float4 ww = __ldg(wv + i);
-                        v[s][l].x = ww.x * v[s][l].x * inv;
-                        v[s][l].y = ww.y * v[s][l].y * inv;
-                        v[s][l].z = ww.z * v[s][l].z * inv;
-                        v[s][l].w = ww.w * v[s][l].w * inv;
+                        v[s][l].x = act_round<T>(ww.x * v[s][l].x * inv);
+                        v[s][l].y = act_round<T>(ww.y * v[s][l].y * inv);
+                        v[s][l].z = act_round<T>(ww.z * v[s][l].z * inv);
+                        v[s][l].w = act_round<T>(ww.w * v[s][l].w * inv);
                     }
                 }
             }
@@ -214,7 +220,7 @@ rope_heads_kernel(const RopeArgs a) {
                 const int i = lane + W * l;
                 // dims past n_rot are untouched by rope: skip the store unless normalised
                 const bool touched = NORM || 4 * i < a.n_rot;
-                if (ptr[s] && i < hd4 && touched) agn_st_stream(ptr[s] + i, v[s][l]);
+                if (ptr[s] && i < hd4 && touched) ActVec<T>::store(ptr[s], i, v[s][l]);
             }
         }
     }
@@ -222,7 +228,7 @@ rope_heads_kernel(const RopeArgs a) {
 
 // Any even n_rot <= head_dim, any head_dim, any alignment: one warp per head, scalar
 // accesses straight from global memory (second touch of an element is an L1/L2 hit).
-template <int LAYOUT, bool NORM>
+template <typename T, int LAYOUT, bool NORM>
 __global__ void __launch_bounds__(256)
 rope_heads_generic_kernel(const RopeArgs a) {
     agn_pdl_prologue();
@@ -236,55 +242,58 @@ rope_heads_generic_kernel(const RopeArgs a) {
     const int n_heads = a.n_q + a.n_kv;
     const int64_t t = blockIdx.x;
     for (int h = warp; h < n_heads; h += n_warps) {
-        float *x;
+        T *x;
         const float *w;
         if (h < a.n_q) {
-            x = a.q + (t * a.n_q + h) * (int64_t)a.head_dim;
+            x = static_cast<T *>(a.q) + (t * a.n_q + h) * (int64_t)a.head_dim;
             w = a.wq;
         } else {
-            x = a.k + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
+            x = static_cast<T *>(a.k) + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
             w = a.wk;
         }
-        float rms = 1.0f;
+        float inv = 1.0f;
         if (NORM) {
             float ss = 0.0f;
-            for (int d = lane; d < a.head_dim; d += 32) ss += x[d] * x[d];
+            for (int d = lane; d < a.head_dim; d += 32) {
+                const float v = ActVec<T>::load1(x, d);
+                ss += v * v;
+            }
             ss = agn_warp_sum(ss);
-            rms = sqrtf(ss / (float)a.head_dim + a.eps);
+            inv = 1.0f / sqrtf(ss / (float)a.head_dim + a.eps);
         }
         for (int d = lane; d < half; d += 32) {
             const int i0 = LAYOUT == AGN_ROPE_NEOX ? d : 2 * d;
             const int i1 = LAYOUT == AGN_ROPE_NEOX ? d + half : 2 * d + 1;
-            float x0 = x[i0], x1 = x[i1];
+            float x0 = ActVec<T>::load1(x, i0), x1 = ActVec<T>::load1(x, i1);
             if (NORM) {
-                x0 = w[i0] * x0 / rms;
-                x1 = w[i1] * x1 / rms;
+                x0 = act_round<T>(w[i0] * x0 * inv);
+                x1 = act_round<T>(w[i1] * x1 * inv);
             }
             const float c = s_cos[d], sn = s_sin[d];
-            x[i0] = x0 * c - x1 * sn;
-            x[i1] = x0 * sn + x1 * c;
+            ActVec<T>::store1(x, i0, x0 * c - x1 * sn);
+            ActVec<T>::store1(x, i1, x0 * sn + x1 * c);
         }
         if (NORM)
-            for (int d = a.n_rot + lane; d < a.head_dim; d += 32) x[d] = w[d] * x[d] / rms;
+            for (int d = a.n_rot + lane; d < a.head_dim; d += 32) ActVec<T>::store1(x, d, w[d] * ActVec<T>::load1(x, d) * inv);
     }
 }
 
-template <int W, int VPL, int MODE>
+template <typename T, int W, int VPL, int MODE>
 void launch_fast3(agn_ctx *ctx, const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem) {
-    if (norm) agn_launch(ctx, rope_heads_kernel<W, VPL, MODE, true>, dim3(grid), dim3(threads), smem, a);
-    else agn_launch(ctx, rope_heads_kernel<W, VPL, MODE, false>, dim3(grid), dim3(threads), smem, a);
+    if (norm) agn_launch(ctx, rope_heads_kernel<T, W, VPL, MODE, true>, dim3(grid), dim3(threads), smem, a);
+    else agn_launch(ctx, rope_heads_kernel<T, W, VPL, MODE, false>, dim3(grid), dim3(threads), smem, a);
 }
 
-template <int W, int VPL>
+template <typename T, int W, int VPL>
 bool launch_fast(agn_ctx *ctx, const RopeArgs &a, bool norm, int mode, unsigned grid, int threads, size_t smem) {
     switch (mode) {
-    case MODE_NORMAL: launch_fast3<W, VPL, MODE_NORMAL>(ctx, a, norm, grid, threads, smem); return true;
-    case MODE_NEOX_SHFL: launch_fast3<W, VPL, MODE_NEOX_SHFL>(ctx, a, norm, grid, threads, smem); return true;
+    case MODE_NORMAL: launch_fast3<T, W, VPL, MODE_NORMAL>(ctx, a, norm, grid, threads, smem); return true;
+    case MODE_NEOX_SHFL: launch_fast3<T, W, VPL, MODE_NEOX_SHFL>(ctx, a, norm, grid, threads, smem); return true;
     case MODE_NEOX_K1:
-        if constexpr (VPL >= 2) { launch_fast3<W, VPL, MODE_NEOX_K1>(ctx, a, norm, grid, threads, smem); return true; }
+        if constexpr (VPL >= 2) { launch_fast3<T, W, VPL, MODE_NEOX_K1>(ctx, a, norm, grid, threads, smem); return true; }
         return false;
     case MODE_NEOX_K2:
-        if constexpr (VPL >= 4) { launch_fast3<W, VPL, MODE_NEOX_K2>(ctx, a, norm, grid, threads, smem); return true; }
+        if constexpr (VPL >= 4) { launch_fast3<T, W, VPL, MODE_NEOX_K2>(ctx, a, norm, grid, threads, smem); return true; }
         return false;
     }
     return false;
@@ -292,7 +301,8 @@ bool launch_fast(agn_ctx *ctx, const RopeArgs &a, bool norm, int mode, unsigned 
 
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
-int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const float *wq, const float *wk,
+template <typename AT>
+int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float *wq, const float *wk,
                       bool norm, int64_t T, int32_t n_q, int32_t n_kv, int32_t head_dim, float eps, int32_t n_rot,
                       const int32_t *pos, int32_t pos_start, float theta, float freq_scale, int32_t layout) {
     if (T < 0 || n_q < 0 || n_kv < 0 || n_q + n_kv <= 0 || head_dim <= 0)
@@ -326,7 +336,8 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
     // is in the same lane and the per-head bookkeeping is amortised over more data.
     int W = 0, VPL = 0, mode = -1;
     const int hq = half / 4;
-    bool fast = head_dim % 4 == 0 && (n_q == 0 || agn_aligned16(q)) && (n_kv == 0 || agn_aligned16(k)) &&
+    constexpr int A = ActVec<AT>::ALIGN;
+    bool fast = head_dim % 4 == 0 && (n_q == 0 || agn_aligned(q, A)) && (n_kv == 0 || agn_aligned(k, A)) &&
                 (!norm || ((n_q == 0 || agn_aligned16(wq)) && (n_kv == 0 || agn_aligned16(wk))));
     if (fast) {
         static const int shapes[7][2] = {{8, 4}, {16, 4}, {32, 4}, {8, 2}, {8, 1}, {32, 2}, {32, 1}};
@@ -365,24 +376,24 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
         const unsigned grid = (unsigned)((T + tpc - 1) / tpc);
         const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
         bool ok = false;
-        if (W == 8 && VPL == 4) ok = launch_fast<8, 4>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 16 && VPL == 4) ok = launch_fast<16, 4>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 32 && VPL == 4) ok = launch_fast<32, 4>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 8 && VPL == 2) ok = launch_fast<8, 2>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 8 && VPL == 1) ok = launch_fast<8, 1>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 32 && VPL == 2) ok = launch_fast<32, 2>(ctx, a, norm, mode, grid, threads, smem);
-        else if (W == 32 && VPL == 1) ok = launch_fast<32, 1>(ctx, a, norm, mode, grid, threads, smem);
+        if (W == 8 && VPL == 4) ok = launch_fast<AT, 8, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 16 && VPL == 4) ok = launch_fast<AT, 16, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 4) ok = launch_fast<AT, 32, 4>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 8 && VPL == 2) ok = launch_fast<AT, 8, 2>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 8 && VPL == 1) ok = launch_fast<AT, 8, 1>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 2) ok = launch_fast<AT, 32, 2>(ctx, a, norm, mode, grid, threads, smem);
+        else if (W == 32 && VPL == 1) ok = launch_fast<AT, 32, 1>(ctx, a, norm, mode, grid, threads, smem);
         if (!ok) return agn_fail(ctx, AGN_EINVAL, "%s: internal dispatch error (W=%d VPL=%d mode=%d)", name, W, VPL, mode);
         AGN_LAUNCHED(ctx, name);
     } else {
         int threads = n_heads >= 8 ? 256 : 32 * n_heads;
         const size_t smem = sizeof(float) * 2 * (size_t)(half > 0 ? half : 1);
         if (layout == AGN_ROPE_NEOX) {
-            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NEOX, true>, dim3((unsigned)T), dim3(threads), smem, a);
-            else agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NEOX, false>, dim3((unsigned)T), dim3(threads), smem, a);
+            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AT, AGN_ROPE_NEOX, true>, dim3((unsigned)T), dim3(threads), smem, a);
+            else agn_launch(ctx, rope_heads_generic_kernel<AT, AGN_ROPE_NEOX, false>, dim3((unsigned)T), dim3(threads), smem, a);
         } else {
-            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NORMAL, true>, dim3((unsigned)T), dim3(threads), smem, a);
-            else agn_launch(ctx, rope_heads_generic_kernel<AGN_ROPE_NORMAL, false>, dim3((unsigned)T), dim3(threads), smem, a);
+            if (norm) agn_launch(ctx, rope_heads_generic_kernel<AT, AGN_ROPE_NORMAL, true>, dim3((unsigned)T), dim3(threads), smem, a);
+            else agn_launch(ctx, rope_heads_generic_kernel<AT, AGN_ROPE_NORMAL, false>, dim3((unsigned)T), dim3(threads), smem, a);
         }
         AGN_LAUNCHED(ctx, name);
     }
@@ -394,7 +405,7 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, float *q, float *k, const 
 extern "C" int32_t agn_rope_f32(agn_ctx *ctx, float *x, int64_t T, int32_t n_heads, int32_t head_dim, int32_t n_rot,
                                 const int32_t *pos, int32_t pos_start, float theta, float freq_scale, int32_t layout) {
     AGN_CHECK_CTX(ctx);
-    return rope_dispatch(ctx, "rope", x, nullptr, nullptr, nullptr, false, T, n_heads, 0, head_dim, 0.0f, n_rot, pos,
+    return rope_dispatch<float>(ctx, "rope", x, nullptr, nullptr, nullptr, false, T, n_heads, 0, head_dim, 0.0f, n_rot, pos,
                          pos_start, theta, freq_scale, layout);
 }
 
@@ -402,7 +413,7 @@ extern "C" int32_t agn_rope_qk_f32(agn_ctx *ctx, float *q, float *k, int64_t T, 
                                    int32_t head_dim, int32_t n_rot, const int32_t *pos, int32_t pos_start, float theta,
                                    float freq_scale, int32_t layout) {
     AGN_CHECK_CTX(ctx);
-    return rope_dispatch(ctx, "rope_qk", q, k, nullptr, nullptr, false, T, n_q_heads, n_kv_heads, head_dim, 0.0f, n_rot,
+    return rope_dispatch<float>(ctx, "rope_qk", q, k, nullptr, nullptr, false, T, n_q_heads, n_kv_heads, head_dim, 0.0f, n_rot,
                          pos, pos_start, theta, freq_scale, layout);
 }
 
@@ -410,7 +421,7 @@ extern "C" int32_t agn_qk_norm_rope_f32(agn_ctx *ctx, float *x, const float *w, 
                                         int32_t head_dim, float eps, int32_t n_rot, const int32_t *pos,
                                         int32_t pos_start, float theta, float freq_scale, int32_t layout) {
     AGN_CHECK_CTX(ctx);
-    return rope_dispatch(ctx, "qk_norm_rope", x, nullptr, w, nullptr, true, T, n_heads, 0, head_dim, eps, n_rot, pos,
+    return rope_dispatch<float>(ctx, "qk_norm_rope", x, nullptr, w, nullptr, true, T, n_heads, 0, head_dim, eps, n_rot, pos,
                          pos_start, theta, freq_scale, layout);
 }
 
@@ -419,6 +430,27 @@ extern "C" int32_t agn_qk_norm_rope_qk_f32(agn_ctx *ctx, float *q, float *k, con
                                            int32_t n_rot, const int32_t *pos, int32_t pos_start, float theta,
                                            float freq_scale, int32_t layout) {
     AGN_CHECK_CTX(ctx);
-    return rope_dispatch(ctx, "qk_norm_rope_qk", q, k, wq, wk, true, T, n_q_heads, n_kv_heads, head_dim, eps, n_rot, pos,
+    return rope_dispatch<float>(ctx, "qk_norm_rope_qk", q, k, wq, wk, true, T, n_q_heads, n_kv_heads, head_dim, eps, n_rot, pos,
                          pos_start, theta, freq_scale, layout);
+}
+
+// f16 activation storage (the reference's `Act = f16`; `rope` / `qk_norm_rope`,
+// src/ops/kernels_wgpu.rs:225-318): q, k are f16, norm weights f32, arithmetic f32.
+// Pass k = NULL, n_kv_heads = 0 for a single buffer; wq = wk = NULL for rope without the norm.
+extern "C" int32_t agn_qk_norm_rope_qk_f16(agn_ctx *ctx, void *q, void *k, const float *wq, const float *wk, int64_t T,
+                                           int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, float eps,
+                                           int32_t n_rot, const int32_t *pos, int32_t pos_start, float theta,
+                                           float freq_scale, int32_t layout) {
+    AGN_CHECK_CTX(ctx);
+    const bool norm = wq != nullptr || wk != nullptr;
+    return rope_dispatch<__half>(ctx, norm ? "qk_norm_rope_qk_f16" : "rope_qk_f16", static_cast<__half *>(q),
+                                 static_cast<__half *>(k), wq, wk, norm, T, n_q_heads, n_kv_heads, head_dim, eps, n_rot, pos,
+                                 pos_start, theta, freq_scale, layout);
+}
+
+extern "C" int32_t agn_rope_qk_f16(agn_ctx *ctx, void *q, void *k, int64_t T, int32_t n_q_heads, int32_t n_kv_heads,
+                                   int32_t head_dim, int32_t n_rot, const int32_t *pos, int32_t pos_start, float theta,
+                                   float freq_scale, int32_t layout) {
+    return agn_qk_norm_rope_qk_f16(ctx, q, k, nullptr, nullptr, T, n_q_heads, n_kv_heads, head_dim, 0.0f, n_rot, pos,
+                                   pos_start, theta, freq_scale, layout);
 }

@@ -123,18 +123,19 @@ WORKLOADS = {
 DTYPE_NAMES = {8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}
 
 
-def op_bytes(cfg, T, ops):
-    """Algorithmic bytes of each op of a step for T token rows (f32 activations, read + write)."""
+def op_bytes(cfg, T, ops, act_bytes=4):
+    """Algorithmic bytes of each op of a step for T token rows (activations of act_bytes each, read + write)."""
     from agention_infer_b200 import CudaBackend
     H, hd, nq, nkv, I = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
-    rope = 8 * T * (nq + nkv) * hd + 4 * T + 2 * cfg.n_rot
+    a = act_bytes
+    rope = 2 * a * T * (nq + nkv) * hd + 4 * T + 2 * cfg.n_rot
     L = T  # c1: causal scores [nq, T, T]
     table = {
-        "get_rows": T * CudaBackend.type_size(cfg.embd_dtype, H) + 4 * T * H + 4 * T,
-        "rms_norm": 8 * T * H + 4 * H,
+        "get_rows": T * CudaBackend.type_size(cfg.embd_dtype, H) + a * T * H + 4 * T,
+        "rms_norm": 2 * a * T * H + 4 * H,
         "rope_qk": rope,
         "qk_norm_rope_qk": rope + 8 * hd,
-        "silu_mul": 12 * T * I * (2 if cfg.n_experts else 1),  # MoE: 2T routed rows
+        "silu_mul": 3 * a * T * I * (2 if cfg.n_experts else 1),  # MoE: 2T routed rows
         "softmax": 4 * (nq * L * (L + 1) // 2 + nq * L * L),
         "router_top2": 4 * T * max(cfg.n_experts, 1) + 16 * T,
         "gather_rows_by_expert": 2 * 2 * T * H * 4,
@@ -314,7 +315,11 @@ def run_ours(args, cfg, ops_list, wl):
     T_total = cfg.T if scaling == "strong" else world * cfg.T
     H, hd, nq, nkv, I, E = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn, cfg.n_experts
     R = 2 * T if E else T  # rows of the SwiGLU operands (MoE: routed rows)
-    ab = op_bytes(cfg, T, ops_list)
+    f16 = args.act == "f16"
+    if f16 and any(o in ops_list for o in ("softmax", "router_top2", "gather_rows_by_expert")):
+        raise SystemExit("--act f16 covers get_rows, rms_norm, rope, fused norm->rope and silu_mul (workloads c2, c4)")
+    adt = torch.float16 if f16 else torch.float32
+    ab = op_bytes(cfg, T, ops_list, 2 if f16 else 4)
     step_bytes = sum(ab.values())
     nsets = NSETS if step_bytes < 4e9 else 2
     table_h = synth.quant_table(cfg.embd_dtype, cfg.vocab, H, cfg_index=cfg.index)
@@ -325,7 +330,7 @@ def run_ours(args, cfg, ops_list, wl):
     wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
     pos = torch.from_numpy(synth.positions(cfg.index, T, cfg.random_pos)).to(dev)
     gen = torch.Generator(device=dev)
-    rn = lambda *shape: torch.randn(*shape, device=dev, generator=gen)
+    rn = lambda *shape: torch.randn(*shape, device=dev, generator=gen).to(adt)
     sets = []
     for s in range(nsets):
         # buffer set 0 holds the same values on every rank (its outputs are compared across ranks
@@ -333,9 +338,9 @@ def run_ours(args, cfg, ops_list, wl):
         salt = 0 if s == 0 else 1 + rank * NSETS + s
         gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index + 7919 * salt)
         ids = torch.from_numpy(synth.token_ids(cfg.index, T, cfg.vocab, salt=salt).astype(np.int32)).to(dev)
-        b = {"ids": ids, "emb": torch.empty(T, H, device=dev), "x": rn(T, H), "xn": torch.empty(T, H, device=dev),
-             "q": rn(T, nq * hd), "k": rn(T, nkv * hd), "gate": rn(R, I), "up": rn(R, I),
-             "act": torch.empty(R, I, device=dev)}
+        b = {"ids": ids, "emb": torch.empty(T, H, device=dev, dtype=adt), "x": rn(T, H),
+             "xn": torch.empty(T, H, device=dev, dtype=adt), "q": rn(T, nq * hd), "k": rn(T, nkv * hd), "gate": rn(R, I),
+             "up": rn(R, I), "act": torch.empty(R, I, device=dev, dtype=adt)}
         if "qk_norm_rope_qk" in ops_list:
             b.update(q2=rn(T, nq * hd), k2=rn(T, nkv * hd))
         if "softmax" in ops_list:
@@ -361,6 +366,16 @@ def run_ours(args, cfg, ops_list, wl):
                                                                     offsets=b["goff"], src_token=b["gtok"],
                                                                     src_slot=b["gslot"]),
     }
+    if f16:  # the same ops on f16 activation buffers (the reference's default `Act`)
+        all_ops.update({
+            "get_rows": lambda b: be.get_rows_f16(cfg.embd_dtype, table, table_bytes, cfg.vocab, H, b["ids"], T, out=b["emb"]),
+            "rms_norm": lambda b: be.launch_rms_norm_f16(b["x"], w, T, H, cfg.eps, out=b["xn"]),
+            "rope_qk": lambda b: be.launch_qk_norm_rope_qk_f16(b["q"], b["k"], None, None, T, nq, nkv, hd, 0.0, cfg.n_rot, pos,
+                                                               cfg.theta),
+            "qk_norm_rope_qk": lambda b: be.launch_qk_norm_rope_qk_f16(b["q2"], b["k2"], wq, wk, T, nq, nkv, hd, cfg.eps,
+                                                                       cfg.n_rot, pos, cfg.theta),
+            "silu_mul": lambda b: be.launch_silu_mul_f16(b["gate"], b["up"], R * I, out=b["act"]),
+        })
     ops = {k: all_ops[k] for k in ops_list}
     order = list(ops)
 
@@ -447,7 +462,7 @@ def run_ours(args, cfg, ops_list, wl):
     #      arrays out, every step, copies inside the timed region
     e2e = None
     e2e_ops = [o for o in order if o in ("get_rows", "rms_norm", "rope_qk", "qk_norm_rope_qk", "silu_mul", "softmax")]
-    if not args.no_e2e and e2e_ops == order and step_bytes < 4e9:  # (the 16 GB configuration would pin 17 GB of host memory)
+    if not args.no_e2e and not f16 and e2e_ops == order and step_bytes < 4e9:  # (the 16 GB configuration would pin 17 GB of host memory)
         b0 = sets[0]
         needs = {"get_rows": (["ids"], ["emb"]), "rms_norm": (["x"], ["xn"]), "rope_qk": (["q", "k"], []),
                  "qk_norm_rope_qk": (["q2", "k2"], []), "silu_mul": (["gate", "up"], ["act"]),
@@ -520,7 +535,7 @@ def run_ours(args, cfg, ops_list, wl):
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "f32" if not f16 else "f16 storage, f32 arithmetic", "data": "synthetic",
             "config": {"workload": cfg.name, "tokens_per_gpu": T, "tokens_total": T_total, "hidden": H, "head_dim": hd,
                        "q_heads": nq, "kv_heads": nkv, "ffn": I,
                        "embedding": f"{DTYPE_NAMES[cfg.embd_dtype]} {cfg.vocab}x{H}", "ops": order,
@@ -531,13 +546,13 @@ def run_ours(args, cfg, ops_list, wl):
             "roofline": {"kernel": "silu_mul_vec4_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of measured (copy bandwidth, MEASURED_PEAKS.json)" if peak_src == "measured"
-                         else "of fallback", "traffic": silu_traffic_bytes(R * I),
+                         else "of fallback", "traffic": silu_traffic_bytes(R * I) if not f16 else None,
                          "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
             "ops": per_op, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk), "outputs_checked": outs, "identical_across_ranks": agree,
                              "how": "checksums of every op's output for identical inputs, gathered over the process group"},
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not f16:
             out["cpu_baseline"] = cpu_baseline(cfg, order)
         print(json.dumps(out))
     if world > 1:
@@ -647,6 +662,8 @@ def main():
                     help="c2 (default, the headline): Qwen2.5-7B-shaped prefill, T=4096 rows per GPU; c1: Llama-3.2-1B "
                          "shapes incl. causal softmax; c3: decode latency sweep; c4: T=65536 Llama-3-8B-shaped rows "
                          "split over the GPUs; c5: Mixtral-shaped MoE routing ops")
+    ap.add_argument("--act", choices=["f32", "f16"], default="f32",
+                    help="activation storage: f32 (the benchmark's contract) or f16 (the reference GPU path's default)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (for comparison)")

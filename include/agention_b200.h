@@ -249,6 +249,35 @@ AGN_API int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, cons
                                               int32_t *offsets, int32_t *src_token,
                                               int32_t *src_slot);
 
+/* ------------------------------------------------- f16 activation storage (`Act = f16`)
+ * The reference's GPU path stores activations as f16 by default and computes in f32
+ * (`Act`, src/ops/mod.rs:36-45; kernels src/ops/kernels_wgpu.rs:22-31, 79-163, 225-318).
+ * These entry points take and return f16 buffers (IEEE binary16, converted with round to
+ * nearest even on store); norm weights stay f32; arguments otherwise as in the _f32 forms.
+ * For rope: k = NULL with n_kv_heads = 0 for one buffer; wq = wk = NULL skips the norm.
+ * Like the reference's f16 kernels, the fused ops round the intermediate (new_x, the
+ * normalised head) to f16 before it is used again. */
+AGN_API int32_t agn_silu_mul_f16(agn_ctx *ctx, const void *gate, const void *up, void *out, int64_t n);
+AGN_API int32_t agn_rms_norm_f16(agn_ctx *ctx, const void *x, const float *w, void *out, int64_t T,
+                                 int64_t H, float eps);
+AGN_API int32_t agn_add_residual_rms_norm_f16(agn_ctx *ctx, const void *x, const void *delta,
+                                              const float *w, void *new_x, void *normed, int64_t T,
+                                              int64_t H, float eps);
+AGN_API int32_t agn_rope_qk_f16(agn_ctx *ctx, void *q, void *k, int64_t T, int32_t n_q_heads,
+                                int32_t n_kv_heads, int32_t head_dim, int32_t n_rot,
+                                const int32_t *pos, int32_t pos_start, float theta, float freq_scale,
+                                int32_t layout);
+AGN_API int32_t agn_qk_norm_rope_qk_f16(agn_ctx *ctx, void *q, void *k, const float *wq,
+                                        const float *wk, int64_t T, int32_t n_q_heads,
+                                        int32_t n_kv_heads, int32_t head_dim, float eps, int32_t n_rot,
+                                        const int32_t *pos, int32_t pos_start, float theta,
+                                        float freq_scale, int32_t layout);
+/* get_rows with the output stored as f16 (`act_encode` of the dequantised row,
+ * src/ops/mod.rs:47-60): out is [T, row_len] f16. */
+AGN_API int32_t agn_get_rows_f16(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes,
+                                 int64_t n_rows, int64_t row_len, const uint32_t *ids, int64_t T,
+                                 void *out);
+
 /* ------------------------------------------------------- host-slice entry points
  * The same ops for callers whose activations live in HOST memory, as the reference's CPU
  * path does (`rms_norm_into(x: &[f32], w, out: &mut [f32])`, src/model/llama/cpu_path.rs:67;
