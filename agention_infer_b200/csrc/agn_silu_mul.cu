@@ -47,6 +47,48 @@ silu_mul_vec4_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__
     }
 }
 
+// f16 storage: at 6 bytes per element the f32 kernel's instruction stream (IEEE division,
+// full-range expf, one 64-bit access per four values) would bound the kernel, not HBM.  This
+// variant moves eight values per 128-bit access and uses the hardware approximations
+// (ex2.approx, rcp.approx: relative error ~2^-22), far below the 2^-11 rounding of the f16
+// result.
+__device__ __forceinline__ float silu_mul1_fast(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+__device__ __forceinline__ uint32_t silu_mul_h2(uint32_t g, uint32_t u) {
+    const float2 gf = __half22float2(*reinterpret_cast<const __half2 *>(&g));
+    const float2 uf = __half22float2(*reinterpret_cast<const __half2 *>(&u));
+    const __half2 r = __floats2half2_rn(silu_mul1_fast(gf.x, uf.x), silu_mul1_fast(gf.y, uf.y));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+template <int UNROLL>
+__global__ void __launch_bounds__(512)
+silu_mul_h8_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up, uint4 *__restrict__ out, int64_t n8) {
+    agn_pdl_prologue();
+    const int64_t tile = (int64_t)blockIdx.x * (UNROLL * blockDim.x);
+    uint4 g[UNROLL], u[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; k++) {
+        const int64_t i = tile + k * blockDim.x + threadIdx.x;
+        if (i < n8) {
+            g[k] = __ldcs(gate + i);
+            u[k] = __ldcs(up + i);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; k++) {
+        const int64_t i = tile + k * blockDim.x + threadIdx.x;
+        if (i < n8) {
+            uint4 o;
+            o.x = silu_mul_h2(g[k].x, u[k].x);
+            o.y = silu_mul_h2(g[k].y, u[k].y);
+            o.z = silu_mul_h2(g[k].z, u[k].z);
+            o.w = silu_mul_h2(g[k].w, u[k].w);
+            __stcs(out + i, o);
+        }
+    }
+}
+
 // Tail (n % 4 elements) and unaligned buffers.
 template <typename T>
 __global__ void silu_mul_scalar_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ out,
@@ -99,6 +141,24 @@ extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float
 // (src/ops/kernels_wgpu.rs:22-31).
 extern "C" int32_t agn_silu_mul_f16(agn_ctx *ctx, const void *gate, const void *up, void *out, int64_t n) {
     AGN_CHECK_CTX(ctx);
-    return silu_mul_dispatch<__half>(ctx, static_cast<const __half *>(gate), static_cast<const __half *>(up),
-                                     static_cast<__half *>(out), n);
+    if (n < 0) return agn_fail(ctx, AGN_EINVAL, "silu_mul_f16: n=%lld < 0", (long long)n);
+    if (n == 0) return AGN_OK;
+    if (!gate || !up || !out) return agn_fail(ctx, AGN_EINVAL, "silu_mul_f16: null pointer");
+    const __half *g = static_cast<const __half *>(gate), *u = static_cast<const __half *>(up);
+    __half *o = static_cast<__half *>(out);
+    int64_t done = 0;
+    if (agn_aligned16(gate) && agn_aligned16(up) && agn_aligned16(out) && n >= 8) {
+        AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+        const int64_t n8 = n / 8;
+        constexpr int THREADS = 256, UNROLL = 4;
+        const int64_t blocks = (n8 + THREADS * UNROLL - 1) / (THREADS * UNROLL);
+        if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul_f16: n too large");
+        agn_launch(ctx, silu_mul_h8_kernel<UNROLL>, dim3((unsigned)blocks), dim3(THREADS), 0, reinterpret_cast<const uint4 *>(gate),
+                   reinterpret_cast<const uint4 *>(up), reinterpret_cast<uint4 *>(out), n8);
+        AGN_LAUNCHED(ctx, "silu_mul_h8");
+        done = n8 * 8;
+    }
+    if (done == n) return AGN_OK;
+    // the remainder (and unaligned buffers) through the generic kernels
+    return silu_mul_dispatch<__half>(ctx, g + done, u + done, o + done, n - done);
 }
