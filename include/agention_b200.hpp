@@ -155,6 +155,52 @@ class CudaBackend {
         return read<float>(out, (size_t)row_len);  // sync inside throws on an out-of-range row
     }
 
+    // ---- f16 activation storage (`Act = f16`, src/ops/mod.rs:36-45): buffers are IEEE binary16
+    DeviceBuffer launch_silu_mul_f16(const void *gate, const void *up, int64_t n) {
+        DeviceBuffer out = empty(2 * (size_t)n);
+        check(agn_silu_mul_f16(ctx_, gate, up, out.ptr(), n));
+        return out;
+    }
+    DeviceBuffer launch_rms_norm_f16(const void *x, const float *w, int64_t T, int64_t H, float eps) {
+        DeviceBuffer out = empty(2 * (size_t)(T * H));
+        check(agn_rms_norm_f16(ctx_, x, w, out.ptr(), T, H, eps));
+        return out;
+    }
+    void launch_qk_norm_rope_qk_f16(void *q, void *k, const float *wq, const float *wk, int64_t T, int n_q, int n_kv,
+                                    int head_dim, float eps, int n_rot, const int32_t *pos, int pos_start, float theta,
+                                    float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {
+        check(agn_qk_norm_rope_qk_f16(ctx_, q, k, wq, wk, T, n_q, n_kv, head_dim, eps, n_rot, pos, pos_start, theta,
+                                      freq_scale, layout));
+    }
+
+    // ---- KV cache: KvCache::write_range / read_up_to (src/model/mod.rs:660-697)
+    void kv_write(int kv_dtype, const float *k, const float *v, void *k_cache, void *v_cache, int64_t T,
+                  int64_t head_dim_kv, const int32_t *pos, int pos_start, int64_t max_seq_len) {
+        check(agn_kv_write_f32(ctx_, kv_dtype, k, v, k_cache, v_cache, T, head_dim_kv, pos, pos_start, max_seq_len));
+    }
+    void kv_read(int kv_dtype, const void *k_cache, const void *v_cache, int64_t n_pos, int64_t head_dim_kv, float *k_out,
+                 float *v_out) {
+        check(agn_kv_read_f32(ctx_, kv_dtype, k_cache, v_cache, n_pos, head_dim_kv, k_out, v_out));
+    }
+
+    // ---- host slices, as the CPU path takes them (src/model/llama/cpu_path.rs:67,975-978)
+    void rms_norm_into(const float *x_host, const float *w_dev, float *out_host, int64_t T, int64_t H, float eps) {
+        check(agn_host_rms_norm_f32(ctx_, x_host, w_dev, out_host, T, H, eps));
+    }
+    void silu_mul_into(const float *gate_host, const float *up_host, float *out_host, int64_t n) {
+        check(agn_host_silu_mul_f32(ctx_, gate_host, up_host, out_host, n));
+    }
+
+    // ---- a recorded chain of ops (the decode loop), replayed with one launch
+    void graph_begin() { check(agn_graph_begin(ctx_)); }
+    agn_graph *graph_end() {
+        agn_graph *g = nullptr;
+        check(agn_graph_end(ctx_, &g));
+        return g;
+    }
+    void graph_launch(agn_graph *g) { check(agn_graph_launch(ctx_, g)); }
+    void graph_destroy(agn_graph *g) { check(agn_graph_destroy(ctx_, g)); }
+
     void check(int32_t st) const {
         if (st != AGN_OK) throw BackendError(st, agn_last_error(ctx_));
     }
