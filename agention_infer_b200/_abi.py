@@ -11,12 +11,23 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libagention_b200.so"
 
 AGN_OK, AGN_EINVAL, AGN_EUNSUPPORTED_DTYPE, AGN_ECUDA, AGN_EOOB_ID, AGN_ENOMEM, AGN_ETIMEOUT = range(7)
+AGN_EFORMAT, AGN_ENOTFOUND, AGN_EIO = 7, 8, 9
 AGN_F32, AGN_F16, AGN_Q8_0, AGN_Q4_K, AGN_Q6_K, AGN_BF16 = 0, 1, 8, 12, 14, 30
 AGN_Q5_0, AGN_Q5_K = 6, 13
 AGN_ROPE_NEOX, AGN_ROPE_NORMAL = 0, 1
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
 _pp = C.POINTER(C.c_void_p)
+
+
+class TensorInfo(C.Structure):
+    """agn_tensor_info"""
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int32), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4),
+                ("byte_offset", C.c_uint64), ("file_offset", C.c_uint64), ("n_rows", C.c_uint64), ("row_len", C.c_uint64),
+                ("row_bytes", C.c_uint64), ("n_bytes", C.c_uint64)]
+
+
+_pti = C.POINTER(TensorInfo)
 
 # name -> (restype, argtypes); must list every AGN_API symbol of the header
 SIGNATURES = {
@@ -55,6 +66,7 @@ SIGNATURES = {
                                        _f32, _f32, _i32]),
     "agn_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_softmax_rows_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32]),
+    "agn_softmax_rows_unnorm_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32]),
     "agn_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_kv_write_f32": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i32, _i64]),
     "agn_kv_read_f32": (_i32, [_vp, _i32, _vp, _vp, _i64, _i64, _vp, _vp]),
@@ -77,6 +89,20 @@ SIGNATURES = {
     "agn_host_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_gather_rows_by_expert_noalloc_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, C.c_char_p,
                                                      _sz]),
+    "agn_gguf_parse": (_i32, [_vp, _sz, _pp, C.c_char_p, _sz]),
+    "agn_gguf_open": (_i32, [C.c_char_p, _pp, C.c_char_p, _sz]),
+    "agn_gguf_close": (_i32, [_vp]),
+    "agn_gguf_version": (C.c_uint32, [_vp]),
+    "agn_gguf_tensor_count": (C.c_uint64, [_vp]),
+    "agn_gguf_metadata_count": (C.c_uint64, [_vp]),
+    "agn_gguf_data_offset": (C.c_uint64, [_vp]),
+    "agn_gguf_get_u64": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "agn_gguf_get_f32": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_float)]),
+    "agn_gguf_get_string": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_char_p)]),
+    "agn_gguf_get_array_info": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
+    "agn_gguf_tensor_at": (_i32, [_vp, C.c_uint64, _pti]),
+    "agn_gguf_find_tensor": (_i32, [_vp, C.c_char_p, _pti]),
+    "agn_gguf_upload_tensor": (_i32, [_vp, _vp, C.c_char_p, _pp, _pti]),
     "agn_type_size": (_sz, [_i32, _sz]),
 }
 

@@ -255,6 +255,17 @@ class CudaBackend:
                                                    _ptr(n_valid), causal_period, causal_offset))
         return out
 
+    def launch_attention_softmax(self, scores, n_heads: int, max_seq: int, pos: int, weights=None, sums=None):
+        """The softmax step of `launch_attention(.., pos, n_heads, max_seq)` (resident.rs:551-565) as the reference's
+        kernel leaves it: unnormalised weights [n_heads, max_seq] and sums [n_heads] over entries 0..=pos."""
+        if weights is None:
+            weights = self.empty(4 * n_heads * max_seq)
+        if sums is None:
+            sums = self.empty(4 * n_heads)
+        self._check(self._lib.agn_softmax_rows_unnorm_f32(self._ctx, _ptr(scores), _ptr(weights), _ptr(sums), n_heads,
+                                                          max_seq, max_seq, None, 1, pos))
+        return weights, sums
+
     def get_rows(self, dtype: int, table, table_bytes: int, n_rows: int, row_len: int, ids, T: int, out=None):
         """Embedding loop `dequant_row(token_embd, token)` for T tokens (cpu_path.rs:865-868)."""
         if out is None:

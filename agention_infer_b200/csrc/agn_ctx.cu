@@ -28,6 +28,9 @@ const char *agn_status_string(int32_t s) {
     case AGN_EOOB_ID: return "row index out of range";
     case AGN_ENOMEM: return "out of memory";
     case AGN_ETIMEOUT: return "device-side wait timed out";
+    case AGN_EFORMAT: return "malformed GGUF data";
+    case AGN_ENOTFOUND: return "not found";
+    case AGN_EIO: return "file cannot be opened or mapped";
     default: return "unknown status";
     }
 }

@@ -1,0 +1,330 @@
+// GGUF container glue: header, metadata and tensor directory of a GGUF v2/v3 file, and the
+// upload of one tensor's bytes to the device (the quantised embedding table that
+// agn_get_rows_* reads, or a norm weight).  Host code only.
+//
+// Reference: `parser::parse` (src/parser.rs:9-66, value decoding :158-186), `loader::load`
+// (src/loader.rs:14-19, memory-mapped), `GgufFile` accessors and `MetadataValue::as_*`
+// (src/types.rs), tensor addressing `data_offset + byte_offset` with dims[0] the contiguous
+// dimension (src/quant/mod.rs:97-135), weight pre-upload (src/model/llama/gpu_resident.rs:112-152).
+#include <errno.h>
+#include <fcntl.h>
+#include <stdarg.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "agn_common.cuh"
+
+namespace {
+
+struct MetaValue {
+    uint32_t type = 0;       // GGUF value type id, 9 = array
+    uint64_t u = 0;          // unsigned / bool payload
+    int64_t i = 0;           // signed payload
+    double f = 0.0;          // float payload
+    std::string s;           // string payload
+    uint32_t elem_type = 0;  // arrays: element type and count (elements are skipped, not kept)
+    uint64_t count = 0;
+};
+
+struct Tensor {
+    std::string name;
+    uint32_t n_dims = 0;
+    uint64_t dims[4] = {1, 1, 1, 1};
+    uint32_t ggml_type = 0;
+    uint64_t byte_offset = 0;
+};
+
+struct Cursor {
+    const uint8_t *data;
+    size_t len, pos;
+    bool ok;
+    size_t err_pos;
+    bool need(size_t n) {
+        if (!ok) return false;
+        if (len - pos < n) {
+            ok = false;
+            err_pos = pos;
+            return false;
+        }
+        return true;
+    }
+    template <typename T> T read() {
+        T v{};
+        if (need(sizeof(T))) {
+            memcpy(&v, data + pos, sizeof(T));
+            pos += sizeof(T);
+        }
+        return v;
+    }
+    std::string read_string() {
+        const uint64_t n = read<uint64_t>();
+        if (!ok) return std::string();
+        if (n > len - pos) {
+            ok = false;
+            err_pos = pos;
+            return std::string();
+        }
+        std::string s(reinterpret_cast<const char *>(data + pos), (size_t)n);
+        pos += (size_t)n;
+        return s;
+    }
+};
+
+int32_t gfail(char *err, size_t err_len, int32_t status, const char *fmt, ...) {
+    if (err && err_len) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, err_len, fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+// the GgmlType ids the reference knows (src/types.rs:9-46); 4 and 5 were removed from ggml
+bool known_ggml_type(uint32_t t) { return t <= 33 && t != 4 && t != 5; }
+
+}  // namespace
+
+struct agn_gguf {
+    uint32_t version = 0;
+    uint64_t tensor_count = 0, data_offset = 0;
+    std::map<std::string, MetaValue> meta;
+    std::vector<Tensor> tensors;
+    const uint8_t *data = nullptr;  // whole file (mapping or caller's memory)
+    size_t len = 0;
+    void *mapping = nullptr;        // non-null when this object owns an mmap
+    size_t map_len = 0;
+};
+
+namespace {
+
+// src/parser.rs:158-186.  Returns false on an unknown type id.
+bool read_value(Cursor &c, uint32_t type, MetaValue &v, bool keep) {
+    v.type = type;
+    switch (type) {
+    case 0: v.u = c.read<uint8_t>(); break;
+    case 1: v.i = c.read<int8_t>(); break;
+    case 2: v.u = c.read<uint16_t>(); break;
+    case 3: v.i = c.read<int16_t>(); break;
+    case 4: v.u = c.read<uint32_t>(); break;
+    case 5: v.i = c.read<int32_t>(); break;
+    case 6: v.f = c.read<float>(); break;
+    case 7: v.u = c.read<uint8_t>() != 0; break;
+    case 8: { std::string s = c.read_string(); if (keep) v.s.swap(s); break; }
+    case 9: {
+        v.elem_type = c.read<uint32_t>();
+        if (c.ok && (v.elem_type > 12 || v.elem_type == 9)) return false;  // MetadataArrayType::from_u32
+        v.count = c.read<uint64_t>();
+        for (uint64_t k = 0; k < v.count && c.ok; k++) {
+            MetaValue e;
+            if (!read_value(c, v.elem_type, e, false)) return false;
+        }
+        break;
+    }
+    case 10: v.u = c.read<uint64_t>(); break;
+    case 11: v.i = c.read<int64_t>(); break;
+    case 12: v.f = c.read<double>(); break;
+    default: return false;
+    }
+    return true;
+}
+
+int32_t parse_into(agn_gguf *g, char *err, size_t err_len) {
+    Cursor c{g->data, g->len, 0, true, 0};
+    // src/parser.rs:12-24
+    uint8_t magic[4] = {0, 0, 0, 0};
+    if (c.need(4)) { memcpy(magic, c.data, 4); c.pos = 4; }
+    if (!c.ok) return gfail(err, err_len, AGN_EFORMAT, "unexpected end of data at offset %zu", c.err_pos);
+    if (memcmp(magic, "GGUF", 4) != 0) return gfail(err, err_len, AGN_EFORMAT, "invalid GGUF magic");
+    g->version = c.read<uint32_t>();
+    if (c.ok && (g->version < 2 || g->version > 3))
+        return gfail(err, err_len, AGN_EFORMAT, "unsupported GGUF version %u", g->version);
+    g->tensor_count = c.read<uint64_t>();
+    const uint64_t kv_count = c.read<uint64_t>();
+    for (uint64_t k = 0; k < kv_count && c.ok; k++) {  // :27-33
+        std::string key = c.read_string();
+        const uint32_t type = c.read<uint32_t>();
+        MetaValue v;
+        if (c.ok && !read_value(c, type, v, true))
+            return gfail(err, err_len, AGN_EFORMAT, "unknown metadata type %u", c.ok ? (type == 9 ? v.elem_type : type) : type);
+        if (c.ok) g->meta[key] = v;
+    }
+    for (uint64_t k = 0; k < g->tensor_count && c.ok; k++) {  // :36-55
+        Tensor t;
+        t.name = c.read_string();
+        t.n_dims = c.read<uint32_t>();
+        if (c.ok && t.n_dims > 4) return gfail(err, err_len, AGN_EFORMAT, "tensor '%s' has %u dimensions", t.name.c_str(), t.n_dims);
+        for (uint32_t d = 0; d < t.n_dims && c.ok; d++) t.dims[d] = c.read<uint64_t>();
+        t.ggml_type = c.read<uint32_t>();
+        if (c.ok && !known_ggml_type(t.ggml_type)) return gfail(err, err_len, AGN_EFORMAT, "unknown ggml type %u", t.ggml_type);
+        t.byte_offset = c.read<uint64_t>();
+        if (c.ok) g->tensors.push_back(t);
+    }
+    if (!c.ok) return gfail(err, err_len, AGN_EFORMAT, "unexpected end of data at offset %zu", c.err_pos);
+    g->data_offset = ((uint64_t)c.pos + 31) & ~(uint64_t)31;  // :58, 32-byte alignment
+    return AGN_OK;
+}
+
+const MetaValue *find_meta(const agn_gguf *g, const char *key) {
+    if (!g || !key) return nullptr;
+    auto it = g->meta.find(key);
+    return it == g->meta.end() ? nullptr : &it->second;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t agn_gguf_parse(const void *data, size_t len, agn_gguf **out, char *err, size_t err_len) {
+    if (err && err_len) err[0] = '\0';
+    if (!out || (!data && len)) return gfail(err, err_len, AGN_EINVAL, "agn_gguf_parse: null argument");
+    *out = nullptr;
+    agn_gguf *g = new agn_gguf();
+    g->data = static_cast<const uint8_t *>(data);
+    g->len = len;
+    const int32_t rc = parse_into(g, err, err_len);
+    if (rc != AGN_OK) {
+        delete g;
+        return rc;
+    }
+    *out = g;
+    return AGN_OK;
+}
+
+int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_len) {
+    if (err && err_len) err[0] = '\0';
+    if (!path || !out) return gfail(err, err_len, AGN_EINVAL, "agn_gguf_open: null argument");
+    *out = nullptr;
+    const int fd = open(path, O_RDONLY);
+    if (fd < 0) return gfail(err, err_len, AGN_EIO, "cannot open %s: %s", path, strerror(errno));
+    struct stat st;
+    if (fstat(fd, &st) != 0 || st.st_size <= 0) {
+        close(fd);
+        return gfail(err, err_len, AGN_EIO, "cannot stat %s or the file is empty", path);
+    }
+    void *m = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (m == MAP_FAILED) return gfail(err, err_len, AGN_EIO, "cannot map %s: %s", path, strerror(errno));
+    agn_gguf *g = new agn_gguf();
+    g->data = static_cast<const uint8_t *>(m);
+    g->len = (size_t)st.st_size;
+    g->mapping = m;
+    g->map_len = (size_t)st.st_size;
+    const int32_t rc = parse_into(g, err, err_len);
+    if (rc != AGN_OK) {
+        munmap(m, g->map_len);
+        delete g;
+        return rc;
+    }
+    *out = g;
+    return AGN_OK;
+}
+
+int32_t agn_gguf_close(agn_gguf *g) {
+    if (!g) return AGN_OK;
+    if (g->mapping) munmap(g->mapping, g->map_len);
+    delete g;
+    return AGN_OK;
+}
+
+uint32_t agn_gguf_version(const agn_gguf *g) { return g ? g->version : 0; }
+uint64_t agn_gguf_tensor_count(const agn_gguf *g) { return g ? g->tensor_count : 0; }
+uint64_t agn_gguf_data_offset(const agn_gguf *g) { return g ? g->data_offset : 0; }
+uint64_t agn_gguf_metadata_count(const agn_gguf *g) { return g ? g->meta.size() : 0; }
+
+// `GgufFile::get_u64` -> `MetadataValue::as_u64` (unsigned types only), src/types.rs
+int32_t agn_gguf_get_u64(const agn_gguf *g, const char *key, uint64_t *out) {
+    const MetaValue *v = find_meta(g, key);
+    if (!v || !out) return AGN_ENOTFOUND;
+    if (v->type == 0 || v->type == 2 || v->type == 4 || v->type == 10) {
+        *out = v->u;
+        return AGN_OK;
+    }
+    return AGN_ENOTFOUND;
+}
+
+// `MetadataValue::as_f32`: Float32, or Float64 narrowed
+int32_t agn_gguf_get_f32(const agn_gguf *g, const char *key, float *out) {
+    const MetaValue *v = find_meta(g, key);
+    if (!v || !out || (v->type != 6 && v->type != 12)) return AGN_ENOTFOUND;
+    *out = (float)v->f;
+    return AGN_OK;
+}
+
+// `GgufFile::get_string`; the pointer lives as long as the agn_gguf
+int32_t agn_gguf_get_string(const agn_gguf *g, const char *key, const char **out) {
+    const MetaValue *v = find_meta(g, key);
+    if (!v || !out || v->type != 8) return AGN_ENOTFOUND;
+    *out = v->s.c_str();
+    return AGN_OK;
+}
+
+// arrays are indexed, not kept: element type id and length
+int32_t agn_gguf_get_array_info(const agn_gguf *g, const char *key, uint32_t *elem_type, uint64_t *count) {
+    const MetaValue *v = find_meta(g, key);
+    if (!v || v->type != 9) return AGN_ENOTFOUND;
+    if (elem_type) *elem_type = v->elem_type;
+    if (count) *count = v->count;
+    return AGN_OK;
+}
+
+int32_t agn_gguf_tensor_at(const agn_gguf *g, uint64_t index, agn_tensor_info *out) {
+    if (!g || !out || index >= g->tensors.size()) return AGN_ENOTFOUND;
+    const Tensor &t = g->tensors[(size_t)index];
+    memset(out, 0, sizeof(*out));
+    out->name = t.name.c_str();
+    out->ggml_type = (int32_t)t.ggml_type;
+    out->n_dims = t.n_dims;
+    for (int d = 0; d < 4; d++) out->dims[d] = t.dims[d];
+    out->byte_offset = t.byte_offset;
+    out->file_offset = g->data_offset + t.byte_offset;
+    uint64_t rows = 1;
+    for (uint32_t d = 1; d < t.n_dims; d++) rows *= t.dims[d];
+    out->n_rows = t.n_dims <= 1 ? 1 : rows;
+    out->row_len = t.n_dims >= 1 ? t.dims[0] : 0;
+    out->row_bytes = agn_type_size((int32_t)t.ggml_type, (size_t)out->row_len);  // 0: no codec for this type
+    out->n_bytes = out->row_bytes * out->n_rows;
+    return AGN_OK;
+}
+
+int32_t agn_gguf_find_tensor(const agn_gguf *g, const char *name, agn_tensor_info *out) {
+    if (!g || !name || !out) return AGN_ENOTFOUND;
+    for (size_t k = 0; k < g->tensors.size(); k++)
+        if (g->tensors[k].name == name) return agn_gguf_tensor_at(g, k, out);
+    return AGN_ENOTFOUND;
+}
+
+// Copies one tensor's bytes into a new device allocation (freed with agn_free).  The copy is
+// stream-ordered on the context's stream and complete when the call returns.
+int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name, void **dptr, agn_tensor_info *info) {
+    AGN_CHECK_CTX(ctx);
+    if (!g || !name || !dptr) return agn_fail(ctx, AGN_EINVAL, "agn_gguf_upload_tensor: null argument");
+    *dptr = nullptr;
+    agn_tensor_info ti;
+    if (agn_gguf_find_tensor(g, name, &ti) != AGN_OK) return agn_fail(ctx, AGN_ENOTFOUND, "tensor '%s' not found", name);
+    if (ti.row_bytes == 0)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "tensor '%s' has ggml type %d, which has no codec here", name, ti.ggml_type);
+    if (ti.file_offset + ti.n_bytes > g->len)  // "tensor row .. extends beyond data section", src/quant/mod.rs:124-131
+        return agn_fail(ctx, AGN_EFORMAT, "tensor '%s' extends beyond the file (offset %llu + %llu bytes > %zu)", name,
+                        (unsigned long long)ti.file_offset, (unsigned long long)ti.n_bytes, g->len);
+    void *d = nullptr;
+    int32_t rc = agn_malloc(ctx, (size_t)ti.n_bytes, &d);
+    if (rc != AGN_OK) return rc;
+    rc = agn_memcpy_h2d(ctx, d, g->data + ti.file_offset, (size_t)ti.n_bytes);
+    if (rc == AGN_OK) rc = agn_sync(ctx);
+    if (rc != AGN_OK) {
+        agn_free(ctx, d);
+        return rc;
+    }
+    *dptr = d;
+    if (info) *info = ti;
+    return AGN_OK;
+}
+
+}  // extern "C"

@@ -21,6 +21,7 @@ struct SoftmaxArgs {
     const float *in;
     float *out;
     const int32_t *n_valid;
+    float *sums;  // non-null: store the unnormalised exp(s - max) and the row sums (the reference's GPU form)
     int64_t n_rows, row_len, row_stride;
     int causal_period, causal_offset;
 };
@@ -84,7 +85,8 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
         sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
     }
     sum = agn_warp_sum(sum);
-    const float inv = 1.0f / sum;  // s / sum of the CPU path as s * (1/sum): <= 1 ulp apart
+    if (a.sums && lane == 0) a.sums[r] = sum;
+    const float inv = a.sums ? 1.0f : 1.0f / sum;  // s / sum of the CPU path as s * (1/sum): <= 1 ulp apart
 #pragma unroll
     for (int k = 0; k < VPL; k++) {
         const int i = lane + 32 * k;
@@ -132,7 +134,8 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     __syncthreads();
     sum = 0.0f;
     for (int w = 0; w < nwarps; w++) sum += red[w];
-    const float inv = 1.0f / sum;
+    if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
+    const float inv = a.sums ? 1.0f : 1.0f / sum;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
@@ -174,15 +177,16 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     __syncthreads();
     sum = 0.0f;
     for (int w = 0; w < nwarps; w++) sum += red[w];
-    for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) out[i] = i < nv ? out[i] / sum : 0.0f;
+    if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
+    const float inv = a.sums ? 1.0f : 1.0f / sum;
+    for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) out[i] = i < nv ? out[i] * inv : 0.0f;
 }
 
 }  // namespace
 
-extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, int64_t n_rows, int64_t row_len,
-                                        int64_t row_stride, const int32_t *n_valid, int32_t causal_period,
-                                        int32_t causal_offset) {
-    AGN_CHECK_CTX(ctx);
+namespace {
+int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums, int64_t n_rows, int64_t row_len,
+                         int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset) {
     if (n_rows < 0 || row_len < 0 || row_stride < row_len || causal_period < 0 || causal_offset < 0)
         return agn_fail(ctx, AGN_EINVAL, "softmax_rows: n_rows=%lld row_len=%lld row_stride=%lld period=%d offset=%d",
                         (long long)n_rows, (long long)row_len, (long long)row_stride, causal_period, causal_offset);
@@ -191,7 +195,7 @@ extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *ou
     if (n_rows > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "softmax_rows: n_rows too large");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     SoftmaxArgs a;
-    a.in = in; a.out = out; a.n_valid = n_valid; a.n_rows = n_rows; a.row_len = row_len; a.row_stride = row_stride;
+    a.in = in; a.out = out; a.sums = sums; a.n_valid = n_valid; a.n_rows = n_rows; a.row_len = row_len; a.row_stride = row_stride;
     a.causal_period = causal_period; a.causal_offset = causal_offset;
     const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned16(out);
     const int64_t n4 = row_len / 4;
@@ -217,4 +221,24 @@ extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *ou
         AGN_LAUNCHED(ctx, "softmax_generic_rows");
     }
     return AGN_OK;
+}
+}  // namespace
+
+extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, int64_t n_rows, int64_t row_len,
+                                        int64_t row_stride, const int32_t *n_valid, int32_t causal_period,
+                                        int32_t causal_offset) {
+    AGN_CHECK_CTX(ctx);
+    return softmax_dispatch(ctx, in, out, nullptr, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
+}
+
+// The softmax step of the reference's GPU attention exactly as its kernel leaves it
+// (`attention_softmax`, src/ops/kernels_wgpu.rs:795-864): weights = exp(s - max) without the
+// division, sums[row] = their sum; the division is left to the consumer (`attention_output`
+// divides by sums[h], :866-898).
+extern "C" int32_t agn_softmax_rows_unnorm_f32(agn_ctx *ctx, const float *in, float *weights, float *sums, int64_t n_rows,
+                                               int64_t row_len, int64_t row_stride, const int32_t *n_valid,
+                                               int32_t causal_period, int32_t causal_offset) {
+    AGN_CHECK_CTX(ctx);
+    if (n_rows > 0 && !sums) return agn_fail(ctx, AGN_EINVAL, "softmax_rows_unnorm: null sums");
+    return softmax_dispatch(ctx, in, weights, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
 }

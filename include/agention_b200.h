@@ -46,7 +46,11 @@ typedef enum agn_status {
     AGN_EOOB_ID = 4,           /* get_rows met a row index >= n_rows ("row index .. out of
                                   range", src/quant/mod.rs:116-120); that output row is zero */
     AGN_ENOMEM = 5,            /* device or pinned allocation failed */
-    AGN_ETIMEOUT = 6           /* a bounded device-side wait gave up (staging barrier) */
+    AGN_ETIMEOUT = 6,          /* a bounded device-side wait gave up (staging barrier) */
+    AGN_EFORMAT = 7,           /* malformed GGUF data (`GgufError::InvalidMagic`, `UnsupportedVersion`,
+                                  `UnexpectedEof`, `UnknownMetadataType`, src/error.rs:3-42) */
+    AGN_ENOTFOUND = 8,         /* no such metadata key / tensor, or a value of another type */
+    AGN_EIO = 9                /* the file cannot be opened or mapped */
 } agn_status;
 
 /* GgmlType discriminants accepted by agn_get_rows_f32 (src/types.rs:9-46). */
@@ -197,6 +201,16 @@ AGN_API int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *out, 
                                      const int32_t *n_valid, int32_t causal_period,
                                      int32_t causal_offset);
 
+/* The same step in the form the reference's GPU kernel leaves it (`attention_softmax`,
+ * src/ops/kernels_wgpu.rs:795-864; called from `launch_attention`, resident.rs:551-565):
+ * weights = exp(s - max) WITHOUT the division, sums[r] = their sum over the valid entries
+ * (`attention_output` divides by it, kernels_wgpu.rs:866-898).  Entries past the valid
+ * length are written as 0; sums of a row with no valid entry is 0. */
+AGN_API int32_t agn_softmax_rows_unnorm_f32(agn_ctx *ctx, const float *in, float *weights, float *sums,
+                                            int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                            const int32_t *n_valid, int32_t causal_period,
+                                            int32_t causal_offset);
+
 /* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
  * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
  * -> dequant_q8_0 / dequant_q4_k / dequant_q6_k (src/quant/q8_0.rs:14-51,
@@ -339,6 +353,44 @@ AGN_API int32_t agn_gather_rows_by_expert_noalloc_f32(void *cuda_stream, const f
                                                       int32_t n_experts, float *out, int32_t *offsets,
                                                       int32_t *src_token, int32_t *src_slot,
                                                       char *err, size_t err_len);
+
+/* ----------------------------------------------------------------- GGUF files
+ * The container side of get_rows: `parser::parse` (src/parser.rs:9-66), `loader::load`
+ * (src/loader.rs:14-19, memory-mapped), `GgufFile::get_*` / `MetadataValue::as_*`
+ * (src/types.rs), and the upload of a tensor's bytes (`pre_upload_gpu`,
+ * src/model/llama/gpu_resident.rs:112-152).  Versions 2 and 3; the data section starts at
+ * the next multiple of 32 after the tensor directory.  Array metadata is indexed (element
+ * type and count), its elements are not kept.  `err` (may be NULL) receives a message. */
+typedef struct agn_gguf agn_gguf;
+typedef struct agn_tensor_info {  /* `TensorInfo` (src/types.rs:373-403) plus derived sizes */
+    const char *name;      /* lives as long as the agn_gguf */
+    int32_t ggml_type;     /* GgmlType id */
+    uint32_t n_dims;
+    uint64_t dims[4];      /* dims[0] is the contiguous dimension (row length) */
+    uint64_t byte_offset;  /* inside the data section */
+    uint64_t file_offset;  /* data_offset + byte_offset */
+    uint64_t n_rows;       /* product of dims[1..], 1 for a 1-D tensor (src/quant/mod.rs:107-111) */
+    uint64_t row_len;      /* dims[0] */
+    uint64_t row_bytes;    /* type_size(row_len); 0 when the type has no codec here */
+    uint64_t n_bytes;      /* row_bytes * n_rows */
+} agn_tensor_info;
+AGN_API int32_t agn_gguf_parse(const void *data, size_t len, agn_gguf **out, char *err, size_t err_len);
+AGN_API int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_len);
+AGN_API int32_t agn_gguf_close(agn_gguf *g);
+AGN_API uint32_t agn_gguf_version(const agn_gguf *g);
+AGN_API uint64_t agn_gguf_tensor_count(const agn_gguf *g);
+AGN_API uint64_t agn_gguf_metadata_count(const agn_gguf *g);
+AGN_API uint64_t agn_gguf_data_offset(const agn_gguf *g);
+AGN_API int32_t agn_gguf_get_u64(const agn_gguf *g, const char *key, uint64_t *out);
+AGN_API int32_t agn_gguf_get_f32(const agn_gguf *g, const char *key, float *out);
+AGN_API int32_t agn_gguf_get_string(const agn_gguf *g, const char *key, const char **out);
+AGN_API int32_t agn_gguf_get_array_info(const agn_gguf *g, const char *key, uint32_t *elem_type, uint64_t *count);
+AGN_API int32_t agn_gguf_tensor_at(const agn_gguf *g, uint64_t index, agn_tensor_info *out);
+AGN_API int32_t agn_gguf_find_tensor(const agn_gguf *g, const char *name, agn_tensor_info *out);
+/* Copies the tensor's bytes into a new device allocation (free with agn_free); complete on
+ * return.  The result is what agn_get_rows_* takes as `table` (n_rows, row_len from info). */
+AGN_API int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name, void **dptr,
+                                       agn_tensor_info *info);
 
 /* `GgmlType::type_size` (src/types.rs:164-168); 0 for a dtype without a kernel. */
 AGN_API size_t agn_type_size(int32_t dtype, size_t n);

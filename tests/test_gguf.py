@@ -1,0 +1,131 @@
+"""GGUF container glue through the C ABI: the reference parser's own unit-test vectors
+(src/parser.rs:209-303), a file with metadata and tensors, and (GPU) get_rows from a tensor
+uploaded out of a GGUF file."""
+import struct
+
+import numpy as np
+import pytest
+
+from agention_infer_b200 import AGN_Q4_K, AGN_Q8_0, _abi, synth
+from agention_infer_b200.gguf import GgufError, GgufFile
+from oracle import oracle as orc
+from tests import gguf_writer as gw
+
+
+def test_parse_minimal_v2():  # src/parser.rs:209-218
+    g = GgufFile(data=gw.header(2, 0, 0))
+    assert g.version == 2 and g.tensor_count == 0 and g.metadata_count == 0 and g.tensors() == []
+
+
+def test_parse_invalid_magic():  # src/parser.rs:220-225
+    with pytest.raises(GgufError) as e:
+        GgufFile(data=bytes(24))
+    assert e.value.status == _abi.AGN_EFORMAT and "magic" in str(e.value)
+
+
+def test_parse_unsupported_version():  # src/parser.rs:227-233
+    with pytest.raises(GgufError) as e:
+        GgufFile(data=gw.header(1, 0, 0))
+    assert "version 1" in str(e.value)
+    with pytest.raises(GgufError):
+        GgufFile(data=gw.header(4, 0, 0))
+
+
+def test_parse_v3_with_metadata():  # src/parser.rs:235-246
+    data = gw.header(3, 0, 1) + gw.gstr("general.architecture") + struct.pack("<I", 8) + gw.gstr("llama")
+    g = GgufFile(data=data)
+    assert g.version == 3 and g.get_string("general.architecture") == "llama"
+    assert g.get_u64("general.architecture") is None and g.get_string("missing") is None
+
+
+def test_parse_metadata_u32():  # src/parser.rs:248-257
+    data = gw.header(3, 0, 1) + gw.gstr("test.value") + struct.pack("<II", 4, 42)
+    assert GgufFile(data=data).get_u64("test.value") == 42
+
+
+def test_parse_with_tensor():  # src/parser.rs:259-275
+    data = gw.header(3, 1, 0) + gw.gstr("output.weight") + struct.pack("<IQQIQ", 2, 4096, 4096, 8, 0)
+    g = GgufFile(data=data)
+    (t,) = g.tensors()
+    assert t.name == "output.weight" and t.dims == [4096, 4096] and t.ggml_type == AGN_Q8_0
+    assert t.row_len == 4096 and t.n_rows == 4096 and t.row_bytes == 4352  # 128 blocks of 34 bytes
+    assert g.data_offset % 32 == 0 and g.data_offset >= len(data)
+
+
+def test_parse_array_metadata():  # src/parser.rs:277-294
+    data = gw.header(3, 0, 1) + gw.gstr("tokenizer.ggml.bos_token_id") + struct.pack("<IIQI", 9, 4, 1, 1)
+    assert GgufFile(data=data).get_array_info("tokenizer.ggml.bos_token_id") == (4, 1)
+
+
+def test_unexpected_eof():  # src/parser.rs:296-303
+    with pytest.raises(GgufError) as e:
+        GgufFile(data=gw.header(3, 0, 1))
+    assert e.value.status == _abi.AGN_EFORMAT and "end of data" in str(e.value)
+
+
+def test_unknown_types_are_errors():
+    with pytest.raises(GgufError) as e:  # `UnknownMetadataType`
+        GgufFile(data=gw.header(3, 0, 1) + gw.gstr("k") + struct.pack("<II", 13, 0))
+    assert "metadata type 13" in str(e.value)
+    with pytest.raises(GgufError):  # `GgmlType::from_u32` rejects the removed ids 4 and 5
+        GgufFile(data=gw.header(3, 1, 0) + gw.gstr("t") + struct.pack("<IQIQ", 1, 32, 4, 0))
+
+
+def _model_file(vocab=96, hidden=256):
+    table = synth.quant_table(AGN_Q4_K, vocab, hidden, cfg_index=2)
+    norm = synth.norm_weight(2, "w", hidden)
+    meta = [("general.architecture", "str", "llama"), ("llama.embedding_length", "u32", hidden),
+            ("llama.attention.layer_norm_rms_epsilon", "f32", 1e-5), ("llama.rope.freq_base", "f64", 500000.0),
+            ("llama.block_count", "u64", 2), ("llama.context_length", "u16", 4096), ("general.flag", "bool", 1),
+            ("tokenizer.ggml.tokens", "array", ("str", ["<s>", "</s>", "hello", "wor", "ld"])),
+            ("tokenizer.ggml.scores", "array", ("f32", [0.0, -1.0, -2.5])), ("general.quant_version", "i32", -2)]
+    tensors = [("token_embd.weight", AGN_Q4_K, [hidden, vocab], table), ("output_norm.weight", 0, [hidden], norm),
+               ("blk.0.ffn_gate.weight", 11, [256, 4], bytes(110 * 4))]  # Q3_K: listed, but no codec here
+    return gw.build(3, meta, tensors), table, norm
+
+
+def test_file_with_metadata_and_tensors(tmp_path):
+    blob, table, norm = _model_file()
+    path = tmp_path / "tiny.gguf"
+    path.write_bytes(blob)
+    for g in (GgufFile(str(path)), GgufFile(data=blob)):
+        assert g.metadata_count == 10 and g.tensor_count == 3
+        assert g.get_u64("llama.embedding_length") == 256 and g.get_u64("llama.block_count") == 2
+        assert g.get_u64("llama.context_length") == 4096 and g.get_u64("general.quant_version") is None  # signed: not a u64
+        assert abs(g.get_f32("llama.attention.layer_norm_rms_epsilon") - 1e-5) < 1e-12
+        assert g.get_f32("llama.rope.freq_base") == 500000.0  # Float64 narrows
+        assert g.get_array_info("tokenizer.ggml.tokens") == (8, 5) and g.get_array_info("tokenizer.ggml.scores") == (6, 3)
+        emb = g.find("token_embd.weight")
+        assert emb.dims == [256, 96] and emb.row_len == 256 and emb.n_rows == 96 and emb.row_bytes == 144
+        assert emb.file_offset == g.data_offset + emb.byte_offset and emb.file_offset % 32 == 0
+        assert blob[emb.file_offset:emb.file_offset + emb.n_bytes] == table.tobytes()
+        nw = g.find("output_norm.weight")
+        assert nw.n_rows == 1 and nw.row_len == 256 and nw.n_bytes == 1024
+        assert np.array_equal(np.frombuffer(blob[nw.file_offset:nw.file_offset + 1024], np.float32), norm)
+        assert g.find("blk.0.ffn_gate.weight").row_bytes == 0 and g.find("nope") is None
+        g.close()
+    with pytest.raises(GgufError) as e:
+        GgufFile(str(tmp_path / "absent.gguf"))
+    assert e.value.status == _abi.AGN_EIO
+
+
+@pytest.mark.gpu
+def test_get_rows_from_a_tensor_uploaded_out_of_a_gguf_file(backend, tmp_path):
+    blob, table, norm = _model_file(vocab=512, hidden=1024)
+    path = tmp_path / "tiny.gguf"
+    path.write_bytes(blob)
+    g = GgufFile(str(path))
+    dtab, info = g.upload(backend, "token_embd.weight")
+    ids = synth.token_ids(2, 100, info.n_rows)
+    out = backend.get_rows(info.ggml_type, dtab, info.n_bytes, info.n_rows, info.row_len, backend.upload(ids), 100)
+    st, ref = orc.get_rows(orc.Q4_K, table, info.n_rows, info.row_len, ids)
+    assert st == orc.OK and np.array_equal(backend.read(out, np.float32, ref.shape).view(np.uint32), ref.view(np.uint32))
+    dnorm, ninfo = g.upload(backend, "output_norm.weight")
+    assert np.array_equal(backend.read(dnorm, np.float32, (ninfo.row_len,)), norm)
+    from agention_infer_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        g.upload(backend, "blk.0.ffn_gate.weight")
+    assert e.value.status == _abi.AGN_EUNSUPPORTED_DTYPE
+    with pytest.raises(BackendError) as e:
+        g.upload(backend, "nope")
+    assert e.value.status == _abi.AGN_ENOTFOUND

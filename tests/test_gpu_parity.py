@@ -248,6 +248,21 @@ def test_softmax_decode_shape_with_offset_and_stride(backend):
     assert np.array_equal(got[:, 512:], s[:, 512:])
 
 
+def test_attention_softmax_unnormalised_form(backend):
+    # the GPU twin's contract: weights = exp(s - max), sums[h] = sum of them, over entries 0..=pos
+    nh, max_seq, pos = 28, 2048, 1500
+    s = synth.activations(3, "scores", (nh, max_seq), std=2.0)
+    w, sums = backend.launch_attention_softmax(backend.upload(s), nh, max_seq, pos)
+    gw = backend.read(w, np.float32, (nh, max_seq)); gs = backend.read(sums, np.float32, (nh,))
+    v = s[:, :pos + 1].astype(np.float64)
+    e = np.exp(v - v.max(axis=1, keepdims=True))
+    assert np.max(np.abs(gw[:, :pos + 1] - e)) <= 2e-6 and not gw[:, pos + 1:].any()
+    assert np.allclose(gs, e.sum(axis=1), rtol=1e-5)
+    # dividing by the sums gives the normalised softmax of the CPU path
+    ref = orc.softmax_rows(s, np.full(nh, pos + 1, np.int32))
+    assert rel(gw / gs[:, None], ref) <= TOL
+
+
 # ------------------------------------------------------------------ get_rows
 
 @pytest.mark.parametrize("dtype,vocab,row_len,T", [
