@@ -44,6 +44,7 @@ struct agn_ctx {
     int tune_rms_vpt;           // 0 = automatic; 1/2/4/8 float4 per thread in rms_norm
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic
+    int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)
     int tune_get_rows_tma;      // stage the quantised row with one bulk asynchronous copy (TMA)
     int tune_silu_unroll;       // float4 pairs in flight per thread in silu_mul: 2, 4 (default) or 8
     int tune_silu_threads;      // 128, 256 (default) or 512

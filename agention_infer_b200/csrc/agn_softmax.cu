@@ -38,30 +38,76 @@ __device__ __forceinline__ int64_t valid_len(const SoftmaxArgs &a, int64_t r) {
 
 __device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
 
-// Load float4 number i of a row whose first nv entries are valid; the rest reads as -inf.
-__device__ __forceinline__ float4 load_masked(const float4 *row, int i, int nv) {
-    float4 v = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+// Float4 number i of a row whose first nv entries are valid.  The load is one predicated
+// instruction (so that a thread's loads are all issued back to back); mask_tail then sets
+// the invalid entries to -inf, and only the one float4 that straddles nv pays for it.
+__device__ __forceinline__ float4 load_valid(const float4 *row, int i, int nv) {
+    return 4 * i < nv ? agn_ld_stream(row + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+}
+__device__ __forceinline__ void mask_tail(float4 &v, int i, int nv) {
     const int e = 4 * i;
-    if (e < nv) {
-        v = agn_ld_stream(row + i);
+    if (e < nv && e + 3 >= nv) {
         if (e + 1 >= nv) v.y = -INFINITY;
         if (e + 2 >= nv) v.z = -INFINITY;
-        if (e + 3 >= nv) v.w = -INFINITY;
+        v.w = -INFINITY;
     }
-    return v;
 }
 
-__device__ __forceinline__ float4 exp4(float4 v, float m, int e, int nv) {
-    float4 o;
-    o.x = e < nv ? expf(v.x - m) : 0.0f;
-    o.y = e + 1 < nv ? expf(v.y - m) : 0.0f;
-    o.z = e + 2 < nv ? expf(v.z - m) : 0.0f;
-    o.w = e + 3 < nv ? expf(v.w - m) : 0.0f;
-    return o;
+// exp(v - m) as 2^((v - m) * log2 e) with the hardware ex2: three instructions per element
+// instead of the ~10 of expf, which made these kernels issue-bound (84 % issue-active at
+// 59 % of DRAM peak).  Arguments are <= 0, so the result is in [0, 1] and its absolute
+// error (~2^-22 + |v - m| * 2^-24 relative) stays far below 1e-5 of the row scale.  A masked
+// entry (-inf) gives exactly 0, so no per-element predicate is needed.
+__device__ __forceinline__ float exp_shifted(float v, float m) {
+    float r;
+    const float t = (v - m) * 1.4426950408889634f;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    return r;
+}
+__device__ __forceinline__ float4 exp4(float4 v, float m) {
+    return make_float4(exp_shifted(v.x, m), exp_shifted(v.y, m), exp_shifted(v.z, m), exp_shifted(v.w, m));
+}
+
+// Very short rows (router logits, <= 32 entries): one thread per row, everything in registers.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+softmax_thread_rows_kernel(const SoftmaxArgs a) {
+    agn_pdl_prologue();
+    const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= a.n_rows) return;
+    const int nv = (int)valid_len(a, r);
+    const int n4 = (int)(a.row_len >> 2);
+    const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
+    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) v[k] = k < n4 ? load_valid(in, k, nv) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) mask_tail(v[k], k, nv);
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    float sum = 0.0f;
+    if (nv > 0) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            v[k] = exp4(v[k], m);
+            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    }
+    if (a.sums) a.sums[r] = sum;
+    const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
+#pragma unroll
+    for (int k = 0; k < VPT; k++)
+        if (k < n4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (4 * k < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
+            agn_st_stream(out + k, o);
+        }
 }
 
 template <int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 softmax_warp_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
     const int lane = threadIdx.x & 31;
@@ -73,28 +119,30 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
     float4 v[VPL];
 #pragma unroll
-    for (int k = 0; k < VPL; k++) v[k] = load_masked(in, lane + 32 * k, nv);
+    for (int k = 0; k < VPL; k++) v[k] = load_valid(in, lane + 32 * k, nv);
+#pragma unroll
+    for (int k = 0; k < VPL; k++) mask_tail(v[k], lane + 32 * k, nv);
     float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < VPL; k++) m = fmaxf(m, max4(v[k]));
     m = agn_warp_max(m);
     float sum = 0.0f;
+    if (nv > 0) {  // (a row without valid entries has m = -inf: skip, everything below writes 0)
 #pragma unroll
-    for (int k = 0; k < VPL; k++) {
-        v[k] = exp4(v[k], m, 4 * (lane + 32 * k), nv);
-        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        for (int k = 0; k < VPL; k++) {
+            v[k] = exp4(v[k], m);
+            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
     }
     sum = agn_warp_sum(sum);
     if (a.sums && lane == 0) a.sums[r] = sum;
-    const float inv = a.sums ? 1.0f : 1.0f / sum;  // s / sum of the CPU path as s * (1/sum): <= 1 ulp apart
+    const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;  // s / sum of the CPU path as s * (1/sum): <= 1 ulp apart
 #pragma unroll
     for (int k = 0; k < VPL; k++) {
         const int i = lane + 32 * k;
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * i < nv) {
-                o.x = v[k].x * inv; o.y = v[k].y * inv; o.z = v[k].z * inv; o.w = v[k].w * inv;
-            }
+            if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
             agn_st_stream(out + i, o);
         }
     }
@@ -113,7 +161,9 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
     float4 v[VPT];
 #pragma unroll
-    for (int k = 0; k < VPT; k++) v[k] = load_masked(in, threadIdx.x + k * blockDim.x, nv);
+    for (int k = 0; k < VPT; k++) v[k] = load_valid(in, threadIdx.x + k * blockDim.x, nv);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) mask_tail(v[k], threadIdx.x + k * blockDim.x, nv);
     float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
@@ -124,10 +174,12 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[w]);
     __syncthreads();
     float sum = 0.0f;
+    if (nv > 0) {
 #pragma unroll
-    for (int k = 0; k < VPT; k++) {
-        v[k] = exp4(v[k], m, 4 * (threadIdx.x + k * blockDim.x), nv);
-        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        for (int k = 0; k < VPT; k++) {
+            v[k] = exp4(v[k], m);
+            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
     }
     sum = agn_warp_sum(sum);
     if (lane == 0) red[warp] = sum;
@@ -135,15 +187,13 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     sum = 0.0f;
     for (int w = 0; w < nwarps; w++) sum += red[w];
     if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
-    const float inv = a.sums ? 1.0f : 1.0f / sum;
+    const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * i < nv) {
-                o.x = v[k].x * inv; o.y = v[k].y * inv; o.z = v[k].z * inv; o.w = v[k].w * inv;
-            }
+            if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
             agn_st_stream(out + i, o);
         }
     }
@@ -178,7 +228,7 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     sum = 0.0f;
     for (int w = 0; w < nwarps; w++) sum += red[w];
     if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
-    const float inv = a.sums ? 1.0f : 1.0f / sum;
+    const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
     for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) out[i] = i < nv ? out[i] * inv : 0.0f;
 }
 
@@ -199,7 +249,13 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
     a.causal_period = causal_period; a.causal_offset = causal_offset;
     const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned16(out);
     const int64_t n4 = row_len / 4;
-    if (vec_ok && n4 <= 256) {
+    if (vec_ok && n4 <= 8) {
+        const unsigned grid = (unsigned)((n_rows + 255) / 256);
+        if (n4 <= 2) agn_launch(ctx, softmax_thread_rows_kernel<2>, dim3(grid), dim3(256), 0, a);
+        else if (n4 <= 4) agn_launch(ctx, softmax_thread_rows_kernel<4>, dim3(grid), dim3(256), 0, a);
+        else agn_launch(ctx, softmax_thread_rows_kernel<8>, dim3(grid), dim3(256), 0, a);
+        AGN_LAUNCHED(ctx, "softmax_thread_rows");
+    } else if (vec_ok && n4 <= 256) {
         const int warps = 8;
         const unsigned grid = (unsigned)((n_rows + warps - 1) / warps);
         if (n4 <= 32) agn_launch(ctx, softmax_warp_rows_kernel<1>, dim3(grid), dim3(32 * warps), 0, a);
@@ -208,10 +264,17 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
         else agn_launch(ctx, softmax_warp_rows_kernel<8>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
     } else if (vec_ok && n4 <= 8192) {
-        int vpt = 2;
-        while (vpt < 8 && (n4 + vpt - 1) / vpt > 512) vpt *= 2;
+        // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries
+        // (fewer warps in the two block-wide reductions, more loads in flight per thread)
+        int vpt = 8;
         int threads = (int)((n4 + vpt - 1) / vpt);
         threads = ((threads + 31) / 32) * 32;
+        if (ctx->tune_softmax_vpt == 2 || ctx->tune_softmax_vpt == 4) {
+            vpt = ctx->tune_softmax_vpt;
+            threads = (int)((n4 + vpt - 1) / vpt);
+            threads = ((threads + 31) / 32) * 32;
+            while (threads > 1024) { vpt *= 2; threads = (int)(((n4 + vpt - 1) / vpt + 31) / 32 * 32); }
+        }
         if (vpt == 2) agn_launch(ctx, softmax_block_rows_kernel<2>, dim3((unsigned)n_rows), dim3(threads), 0, a);
         else if (vpt == 4) agn_launch(ctx, softmax_block_rows_kernel<4>, dim3((unsigned)n_rows), dim3(threads), 0, a);
         else agn_launch(ctx, softmax_block_rows_kernel<8>, dim3((unsigned)n_rows), dim3(threads), 0, a);
