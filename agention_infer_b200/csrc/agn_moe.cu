@@ -136,7 +136,21 @@ gather_rows_kernel(const float *__restrict__ x, const int32_t *__restrict__ src_
     if (vec) {
         const float4 *s = reinterpret_cast<const float4 *>(x + t * H);
         float4 *d = reinterpret_cast<float4 *>(out + r * H);
-        for (int i = threadIdx.x; i < (int)(H >> 2); i += blockDim.x) agn_st_stream(d + i, __ldg(s + i));
+        const int n4 = (int)(H >> 2);
+        // four loads in flight per thread before the first store
+        for (int base = threadIdx.x; base < n4; base += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = base + k * blockDim.x;
+                v[k] = i < n4 ? __ldg(s + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = base + k * blockDim.x;
+                if (i < n4) agn_st_stream(d + i, v[k]);
+            }
+        }
     } else {
         for (int64_t i = threadIdx.x; i < H; i += blockDim.x) out[r * H + i] = x[t * H + i];
     }
