@@ -37,44 +37,60 @@ __device__ __forceinline__ int64_t kv_slot(const KvArgs &a, int64_t t) {
     return (p >= 0 && p < a.max_seq) ? p : -1;
 }
 
-// grid.x covers (token, block-of-32) pairs, 8 lanes each; blockIdx.y = 0 (K) or 1 (V)
+// One CTA per (token, K or V): blockIdx.x = token, blockIdx.y = 0 (K) or 1 (V).  Eight lanes own
+// one 32-value block (a float4 each), so a warp packs four blocks per pass.
 __global__ void __launch_bounds__(256)
 kv_write_q8_0_kernel(const KvArgs a) {
     agn_pdl_prologue();
+    const int64_t t = blockIdx.x;
     const int lane8 = threadIdx.x & 7;
-    const int64_t nblk = (a.hd + 31) >> 5;
-    const int64_t unit = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // (token, block)
-    const bool on = unit < a.T * nblk;
-    const int64_t t = on ? unit / nblk : 0;
-    const int64_t b = on ? unit - t * nblk : 0;
-    const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd + b * 32;
-    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
-    const int e0 = lane8 * 4;
-    const int64_t left = a.hd - b * 32;  // elements of this (possibly partial) block
-    float x[4] = {0.f, 0.f, 0.f, 0.f};
-    if (on) {
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-            if (e0 + i < left) x[i] = src[e0 + i];
-    }
-    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (!on) return;
+    const int nblk = (int)((a.hd + 31) >> 5);
+    const float *src_row = (blockIdx.y ? a.v : a.k) + t * a.hd;
     const int64_t slot = kv_slot(a, t);
-    if (slot < 0) {
-        if (lane8 == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+    if (slot < 0) {  // same answer for the whole CTA
+        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
         return;
     }
-    const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-    unsigned char *blk = cache + slot * a.bytes_per_token + b * 34;
-    if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+    unsigned char *tok = (blockIdx.y ? a.v_cache : a.k_cache) + slot * a.bytes_per_token;
+    const bool vec = (a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src_row) & 15) == 0);
+    // all lanes of a warp run the same number of passes (the shuffles below need them)
+    const int passes = (nblk + (int)(blockDim.x >> 3) - 1) / (int)(blockDim.x >> 3);
+    for (int p = 0; p < passes; p++) {
+        const int b = p * (int)(blockDim.x >> 3) + (int)(threadIdx.x >> 3);
+        const bool on = b < nblk;
+        const int e0 = lane8 * 4;
+        const int left = on ? (int)(a.hd - (int64_t)b * 32) : 0;  // elements of this (possibly partial) block
+        const float *src = src_row + (int64_t)b * 32;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (on && vec && e0 + 3 < left) {
+            const float4 q = __ldcs(reinterpret_cast<const float4 *>(src + e0));
+            x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
+        } else if (on) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        if (e0 + i < left) {
-            float q = roundf(__fdiv_rn(x[i], scale));
-            q = fminf(fmaxf(q, -127.0f), 127.0f);
-            blk[2 + e0 + i] = (unsigned char)(signed char)(int)q;
+            for (int i = 0; i < 4; i++)
+                if (e0 + i < left) x[i] = src[e0 + i];
+        }
+        float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (!on) continue;
+        const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        unsigned char *blk = tok + b * 34;
+        if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+        unsigned char q[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float r = roundf(__fdiv_rn(x[i], scale));
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            q[i] = (unsigned char)(signed char)(int)r;
+        }
+        if (e0 + 3 < left) {  // blocks are 2-byte aligned: two 16-bit stores
+            *reinterpret_cast<uint16_t *>(blk + 2 + e0) = (uint16_t)(q[0] | (q[1] << 8));
+            *reinterpret_cast<uint16_t *>(blk + 4 + e0) = (uint16_t)(q[2] | (q[3] << 8));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (e0 + i < left) blk[2 + e0 + i] = q[i];
         }
     }
 }
@@ -82,37 +98,63 @@ kv_write_q8_0_kernel(const KvArgs a) {
 __global__ void __launch_bounds__(256)
 kv_write_f16_kernel(const KvArgs a) {
     agn_pdl_prologue();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= a.T * a.hd) return;
-    const int64_t t = i / a.hd, d = i - t * a.hd;
+    const int64_t t = blockIdx.x;
     const int64_t slot = kv_slot(a, t);
     if (slot < 0) {
-        if (d == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
         return;
     }
-    const float *src = blockIdx.y ? a.v : a.k;
-    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
-    reinterpret_cast<uint16_t *>(cache + slot * a.bytes_per_token)[d] = __half_as_ushort(__float2half_rn(src[i]));
+    const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd;
+    __half *dst = reinterpret_cast<__half *>((blockIdx.y ? a.v_cache : a.k_cache) + slot * a.bytes_per_token);
+    if ((a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+        for (int i = threadIdx.x; i < (int)(a.hd >> 2); i += blockDim.x)
+            ActVec<__half>::store(dst, i, __ldcs(reinterpret_cast<const float4 *>(src) + i));
+    } else {
+        for (int i = threadIdx.x; i < (int)a.hd; i += blockDim.x) dst[i] = __float2half_rn(src[i]);
+    }
 }
 
-// read positions [0, n_pos): one thread per element
+// read positions [0, n_pos): one CTA per (position, K or V), four values per thread
 __global__ void __launch_bounds__(256)
 kv_read_kernel(const unsigned char *__restrict__ k_cache, const unsigned char *__restrict__ v_cache, int64_t n_pos, int64_t hd,
                int bytes_per_token, int q8, float *__restrict__ k_out, float *__restrict__ v_out) {
     agn_pdl_prologue();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_pos * hd) return;
-    const int64_t p = i / hd, d = i - p * hd;
+    const int64_t p = blockIdx.x;
     const unsigned char *tok = (blockIdx.y ? v_cache : k_cache) + p * bytes_per_token;
-    float val;
-    if (q8) {
-        const unsigned char *blk = tok + (d >> 5) * 34;
-        const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
-        val = __fmul_rn((float)(signed char)blk[2 + (d & 31)], scale);
+    float *dst = (blockIdx.y ? v_out : k_out) + p * hd;
+    const bool vec = (hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) &&
+                     (q8 || (reinterpret_cast<uintptr_t>(tok) & 7) == 0);
+    if (vec) {
+        for (int i = threadIdx.x; i < (int)(hd >> 2); i += blockDim.x) {
+            float4 o;
+            if (q8) {
+                const int d = 4 * i;
+                const unsigned char *blk = tok + (d >> 5) * 34;
+                const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
+                const uint32_t lo = *reinterpret_cast<const uint16_t *>(blk + 2 + (d & 31));
+                const uint32_t hi = *reinterpret_cast<const uint16_t *>(blk + 4 + (d & 31));
+                o.x = __fmul_rn((float)(signed char)(lo & 0xff), scale);
+                o.y = __fmul_rn((float)(signed char)(lo >> 8), scale);
+                o.z = __fmul_rn((float)(signed char)(hi & 0xff), scale);
+                o.w = __fmul_rn((float)(signed char)(hi >> 8), scale);
+            } else {
+                o = ActVec<__half>::load(reinterpret_cast<const __half *>(tok), i);
+            }
+            __stcs(reinterpret_cast<float4 *>(dst) + i, o);
+        }
     } else {
-        val = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t *>(tok)[d]));
+        for (int d = threadIdx.x; d < (int)hd; d += blockDim.x) {
+            float val;
+            if (q8) {
+                const unsigned char *blk = tok + (d >> 5) * 34;
+                const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
+                val = __fmul_rn((float)(signed char)blk[2 + (d & 31)], scale);
+            } else {
+                val = __half2float(reinterpret_cast<const __half *>(tok)[d]);
+            }
+            dst[d] = val;
+        }
     }
-    (blockIdx.y ? v_out : k_out)[i] = val;
 }
 
 int kv_bytes_per_token(int32_t dtype, int64_t hd) {
@@ -147,14 +189,16 @@ extern "C" int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float 
     a.pos = pos; a.T = T; a.hd = head_dim_kv; a.max_seq = max_seq_len; a.pos_start = pos_start; a.bytes_per_token = bpt;
     a.flags = ctx->d_flags;
     if (kv_dtype == AGN_Q8_0) {
-        const int64_t units = T * ((head_dim_kv + 31) / 32);
-        const int64_t blocks = (units * 8 + 255) / 256;
-        if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
-        agn_launch(ctx, kv_write_q8_0_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, a);
+        if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
+        int threads = (int)(((head_dim_kv + 31) / 32) * 8);  // eight lanes per 32-value block
+        threads = ((threads + 31) / 32) * 32;
+        if (threads > 256) threads = 256;
+        agn_launch(ctx, kv_write_q8_0_kernel, dim3((unsigned)T, 2), dim3(threads), 0, a);
     } else {
-        const int64_t blocks = (T * head_dim_kv + 255) / 256;
-        if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
-        agn_launch(ctx, kv_write_f16_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, a);
+        if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
+        int threads = (int)(((head_dim_kv + 3) / 4 + 31) / 32 * 32);
+        if (threads > 256) threads = 256;
+        agn_launch(ctx, kv_write_f16_kernel, dim3((unsigned)T, 2), dim3(threads), 0, a);
     }
     ctx->flags_dirty = true;
     AGN_LAUNCHED(ctx, "kv_write");
@@ -171,9 +215,10 @@ extern "C" int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k
     if (n_pos == 0) return AGN_OK;
     if (!k_cache || !v_cache || !k_out || !v_out) return agn_fail(ctx, AGN_EINVAL, "kv_read: null pointer");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const int64_t blocks = (n_pos * head_dim_kv + 255) / 256;
-    if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_read: too many positions");
-    agn_launch(ctx, kv_read_kernel, dim3((unsigned)blocks, 2), dim3(256), 0, static_cast<const unsigned char *>(k_cache),
+    if (n_pos > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_read: too many positions");
+    int threads = (int)(((head_dim_kv + 3) / 4 + 31) / 32 * 32);
+    if (threads > 256) threads = 256;
+    agn_launch(ctx, kv_read_kernel, dim3((unsigned)n_pos, 2), dim3(threads), 0, static_cast<const unsigned char *>(k_cache),
                static_cast<const unsigned char *>(v_cache), n_pos, head_dim_kv, kv_bytes_per_token(kv_dtype, head_dim_kv),
                kv_dtype == AGN_Q8_0 ? 1 : 0, k_out, v_out);
     AGN_LAUNCHED(ctx, "kv_read");

@@ -454,6 +454,45 @@ def run_ours(args, cfg, ops_list, wl):
         per_op[name]["copy_same_bytes_us"] = round(cus, 2)
         per_op[name]["frac_of_copy_same_bytes"] = round(cus / us, 3)
         del srcs, dsts
+    # ---- ops of the path that are not part of this configuration's step, each alone (f32 only):
+    #      fused residual-add + norm, KV-cache packing, and a causal softmax at prefill size
+    extra_ops = {}
+    if not f16 and not args.no_extras and step_bytes < 4e9:
+        from agention_infer_b200 import AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
+        hd_kv = nkv * hd
+        Ls = min(T, 2048)
+        ex_sets = []
+        for s_ in range(nsets):
+            ex_sets.append({"x": rn(T, H), "d": rn(T, H), "nx": torch.empty(T, H, device=dev), "nm": torch.empty(T, H, device=dev),
+                            "k": rn(T, hd_kv), "v": rn(T, hd_kv),
+                            "kc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
+                            "vc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
+                            "kh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
+                            "vh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
+                            "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev)})
+        extras = {
+            "add_residual_rms_norm": (lambda b: be.launch_add_residual_rms_norm(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], normed=b["nm"]),
+                                      16 * T * H + 4 * H),
+            "kv_write_q8_0": (lambda b: be.kv_write(KV_Q8_0, b["k"], b["v"], b["kc"], b["vc"], T, hd_kv, None, T),
+                              2 * T * (4 * hd_kv + be.kv_bytes_per_token(KV_Q8_0, hd_kv))),
+            "kv_write_f16": (lambda b: be.kv_write(KV_F16, b["k"], b["v"], b["kh"], b["vh"], T, hd_kv, None, T),
+                             2 * T * (4 * hd_kv + 2 * hd_kv)),
+            f"softmax_causal_{nq}x{Ls}x{Ls}": (lambda b: be.launch_softmax_rows(b["sc"], nq * Ls, Ls, out=b["pr"], causal_period=Ls),
+                                               4 * (nq * Ls * (Ls + 1) // 2 + nq * Ls * Ls)),
+        }
+        for name, (fn, nbytes) in extras.items():
+            for i in range(4):
+                fn(ex_sets[i % nsets])
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for i in range(reps):
+                fn(ex_sets[i % nsets])
+            b.record(stream)
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / reps
+            extra_ops[name] = {"us": round(us, 2), "gbs": round(nbytes / (us * 1e-6) / 1e9, 1), "bytes": nbytes}
+        del ex_sets
     if sampler:
         sampler.mark_load(False)
     clocks = sampler.stop() if sampler else None
@@ -548,7 +587,7 @@ def run_ours(args, cfg, ops_list, wl):
                          "peak_source": "of measured (copy bandwidth, MEASURED_PEAKS.json)" if peak_src == "measured"
                          else "of fallback", "traffic": silu_traffic_bytes(R * I) if not f16 else None,
                          "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
-            "ops": per_op, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+            "ops": per_op, "extra_ops": extra_ops, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk), "outputs_checked": outs, "identical_across_ranks": agree,
                              "how": "checksums of every op's output for identical inputs, gathered over the process group"},
         }
@@ -666,6 +705,7 @@ def main():
                     help="activation storage: f32 (the benchmark's contract) or f16 (the reference GPU path's default)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the ops measured outside the step")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (for comparison)")
     ap.add_argument("--warm-seconds", type=float, default=0.6,
                     help="minimum duration of the warm-up (0 for profiling runs)")
