@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libagention_b200.so"
 AGN_OK, AGN_EINVAL, AGN_EUNSUPPORTED_DTYPE, AGN_ECUDA, AGN_EOOB_ID, AGN_ENOMEM, AGN_ETIMEOUT = range(7)
 AGN_EFORMAT, AGN_ENOTFOUND, AGN_EIO = 7, 8, 9
 AGN_F32, AGN_F16, AGN_Q8_0, AGN_Q4_K, AGN_Q6_K, AGN_BF16 = 0, 1, 8, 12, 14, 30
-AGN_Q5_0, AGN_Q5_K = 6, 13
+AGN_Q5_0, AGN_Q5_K, AGN_Q2_K = 6, 13, 10
 AGN_ROPE_NEOX, AGN_ROPE_NORMAL = 0, 1
 
 _vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_size_t
@@ -74,6 +74,9 @@ SIGNATURES = {
     "agn_router_top2_f32": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
     "agn_silu_mul_f16": (_i32, [_vp, _vp, _vp, _vp, _i64]),
+    "agn_softmax_rows_scaled_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32, _f32]),
+    "agn_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
+    "agn_add_residual_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
     "agn_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_add_residual_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_rope_qk_f16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),

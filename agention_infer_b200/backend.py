@@ -255,6 +255,19 @@ class CudaBackend:
                                                    _ptr(n_valid), causal_period, causal_offset))
         return out
 
+    def launch_softmax_rows_scaled(self, scores, n_rows: int, row_len: int, scale: float, out=None, sums=None,
+                                   row_stride: Optional[int] = None, n_valid=None, causal_period: int = 0,
+                                   causal_offset: int = 0):
+        """Softmax of scale * scores (`attention_scores` writes dot * scale, kernels_wgpu.rs:773-782, then the
+        softmax runs); sums given: unnormalised weights + row sums."""
+        if row_stride is None:
+            row_stride = row_len
+        if out is None:
+            out = self.empty(4 * n_rows * row_stride)
+        self._check(self._lib.agn_softmax_rows_scaled_f32(self._ctx, _ptr(scores), _ptr(out), _ptr(sums), n_rows, row_len,
+                                                          row_stride, _ptr(n_valid), causal_period, causal_offset, scale))
+        return out
+
     def launch_attention_softmax(self, scores, n_heads: int, max_seq: int, pos: int, weights=None, sums=None):
         """The softmax step of `launch_attention(.., pos, n_heads, max_seq)` (resident.rs:551-565) as the reference's
         kernel leaves it: unnormalised weights [n_heads, max_seq] and sums [n_heads] over entries 0..=pos."""
@@ -337,6 +350,24 @@ class CudaBackend:
             out = self.empty(2 * T * H)
         self._check(self._lib.agn_rms_norm_f16(self._ctx, _ptr(x), _ptr(w), _ptr(out), T, H, eps))
         return out
+
+    def launch_rms_norm_out16(self, x, w, T: int, H: int, eps: float, out_dtype: int, out=None):
+        """f32 rows in, normed rows out as f16 / bf16 (the operand of a half-precision matmul)."""
+        if out is None:
+            out = self.empty(2 * T * H)
+        self._check(self._lib.agn_rms_norm_f32_out16(self._ctx, _ptr(x), _ptr(w), _ptr(out), T, H, eps, out_dtype))
+        return out
+
+    def launch_add_residual_rms_norm_out16(self, x, delta, w, T: int, H: int, eps: float, out_dtype: int, new_x=None,
+                                           normed=None):
+        """new_x = x + delta stays f32; normed is stored as f16 / bf16."""
+        if new_x is None:
+            new_x = self.empty(4 * T * H)
+        if normed is None:
+            normed = self.empty(2 * T * H)
+        self._check(self._lib.agn_add_residual_rms_norm_f32_out16(self._ctx, _ptr(x), _ptr(delta), _ptr(w), _ptr(new_x),
+                                                                  _ptr(normed), T, H, eps, out_dtype))
+        return new_x, normed
 
     def launch_add_residual_rms_norm_f16(self, x, delta, w, T: int, H: int, eps: float, new_x=None, normed=None):
         if new_x is None:

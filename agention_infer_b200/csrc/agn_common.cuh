@@ -170,6 +170,26 @@ template <> struct ActVec<__half> {
     static __device__ __forceinline__ void store1(__half *p, int64_t i, float v) { p[i] = __float2half_rn(v); }
 };
 
+#include <cuda_bf16.h>
+// bf16 is an OUTPUT format only (a normed row handed to a matmul that takes bf16 operands).
+template <> struct ActVec<__nv_bfloat16> {
+    static constexpr int ALIGN = 8;
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16 *p, int64_t vec) {
+        const uint2 r = __ldcs(reinterpret_cast<const uint2 *>(p) + vec);
+        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                           __uint_as_float(r.y & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, int64_t vec, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<const uint32_t *>(&a);
+        r.y = *reinterpret_cast<const uint32_t *>(&b);
+        __stcs(reinterpret_cast<uint2 *>(p) + vec, r);
+    }
+    static __device__ __forceinline__ float load1(const __nv_bfloat16 *p, int64_t i) { return __bfloat162float(p[i]); }
+    static __device__ __forceinline__ void store1(__nv_bfloat16 *p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+};
+
 // Streaming (read-once / write-once) 128-bit accesses: keep them from displacing
 // reusable lines (weights, tables) in L1/L2.
 __device__ __forceinline__ float4 agn_ld_stream(const float4 *p) { return __ldcs(p); }

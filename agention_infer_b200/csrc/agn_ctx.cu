@@ -300,6 +300,7 @@ size_t agn_type_size(int32_t dtype, size_t n) {
     case AGN_Q8_0: bs = 32; bb = 34; break;
     case AGN_Q5_0: bs = 32; bb = 22; break;
     case AGN_Q5_K: bs = 256; bb = 176; break;
+    case AGN_Q2_K: bs = 256; bb = 84; break;  // the codec's block, src/quant/q2_k.rs:24 (types.rs:137 lists 256)
     case AGN_Q4_K: bs = 256; bb = 144; break;
     case AGN_Q6_K: bs = 256; bb = 210; break;
     default: return 0;

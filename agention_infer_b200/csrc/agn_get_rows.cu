@@ -1,4 +1,4 @@
-// Embedding get_rows with inline dequantisation (Q8_0 / Q4_K / Q6_K / Q5_K / Q5_0 / F16 / BF16 / F32).
+// Embedding get_rows with inline dequantisation (Q8_0 / Q4_K / Q6_K / Q5_K / Q5_0 / Q2_K / F16 / BF16 / F32).
 //
 // Reference: `quant::dequant_row` + `row_view` (src/quant/mod.rs:30-47, :97-135) and the
 // codecs `dequant_q8_0` (src/quant/q8_0.rs:14-51), `get_scale_min_k4` + `dequant_q4_k`
@@ -159,6 +159,33 @@ __device__ __forceinline__ void decode8<AGN_Q5_K>(const uint8_t *row, int u, int
 }
 
 template <>
+__device__ __forceinline__ void decode8<AGN_Q2_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
+    // src/quant/q2_k.rs:47-93: scales[16] | qs[64] | f16 d | f16 dmin; value e of the super-block is
+    // ((qs[32*(e/128) + e%32] >> 2*((e%128)/32)) & 3) * d*(scales[e/16] & 0xF) - dmin*(scales[e/16] >> 4).
+    // One unit = four quant bytes at two adjacent shifts (outputs 32 apart).
+    const uint8_t *blk = row + (u >> 5) * 84;
+    const int r = u & 31, g = r >> 4, jp = (r >> 3) & 1, l = (r & 7) * 4;
+    const int e = 128 * g + 64 * jp + l;
+    ea = (u >> 5) * 256 + e;
+    eb = ea + 32;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk + 80);
+    const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
+    const uint32_t sa = blk[e >> 4], sb = blk[(e >> 4) + 2];
+    const float d1 = __fmul_rn(d, (float)(sa & 0xF)), mm1 = __fmul_rn(dmin, (float)(sa >> 4));
+    const float d2 = __fmul_rn(d, (float)(sb & 0xF)), mm2 = __fmul_rn(dmin, (float)(sb >> 4));
+    const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l) >> (4 * jp);
+    va.x = __fsub_rn(__fmul_rn(d1, (float)(q & 3)), mm1);
+    va.y = __fsub_rn(__fmul_rn(d1, (float)((q >> 8) & 3)), mm1);
+    va.z = __fsub_rn(__fmul_rn(d1, (float)((q >> 16) & 3)), mm1);
+    va.w = __fsub_rn(__fmul_rn(d1, (float)((q >> 24) & 3)), mm1);
+    vb.x = __fsub_rn(__fmul_rn(d2, (float)((q >> 2) & 3)), mm2);
+    vb.y = __fsub_rn(__fmul_rn(d2, (float)((q >> 10) & 3)), mm2);
+    vb.z = __fsub_rn(__fmul_rn(d2, (float)((q >> 18) & 3)), mm2);
+    vb.w = __fsub_rn(__fmul_rn(d2, (float)((q >> 26) & 3)), mm2);
+}
+
+template <>
 __device__ __forceinline__ void decode8<AGN_Q6_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
     const uint8_t *blk = row + (u >> 5) * 210;
     const int r = u & 31, h = r >> 4, cp = (r >> 3) & 1, l = (r & 7) * 4;
@@ -271,7 +298,7 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     // a partial last block is fully present in the table (type_size rounds up to whole blocks),
     // so decoding past row_len inside it stays in bounds; only the stores are clipped
     // K-quant units are numbered per 256-value super-block (32 units each, not in element order)
-    constexpr bool K_QUANT = DTYPE == AGN_Q4_K || DTYPE == AGN_Q5_K || DTYPE == AGN_Q6_K;
+    constexpr bool K_QUANT = DTYPE == AGN_Q4_K || DTYPE == AGN_Q5_K || DTYPE == AGN_Q6_K || DTYPE == AGN_Q2_K;
     const int n8 = K_QUANT ? ((row_len + 255) >> 8) * 32 : (row_len + 7) >> 3;
     for (int u = threadIdx.x; u < n8; u += blockDim.x) {
         int ea, eb;
@@ -318,11 +345,13 @@ template <typename OUT>
 int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t table_bytes, int64_t n_rows, int64_t row_len,
                           const uint32_t *ids, int64_t T, OUT *out) {
     const size_t row_bytes = agn_type_size(dtype, (size_t)(row_len > 0 ? row_len : 0));
-    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_Q5_K && dtype != AGN_Q5_0 && dtype != AGN_F16 &&
+    if (dtype != AGN_Q8_0 && dtype != AGN_Q4_K && dtype != AGN_Q6_K && dtype != AGN_Q5_K && dtype != AGN_Q5_0 && dtype != AGN_Q2_K && dtype != AGN_F16 &&
         dtype != AGN_BF16 && dtype != AGN_F32)
         return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "get_rows: dequantization not implemented for ggml type %d", dtype);
     if (T < 0 || n_rows < 0 || row_len <= 0)
         return agn_fail(ctx, AGN_EINVAL, "get_rows: T=%lld n_rows=%lld row_len=%lld", (long long)T, (long long)n_rows, (long long)row_len);
+    if (dtype == AGN_Q2_K && row_len % 256 != 0)  // src/quant/q2_k.rs:31-35
+        return agn_fail(ctx, AGN_EINVAL, "get_rows: Q2_K row length %lld is not a multiple of 256", (long long)row_len);
     if (T == 0) return AGN_OK;
     if (!table || !ids || !out) return agn_fail(ctx, AGN_EINVAL, "get_rows: null pointer");
     if (!agn_aligned16(table)) return agn_fail(ctx, AGN_EINVAL, "get_rows: table must be 16-byte aligned");
@@ -350,6 +379,7 @@ int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t
     case AGN_Q4_K: e = launch_get_rows<AGN_Q4_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q6_K: e = launch_get_rows<AGN_Q6_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q5_K: e = launch_get_rows<AGN_Q5_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q2_K: e = launch_get_rows<AGN_Q2_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q5_0: e = launch_get_rows<AGN_Q5_0, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_F16: e = launch_get_rows<AGN_F16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_BF16: e = launch_get_rows<AGN_BF16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;

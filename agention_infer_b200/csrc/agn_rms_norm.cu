@@ -27,10 +27,12 @@ __device__ __forceinline__ float block_sum(float v, float *smem) {
     return total;
 }
 
-template <typename T, int VPT, bool RESIDUAL, bool RECIP>
+// T: storage type of x, delta and new_x; OT: storage type of the normed output (T, or a 16-bit
+// type for a row that feeds a matmul with half-precision operands).
+template <typename T, typename OT, int VPT, bool RESIDUAL, bool RECIP>
 __global__ void __launch_bounds__(1024)
 rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float4 *__restrict__ w,
-                     T *__restrict__ new_x, T *__restrict__ out, int n4, float n_f, float eps) {
+                     T *__restrict__ new_x, OT *__restrict__ out, int n4, float n_f, float eps) {
     agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * n4;  // in vectors of four activations
@@ -81,17 +83,17 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
                 o.z = ww.z * v[k].z / rms;
                 o.w = ww.w * v[k].w / rms;
             }
-            ActVec<T>::store(out, row + i, o);
+            ActVec<OT>::store(out, row + i, o);
         }
     }
 }
 
 // Any H, any alignment, rows too long for registers: two passes over the row, the second
 // one served by L2 for rows that fit there.
-template <typename T, bool RESIDUAL>
+template <typename T, typename OT, bool RESIDUAL>
 __global__ void __launch_bounds__(1024)
 rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float *__restrict__ w,
-                             T *__restrict__ new_x, T *__restrict__ out, int64_t H, float eps) {
+                             T *__restrict__ new_x, OT *__restrict__ out, int64_t H, float eps) {
     agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * H;
@@ -109,23 +111,23 @@ rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delt
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     const T *src = RESIDUAL ? new_x : x;
     for (int64_t i = threadIdx.x; i < H; i += blockDim.x)
-        ActVec<T>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
+        ActVec<OT>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
 }
 
-template <typename T, int VPT, bool RESIDUAL>
-void launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, T *out, int64_t T_rows, int n4,
+template <typename T, typename OT, int VPT, bool RESIDUAL>
+void launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, OT *out, int64_t T_rows, int n4,
                 float eps, int threads) {
     const float4 *w4 = reinterpret_cast<const float4 *>(w);
     if (ctx->tune_rms_recip)
-        agn_launch(ctx, rms_norm_rows_kernel<T, VPT, RESIDUAL, true>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
+        agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, true>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
                    new_x, out, n4, (float)(n4 * 4), eps);
     else
-        agn_launch(ctx, rms_norm_rows_kernel<T, VPT, RESIDUAL, false>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
+        agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, false>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
                    new_x, out, n4, (float)(n4 * 4), eps);
 }
 
-template <typename T, bool RESIDUAL>
-int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, T *out, int64_t T_rows,
+template <typename T, typename OT, bool RESIDUAL>
+int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, OT *out, int64_t T_rows,
                           int64_t H, float eps, const char *name) {
     if (T_rows < 0 || H <= 0) return agn_fail(ctx, AGN_EINVAL, "%s: T=%lld H=%lld", name, (long long)T_rows, (long long)H);
     if (T_rows == 0) return AGN_OK;
@@ -133,7 +135,7 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float 
     if (T_rows > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "%s: T too large", name);
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     constexpr int A = ActVec<T>::ALIGN;
-    const bool vec_ok = (H % 4 == 0) && agn_aligned(x, A) && agn_aligned16(w) && agn_aligned(out, A) &&
+    const bool vec_ok = (H % 4 == 0) && agn_aligned(x, A) && agn_aligned16(w) && agn_aligned(out, ActVec<OT>::ALIGN) &&
                         (!RESIDUAL || (agn_aligned(delta, A) && agn_aligned(new_x, A))) && H <= 32768;
     if (vec_ok) {
         const int n4 = (int)(H / 4);
@@ -149,16 +151,16 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float 
         threads = ((threads + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         switch (vpt) {
-        case 1: launch_vec<T, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        case 2: launch_vec<T, 2, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        case 4: launch_vec<T, 4, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        default: launch_vec<T, 8, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 1: launch_vec<T, OT, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 2: launch_vec<T, OT, 2, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 4: launch_vec<T, OT, 4, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        default: launch_vec<T, OT, 8, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
         }
         AGN_LAUNCHED(ctx, name);
     } else {
         int threads = H >= 1024 ? 256 : (int)(((H + 31) / 32) * 32);
         if (threads > 256) threads = 256;
-        agn_launch(ctx, rms_norm_rows_generic_kernel<T, RESIDUAL>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w, new_x,
+        agn_launch(ctx, rms_norm_rows_generic_kernel<T, OT, RESIDUAL>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w, new_x,
                    out, H, eps);
         AGN_LAUNCHED(ctx, name);
     }
@@ -170,28 +172,58 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float 
 extern "C" int32_t agn_rms_norm_f32(agn_ctx *ctx, const float *x, const float *w, float *out,
                                     int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<float, false>(ctx, x, nullptr, w, nullptr, out, T, H, eps, "rms_norm");
+    return rms_norm_dispatch<float, float, false>(ctx, x, nullptr, w, nullptr, out, T, H, eps, "rms_norm");
 }
 
 extern "C" int32_t agn_add_residual_rms_norm_f32(agn_ctx *ctx, const float *x, const float *delta,
                                                  const float *w, float *new_x, float *normed,
                                                  int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<float, true>(ctx, x, delta, w, new_x, normed, T, H, eps, "add_residual_rms_norm");
+    return rms_norm_dispatch<float, float, true>(ctx, x, delta, w, new_x, normed, T, H, eps, "add_residual_rms_norm");
 }
 
 // f16 activation storage (the reference's `Act = f16`, src/ops/kernels_wgpu.rs:79-163): x, delta,
 // new_x and the output are f16, the weight is f32, the arithmetic is f32.
 extern "C" int32_t agn_rms_norm_f16(agn_ctx *ctx, const void *x, const float *w, void *out, int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<__half, false>(ctx, static_cast<const __half *>(x), nullptr, w, nullptr, static_cast<__half *>(out),
+    return rms_norm_dispatch<__half, __half, false>(ctx, static_cast<const __half *>(x), nullptr, w, nullptr, static_cast<__half *>(out),
                                             T, H, eps, "rms_norm_f16");
 }
 
 extern "C" int32_t agn_add_residual_rms_norm_f16(agn_ctx *ctx, const void *x, const void *delta, const float *w, void *new_x,
                                                  void *normed, int64_t T, int64_t H, float eps) {
     AGN_CHECK_CTX(ctx);
-    return rms_norm_dispatch<__half, true>(ctx, static_cast<const __half *>(x), static_cast<const __half *>(delta), w,
+    return rms_norm_dispatch<__half, __half, true>(ctx, static_cast<const __half *>(x), static_cast<const __half *>(delta), w,
                                            static_cast<__half *>(new_x), static_cast<__half *>(normed), T, H, eps,
                                            "add_residual_rms_norm_f16");
+}
+
+// f32 rows in, normed row stored as f16 or bf16 (round to nearest even of the f32 result): the
+// input a matmul with half-precision operands wants, written once instead of an f32 row plus a
+// cast pass.  out_dtype is AGN_F16 or AGN_BF16.  No counterpart in the reference, whose norm
+// kernels store `Act` in and out (src/ops/kernels_wgpu.rs:79-163); the residual stream (new_x)
+// stays f32.
+extern "C" int32_t agn_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *w, void *out, int64_t T, int64_t H,
+                                          float eps, int32_t out_dtype) {
+    AGN_CHECK_CTX(ctx);
+    if (out_dtype == AGN_F16)
+        return rms_norm_dispatch<float, __half, false>(ctx, x, nullptr, w, nullptr, static_cast<__half *>(out), T, H, eps,
+                                                       "rms_norm_out_f16");
+    if (out_dtype == AGN_BF16)
+        return rms_norm_dispatch<float, __nv_bfloat16, false>(ctx, x, nullptr, w, nullptr, static_cast<__nv_bfloat16 *>(out), T, H,
+                                                              eps, "rms_norm_out_bf16");
+    return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "rms_norm_f32_out16: output type %d is neither f16 nor bf16", out_dtype);
+}
+
+extern "C" int32_t agn_add_residual_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *delta, const float *w,
+                                                       float *new_x, void *normed, int64_t T, int64_t H, float eps,
+                                                       int32_t out_dtype) {
+    AGN_CHECK_CTX(ctx);
+    if (out_dtype == AGN_F16)
+        return rms_norm_dispatch<float, __half, true>(ctx, x, delta, w, new_x, static_cast<__half *>(normed), T, H, eps,
+                                                      "add_residual_rms_norm_out_f16");
+    if (out_dtype == AGN_BF16)
+        return rms_norm_dispatch<float, __nv_bfloat16, true>(ctx, x, delta, w, new_x, static_cast<__nv_bfloat16 *>(normed), T, H,
+                                                             eps, "add_residual_rms_norm_out_bf16");
+    return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "add_residual_rms_norm_f32_out16: output type %d is neither f16 nor bf16", out_dtype);
 }

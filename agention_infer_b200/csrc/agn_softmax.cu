@@ -24,6 +24,8 @@ struct SoftmaxArgs {
     float *sums;  // non-null: store the unnormalised exp(s - max) and the row sums (the reference's GPU form)
     int64_t n_rows, row_len, row_stride;
     int causal_period, causal_offset;
+    float scale;     // scores are multiplied by this (> 0) before the softmax; 1 for the plain form
+    float exp_coef;  // scale * log2(e): exp(scale * (s - max)) = 2^((s - max) * exp_coef)
 };
 
 __device__ __forceinline__ int64_t valid_len(const SoftmaxArgs &a, int64_t r) {
@@ -58,14 +60,15 @@ __device__ __forceinline__ void mask_tail(float4 &v, int i, int nv) {
 // 59 % of DRAM peak).  Arguments are <= 0, so the result is in [0, 1] and its absolute
 // error (~2^-22 + |v - m| * 2^-24 relative) stays far below 1e-5 of the row scale.  A masked
 // entry (-inf) gives exactly 0, so no per-element predicate is needed.
-__device__ __forceinline__ float exp_shifted(float v, float m) {
+// A positive score scale folds into the coefficient: max(scale * s) = scale * max(s).
+__device__ __forceinline__ float exp_shifted(float v, float m, float coef) {
     float r;
-    const float t = (v - m) * 1.4426950408889634f;
+    const float t = (v - m) * coef;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
     return r;
 }
-__device__ __forceinline__ float4 exp4(float4 v, float m) {
-    return make_float4(exp_shifted(v.x, m), exp_shifted(v.y, m), exp_shifted(v.z, m), exp_shifted(v.w, m));
+__device__ __forceinline__ float4 exp4(float4 v, float m, float coef) {
+    return make_float4(exp_shifted(v.x, m, coef), exp_shifted(v.y, m, coef), exp_shifted(v.z, m, coef), exp_shifted(v.w, m, coef));
 }
 
 // Very short rows (router logits, <= 32 entries): one thread per row, everything in registers.
@@ -91,7 +94,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
     if (nv > 0) {
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
-            v[k] = exp4(v[k], m);
+            v[k] = exp4(v[k], m, a.exp_coef);
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
     }
@@ -130,7 +133,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     if (nv > 0) {  // (a row without valid entries has m = -inf: skip, everything below writes 0)
 #pragma unroll
         for (int k = 0; k < VPL; k++) {
-            v[k] = exp4(v[k], m);
+            v[k] = exp4(v[k], m, a.exp_coef);
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
     }
@@ -177,7 +180,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     if (nv > 0) {
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
-            v[k] = exp4(v[k], m);
+            v[k] = exp4(v[k], m, a.exp_coef);
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
     }
@@ -218,7 +221,7 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     __syncthreads();
     float sum = 0.0f;
     for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
-        const float e = expf(in[i] - m);
+        const float e = expf((in[i] - m) * a.scale);
         out[i] = e;  // in may alias out: element i is only ever touched by this thread
         sum += e;
     }
@@ -236,7 +239,10 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
 
 namespace {
 int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums, int64_t n_rows, int64_t row_len,
-                         int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset) {
+                         int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset,
+                         float scale = 1.0f) {
+    if (!(scale > 0.0f) || !(scale < INFINITY))
+        return agn_fail(ctx, AGN_EINVAL, "softmax_rows: scale %g is not a positive finite number", (double)scale);
     if (n_rows < 0 || row_len < 0 || row_stride < row_len || causal_period < 0 || causal_offset < 0)
         return agn_fail(ctx, AGN_EINVAL, "softmax_rows: n_rows=%lld row_len=%lld row_stride=%lld period=%d offset=%d",
                         (long long)n_rows, (long long)row_len, (long long)row_stride, causal_period, causal_offset);
@@ -247,6 +253,8 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
     SoftmaxArgs a;
     a.in = in; a.out = out; a.sums = sums; a.n_valid = n_valid; a.n_rows = n_rows; a.row_len = row_len; a.row_stride = row_stride;
     a.causal_period = causal_period; a.causal_offset = causal_offset;
+    a.scale = scale;
+    a.exp_coef = scale == 1.0f ? 1.4426950408889634f : (float)((double)scale * 1.4426950408889634);
     const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned16(out);
     const int64_t n4 = row_len / 4;
     if (vec_ok && n4 <= 8) {
@@ -304,4 +312,18 @@ extern "C" int32_t agn_softmax_rows_unnorm_f32(agn_ctx *ctx, const float *in, fl
     AGN_CHECK_CTX(ctx);
     if (n_rows > 0 && !sums) return agn_fail(ctx, AGN_EINVAL, "softmax_rows_unnorm: null sums");
     return softmax_dispatch(ctx, in, weights, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
+}
+
+// Softmax of scale * scores: the reference's GPU attention writes `dot * scale` with
+// scale = 1 / sqrt(head_dim) in a kernel of its own (`attention_scores`,
+// src/ops/kernels_wgpu.rs:773-782; the CPU path divides by sqrt(head_dim),
+// src/model/llama/cpu_path.rs:172) and then runs the softmax over that buffer.  Taking the
+// scale here lets the caller hand over raw dot products and saves that pass.  scale must be
+// positive and finite.  sums == NULL: normalised probabilities; else exp(scale * (s - max))
+// and the row sums, as agn_softmax_rows_unnorm_f32.
+extern "C" int32_t agn_softmax_rows_scaled_f32(agn_ctx *ctx, const float *in, float *out, float *sums, int64_t n_rows,
+                                               int64_t row_len, int64_t row_stride, const int32_t *n_valid,
+                                               int32_t causal_period, int32_t causal_offset, float scale) {
+    AGN_CHECK_CTX(ctx);
+    return softmax_dispatch(ctx, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset, scale);
 }

@@ -12,7 +12,7 @@ from typing import Optional
 
 import numpy as np
 
-from ._abi import AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0
+from ._abi import AGN_Q2_K, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0
 
 BASE_SEED = 20261125
 STREAMS = {name: i for i, name in enumerate(
@@ -113,6 +113,11 @@ def quant_table(dtype: int, n_rows: int, row_len: int, cfg_index: int = 0, salt:
         nb = n_rows * ((row_len + 31) // 32)
         t = r.integers(0, 256, size=(nb, 22), dtype=np.uint8)
         t[:, 0:2] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
+    elif dtype == AGN_Q2_K:  # 16 scale/min nibble bytes, 64 bytes of 2-bit values, f16 d, f16 dmin
+        nb = n_rows * ((row_len + 255) // 256)
+        t = r.integers(0, 256, size=(nb, 84), dtype=np.uint8)
+        t[:, 80:82] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
+        t[:, 82:84] = _f16_scales(r, nb).view(np.uint8).reshape(nb, 2)
     elif dtype == AGN_Q6_K:
         nb = n_rows * ((row_len + 255) // 256)
         t = r.integers(0, 256, size=(nb, 210), dtype=np.uint8)

@@ -472,12 +472,13 @@ def run_ours(args, cfg, ops_list, wl):
     #      fused residual-add + norm, KV-cache packing, and a causal softmax at prefill size
     extra_ops = {}
     if not f16 and not args.no_extras and step_bytes < 4e9:
-        from agention_infer_b200 import AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
+        from agention_infer_b200 import AGN_BF16, AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
         hd_kv = nkv * hd
         Ls = min(T, 2048)
         ex_sets = []
         for s_ in range(nsets):
             ex_sets.append({"x": rn(T, H), "d": rn(T, H), "nx": torch.empty(T, H, device=dev), "nm": torch.empty(T, H, device=dev),
+                            "nb": torch.empty(T, H, dtype=torch.bfloat16, device=dev),
                             "k": rn(T, hd_kv), "v": rn(T, hd_kv),
                             "kc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
                             "vc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
@@ -487,6 +488,10 @@ def run_ours(args, cfg, ops_list, wl):
         extras = {
             "add_residual_rms_norm": (lambda b: be.launch_add_residual_rms_norm(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], normed=b["nm"]),
                                       16 * T * H + 4 * H),
+            "rms_norm_out_bf16": (lambda b: be.launch_rms_norm_out16(b["x"], w, T, H, cfg.eps, AGN_BF16, out=b["nb"]), 6 * T * H + 4 * H),
+            "add_residual_rms_norm_out_bf16": (lambda b: be.launch_add_residual_rms_norm_out16(b["x"], b["d"], w, T, H, cfg.eps, AGN_BF16,
+                                                                                                new_x=b["nx"], normed=b["nb"]),
+                                               14 * T * H + 4 * H),
             "kv_write_q8_0": (lambda b: be.kv_write(KV_Q8_0, b["k"], b["v"], b["kc"], b["vc"], T, hd_kv, None, T),
                               2 * T * (4 * hd_kv + be.kv_bytes_per_token(KV_Q8_0, hd_kv))),
             "kv_write_f16": (lambda b: be.kv_write(KV_F16, b["k"], b["v"], b["kh"], b["vh"], T, hd_kv, None, T),

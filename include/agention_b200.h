@@ -59,6 +59,7 @@ typedef enum agn_dtype {
     AGN_F16 = 1,
     AGN_Q5_0 = 6,
     AGN_Q8_0 = 8,
+    AGN_Q2_K = 10,
     AGN_Q4_K = 12,
     AGN_Q5_K = 13,
     AGN_Q6_K = 14,
@@ -211,11 +212,27 @@ AGN_API int32_t agn_softmax_rows_unnorm_f32(agn_ctx *ctx, const float *in, float
                                             const int32_t *n_valid, int32_t causal_period,
                                             int32_t causal_offset);
 
+/* Softmax of scale * scores in one pass.  The reference's GPU attention stores `dot * scale`,
+ * scale = 1 / sqrt(head_dim), from a kernel of its own (`attention_scores`,
+ * src/ops/kernels_wgpu.rs:773-782; the CPU path divides by sqrt(head_dim),
+ * src/model/llama/cpu_path.rs:172) and runs the softmax over that buffer; with the scale taken
+ * here the caller hands over raw dot products.  scale must be positive and finite (AGN_EINVAL
+ * otherwise).  sums == NULL: out = normalised probabilities (agn_softmax_rows_f32 of the scaled
+ * scores); sums != NULL: out = exp(scale * (s - max)) and sums[r], as
+ * agn_softmax_rows_unnorm_f32.  Other arguments as agn_softmax_rows_f32. */
+AGN_API int32_t agn_softmax_rows_scaled_f32(agn_ctx *ctx, const float *in, float *out, float *sums,
+                                            int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                            const int32_t *n_valid, int32_t causal_period,
+                                            int32_t causal_offset, float scale);
+
 /* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
  * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
  * -> dequant_q8_0 / dequant_q4_k / dequant_q6_k (src/quant/q8_0.rs:14-51,
  * q4_k.rs:37-91, q6_k.rs:34-77), also dequant_q5_k (q5_k.rs:43-103) and dequant_q5_0
- * (q5_0.rs:20-62), looped over tokens as cpu_path.rs:865-868 does.
+ * (q5_0.rs:20-62), and dequant_q2_k (q2_k.rs:30-98; 84-byte super-blocks as that codec reads
+ * them, rows 84 * row_len / 256 bytes apart as in a GGUF file, although GgmlType::block_bytes,
+ * src/types.rs:137, lists 256 for the type; row_len must be a multiple of 256, else AGN_EINVAL
+ * as q2_k.rs:31-35 returns Err), looped over tokens as cpu_path.rs:865-868 does.
  * table: n_rows rows of type_size(dtype, row_len) bytes each, 16-byte aligned;
  * table_bytes = readable bytes at table; ids: device u32 [T]; out: [T, row_len] f32.
  * Bit-exact with the CPU codecs.  An id >= n_rows zero-fills its row and makes the
@@ -277,6 +294,18 @@ AGN_API int32_t agn_rms_norm_f16(agn_ctx *ctx, const void *x, const float *w, vo
 AGN_API int32_t agn_add_residual_rms_norm_f16(agn_ctx *ctx, const void *x, const void *delta,
                                               const float *w, void *new_x, void *normed, int64_t T,
                                               int64_t H, float eps);
+/* f32 rows in, the NORMED row out as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16): the f32
+ * result of agn_rms_norm_f32 / agn_add_residual_rms_norm_f32 rounded to nearest even on store,
+ * i.e. the operand a half-precision matmul takes, without an f32 row and a cast pass in
+ * between (6 instead of 8 bytes per element, 14 instead of 16 for the residual form).  new_x,
+ * the residual stream, stays f32.  No counterpart in the reference, whose norm kernels read and
+ * write the same `Act` type (src/ops/kernels_wgpu.rs:79-163).  Any other out_dtype:
+ * AGN_EUNSUPPORTED_DTYPE. */
+AGN_API int32_t agn_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *w, void *out,
+                                       int64_t T, int64_t H, float eps, int32_t out_dtype);
+AGN_API int32_t agn_add_residual_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *delta,
+                                                    const float *w, float *new_x, void *normed,
+                                                    int64_t T, int64_t H, float eps, int32_t out_dtype);
 AGN_API int32_t agn_rope_qk_f16(agn_ctx *ctx, void *q, void *k, int64_t T, int32_t n_q_heads,
                                 int32_t n_kv_heads, int32_t head_dim, int32_t n_rot,
                                 const int32_t *pos, int32_t pos_start, float theta, float freq_scale,

@@ -166,6 +166,25 @@ class CudaBackend {
         check(agn_rms_norm_f16(ctx_, x, w, out.ptr(), T, H, eps));
         return out;
     }
+    // f32 rows in, normed rows out as f16 / bf16 (out_dtype = AGN_F16 | AGN_BF16)
+    DeviceBuffer launch_rms_norm_out16(const float *x, const float *w, int64_t T, int64_t H, float eps, int out_dtype) {
+        DeviceBuffer out = empty(2 * (size_t)(T * H));
+        check(agn_rms_norm_f32_out16(ctx_, x, w, out.ptr(), T, H, eps, out_dtype));
+        return out;
+    }
+    std::pair<DeviceBuffer, DeviceBuffer> launch_add_residual_rms_norm_out16(const float *x, const float *delta, const float *w,
+                                                                             int64_t T, int64_t H, float eps, int out_dtype) {
+        DeviceBuffer new_x = empty(4 * (size_t)(T * H)), normed = empty(2 * (size_t)(T * H));
+        check(agn_add_residual_rms_norm_f32_out16(ctx_, x, delta, w, static_cast<float *>(new_x.ptr()), normed.ptr(), T, H, eps,
+                                                  out_dtype));
+        return {std::move(new_x), std::move(normed)};
+    }
+    // softmax of scale * scores; sums != nullptr: unnormalised weights + row sums
+    void launch_softmax_rows_scaled(const float *in, float *out, float *sums, int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                    const int32_t *n_valid, int causal_period, int causal_offset, float scale) {
+        check(agn_softmax_rows_scaled_f32(ctx_, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset,
+                                          scale));
+    }
     void launch_qk_norm_rope_qk_f16(void *q, void *k, const float *wq, const float *wk, int64_t T, int n_q, int n_kv,
                                     int head_dim, float eps, int n_rot, const int32_t *pos, int pos_start, float theta,
                                     float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {

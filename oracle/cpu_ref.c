@@ -21,7 +21,7 @@ size_t orc_block_size(int dtype) {
     switch (dtype) {
     case ORC_F32: case ORC_F16: case ORC_BF16: return 1;
     case ORC_Q8_0: case ORC_Q5_0: return 32;
-    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return 256;
+    case ORC_Q2_K: case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -34,6 +34,7 @@ size_t orc_block_bytes(int dtype) {
     case ORC_Q8_0: return 34;
     case ORC_Q5_0: return 22;
     case ORC_Q5_K: return 176;
+    case ORC_Q2_K: return 84; /* q2_k.rs:24 (the codec), not types.rs:137 */
     case ORC_Q4_K: return 144;
     case ORC_Q6_K: return 210;
     default: return 0;
@@ -320,6 +321,38 @@ int orc_dequant_q5_k(const uint8_t *data, size_t data_len, size_t n, float *out)
     return ORC_OK;
 }
 
+/* src/quant/q2_k.rs:30-98 */
+int orc_dequant_q2_k(const uint8_t *data, size_t data_len, size_t n, float *out) {
+    if (n % 256 != 0) return ORC_ELEN;
+    size_t n_blocks = n / 256;
+    if (data_len < n_blocks * 84) return ORC_ESHORT;
+    for (size_t b = 0; b < n_blocks; b++) {
+        const uint8_t *blk = data + b * 84;
+        const uint8_t *scales = blk, *qs = blk + 16;
+        float d = orc_f16_to_f32(rd_u16(blk + 80));
+        float dmin = orc_f16_to_f32(rd_u16(blk + 82));
+        float *o = out + b * 256;
+        size_t is = 0, q_off = 0;
+        for (int group = 0; group < 2; group++) {
+            unsigned shift = 0;
+            for (int j = 0; j < 4; j++) {
+                for (int half = 0; half < 2; half++) {
+                    uint8_t sc = scales[is++];
+                    float dl = d * (float)(sc & 0xF);
+                    float ml = dmin * (float)(sc >> 4);
+                    for (size_t l = 0; l < 16; l++) {
+                        int8_t quant = (int8_t)((qs[q_off + 16 * half + l] >> shift) & 3);
+                        *o++ = dl * (float)quant - ml;
+                    }
+                }
+                shift += 2;
+            }
+            q_off += 32;
+        }
+    }
+    return ORC_OK;
+}
+
 /* src/quant/q5_0.rs:20-62 */
 int orc_dequant_q5_0(const uint8_t *data, size_t data_len, size_t n, float *out) {
     size_t n_blocks = (n + 31) / 32;
@@ -419,6 +452,7 @@ int orc_dequant_row(int dtype, const uint8_t *data, size_t data_len, size_t byte
     case ORC_Q8_0: return orc_dequant_q8_0(p, avail, row_len, out);
     case ORC_Q4_K: return orc_dequant_q4_k(p, avail, row_len, out);
     case ORC_Q5_K: return orc_dequant_q5_k(p, avail, row_len, out);
+    case ORC_Q2_K: return orc_dequant_q2_k(p, avail, row_len, out);
     case ORC_Q5_0: return orc_dequant_q5_0(p, avail, row_len, out);
     case ORC_Q6_K: return orc_dequant_q6_k(p, avail, row_len, out);
     default: return ORC_EDTYPE;

@@ -41,13 +41,14 @@ enum {
     ORC_F16 = 1,
     ORC_Q5_0 = 6,
     ORC_Q8_0 = 8,
+    ORC_Q2_K = 10,
     ORC_Q4_K = 12,
     ORC_Q5_K = 13,
     ORC_Q6_K = 14,
     ORC_BF16 = 30
 };
 
-enum { ORC_OK = 0, ORC_ESHORT = 1, ORC_EROW = 2, ORC_EDTYPE = 3 };
+enum { ORC_OK = 0, ORC_ESHORT = 1, ORC_EROW = 2, ORC_EDTYPE = 3, ORC_ELEN = 4 };
 
 /* layout of the rotated pairs */
 enum { ORC_ROPE_NEOX = 0, ORC_ROPE_NORMAL = 1 };
@@ -116,6 +117,11 @@ int orc_dequant_q6_k(const uint8_t *data, size_t data_len, size_t n, float *out)
 /* src/quant/q5_k.rs:43-103, src/quant/q5_0.rs:20-62 */
 int orc_dequant_q5_k(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_q5_0(const uint8_t *data, size_t data_len, size_t n, float *out);
+/* src/quant/q2_k.rs:30-98: 84-byte super-blocks (the codec's BLOCK_BYTES, :24; the row
+ * stride used here is 84 bytes per 256 values, the GGUF file layout, although
+ * GgmlType::block_bytes lists 256 for this type, src/types.rs:137).  ORC_ELEN when n is not
+ * a multiple of 256, as the reference returns Err (:31-35). */
+int orc_dequant_q2_k(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_f32(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_f16(const uint8_t *data, size_t data_len, size_t n, float *out);
 int orc_dequant_bf16(const uint8_t *data, size_t data_len, size_t n, float *out);

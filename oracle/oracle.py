@@ -15,9 +15,9 @@ HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
-Q5_0, Q5_K = 6, 13
+Q5_0, Q5_K, Q2_K = 6, 13, 10
 NEOX, NORMAL = 0, 1
-OK, ESHORT, EROW, EDTYPE = 0, 1, 2, 3
+OK, ESHORT, EROW, EDTYPE, ELEN = 0, 1, 2, 3, 4
 
 
 def build(force: bool = False) -> Path:
@@ -51,6 +51,7 @@ def lib() -> C.CDLL:
             "orc_get_scale_min_k4": (None, [_sz, _vp, _vp, _vp]),
             "orc_dequant_q8_0": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_q4_k": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_q5_k": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_q5_0": (_i, [_vp, _sz, _sz, _vp]),
+            "orc_dequant_q2_k": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_q6_k": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_f32": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_f16": (_i, [_vp, _sz, _sz, _vp]), "orc_dequant_bf16": (_i, [_vp, _sz, _sz, _vp]),
             "orc_dequant_row": (_i, [_i, _vp, _sz, _sz, _sz, _sz, _sz, _vp]),
@@ -161,7 +162,7 @@ def get_scale_min_k4(j: int, scales) -> tuple:
     return int(sc.value), int(m.value)
 
 
-_DEQ = {Q5_0: "orc_dequant_q5_0", Q5_K: "orc_dequant_q5_k", Q8_0: "orc_dequant_q8_0", Q4_K: "orc_dequant_q4_k", Q6_K: "orc_dequant_q6_k", F32: "orc_dequant_f32",
+_DEQ = {Q2_K: "orc_dequant_q2_k", Q5_0: "orc_dequant_q5_0", Q5_K: "orc_dequant_q5_k", Q8_0: "orc_dequant_q8_0", Q4_K: "orc_dequant_q4_k", Q6_K: "orc_dequant_q6_k", F32: "orc_dequant_f32",
         F16: "orc_dequant_f16", BF16: "orc_dequant_bf16"}
 
 

@@ -100,6 +100,17 @@ cases["q5_k_block"] = {"cite": "src/quant/q5_k.rs:375-392",
                                           [((i * 29) + 3) & 0xFF for i in range(32)],
                                           [(i * 13) & 0xFF for i in range(128)]), "n": 256}
 
+# src/quant/q2_k.rs:113-177  zero block and basic pattern (scales[16] | qs[64] | f16 d | f16 dmin)
+def q2_k_block(d, dmin, scales, qs):
+    return list(scales) + list(qs) + [int(b) for b in f16_bytes(d)] + [int(b) for b in f16_bytes(dmin)]
+
+
+cases["q2_k_zero_block"] = {"cite": "src/quant/q2_k.rs:113-127", "data": q2_k_block(1.0, 0.0, [0] * 16, [0] * 64),
+                            "n": 256, "expected_all": 0.0, "tol": 0.0}
+cases["q2_k_basic_pattern"] = {"cite": "src/quant/q2_k.rs:129-177",
+                               "data": q2_k_block(2.0, 0.5, [0x21, 0x43] + [0] * 14, [0xFF] * 32 + [0] * 32), "n": 256,
+                               "expected_ranges": [[0, 16, 5.0], [16, 32, 16.0]], "tol": 1e-5}
+
 # src/quant/mod.rs:176-205  f32 / f16 / bf16 rows
 cases["f32_row"] = {"cite": "src/quant/mod.rs:176-185",
                     "data": [int(b) for b in np.array([1.0, 2.0, -3.5], dtype="<f4").view(np.uint8)], "n": 3,

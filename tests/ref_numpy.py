@@ -78,6 +78,21 @@ def dequant_q5_0(data: np.ndarray, n: int) -> np.ndarray:
     return (x * d[:, None]).astype(np.float32).reshape(-1)[:n]
 
 
+def dequant_q2_k(data: np.ndarray, n: int) -> np.ndarray:
+    nb = n // 256
+    blk = np.ascontiguousarray(data[: nb * 84]).reshape(nb, 84)
+    sc = blk[:, 0:16]
+    qs = blk[:, 16:80].reshape(nb, 2, 32)                 # [group][byte]
+    d, dmin = f16(blk[:, 80:82]), f16(blk[:, 82:84])
+    shifts = np.arange(4, dtype=np.uint8) * 2
+    q = ((qs[:, :, None, :] >> shifts[None, None, :, None]) & 3).astype(np.float32)   # [nb, group, shift, 32]
+    q = q.reshape(nb, 16, 16)                             # 16 runs of 16 values, one scale byte each
+    dl = (d[:, None] * (sc & 0xF).astype(np.float32)).astype(np.float32)
+    ml = (dmin[:, None] * (sc >> 4).astype(np.float32)).astype(np.float32)
+    out = (dl[:, :, None] * q).astype(np.float32) - ml[:, :, None]
+    return out.astype(np.float32).reshape(-1)[:n]
+
+
 def dequant_q6_k(data: np.ndarray, n: int) -> np.ndarray:
     nb = (n + 255) // 256
     blk = np.ascontiguousarray(data[: nb * 210]).reshape(nb, 210)

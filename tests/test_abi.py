@@ -45,7 +45,8 @@ def test_type_size_matches_reference_table(lib):  # src/types.rs:88-168
     assert lib.agn_type_size(_abi.AGN_BF16, 5) == 10
     assert lib.agn_type_size(_abi.AGN_Q5_K, 512) == 352
     assert lib.agn_type_size(_abi.AGN_Q5_0, 64) == 44
-    assert lib.agn_type_size(10, 256) == 0  # Q2_K: no kernel
+    assert lib.agn_type_size(_abi.AGN_Q2_K, 512) == 168  # the codec's 84-byte block, src/quant/q2_k.rs:24
+    assert lib.agn_type_size(11, 256) == 0  # Q3_K: no kernel
 
 
 def test_status_strings_and_name(lib):

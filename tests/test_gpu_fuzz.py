@@ -3,7 +3,7 @@ blocks, ragged lengths — the cases the fixed parity tests do not enumerate."""
 import numpy as np
 import pytest
 
-from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
+from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q2_K, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
                                  AGN_ROPE_NORMAL, synth)
 from oracle import oracle as orc
 
@@ -96,11 +96,12 @@ def test_fuzz_silu_mul(backend):
         assert np.max(np.abs(backend.read(out, np.float32, (n,)) - ref) / np.maximum(np.abs(ref), 1.0)) <= TOL, (n, off)
 
 
-@pytest.mark.parametrize("dtype", [AGN_Q8_0, AGN_Q4_K, AGN_Q5_K, AGN_Q5_0, AGN_Q6_K])
+@pytest.mark.parametrize("dtype", [AGN_Q8_0, AGN_Q4_K, AGN_Q5_K, AGN_Q5_0, AGN_Q6_K, AGN_Q2_K])
 def test_fuzz_get_rows(backend, dtype):
     r = np.random.default_rng(105 + dtype)
+    lens = [256, 512, 768, 1024, 2048, 2304] if dtype == AGN_Q2_K else [1, 3, 31, 32, 33, 64, 100, 255, 256, 257, 300, 511, 512, 768, 1000, 2049]
     for it in range(25):
-        vocab = int(r.integers(1, 40)); row_len = int(r.choice([1, 3, 31, 32, 33, 64, 100, 255, 256, 257, 300, 511, 512, 768, 1000, 2049]))
+        vocab = int(r.integers(1, 40)); row_len = int(r.choice(lens))
         T = int(r.integers(1, 30))
         table = synth.quant_table(dtype, vocab, row_len, cfg_index=it % 5, salt=it)
         ids = r.integers(0, vocab, size=T).astype(np.uint32)

@@ -4,7 +4,7 @@ same seeded inputs.  get_rows is bit-exact; the float ops are within 1e-5 of the
 import numpy as np
 import pytest
 
-from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
+from agention_infer_b200 import (AGN_BF16, AGN_F16, AGN_F32, AGN_Q2_K, AGN_Q4_K, AGN_Q5_0, AGN_Q5_K, AGN_Q6_K, AGN_Q8_0, AGN_ROPE_NEOX,
                                  AGN_ROPE_NORMAL, BackendError, synth)
 from oracle import oracle as orc
 
@@ -270,7 +270,7 @@ def test_attention_softmax_unnormalised_form(backend):
     (AGN_Q4_K, 32000, 4096, 512), (AGN_Q8_0, 100, 96, 33), (AGN_Q8_0, 64, 33, 17), (AGN_Q6_K, 50, 768, 50),
     (AGN_Q6_K, 20, 300, 9), (AGN_Q4_K, 20, 300, 9), (AGN_Q4_K, 7, 256, 1), (AGN_Q8_0, 1, 32, 5),
     (AGN_Q5_K, 32000, 4096, 2048), (AGN_Q5_K, 20, 300, 9), (AGN_Q5_0, 4096, 2048, 1024), (AGN_Q5_0, 64, 33, 17),
-    (AGN_Q5_0, 10, 96, 33),
+    (AGN_Q5_0, 10, 96, 33), (AGN_Q2_K, 32000, 4096, 2048), (AGN_Q2_K, 33, 256, 40), (AGN_Q2_K, 5, 768, 9),
 ])
 def test_get_rows_bit_exact(backend, dtype, vocab, row_len, T):
     table = synth.quant_table(dtype, vocab, row_len, cfg_index=2)
@@ -285,7 +285,7 @@ def test_get_rows_bit_exact(backend, dtype, vocab, row_len, T):
 
 
 @pytest.mark.parametrize("dtype,vocab,row_len,T", [(AGN_Q4_K, 4096, 3584, 2048), (AGN_Q8_0, 300, 96, 300),
-                                                   (AGN_Q6_K, 128, 768, 128), (AGN_Q5_0, 64, 33, 64), (AGN_Q6_K, 50, 4096, 50)])
+                                                   (AGN_Q6_K, 128, 768, 128), (AGN_Q5_0, 64, 33, 64), (AGN_Q6_K, 50, 4096, 50), (AGN_Q2_K, 77, 512, 77)])
 def test_get_rows_both_staging_paths_bit_exact(backend, dtype, vocab, row_len, T):
     # default staging is one bulk asynchronous copy (TMA, cp.async.bulk + mbarrier) per row, with
     # rows that start off a 16-byte boundary and the last row of the table (which falls back to
@@ -346,6 +346,9 @@ def test_get_rows_argument_errors(backend):
     assert e.value.status == 2
     with pytest.raises(BackendError) as e:  # rows extend beyond the data section
         backend.get_rows(AGN_Q4_K, t, 100, 1, 256, ids, 1, out=o)
+    assert e.value.status == 1
+    with pytest.raises(BackendError) as e:  # "Q2_K row length .. is not a multiple of 256", src/quant/q2_k.rs:31-35
+        backend.get_rows(AGN_Q2_K, t, 4096, 1, 300, ids, 1, out=backend.empty(4 * 300))
     assert e.value.status == 1
 
 

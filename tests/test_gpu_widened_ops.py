@@ -1,0 +1,108 @@
+"""Entry points that widen the path toward its callers: normed rows stored as f16 / bf16 from
+f32 inputs, and a softmax that takes the score scale.
+
+16-bit outputs: the kernel computes the same f32 value as the f32 entry point and rounds it to
+nearest even on store, so (a) it must equal the f32 entry point's own output rounded on the host
+bit for bit, and (b) it sits within one ulp of the 16-bit format (2^-10 of the row scale for f16,
+2^-7 for bf16) of the oracle's f32 result rounded the same way.
+Scaled softmax: the oracle runs the softmax over scale * scores computed in f32 first (what the
+reference's `attention_scores` stores, src/ops/kernels_wgpu.rs:773-782); tolerance 1e-5 of the
+row scale as for the plain softmax."""
+import numpy as np
+import pytest
+
+from agention_infer_b200 import AGN_BF16, AGN_F16, AGN_Q8_0, BackendError, synth
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+THREADS = max(1, orc.max_threads())
+TOL = 1e-5
+
+
+def to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    """f32 -> bf16 bit patterns, round to nearest even (finite inputs)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def check16(backend, buf, f32_gpu, f32_ref, out_dtype, shape):
+    if out_dtype == AGN_F16:
+        got = backend.read(buf, np.float16, shape)
+        assert np.array_equal(got.view(np.uint16), f32_gpu.astype(np.float16).view(np.uint16))
+        assert synth.max_rel_to_row_scale(got.astype(np.float32), f32_ref.astype(np.float16).astype(np.float32)) <= 2.0 ** -10
+    else:
+        got = backend.read(buf, np.uint16, shape)
+        assert np.array_equal(got, to_bf16_bits(f32_gpu))
+        assert synth.max_rel_to_row_scale(from_bf16_bits(got), from_bf16_bits(to_bf16_bits(f32_ref))) <= 2.0 ** -7
+
+
+@pytest.mark.parametrize("out_dtype", [AGN_F16, AGN_BF16])
+@pytest.mark.parametrize("T,H", [(512, 2048), (256, 3584), (3, 250), (2, 40000), (1, 4)])
+def test_rms_norm_f32_to_16bit_output(backend, T, H, out_dtype):
+    x, w = synth.activations(2, "x", (T, H)), synth.norm_weight(2, "w", H)
+    ref = orc.rms_norm_rows(x, w, 1e-6, THREADS)
+    dx, dw = backend.upload(x), backend.upload(w)
+    f32_gpu = backend.read(backend.launch_rms_norm(dx, dw, T, H, 1e-6), np.float32, (T, H))
+    out = backend.launch_rms_norm_out16(dx, dw, T, H, 1e-6, out_dtype)
+    check16(backend, out, f32_gpu, ref, out_dtype, (T, H))
+
+
+@pytest.mark.parametrize("out_dtype", [AGN_F16, AGN_BF16])
+@pytest.mark.parametrize("T,H", [(128, 4096), (5, 250)])
+def test_add_residual_rms_norm_f32_to_16bit_output(backend, T, H, out_dtype):
+    x, d, w = synth.activations(4, "x", (T, H)), synth.activations(4, "delta", (T, H)), synth.norm_weight(4, "w", H)
+    ref_x, ref_n = orc.add_residual_rms_norm_rows(x, d, w, 1e-5, THREADS)
+    dx, dd, dw = backend.upload(x), backend.upload(d), backend.upload(w)
+    nx32, nm32 = backend.launch_add_residual_rms_norm(dx, dd, dw, T, H, 1e-5)
+    f32_gpu = backend.read(nm32, np.float32, (T, H))
+    nx, nm = backend.launch_add_residual_rms_norm_out16(dx, dd, dw, T, H, 1e-5, out_dtype)
+    # the residual stream stays f32 and is the exact sum
+    assert np.array_equal(backend.read(nx, np.float32, (T, H)).view(np.uint32), ref_x.view(np.uint32))
+    check16(backend, nm, f32_gpu, ref_n, out_dtype, (T, H))
+
+
+def test_16bit_output_rejects_other_types(backend):
+    x, w = backend.upload(np.ones((1, 8), np.float32)), backend.upload(np.ones(8, np.float32))
+    with pytest.raises(BackendError) as e:
+        backend.launch_rms_norm_out16(x, w, 1, 8, 1e-6, AGN_Q8_0)
+    assert e.value.status == 2
+
+
+@pytest.mark.parametrize("nh,L,hd", [(32, 512, 64), (28, 1024, 128), (4, 9999, 128), (2, 20000, 128), (3, 37, 80), (64, 8, 128), (5, 200, 96)])
+def test_softmax_scaled_causal(backend, nh, L, hd):
+    rows = min(L, 64)  # the last `rows` query positions of each head
+    s = synth.activations(1, "scores", (nh, rows, L), std=2.0 * np.sqrt(hd))  # raw dot products: std grows with sqrt(hd)
+    scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+    nv = np.tile(np.arange(L - rows, L, dtype=np.int32) + 1, nh)
+    ref = orc.softmax_rows((s * scale).astype(np.float32).reshape(nh * rows, L), nv, THREADS)
+    out = backend.launch_softmax_rows_scaled(backend.upload(s), nh * rows, L, float(scale), causal_period=rows,
+                                             causal_offset=L - rows)
+    got = backend.read(out, np.float32, (nh * rows, L))
+    assert synth.max_rel_to_row_scale(got, ref) <= TOL
+    assert np.all(got[np.arange(L)[None, :] >= nv[:, None]] == 0.0)
+    # unnormalised form: weights / sums reproduces the probabilities
+    sums = backend.empty(4 * nh * rows)
+    wts = backend.launch_softmax_rows_scaled(backend.upload(s), nh * rows, L, float(scale), sums=sums, causal_period=rows,
+                                             causal_offset=L - rows)
+    gw, gs = backend.read(wts, np.float32, (nh * rows, L)), backend.read(sums, np.float32, (nh * rows,))
+    assert synth.max_rel_to_row_scale(gw / gs[:, None], ref) <= TOL
+
+
+def test_softmax_scale_one_is_the_plain_softmax(backend):
+    s = synth.activations(1, "scores", (64, 512), std=2.0)
+    ds = backend.upload(s)
+    a = backend.read(backend.launch_softmax_rows(ds, 64, 512), np.float32, (64, 512))
+    b = backend.read(backend.launch_softmax_rows_scaled(ds, 64, 512, 1.0), np.float32, (64, 512))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("scale", [0.0, -1.0, float("inf"), float("nan")])
+def test_softmax_scale_must_be_positive_and_finite(backend, scale):
+    s = backend.upload(np.zeros((1, 8), np.float32))
+    with pytest.raises(BackendError) as e:
+        backend.launch_softmax_rows_scaled(s, 1, 8, scale)
+    assert e.value.status == 1

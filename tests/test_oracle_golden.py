@@ -58,7 +58,23 @@ def test_q5_k_reference_vectors():  # src/quant/q5_k.rs:348-373
         assert st == orc.OK and np.all(np.abs(out - c["expected_all"]) <= c["tol"])
 
 
+def test_q2_k_reference_vectors():  # src/quant/q2_k.rs:108-177
+    assert orc.type_size(orc.Q2_K, 256) == 84 and orc.type_size(orc.Q2_K, 512) == 168
+    c = KA["q2_k_zero_block"]
+    st, out = orc.dequant(orc.Q2_K, _data("q2_k_zero_block"), 256)
+    assert st == orc.OK and np.all(out == c["expected_all"])
+    c = KA["q2_k_basic_pattern"]
+    st, out = orc.dequant(orc.Q2_K, _data("q2_k_basic_pattern"), 256)
+    assert st == orc.OK
+    for lo, hi, v in c["expected_ranges"]:
+        assert np.all(np.abs(out[lo:hi] - v) < c["tol"])
+    # "row length is not a multiple of 256" and "data too short" are errors (q2_k.rs:31-46)
+    assert orc.dequant(orc.Q2_K, _data("q2_k_basic_pattern"), 100)[0] == orc.ELEN
+    assert orc.dequant(orc.Q2_K, _data("q2_k_basic_pattern")[:80], 256)[0] == orc.ESHORT
+
+
 @pytest.mark.parametrize("name,dtype,fn", [("q8_0_three_blocks", orc.Q8_0, rn.dequant_q8_0),
+                                           ("q2_k_basic_pattern", orc.Q2_K, rn.dequant_q2_k),
                                            ("q5_k_block", orc.Q5_K, rn.dequant_q5_k),
                                            ("q5_0_roundtrip", orc.Q5_0, rn.dequant_q5_0),
                                            ("q4_k_block", orc.Q4_K, rn.dequant_q4_k),
@@ -119,7 +135,7 @@ def test_f16_widening_is_exact_for_every_bit_pattern():
 
 @pytest.mark.parametrize("dtype,fn,blk", [(orc.Q8_0, rn.dequant_q8_0, 34 / 32), (orc.Q4_K, rn.dequant_q4_k, 144 / 256),
                                           (orc.Q5_K, rn.dequant_q5_k, 176 / 256), (orc.Q5_0, rn.dequant_q5_0, 22 / 32),
-                                          (orc.Q6_K, rn.dequant_q6_k, 210 / 256)])
+                                          (orc.Q6_K, rn.dequant_q6_k, 210 / 256), (orc.Q2_K, rn.dequant_q2_k, 84 / 256)])
 def test_random_blocks_match_numpy_statement_bitwise(dtype, fn, blk):
     from agention_infer_b200 import synth
     row_len, n_rows = 1024, 64
