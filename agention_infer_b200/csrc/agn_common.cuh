@@ -44,6 +44,8 @@ struct agn_ctx {
     int tune_rms_vpt;           // 0 = automatic; 1/2/4/8 float4 per thread in rms_norm
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic
+    int tune_softmax_cluster;   // rows of 16K-128K entries: 1 = one thread-block cluster per row, CTAs of <= 512 threads
+                                // (default); 2 = CTAs of <= 256 threads; 0 = no clusters
     int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)
     int tune_get_rows_tma;      // stage the quantised row with one bulk asynchronous copy (TMA)
     int tune_silu_unroll;       // float4 pairs in flight per thread in silu_mul: 2, 4 (default) or 8
@@ -119,6 +121,27 @@ inline void agn_launch(agn_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 b
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in AGN_LAUNCHED
+}
+
+// The same with a thread-block cluster of cluster_x CTAs along x (grid.x must be a multiple of it).
+template <typename... KArgs, typename... Args>
+inline void agn_launch_cluster(agn_ctx *ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 2 : 1;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in AGN_LAUNCHED
 }
 

@@ -13,7 +13,11 @@
 //   - anything else (odd lengths, unaligned, longer): three passes over global memory.
 #include <math.h>
 
+#include <cooperative_groups.h>
+
 #include "agn_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -202,6 +206,92 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     }
 }
 
+// Long rows (8K-64K entries): one thread-block CLUSTER per row.  Each of the C CTAs (256 threads,
+// 8 float4 per thread) owns 8192 consecutive entries in registers; the row maximum and the row
+// sum are combined across the cluster through distributed shared memory (each CTA publishes its
+// partial in its own shared memory, every CTA reads all C partials in rank order after a cluster
+// barrier, so all CTAs compute the same value).  Each CTA finishes its own part first (maximum
+// m_c, e = exp(v - m_c), sum s_c) and the parts are merged afterwards (M = max m_c,
+// S = sum s_c exp(m_c - M), entry = e exp(m_c - M) / S), so one cluster barrier is enough.
+// Against one 1024-thread CTA per row this keeps several independent CTAs resident per SM, so
+// the loads of one row overlap the exponentials and stores of another.  Cluster barriers are
+// hardware barriers: no spin-waits.
+template <int VPT>
+__global__ void __launch_bounds__(512)
+softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
+    agn_pdl_prologue();
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float red[16];
+    __shared__ float xch[2];  // this CTA's partial maximum and partial sum, read by its peers
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int rank = (int)cluster.block_rank();
+    const int64_t r = blockIdx.x / cluster_size;
+    const int nv = (int)valid_len(a, r);
+    const int n4 = (int)(a.row_len >> 2);
+    const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
+    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    // tiles of blockDim float4 are dealt round-robin to the CTAs of the cluster, so the valid prefix
+    // of a causal row is spread evenly over them
+    const int base = rank * blockDim.x + threadIdx.x, step = cluster_size * blockDim.x;
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) v[k] = load_valid(in, base + k * step, nv);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) mask_tail(v[k], base + k * step, nv);
+    // this CTA's part on its own: maximum m_c, then e = exp(v - m_c) and their sum s_c
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    m = agn_warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+    for (int w = 1; w < nwarps; w++) m = fmaxf(m, red[w]);
+    __syncthreads();
+    const float m_c = m == -INFINITY ? 0.0f : m;  // a part with no valid entry: every e is exp(-inf) = 0
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        v[k] = exp4(v[k], m_c, a.exp_coef);
+        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    sum = agn_warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < nwarps; w++) t += red[w];
+        xch[0] = m;
+        xch[1] = t;
+    }
+    cluster.sync();
+    // combine the parts in rank order (the same value in every CTA):
+    // M = max m_c, S = sum s_c * exp(m_c - M); this CTA's entries are e * exp(m_c - M) / S
+    float M = -INFINITY;
+    for (int c = 0; c < cluster_size; c++) M = fmaxf(M, *cluster.map_shared_rank(&xch[0], c));
+    float S = 0.0f;
+    for (int c = 0; c < cluster_size; c++) {
+        const float mc = *cluster.map_shared_rank(&xch[0], c), sc = *cluster.map_shared_rank(&xch[1], c);
+        if (mc != -INFINITY) S += sc * exp_shifted(mc, M, a.exp_coef);
+    }
+    // arrive now, wait before leaving: no CTA may exit (and give up its shared memory) while a
+    // peer still reads it, but the stores below need not wait for that
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    if (a.sums && rank == 0 && threadIdx.x == 0) a.sums[r] = S;
+    float f = 0.0f;
+    if (nv > 0 && m != -INFINITY) f = exp_shifted(m, M, a.exp_coef) * (a.sums ? 1.0f : 1.0f / S);
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int i = base + k * step;
+        if (i < n4) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (4 * i < nv) o = make_float4(v[k].x * f, v[k].y * f, v[k].z * f, v[k].w * f);
+            agn_st_stream(out + i, o);
+        }
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
 __global__ void __launch_bounds__(256)
 softmax_generic_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
@@ -271,6 +361,13 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
         else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<4>, dim3(grid), dim3(32 * warps), 0, a);
         else agn_launch(ctx, softmax_warp_rows_kernel<8>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
+    } else if (vec_ok && n4 > 4096 && ctx->tune_softmax_cluster && n_rows <= 0x7fffffffLL / 8 &&
+               n4 <= 8 * 8 * (ctx->tune_softmax_cluster == 2 ? 256 : 512)) {
+        const int tmax = ctx->tune_softmax_cluster == 2 ? 256 : 512;  // measured: fewer, larger CTAs per cluster are faster
+        const int cs = (int)((n4 + 8 * tmax - 1) / (8 * tmax));  // 2..8 CTAs, the portable cluster limit
+        const int threads = (int)(((n4 + 8 * cs - 1) / (8 * cs) + 31) / 32 * 32);  // an even share, no idle tile
+        agn_launch_cluster(ctx, softmax_cluster_rows_kernel<8>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
+        AGN_LAUNCHED(ctx, "softmax_cluster_rows");
     } else if (vec_ok && n4 <= 8192) {
         // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries
         // (fewer warps in the two block-wide reductions, more loads in flight per thread)

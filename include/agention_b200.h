@@ -94,7 +94,13 @@ AGN_API int32_t agn_ctx_set_stream(agn_ctx *ctx, void *cuda_stream);
 AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
 /* Options.  "pdl" (default 1): launch kernels with programmatic stream serialization, so
  * that a kernel's launch latency overlaps the tail of the previous kernel of the stream
- * (every kernel still waits for the previous one to complete before its first access). */
+ * (every kernel still waits for the previous one to complete before its first access).
+ * Tuning knobs, all with measured defaults: "rms_vpt" (1, 2, 4, 8 vectors per thread; 0 = automatic),
+ * "rms_recip" (1: one reciprocal per row, 0: IEEE division per element), "silu_unroll" (2, 4, 8),
+ * "silu_threads" (128, 256, 512), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more
+ * than 16384 entries: 1 = one thread-block cluster per row, 2 = the same with smaller CTAs, 0 = one
+ * CTA per row), "get_rows_tma" (1: bulk-copy staging, 0: cp.async), "get_rows_threads" (32..256;
+ * 0 = automatic).  An unknown name is AGN_EINVAL. */
 AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value);
 /* Launches one empty kernel: the per-launch floor for launch-bound (decode-shaped) timings,
  * the counterpart of the reference's "dispatch floor" probe

@@ -106,3 +106,31 @@ def test_softmax_scale_must_be_positive_and_finite(backend, scale):
     with pytest.raises(BackendError) as e:
         backend.launch_softmax_rows_scaled(s, 1, 8, scale)
     assert e.value.status == 1
+
+
+@pytest.mark.parametrize("L", [16388, 20000, 32768, 49152])
+@pytest.mark.parametrize("cluster", [1, 2, 0])
+def test_softmax_long_rows_cluster_kernel(backend, L, cluster):
+    """Rows of more than 16384 entries run as one thread-block cluster per row (partial maxima and
+    sums merged through distributed shared memory); every valid length, the unnormalised form and
+    the scaled form must agree with the oracle like the one-CTA kernels do."""
+    R = 8
+    s = synth.activations(1, "scores", (R, L), std=2.0)
+    nv = np.array([L, L - 1, 1, 0, L // 2 + 1, 8193, 4, L - 4097], dtype=np.int32)
+    ref = orc.softmax_rows(s, nv, THREADS)
+    ds, dnv = backend.upload(s), backend.upload(nv)
+    backend.set_option("softmax_cluster", cluster)
+    try:
+        got = backend.read(backend.launch_softmax_rows(ds, R, L, n_valid=dnv), np.float32, (R, L))
+        sums = backend.empty(4 * R)
+        wts = backend.read(backend.launch_softmax_rows_scaled(ds, R, L, 1.0, sums=sums, n_valid=dnv), np.float32, (R, L))
+        gs = backend.read(sums, np.float32, (R,))
+        sc = backend.read(backend.launch_softmax_rows_scaled(ds, R, L, 0.5, n_valid=dnv), np.float32, (R, L))
+    finally:
+        backend.set_option("softmax_cluster", 1)
+    assert synth.max_rel_to_row_scale(got, ref) <= TOL
+    assert np.all(got[np.arange(L)[None, :] >= nv[:, None]] == 0.0)
+    ok = nv > 0
+    assert synth.max_rel_to_row_scale(wts[ok] / gs[ok, None], ref[ok]) <= TOL and np.all(wts[~ok] == 0.0) and np.all(gs[~ok] == 0.0)
+    ref_half = orc.softmax_rows((s * np.float32(0.5)).astype(np.float32), nv, THREADS)
+    assert synth.max_rel_to_row_scale(sc, ref_half) <= TOL
