@@ -361,12 +361,18 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
         else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<4>, dim3(grid), dim3(32 * warps), 0, a);
         else agn_launch(ctx, softmax_warp_rows_kernel<8>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
-    } else if (vec_ok && n4 > 4096 && ctx->tune_softmax_cluster && n_rows <= 0x7fffffffLL / 8 &&
-               n4 <= 8 * 8 * (ctx->tune_softmax_cluster == 2 ? 256 : 512)) {
-        const int tmax = ctx->tune_softmax_cluster == 2 ? 256 : 512;  // measured: fewer, larger CTAs per cluster are faster
-        const int cs = (int)((n4 + 8 * tmax - 1) / (8 * tmax));  // 2..8 CTAs, the portable cluster limit
-        const int threads = (int)(((n4 + 8 * cs - 1) / (8 * cs) + 31) / 32 * 32);  // an even share, no idle tile
-        agn_launch_cluster(ctx, softmax_cluster_rows_kernel<8>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
+    } else if (vec_ok && n4 > 4096 && ctx->tune_softmax_cluster && n_rows <= 0x7fffffffLL / 8 && n4 <= 8 * 16 * 512) {
+        // 2..8 CTAs (the portable cluster limit) of <= 512 threads; 8 float4 per thread, or 16 for rows
+        // of more than 131072 entries (a sampler's softmax over a 150K-entry vocabulary: few rows, so
+        // the registers of the wider variant cost no occupancy that matters)
+        const int tmax = ctx->tune_softmax_cluster == 2 && n4 <= 8 * 8 * 256 ? 256 : 512;  // measured: fewer, larger CTAs are faster
+        const int vpt = n4 > 8 * 8 * 512 ? 16 : 8;
+        const int cs = (int)((n4 + vpt * tmax - 1) / (vpt * tmax));
+        const int threads = (int)(((n4 + vpt * cs - 1) / (vpt * cs) + 31) / 32 * 32);  // an even share, no idle tile
+        if (vpt == 8)
+            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<8>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
+        else
+            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<16>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
         AGN_LAUNCHED(ctx, "softmax_cluster_rows");
     } else if (vec_ok && n4 <= 8192) {
         // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries

@@ -235,8 +235,8 @@ def run_reference(args, cfg, ops, wl):
     orc, rows, data, c, vocab = cpu_sample(cfg, ops)
     threads = host_threads()
     t1 = time_cpu(orc, c, data, rows, ops, threads, 1)
-    budget = 120.0
-    while rows > 64 and "softmax" not in ops and t1 * (args.steps + args.warmup) > budget:
+    limit_s = 120.0
+    while rows > 64 and "softmax" not in ops and t1 * (args.steps + args.warmup) > limit_s:
         rows //= 2
         t1 = time_cpu(orc, c, data, rows, ops, threads, 1)
     for _ in range(args.warmup):
