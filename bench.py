@@ -589,6 +589,9 @@ def run_ours(args, cfg, ops_list, wl):
 
     if rank == 0:
         peak, peak_src = measured_peaks()
+        for rec in list(per_op.values()) + list(extra_ops.values()):
+            rec["frac_of_peak"] = round(rec["gbs"] / peak, 3)
+            rec["frac_of_nominal_8tbs"] = round(rec["gbs"] / 8000.0, 3)
         if silu_ms is None:  # the step ran as a graph replay: no events inside it; use the kernel-alone time
             silu_ms = per_op["silu_mul"]["us"] * 1e-3
         achieved = ab["silu_mul"] / (silu_ms * 1e-3) / 1e9
@@ -604,6 +607,7 @@ def run_ours(args, cfg, ops_list, wl):
                        "launch": "one CUDA graph replay per step" if use_graph else "stream launches"},
             "hbm_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9 * world,
             "hbm_frac_of_measured_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+            "hbm_frac_of_nominal_8tbs": step_bytes / (ms_per_step * 1e-3) / 1e9 / 8000.0,
             "roofline": {"kernel": "silu_mul_vec4_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of measured (copy bandwidth, MEASURED_PEAKS.json)" if peak_src == "measured"
