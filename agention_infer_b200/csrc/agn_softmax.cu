@@ -59,6 +59,17 @@ __device__ __forceinline__ void mask_tail(float4 &v, int i, int nv) {
     }
 }
 
+// Entries past the valid length are defined as 0 whatever the row holds (a NaN or an infinity in
+// the row makes the factor NaN, and 0 * NaN would leak into the straddling float4).
+__device__ __forceinline__ void zero_tail(float4 &v, int i, int nv) {
+    const int e = 4 * i;
+    if (e < nv && e + 3 >= nv) {
+        if (e + 1 >= nv) v.y = 0.0f;
+        if (e + 2 >= nv) v.z = 0.0f;
+        v.w = 0.0f;
+    }
+}
+
 // exp(v - m) as 2^((v - m) * log2 e) with the hardware ex2: three instructions per element
 // instead of the ~10 of expf, which made these kernels issue-bound (84 % issue-active at
 // 59 % of DRAM peak).  Arguments are <= 0, so the result is in [0, 1] and its absolute
@@ -109,6 +120,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
         if (k < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * k < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
+            zero_tail(o, k, nv);
             agn_st_stream(out + k, o);
         }
 }
@@ -150,6 +162,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
+            zero_tail(o, i, nv);
             agn_st_stream(out + i, o);
         }
     }
@@ -201,6 +214,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
+            zero_tail(o, i, nv);
             agn_st_stream(out + i, o);
         }
     }
@@ -280,12 +294,16 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
     if (a.sums && rank == 0 && threadIdx.x == 0) a.sums[r] = S;
     float f = 0.0f;
     if (nv > 0 && m != -INFINITY) f = exp_shifted(m, M, a.exp_coef) * (a.sums ? 1.0f : 1.0f / S);
+    // a row whose valid entries are all -inf: exp(-inf - -inf) is NaN in the reference's loop and
+    // in the one-CTA kernels; give the same answer here
+    if (nv > 0 && M == -INFINITY) f = __int_as_float(0x7fc00000);
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = base + k * step;
         if (i < n4) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * f, v[k].y * f, v[k].z * f, v[k].w * f);
+            zero_tail(o, i, nv);
             agn_st_stream(out + i, o);
         }
     }
