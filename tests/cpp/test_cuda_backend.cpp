@@ -92,6 +92,35 @@ int main() {
         double e = rel_to_row_scale(be.read<float>(out, R * L), ref, L);
         expect(e <= TOL, "launch_softmax_rows", e);
     }
+    {  // softmax that takes the score scale (raw dot products in, 1/sqrt(head_dim) folded in)
+        const int64_t L = 384, R = 64;
+        auto s = randn(R * L);
+        const float scale = 1.0f / std::sqrt(128.0f);
+        std::vector<float> scaled(s.size()), ref(R * L);
+        for (size_t i = 0; i < s.size(); i++) { s[i] *= 22.f; scaled[i] = s[i] * scale; }
+        orc_softmax_rows(scaled.data(), ref.data(), R, L, L, nullptr, 1);
+        auto ds = be.upload(s);
+        auto out = be.empty(4 * R * L);
+        be.launch_softmax_rows_scaled(ds.as<float>(), out.as<float>(), nullptr, R, L, L, nullptr, 0, 0, scale);
+        double e = rel_to_row_scale(be.read<float>(out, R * L), ref, L);
+        expect(e <= TOL, "launch_softmax_rows_scaled", e);
+    }
+    {  // residual add + norm with the normed row stored as f16: the f32 result, rounded
+        auto x = randn(T * H), d = randn(T * H), w = weight(H);
+        auto dx = be.upload(x), dd = be.upload(d), dw = be.upload(w);
+        auto f32pair = be.launch_add_residual_rms_norm(dx.as<float>(), dd.as<float>(), dw.as<float>(), T, H, 1e-6f);
+        auto h16pair = be.launch_add_residual_rms_norm_out16(dx.as<float>(), dd.as<float>(), dw.as<float>(), T, H, 1e-6f, AGN_F16);
+        auto n32 = be.read<float>(f32pair.second, T * H);
+        auto n16 = be.read<uint16_t>(h16pair.second, T * H);
+        auto x32 = be.read<float>(f32pair.first, T * H), x32b = be.read<float>(h16pair.first, T * H);
+        // decode the halves exactly and compare with the f32 result: half an f16 ulp at most
+        double worst = 0.0;
+        for (size_t i = 0; i < n32.size(); i++) {
+            const double v = (double)orc_f16_to_f32(n16[i]);
+            worst = std::fmax(worst, std::fabs(v - (double)n32[i]) / std::fmax(std::fabs((double)n32[i]), 6.2e-5));
+        }
+        expect(worst <= 4.9e-4 && std::memcmp(x32.data(), x32b.data(), x32.size() * 4) == 0, "add_residual_rms_norm_out16", worst);
+    }
     for (int dtype : {AGN_Q8_0, AGN_Q4_K, AGN_Q6_K}) {  // get_rows, bit-exact
         const size_t rb = agn_type_size(dtype, H);
         std::vector<uint8_t> table(vocab * rb);
