@@ -132,6 +132,59 @@ __device__ __forceinline__ void decode8<AGN_Q4_K>(const uint8_t *row, int u, int
     vb.w = __fsub_rn(__fmul_rn(d2, (float)(q >> 28)), mm2);
 }
 
+// Four small unsigned integers (one per byte of x, each < 256) as floats without a conversion
+// instruction: byte k is placed into the mantissa of 2^23 (0x4B000000) by one byte permute,
+// and 2^23 + n - 2^23 = n exactly.
+__device__ __forceinline__ float4 bytes_to_float4(uint32_t x) {
+    float4 f;
+    f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - 8388608.0f;
+    f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - 8388608.0f;
+    f.z = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - 8388608.0f;
+    f.w = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - 8388608.0f;
+    return f;
+}
+__device__ __forceinline__ float4 scale_sub4(float4 q, float d, float m) {  // d * q - m, two roundings each
+    return make_float4(__fsub_rn(__fmul_rn(d, q.x), m), __fsub_rn(__fmul_rn(d, q.y), m), __fsub_rn(__fmul_rn(d, q.z), m),
+                       __fsub_rn(__fmul_rn(d, q.w), m));
+}
+
+// Q4_K, sixteen outputs per call: two 4-byte words of one 64-value group, 16 bytes apart, give
+// low-nibble values at elements e and e + 16 and high-nibble values at e + 32 and e + 48 (four
+// neighbouring lanes then write 64 contiguous bytes with every store instruction).  The block header (d, dmin and the
+// twelve packed scale bytes, src/quant/q4_k.rs:26-35) is one 128-bit shared-memory load and the
+// 6-bit scales are cut out of its words, shared by all sixteen outputs.  Q4_K rows are multiples
+// of 144 bytes, so every block starts on a 16-byte boundary of the staging buffer.
+__device__ __forceinline__ void decode16_q4_k(const uint8_t *row, int u, int &e, float4 lo[2], float4 hi[2]) {
+    const uint8_t *blk = row + (u >> 4) * 144;
+    const int r = u & 15, g = r >> 2, l = (r & 3) * 4;
+    e = (u >> 4) * 256 + 64 * g + l;
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+    const float d = f16_bits_to_f32((uint16_t)(hdr.x & 0xffff));
+    const float dmin = f16_bits_to_f32((uint16_t)(hdr.x >> 16));
+    uint32_t s0, m0, s1, m1;
+    if (g < 2) {  // sub-blocks 0..3: the low six bits of scale bytes j and j + 4
+        const int sh = 16 * g;
+        s0 = (hdr.y >> sh) & 63;
+        m0 = (hdr.z >> sh) & 63;
+        s1 = (hdr.y >> (sh + 8)) & 63;
+        m1 = (hdr.z >> (sh + 8)) & 63;
+    } else {  // sub-blocks 4..7: a nibble of byte j + 4 and the top two bits of bytes j - 4 and j
+        const int sh = 16 * (g - 2);
+        s0 = ((hdr.w >> sh) & 0xF) | (((hdr.y >> (sh + 6)) & 3) << 4);
+        m0 = ((hdr.w >> (sh + 4)) & 0xF) | (((hdr.z >> (sh + 6)) & 3) << 4);
+        s1 = ((hdr.w >> (sh + 8)) & 0xF) | (((hdr.y >> (sh + 14)) & 3) << 4);
+        m1 = ((hdr.w >> (sh + 12)) & 0xF) | (((hdr.z >> (sh + 14)) & 3) << 4);
+    }
+    const float d1 = __fmul_rn(d, (float)s0), mm1 = __fmul_rn(dmin, (float)m0);
+    const float d2 = __fmul_rn(d, (float)s1), mm2 = __fmul_rn(dmin, (float)m1);
+    const uint32_t qa = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l);
+    const uint32_t qb = *reinterpret_cast<const uint32_t *>(blk + 32 + 32 * g + l);
+    lo[0] = scale_sub4(bytes_to_float4(qa & 0x0F0F0F0Fu), d1, mm1);
+    lo[1] = scale_sub4(bytes_to_float4(qb & 0x0F0F0F0Fu), d1, mm1);
+    hi[0] = scale_sub4(bytes_to_float4((qa >> 4) & 0x0F0F0F0Fu), d2, mm2);
+    hi[1] = scale_sub4(bytes_to_float4((qb >> 4) & 0x0F0F0F0Fu), d2, mm2);
+}
+
 template <>
 __device__ __forceinline__ void decode8<AGN_Q5_K>(const uint8_t *row, int u, int, int &ea, float4 &va, int &eb, float4 &vb) {
     const uint8_t *blk = row + (u >> 5) * 176;
@@ -299,6 +352,19 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     // so decoding past row_len inside it stays in bounds; only the stores are clipped
     // K-quant units are numbered per 256-value super-block (32 units each, not in element order)
     constexpr bool K_QUANT = DTYPE == AGN_Q4_K || DTYPE == AGN_Q5_K || DTYPE == AGN_Q6_K || DTYPE == AGN_Q2_K;
+    if (DTYPE == AGN_Q4_K && VEC_OUT) {
+        const int n16 = ((row_len + 255) >> 8) * 16;
+        for (int u = threadIdx.x; u < n16; u += blockDim.x) {
+            int e;
+            float4 lo[2], hi[2];
+            decode16_q4_k(row, u, e, lo, hi);
+            if (e < row_len) ActVec<OUT>::store(o_row, e >> 2, lo[0]);
+            if (e + 16 < row_len) ActVec<OUT>::store(o_row, (e >> 2) + 4, lo[1]);
+            if (e + 32 < row_len) ActVec<OUT>::store(o_row, (e >> 2) + 8, hi[0]);
+            if (e + 48 < row_len) ActVec<OUT>::store(o_row, (e >> 2) + 12, hi[1]);
+        }
+        return;
+    }
     const int n8 = K_QUANT ? ((row_len + 255) >> 8) * 32 : (row_len + 7) >> 3;
     for (int u = threadIdx.x; u < n8; u += blockDim.x) {
         int ea, eb;
