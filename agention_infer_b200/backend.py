@@ -268,6 +268,19 @@ class CudaBackend:
                                                           row_stride, _ptr(n_valid), causal_period, causal_offset, scale))
         return out
 
+    def launch_softmax_rows_scaled_out16(self, scores, n_rows: int, row_len: int, scale: float, out_dtype: int, out=None,
+                                         sums=None, row_stride: Optional[int] = None, n_valid=None, causal_period: int = 0,
+                                         causal_offset: int = 0):
+        """The scaled softmax with the probabilities stored as f16 / bf16 (operand of a half-precision P x V)."""
+        if row_stride is None:
+            row_stride = row_len
+        if out is None:
+            out = self.empty(2 * n_rows * row_stride)
+        self._check(self._lib.agn_softmax_rows_scaled_f32_out16(self._ctx, _ptr(scores), _ptr(out), _ptr(sums), n_rows,
+                                                                row_len, row_stride, _ptr(n_valid), causal_period,
+                                                                causal_offset, scale, out_dtype))
+        return out
+
     def launch_attention_softmax(self, scores, n_heads: int, max_seq: int, pos: int, weights=None, sums=None):
         """The softmax step of `launch_attention(.., pos, n_heads, max_seq)` (resident.rs:551-565) as the reference's
         kernel leaves it: unnormalised weights [n_heads, max_seq] and sums [n_heads] over entries 0..=pos."""

@@ -23,7 +23,7 @@ namespace {
 
 struct SoftmaxArgs {
     const float *in;
-    float *out;
+    void *out;  // probabilities: float, or __half / __nv_bfloat16 (the kernels' template parameter OT)
     const int32_t *n_valid;
     float *sums;  // non-null: store the unnormalised exp(s - max) and the row sums (the reference's GPU form)
     int64_t n_rows, row_len, row_stride;
@@ -87,7 +87,7 @@ __device__ __forceinline__ float4 exp4(float4 v, float m, float coef) {
 }
 
 // Very short rows (router logits, <= 32 entries): one thread per row, everything in registers.
-template <int VPT>
+template <typename OT, int VPT>
 __global__ void __launch_bounds__(256)
 softmax_thread_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
@@ -96,7 +96,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
     const int nv = (int)valid_len(a, r);
     const int n4 = (int)(a.row_len >> 2);
     const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
-    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
     float4 v[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; k++) v[k] = k < n4 ? load_valid(in, k, nv) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
@@ -121,11 +121,11 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * k < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
             zero_tail(o, k, nv);
-            agn_st_stream(out + k, o);
+            ActVec<OT>::store(out, k, o);
         }
 }
 
-template <int VPL>
+template <typename OT, int VPL>
 __global__ void __launch_bounds__(256, 4)
 softmax_warp_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
@@ -135,7 +135,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     const int nv = (int)valid_len(a, r);
     const int n4 = (int)(a.row_len >> 2);
     const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
-    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
     float4 v[VPL];
 #pragma unroll
     for (int k = 0; k < VPL; k++) v[k] = load_valid(in, lane + 32 * k, nv);
@@ -163,12 +163,12 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
             zero_tail(o, i, nv);
-            agn_st_stream(out + i, o);
+            ActVec<OT>::store(out, i, o);
         }
     }
 }
 
-template <int VPT>
+template <typename OT, int VPT>
 __global__ void __launch_bounds__(1024)
 softmax_block_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
@@ -178,7 +178,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     const int nv = (int)valid_len(a, r);
     const int n4 = (int)(a.row_len >> 2);
     const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
-    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
     float4 v[VPT];
 #pragma unroll
     for (int k = 0; k < VPT; k++) v[k] = load_valid(in, threadIdx.x + k * blockDim.x, nv);
@@ -215,7 +215,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
             zero_tail(o, i, nv);
-            agn_st_stream(out + i, o);
+            ActVec<OT>::store(out, i, o);
         }
     }
 }
@@ -230,7 +230,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
 // Against one 1024-thread CTA per row this keeps several independent CTAs resident per SM, so
 // the loads of one row overlap the exponentials and stores of another.  Cluster barriers are
 // hardware barriers: no spin-waits.
-template <int VPT>
+template <typename OT, int VPT>
 __global__ void __launch_bounds__(512)
 softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
     agn_pdl_prologue();
@@ -243,7 +243,7 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
     const int nv = (int)valid_len(a, r);
     const int n4 = (int)(a.row_len >> 2);
     const float4 *in = reinterpret_cast<const float4 *>(a.in + r * a.row_stride);
-    float4 *out = reinterpret_cast<float4 *>(a.out + r * a.row_stride);
+    OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
     // tiles of blockDim float4 are dealt round-robin to the CTAs of the cluster, so the valid prefix
     // of a causal row is spread evenly over them
     const int base = rank * blockDim.x + threadIdx.x, step = cluster_size * blockDim.x;
@@ -304,12 +304,13 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i < nv) o = make_float4(v[k].x * f, v[k].y * f, v[k].z * f, v[k].w * f);
             zero_tail(o, i, nv);
-            agn_st_stream(out + i, o);
+            ActVec<OT>::store(out, i, o);
         }
     }
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
+template <typename OT>
 __global__ void __launch_bounds__(256)
 softmax_generic_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
@@ -318,7 +319,8 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     const int64_t r = blockIdx.x;
     const int64_t nv = valid_len(a, r);
     const float *in = a.in + r * a.row_stride;
-    float *out = a.out + r * a.row_stride;
+    OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
+    constexpr bool F32_OUT = sizeof(OT) == 4;
     float m = -INFINITY;
     for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) m = fmaxf(m, in[i]);
     m = agn_warp_max(m);
@@ -330,7 +332,10 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     float sum = 0.0f;
     for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
         const float e = expf((in[i] - m) * a.scale);
-        out[i] = e;  // in may alias out: element i is only ever touched by this thread
+        // f32 output: park e in the output row (in may alias out: element i is only ever touched
+        // by this thread); a 16-bit output row cannot hold it without rounding, so the last pass
+        // evaluates the exponential again
+        if (F32_OUT) ActVec<OT>::store1(out, i, e);
         sum += e;
     }
     sum = agn_warp_sum(sum);
@@ -340,13 +345,18 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
     for (int w = 0; w < nwarps; w++) sum += red[w];
     if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
     const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
-    for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) out[i] = i < nv ? out[i] * inv : 0.0f;
+    for (int64_t i = threadIdx.x; i < a.row_len; i += blockDim.x) {
+        float o = 0.0f;
+        if (i < nv) o = (F32_OUT ? ActVec<OT>::load1(out, i) : expf((in[i] - m) * a.scale)) * inv;
+        ActVec<OT>::store1(out, i, o);
+    }
 }
 
 }  // namespace
 
 namespace {
-int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums, int64_t n_rows, int64_t row_len,
+template <typename OT>
+int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, int64_t n_rows, int64_t row_len,
                          int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset,
                          float scale = 1.0f) {
     if (!(scale > 0.0f) || !(scale < INFINITY))
@@ -363,21 +373,21 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
     a.causal_period = causal_period; a.causal_offset = causal_offset;
     a.scale = scale;
     a.exp_coef = scale == 1.0f ? 1.4426950408889634f : (float)((double)scale * 1.4426950408889634);
-    const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned16(out);
+    const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned(out, ActVec<OT>::ALIGN);
     const int64_t n4 = row_len / 4;
     if (vec_ok && n4 <= 8) {
         const unsigned grid = (unsigned)((n_rows + 255) / 256);
-        if (n4 <= 2) agn_launch(ctx, softmax_thread_rows_kernel<2>, dim3(grid), dim3(256), 0, a);
-        else if (n4 <= 4) agn_launch(ctx, softmax_thread_rows_kernel<4>, dim3(grid), dim3(256), 0, a);
-        else agn_launch(ctx, softmax_thread_rows_kernel<8>, dim3(grid), dim3(256), 0, a);
+        if (n4 <= 2) agn_launch(ctx, softmax_thread_rows_kernel<OT, 2>, dim3(grid), dim3(256), 0, a);
+        else if (n4 <= 4) agn_launch(ctx, softmax_thread_rows_kernel<OT, 4>, dim3(grid), dim3(256), 0, a);
+        else agn_launch(ctx, softmax_thread_rows_kernel<OT, 8>, dim3(grid), dim3(256), 0, a);
         AGN_LAUNCHED(ctx, "softmax_thread_rows");
     } else if (vec_ok && n4 <= 256) {
         const int warps = 8;
         const unsigned grid = (unsigned)((n_rows + warps - 1) / warps);
-        if (n4 <= 32) agn_launch(ctx, softmax_warp_rows_kernel<1>, dim3(grid), dim3(32 * warps), 0, a);
-        else if (n4 <= 64) agn_launch(ctx, softmax_warp_rows_kernel<2>, dim3(grid), dim3(32 * warps), 0, a);
-        else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<4>, dim3(grid), dim3(32 * warps), 0, a);
-        else agn_launch(ctx, softmax_warp_rows_kernel<8>, dim3(grid), dim3(32 * warps), 0, a);
+        if (n4 <= 32) agn_launch(ctx, softmax_warp_rows_kernel<OT, 1>, dim3(grid), dim3(32 * warps), 0, a);
+        else if (n4 <= 64) agn_launch(ctx, softmax_warp_rows_kernel<OT, 2>, dim3(grid), dim3(32 * warps), 0, a);
+        else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<OT, 4>, dim3(grid), dim3(32 * warps), 0, a);
+        else agn_launch(ctx, softmax_warp_rows_kernel<OT, 8>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
     } else if (vec_ok && n4 > 4096 && ctx->tune_softmax_cluster && n_rows <= 0x7fffffffLL / 8 && n4 <= 8 * 16 * 512) {
         // 2..8 CTAs (the portable cluster limit) of <= 512 threads; 8 float4 per thread, or 16 for rows
@@ -388,9 +398,9 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
         const int cs = (int)((n4 + vpt * tmax - 1) / (vpt * tmax));
         const int threads = (int)(((n4 + vpt * cs - 1) / (vpt * cs) + 31) / 32 * 32);  // an even share, no idle tile
         if (vpt == 8)
-            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<8>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
+            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<OT, 8>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
         else
-            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<16>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
+            agn_launch_cluster(ctx, softmax_cluster_rows_kernel<OT, 16>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
         AGN_LAUNCHED(ctx, "softmax_cluster_rows");
     } else if (vec_ok && n4 <= 8192) {
         // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries
@@ -404,12 +414,12 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, float *out, float *sums,
             threads = ((threads + 31) / 32) * 32;
             while (threads > 1024) { vpt *= 2; threads = (int)(((n4 + vpt - 1) / vpt + 31) / 32 * 32); }
         }
-        if (vpt == 2) agn_launch(ctx, softmax_block_rows_kernel<2>, dim3((unsigned)n_rows), dim3(threads), 0, a);
-        else if (vpt == 4) agn_launch(ctx, softmax_block_rows_kernel<4>, dim3((unsigned)n_rows), dim3(threads), 0, a);
-        else agn_launch(ctx, softmax_block_rows_kernel<8>, dim3((unsigned)n_rows), dim3(threads), 0, a);
+        if (vpt == 2) agn_launch(ctx, softmax_block_rows_kernel<OT, 2>, dim3((unsigned)n_rows), dim3(threads), 0, a);
+        else if (vpt == 4) agn_launch(ctx, softmax_block_rows_kernel<OT, 4>, dim3((unsigned)n_rows), dim3(threads), 0, a);
+        else agn_launch(ctx, softmax_block_rows_kernel<OT, 8>, dim3((unsigned)n_rows), dim3(threads), 0, a);
         AGN_LAUNCHED(ctx, "softmax_block_rows");
     } else {
-        agn_launch(ctx, softmax_generic_rows_kernel, dim3((unsigned)n_rows), dim3(256), 0, a);
+        agn_launch(ctx, softmax_generic_rows_kernel<OT>, dim3((unsigned)n_rows), dim3(256), 0, a);
         AGN_LAUNCHED(ctx, "softmax_generic_rows");
     }
     return AGN_OK;
@@ -420,7 +430,7 @@ extern "C" int32_t agn_softmax_rows_f32(agn_ctx *ctx, const float *in, float *ou
                                         int64_t row_stride, const int32_t *n_valid, int32_t causal_period,
                                         int32_t causal_offset) {
     AGN_CHECK_CTX(ctx);
-    return softmax_dispatch(ctx, in, out, nullptr, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
+    return softmax_dispatch<float>(ctx, in, out, nullptr, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
 }
 
 // The softmax step of the reference's GPU attention exactly as its kernel leaves it
@@ -432,7 +442,7 @@ extern "C" int32_t agn_softmax_rows_unnorm_f32(agn_ctx *ctx, const float *in, fl
                                                int32_t causal_period, int32_t causal_offset) {
     AGN_CHECK_CTX(ctx);
     if (n_rows > 0 && !sums) return agn_fail(ctx, AGN_EINVAL, "softmax_rows_unnorm: null sums");
-    return softmax_dispatch(ctx, in, weights, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
+    return softmax_dispatch<float>(ctx, in, weights, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset);
 }
 
 // Softmax of scale * scores: the reference's GPU attention writes `dot * scale` with
@@ -446,5 +456,26 @@ extern "C" int32_t agn_softmax_rows_scaled_f32(agn_ctx *ctx, const float *in, fl
                                                int64_t row_len, int64_t row_stride, const int32_t *n_valid,
                                                int32_t causal_period, int32_t causal_offset, float scale) {
     AGN_CHECK_CTX(ctx);
-    return softmax_dispatch(ctx, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset, scale);
+    return softmax_dispatch<float>(ctx, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset, scale);
+}
+
+// The same with the probabilities stored as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16), round to
+// nearest even of the f32 value: the operand of a half-precision weights x V product, and two
+// thirds of a causal softmax's traffic is the output row.  The scores stay f32; sums (optional,
+// f32) as in agn_softmax_rows_scaled_f32.  out must not alias in.  No counterpart in the
+// reference, whose attention weights are f32 (src/ops/kernels_wgpu.rs:795-864).
+extern "C" int32_t agn_softmax_rows_scaled_f32_out16(agn_ctx *ctx, const float *in, void *out, float *sums, int64_t n_rows,
+                                                     int64_t row_len, int64_t row_stride, const int32_t *n_valid,
+                                                     int32_t causal_period, int32_t causal_offset, float scale,
+                                                     int32_t out_dtype) {
+    AGN_CHECK_CTX(ctx);
+    if (out == static_cast<const void *>(in) && n_rows > 0)
+        return agn_fail(ctx, AGN_EINVAL, "softmax_rows_scaled_f32_out16: a 16-bit output row cannot alias the f32 scores");
+    if (out_dtype == AGN_F16)
+        return softmax_dispatch<__half>(ctx, in, static_cast<__half *>(out), sums, n_rows, row_len, row_stride, n_valid,
+                                        causal_period, causal_offset, scale);
+    if (out_dtype == AGN_BF16)
+        return softmax_dispatch<__nv_bfloat16>(ctx, in, static_cast<__nv_bfloat16 *>(out), sums, n_rows, row_len, row_stride,
+                                               n_valid, causal_period, causal_offset, scale);
+    return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "softmax_rows_scaled_f32_out16: output type %d is neither f16 nor bf16", out_dtype);
 }

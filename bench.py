@@ -484,7 +484,8 @@ def run_ours(args, cfg, ops_list, wl):
                             "vc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
                             "kh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
                             "vh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
-                            "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev)})
+                            "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev),
+                            "pb": torch.empty(nq, Ls, Ls, dtype=torch.bfloat16, device=dev)})
         extras = {
             "add_residual_rms_norm": (lambda b: be.launch_add_residual_rms_norm(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], normed=b["nm"]),
                                       16 * T * H + 4 * H),
@@ -498,6 +499,10 @@ def run_ours(args, cfg, ops_list, wl):
                              2 * T * (4 * hd_kv + 2 * hd_kv)),
             f"softmax_causal_{nq}x{Ls}x{Ls}": (lambda b: be.launch_softmax_rows(b["sc"], nq * Ls, Ls, out=b["pr"], causal_period=Ls),
                                                4 * (nq * Ls * (Ls + 1) // 2 + nq * Ls * Ls)),
+            f"softmax_causal_scaled_out_bf16_{nq}x{Ls}x{Ls}": (
+                lambda b: be.launch_softmax_rows_scaled_out16(b["sc"], nq * Ls, Ls, float(hd) ** -0.5, AGN_BF16, out=b["pb"],
+                                                              causal_period=Ls),
+                4 * (nq * Ls * (Ls + 1) // 2) + 2 * nq * Ls * Ls),
         }
         for name, (fn, nbytes) in extras.items():
             for i in range(4):

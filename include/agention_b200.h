@@ -231,6 +231,17 @@ AGN_API int32_t agn_softmax_rows_scaled_f32(agn_ctx *ctx, const float *in, float
                                             const int32_t *n_valid, int32_t causal_period,
                                             int32_t causal_offset, float scale);
 
+/* The same with the probabilities stored as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16), the f32
+ * value rounded to nearest even: the operand of a half-precision weights x V product (two thirds
+ * of a causal softmax's traffic is the output row).  Scores and sums stay f32; row_stride counts
+ * elements of either buffer; out must not alias in (AGN_EINVAL).  No counterpart in the reference,
+ * whose attention weights are f32 (src/ops/kernels_wgpu.rs:795-864).  Any other out_dtype:
+ * AGN_EUNSUPPORTED_DTYPE. */
+AGN_API int32_t agn_softmax_rows_scaled_f32_out16(agn_ctx *ctx, const float *in, void *out, float *sums,
+                                                  int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                                  const int32_t *n_valid, int32_t causal_period,
+                                                  int32_t causal_offset, float scale, int32_t out_dtype);
+
 /* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
  * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
  * -> dequant_q8_0 / dequant_q4_k / dequant_q6_k (src/quant/q8_0.rs:14-51,

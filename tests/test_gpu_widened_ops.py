@@ -164,3 +164,42 @@ def test_sampler_softmax_with_temperature(backend, vocab):
     check_softmax(got, scaled, None, orc.softmax_rows(scaled, None, THREADS))
     assert np.all(np.abs(got.sum(axis=1, dtype=np.float64) - 1.0) < 1e-4)
     assert np.array_equal(got.argmax(axis=1), logits.argmax(axis=1))
+
+
+@pytest.mark.parametrize("out_dtype", [AGN_F16, AGN_BF16])
+@pytest.mark.parametrize("R,L,causal", [(64, 8, 0), (96, 200, 1), (512, 512, 1), (64, 4096, 1), (6, 9999, 0), (4, 20000, 1)])
+def test_softmax_with_16bit_probabilities(backend, R, L, causal, out_dtype):
+    """Every kernel family (thread, warp, CTA, scalar fallback, cluster): the 16-bit row is the f32
+    entry point's own output rounded to nearest even."""
+    s = synth.activations(1, "scores", (R, L), std=2.0 * 8.0)
+    scale = 0.125
+    ds = backend.upload(s)
+    kw = dict(causal_period=min(R, L) if causal else 0, causal_offset=L - min(R, L) if causal else 0)
+    f32_gpu = backend.read(backend.launch_softmax_rows_scaled(ds, R, L, scale, **kw), np.float32, (R, L))
+    sums16 = backend.empty(4 * R)
+    out = backend.launch_softmax_rows_scaled_out16(ds, R, L, scale, out_dtype, **kw)
+    if out_dtype == AGN_F16:
+        got = backend.read(out, np.float16, (R, L))
+        assert np.array_equal(got.view(np.uint16), f32_gpu.astype(np.float16).view(np.uint16))
+    else:
+        assert np.array_equal(backend.read(out, np.uint16, (R, L)), to_bf16_bits(f32_gpu))
+    # unnormalised weights in 16 bits + f32 sums
+    w32 = backend.empty(4 * R * L); s32 = backend.empty(4 * R)
+    backend.launch_softmax_rows_scaled(ds, R, L, scale, out=w32, sums=s32, **kw)
+    w16 = backend.launch_softmax_rows_scaled_out16(ds, R, L, scale, out_dtype, sums=sums16, **kw)
+    assert np.array_equal(backend.read(sums16, np.float32, (R,)).view(np.uint32), backend.read(s32, np.float32, (R,)).view(np.uint32))
+    ref_w = backend.read(w32, np.float32, (R, L))
+    if out_dtype == AGN_F16:
+        assert np.array_equal(backend.read(w16, np.float16, (R, L)).view(np.uint16), ref_w.astype(np.float16).view(np.uint16))
+    else:
+        assert np.array_equal(backend.read(w16, np.uint16, (R, L)), to_bf16_bits(ref_w))
+
+
+def test_softmax_16bit_output_argument_errors(backend):
+    s = backend.upload(np.zeros((2, 8), np.float32))
+    with pytest.raises(BackendError) as e:
+        backend.launch_softmax_rows_scaled_out16(s, 2, 8, 1.0, AGN_Q8_0)
+    assert e.value.status == 2
+    with pytest.raises(BackendError) as e:
+        backend.launch_softmax_rows_scaled_out16(s, 2, 8, 1.0, AGN_F16, out=s)
+    assert e.value.status == 1
