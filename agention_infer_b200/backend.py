@@ -364,6 +364,13 @@ class CudaBackend:
         self._check(self._lib.agn_rms_norm_f16(self._ctx, _ptr(x), _ptr(w), _ptr(out), T, H, eps))
         return out
 
+    def launch_silu_mul_out16(self, gate, up, n: int, out_dtype: int, out=None):
+        """f32 gate / up in, silu(gate) * up stored as f16 / bf16 (operand of a half-precision down projection)."""
+        if out is None:
+            out = self.empty(2 * n)
+        self._check(self._lib.agn_silu_mul_f32_out16(self._ctx, _ptr(gate), _ptr(up), _ptr(out), n, out_dtype))
+        return out
+
     def launch_rms_norm_out16(self, x, w, T: int, H: int, eps: float, out_dtype: int, out=None):
         """f32 rows in, normed rows out as f16 / bf16 (the operand of a half-precision matmul)."""
         if out is None:

@@ -26,9 +26,11 @@ __device__ __forceinline__ float4 silu_mul4(float4 g, float4 u) {
 // Each CTA owns a contiguous tile of UNROLL * blockDim vectors of four activations; a thread
 // issues all of its 2*UNROLL loads before the first use so that UNROLL*32 B (f32) per thread
 // are in flight.
-template <typename T, int UNROLL>
+// T: storage type of gate and up; OT: storage type of the result (T, or a 16-bit type when the
+// product feeds a matmul with half-precision operands).
+template <typename T, typename OT, int UNROLL>
 __global__ void __launch_bounds__(512)
-silu_mul_vec4_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ out, int64_t n4) {
+silu_mul_vec4_kernel(const T *__restrict__ gate, const T *__restrict__ up, OT *__restrict__ out, int64_t n4) {
     agn_pdl_prologue();
     const int64_t tile = (int64_t)blockIdx.x * (UNROLL * blockDim.x);
     float4 g[UNROLL], u[UNROLL];
@@ -43,7 +45,7 @@ silu_mul_vec4_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__
 #pragma unroll
     for (int k = 0; k < UNROLL; k++) {
         const int64_t i = tile + k * blockDim.x + threadIdx.x;
-        if (i < n4) ActVec<T>::store(out, i, silu_mul4(g[k], u[k]));
+        if (i < n4) ActVec<OT>::store(out, i, silu_mul4(g[k], u[k]));
     }
 }
 
@@ -90,16 +92,16 @@ silu_mul_h8_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
 }
 
 // Tail (n % 4 elements) and unaligned buffers.
-template <typename T>
-__global__ void silu_mul_scalar_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ out,
+template <typename T, typename OT>
+__global__ void silu_mul_scalar_kernel(const T *__restrict__ gate, const T *__restrict__ up, OT *__restrict__ out,
                                        int64_t begin, int64_t n) {
     agn_pdl_prologue();
     const int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) ActVec<T>::store1(out, i, silu_mul1(ActVec<T>::load1(gate, i), ActVec<T>::load1(up, i)));
+    if (i < n) ActVec<OT>::store1(out, i, silu_mul1(ActVec<T>::load1(gate, i), ActVec<T>::load1(up, i)));
 }
 
-template <typename T>
-int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, T *out, int64_t n) {
+template <typename T, typename OT>
+int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, OT *out, int64_t n) {
     if (n < 0) return agn_fail(ctx, AGN_EINVAL, "silu_mul: n=%lld < 0", (long long)n);
     if (n == 0) return AGN_OK;
     if (!gate || !up || !out) return agn_fail(ctx, AGN_EINVAL, "silu_mul: null pointer");
@@ -107,15 +109,15 @@ int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, T *out, int6
     const int THREADS = ctx->tune_silu_threads, UNROLL = ctx->tune_silu_unroll;
     constexpr int A = ActVec<T>::ALIGN;
     int64_t done = 0;
-    if (agn_aligned(gate, A) && agn_aligned(up, A) && agn_aligned(out, A)) {
+    if (agn_aligned(gate, A) && agn_aligned(up, A) && agn_aligned(out, ActVec<OT>::ALIGN)) {
         const int64_t n4 = n / 4;
         if (n4 > 0) {
             const int64_t per_cta = (int64_t)THREADS * UNROLL;
             const int64_t blocks = (n4 + per_cta - 1) / per_cta;
             if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: n too large");
-            if (UNROLL == 2) agn_launch(ctx, silu_mul_vec4_kernel<T, 2>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
-            else if (UNROLL == 8) agn_launch(ctx, silu_mul_vec4_kernel<T, 8>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
-            else agn_launch(ctx, silu_mul_vec4_kernel<T, 4>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
+            if (UNROLL == 2) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 2>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
+            else if (UNROLL == 8) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 8>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
+            else agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 4>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
             AGN_LAUNCHED(ctx, "silu_mul_vec4");
         }
         done = n4 * 4;
@@ -124,7 +126,7 @@ int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, T *out, int6
         const int64_t rest = n - done;
         const int64_t blocks = (rest + THREADS - 1) / THREADS;
         if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: unaligned n too large");
-        agn_launch(ctx, silu_mul_scalar_kernel<T>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, done, n);
+        agn_launch(ctx, silu_mul_scalar_kernel<T, OT>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, done, n);
         AGN_LAUNCHED(ctx, "silu_mul_scalar");
     }
     return AGN_OK;
@@ -134,7 +136,7 @@ int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, T *out, int6
 
 extern "C" int32_t agn_silu_mul_f32(agn_ctx *ctx, const float *gate, const float *up, float *out, int64_t n) {
     AGN_CHECK_CTX(ctx);
-    return silu_mul_dispatch<float>(ctx, gate, up, out, n);
+    return silu_mul_dispatch<float, float>(ctx, gate, up, out, n);
 }
 
 // f16 activation storage, f32 arithmetic: the reference's GPU `silu_mul` with `Act = f16`
@@ -160,5 +162,18 @@ extern "C" int32_t agn_silu_mul_f16(agn_ctx *ctx, const void *gate, const void *
     }
     if (done == n) return AGN_OK;
     // the remainder (and unaligned buffers) through the generic kernels
-    return silu_mul_dispatch<__half>(ctx, g + done, u + done, o + done, n - done);
+    return silu_mul_dispatch<__half, __half>(ctx, g + done, u + done, o + done, n - done);
+}
+
+// f32 gate and up in, the product stored as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16): the f32
+// result of agn_silu_mul_f32 rounded to nearest even, i.e. the operand the down projection takes
+// when it runs in half precision (10 instead of 12 bytes per element on the kernel that dominates
+// the layer's elementwise time).  No counterpart in the reference, whose `silu_mul` reads and
+// writes the same `Act` type (src/ops/kernels_wgpu.rs:22-31).
+extern "C" int32_t agn_silu_mul_f32_out16(agn_ctx *ctx, const float *gate, const float *up, void *out, int64_t n,
+                                          int32_t out_dtype) {
+    AGN_CHECK_CTX(ctx);
+    if (out_dtype == AGN_F16) return silu_mul_dispatch<float, __half>(ctx, gate, up, static_cast<__half *>(out), n);
+    if (out_dtype == AGN_BF16) return silu_mul_dispatch<float, __nv_bfloat16>(ctx, gate, up, static_cast<__nv_bfloat16 *>(out), n);
+    return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "silu_mul_f32_out16: output type %d is neither f16 nor bf16", out_dtype);
 }

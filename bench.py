@@ -485,10 +485,13 @@ def run_ours(args, cfg, ops_list, wl):
                             "kh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
                             "vh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
                             "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev),
-                            "pb": torch.empty(nq, Ls, Ls, dtype=torch.bfloat16, device=dev)})
+                            "pb": torch.empty(nq, Ls, Ls, dtype=torch.bfloat16, device=dev),
+                            "ab": torch.empty(R, I, dtype=torch.bfloat16, device=dev),
+                            "g": sets[s_]["gate"], "u": sets[s_]["up"]})
         extras = {
             "add_residual_rms_norm": (lambda b: be.launch_add_residual_rms_norm(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], normed=b["nm"]),
                                       16 * T * H + 4 * H),
+            "silu_mul_out_bf16": (lambda b: be.launch_silu_mul_out16(b["g"], b["u"], R * I, AGN_BF16, out=b["ab"]), 10 * R * I),
             "rms_norm_out_bf16": (lambda b: be.launch_rms_norm_out16(b["x"], w, T, H, cfg.eps, AGN_BF16, out=b["nb"]), 6 * T * H + 4 * H),
             "add_residual_rms_norm_out_bf16": (lambda b: be.launch_add_residual_rms_norm_out16(b["x"], b["d"], w, T, H, cfg.eps, AGN_BF16,
                                                                                                 new_x=b["nx"], normed=b["nb"]),

@@ -311,13 +311,19 @@ AGN_API int32_t agn_rms_norm_f16(agn_ctx *ctx, const void *x, const float *w, vo
 AGN_API int32_t agn_add_residual_rms_norm_f16(agn_ctx *ctx, const void *x, const void *delta,
                                               const float *w, void *new_x, void *normed, int64_t T,
                                               int64_t H, float eps);
-/* f32 rows in, the NORMED row out as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16): the f32
+/* f32 in, 16-bit out.  agn_silu_mul_f32_out16: the f32 result of agn_silu_mul_f32 rounded to
+ * nearest even and stored as f16 / bf16, the operand of a half-precision down projection (10
+ * instead of 12 bytes per element); no counterpart in the reference, whose `silu_mul` keeps the
+ * `Act` type (src/ops/kernels_wgpu.rs:22-31).
+ * The norms: f32 rows in, the NORMED row out as f16 (out_dtype = AGN_F16) or bf16 (AGN_BF16): the f32
  * result of agn_rms_norm_f32 / agn_add_residual_rms_norm_f32 rounded to nearest even on store,
  * i.e. the operand a half-precision matmul takes, without an f32 row and a cast pass in
  * between (6 instead of 8 bytes per element, 14 instead of 16 for the residual form).  new_x,
  * the residual stream, stays f32.  No counterpart in the reference, whose norm kernels read and
  * write the same `Act` type (src/ops/kernels_wgpu.rs:79-163).  Any other out_dtype:
  * AGN_EUNSUPPORTED_DTYPE. */
+AGN_API int32_t agn_silu_mul_f32_out16(agn_ctx *ctx, const float *gate, const float *up, void *out,
+                                       int64_t n, int32_t out_dtype);
 AGN_API int32_t agn_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *w, void *out,
                                        int64_t T, int64_t H, float eps, int32_t out_dtype);
 AGN_API int32_t agn_add_residual_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *delta,

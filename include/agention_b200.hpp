@@ -166,6 +166,11 @@ class CudaBackend {
         check(agn_rms_norm_f16(ctx_, x, w, out.ptr(), T, H, eps));
         return out;
     }
+    DeviceBuffer launch_silu_mul_out16(const float *gate, const float *up, int64_t n, int out_dtype) {
+        DeviceBuffer out = empty(2 * (size_t)n);
+        check(agn_silu_mul_f32_out16(ctx_, gate, up, out.ptr(), n, out_dtype));
+        return out;
+    }
     // f32 rows in, normed rows out as f16 / bf16 (out_dtype = AGN_F16 | AGN_BF16)
     DeviceBuffer launch_rms_norm_out16(const float *x, const float *w, int64_t T, int64_t H, float eps, int out_dtype) {
         DeviceBuffer out = empty(2 * (size_t)(T * H));

@@ -203,3 +203,21 @@ def test_softmax_16bit_output_argument_errors(backend):
     with pytest.raises(BackendError) as e:
         backend.launch_softmax_rows_scaled_out16(s, 2, 8, 1.0, AGN_F16, out=s)
     assert e.value.status == 1
+
+
+@pytest.mark.parametrize("out_dtype", [AGN_F16, AGN_BF16])
+@pytest.mark.parametrize("n", [4096 * 18944 // 8, 4096 * 3 + 1, 7, 1])
+def test_silu_mul_f32_to_16bit_output(backend, n, out_dtype):
+    g, u = synth.activations(2, "gate", (n,)), synth.activations(2, "up", (n,))
+    ref = orc.silu_mul(g, u, THREADS)
+    dg, du = backend.upload(g), backend.upload(u)
+    f32_gpu = backend.read(backend.launch_silu_mul(dg, du, n), np.float32, (n,))
+    out = backend.launch_silu_mul_out16(dg, du, n, out_dtype)
+    if out_dtype == AGN_F16:
+        got = backend.read(out, np.float16, (n,))
+        assert np.array_equal(got.view(np.uint16), f32_gpu.astype(np.float16).view(np.uint16))
+        assert np.max(np.abs(got.astype(np.float32) - ref) / np.maximum(np.abs(ref), 1.0)) <= 2.0 ** -10
+    else:
+        got = backend.read(out, np.uint16, (n,))
+        assert np.array_equal(got, to_bf16_bits(f32_gpu))
+        assert np.max(np.abs(from_bf16_bits(got) - ref) / np.maximum(np.abs(ref), 1.0)) <= 2.0 ** -7
