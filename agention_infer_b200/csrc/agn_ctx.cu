@@ -65,6 +65,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_get_rows_threads = 0;
     ctx->tune_softmax_vpt = 0;
     ctx->tune_softmax_cluster = 1;
+    ctx->tune_moe_small_sort = 1;
     ctx->tune_get_rows_tma = 1;
     ctx->tune_silu_unroll = 4;
     ctx->tune_silu_threads = 256;
@@ -142,6 +143,10 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     }
     if (strcmp(name, "silu_threads") == 0 && (value == 128 || value == 256 || value == 512)) {
         ctx->tune_silu_threads = (int)value;
+        return AGN_OK;
+    }
+    if (strcmp(name, "moe_small_sort") == 0) {
+        ctx->tune_moe_small_sort = value != 0;
         return AGN_OK;
     }
     if (strcmp(name, "softmax_cluster") == 0) {

@@ -126,6 +126,86 @@ expert_place_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, con
     }
 }
 
+// Up to SMALL_SORT_PAIRS pairs (decode and small prefill batches): the whole counting sort in ONE
+// CTA and one launch (count, scan and place of the three-kernel path, plus the -1 fill of the slots
+// that dropped pairs leave empty).  At this size three dependent launches and a memset cost more
+// in launch latency than the sort itself (T = 64: 17.4 -> 9.3 us for sort + copy; T = 2048: 27.4 ->
+// 22.9 us); from 8192 tokens on, one CTA is slower than the three grids (94 vs 90 us).  Warp w owns the contiguous segment
+// [w * seg, (w + 1) * seg) of the pairs, so "warp order, then iteration order, then lane order" is
+// pair order and the sort is stable.
+constexpr int SMALL_SORT_PAIRS = 4096;
+constexpr int SMALL_SORT_WARPS = 32;
+
+__global__ void __launch_bounds__(SMALL_SORT_WARPS * 32)
+expert_sort_small_kernel(const int32_t *__restrict__ idx, int n_pairs, int E, int32_t *__restrict__ offsets,
+                         int32_t *__restrict__ src_token, int32_t *__restrict__ src_slot, uint32_t *flags) {
+    agn_pdl_prologue();
+    __shared__ int base[SMALL_SORT_WARPS][MAX_EXPERTS];  // counts, then running destination of (warp, expert)
+    __shared__ int total[MAX_EXPERTS + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < SMALL_SORT_WARPS * MAX_EXPERTS; k += blockDim.x) (&base[0][0])[k] = 0;
+    __syncthreads();
+    const int seg = ((n_pairs + SMALL_SORT_WARPS - 1) / SMALL_SORT_WARPS + 31) & ~31;  // a multiple of the warp size
+    const int begin = warp * seg, end = min(begin + seg, n_pairs);
+    bool bad = false;
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        const int i = i0 + lane;
+        int e = -1;
+        if (i < end) {
+            e = idx[i];
+            if (e < 0 || e >= E) { e = -1; bad = true; }
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) base[warp][e] += __popc(same);  // one lane per expert present
+        __syncwarp();
+    }
+    if (bad) atomicOr(flags, AGN_FLAG_OOB_ID);
+    __syncthreads();
+    if (threadIdx.x < E) {  // exclusive scan over the warps of one expert
+        const int e = threadIdx.x;
+        int run = 0;
+        for (int w = 0; w < SMALL_SORT_WARPS; w++) {
+            const int v = base[w][e];
+            base[w][e] = run;
+            run += v;
+        }
+        total[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int k = 0; k < E; k++) {
+            const int v = total[k];
+            total[k] = run;
+            offsets[k] = run;
+            run += v;
+        }
+        total[E] = run;
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        const int i = i0 + lane;
+        int e = -1;
+        if (i < end) {
+            e = idx[i];  // second touch: an L1 / L2 hit
+            if (e < 0 || e >= E) e = -1;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        if (e >= 0) {
+            const int dst = total[e] + base[warp][e] + rank;
+            src_token[dst] = i >> 1;
+            src_slot[dst] = i & 1;
+        }
+        __syncwarp();
+        if (e >= 0 && rank == 0) base[warp][e] += __popc(same);
+        __syncwarp();
+    }
+    // slots past the last placed pair belong to dropped pairs (expert out of range): mark them empty
+    for (int k = total[E] + threadIdx.x; k < n_pairs; k += blockDim.x) src_token[k] = -1;
+}
+
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float *__restrict__ x, const int32_t *__restrict__ src_token, int64_t n_out, int64_t T,
                    int64_t H, float *__restrict__ out, int vec) {
@@ -169,6 +249,16 @@ int32_t agn_gather_rows_by_expert_impl(agn_ctx *ctx, const float *x, const int32
                                        int32_t *src_slot, int32_t *scratch) {
     const int64_t n_pairs = 2 * T;
     const int n_chunks = (int)((n_pairs + CHUNK - 1) / CHUNK);
+    const int vec = (H % 4 == 0 && agn_aligned16(x) && agn_aligned16(out)) ? 1 : 0;
+    if (n_pairs <= SMALL_SORT_PAIRS && ctx->tune_moe_small_sort) {
+        agn_launch(ctx, expert_sort_small_kernel, dim3(1), dim3(SMALL_SORT_WARPS * 32), 0, idx, (int)n_pairs, n_experts, offsets,
+                   src_token, src_slot, ctx->d_flags);
+        AGN_LAUNCHED(ctx, "expert_sort_small");
+        agn_launch(ctx, gather_rows_kernel, dim3((unsigned)n_pairs), dim3(256), 0, x, src_token, n_pairs, T, H, out, vec);
+        AGN_LAUNCHED(ctx, "gather_rows");
+        ctx->flags_dirty = true;
+        return AGN_OK;
+    }
     // pairs with an out-of-range expert are skipped by `place`; mark their slots as empty
     AGN_CUDA(ctx, cudaMemsetAsync(src_token, 0xFF, sizeof(int32_t) * (size_t)n_pairs, ctx->stream));
     agn_launch(ctx, expert_count_kernel, dim3(n_chunks), dim3(CHUNK), 0, idx, n_pairs, n_experts, scratch, ctx->d_flags);
@@ -177,7 +267,6 @@ int32_t agn_gather_rows_by_expert_impl(agn_ctx *ctx, const float *x, const int32
     AGN_LAUNCHED(ctx, "expert_scan");
     agn_launch(ctx, expert_place_kernel, dim3(n_chunks), dim3(CHUNK), 0, idx, n_pairs, n_experts, scratch, src_token, src_slot);
     AGN_LAUNCHED(ctx, "expert_place");
-    const int vec = (H % 4 == 0 && agn_aligned16(x) && agn_aligned16(out)) ? 1 : 0;
     agn_launch(ctx, gather_rows_kernel, dim3((unsigned)n_pairs), dim3(256), 0, x, src_token, n_pairs, T, H, out, vec);
     AGN_LAUNCHED(ctx, "gather_rows");
     ctx->flags_dirty = true;

@@ -100,7 +100,8 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
  * "silu_threads" (128, 256, 512), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more
  * than 16384 entries: 1 = one thread-block cluster per row, 2 = the same with smaller CTAs, 0 = one
  * CTA per row), "get_rows_tma" (1: bulk-copy staging, 0: cp.async), "get_rows_threads" (32..256;
- * 0 = automatic).  An unknown name is AGN_EINVAL. */
+ * 0 = automatic), "moe_small_sort" (1: up to 4096 (token, slot) pairs are sorted by one CTA in one
+ * launch, 0: always the three-kernel counting sort).  An unknown name is AGN_EINVAL. */
 AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value);
 /* Launches one empty kernel: the per-launch floor for launch-bound (decode-shaped) timings,
  * the counterpart of the reference's "dispatch floor" probe

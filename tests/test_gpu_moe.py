@@ -22,14 +22,21 @@ def test_router_top2(backend, T, E):
     assert synth.max_rel_to_row_scale(backend.read(w, np.float32, (T, 2)), ref_w) <= TOL
 
 
-@pytest.mark.parametrize("T,H,E", [(8192, 4096, 8), (1, 64, 8), (1000, 130, 4), (513, 256, 64), (2048, 100, 3)])
-def test_gather_rows_by_expert(backend, T, H, E):
+@pytest.mark.parametrize("small_sort", [1, 0])
+@pytest.mark.parametrize("T,H,E", [(8192, 4096, 8), (1, 64, 8), (1000, 130, 4), (513, 256, 64), (2048, 100, 3), (2049, 64, 8),
+                                   (16385, 64, 8), (17, 32, 1), (40000, 32, 16), (2048, 64, 64), (33, 16, 5)])
+def test_gather_rows_by_expert(backend, T, H, E, small_sort):
+    """Both sorts: one CTA for up to 4096 pairs (T <= 2048), three kernels beyond or with the option off."""
     x = synth.activations(5, "x", (T, H))
     logits = synth.activations(5, "logits", (T, max(E, 2)))
     idx, _ = orc.router_top2(logits)
     idx = np.ascontiguousarray(idx % E)
     ref_out, ref_off, ref_tok, ref_slot = orc.gather_rows_by_expert(x, idx, E)
-    out, off, tok, slot = backend.gather_rows_by_expert(backend.upload(x), backend.upload(idx), T, H, E)
+    backend.set_option("moe_small_sort", small_sort)
+    try:
+        out, off, tok, slot = backend.gather_rows_by_expert(backend.upload(x), backend.upload(idx), T, H, E)
+    finally:
+        backend.set_option("moe_small_sort", 1)
     assert np.array_equal(backend.read(off, np.int32, (E + 1,)), ref_off)
     assert np.array_equal(backend.read(tok, np.int32, (2 * T,)), ref_tok)
     assert np.array_equal(backend.read(slot, np.int32, (2 * T,)), ref_slot)
@@ -58,15 +65,25 @@ def test_per_expert_silu_over_routed_rows(backend):
     assert synth.max_rel_to_row_scale(backend.read(out, np.float32, (2 * T, I)), orc.silu_mul(gate, up)) <= TOL
 
 
-def test_gather_bad_expert_index_is_reported(backend):
+@pytest.mark.parametrize("small_sort", [1, 0])
+def test_gather_bad_expert_index_is_reported(backend, small_sort):
     T, H, E = 40, 32, 4
     x = synth.activations(5, "x", (T, H))
-    idx = np.zeros((T, 2), np.int32); idx[:, 1] = 1; idx[7, 0] = 9
-    backend.gather_rows_by_expert(backend.upload(x), backend.upload(idx), T, H, E)
+    idx = np.zeros((T, 2), np.int32); idx[:, 1] = 1; idx[7, 0] = 9; idx[20, 1] = -3
+    backend.set_option("moe_small_sort", small_sort)
+    try:
+        out, off, tok, slot = backend.gather_rows_by_expert(backend.upload(x), backend.upload(idx), T, H, E)
+    finally:
+        backend.set_option("moe_small_sort", 1)
     with pytest.raises(BackendError) as e:
         backend.sync()
     assert e.value.status == 4
     backend.sync()
+    # the two bad pairs are dropped: 78 rows placed, the last two slots marked empty, the rest in order
+    tok_h = backend.read(tok, np.int32, (2 * T,))
+    assert backend.read(off, np.int32, (E + 1,)).tolist() == [0, 39, 78, 78, 78]
+    assert tok_h[78:].tolist() == [-1, -1]
+    assert tok_h[:39].tolist() == [t for t in range(T) if t != 7] and tok_h[39:78].tolist() == [t for t in range(T) if t != 20]
 
 
 def test_moe_argument_errors(backend):
