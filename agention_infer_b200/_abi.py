@@ -86,6 +86,7 @@ SIGNATURES = {
                                        _f32, _i32]),
     "agn_get_rows_f16": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_host_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "agn_host_add_residual_rms_norm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_host_silu_mul_f32": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_host_rope_qk_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),
     "agn_host_qk_norm_rope_qk_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32,

@@ -428,6 +428,12 @@ class CudaBackend:
         self._check(self._lib.agn_host_rms_norm_f32(self._ctx, self._h(x, np.float32), _ptr(w_dev),
                                                     self._h(out, np.float32), T, H, eps))
 
+    def add_residual_rms_norm_into(self, x: np.ndarray, delta: np.ndarray, w_dev, normed: np.ndarray, eps: float) -> None:
+        """`x += delta` (cpu_path.rs:785-787) then `rms_norm_into(x, weight, normed)` (:790); host x is updated in place."""
+        T, H = x.shape
+        self._check(self._lib.agn_host_add_residual_rms_norm_f32(self._ctx, self._h(x, np.float32), self._h(delta, np.float32),
+                                                                 _ptr(w_dev), self._h(normed, np.float32), T, H, eps))
+
     def silu_mul_into(self, gate: np.ndarray, up: np.ndarray, out: np.ndarray) -> None:
         """The batched silu-combine loop (cpu_path.rs:975-978) on host arrays; out may be gate."""
         self._check(self._lib.agn_host_silu_mul_f32(self._ctx, self._h(gate, np.float32), self._h(up, np.float32),

@@ -205,6 +205,22 @@ int32_t agn_host_rms_norm_f32(agn_ctx *ctx, const float *x_host, const float *w_
     });
 }
 
+// The residual loop `x[i] += delta[i]` (src/model/llama/cpu_path.rs:785-787) followed by
+// `rms_norm_into(x, w, normed)` (:790): x_host is updated in place, like the CPU path's x.
+int32_t agn_host_add_residual_rms_norm_f32(agn_ctx *ctx, float *x_host, const float *delta_host, const float *w_dev,
+                                           float *normed_host, int64_t T, int64_t H, float eps) {
+    AGN_CHECK_CTX(ctx);
+    if (T < 0 || H <= 0) return agn_fail(ctx, AGN_EINVAL, "host_add_residual_rms_norm: T=%lld H=%lld", (long long)T, (long long)H);
+    if (T > 0 && (!x_host || !delta_host || !w_dev || !normed_host))
+        return agn_fail(ctx, AGN_EINVAL, "host_add_residual_rms_norm: null pointer");
+    const HostBuf bufs[3] = {{x_host, x_host, sizeof(float) * (size_t)H}, {delta_host, nullptr, sizeof(float) * (size_t)H},
+                             {nullptr, normed_host, sizeof(float) * (size_t)H}};
+    return run_pipelined(ctx, "host_add_residual_rms_norm", T, bufs, 3, [&](int64_t rows, void **d, int64_t) {
+        return agn_add_residual_rms_norm_f32(ctx, (const float *)d[0], (const float *)d[1], w_dev, (float *)d[0], (float *)d[2],
+                                             rows, H, eps);
+    });
+}
+
 int32_t agn_host_silu_mul_f32(agn_ctx *ctx, const float *gate_host, const float *up_host, float *out_host, int64_t n) {
     AGN_CHECK_CTX(ctx);
     if (n < 0) return agn_fail(ctx, AGN_EINVAL, "host_silu_mul: n=%lld", (long long)n);

@@ -358,6 +358,11 @@ AGN_API int32_t agn_get_rows_f16(agn_ctx *ctx, int32_t dtype, const void *table,
  * before it.  Arguments otherwise as in the device-pointer entry points. */
 AGN_API int32_t agn_host_rms_norm_f32(agn_ctx *ctx, const float *x_host, const float *w_dev,
                                       float *out_host, int64_t T, int64_t H, float eps);
+/* x_host += delta_host in place (the residual loop, cpu_path.rs:785-787), then the norm of the
+ * sum into normed_host (:790). */
+AGN_API int32_t agn_host_add_residual_rms_norm_f32(agn_ctx *ctx, float *x_host, const float *delta_host,
+                                                   const float *w_dev, float *normed_host, int64_t T,
+                                                   int64_t H, float eps);
 AGN_API int32_t agn_host_silu_mul_f32(agn_ctx *ctx, const float *gate_host, const float *up_host,
                                       float *out_host, int64_t n);
 /* In place on q_host / k_host; pos_host may be NULL (positions pos_start + t). */

@@ -217,6 +217,10 @@ class CudaBackend {
     void rms_norm_into(const float *x_host, const float *w_dev, float *out_host, int64_t T, int64_t H, float eps) {
         check(agn_host_rms_norm_f32(ctx_, x_host, w_dev, out_host, T, H, eps));
     }
+    void add_residual_rms_norm_into(float *x_host, const float *delta_host, const float *w_dev, float *normed_host, int64_t T,
+                                    int64_t H, float eps) {  // x += delta (cpu_path.rs:785-787), then the norm (:790)
+        check(agn_host_add_residual_rms_norm_f32(ctx_, x_host, delta_host, w_dev, normed_host, T, H, eps));
+    }
     void silu_mul_into(const float *gate_host, const float *up_host, float *out_host, int64_t n) {
         check(agn_host_silu_mul_f32(ctx_, gate_host, up_host, out_host, n));
     }

@@ -27,6 +27,16 @@ def test_host_rms_norm_pageable_and_pinned(backend):
     backend.free_pinned(px); backend.free_pinned(po)
 
 
+def test_host_add_residual_rms_norm_updates_x_in_place(backend):
+    T, H = 3000, 4096  # 147 MB over the three buffers
+    x = synth.activations(4, "x", (T, H)); d = synth.activations(4, "delta", (T, H)); w = synth.norm_weight(4, "w", H)
+    ref_x, ref_n = orc.add_residual_rms_norm_rows(x, d, w, 1e-5, THREADS)
+    hx = x.copy(); normed = np.empty_like(x)
+    backend.add_residual_rms_norm_into(hx, d, backend.upload(w), normed, 1e-5); backend.sync()
+    assert np.array_equal(hx.view(np.uint32), ref_x.view(np.uint32))  # the sum is exact
+    assert synth.max_rel_to_row_scale(normed, ref_n) <= TOL
+
+
 def test_host_silu_mul_with_tail_and_in_place(backend):
     n = 4096 * 3000 + 123
     g = synth.activations(2, "gate", (n,)); u = synth.activations(2, "up", (n,))
