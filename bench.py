@@ -46,11 +46,12 @@ def measured_peaks():
 
 
 def silu_traffic_bytes(n_elements):
-    """DRAM bytes of one silu_mul launch, scaled from an ncu capture of this kernel on 2048 rows
-    (summarised with the other hot kernels under profiles/; 38,797,312 elements: dram read 310.4 MB = 8.00 B per
-    element, i.e. no re-reads; of the 155.2 MB written, 43.5 MB were still dirty in L2 when the kernel
-    ended).  Reads and writes scale with the element count; the dirty remainder does not."""
-    dirty_left = 43.5e6
+    """DRAM bytes of one silu_mul launch (dram__bytes_read.sum + dram__bytes_write.sum), from one-pass ncu
+    captures of this kernel summarised under profiles/: at the headline size (4096 rows, 77,594,624 elements)
+    620.8 MB read = 8.00 B per element, i.e. no re-reads, and 262.4 MB of the 310.4 MB written, the other 48 MB
+    still dirty in L2 when the kernel ends (43.5 MB at 2048 rows).  Other sizes: reads and writes scale with the
+    element count, the dirty remainder does not."""
+    dirty_left = 48.0e6
     return 8.0 * n_elements + max(4.0 * n_elements - dirty_left, 0.0)
 
 
