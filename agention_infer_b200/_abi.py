@@ -75,6 +75,8 @@ SIGNATURES = {
     "agn_gather_rows_by_expert_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp]),
     "agn_silu_mul_f16": (_i32, [_vp, _vp, _vp, _vp, _i64]),
     "agn_softmax_rows_scaled_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32, _f32]),
+    "agn_qk_norm_rope_kv_write_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32, _f32, _f32,
+                                             _i32, _i32, _vp, _vp, _i64]),
     "agn_softmax_rows_scaled_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32, _f32, _i32]),
     "agn_silu_mul_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32]),
     "agn_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),

@@ -310,6 +310,16 @@ class CudaBackend:
         self._check(self._lib.agn_kv_write_f32(self._ctx, kv_dtype, _ptr(k), _ptr(v), _ptr(k_cache), _ptr(v_cache), T,
                                                head_dim_kv, _ptr(pos), pos_start, max_seq_len))
 
+    def launch_qk_norm_rope_kv_write(self, q, k, v, wq, wk, T: int, n_q_heads: int, n_kv_heads: int, head_dim: int, eps: float,
+                                     n_rot: int, pos, theta: float, kv_dtype: int, k_cache, v_cache, max_seq_len: int,
+                                     freq_scale: float = 1.0, layout: int = AGN_ROPE_NEOX, pos_start: int = 0) -> None:
+        """QK-norm -> RoPE of q and k in place (wq = wk = None: rope only) and the cache write of the rotated k and of v,
+        one launch: `launch_qk_norm_rope` x 2 + `kv_cache_write` of the reference's per-layer sequence."""
+        self._check(self._lib.agn_qk_norm_rope_kv_write_f32(self._ctx, _ptr(q), _ptr(k), _ptr(v), _ptr(wq), _ptr(wk), T,
+                                                            n_q_heads, n_kv_heads, head_dim, eps, n_rot, _ptr(pos), pos_start,
+                                                            theta, freq_scale, layout, kv_dtype, _ptr(k_cache), _ptr(v_cache),
+                                                            max_seq_len))
+
     def kv_read(self, kv_dtype: int, k_cache, v_cache, n_pos: int, head_dim_kv: int, k_out=None, v_out=None):
         """`KvCache::read_up_to(layer, pos)` (src/model/mod.rs:678-697) with n_pos = pos + 1."""
         if k_out is None:

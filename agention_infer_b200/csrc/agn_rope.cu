@@ -20,6 +20,8 @@
 // lane (head_dim 128: W=8, VPL=4, partner two registers on), which needs no shuffle; the
 // norm statistic is a log2(W)-step shuffle reduction inside the group.  The intermediate
 // normalised head never leaves registers.
+#include <cuda_fp16.h>
+
 #include "agn_common.cuh"
 
 namespace {
@@ -36,7 +38,48 @@ struct RopeArgs {
     int pos_start;
     int tpc;  // tokens per CTA
     float freq_scale, eps;
+    // fused KV-cache write (template parameter KV != 0): the rotated K heads and the V heads of the
+    // token are packed into one layer's cache at slot pos (`KvCache::write`, src/model/mod.rs:648-672)
+    const float *v;
+    unsigned char *k_cache, *v_cache;
+    int64_t max_seq;
+    int bytes_per_token;
+    uint32_t *flags;
 };
+
+enum { KV_NONE = 0, KV_F16 = 1, KV_Q8_0 = 2 };
+
+// Four values of a K or V head (float4 number i of the head) into the cache slot of the token.
+// f16: `half::f16::from_f32` per element.  Q8_0 (`KvDtype::pack`, src/model/mod.rs:567-585): the
+// eight lanes that hold one 32-value block (float4 numbers 8b .. 8b+7) share amax through three
+// shuffles; scale = amax / 127 (1 if amax is 0), q = clamp(round(v / scale)).  Must be called by
+// every lane of the warp (`on` = this lane holds data of a K / V row with a valid slot).
+template <int KV>
+__device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_head, int i, int blocks_before) {
+    if (KV == KV_F16) {
+        if (on) ActVec<__half>::store(reinterpret_cast<__half *>(tok_head), i, x);
+    } else if (KV == KV_Q8_0) {
+        float amax = on ? fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))) : 0.0f;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (on) {
+            const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            unsigned char *blk = tok_head + (size_t)(blocks_before + (i >> 3)) * 34;
+            const int lane8 = i & 7;
+            if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+            uint32_t q[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float r = roundf(__fdiv_rn(xs[j], scale));
+                r = fminf(fmaxf(r, -127.0f), 127.0f);
+                q[j] = (uint32_t)(unsigned char)(signed char)(int)r;
+            }
+            *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
+            *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+        }
+    }
+}
 
 // With f16 storage the reference's fused kernel writes the normalised head to the f16 buffer
 // and reads it back for the rotation (src/ops/kernels_wgpu.rs:296-316): the value that is
@@ -69,14 +112,14 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
        MODE_NEOX_SHFL = 3 // NeoX, n_rot/8 < W (power of two): partner is register 0 of lane ^ (n_rot/8)
 };
 
-template <typename T, int W, int VPL, int MODE, bool NORM>
+template <typename T, int W, int VPL, int MODE, bool NORM, int KV = KV_NONE>
 __global__ void __launch_bounds__(256)
 rope_heads_kernel(const RopeArgs a) {
     agn_pdl_launch_dependents();
     constexpr int NS = VPL == 4 ? 2 : 4;  // head rows in flight per lane group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int half = a.n_rot >> 1;
-    const int n_heads = a.n_q + a.n_kv;
+    const int n_heads = a.n_q + a.n_kv + (KV != KV_NONE ? a.n_kv : 0);  // head rows per token: Q, K and (fused cache write) V
     const int rows = a.tpc * n_heads;  // head rows of this CTA
     // shared memory: row pointers | row meta (token in CTA, is-K flag) | cos | sin
     T **s_ptr = reinterpret_cast<T **>(smem_raw);
@@ -90,11 +133,15 @@ rope_heads_kernel(const RopeArgs a) {
         const int tt = hr / n_heads, h = hr - tt * n_heads;
         const int64_t t = t0 + tt;
         T *p = nullptr;
-        if (t < a.T)
-            p = h < a.n_q ? static_cast<T *>(a.q) + (t * a.n_q + h) * (int64_t)a.head_dim
-                          : static_cast<T *>(a.k) + (t * a.n_kv + (h - a.n_q)) * (int64_t)a.head_dim;
+        const int kind = h < a.n_q ? 0 : (h < a.n_q + a.n_kv ? 1 : 2);  // Q, K, V
+        const int hk = kind == 0 ? 0 : h - a.n_q - (kind == 2 ? a.n_kv : 0);  // head index inside K / V
+        if (t < a.T) {
+            if (kind == 0) p = static_cast<T *>(a.q) + (t * a.n_q + h) * (int64_t)a.head_dim;
+            else if (kind == 1) p = static_cast<T *>(a.k) + (t * a.n_kv + hk) * (int64_t)a.head_dim;
+            else p = reinterpret_cast<T *>(const_cast<float *>(a.v)) + (t * a.n_kv + hk) * (int64_t)a.head_dim;  // read only
+        }
         s_ptr[hr] = p;
-        s_meta[hr] = tt | (h < a.n_q ? 0 : 1 << 16);
+        s_meta[hr] = tt | (kind << 16) | (hk << 18);
     }
     __syncthreads();
     // everything above used kernel parameters and shared memory only; global memory (which the
@@ -129,6 +176,7 @@ rope_heads_kernel(const RopeArgs a) {
         }
 #pragma unroll
         for (int s = 0; s < NS; s++) {
+            const int kind = (meta[s] >> 16) & 3;
             if (NORM) {
                 float ss = 0.0f;
 #pragma unroll
@@ -139,11 +187,11 @@ rope_heads_kernel(const RopeArgs a) {
                 // (w*x)/rms of the CPU path, evaluated as (w*x)*(1/rms): one IEEE division per
                 // head instead of one per element; differs from the CPU order by <= 1 ulp
                 const float inv = 1.0f / sqrtf(ss / (float)a.head_dim + a.eps);
-                const float4 *wv = reinterpret_cast<const float4 *>((meta[s] >> 16) ? a.wk : a.wq);
+                const float4 *wv = reinterpret_cast<const float4 *>(kind == 1 ? a.wk : a.wq);
 #pragma unroll
                 for (int l = 0; l < VPL; l++) {
                     const int i = lane + W * l;
-                    if (ptr[s] && i < hd4) {
+                    if (ptr[s] && i < hd4 && kind < 2) {
                         const float4 ww = __ldg(wv + i);
                         v[s][l].x = act_round<T>(ww.x * v[s][l].x * inv);
                         v[s][l].y = act_round<T>(ww.y * v[s][l].y * inv);
@@ -158,7 +206,7 @@ rope_heads_kernel(const RopeArgs a) {
                 constexpr int K = MODE == MODE_NEOX_K2 ? 2 : 1;
 #pragma unroll
                 for (int l = 0; l < K; l++) {
-                    if (l + K < VPL && ptr[s]) {
+                    if (l + K < VPL && ptr[s] && kind < 2) {
                         const int i = lane + W * l;
                         const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
                         const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
@@ -183,7 +231,7 @@ rope_heads_kernel(const RopeArgs a) {
                 oth.y = __shfl_xor_sync(0xffffffffu, mine.y, hq);
                 oth.z = __shfl_xor_sync(0xffffffffu, mine.z, hq);
                 oth.w = __shfl_xor_sync(0xffffffffu, mine.w, hq);
-                if (ptr[s] && lane < 2 * hq) {
+                if (ptr[s] && lane < 2 * hq && kind < 2) {
                     const bool low = lane < hq;
                     const int i = low ? lane : lane - hq;
                     const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
@@ -204,7 +252,7 @@ rope_heads_kernel(const RopeArgs a) {
 #pragma unroll
                 for (int l = 0; l < VPL; l++) {
                     const int i = lane + W * l;
-                    if (ptr[s] && 4 * i < a.n_rot) {
+                    if (ptr[s] && 4 * i < a.n_rot && kind < 2) {
                         const float2 c = *reinterpret_cast<const float2 *>(c_tab + 2 * i);
                         const float2 sn = *reinterpret_cast<const float2 *>(s_tab + 2 * i);
                         const float4 x = v[s][l];
@@ -220,7 +268,29 @@ rope_heads_kernel(const RopeArgs a) {
                 const int i = lane + W * l;
                 // dims past n_rot are untouched by rope: skip the store unless normalised
                 const bool touched = NORM || 4 * i < a.n_rot;
-                if (ptr[s] && i < hd4 && touched) ActVec<T>::store(ptr[s], i, v[s][l]);
+                if (ptr[s] && i < hd4 && touched && kind < 2) ActVec<T>::store(ptr[s], i, v[s][l]);
+            }
+            if (KV != KV_NONE) {
+                // the rotated K head (still in registers) and the V head go into the token's cache slot
+                const int hk = meta[s] >> 18;
+                int64_t slot = -1;
+                if (ptr[s] && kind >= 1) {
+                    const int64_t t = t0 + (meta[s] & 0xffff);
+                    const int64_t p = a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t;
+                    if (p >= 0 && p < a.max_seq) slot = p;
+                    else if (lane == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);  // skipped and reported, never a fault
+                }
+                unsigned char *tok_head = nullptr;
+                if (slot >= 0) {
+                    tok_head = (kind == 1 ? a.k_cache : a.v_cache) + slot * a.bytes_per_token;
+                    if (KV == KV_F16) tok_head += (size_t)hk * a.head_dim * 2;
+                }
+                const int blocks_before = hk * (a.head_dim >> 5);
+#pragma unroll
+                for (int l = 0; l < VPL; l++) {
+                    const int i = lane + W * l;
+                    kv_pack4<KV>(v[s][l], slot >= 0 && i < hd4, tok_head, i, blocks_before);
+                }
             }
         }
     }
@@ -278,6 +348,27 @@ rope_heads_generic_kernel(const RopeArgs a) {
     }
 }
 
+// Fused cache write: f32 activations, head_dim 128 (W = 8, VPL = 4) or 64 (W = 8, VPL = 2), the
+// same-lane NeoX modes and the normal layout.  Everything else runs as two launches.
+template <int W, int VPL, int MODE>
+void launch_kv3(agn_ctx *ctx, const RopeArgs &a, bool norm, int kv, unsigned grid, int threads, size_t smem) {
+    if (kv == KV_F16) {
+        if (norm) agn_launch(ctx, rope_heads_kernel<float, W, VPL, MODE, true, KV_F16>, dim3(grid), dim3(threads), smem, a);
+        else agn_launch(ctx, rope_heads_kernel<float, W, VPL, MODE, false, KV_F16>, dim3(grid), dim3(threads), smem, a);
+    } else {
+        if (norm) agn_launch(ctx, rope_heads_kernel<float, W, VPL, MODE, true, KV_Q8_0>, dim3(grid), dim3(threads), smem, a);
+        else agn_launch(ctx, rope_heads_kernel<float, W, VPL, MODE, false, KV_Q8_0>, dim3(grid), dim3(threads), smem, a);
+    }
+}
+
+bool launch_kv(agn_ctx *ctx, const RopeArgs &a, bool norm, int kv, int W, int VPL, int mode, unsigned grid, int threads, size_t smem) {
+    if (W == 8 && VPL == 4 && mode == MODE_NEOX_K2) { launch_kv3<8, 4, MODE_NEOX_K2>(ctx, a, norm, kv, grid, threads, smem); return true; }
+    if (W == 8 && VPL == 4 && mode == MODE_NORMAL) { launch_kv3<8, 4, MODE_NORMAL>(ctx, a, norm, kv, grid, threads, smem); return true; }
+    if (W == 8 && VPL == 2 && mode == MODE_NEOX_K1) { launch_kv3<8, 2, MODE_NEOX_K1>(ctx, a, norm, kv, grid, threads, smem); return true; }
+    if (W == 8 && VPL == 2 && mode == MODE_NORMAL) { launch_kv3<8, 2, MODE_NORMAL>(ctx, a, norm, kv, grid, threads, smem); return true; }
+    return false;
+}
+
 template <typename T, int W, int VPL, int MODE>
 void launch_fast3(agn_ctx *ctx, const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem) {
     if (norm) agn_launch(ctx, rope_heads_kernel<T, W, VPL, MODE, true>, dim3(grid), dim3(threads), smem, a);
@@ -301,10 +392,23 @@ bool launch_fast(agn_ctx *ctx, const RopeArgs &a, bool norm, int mode, unsigned 
 
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
+// What the fused cache write needs besides the rope arguments.
+struct KvFuse {
+    int kv;  // KV_F16 or KV_Q8_0
+    const float *v;
+    unsigned char *k_cache, *v_cache;
+    int64_t max_seq;
+    int bytes_per_token;
+};
+
+// kvf != nullptr: try to pack K (after the rotation) and V into the cache in the same launch;
+// *fused tells the caller whether that happened (if not, only the rope ran).
 template <typename AT>
 int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float *wq, const float *wk,
                       bool norm, int64_t T, int32_t n_q, int32_t n_kv, int32_t head_dim, float eps, int32_t n_rot,
-                      const int32_t *pos, int32_t pos_start, float theta, float freq_scale, int32_t layout) {
+                      const int32_t *pos, int32_t pos_start, float theta, float freq_scale, int32_t layout,
+                      const KvFuse *kvf = nullptr, bool *fused = nullptr) {
+    if (fused) *fused = false;
     if (T < 0 || n_q < 0 || n_kv < 0 || n_q + n_kv <= 0 || head_dim <= 0)
         return agn_fail(ctx, AGN_EINVAL, "%s: T=%lld heads=%d+%d head_dim=%d", name, (long long)T, n_q, n_kv, head_dim);
     if (n_rot < 0 || n_rot > head_dim || (n_rot & 1))
@@ -323,6 +427,7 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
     a.n_q = n_q; a.n_kv = n_kv; a.head_dim = head_dim; a.n_rot = n_rot;
     a.pos_start = pos_start; a.freq_scale = freq_scale; a.eps = eps; a.tpc = 1;
     a.denom = nullptr;
+    a.v = nullptr; a.k_cache = nullptr; a.v_cache = nullptr; a.max_seq = 0; a.bytes_per_token = 0; a.flags = ctx->d_flags;
     if (n_rot >= 2) {
         int32_t rc = agn_rope_table(ctx, theta, n_rot, &a.denom);
         if (rc != AGN_OK) return rc;
@@ -360,8 +465,21 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
         }
         fast = found;
     }
+    bool kv_ok = false;
+    // Q8_0 packing is division-heavy (an IEEE division and a rounding per value): on a handful of
+    // tokens the one CTA that holds them is slower with it than a second small launch (T = 1: 4.2 vs
+    // 4.1 us), so small batches fuse only the f16 cache.
+    if (kvf && fast && sizeof(AT) == 4 && n_kv > 0 && W == 8 && (VPL == 4 || VPL == 2) && (kvf->kv == KV_F16 || T >= 512) &&
+        (mode == MODE_NORMAL || mode == (VPL == 4 ? MODE_NEOX_K2 : MODE_NEOX_K1)) && agn_aligned16(kvf->v) &&
+        (kvf->kv == KV_F16 ? (agn_aligned(kvf->k_cache, 8) && agn_aligned(kvf->v_cache, 8) && kvf->bytes_per_token % 8 == 0)
+                           : (head_dim % 32 == 0 && agn_aligned(kvf->k_cache, 2) && agn_aligned(kvf->v_cache, 2)))) {
+        kv_ok = true;
+        a.v = kvf->v; a.k_cache = kvf->k_cache; a.v_cache = kvf->v_cache; a.max_seq = kvf->max_seq;
+        a.bytes_per_token = kvf->bytes_per_token;
+    }
     if (fast) {
         // tokens per CTA: aim at 32 head rows per CTA, keep the sin/cos table small
+        const int n_heads = n_q + n_kv + (kv_ok ? n_kv : 0);  // head rows per token (V rows only for the fused cache write)
         int tpc = 32 / n_heads;
         if (tpc < 1) tpc = 1;
         if (half > 0 && tpc * half > 2048) tpc = 2048 / half > 0 ? 2048 / half : 1;
@@ -376,7 +494,13 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
         const unsigned grid = (unsigned)((T + tpc - 1) / tpc);
         const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
         bool ok = false;
-        if (W == 8 && VPL == 4) ok = launch_fast<AT, 8, 4>(ctx, a, norm, mode, grid, threads, smem);
+        if (kv_ok) {
+            ok = launch_kv(ctx, a, norm, kvf->kv, W, VPL, mode, grid, threads, smem);
+            if (ok) {
+                ctx->flags_dirty = true;
+                if (fused) *fused = true;
+            }
+        } else if (W == 8 && VPL == 4) ok = launch_fast<AT, 8, 4>(ctx, a, norm, mode, grid, threads, smem);
         else if (W == 16 && VPL == 4) ok = launch_fast<AT, 16, 4>(ctx, a, norm, mode, grid, threads, smem);
         else if (W == 32 && VPL == 4) ok = launch_fast<AT, 32, 4>(ctx, a, norm, mode, grid, threads, smem);
         else if (W == 8 && VPL == 2) ok = launch_fast<AT, 8, 2>(ctx, a, norm, mode, grid, threads, smem);
@@ -432,6 +556,41 @@ extern "C" int32_t agn_qk_norm_rope_qk_f32(agn_ctx *ctx, float *q, float *k, con
     AGN_CHECK_CTX(ctx);
     return rope_dispatch<float>(ctx, "qk_norm_rope_qk", q, k, wq, wk, true, T, n_q_heads, n_kv_heads, head_dim, eps, n_rot, pos,
                          pos_start, theta, freq_scale, layout);
+}
+
+// Per-position QK-norm -> RoPE of Q and K, then the KV-cache write of the rotated K and of V: the
+// three steps the reference runs back to back for every layer and token (`launch_qk_norm_rope` on q
+// and on k, then `kv_cache_write` / `kv_cache_write_q8_0`; src/model/llama/gpu_resident.rs and
+// src/ops/kernels_wgpu.rs:566-698) in one launch: K is packed from the registers that hold its
+// rotated values, V is read once and packed.  q and k are still updated in place.  The result is
+// byte for byte what agn_qk_norm_rope_qk_f32 (or agn_rope_qk_f32 when wq = wk = NULL) followed by
+// agn_kv_write_f32 gives; shapes outside the fused kernel's reach run as exactly those two launches.
+extern "C" int32_t agn_qk_norm_rope_kv_write_f32(agn_ctx *ctx, float *q, float *k, const float *v, const float *wq,
+                                                 const float *wk, int64_t T, int32_t n_q_heads, int32_t n_kv_heads,
+                                                 int32_t head_dim, float eps, int32_t n_rot, const int32_t *pos,
+                                                 int32_t pos_start, float theta, float freq_scale, int32_t layout,
+                                                 int32_t kv_dtype, void *k_cache, void *v_cache, int64_t max_seq_len) {
+    AGN_CHECK_CTX(ctx);
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "qk_norm_rope_kv_write: cache type %d is neither f16 nor q8_0", kv_dtype);
+    if (n_kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0)
+        return agn_fail(ctx, AGN_EINVAL, "qk_norm_rope_kv_write: n_kv_heads=%d head_dim=%d max_seq_len=%lld", n_kv_heads, head_dim,
+                        (long long)max_seq_len);
+    if (T > 0 && (!k || !v || !k_cache || !v_cache)) return agn_fail(ctx, AGN_EINVAL, "qk_norm_rope_kv_write: null pointer");
+    const bool norm = wq != nullptr || wk != nullptr;
+    const int64_t hd_kv = (int64_t)n_kv_heads * head_dim;
+    KvFuse f;
+    f.kv = kv_dtype == AGN_F16 ? KV_F16 : KV_Q8_0;
+    f.v = v;
+    f.k_cache = static_cast<unsigned char *>(k_cache);
+    f.v_cache = static_cast<unsigned char *>(v_cache);
+    f.max_seq = max_seq_len;
+    f.bytes_per_token = (int)agn_kv_bytes_per_token(kv_dtype, hd_kv);
+    bool fused = false;
+    int32_t rc = rope_dispatch<float>(ctx, "qk_norm_rope_kv_write", q, k, wq, wk, norm, T, n_q_heads, n_kv_heads, head_dim, eps,
+                                      n_rot, pos, pos_start, theta, freq_scale, layout, &f, &fused);
+    if (rc != AGN_OK || fused) return rc;
+    return agn_kv_write_f32(ctx, kv_dtype, k, v, k_cache, v_cache, T, hd_kv, pos, pos_start, max_seq_len);
 }
 
 // f16 activation storage (the reference's `Act = f16`; `rope` / `qk_norm_rope`,

@@ -262,6 +262,23 @@ impl CudaBackend {
         })
     }
 
+    /// `launch_qk_norm_rope` on q and on k followed by `kv_cache_write` (the per-layer, per-token
+    /// sequence of the resident path) as one launch; `wq`/`wk` = `None`: rope without the norm.
+    #[allow(clippy::too_many_arguments)]
+    pub fn launch_qk_norm_rope_kv_write(&self, q: &DevBuf, k: &DevBuf, v: &DevBuf, wq: Option<&DevBuf>, wk: Option<&DevBuf>,
+                                        t: usize, n_q_heads: usize, n_kv_heads: usize, head_dim: usize, eps: f32,
+                                        n_rot: usize, pos_start: usize, theta: f32, freq_scale: f32, layout: RopeLayout,
+                                        kv_dtype: i32, k_cache: &DevBuf, v_cache: &DevBuf, max_seq_len: usize) -> Result<()> {
+        let wq_ptr = wq.map_or(std::ptr::null(), |b| b.ptr as *const f32);
+        let wk_ptr = wk.map_or(std::ptr::null(), |b| b.ptr as *const f32);
+        self.check(unsafe {
+            agn_qk_norm_rope_kv_write_f32(self.ctx, q.ptr as *mut f32, k.ptr as *mut f32, v.ptr as *const f32, wq_ptr, wk_ptr,
+                                          t as i64, n_q_heads as i32, n_kv_heads as i32, head_dim as i32, eps, n_rot as i32,
+                                          std::ptr::null(), pos_start as i32, theta, freq_scale, layout as i32, kv_dtype,
+                                          k_cache.ptr, v_cache.ptr, max_seq_len as i64)
+        })
+    }
+
     /// Router logits `[t, n_experts]` -> the two largest per token (ties to the lower index) and
     /// their softmax probabilities, not renormalised (docs/08-moe-routing.md:27-33).
     pub fn router_top2(&self, logits: &DevBuf, t: usize, n_experts: usize) -> Result<(DevBuf, DevBuf)> {

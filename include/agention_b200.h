@@ -271,6 +271,21 @@ AGN_API int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float *k,
                                  const int32_t *pos, int32_t pos_start, int64_t max_seq_len);
 /* `KvCache::read_up_to` (src/model/mod.rs:678-697) with `KvDtype::unpack` (:587-604):
  * dequantises slots [0, n_pos) into k_out, v_out [n_pos, head_dim_kv] f32. */
+/* QK-norm -> RoPE of Q and K (in place) and the cache write of the rotated K and of V in one launch:
+ * the per-layer sequence `launch_qk_norm_rope` (q), `launch_qk_norm_rope` (k), `kv_cache_write`
+ * of the reference's resident path (src/ops/wgpu_backend/resident.rs:414-443,
+ * src/ops/kernels_wgpu.rs:566-698).  wq = wk = NULL: rope without the norm.  Arguments as in
+ * agn_qk_norm_rope_qk_f32 and agn_kv_write_f32 (head_dim_kv = n_kv_heads * head_dim; token t goes
+ * to slot pos[t] or pos_start + t).  Byte for byte the result of those two calls; head sizes the
+ * fused kernel does not cover (anything but head_dim 64 / 128 with full or normal-layout rotation)
+ * run as those two launches. */
+AGN_API int32_t agn_qk_norm_rope_kv_write_f32(agn_ctx *ctx, float *q, float *k, const float *v,
+                                              const float *wq, const float *wk, int64_t T,
+                                              int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                              float eps, int32_t n_rot, const int32_t *pos,
+                                              int32_t pos_start, float theta, float freq_scale,
+                                              int32_t layout, int32_t kv_dtype, void *k_cache,
+                                              void *v_cache, int64_t max_seq_len);
 AGN_API int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k_cache,
                                 const void *v_cache, int64_t n_pos, int64_t head_dim_kv,
                                 float *k_out, float *v_out);

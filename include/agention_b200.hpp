@@ -204,6 +204,14 @@ class CudaBackend {
     }
 
     // ---- KV cache: KvCache::write_range / read_up_to (src/model/mod.rs:660-697)
+    // norm -> rope of q and k in place and the cache write of the rotated k and of v, one launch
+    void launch_qk_norm_rope_kv_write(float *q, float *k, const float *v, const float *wq, const float *wk, int64_t T, int n_q,
+                                      int n_kv, int head_dim, float eps, int n_rot, const int32_t *pos, int pos_start, float theta,
+                                      int kv_dtype, void *k_cache, void *v_cache, int64_t max_seq_len, float freq_scale = 1.0f,
+                                      int layout = AGN_ROPE_NEOX) {
+        check(agn_qk_norm_rope_kv_write_f32(ctx_, q, k, v, wq, wk, T, n_q, n_kv, head_dim, eps, n_rot, pos, pos_start, theta,
+                                            freq_scale, layout, kv_dtype, k_cache, v_cache, max_seq_len));
+    }
     void kv_write(int kv_dtype, const float *k, const float *v, void *k_cache, void *v_cache, int64_t T,
                   int64_t head_dim_kv, const int32_t *pos, int pos_start, int64_t max_seq_len) {
         check(agn_kv_write_f32(ctx_, kv_dtype, k, v, k_cache, v_cache, T, head_dim_kv, pos, pos_start, max_seq_len));

@@ -106,3 +106,76 @@ def test_kv_write_pos_start_and_out_of_range_slot(backend):
     with pytest.raises(BackendError) as e:
         backend.kv_write(12, dkc, dkc, dkc, dvc, 1, hd, None, max_seq)
     assert e.value.status == 2
+
+
+# ---------------------------------------------------------------- norm -> rope + cache write, one launch
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kv_dtype", [1, 8])  # f16, q8_0
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("T,nq,nkv,hd,n_rot,layout", [
+    (1, 28, 4, 128, 128, 0), (64, 28, 4, 128, 128, 0), (300, 32, 8, 128, 128, 1), (600, 28, 4, 128, 128, 0), (513, 8, 2, 64, 64, 0), (5, 32, 8, 64, 64, 0), (17, 8, 2, 64, 64, 1),
+    (9, 4, 2, 128, 64, 0),    # partial rotation: not covered by the fused kernel, runs as two launches
+    (7, 3, 1, 80, 80, 0),     # head_dim 80: two launches
+    (4, 2, 2, 256, 256, 0),   # head_dim 256: two launches
+])
+def test_fused_rope_kv_write_equals_the_two_ops(backend, kv_dtype, norm, T, nq, nkv, hd, n_rot, layout):
+    """q, k and both caches must be byte for byte what rope (or norm -> rope) followed by kv_write gives."""
+    max_seq = 1024
+    q, k, v = synth.activations(2, "q", (T, nq * hd)), synth.activations(2, "k", (T, nkv * hd)), synth.activations(2, "x", (T, nkv * hd))
+    k[0, :32] = 0.0  # an all-zero block: scale 1
+    wq, wk = synth.norm_weight(2, "wq", hd), synth.norm_weight(2, "wk", hd)
+    pos = synth.rng_for(2, "pos").permutation(max_seq)[:T].astype(np.int32)
+    bpt = backend.kv_bytes_per_token(kv_dtype, nkv * hd)
+    dwq, dwk = (backend.upload(wq), backend.upload(wk)) if norm else (None, None)
+    dp, dv = backend.upload(pos), backend.upload(v)
+
+    def caches():
+        kc, vc = backend.empty(max_seq * bpt), backend.empty(max_seq * bpt)
+        backend.copy_h2d(kc, np.full(max_seq * bpt, 0x5A, np.uint8)); backend.copy_h2d(vc, np.full(max_seq * bpt, 0x5A, np.uint8))
+        backend.sync()
+        return kc, vc
+
+    # the two ops
+    q1, k1 = backend.upload(q), backend.upload(k)
+    kc1, vc1 = caches()
+    if norm:
+        backend.launch_qk_norm_rope_qk(q1, k1, dwq, dwk, T, nq, nkv, hd, 1e-6, n_rot, dp, 1e6, 1.0, layout)
+    else:
+        backend.launch_rope_qk(q1, k1, T, nq, nkv, hd, n_rot, dp, 1e6, 1.0, layout)
+    backend.kv_write(kv_dtype, k1, dv, kc1, vc1, T, nkv * hd, dp, max_seq)
+    # one call
+    q2, k2 = backend.upload(q), backend.upload(k)
+    kc2, vc2 = caches()
+    n0 = backend.launch_count
+    backend.launch_qk_norm_rope_kv_write(q2, k2, dv, dwq, dwk, T, nq, nkv, hd, 1e-6, n_rot, dp, 1e6, kv_dtype, kc2, vc2, max_seq,
+                                         layout=layout)
+    launches = backend.launch_count - n0
+    covered = hd in (64, 128) and n_rot == hd and (kv_dtype == 1 or T >= 512)  # small batches fuse only the f16 cache
+    assert launches == (1 if covered else 2)
+    for a, b, dt, shape in ((q1, q2, np.uint32, (T, nq * hd)), (k1, k2, np.uint32, (T, nkv * hd)),
+                            (kc1, kc2, np.uint8, (max_seq, bpt)), (vc1, vc2, np.uint8, (max_seq, bpt))):
+        assert np.array_equal(backend.read(a, dt, shape), backend.read(b, dt, shape))
+    # and the cache is what the oracle packs from the oracle's rotated k
+    rk = orc.qk_norm_rope_rows(k, wk, nkv, hd, 1e-6, n_rot, pos, 1e6, 1.0, layout) if norm else orc.rope_rows(k, nkv, hd, n_rot, pos, 1e6, 1.0, layout)
+    got_k = backend.read(backend.kv_read(kv_dtype, kc2, vc2, max_seq, nkv * hd)[0], np.float32, (max_seq, nkv * hd))
+    tol = 2.0 ** -10 if kv_dtype == 1 else 1.0 / 127
+    assert synth.max_rel_to_row_scale(got_k[pos].reshape(T * nkv, hd), rk.reshape(T * nkv, hd)) <= tol + 1e-5
+
+
+@pytest.mark.gpu
+def test_fused_rope_kv_write_reports_a_slot_out_of_range(backend):
+    T, nq, nkv, hd, max_seq = 4, 4, 2, 128, 8
+    q, k, v = synth.activations(2, "q", (T, nq * hd)), synth.activations(2, "k", (T, nkv * hd)), synth.activations(2, "x", (T, nkv * hd))
+    pos = np.array([0, 9, 3, -1], np.int32)
+    bpt = backend.kv_bytes_per_token(1, nkv * hd)
+    kc, vc = backend.empty(max_seq * bpt), backend.empty(max_seq * bpt)
+    backend.copy_h2d(kc, np.zeros(max_seq * bpt, np.uint8)); backend.copy_h2d(vc, np.zeros(max_seq * bpt, np.uint8)); backend.sync()
+    backend.launch_qk_norm_rope_kv_write(backend.upload(q), backend.upload(k), backend.upload(v), None, None, T, nq, nkv, hd, 0.0, hd,
+                                         backend.upload(pos), 1e6, 1, kc, vc, max_seq)
+    from agention_infer_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        backend.sync()
+    assert e.value.status == 4
+    got = backend.read(vc, np.uint8, (max_seq, bpt))
+    assert np.all(got[[1, 2, 4, 5, 6, 7]] == 0) and np.any(got[0] != 0) and np.any(got[3] != 0)  # only slots 0 and 3 were written
