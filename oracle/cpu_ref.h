@@ -6,11 +6,15 @@
  * baseline.  Nothing in the shipped CUDA path may call it.
  *
  * Parity pinning:
- *   - quant codecs (Q8_0 / Q4_K / Q6_K / F16 / BF16 / F32 rows) are pinned by
- *     the reference's own unit-test vectors (src/quant/q8_0.rs:110-148,
- *     src/quant/q4_k.rs:229-241, src/quant/mod.rs:176-205) re-created in the
+ *   - quant codecs (Q8_0 / Q4_K / Q6_K / Q5_K / Q5_0 / Q2_K / F16 / BF16 / F32
+ *     rows) are pinned by the reference's own unit-test vectors
+ *     (src/quant/q8_0.rs:110-148, src/quant/q4_k.rs:229-241,
+ *     src/quant/q5_0.rs:89-125, src/quant/q5_k.rs:348-392,
+ *     src/quant/q2_k.rs:113-177, src/quant/mod.rs:176-205) re-created in the
  *     test-suite, and compute_rope_freq_scale by
  *     src/model/llama/cpu_path.rs:1034-1060.
+ *   - KV-cache packing (KvDtype::pack / unpack, src/model/mod.rs:567-604): the
+ *     reference has no test for it -> "parity unpinned"; restated line by line.
  *   - rms_norm, qk_norm, rope rotation, softmax, silu*mul: the reference has
  *     no op-level test or golden vector -> "parity unpinned" at op level; the
  *     restatement follows the cited lines statement by statement and is
