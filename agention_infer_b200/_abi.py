@@ -98,6 +98,7 @@ SIGNATURES = {
     "agn_gather_rows_by_expert_noalloc_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, C.c_char_p,
                                                      _sz]),
     "agn_gguf_parse": (_i32, [_vp, _sz, _pp, C.c_char_p, _sz]),
+    "agn_gguf_split_index": (_i32, [C.c_char_p, _vp, _vp]),
     "agn_gguf_open": (_i32, [C.c_char_p, _pp, C.c_char_p, _sz]),
     "agn_gguf_close": (_i32, [_vp]),
     "agn_gguf_version": (C.c_uint32, [_vp]),

@@ -100,6 +100,23 @@ struct agn_gguf {
     size_t len = 0;
     void *mapping = nullptr;        // non-null when this object owns an mmap
     size_t map_len = 0;
+    // further files of a split model (`MultiFileMmap`, src/loader.rs:44-90): only the first file
+    // holds the header; tensor offsets run on through the files as if they were concatenated
+    struct Part {
+        void *mapping;
+        size_t len;
+        uint64_t start;  // offset of this file's first byte in the concatenated byte space
+    };
+    std::vector<Part> parts;
+
+    // `MultiFileMmap::slice`: the bytes [offset, offset + n) if they lie inside one file, else null
+    const uint8_t *slice(uint64_t offset, uint64_t n) const {
+        if (offset + n <= len) return data + offset;
+        for (const Part &p : parts)
+            if (p.start <= offset && offset + n <= p.start + p.len)
+                return static_cast<const uint8_t *>(p.mapping) + (offset - p.start);
+        return nullptr;
+    }
 };
 
 namespace {
@@ -197,10 +214,40 @@ int32_t agn_gguf_parse(const void *data, size_t len, agn_gguf **out, char *err, 
     return AGN_OK;
 }
 
-int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_len) {
-    if (err && err_len) err[0] = '\0';
-    if (!path || !out) return gfail(err, err_len, AGN_EINVAL, "agn_gguf_open: null argument");
-    *out = nullptr;
+// `parse_split_index` (src/loader.rs:25-38): "name-00001-of-00004.gguf" -> (1, 4).
+int32_t agn_gguf_split_index(const char *name, uint64_t *index, uint64_t *total) {
+    if (!name) return AGN_EINVAL;
+    std::string s(name);
+    const std::string suffix = ".gguf";
+    if (s.size() < suffix.size() || s.compare(s.size() - suffix.size(), suffix.size(), suffix) != 0) return AGN_ENOTFOUND;
+    s.erase(s.size() - suffix.size());
+    const size_t of_pos = s.rfind("-of-");
+    if (of_pos == std::string::npos) return AGN_ENOTFOUND;
+    const std::string total_str = s.substr(of_pos + 4), before = s.substr(0, of_pos);
+    const size_t dash = before.rfind('-');
+    if (dash == std::string::npos) return AGN_ENOTFOUND;
+    const std::string index_str = before.substr(dash + 1);
+    auto parse = [](const std::string &t, uint64_t *v) {  // str::parse::<usize>: digits only (a leading '+' is allowed)
+        size_t i = (!t.empty() && t[0] == '+') ? 1 : 0;
+        if (i >= t.size()) return false;
+        uint64_t acc = 0;
+        for (; i < t.size(); i++) {
+            if (t[i] < '0' || t[i] > '9') return false;
+            if (acc > (UINT64_MAX - (uint64_t)(t[i] - '0')) / 10) return false;
+            acc = acc * 10 + (uint64_t)(t[i] - '0');
+        }
+        *v = acc;
+        return true;
+    };
+    uint64_t i = 0, n = 0;
+    if (!parse(index_str, &i) || !parse(total_str, &n)) return AGN_ENOTFOUND;
+    if (index) *index = i;
+    if (total) *total = n;
+    return AGN_OK;
+}
+
+namespace {
+int32_t map_file(const char *path, void **m, size_t *len, char *err, size_t err_len) {
     const int fd = open(path, O_RDONLY);
     if (fd < 0) return gfail(err, err_len, AGN_EIO, "cannot open %s: %s", path, strerror(errno));
     struct stat st;
@@ -208,18 +255,56 @@ int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_le
         close(fd);
         return gfail(err, err_len, AGN_EIO, "cannot stat %s or the file is empty", path);
     }
-    void *m = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    void *p = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
     close(fd);
-    if (m == MAP_FAILED) return gfail(err, err_len, AGN_EIO, "cannot map %s: %s", path, strerror(errno));
+    if (p == MAP_FAILED) return gfail(err, err_len, AGN_EIO, "cannot map %s: %s", path, strerror(errno));
+    *m = p;
+    *len = (size_t)st.st_size;
+    return AGN_OK;
+}
+}  // namespace
+
+int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_len) {
+    if (err && err_len) err[0] = '\0';
+    if (!path || !out) return gfail(err, err_len, AGN_EINVAL, "agn_gguf_open: null argument");
+    *out = nullptr;
+    void *m = nullptr;
+    size_t len = 0;
+    int32_t rc = map_file(path, &m, &len, err, err_len);
+    if (rc != AGN_OK) return rc;
     agn_gguf *g = new agn_gguf();
     g->data = static_cast<const uint8_t *>(m);
-    g->len = (size_t)st.st_size;
+    g->len = len;
     g->mapping = m;
-    g->map_len = (size_t)st.st_size;
-    const int32_t rc = parse_into(g, err, err_len);
+    g->map_len = len;
+    rc = parse_into(g, err, err_len);
+    // a split model: file 1 of N names its siblings (`MultiFileMmap::load`, `sibling_path`, src/loader.rs:49-103)
+    const std::string full(path);
+    const size_t slash = full.rfind('/');
+    const std::string dir = slash == std::string::npos ? std::string() : full.substr(0, slash + 1);
+    const std::string base = slash == std::string::npos ? full : full.substr(slash + 1);
+    uint64_t index = 1, total = 1;
+    if (rc == AGN_OK && agn_gguf_split_index(base.c_str(), &index, &total) == AGN_OK && total > 1 && total <= 99999) {
+        char pat[32];
+        snprintf(pat, sizeof pat, "-00001-of-%05llu", (unsigned long long)total);
+        const size_t at = base.find(pat);
+        uint64_t cumulative = len;
+        for (uint64_t i = 2; at != std::string::npos && i <= total && rc == AGN_OK; i++) {
+            char rep[32];
+            snprintf(rep, sizeof rep, "-%05llu-of-%05llu", (unsigned long long)i, (unsigned long long)total);
+            std::string sib = base;
+            sib.replace(at, strlen(pat), rep);
+            void *pm = nullptr;
+            size_t pl = 0;
+            rc = map_file((dir + sib).c_str(), &pm, &pl, err, err_len);
+            if (rc == AGN_OK) {
+                g->parts.push_back({pm, pl, cumulative});
+                cumulative += pl;
+            }
+        }
+    }
     if (rc != AGN_OK) {
-        munmap(m, g->map_len);
-        delete g;
+        agn_gguf_close(g);
         return rc;
     }
     *out = g;
@@ -229,6 +314,7 @@ int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_le
 int32_t agn_gguf_close(agn_gguf *g) {
     if (!g) return AGN_OK;
     if (g->mapping) munmap(g->mapping, g->map_len);
+    for (const agn_gguf::Part &p : g->parts) munmap(p.mapping, p.len);
     delete g;
     return AGN_OK;
 }
@@ -310,13 +396,16 @@ int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name
     if (agn_gguf_find_tensor(g, name, &ti) != AGN_OK) return agn_fail(ctx, AGN_ENOTFOUND, "tensor '%s' not found", name);
     if (ti.row_bytes == 0)
         return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "tensor '%s' has ggml type %d, which has no codec here", name, ti.ggml_type);
-    if (ti.file_offset + ti.n_bytes > g->len)  // "tensor row .. extends beyond data section", src/quant/mod.rs:124-131
-        return agn_fail(ctx, AGN_EFORMAT, "tensor '%s' extends beyond the file (offset %llu + %llu bytes > %zu)", name,
-                        (unsigned long long)ti.file_offset, (unsigned long long)ti.n_bytes, g->len);
+    // "tensor row .. extends beyond data section", src/quant/mod.rs:124-131; in a split model the
+    // bytes must lie inside one of the files (`MultiFileMmap::slice`, src/loader.rs:79-89)
+    const uint8_t *src = g->slice(ti.file_offset, ti.n_bytes);
+    if (!src)
+        return agn_fail(ctx, AGN_EFORMAT, "tensor '%s' extends beyond the file or straddles two files (offset %llu + %llu bytes)",
+                        name, (unsigned long long)ti.file_offset, (unsigned long long)ti.n_bytes);
     void *d = nullptr;
     int32_t rc = agn_malloc(ctx, (size_t)ti.n_bytes, &d);
     if (rc != AGN_OK) return rc;
-    rc = agn_memcpy_h2d(ctx, d, g->data + ti.file_offset, (size_t)ti.n_bytes);
+    rc = agn_memcpy_h2d(ctx, d, src, (size_t)ti.n_bytes);
     if (rc == AGN_OK) rc = agn_sync(ctx);
     if (rc != AGN_OK) {
         agn_free(ctx, d);

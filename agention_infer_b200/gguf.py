@@ -34,6 +34,15 @@ class TensorInfo:
         return f"TensorInfo({self.name!r}, type={self.ggml_type}, dims={self.dims}, offset={self.byte_offset})"
 
 
+def split_index(name: str):
+    """`parse_split_index` (src/loader.rs:25-38): (file_index, total_files) of "name-00001-of-00004.gguf", else None."""
+    lib = _abi.load()
+    i, n = C.c_uint64(), C.c_uint64()
+    if lib.agn_gguf_split_index(name.encode(), C.byref(i), C.byref(n)) != _abi.AGN_OK:
+        return None
+    return int(i.value), int(n.value)
+
+
 class GgufFile:
     """A parsed GGUF file: `GgufFile(path)` memory-maps it, `GgufFile(data=bytes)` parses a buffer."""
 

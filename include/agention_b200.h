@@ -448,7 +448,13 @@ typedef struct agn_tensor_info {  /* `TensorInfo` (src/types.rs:373-403) plus de
     uint64_t n_bytes;      /* row_bytes * n_rows */
 } agn_tensor_info;
 AGN_API int32_t agn_gguf_parse(const void *data, size_t len, agn_gguf **out, char *err, size_t err_len);
+/* agn_gguf_open on file 1 of a split model ("name-00001-of-0000N.gguf") also maps files 2..N,
+ * which hold only tensor data at offsets that run on from the previous file (`MultiFileMmap`,
+ * src/loader.rs:40-103); a tensor must lie inside one file to be uploaded. */
 AGN_API int32_t agn_gguf_open(const char *path, agn_gguf **out, char *err, size_t err_len);
+/* `parse_split_index` (src/loader.rs:25-38): "name-00003-of-00005.gguf" -> index 3, total 5
+ * (1-based); AGN_ENOTFOUND when the name does not follow the pattern. */
+AGN_API int32_t agn_gguf_split_index(const char *name, uint64_t *index, uint64_t *total);
 AGN_API int32_t agn_gguf_close(agn_gguf *g);
 AGN_API uint32_t agn_gguf_version(const agn_gguf *g);
 AGN_API uint64_t agn_gguf_tensor_count(const agn_gguf *g);

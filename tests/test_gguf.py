@@ -109,6 +109,55 @@ def test_file_with_metadata_and_tensors(tmp_path):
     assert e.value.status == _abi.AGN_EIO
 
 
+def test_split_index_reference_vectors():  # src/loader.rs:108-119
+    from agention_infer_b200.gguf import split_index
+    assert split_index("MiniMax-M2.7-UD-IQ4_XS-00001-of-00004.gguf") == (1, 4)
+    assert split_index("model-00003-of-00005.gguf") == (3, 5)
+    assert split_index("single.gguf") is None
+    assert split_index("model-0000x-of-00005.gguf") is None and split_index("model-00001-of-00002.bin") is None
+
+
+def test_split_model_maps_the_sibling_files(tmp_path):
+    """File 1 holds the header and the first tensors, file 2 only tensor bytes; offsets run on
+    (`MultiFileMmap::load` / `slice`, src/loader.rs:49-90)."""
+    blob, table, norm = _model_file()
+    g0 = GgufFile(data=blob)
+    nw = g0.find("output_norm.weight")
+    cut = nw.file_offset  # the norm weight and everything after it go to the second file
+    (tmp_path / "m-00001-of-00002.gguf").write_bytes(blob[:cut])
+    with pytest.raises(GgufError) as e:  # the sibling is missing
+        GgufFile(str(tmp_path / "m-00001-of-00002.gguf"))
+    assert e.value.status == _abi.AGN_EIO
+    (tmp_path / "m-00002-of-00002.gguf").write_bytes(blob[cut:])
+    g = GgufFile(str(tmp_path / "m-00001-of-00002.gguf"))
+    assert g.tensor_count == 3 and g.find("output_norm.weight").file_offset == cut
+    g.close(); g0.close()
+
+
+@pytest.mark.gpu
+def test_upload_from_a_split_model(backend, tmp_path):
+    blob, table, norm = _model_file(vocab=64, hidden=512)
+    g0 = GgufFile(data=blob)
+    cut = g0.find("output_norm.weight").file_offset
+    (tmp_path / "m-00001-of-00002.gguf").write_bytes(blob[:cut])
+    (tmp_path / "m-00002-of-00002.gguf").write_bytes(blob[cut:])
+    g = GgufFile(str(tmp_path / "m-00001-of-00002.gguf"))
+    dtab, info = g.upload(backend, "token_embd.weight")       # lies in file 1
+    assert backend.read(dtab, np.uint8, (info.n_bytes,)).tobytes() == table.tobytes()
+    dnorm, ninfo = g.upload(backend, "output_norm.weight")    # lies in file 2
+    assert np.array_equal(backend.read(dnorm, np.float32, (ninfo.row_len,)), norm)
+    # a tensor cut in two by the file boundary cannot be served from one mapping
+    cut2 = g0.find("token_embd.weight").file_offset + 1000
+    (tmp_path / "n-00001-of-00002.gguf").write_bytes(blob[:cut2])
+    (tmp_path / "n-00002-of-00002.gguf").write_bytes(blob[cut2:])
+    g2 = GgufFile(str(tmp_path / "n-00001-of-00002.gguf"))
+    from agention_infer_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        g2.upload(backend, "token_embd.weight")
+    assert e.value.status == _abi.AGN_EFORMAT
+    g.close(); g2.close(); g0.close()
+
+
 @pytest.mark.gpu
 def test_get_rows_from_a_tensor_uploaded_out_of_a_gguf_file(backend, tmp_path):
     blob, table, norm = _model_file(vocab=512, hidden=1024)
