@@ -97,6 +97,7 @@ SIGNATURES = {
     "agn_host_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_gather_rows_by_expert_noalloc_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, C.c_char_p,
                                                      _sz]),
+    "agn_rope_freq_scale": (_i32, [C.c_char_p, _i32, _f32, _vp]),
     "agn_gguf_parse": (_i32, [_vp, _sz, _pp, C.c_char_p, _sz]),
     "agn_gguf_split_index": (_i32, [C.c_char_p, _vp, _vp]),
     "agn_gguf_open": (_i32, [C.c_char_p, _pp, C.c_char_p, _sz]),

@@ -301,6 +301,23 @@ int32_t agn_event_destroy(agn_ctx *ctx, agn_event *ev) {
     return AGN_OK;
 }
 
+// `compute_rope_freq_scale` (src/model/llama/cpu_path.rs:34-40): absent / "" / "none" -> 1,
+// "linear" -> 1 / max(factor or 1, 1e-6), anything else (e.g. "yarn") -> not applied.
+int32_t agn_rope_freq_scale(const char *scaling_type, int32_t has_factor, float factor, float *scale) {
+    if (!scale) return AGN_EINVAL;
+    if (!scaling_type || scaling_type[0] == '\0' || strcmp(scaling_type, "none") == 0) {
+        *scale = 1.0f;
+        return AGN_OK;
+    }
+    if (strcmp(scaling_type, "linear") == 0) {
+        float f = has_factor ? factor : 1.0f;
+        if (!(f > 1e-6f)) f = 1e-6f;  // f32::max(1e-6); a NaN factor also ends up here
+        *scale = 1.0f / f;
+        return AGN_OK;
+    }
+    return AGN_ENOTFOUND;
+}
+
 size_t agn_type_size(int32_t dtype, size_t n) {
     // GgmlType::block_size / block_bytes / type_size, src/types.rs:88-168
     size_t bs, bb;

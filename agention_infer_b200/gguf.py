@@ -5,6 +5,8 @@ accessors (src/types.rs).  Parsing needs no GPU."""
 from __future__ import annotations
 
 import ctypes as C
+import dataclasses
+import warnings
 from typing import List, Optional, Union
 
 from . import _abi
@@ -32,6 +34,43 @@ class TensorInfo:
 
     def __repr__(self):
         return f"TensorInfo({self.name!r}, type={self.ggml_type}, dims={self.dims}, offset={self.byte_offset})"
+
+
+def rope_freq_scale(scaling_type: Optional[str], factor: Optional[float]) -> Optional[float]:
+    """`compute_rope_freq_scale` (src/model/llama/cpu_path.rs:34-40): the freq_scale of the rope entry points, or None
+    for a scheme that is not applied (e.g. "yarn")."""
+    out = C.c_float()
+    st = _abi.load().agn_rope_freq_scale(None if scaling_type is None else scaling_type.encode(), 0 if factor is None else 1,
+                                         0.0 if factor is None else float(factor), C.byref(out))
+    return float(out.value) if st == _abi.AGN_OK else None
+
+
+@dataclasses.dataclass
+class ModelConfig:
+    """`ModelConfig::from_gguf` (src/model/mod.rs:196-286): the hyper-parameters the layer ops take, read from the GGUF
+    metadata under the architecture's prefix, with the reference's defaults."""
+    architecture: str
+    context_length: int
+    embedding_length: int
+    block_count: int
+    head_count: int
+    head_count_kv: int
+    head_dim: int
+    feed_forward_length: int
+    rope_freq_base: float
+    rope_scaling_type: Optional[str]
+    rope_scaling_factor: Optional[float]
+    layer_norm_rms_epsilon: float
+    vocab_size: int
+
+    @property
+    def freq_scale(self) -> float:
+        """`LlamaModel::rope_freq_scale` (src/model/llama/cpu_path.rs:44-60): 1.0 with a warning for an unapplied scheme."""
+        s = rope_freq_scale(self.rope_scaling_type, self.rope_scaling_factor)
+        if s is None:
+            warnings.warn(f"rope scaling type '{self.rope_scaling_type}' is not applied; positions are used unscaled")
+            return 1.0
+        return s
 
 
 def split_index(name: str):
@@ -122,6 +161,36 @@ class GgufFile:
             return None
         return TensorInfo(raw)
 
+    def model_config(self) -> ModelConfig:
+        """`ModelConfig::from_gguf` (src/model/mod.rs:213-286).  (A per-layer `head_count_kv` array, which the reference
+        reduces to its maximum, is not read here: the scalar form or the fallback to `head_count` is used.)"""
+        arch = self.get_string("general.architecture")
+        if arch is None:
+            raise GgufError(_abi.AGN_ENOTFOUND, "missing metadata: general.architecture")
+
+        def need(field):
+            v = self.get_u64(f"{arch}.{field}")
+            if v is None:
+                raise GgufError(_abi.AGN_ENOTFOUND, f"missing metadata: {arch}.{field}")
+            return v
+
+        head_count, embedding_length = need("attention.head_count"), need("embedding_length")
+        key_length = self.get_u64(f"{arch}.attention.key_length")
+        emb = self.find("token_embd.weight")
+        if emb is None:
+            raise GgufError(_abi.AGN_ENOTFOUND, "missing metadata: token_embd.weight tensor")
+        u = lambda f, d: d if self.get_u64(f"{arch}.{f}") is None else self.get_u64(f"{arch}.{f}")
+        fl = lambda f, d: d if self.get_f32(f"{arch}.{f}") is None else self.get_f32(f"{arch}.{f}")
+        return ModelConfig(
+            architecture=arch, context_length=u("context_length", 4096), embedding_length=embedding_length,
+            block_count=u("block_count", 32), head_count=head_count, head_count_kv=u("attention.head_count_kv", head_count),
+            head_dim=key_length if key_length is not None else embedding_length // head_count,
+            feed_forward_length=u("feed_forward_length", 0), rope_freq_base=fl("rope.freq_base", 10000.0),
+            rope_scaling_type=self.get_string(f"{arch}.rope.scaling.type"),
+            rope_scaling_factor=self.get_f32(f"{arch}.rope.scaling.factor"),
+            layer_norm_rms_epsilon=fl("attention.layer_norm_rms_epsilon", 1e-5),
+            vocab_size=emb.dims[1] if len(emb.dims) >= 2 else emb.dims[0])
+
     def upload(self, backend: CudaBackend, name: str):
         """Copies the tensor to the device: (DeviceBuffer, TensorInfo) — the `table` of get_rows."""
         raw = _abi.TensorInfo()
@@ -131,3 +200,14 @@ class GgufFile:
             raise BackendError(st, self._lib.agn_last_error(backend._ctx).decode())
         info = TensorInfo(raw)
         return DeviceBuffer(backend, p.value, info.n_bytes), info
+
+    def dequant_tensor(self, backend: CudaBackend, name: str):
+        """`WeightMap::dequant_tensor` (src/model/mod.rs:318-345): the whole tensor as f32 [n_rows, row_len] on the device
+        (every row through the get_rows kernel).  Returns (DeviceBuffer, TensorInfo)."""
+        import numpy as np
+        table, info = self.upload(backend, name)
+        ids = backend.upload(np.arange(info.n_rows, dtype=np.uint32))
+        out = backend.get_rows(info.ggml_type, table, info.n_bytes, info.n_rows, info.row_len, ids, info.n_rows)
+        backend.sync()
+        table.free(); ids.free()
+        return out, info

@@ -159,6 +159,13 @@ AGN_API int32_t agn_add_residual_rms_norm_f32(agn_ctx *ctx, const float *x, cons
                                               const float *w, float *new_x, float *normed,
                                               int64_t T, int64_t H, float eps);
 
+/* `compute_rope_freq_scale` (src/model/llama/cpu_path.rs:34-40), the freq_scale argument of the
+ * rope entry points from the model's `rope.scaling.type` / `rope.scaling.factor` metadata:
+ * NULL, "" or "none" -> 1; "linear" -> 1 / max(factor, 1e-6) (has_factor = 0: factor 1).
+ * AGN_OK with *scale set; AGN_ENOTFOUND for any other scheme (e.g. "yarn": the reference's `None`,
+ * "not applied yet" — its caller warns and uses 1.0).  Host arithmetic only; no context. */
+AGN_API int32_t agn_rope_freq_scale(const char *scaling_type, int32_t has_factor, float factor, float *scale);
+
 /* `LlamaModel::rope` / `rope_partial` (src/model/llama/cpu_path.rs:99-133,461-496),
  * GPU twin `launch_rope` (src/ops/wgpu_backend/resident.rs:326-353), in place on
  * x [T, n_heads*head_dim].  Token t rotates with position pos[t] (device int32

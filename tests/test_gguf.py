@@ -109,6 +109,40 @@ def test_file_with_metadata_and_tensors(tmp_path):
     assert e.value.status == _abi.AGN_EIO
 
 
+def test_rope_freq_scale_reference_vectors():  # src/model/llama/cpu_path.rs:1034-1060, the product's own host function
+    from agention_infer_b200.gguf import rope_freq_scale as scale
+    assert scale(None, None) == 1.0 and scale("none", 8.0) == 1.0 and scale("", 8.0) == 1.0
+    assert scale("linear", 4.0) == 0.25 and scale("linear", 2.0) == 0.5 and scale("linear", None) == 1.0
+    assert scale("yarn", 4.0) is None
+    assert scale("linear", 0.0) == pytest.approx(1e6, rel=1e-6)  # factor.max(1e-6): no division by zero
+
+
+def test_model_config_from_metadata():  # src/model/mod.rs:213-286
+    table = synth.quant_table(AGN_Q4_K, 96, 256, cfg_index=2)
+    meta = [("general.architecture", "str", "llama"), ("llama.embedding_length", "u32", 256), ("llama.attention.head_count", "u32", 4),
+            ("llama.attention.layer_norm_rms_epsilon", "f32", 1e-5), ("llama.rope.freq_base", "f64", 500000.0),
+            ("llama.block_count", "u64", 2), ("llama.context_length", "u16", 4096)]
+    blob = gw.build(3, meta, [("token_embd.weight", AGN_Q4_K, [256, 96], table)])
+    cfg = GgufFile(data=blob).model_config()
+    assert cfg.architecture == "llama" and cfg.embedding_length == 256 and cfg.block_count == 2 and cfg.context_length == 4096
+    assert cfg.vocab_size == 96 and cfg.rope_freq_base == 500000.0 and abs(cfg.layer_norm_rms_epsilon - 1e-5) < 1e-12
+    assert cfg.feed_forward_length == 0 and cfg.rope_scaling_type is None and cfg.freq_scale == 1.0
+    # head_count is mandatory
+    assert cfg.head_count == 4 and cfg.head_count_kv == 4 and cfg.head_dim == 64  # kv falls back to head_count, dim to H / heads
+    meta = [("general.architecture", "str", "qwen3"), ("qwen3.embedding_length", "u32", 1024), ("qwen3.attention.head_count", "u32", 16),
+            ("qwen3.attention.head_count_kv", "u32", 8), ("qwen3.attention.key_length", "u32", 128),
+            ("qwen3.rope.scaling.type", "str", "linear"), ("qwen3.rope.scaling.factor", "f32", 4.0),
+            ("qwen3.feed_forward_length", "u32", 3072)]
+    with pytest.raises(GgufError):  # "missing metadata: llama.attention.head_count"
+        GgufFile(data=_model_file()[0]).model_config()
+    table = synth.quant_table(AGN_Q4_K, 32, 1024, cfg_index=2)
+    cfg2 = GgufFile(data=gw.build(3, meta, [("token_embd.weight", AGN_Q4_K, [1024, 32], table)])).model_config()
+    assert (cfg2.head_count, cfg2.head_count_kv, cfg2.head_dim, cfg2.feed_forward_length) == (16, 8, 128, 3072)
+    assert cfg2.rope_freq_base == 10000.0 and cfg2.context_length == 4096 and cfg2.block_count == 32 and cfg2.freq_scale == 0.25
+    with pytest.raises(GgufError):  # "missing metadata: general.architecture"
+        GgufFile(data=gw.build(3, [("x.y", "u32", 1)], [("token_embd.weight", AGN_Q4_K, [1024, 32], table)])).model_config()
+
+
 def test_split_index_reference_vectors():  # src/loader.rs:108-119
     from agention_infer_b200.gguf import split_index
     assert split_index("MiniMax-M2.7-UD-IQ4_XS-00001-of-00004.gguf") == (1, 4)
@@ -132,6 +166,17 @@ def test_split_model_maps_the_sibling_files(tmp_path):
     g = GgufFile(str(tmp_path / "m-00001-of-00002.gguf"))
     assert g.tensor_count == 3 and g.find("output_norm.weight").file_offset == cut
     g.close(); g0.close()
+
+
+@pytest.mark.gpu
+def test_dequant_whole_tensor(backend):  # WeightMap::dequant_tensor, src/model/mod.rs:318-345
+    blob, table, norm = _model_file(vocab=40, hidden=768)
+    g = GgufFile(data=blob)
+    out, info = g.dequant_tensor(backend, "token_embd.weight")
+    st, ref = orc.get_rows(orc.Q4_K, table, 40, 768, np.arange(40, dtype=np.uint32))
+    assert st == orc.OK and np.array_equal(backend.read(out, np.float32, (40, 768)).view(np.uint32), ref.view(np.uint32))
+    out, info = g.dequant_tensor(backend, "output_norm.weight")
+    assert np.array_equal(backend.read(out, np.float32, (768,)), norm)
 
 
 @pytest.mark.gpu
