@@ -109,6 +109,7 @@ SIGNATURES = {
     "agn_gguf_get_u64": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
     "agn_gguf_get_f32": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_float)]),
     "agn_gguf_get_string": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_char_p)]),
+    "agn_gguf_get_array_i64": (_i32, [_vp, C.c_char_p, _vp, C.c_uint64, _vp]),
     "agn_gguf_get_array_info": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
     "agn_gguf_tensor_at": (_i32, [_vp, C.c_uint64, _pti]),
     "agn_gguf_find_tensor": (_i32, [_vp, C.c_char_p, _pti]),

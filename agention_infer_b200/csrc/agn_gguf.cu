@@ -28,8 +28,9 @@ struct MetaValue {
     int64_t i = 0;           // signed payload
     double f = 0.0;          // float payload
     std::string s;           // string payload
-    uint32_t elem_type = 0;  // arrays: element type and count (elements are skipped, not kept)
-    uint64_t count = 0;
+    uint32_t elem_type = 0;  // arrays: element type and count; string / float elements are skipped,
+    uint64_t count = 0;      // integer elements are kept (as i64, `MetadataValue::as_i64`) in ints
+    std::vector<int64_t> ints;
 };
 
 struct Tensor {
@@ -138,9 +139,13 @@ bool read_value(Cursor &c, uint32_t type, MetaValue &v, bool keep) {
         v.elem_type = c.read<uint32_t>();
         if (c.ok && (v.elem_type > 12 || v.elem_type == 9)) return false;  // MetadataArrayType::from_u32
         v.count = c.read<uint64_t>();
+        // integer arrays (token types, a per-layer head_count_kv) keep their values; types 0-5, 10, 11
+        const bool ints = v.elem_type <= 5 || v.elem_type == 10 || v.elem_type == 11;
+        const bool is_signed = v.elem_type == 1 || v.elem_type == 3 || v.elem_type == 5 || v.elem_type == 11;
         for (uint64_t k = 0; k < v.count && c.ok; k++) {
             MetaValue e;
             if (!read_value(c, v.elem_type, e, false)) return false;
+            if (keep && ints && c.ok) v.ints.push_back(is_signed ? e.i : (int64_t)e.u);
         }
         break;
     }
@@ -357,6 +362,20 @@ int32_t agn_gguf_get_array_info(const agn_gguf *g, const char *key, uint32_t *el
     if (!v || v->type != 9) return AGN_ENOTFOUND;
     if (elem_type) *elem_type = v->elem_type;
     if (count) *count = v->count;
+    return AGN_OK;
+}
+
+// `GgufFile::get_i64_array` (src/types.rs:451-454): an array of integers of any width as i64.
+// *count receives the array length; up to cap values are copied to out (out may be NULL to ask
+// for the length only).  AGN_ENOTFOUND: no such key, not an array, or not an array of integers.
+int32_t agn_gguf_get_array_i64(const agn_gguf *g, const char *key, int64_t *out, uint64_t cap, uint64_t *count) {
+    const MetaValue *v = find_meta(g, key);
+    if (!v || v->type != 9) return AGN_ENOTFOUND;
+    const bool ints = v->elem_type <= 5 || v->elem_type == 10 || v->elem_type == 11;
+    if (!ints || v->ints.size() != v->count) return AGN_ENOTFOUND;
+    if (count) *count = v->count;
+    if (out)
+        for (uint64_t k = 0; k < v->count && k < cap; k++) out[k] = v->ints[(size_t)k];
     return AGN_OK;
 }
 

@@ -147,6 +147,15 @@ class GgufFile:
             return None
         return int(t.value), int(n.value)
 
+    def get_i64_array(self, key: str) -> Optional[List[int]]:
+        """`GgufFile::get_i64_array` (src/types.rs:451-454): an integer array of any element width, else None."""
+        n = C.c_uint64()
+        if self._lib.agn_gguf_get_array_i64(self._g, key.encode(), None, 0, C.byref(n)) != _abi.AGN_OK:
+            return None
+        buf = (C.c_int64 * max(int(n.value), 1))()
+        self._lib.agn_gguf_get_array_i64(self._g, key.encode(), buf, n.value, C.byref(n))
+        return [int(buf[i]) for i in range(int(n.value))]
+
     def tensors(self) -> List[TensorInfo]:
         out = []
         raw = _abi.TensorInfo()
@@ -162,8 +171,8 @@ class GgufFile:
         return TensorInfo(raw)
 
     def model_config(self) -> ModelConfig:
-        """`ModelConfig::from_gguf` (src/model/mod.rs:213-286).  (A per-layer `head_count_kv` array, which the reference
-        reduces to its maximum, is not read here: the scalar form or the fallback to `head_count` is used.)"""
+        """`ModelConfig::from_gguf` (src/model/mod.rs:213-286); a per-layer `head_count_kv` array (0 for layers without
+        attention) is reduced to its largest positive entry, as the reference does (:236-246)."""
         arch = self.get_string("general.architecture")
         if arch is None:
             raise GgufError(_abi.AGN_ENOTFOUND, "missing metadata: general.architecture")
@@ -180,10 +189,14 @@ class GgufFile:
         if emb is None:
             raise GgufError(_abi.AGN_ENOTFOUND, "missing metadata: token_embd.weight tensor")
         u = lambda f, d: d if self.get_u64(f"{arch}.{f}") is None else self.get_u64(f"{arch}.{f}")
+        head_count_kv = self.get_u64(f"{arch}.attention.head_count_kv")
+        if head_count_kv is None:
+            per_layer = [v for v in (self.get_i64_array(f"{arch}.attention.head_count_kv") or []) if v > 0]
+            head_count_kv = max(per_layer) if per_layer else head_count
         fl = lambda f, d: d if self.get_f32(f"{arch}.{f}") is None else self.get_f32(f"{arch}.{f}")
         return ModelConfig(
             architecture=arch, context_length=u("context_length", 4096), embedding_length=embedding_length,
-            block_count=u("block_count", 32), head_count=head_count, head_count_kv=u("attention.head_count_kv", head_count),
+            block_count=u("block_count", 32), head_count=head_count, head_count_kv=head_count_kv,
             head_dim=key_length if key_length is not None else embedding_length // head_count,
             feed_forward_length=u("feed_forward_length", 0), rope_freq_base=fl("rope.freq_base", 10000.0),
             rope_scaling_type=self.get_string(f"{arch}.rope.scaling.type"),

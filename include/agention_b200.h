@@ -470,6 +470,11 @@ AGN_API uint64_t agn_gguf_data_offset(const agn_gguf *g);
 AGN_API int32_t agn_gguf_get_u64(const agn_gguf *g, const char *key, uint64_t *out);
 AGN_API int32_t agn_gguf_get_f32(const agn_gguf *g, const char *key, float *out);
 AGN_API int32_t agn_gguf_get_string(const agn_gguf *g, const char *key, const char **out);
+/* `GgufFile::get_i64_array` (src/types.rs:451-454): an integer array of any element width as
+ * int64 (token types, a per-layer head_count_kv).  *count = array length; at most cap values are
+ * written to out (NULL: length only).  AGN_ENOTFOUND if the key is absent or not an integer array. */
+AGN_API int32_t agn_gguf_get_array_i64(const agn_gguf *g, const char *key, int64_t *out, uint64_t cap,
+                                       uint64_t *count);
 AGN_API int32_t agn_gguf_get_array_info(const agn_gguf *g, const char *key, uint32_t *elem_type, uint64_t *count);
 AGN_API int32_t agn_gguf_tensor_at(const agn_gguf *g, uint64_t index, agn_tensor_info *out);
 AGN_API int32_t agn_gguf_find_tensor(const agn_gguf *g, const char *name, agn_tensor_info *out);

@@ -95,6 +95,7 @@ def test_file_with_metadata_and_tensors(tmp_path):
         assert abs(g.get_f32("llama.attention.layer_norm_rms_epsilon") - 1e-5) < 1e-12
         assert g.get_f32("llama.rope.freq_base") == 500000.0  # Float64 narrows
         assert g.get_array_info("tokenizer.ggml.tokens") == (8, 5) and g.get_array_info("tokenizer.ggml.scores") == (6, 3)
+        assert g.get_i64_array("tokenizer.ggml.scores") is None and g.get_i64_array("tokenizer.ggml.tokens") is None  # not integers
         emb = g.find("token_embd.weight")
         assert emb.dims == [256, 96] and emb.row_len == 256 and emb.n_rows == 96 and emb.row_bytes == 144
         assert emb.file_offset == g.data_offset + emb.byte_offset and emb.file_offset % 32 == 0
@@ -139,6 +140,12 @@ def test_model_config_from_metadata():  # src/model/mod.rs:213-286
     cfg2 = GgufFile(data=gw.build(3, meta, [("token_embd.weight", AGN_Q4_K, [1024, 32], table)])).model_config()
     assert (cfg2.head_count, cfg2.head_count_kv, cfg2.head_dim, cfg2.feed_forward_length) == (16, 8, 128, 3072)
     assert cfg2.rope_freq_base == 10000.0 and cfg2.context_length == 4096 and cfg2.block_count == 32 and cfg2.freq_scale == 0.25
+    # a per-layer head_count_kv array (LFM2: 0 for the short-conv layers): the largest positive entry
+    meta3 = [("general.architecture", "str", "lfm2"), ("lfm2.embedding_length", "u32", 1024), ("lfm2.attention.head_count", "u32", 16),
+             ("lfm2.attention.head_count_kv", "array", ("i32", [0, 0, 8, 0, 4, 8]))]
+    g3 = GgufFile(data=gw.build(3, meta3, [("token_embd.weight", AGN_Q4_K, [1024, 32], table)]))
+    assert g3.get_i64_array("lfm2.attention.head_count_kv") == [0, 0, 8, 0, 4, 8] and g3.get_i64_array("nope") is None
+    assert g3.model_config().head_count_kv == 8
     with pytest.raises(GgufError):  # "missing metadata: general.architecture"
         GgufFile(data=gw.build(3, [("x.y", "u32", 1)], [("token_embd.weight", AGN_Q4_K, [1024, 32], table)])).model_config()
 
