@@ -251,4 +251,44 @@ class CudaBackend {
     agn_ctx *ctx_ = nullptr;
 };
 
+// A parsed GGUF container (`loader::load` + `parser::parse`, src/loader.rs:14-19, src/parser.rs:9-66):
+// metadata accessors like `GgufFile::get_*` (src/types.rs) and tensor upload for get_rows.
+class GgufFile {
+  public:
+    explicit GgufFile(const std::string &path) {  // memory-maps the file (and the siblings of a split model)
+        char err[256];
+        const int32_t st = agn_gguf_open(path.c_str(), &g_, err, sizeof err);
+        if (st != AGN_OK) throw BackendError(st, err);
+    }
+    GgufFile(const void *data, size_t len) {  // parses caller-owned memory, which must outlive this object
+        char err[256];
+        const int32_t st = agn_gguf_parse(data, len, &g_, err, sizeof err);
+        if (st != AGN_OK) throw BackendError(st, err);
+    }
+    GgufFile(const GgufFile &) = delete;
+    GgufFile &operator=(const GgufFile &) = delete;
+    ~GgufFile() { agn_gguf_close(g_); }
+
+    uint32_t version() const { return agn_gguf_version(g_); }
+    uint64_t tensor_count() const { return agn_gguf_tensor_count(g_); }
+    bool get_u64(const char *key, uint64_t *out) const { return agn_gguf_get_u64(g_, key, out) == AGN_OK; }
+    bool get_f32(const char *key, float *out) const { return agn_gguf_get_f32(g_, key, out) == AGN_OK; }
+    const char *get_string(const char *key) const {  // nullptr when absent or not a string
+        const char *s = nullptr;
+        return agn_gguf_get_string(g_, key, &s) == AGN_OK ? s : nullptr;
+    }
+    bool find(const char *name, agn_tensor_info *out) const { return agn_gguf_find_tensor(g_, name, out) == AGN_OK; }
+    // the tensor's bytes in a new device allocation: the `table` argument of get_rows
+    DeviceBuffer upload(CudaBackend &be, const char *name, agn_tensor_info *info = nullptr) const {
+        void *d = nullptr;
+        agn_tensor_info ti;
+        be.check(agn_gguf_upload_tensor(be.ctx(), g_, name, &d, &ti));
+        if (info) *info = ti;
+        return DeviceBuffer(be.ctx(), d, (size_t)ti.n_bytes);
+    }
+
+  private:
+    agn_gguf *g_ = nullptr;
+};
+
 }  // namespace agn

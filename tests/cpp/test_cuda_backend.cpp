@@ -149,6 +149,31 @@ int main() {
             expect(threw, "dequant_row out of range");
         }
     }
+    {  // a GGUF container parsed from memory: one metadata value, one F32 tensor, uploaded and read back through get_rows
+        std::vector<uint8_t> blob;
+        auto put = [&](const void *p, size_t n) { const uint8_t *b = (const uint8_t *)p; blob.insert(blob.end(), b, b + n); };
+        auto put_u32 = [&](uint32_t v) { put(&v, 4); };
+        auto put_u64 = [&](uint64_t v) { put(&v, 8); };
+        auto put_str = [&](const char *s) { put_u64(std::strlen(s)); put(s, std::strlen(s)); };
+        put("GGUF", 4); put_u32(3); put_u64(1); put_u64(1);           // magic, version, 1 tensor, 1 key
+        put_str("llama.embedding_length"); put_u32(4); put_u32(8);     // u32 value 8
+        put_str("w"); put_u32(2); put_u64(8); put_u64(3); put_u32(0); put_u64(0);  // tensor "w": dims [8, 3], F32, offset 0
+        while (blob.size() % 32) blob.push_back(0);                    // data section alignment
+        std::vector<float> w(24);
+        for (int i = 0; i < 24; i++) w[i] = 0.5f * (float)i - 3.f;
+        put(w.data(), w.size() * 4);
+        agn::GgufFile g(blob.data(), blob.size());
+        uint64_t h = 0;
+        agn_tensor_info ti;
+        auto table = g.upload(be, "w", &ti);
+        const uint32_t ids_h[2] = {2, 0};
+        auto di = be.upload(std::vector<uint32_t>(ids_h, ids_h + 2));
+        auto rows = be.read<float>(be.get_rows(ti.ggml_type, table.ptr(), (size_t)ti.n_bytes, (int64_t)ti.n_rows, (int64_t)ti.row_len,
+                                               di.as<uint32_t>(), 2), 16);
+        bool same = g.get_u64("llama.embedding_length", &h) && h == 8 && g.version() == 3 && ti.n_rows == 3 && ti.row_len == 8;
+        for (int i = 0; i < 8; i++) same = same && rows[i] == w[16 + i] && rows[8 + i] == w[i];
+        expect(same, "GgufFile parse + upload + get_rows");
+    }
     {  // error behaviour: bad argument -> status + message, context still usable
         bool threw = false;
         auto d = be.empty(512);
