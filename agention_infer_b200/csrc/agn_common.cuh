@@ -45,6 +45,7 @@ struct agn_ctx {
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic
     int tune_moe_small_sort;    // 1 = up to 4096 (token, slot) pairs are sorted by one CTA in one launch (default)
+    int tune_softmax_leave_tail; // 1 = softmax leaves entries past the valid length untouched instead of writing 0 (default 0)
     int tune_softmax_cluster;   // rows of 16K-128K entries: 1 = one thread-block cluster per row, CTAs of <= 512 threads
                                 // (default); 2 = CTAs of <= 256 threads; 0 = no clusters
     int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)

@@ -65,6 +65,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_get_rows_threads = 0;
     ctx->tune_softmax_vpt = 0;
     ctx->tune_softmax_cluster = 1;
+    ctx->tune_softmax_leave_tail = 0;
     ctx->tune_moe_small_sort = 1;
     ctx->tune_get_rows_tma = 1;
     ctx->tune_silu_unroll = 4;
@@ -147,6 +148,10 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     }
     if (strcmp(name, "moe_small_sort") == 0) {
         ctx->tune_moe_small_sort = value != 0;
+        return AGN_OK;
+    }
+    if (strcmp(name, "softmax_leave_tail") == 0) {
+        ctx->tune_softmax_leave_tail = value != 0;
         return AGN_OK;
     }
     if (strcmp(name, "softmax_cluster") == 0) {

@@ -95,6 +95,10 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
 /* Options.  "pdl" (default 1): launch kernels with programmatic stream serialization, so
  * that a kernel's launch latency overlaps the tail of the previous kernel of the stream
  * (every kernel still waits for the previous one to complete before its first access).
+ * "softmax_leave_tail" (default 0): 1 makes every softmax entry point leave the output entries past a
+ * row's valid length untouched, as the reference's loop over `scores[..seq_len]` does
+ * (src/model/llama/cpu_path.rs:168-183), instead of writing them as 0; a causal softmax then writes
+ * half as much.
  * Tuning knobs, all with measured defaults: "rms_vpt" (1, 2, 4, 8 vectors per thread; 0 = automatic),
  * "rms_recip" (1: one reciprocal per row, 0: IEEE division per element), "silu_unroll" (2, 4, 8),
  * "silu_threads" (128, 256, 512), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more
