@@ -78,6 +78,7 @@ SIGNATURES = {
     "agn_qk_norm_rope_kv_write_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32, _f32, _f32,
                                              _i32, _i32, _vp, _vp, _i64]),
     "agn_softmax_rows_scaled_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32, _f32, _i32]),
+    "agn_softmax_rows_valid_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _i32, _f32, _i32]),
     "agn_silu_mul_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32]),
     "agn_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
     "agn_add_residual_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),

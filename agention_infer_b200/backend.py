@@ -281,6 +281,18 @@ class CudaBackend:
                                                                 causal_offset, scale, out_dtype))
         return out
 
+    def launch_softmax_rows_valid(self, scores, n_rows: int, row_len: int, out, scale: float = 1.0, out_dtype: int = AGN_F32,
+                                  sums=None, row_stride: Optional[int] = None, n_valid=None, causal_period: int = 0,
+                                  causal_offset: int = 0):
+        """The softmax as the CPU loop leaves its buffer (cpu_path.rs:168-183): entries past a row's valid
+        length are not written.  `out` is required (its tail keeps what it held); f32, f16 or bf16 rows."""
+        if row_stride is None:
+            row_stride = row_len
+        self._check(self._lib.agn_softmax_rows_valid_f32(self._ctx, _ptr(scores), _ptr(out), _ptr(sums), n_rows, row_len,
+                                                         row_stride, _ptr(n_valid), causal_period, causal_offset, scale,
+                                                         out_dtype))
+        return out
+
     def launch_attention_softmax(self, scores, n_heads: int, max_seq: int, pos: int, weights=None, sums=None):
         """The softmax step of `launch_attention(.., pos, n_heads, max_seq)` (resident.rs:551-565) as the reference's
         kernel leaves it: unnormalised weights [n_heads, max_seq] and sums [n_heads] over entries 0..=pos."""

@@ -5,14 +5,22 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <map>
 #include <mutex>
 #include <string>
+#include <tuple>
 
 #include "agention_b200.h"
 
 // Device-side error bits kernels may OR into agn_ctx::d_flags[0].
-#define AGN_FLAG_OOB_ID 1u
-#define AGN_FLAG_TIMEOUT 2u
+#define AGN_FLAG_OOB_ID 1u       // get_rows: token id >= n_rows
+#define AGN_FLAG_TIMEOUT 2u      // a bounded staging wait gave up
+#define AGN_FLAG_OOB_EXPERT 4u   // gather_rows_by_expert: expert index outside [0, n_experts)
+#define AGN_FLAG_OOB_SLOT 8u     // kv_write / fused cache write: position outside [0, max_seq_len)
+
+// Polls of an mbarrier before a staging wait gives up (a few hundred ms at most); the option
+// "mbar_spin_limit" overrides it per context.
+#define AGN_MBAR_SPIN_LIMIT_DEFAULT (1 << 22)
 
 #define AGN_ROPE_CACHE_SLOTS 16
 #define AGN_ROPE_MAX_HALF 512  // n_rot <= 1024
@@ -24,6 +32,7 @@ struct agn_rope_slot {
     uint32_t theta_bits;
     int32_t n_rot;
     bool used;
+    bool in_graph;  // handed out while a graph capture was open: a recorded graph points at it, never evicted
 };
 
 struct agn_ctx {
@@ -45,13 +54,22 @@ struct agn_ctx {
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic
     int tune_moe_small_sort;    // 1 = up to 4096 (token, slot) pairs are sorted by one CTA in one launch (default)
-    int tune_softmax_leave_tail; // 1 = softmax leaves entries past the valid length untouched instead of writing 0 (default 0)
     int tune_softmax_cluster;   // rows of 16K-128K entries: 1 = one thread-block cluster per row, CTAs of <= 512 threads
                                 // (default); 2 = CTAs of <= 256 threads; 0 = no clusters
     int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)
     int tune_get_rows_tma;      // stage the quantised row with one bulk asynchronous copy (TMA)
     int tune_silu_unroll;       // float4 pairs in flight per thread in silu_mul: 2, 4 (default) or 8
     int tune_silu_threads;      // 128, 256 (default) or 512
+    // Persistent kernels with a shared-memory row ring (rows staged by bulk asynchronous copies
+    // ahead of the row being processed).  *_ring: 0 = never, 1 = automatic (default), >= 2 = that
+    // many slots; *_ring_ctas: resident CTAs per SM (0 = as many as fit).
+    int tune_rms_ring, tune_rms_ring_ctas;
+    int tune_rope_ring, tune_rope_ring_ctas;
+    int tune_get_rows_ring, tune_get_rows_ring_ctas;
+    int tune_ring_force;        // 1 = take the persistent form whenever it applies, however few rows (tests)
+    int mbar_spin_limit;        // polls before a staging wait gives up
+    int test_mbar_extra_bytes;  // test hook: get_rows arms its staging barrier for this many bytes more than the
+                                // copy delivers, so the bounded wait runs out (0 in normal use)
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync
@@ -100,6 +118,37 @@ static inline bool agn_aligned(const void *p, int a) { return (reinterpret_cast<
 
 #ifdef __CUDACC__
 
+// --- bulk asynchronous copies (TMA, 1-D, this CTA's own shared memory only; no multicast) -----------
+// A copy needs 16-byte aligned source, destination and size; it completes on an mbarrier whose
+// wait is bounded: after `limit` polls the caller raises AGN_FLAG_TIMEOUT and leaves.
+__device__ __forceinline__ uint32_t agn_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void agn_mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(agn_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void agn_mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void agn_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(agn_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void agn_bulk_g2s(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     agn_smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(agn_smem_u32(bar))
+                 : "memory");
+}
+// true once the phase with the given parity has completed; false after `limit` polls
+__device__ __forceinline__ bool agn_mbar_wait(uint64_t *bar, uint32_t parity, int limit) {
+    const uint32_t b = agn_smem_u32(bar);
+    for (int it = 0; it < limit; it++) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done)
+                     : "r"(b), "r"(parity)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // Programmatic dependent launch.  Every kernel of this library starts with
 // agn_pdl_prologue(): it lets the next kernel in the stream be scheduled onto SMs as this
 // grid's CTAs retire (hiding its launch latency), and it blocks until the previous grid has
@@ -147,6 +196,40 @@ inline void agn_launch_cluster(agn_ctx *ctx, void (*kernel)(KArgs...), dim3 grid
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // errors surface in AGN_LAUNCHED
 }
 
+// Resident CTAs per SM of a persistent kernel for a launch shape, asked of the runtime once per
+// (device, kernel, threads, shared memory).  The first call for a (device, kernel) also opts the
+// kernel in to the device's largest dynamic shared-memory size, once, so that later launches with
+// any smaller or larger ring are all valid.
+template <typename K>
+inline int agn_ring_ctas_per_sm(agn_ctx *ctx, K kernel, int threads, size_t smem) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, const void *, int, size_t>, int> cache;
+    static std::map<std::tuple<int, const void *>, int> opted;  // value: the opt-in limit in bytes, 0 = failed
+    std::lock_guard<std::mutex> lock(mu);
+    const void *kp = reinterpret_cast<const void *>(kernel);
+    auto o = opted.find(std::make_tuple(ctx->device, kp));
+    if (o == opted.end()) {
+        int lim = 0;
+        if (cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device) != cudaSuccess ||
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim) != cudaSuccess) {
+            (void)cudaGetLastError();
+            lim = 0;
+        }
+        o = opted.emplace(std::make_tuple(ctx->device, kp), lim).first;
+    }
+    if ((size_t)o->second < smem + 1024) return 0;  // (static shared memory of the kernel counts against the limit too)
+    const auto key = std::make_tuple(ctx->device, kp, threads, smem);
+    auto f = cache.find(key);
+    if (f != cache.end()) return f->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    cache[key] = n;
+    return n;
+}
+
 __device__ __forceinline__ float agn_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -174,6 +257,8 @@ template <> struct ActVec<float> {
     }
     static __device__ __forceinline__ float load1(const float *p, int64_t i) { return p[i]; }
     static __device__ __forceinline__ void store1(float *p, int64_t i, float v) { p[i] = v; }
+    // the same four activations from a staged row in shared memory
+    static __device__ __forceinline__ float4 load_shared(const float *p, int vec) { return reinterpret_cast<const float4 *>(p)[vec]; }
 };
 #include <cuda_fp16.h>
 template <> struct ActVec<__half> {
@@ -193,6 +278,12 @@ template <> struct ActVec<__half> {
     }
     static __device__ __forceinline__ float load1(const __half *p, int64_t i) { return __half2float(p[i]); }
     static __device__ __forceinline__ void store1(__half *p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+    static __device__ __forceinline__ float4 load_shared(const __half *p, int vec) {
+        const uint2 r = reinterpret_cast<const uint2 *>(p)[vec];
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
 };
 
 #include <cuda_bf16.h>

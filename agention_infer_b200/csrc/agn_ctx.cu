@@ -65,11 +65,19 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_get_rows_threads = 0;
     ctx->tune_softmax_vpt = 0;
     ctx->tune_softmax_cluster = 1;
-    ctx->tune_softmax_leave_tail = 0;
     ctx->tune_moe_small_sort = 1;
     ctx->tune_get_rows_tma = 1;
     ctx->tune_silu_unroll = 4;
     ctx->tune_silu_threads = 256;
+    ctx->tune_rms_ring = 1;
+    ctx->tune_rms_ring_ctas = 0;
+    ctx->tune_rope_ring = 1;
+    ctx->tune_rope_ring_ctas = 0;
+    ctx->tune_get_rows_ring = 1;
+    ctx->tune_get_rows_ring_ctas = 0;
+    ctx->tune_ring_force = 0;
+    ctx->mbar_spin_limit = AGN_MBAR_SPIN_LIMIT_DEFAULT;
+    ctx->test_mbar_extra_bytes = 0;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -150,10 +158,6 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
         ctx->tune_moe_small_sort = value != 0;
         return AGN_OK;
     }
-    if (strcmp(name, "softmax_leave_tail") == 0) {
-        ctx->tune_softmax_leave_tail = value != 0;
-        return AGN_OK;
-    }
     if (strcmp(name, "softmax_cluster") == 0) {
         ctx->tune_softmax_cluster = (int)value;
         return AGN_OK;
@@ -173,6 +177,27 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     if (strcmp(name, "rms_recip") == 0) {
         ctx->tune_rms_recip = value != 0;
         return AGN_OK;
+    }
+    {
+        struct { const char *name; int *field; int64_t lo, hi; } ints[] = {
+            {"rms_ring", &ctx->tune_rms_ring, 0, 8},
+            {"rms_ring_ctas", &ctx->tune_rms_ring_ctas, 0, 32},
+            {"rope_ring", &ctx->tune_rope_ring, 0, 8},
+            {"rope_ring_ctas", &ctx->tune_rope_ring_ctas, 0, 32},
+            {"get_rows_ring", &ctx->tune_get_rows_ring, 0, 16},
+            {"get_rows_ring_ctas", &ctx->tune_get_rows_ring_ctas, 0, 32},
+            {"ring_force", &ctx->tune_ring_force, 0, 1},
+            {"mbar_spin_limit", &ctx->mbar_spin_limit, 1, 1 << 30},
+            {"test_mbar_extra_bytes", &ctx->test_mbar_extra_bytes, 0, 1 << 20},
+        };
+        for (auto &o : ints) {
+            if (strcmp(name, o.name) != 0) continue;
+            if (value < o.lo || value > o.hi)
+                return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: %s=%lld outside [%lld, %lld]", name, (long long)value,
+                                (long long)o.lo, (long long)o.hi);
+            *o.field = (int)value;
+            return AGN_OK;
+        }
     }
     return agn_fail(ctx, AGN_EINVAL, "agn_ctx_set_option: unknown option '%s'", name);
 }
@@ -229,6 +254,7 @@ int32_t agn_memcpy_h2d(agn_ctx *ctx, void *dst, const void *src, size_t bytes) {
     AGN_CHECK_CTX(ctx);
     if (bytes == 0) return AGN_OK;
     if (!dst || !src) return agn_fail(ctx, AGN_EINVAL, "agn_memcpy_h2d: null pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     return AGN_OK;
 }
@@ -237,6 +263,7 @@ int32_t agn_memcpy_d2h(agn_ctx *ctx, void *dst, const void *src, size_t bytes) {
     AGN_CHECK_CTX(ctx);
     if (bytes == 0) return AGN_OK;
     if (!dst || !src) return agn_fail(ctx, AGN_EINVAL, "agn_memcpy_d2h: null pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     return AGN_OK;
 }
@@ -245,6 +272,7 @@ int32_t agn_memset(agn_ctx *ctx, void *dst, int value, size_t bytes) {
     AGN_CHECK_CTX(ctx);
     if (bytes == 0) return AGN_OK;
     if (!dst) return agn_fail(ctx, AGN_EINVAL, "agn_memset: null pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream));
     return AGN_OK;
 }
@@ -252,6 +280,7 @@ int32_t agn_memset(agn_ctx *ctx, void *dst, int value, size_t bytes) {
 int32_t agn_sync(agn_ctx *ctx) {
     AGN_CHECK_CTX(ctx);
     if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_sync: not allowed while a graph capture is open");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     if (ctx->flags_dirty) {
         AGN_CUDA(ctx, cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     }
@@ -264,7 +293,14 @@ int32_t agn_sync(agn_ctx *ctx) {
             AGN_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
             if (f & AGN_FLAG_TIMEOUT)
                 return agn_fail(ctx, AGN_ETIMEOUT, "a staging wait in a kernel gave up; outputs of that launch are invalid");
-            return agn_fail(ctx, AGN_EOOB_ID, "get_rows: row index out of range (those output rows are zero)");
+            // one bit per class of index, so the message names the op that met it
+            std::string msg;
+            if (f & AGN_FLAG_OOB_ID) msg += "get_rows: row index out of range (those output rows are zero); ";
+            if (f & AGN_FLAG_OOB_EXPERT) msg += "gather_rows_by_expert: expert index out of range (those pairs are dropped); ";
+            if (f & AGN_FLAG_OOB_SLOT) msg += "kv_write: position outside the cache (those tokens are not written); ";
+            if (msg.empty()) msg = "a kernel reported an index out of range; ";
+            msg.resize(msg.size() - 2);
+            return agn_fail(ctx, AGN_EOOB_ID, "%s", msg.c_str());
         }
     }
     return AGN_OK;
@@ -273,6 +309,7 @@ int32_t agn_sync(agn_ctx *ctx) {
 int32_t agn_event_create(agn_ctx *ctx, agn_event **ev) {
     AGN_CHECK_CTX(ctx);
     if (!ev) return agn_fail(ctx, AGN_EINVAL, "agn_event_create: null out pointer");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     agn_event *e = new agn_event();
     cudaError_t ce = cudaEventCreate(&e->ev);
     if (ce != cudaSuccess) {
@@ -286,6 +323,7 @@ int32_t agn_event_create(agn_ctx *ctx, agn_event **ev) {
 int32_t agn_event_record(agn_ctx *ctx, agn_event *ev) {
     AGN_CHECK_CTX(ctx);
     if (!ev) return agn_fail(ctx, AGN_EINVAL, "agn_event_record: null event");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaEventRecord(ev->ev, ctx->stream));
     return AGN_OK;
 }
@@ -391,6 +429,7 @@ extern "C" int32_t agn_graph_end(agn_ctx *ctx, agn_graph **out) {
 extern "C" int32_t agn_graph_launch(agn_ctx *ctx, agn_graph *g) {
     AGN_CHECK_CTX(ctx);
     if (!g || !g->exec) return agn_fail(ctx, AGN_EINVAL, "agn_graph_launch: null graph");
+    AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     AGN_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
     ctx->launches += g->kernels;
     return AGN_OK;
@@ -431,12 +470,25 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
     for (int s = 0; s < AGN_ROPE_CACHE_SLOTS; s++) {
         const agn_rope_slot &sl = ctx->rope_slots[s];
         if (sl.used && sl.theta_bits == bits && sl.n_rot == n_rot) {
+            if (ctx->capturing) ctx->rope_slots[s].in_graph = true;
             *d_table = ctx->d_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
             return AGN_OK;
         }
     }
-    const int s = ctx->rope_next;
-    ctx->rope_next = (ctx->rope_next + 1) % AGN_ROPE_CACHE_SLOTS;
+    // Building a table copies from a pinned staging slot and may synchronise the stream: neither
+    // can be recorded into a graph (a replay would re-copy whatever the staging slot holds by then).
+    if (ctx->capturing)
+        return agn_fail(ctx, AGN_EINVAL, "rope: the table for theta=%g n_rot=%d does not exist yet; run the op once before "
+                        "recording it into a graph", (double)theta, n_rot);
+    // round robin over the slots that no recorded graph points at
+    int s = -1;
+    for (int k = 0; k < AGN_ROPE_CACHE_SLOTS; k++) {
+        const int c = (ctx->rope_next + k) % AGN_ROPE_CACHE_SLOTS;
+        if (!ctx->rope_slots[c].in_graph) { s = c; break; }
+    }
+    if (s < 0)
+        return agn_fail(ctx, AGN_EINVAL, "rope: all %d (theta, n_rot) table slots are in use by recorded graphs", AGN_ROPE_CACHE_SLOTS);
+    ctx->rope_next = (s + 1) % AGN_ROPE_CACHE_SLOTS;
     float *h = ctx->h_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
     float *d = ctx->d_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
     if (ctx->rope_slots[s].used) {

@@ -272,82 +272,9 @@ __device__ __forceinline__ void cp_async_wait_all() {
 // thread and completed on an mbarrier; it needs 16-byte aligned source, destination and size,
 // which holds whenever the 16-byte rounded row lies inside the table.  Otherwise (the last
 // bytes of the table) 16-byte cp.async copies with a byte-wise tail.
-constexpr int MBAR_SPIN_LIMIT = 1 << 22;  // bounded wait: a few hundred ms at most, then an error flag
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a), "r"(count) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-}
-__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(b), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(d),
-                 "l"(gmem_src), "r"(bytes), "r"(b)
-                 : "memory");
-}
-// true once the phase with the given parity has completed; gives up after MBAR_SPIN_LIMIT polls
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
-    for (int it = 0; it < MBAR_SPIN_LIMIT; it++) {
-        uint32_t done;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done)
-                     : "r"(b), "r"(parity)
-                     : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-template <int DTYPE, typename OUT, bool VEC_OUT, bool TMA>
-__global__ void __launch_bounds__(256)
-get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
-                const uint32_t *__restrict__ ids, OUT *__restrict__ out, uint32_t *flags) {
-    extern __shared__ __align__(128) uint8_t stage[];
-    __shared__ __align__(8) uint64_t bar;
-    if (TMA) {
-        if (threadIdx.x == 0) mbar_init(&bar, 1);
-        __syncthreads();  // barrier initialised before anyone polls it (runs ahead of the dependency wait)
-    }
-    agn_pdl_prologue();
-    const int64_t t = blockIdx.x;
-    const uint32_t id = ids[t];
-    OUT *o_row = out + t * (int64_t)row_len;
-    if ((int64_t)id >= n_rows) {
-        // "row index out of range": zero row + error flag, never a trap
-        for (int j = threadIdx.x; j < row_len; j += blockDim.x) ActVec<OUT>::store1(o_row, j, 0.0f);
-        if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_OOB_ID);
-        return;
-    }
-    const size_t start = (size_t)id * (size_t)row_bytes;
-    const size_t a0 = start & ~(size_t)15;
-    const int lead = (int)(start - a0);
-    const int n16 = (lead + row_bytes + 15) >> 4;
-    const bool bulk = TMA && a0 + 16 * (size_t)n16 <= table_bytes;  // same answer in every thread of the CTA
-    if (bulk) {
-        if (threadIdx.x == 0) bulk_load(stage, table + a0, 16u * (uint32_t)n16, &bar);
-        if (!mbar_wait(&bar, 0)) {
-            // the copy may still be writing shared memory: wait once more, bounded, before leaving
-            if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_TIMEOUT);
-            (void)mbar_wait(&bar, 0);
-            return;
-        }
-    } else {
-        for (int c = threadIdx.x; c < n16; c += blockDim.x) {
-            const size_t off = a0 + 16 * (size_t)c;
-            if (off + 16 <= table_bytes) {
-                cp_async16(stage + 16 * c, table + off);
-            } else {
-                // last chunk of the table: copy only the bytes that exist
-                for (int b = 0; b < 16; b++) stage[16 * c + b] = off + b < table_bytes ? table[off + b] : 0;
-            }
-        }
-        cp_async_wait_all();
-        __syncthreads();
-    }
-    const uint8_t *row = stage + lead;
+// Decodes a staged row and writes its row_len outputs.
+template <int DTYPE, typename OUT, bool VEC_OUT>
+__device__ __forceinline__ void decode_row(const uint8_t *row, int row_len, OUT *o_row) {
     // a partial last block is fully present in the table (type_size rounds up to whole blocks),
     // so decoding past row_len inside it stays in bounds; only the stores are clipped
     // K-quant units are numbered per 256-value super-block (32 units each, not in element order)
@@ -384,9 +311,180 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     }
 }
 
+// 16-byte cp.async copies of the 16-byte-rounded row, byte-wise for a last chunk that would
+// reach past the end of the table.
+__device__ __forceinline__ void stage_row_chunks(uint8_t *stage, const uint8_t *table, size_t table_bytes, size_t a0, int n16) {
+    for (int c = threadIdx.x; c < n16; c += blockDim.x) {
+        const size_t off = a0 + 16 * (size_t)c;
+        if (off + 16 <= table_bytes) {
+            cp_async16(stage + 16 * c, table + off);
+        } else {
+            for (int b = 0; b < 16; b++) stage[16 * c + b] = off + b < table_bytes ? table[off + b] : 0;
+        }
+    }
+    cp_async_wait_all();
+}
+
+template <int DTYPE, typename OUT, bool VEC_OUT, bool TMA>
+__global__ void __launch_bounds__(256)
+get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
+                const uint32_t *__restrict__ ids, OUT *__restrict__ out, uint32_t *flags, int spin_limit, int test_extra_bytes) {
+    extern __shared__ __align__(128) uint8_t stage[];
+    __shared__ __align__(8) uint64_t bar;
+    if (TMA) {
+        if (threadIdx.x == 0) {
+            agn_mbar_init(&bar, 1);
+            agn_mbar_init_fence();
+        }
+        __syncthreads();  // barrier initialised before anyone polls it (runs ahead of the dependency wait)
+    }
+    agn_pdl_prologue();
+    const int64_t t = blockIdx.x;
+    const uint32_t id = ids[t];
+    OUT *o_row = out + t * (int64_t)row_len;
+    if ((int64_t)id >= n_rows) {
+        // "row index out of range": zero row + error flag, never a trap
+        for (int j = threadIdx.x; j < row_len; j += blockDim.x) ActVec<OUT>::store1(o_row, j, 0.0f);
+        if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_OOB_ID);
+        return;
+    }
+    const size_t start = (size_t)id * (size_t)row_bytes;
+    const size_t a0 = start & ~(size_t)15;
+    const int lead = (int)(start - a0);
+    const int n16 = (lead + row_bytes + 15) >> 4;
+    const bool bulk = TMA && a0 + 16 * (size_t)n16 <= table_bytes;  // same answer in every thread of the CTA
+    if (bulk) {
+        if (threadIdx.x == 0) {
+            // test_extra_bytes is 0 outside the test of the bounded wait, which arms the barrier
+            // for more bytes than the copy brings so that the wait below runs out
+            agn_mbar_expect_tx(&bar, 16u * (uint32_t)n16 + (uint32_t)test_extra_bytes);
+            agn_bulk_g2s(stage, table + a0, 16u * (uint32_t)n16, &bar);
+        }
+        if (!agn_mbar_wait(&bar, 0, spin_limit)) {
+            // the copy may still be writing shared memory: wait once more, bounded, before leaving
+            if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_TIMEOUT);
+            (void)agn_mbar_wait(&bar, 0, spin_limit);
+            return;
+        }
+    } else {
+        stage_row_chunks(stage, table, table_bytes, a0, n16);
+        __syncthreads();
+    }
+    decode_row<DTYPE, OUT, VEC_OUT>(stage + lead, row_len, o_row);
+}
+
+// Persistent form: a few small CTAs per SM, each looping over tokens blockIdx.x, blockIdx.x +
+// gridDim.x, ...  The quantised rows of the CTA's next `slots` tokens are already on their way
+// into a ring of shared-memory slots (thread 0 reads their ids and issues one bulk copy each)
+// while the current row is decoded, so the id -> row address -> row bytes latency chain of a
+// token is hidden behind the decode of the tokens before it.
+template <int DTYPE, typename OUT, bool VEC_OUT>
+__global__ void __launch_bounds__(256)
+get_rows_ring_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
+                     const uint32_t *__restrict__ ids, OUT *__restrict__ out, int64_t T, int slots, int slot_bytes,
+                     uint32_t *flags, int spin_limit) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(ring + (size_t)slots * slot_bytes);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < slots; s++) agn_mbar_init(&full[s], 1);
+        agn_mbar_init_fence();
+    }
+    __syncthreads();
+    agn_pdl_launch_dependents();
+    agn_pdl_wait();
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    const int n_my = first < T ? (int)((T - first + stride - 1) / stride) : 0;
+    // Whether a token's row comes by bulk copy is a function of its id alone, so the issuing
+    // thread and the consuming threads reach the same answer independently.
+    auto row_span = [&](uint32_t id, size_t &a0, int &lead, int &n16) -> int {  // 0: id out of range, 1: bulk copy, 2: chunked copy
+        if ((int64_t)id >= n_rows) return 0;
+        const size_t start = (size_t)id * (size_t)row_bytes;
+        a0 = start & ~(size_t)15;
+        lead = (int)(start - a0);
+        n16 = (lead + row_bytes + 15) >> 4;
+        return a0 + 16 * (size_t)n16 <= table_bytes ? 1 : 2;
+    };
+    auto issue = [&](int j) {  // thread 0 only
+        size_t a0; int lead, n16;
+        if (row_span(ids[first + (int64_t)j * stride], a0, lead, n16) != 1) return;
+        uint64_t *bar = &full[j % slots];
+        agn_mbar_expect_tx(bar, 16u * (uint32_t)n16);
+        agn_bulk_g2s(ring + (size_t)(j % slots) * slot_bytes, table + a0, 16u * (uint32_t)n16, bar);
+    };
+    if (threadIdx.x == 0)
+        for (int j = 0; j < slots && j < n_my; j++) issue(j);
+
+    // parity of a slot's barrier flips only when a bulk copy completed on it
+    uint32_t phase_bits = 0;  // bit s: parity the next wait on slot s expects
+    for (int it = 0; it < n_my; it++) {
+        const int slot = it % slots;
+        const int64_t t = first + (int64_t)it * stride;
+        OUT *o_row = out + t * (int64_t)row_len;
+        uint8_t *stage = ring + (size_t)slot * slot_bytes;
+        size_t a0 = 0; int lead = 0, n16 = 0;
+        const int kind = row_span(ids[t], a0, lead, n16);
+        int failed = 0;
+        if (kind == 1) {
+            failed = !agn_mbar_wait(&full[slot], (phase_bits >> slot) & 1u, spin_limit);
+            phase_bits ^= 1u << slot;
+        } else if (kind == 2) {
+            stage_row_chunks(stage, table, table_bytes, a0, n16);
+            __syncthreads();
+        }
+        if (kind == 0) {
+            for (int j = threadIdx.x; j < row_len; j += blockDim.x) ActVec<OUT>::store1(o_row, j, 0.0f);
+            if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_OOB_ID);
+        } else if (!failed) {
+            decode_row<DTYPE, OUT, VEC_OUT>(stage + lead, row_len, o_row);
+        }
+        // every thread is done with the slot; one CTA-wide answer to "did any thread's wait run
+        // out", so that all threads leave together
+        if (__syncthreads_or(failed)) {
+            // report it and give the copies still in flight (they target this
+            // CTA's shared memory) one more bounded wait each before leaving
+            if (threadIdx.x == 0) {
+                atomicOr(flags, AGN_FLAG_TIMEOUT);
+                for (int j = it; j < n_my && j < it + slots; j++) {
+                    size_t b0; int l2, m16;
+                    const bool waited_already = j == it;  // its parity bit has been flipped above
+                    if (row_span(ids[first + (int64_t)j * stride], b0, l2, m16) == 1)
+                        (void)agn_mbar_wait(&full[j % slots], ((phase_bits >> (j % slots)) & 1u) ^ (waited_already ? 1u : 0u), spin_limit);
+                }
+            }
+            return;
+        }
+        if (threadIdx.x == 0 && it + slots < n_my) issue(it + slots);
+    }
+}
+
+template <int DTYPE, typename OUT, bool VEC_OUT>
+bool launch_get_rows_ring(agn_ctx *ctx, int threads, const uint8_t *table, size_t table_bytes, int64_t n_rows, int row_len,
+                          int row_bytes, const uint32_t *ids, int64_t T, OUT *out) {
+    if (ctx->tune_get_rows_ring == 0 || !ctx->tune_get_rows_tma || ctx->test_mbar_extra_bytes) return false;
+    const int slot_bytes = (((row_bytes + 15) / 16 + 2) * 16 + 127) & ~127;
+    int slots = ctx->tune_get_rows_ring >= 2 ? ctx->tune_get_rows_ring : 4;
+    while (slots > 2 && (size_t)slots * slot_bytes > 48 * 1024) slots--;
+    const size_t smem = (size_t)slots * slot_bytes + 8 * (size_t)slots;
+    if (smem > 200 * 1024) return false;
+    auto kernel = get_rows_ring_kernel<DTYPE, OUT, VEC_OUT>;
+    int per_sm = agn_ring_ctas_per_sm(ctx, kernel, threads, smem);
+    if (per_sm < 1) return false;
+    if (ctx->tune_get_rows_ring_ctas > 0 && ctx->tune_get_rows_ring_ctas < per_sm) per_sm = ctx->tune_get_rows_ring_ctas;
+    int64_t grid = (int64_t)per_sm * ctx->sm_count;
+    if (T < 2 * grid && !ctx->tune_ring_force) return false;  // too few tokens per CTA for a ring to pay
+    if (grid > T) grid = T;
+    agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, T,
+               slots, slot_bytes, ctx->d_flags, ctx->mbar_spin_limit);
+    return true;
+}
+
 template <int DTYPE, typename OUT>
-cudaError_t launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, size_t smem, const uint8_t *table,
+cudaError_t launch_get_rows(agn_ctx *ctx, bool vec, int64_t T, int threads, size_t smem, const uint8_t *table,
                             size_t table_bytes, int64_t n_rows, int row_len, int row_bytes, const uint32_t *ids, OUT *out) {
+    if (vec ? launch_get_rows_ring<DTYPE, OUT, true>(ctx, threads, table, table_bytes, n_rows, row_len, row_bytes, ids, T, out)
+            : launch_get_rows_ring<DTYPE, OUT, false>(ctx, threads, table, table_bytes, n_rows, row_len, row_bytes, ids, T, out))
+        return cudaSuccess;
+    const unsigned grid = (unsigned)T;
     cudaError_t e = cudaSuccess;
     if (smem > 48 * 1024) {  // opt in to large dynamic shared memory for very long rows
         e = cudaFuncSetAttribute(get_rows_kernel<DTYPE, OUT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -396,14 +494,15 @@ cudaError_t launch_get_rows(agn_ctx *ctx, bool vec, unsigned grid, int threads, 
         if (e != cudaSuccess) return e;
     }
     const bool tma = ctx->tune_get_rows_tma != 0;
+    const int lim = ctx->mbar_spin_limit, extra = ctx->test_mbar_extra_bytes;
     if (vec && tma)
-        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags, lim, extra);
     else if (vec)
-        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags, lim, extra);
     else if (tma)
-        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags, lim, extra);
     else
-        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags);
+        agn_launch(ctx, get_rows_kernel<DTYPE, OUT, false, false>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags, lim, extra);
     return cudaSuccess;
 }
 
@@ -421,9 +520,9 @@ int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t
     if (T == 0) return AGN_OK;
     if (!table || !ids || !out) return agn_fail(ctx, AGN_EINVAL, "get_rows: null pointer");
     if (!agn_aligned16(table)) return agn_fail(ctx, AGN_EINVAL, "get_rows: table must be 16-byte aligned");
-    if ((size_t)n_rows * row_bytes > table_bytes)
-        return agn_fail(ctx, AGN_EINVAL, "get_rows: tensor rows extend beyond the data (need %zu bytes, have %zu)",
-                        (size_t)n_rows * row_bytes, table_bytes);
+    if (row_bytes == 0 || (size_t)n_rows > table_bytes / row_bytes)  // division: n_rows * row_bytes may not fit 64 bits
+        return agn_fail(ctx, AGN_EINVAL, "get_rows: tensor rows extend beyond the data (%lld rows of %zu bytes, have %zu)",
+                        (long long)n_rows, row_bytes, table_bytes);
     if (row_bytes + 32 > 200 * 1024) return agn_fail(ctx, AGN_EINVAL, "get_rows: row of %zu bytes exceeds the staging buffer", row_bytes);
     if (T > 0x7fffffffLL || row_len > 0x3fffffffLL) return agn_fail(ctx, AGN_EINVAL, "get_rows: T or row_len too large");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -437,19 +536,18 @@ int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t
     if (ctx->tune_get_rows_threads >= 32 && ctx->tune_get_rows_threads <= 256) threads = ctx->tune_get_rows_threads & ~31;
     const size_t smem = ((row_bytes + 15) / 16 + 2) * 16;
     const uint8_t *tb = static_cast<const uint8_t *>(table);
-    const unsigned grid = (unsigned)T;
     const int rl = (int)row_len, rb = (int)row_bytes;
     cudaError_t e;
     switch (dtype) {
-    case AGN_Q8_0: e = launch_get_rows<AGN_Q8_0, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q4_K: e = launch_get_rows<AGN_Q4_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q6_K: e = launch_get_rows<AGN_Q6_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q5_K: e = launch_get_rows<AGN_Q5_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q2_K: e = launch_get_rows<AGN_Q2_K, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_Q5_0: e = launch_get_rows<AGN_Q5_0, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_F16: e = launch_get_rows<AGN_F16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    case AGN_BF16: e = launch_get_rows<AGN_BF16, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
-    default: e = launch_get_rows<AGN_F32, OUT>(ctx, vec, grid, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q8_0: e = launch_get_rows<AGN_Q8_0, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q4_K: e = launch_get_rows<AGN_Q4_K, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q6_K: e = launch_get_rows<AGN_Q6_K, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_K: e = launch_get_rows<AGN_Q5_K, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q2_K: e = launch_get_rows<AGN_Q2_K, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_Q5_0: e = launch_get_rows<AGN_Q5_0, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_F16: e = launch_get_rows<AGN_F16, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    case AGN_BF16: e = launch_get_rows<AGN_BF16, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
+    default: e = launch_get_rows<AGN_F32, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     }
     AGN_CUDA(ctx, e);
     ctx->flags_dirty = true;

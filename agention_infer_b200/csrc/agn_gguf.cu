@@ -111,10 +111,11 @@ struct agn_gguf {
     std::vector<Part> parts;
 
     // `MultiFileMmap::slice`: the bytes [offset, offset + n) if they lie inside one file, else null
+    // (offsets and sizes come from the file: every comparison is written so that it cannot wrap)
     const uint8_t *slice(uint64_t offset, uint64_t n) const {
-        if (offset + n <= len) return data + offset;
+        if (n <= len && offset <= len - n) return data + offset;
         for (const Part &p : parts)
-            if (p.start <= offset && offset + n <= p.start + p.len)
+            if (p.start <= offset && n <= p.len && offset - p.start <= p.len - n)
                 return static_cast<const uint8_t *>(p.mapping) + (offset - p.start);
         return nullptr;
     }
@@ -388,12 +389,21 @@ int32_t agn_gguf_tensor_at(const agn_gguf *g, uint64_t index, agn_tensor_info *o
     out->n_dims = t.n_dims;
     for (int d = 0; d < 4; d++) out->dims[d] = t.dims[d];
     out->byte_offset = t.byte_offset;
+    // dims and offsets are whatever the file says: a product or sum that does not fit 64 bits is a
+    // malformed file (the reference's checked slices reject it, src/quant/mod.rs:124-131), never
+    // a wrapped-around small number
+    if (t.byte_offset > UINT64_MAX - g->data_offset) return AGN_EFORMAT;
     out->file_offset = g->data_offset + t.byte_offset;
     uint64_t rows = 1;
-    for (uint32_t d = 1; d < t.n_dims; d++) rows *= t.dims[d];
+    for (uint32_t d = 1; d < t.n_dims; d++) {
+        if (t.dims[d] != 0 && rows > UINT64_MAX / t.dims[d]) return AGN_EFORMAT;
+        rows *= t.dims[d];
+    }
     out->n_rows = t.n_dims <= 1 ? 1 : rows;
     out->row_len = t.n_dims >= 1 ? t.dims[0] : 0;
+    if (out->row_len > (UINT64_MAX >> 4)) return AGN_EFORMAT;  // type_size rounds up to blocks of at most 256 bytes per value group
     out->row_bytes = agn_type_size((int32_t)t.ggml_type, (size_t)out->row_len);  // 0: no codec for this type
+    if (out->n_rows != 0 && out->row_bytes > UINT64_MAX / out->n_rows) return AGN_EFORMAT;
     out->n_bytes = out->row_bytes * out->n_rows;
     return AGN_OK;
 }
@@ -412,7 +422,9 @@ int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name
     if (!g || !name || !dptr) return agn_fail(ctx, AGN_EINVAL, "agn_gguf_upload_tensor: null argument");
     *dptr = nullptr;
     agn_tensor_info ti;
-    if (agn_gguf_find_tensor(g, name, &ti) != AGN_OK) return agn_fail(ctx, AGN_ENOTFOUND, "tensor '%s' not found", name);
+    const int32_t frc = agn_gguf_find_tensor(g, name, &ti);
+    if (frc == AGN_EFORMAT) return agn_fail(ctx, AGN_EFORMAT, "tensor '%s': dimensions or offset overflow 64 bits", name);
+    if (frc != AGN_OK) return agn_fail(ctx, AGN_ENOTFOUND, "tensor '%s' not found", name);
     if (ti.row_bytes == 0)
         return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "tensor '%s' has ggml type %d, which has no codec here", name, ti.ggml_type);
     // "tensor row .. extends beyond data section", src/quant/mod.rs:124-131; in a split model the

@@ -48,7 +48,7 @@ kv_write_q8_0_kernel(const KvArgs a) {
     const float *src_row = (blockIdx.y ? a.v : a.k) + t * a.hd;
     const int64_t slot = kv_slot(a, t);
     if (slot < 0) {  // same answer for the whole CTA
-        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
         return;
     }
     unsigned char *tok = (blockIdx.y ? a.v_cache : a.k_cache) + slot * a.bytes_per_token;
@@ -81,7 +81,7 @@ kv_write_q8_0_kernel(const KvArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             float r = roundf(__fdiv_rn(x[i], scale));
-            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0 (a NaN value, or inf / inf)
             q[i] = (unsigned char)(signed char)(int)r;
         }
         if (e0 + 3 < left) {  // blocks are 2-byte aligned: two 16-bit stores
@@ -101,7 +101,7 @@ kv_write_f16_kernel(const KvArgs a) {
     const int64_t t = blockIdx.x;
     const int64_t slot = kv_slot(a, t);
     if (slot < 0) {
-        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);
+        if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
         return;
     }
     const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd;

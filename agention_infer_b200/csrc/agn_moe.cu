@@ -61,7 +61,7 @@ expert_count_kernel(const int32_t *__restrict__ idx, int64_t n_pairs, int E, int
     if (i < n_pairs) {
         const int e = idx[i];
         if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
-        else atomicOr(flags, AGN_FLAG_OOB_ID);
+        else atomicOr(flags, AGN_FLAG_OOB_EXPERT);
     }
     __syncthreads();
     if (threadIdx.x < E) chunk_counts[(int64_t)blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
@@ -159,7 +159,7 @@ expert_sort_small_kernel(const int32_t *__restrict__ idx, int n_pairs, int E, in
         if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) base[warp][e] += __popc(same);  // one lane per expert present
         __syncwarp();
     }
-    if (bad) atomicOr(flags, AGN_FLAG_OOB_ID);
+    if (bad) atomicOr(flags, AGN_FLAG_OOB_EXPERT);
     __syncthreads();
     if (threadIdx.x < E) {  // exclusive scan over the warps of one expert
         const int e = threadIdx.x;
@@ -321,12 +321,17 @@ extern "C" int32_t agn_gather_rows_by_expert_f32(agn_ctx *ctx, const float *x, c
 // creation allocates the workspace this op normally uses.  This entry point therefore takes
 // no context and gets its scratch from a fixed array that is part of the loaded library.
 //
-// The array lives in every GPU that loads the library, from load until exit; its size is the
-// limit of the problem size (see AGN_NOALLOC_SCRATCH_BYTES).  All calls share it: it still
+// The array lives in every GPU on which the library's device code has been loaded (with lazy
+// module loading: from the first call on that device, which is why hosts make a T = 0 warm-up
+// call at start-up) until the process exits; its size is the limit of the problem size (see
+// AGN_NOALLOC_SCRATCH_BYTES).  All calls share it: it still
 // holds the previous call's counts when the next call starts, and two calls that run on the
 // GPU at the same time (different streams, no event between them) overwrite each other.
 #define AGN_NOALLOC_SCRATCH_BYTES (256 * 1024)
-#define AGN_NOALLOC_HEADER_BYTES 256  // word 0: "an expert index was out of range" flag
+// Word 0 of the header takes the count kernel's "expert index out of range" bit.  It is write-only
+// here: no entry point reads it back (that would need a synchronisation); the kernel is shared
+// with the context-based op, which does report the bit.  A dropped pair shows in the outputs instead.
+#define AGN_NOALLOC_HEADER_BYTES 256
 static __device__ __align__(256) unsigned char g_noalloc_scratch[AGN_NOALLOC_SCRATCH_BYTES];
 
 namespace {
@@ -373,7 +378,8 @@ extern "C" int32_t agn_gather_rows_by_expert_noalloc_f32(void *cuda_stream, cons
                             cudaGetErrorString(e));
     }
     // Set-up, once per device, with that device current: in host code the array's name is
-    // only a handle; the address kernels can use comes from cudaGetSymbolAddress.
+    // only a handle; the address kernels can use comes from cudaGetSymbolAddress.  The stream
+    // must belong to this (the current) device.
     void *scratch = nullptr;
     {
         std::lock_guard<std::mutex> lock(g_noalloc_mutex);

@@ -72,7 +72,7 @@ __device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_h
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 float r = roundf(__fdiv_rn(xs[j], scale));
-                r = fminf(fmaxf(r, -127.0f), 127.0f);
+                r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0
                 q[j] = (uint32_t)(unsigned char)(signed char)(int)r;
             }
             *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
@@ -87,9 +87,8 @@ __device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_h
 template <typename T> __device__ __forceinline__ float act_round(float v) { return v; }
 template <> __device__ __forceinline__ float act_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
 
-// (cos, sin) of every (token of this CTA, d < half) into shared memory.
-__device__ __forceinline__ void fill_sincos(const RopeArgs &a, float *s_cos, float *s_sin, int half) {
-    const int64_t t0 = (int64_t)blockIdx.x * a.tpc;
+// (cos, sin) of every (token t0 + tt, d < half), tt < a.tpc, into shared memory.
+__device__ __forceinline__ void fill_sincos(const RopeArgs &a, float *s_cos, float *s_sin, int half, int64_t t0) {
     for (int i = threadIdx.x; i < a.tpc * half; i += blockDim.x) {
         const int tt = i / half, d = i - tt * half;
         const int64_t t = t0 + tt;
@@ -111,6 +110,96 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
        MODE_NEOX_K2 = 2,  // NeoX, n_rot/8 == 2*W : partner float4 is register l+2 of the same lane
        MODE_NEOX_SHFL = 3 // NeoX, n_rot/8 < W (power of two): partner is register 0 of lane ^ (n_rot/8)
 };
+
+// Norm (optional) and rotation of one head held in the registers of a lane group: float4 number
+// lane + W*l of the head is v[l].  `rot`: the head is a Q or K row with data (V rows of the fused
+// cache write and idle slots pass false; they still take part in the shuffles).
+template <typename T, int W, int VPL, int MODE, bool NORM>
+__device__ __forceinline__ void rope_head_math(float4 (&v)[VPL], bool rot, const float4 *wv, const float *c_tab,
+                                               const float *s_tab, int lane, int hd4, int hq, int head_dim, int n_rot, float eps) {
+    if (NORM) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int l = 0; l < VPL; l++) ss += v[l].x * v[l].x + v[l].y * v[l].y + v[l].z * v[l].z + v[l].w * v[l].w;
+#pragma unroll
+        for (int o = W / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        // (w*x)/rms of the CPU path, evaluated as (w*x)*(1/rms): one IEEE division per
+        // head instead of one per element; differs from the CPU order by <= 1 ulp
+        const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+#pragma unroll
+        for (int l = 0; l < VPL; l++) {
+            const int i = lane + W * l;
+            if (rot && i < hd4) {
+                const float4 ww = __ldg(wv + i);
+                v[l].x = act_round<T>(ww.x * v[l].x * inv);
+                v[l].y = act_round<T>(ww.y * v[l].y * inv);
+                v[l].z = act_round<T>(ww.z * v[l].z * inv);
+                v[l].w = act_round<T>(ww.w * v[l].w * inv);
+            }
+        }
+    }
+    if (MODE == MODE_NEOX_K1 || MODE == MODE_NEOX_K2) {
+        constexpr int K = MODE == MODE_NEOX_K2 ? 2 : 1;
+#pragma unroll
+        for (int l = 0; l < K; l++) {
+            if (l + K < VPL && rot) {
+                const int i = lane + W * l;
+                const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
+                const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
+                const float4 x0 = v[l], x1 = v[(l + K) % VPL];
+                float4 y0, y1;
+                y0.x = x0.x * c.x - x1.x * sn.x;
+                y0.y = x0.y * c.y - x1.y * sn.y;
+                y0.z = x0.z * c.z - x1.z * sn.z;
+                y0.w = x0.w * c.w - x1.w * sn.w;
+                y1.x = x0.x * sn.x + x1.x * c.x;
+                y1.y = x0.y * sn.y + x1.y * c.y;
+                y1.z = x0.z * sn.z + x1.z * c.z;
+                y1.w = x0.w * sn.w + x1.w * c.w;
+                v[l] = y0;
+                v[(l + K) % VPL] = y1;
+            }
+        }
+    } else if (MODE == MODE_NEOX_SHFL) {
+        const float4 mine = v[0];
+        float4 oth;
+        oth.x = __shfl_xor_sync(0xffffffffu, mine.x, hq);
+        oth.y = __shfl_xor_sync(0xffffffffu, mine.y, hq);
+        oth.z = __shfl_xor_sync(0xffffffffu, mine.z, hq);
+        oth.w = __shfl_xor_sync(0xffffffffu, mine.w, hq);
+        if (rot && lane < 2 * hq) {
+            const bool low = lane < hq;
+            const int i = low ? lane : lane - hq;
+            const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
+            const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
+            if (low) {  // x0 = mine, x1 = oth
+                v[0].x = mine.x * c.x - oth.x * sn.x;
+                v[0].y = mine.y * c.y - oth.y * sn.y;
+                v[0].z = mine.z * c.z - oth.z * sn.z;
+                v[0].w = mine.w * c.w - oth.w * sn.w;
+            } else {  // x0 = oth, x1 = mine
+                v[0].x = oth.x * sn.x + mine.x * c.x;
+                v[0].y = oth.y * sn.y + mine.y * c.y;
+                v[0].z = oth.z * sn.z + mine.z * c.z;
+                v[0].w = oth.w * sn.w + mine.w * c.w;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int l = 0; l < VPL; l++) {
+            const int i = lane + W * l;
+            if (rot && 4 * i < n_rot) {
+                const float2 c = *reinterpret_cast<const float2 *>(c_tab + 2 * i);
+                const float2 sn = *reinterpret_cast<const float2 *>(s_tab + 2 * i);
+                const float4 x = v[l];
+                v[l].x = x.x * c.x - x.y * sn.x;
+                v[l].y = x.x * sn.x + x.y * c.x;
+                v[l].z = x.z * c.y - x.w * sn.y;
+                v[l].w = x.z * sn.y + x.w * c.y;
+            }
+        }
+    }
+}
 
 template <typename T, int W, int VPL, int MODE, bool NORM, int KV = KV_NONE>
 __global__ void __launch_bounds__(256)
@@ -171,98 +260,17 @@ rope_heads_kernel(const RopeArgs a) {
         }
         if (base == 0) {
             // The sin/cos table is built while the HBM loads issued above are in flight.
-            fill_sincos(a, s_cos, s_sin, half);
+            fill_sincos(a, s_cos, s_sin, half, (int64_t)blockIdx.x * a.tpc);
             __syncthreads();
         }
 #pragma unroll
         for (int s = 0; s < NS; s++) {
             const int kind = (meta[s] >> 16) & 3;
-            if (NORM) {
-                float ss = 0.0f;
-#pragma unroll
-                for (int l = 0; l < VPL; l++)
-                    ss += v[s][l].x * v[s][l].x + v[s][l].y * v[s][l].y + v[s][l].z * v[s][l].z + v[s][l].w * v[s][l].w;
-#pragma unroll
-                for (int o = W / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                // (w*x)/rms of the CPU path, evaluated as (w*x)*(1/rms): one IEEE division per
-                // head instead of one per element; differs from the CPU order by <= 1 ulp
-                const float inv = 1.0f / sqrtf(ss / (float)a.head_dim + a.eps);
-                const float4 *wv = reinterpret_cast<const float4 *>(kind == 1 ? a.wk : a.wq);
-#pragma unroll
-                for (int l = 0; l < VPL; l++) {
-                    const int i = lane + W * l;
-                    if (ptr[s] && i < hd4 && kind < 2) {
-                        const float4 ww = __ldg(wv + i);
-                        v[s][l].x = act_round<T>(ww.x * v[s][l].x * inv);
-                        v[s][l].y = act_round<T>(ww.y * v[s][l].y * inv);
-                        v[s][l].z = act_round<T>(ww.z * v[s][l].z * inv);
-                        v[s][l].w = act_round<T>(ww.w * v[s][l].w * inv);
-                    }
-                }
-            }
             const float *c_tab = s_cos + (meta[s] & 0xffff) * half;
             const float *s_tab = s_sin + (meta[s] & 0xffff) * half;
-            if (MODE == MODE_NEOX_K1 || MODE == MODE_NEOX_K2) {
-                constexpr int K = MODE == MODE_NEOX_K2 ? 2 : 1;
-#pragma unroll
-                for (int l = 0; l < K; l++) {
-                    if (l + K < VPL && ptr[s] && kind < 2) {
-                        const int i = lane + W * l;
-                        const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
-                        const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
-                        const float4 x0 = v[s][l], x1 = v[s][(l + K) % VPL];
-                        float4 y0, y1;
-                        y0.x = x0.x * c.x - x1.x * sn.x;
-                        y0.y = x0.y * c.y - x1.y * sn.y;
-                        y0.z = x0.z * c.z - x1.z * sn.z;
-                        y0.w = x0.w * c.w - x1.w * sn.w;
-                        y1.x = x0.x * sn.x + x1.x * c.x;
-                        y1.y = x0.y * sn.y + x1.y * c.y;
-                        y1.z = x0.z * sn.z + x1.z * c.z;
-                        y1.w = x0.w * sn.w + x1.w * c.w;
-                        v[s][l] = y0;
-                        v[s][(l + K) % VPL] = y1;
-                    }
-                }
-            } else if (MODE == MODE_NEOX_SHFL) {
-                const float4 mine = v[s][0];
-                float4 oth;
-                oth.x = __shfl_xor_sync(0xffffffffu, mine.x, hq);
-                oth.y = __shfl_xor_sync(0xffffffffu, mine.y, hq);
-                oth.z = __shfl_xor_sync(0xffffffffu, mine.z, hq);
-                oth.w = __shfl_xor_sync(0xffffffffu, mine.w, hq);
-                if (ptr[s] && lane < 2 * hq && kind < 2) {
-                    const bool low = lane < hq;
-                    const int i = low ? lane : lane - hq;
-                    const float4 c = *reinterpret_cast<const float4 *>(c_tab + 4 * i);
-                    const float4 sn = *reinterpret_cast<const float4 *>(s_tab + 4 * i);
-                    if (low) {  // x0 = mine, x1 = oth
-                        v[s][0].x = mine.x * c.x - oth.x * sn.x;
-                        v[s][0].y = mine.y * c.y - oth.y * sn.y;
-                        v[s][0].z = mine.z * c.z - oth.z * sn.z;
-                        v[s][0].w = mine.w * c.w - oth.w * sn.w;
-                    } else {  // x0 = oth, x1 = mine
-                        v[s][0].x = oth.x * sn.x + mine.x * c.x;
-                        v[s][0].y = oth.y * sn.y + mine.y * c.y;
-                        v[s][0].z = oth.z * sn.z + mine.z * c.z;
-                        v[s][0].w = oth.w * sn.w + mine.w * c.w;
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int l = 0; l < VPL; l++) {
-                    const int i = lane + W * l;
-                    if (ptr[s] && 4 * i < a.n_rot && kind < 2) {
-                        const float2 c = *reinterpret_cast<const float2 *>(c_tab + 2 * i);
-                        const float2 sn = *reinterpret_cast<const float2 *>(s_tab + 2 * i);
-                        const float4 x = v[s][l];
-                        v[s][l].x = x.x * c.x - x.y * sn.x;
-                        v[s][l].y = x.x * sn.x + x.y * c.x;
-                        v[s][l].z = x.z * c.y - x.w * sn.y;
-                        v[s][l].w = x.z * sn.y + x.w * c.y;
-                    }
-                }
-            }
+            rope_head_math<T, W, VPL, MODE, NORM>(v[s], ptr[s] != nullptr && kind < 2,
+                                                  reinterpret_cast<const float4 *>(kind == 1 ? a.wk : a.wq), c_tab, s_tab, lane, hd4, hq,
+                                                  a.head_dim, a.n_rot, a.eps);
 #pragma unroll
             for (int l = 0; l < VPL; l++) {
                 const int i = lane + W * l;
@@ -278,7 +286,7 @@ rope_heads_kernel(const RopeArgs a) {
                     const int64_t t = t0 + (meta[s] & 0xffff);
                     const int64_t p = a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t;
                     if (p >= 0 && p < a.max_seq) slot = p;
-                    else if (lane == 0) atomicOr(a.flags, AGN_FLAG_OOB_ID);  // skipped and reported, never a fault
+                    else if (lane == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);  // skipped and reported, never a fault
                 }
                 unsigned char *tok_head = nullptr;
                 if (slot >= 0) {
@@ -296,6 +304,129 @@ rope_heads_kernel(const RopeArgs a) {
     }
 }
 
+// Persistent form of rope_heads_kernel for large batches.  A unit is a.tpc consecutive tokens,
+// i.e. one contiguous piece of q and one of k; a CTA loops over units blockIdx.x, blockIdx.x +
+// gridDim.x, ... and the pieces of its next units are already on their way into a ring of
+// shared-memory slots (two bulk asynchronous copies per unit, issued by one thread, completing
+// on the slot's mbarrier).  Lane groups then read their heads from the slot instead of from
+// global memory, rotate them in registers exactly as above and store them straight back to q / k.
+// Shared memory: slots x [q piece | k piece] | mbarriers | per-row table | two sin/cos tables.
+template <typename T, int W, int VPL, int MODE, bool NORM>
+__global__ void __launch_bounds__(256)
+rope_heads_ring_kernel(const RopeArgs a, int slots, int slot_bytes, int spin_limit) {
+    constexpr int NS = VPL == 4 ? 2 : 4;
+    extern __shared__ __align__(128) unsigned char ring_raw[];
+    const int half = a.n_rot >> 1;
+    const int n_heads = a.n_q + a.n_kv;
+    const int rows_max = a.tpc * n_heads;
+    const uint32_t q_tok_bytes = (uint32_t)a.n_q * a.head_dim * sizeof(T), k_tok_bytes = (uint32_t)a.n_kv * a.head_dim * sizeof(T);
+    const uint32_t k_off = (uint32_t)a.tpc * q_tok_bytes;  // the k piece follows the largest q piece
+    uint64_t *full = reinterpret_cast<uint64_t *>(ring_raw + (size_t)slots * slot_bytes);
+    int *s_row = reinterpret_cast<int *>(full + slots);                      // [rows_max][2]: byte offset in the slot, meta
+    float *s_tab = reinterpret_cast<float *>(s_row + 2 * rows_max + ((2 * rows_max) & 1) + 2);  // 16-byte aligned below
+    s_tab = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(s_tab) + 15) & ~(uintptr_t)15);
+    const int tab_stride = 2 * a.tpc * (half > 0 ? half : 1);  // floats per table: cos then sin
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < slots; s++) agn_mbar_init(&full[s], 1);
+        agn_mbar_init_fence();
+    }
+    for (int hr = threadIdx.x; hr < rows_max; hr += blockDim.x) {
+        const int tt = hr / n_heads, h = hr - tt * n_heads;
+        const bool is_k = h >= a.n_q;
+        s_row[2 * hr] = is_k ? (int)(k_off + (uint32_t)tt * k_tok_bytes + (uint32_t)(h - a.n_q) * a.head_dim * sizeof(T))
+                             : (int)((uint32_t)tt * q_tok_bytes + (uint32_t)h * a.head_dim * sizeof(T));
+        s_row[2 * hr + 1] = tt | ((is_k ? 1 : 0) << 16);
+    }
+    __syncthreads();
+    agn_pdl_launch_dependents();
+    agn_pdl_wait();  // global memory is touched from here on
+
+    const int64_t n_units = (a.T + a.tpc - 1) / a.tpc;
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    const int n_my = first < n_units ? (int)((n_units - first + stride - 1) / stride) : 0;
+    unsigned char *qb = static_cast<unsigned char *>(a.q), *kb = static_cast<unsigned char *>(a.k);
+    auto issue = [&](int j) {  // thread 0 only: unit number j of this CTA into slot j % slots
+        const int64_t t0 = (first + (int64_t)j * stride) * a.tpc;
+        const uint32_t ntok = (uint32_t)(a.T - t0 < a.tpc ? a.T - t0 : a.tpc);
+        unsigned char *dst = ring_raw + (size_t)(j % slots) * slot_bytes;
+        uint64_t *bar = &full[j % slots];
+        agn_mbar_expect_tx(bar, ntok * (q_tok_bytes + k_tok_bytes));
+        if (q_tok_bytes) agn_bulk_g2s(dst, qb + t0 * q_tok_bytes, ntok * q_tok_bytes, bar);
+        if (k_tok_bytes) agn_bulk_g2s(dst + k_off, kb + t0 * k_tok_bytes, ntok * k_tok_bytes, bar);
+    };
+    int issued = 0;
+    if (threadIdx.x == 0)
+        for (; issued < slots - 1 && issued < n_my; issued++) issue(issued);
+
+    const int lane = threadIdx.x & (W - 1);
+    const int group = threadIdx.x / W;
+    const int n_groups = blockDim.x / W;
+    const int hd4 = a.head_dim >> 2;
+    const int hq = half >> 2;
+
+    int failed = 0;  // this thread's staging wait ran out
+    for (int it = 0; it < n_my; it++) {
+        const int slot = it % slots;
+        const int64_t t0 = (first + (int64_t)it * stride) * a.tpc;
+        const int ntok = (int)(a.T - t0 < a.tpc ? a.T - t0 : a.tpc);
+        const int rows = ntok * n_heads;
+        float *s_cos = s_tab + (it & 1) * tab_stride, *s_sin = s_cos + a.tpc * half;
+        fill_sincos(a, s_cos, s_sin, half, t0);  // this unit's table, while its copies are in flight
+        // table visible; every thread has finished reading the previous unit's slot; and one
+        // CTA-wide answer to "did any thread's wait run out", so that all leave together
+        if (__syncthreads_or(failed)) break;
+        // the slot that the previous iteration emptied takes the unit slots - 1 ahead of this one
+        if (threadIdx.x == 0 && issued < n_my) issue(issued++);
+        if (!agn_mbar_wait(&full[slot], (uint32_t)(it / slots) & 1u, spin_limit)) {
+            failed = 1;
+            atomicOr(a.flags, AGN_FLAG_TIMEOUT);
+            continue;  // the data did not arrive: store nothing; the CTA leaves at the next barrier
+        }
+        const unsigned char *sl = ring_raw + (size_t)slot * slot_bytes;
+        for (int base = 0; base < rows; base += n_groups * NS) {
+            float4 v[NS][VPL];
+            int off[NS], meta[NS];
+            bool live[NS];
+#pragma unroll
+            for (int s = 0; s < NS; s++) {
+                const int hr = base + group + s * n_groups;
+                live[s] = hr < rows;
+                off[s] = live[s] ? s_row[2 * hr] : 0;
+                meta[s] = live[s] ? s_row[2 * hr + 1] : 0;
+#pragma unroll
+                for (int l = 0; l < VPL; l++) {
+                    const int i = lane + W * l;
+                    v[s][l] = (live[s] && i < hd4) ? ActVec<T>::load_shared(reinterpret_cast<const T *>(sl + off[s]), i)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < NS; s++) {
+                const bool is_k = (meta[s] >> 16) & 1;
+                const float *c_tab = s_cos + (meta[s] & 0xffff) * half;
+                const float *sn_tab = s_sin + (meta[s] & 0xffff) * half;
+                rope_head_math<T, W, VPL, MODE, NORM>(v[s], live[s], reinterpret_cast<const float4 *>(is_k ? a.wk : a.wq), c_tab, sn_tab,
+                                                      lane, hd4, hq, a.head_dim, a.n_rot, a.eps);
+                // the head's place in q / k: the slot holds the pieces in the same order as global memory
+                T *dst = is_k ? reinterpret_cast<T *>(kb + t0 * k_tok_bytes + (off[s] - (int)k_off))
+                              : reinterpret_cast<T *>(qb + t0 * q_tok_bytes + off[s]);
+#pragma unroll
+                for (int l = 0; l < VPL; l++) {
+                    const int i = lane + W * l;
+                    const bool touched = NORM || 4 * i < a.n_rot;
+                    if (live[s] && i < hd4 && touched) ActVec<T>::store(dst, i, v[s][l]);
+                }
+            }
+        }
+    }
+    if (__syncthreads_or(failed) && threadIdx.x == 0) {
+        // a staging wait ran out (reported above): give every copy that may still be in flight
+        // into this CTA's shared memory one more bounded wait before leaving
+        for (int j = issued - slots > 0 ? issued - slots : 0; j < issued; j++)
+            (void)agn_mbar_wait(&full[j % slots], (uint32_t)(j / slots) & 1u, spin_limit);
+    }
+}
+
 // Any even n_rot <= head_dim, any head_dim, any alignment: one warp per head, scalar
 // accesses straight from global memory (second touch of an element is an L1/L2 hit).
 template <typename T, int LAYOUT, bool NORM>
@@ -306,7 +437,7 @@ rope_heads_generic_kernel(const RopeArgs a) {
     const int half = a.n_rot >> 1;
     float *s_cos = smem;
     float *s_sin = smem + half;  // tpc == 1
-    fill_sincos(a, s_cos, s_sin, half);
+    fill_sincos(a, s_cos, s_sin, half, (int64_t)blockIdx.x * a.tpc);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int n_heads = a.n_q + a.n_kv;
@@ -369,8 +500,36 @@ bool launch_kv(agn_ctx *ctx, const RopeArgs &a, bool norm, int kv, int W, int VP
     return false;
 }
 
+// Persistent form for large batches; false = not applicable (the caller launches the CTA-per-unit kernel).
+template <typename T, int W, int VPL, int MODE, bool NORM>
+bool launch_ring4(agn_ctx *ctx, const RopeArgs &a, int threads) {
+    const size_t q_tok = (size_t)a.n_q * a.head_dim * sizeof(T), k_tok = (size_t)a.n_kv * a.head_dim * sizeof(T);
+    if (q_tok % 16 || k_tok % 16 || (a.n_q && !agn_aligned16(a.q)) || (a.n_kv && !agn_aligned16(a.k))) return false;
+    const int slot_bytes = (int)(((size_t)a.tpc * (q_tok + k_tok) + 127) & ~(size_t)127);
+    int slots = ctx->tune_rope_ring >= 2 ? ctx->tune_rope_ring : 3;
+    while (slots > 2 && (size_t)slots * slot_bytes > 100 * 1024) slots--;
+    const int half = a.n_rot >> 1, rows = a.tpc * (a.n_q + a.n_kv);
+    const size_t smem = (size_t)slots * slot_bytes + 8 * (size_t)slots + 8 * (size_t)rows + 32 +
+                        sizeof(float) * 4 * (size_t)a.tpc * (half > 0 ? half : 1);
+    if (smem > 200 * 1024) return false;
+    auto kernel = rope_heads_ring_kernel<T, W, VPL, MODE, NORM>;
+    int per_sm = agn_ring_ctas_per_sm(ctx, kernel, threads, smem);
+    if (per_sm < 1) return false;
+    if (ctx->tune_rope_ring_ctas > 0 && ctx->tune_rope_ring_ctas < per_sm) per_sm = ctx->tune_rope_ring_ctas;
+    int64_t grid = (int64_t)per_sm * ctx->sm_count;
+    const int64_t n_units = (a.T + a.tpc - 1) / a.tpc;
+    if (n_units < 2 * grid && !ctx->tune_ring_force) return false;  // too few units per CTA for a ring to pay
+    if (grid > n_units) grid = n_units;
+    agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, a, slots, slot_bytes, ctx->mbar_spin_limit);
+    ctx->flags_dirty = true;
+    return true;
+}
+
 template <typename T, int W, int VPL, int MODE>
 void launch_fast3(agn_ctx *ctx, const RopeArgs &a, bool norm, unsigned grid, int threads, size_t smem) {
+    if (ctx->tune_rope_ring != 0 &&
+        (norm ? launch_ring4<T, W, VPL, MODE, true>(ctx, a, threads) : launch_ring4<T, W, VPL, MODE, false>(ctx, a, threads)))
+        return;
     if (norm) agn_launch(ctx, rope_heads_kernel<T, W, VPL, MODE, true>, dim3(grid), dim3(threads), smem, a);
     else agn_launch(ctx, rope_heads_kernel<T, W, VPL, MODE, false>, dim3(grid), dim3(threads), smem, a);
 }

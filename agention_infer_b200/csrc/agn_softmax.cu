@@ -89,6 +89,12 @@ __device__ __forceinline__ void store_probs(OT *out, int i, float4 o, int nv, in
     }
 }
 
+// Float4 number i of an output row when it lies wholly past the valid length: zeros, or nothing.
+template <typename OT>
+__device__ __forceinline__ void store_past_valid(OT *out, int i, int n4, bool leave_tail) {
+    if (!leave_tail && i < n4) ActVec<OT>::store(out, i, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
 // exp(v - m) as 2^((v - m) * log2 e) with the hardware ex2: three instructions per element
 // instead of the ~10 of expf, which made these kernels issue-bound (84 % issue-active at
 // 59 % of DRAM peak).  Arguments are <= 0, so the result is in [0, 1] and its absolute
@@ -159,14 +165,17 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPL; k++) v[k] = load_valid(in, lane + 32 * k, nv);
 #pragma unroll
     for (int k = 0; k < VPL; k++) mask_tail(v[k], lane + 32 * k, nv);
+    // float4 that lie wholly past the valid length (half of a causal matrix) cost nothing below:
+    // for k >= 1 a whole warp is on the same side of the boundary, so the branches are uniform
     float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < VPL; k++) m = fmaxf(m, max4(v[k]));
+    for (int k = 0; k < VPL; k++)
+        if (4 * (lane + 32 * k) < nv) m = fmaxf(m, max4(v[k]));
     m = agn_warp_max(m);
     float sum = 0.0f;
-    if (nv > 0) {  // (a row without valid entries has m = -inf: skip, everything below writes 0)
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
+    for (int k = 0; k < VPL; k++) {
+        if (4 * (lane + 32 * k) < nv) {
             v[k] = exp4(v[k], m, a.exp_coef);
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
@@ -177,11 +186,8 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
 #pragma unroll
     for (int k = 0; k < VPL; k++) {
         const int i = lane + 32 * k;
-        {
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
-            store_probs<OT>(out, i, o, nv, n4, a.leave_tail != 0);
-        }
+        if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+        else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
     }
 }
 
@@ -201,9 +207,12 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPT; k++) v[k] = load_valid(in, threadIdx.x + k * blockDim.x, nv);
 #pragma unroll
     for (int k = 0; k < VPT; k++) mask_tail(v[k], threadIdx.x + k * blockDim.x, nv);
+    // float4 that lie wholly past the valid length (half of a causal matrix) cost nothing below:
+    // a whole warp is on the same side of the boundary except for one, so the branches are uniform
     float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    for (int k = 0; k < VPT; k++)
+        if (4 * (threadIdx.x + k * blockDim.x) < nv) m = fmaxf(m, max4(v[k]));
     m = agn_warp_max(m);
     if (lane == 0) red[warp] = m;
     __syncthreads();
@@ -211,9 +220,9 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[w]);
     __syncthreads();
     float sum = 0.0f;
-    if (nv > 0) {
 #pragma unroll
-        for (int k = 0; k < VPT; k++) {
+    for (int k = 0; k < VPT; k++) {
+        if (4 * (threadIdx.x + k * blockDim.x) < nv) {
             v[k] = exp4(v[k], m, a.exp_coef);
             sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
@@ -228,11 +237,8 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
-        {
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * i < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
-            store_probs<OT>(out, i, o, nv, n4, a.leave_tail != 0);
-        }
+        if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+        else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
     }
 }
 
@@ -374,7 +380,7 @@ namespace {
 template <typename OT>
 int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, int64_t n_rows, int64_t row_len,
                          int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset,
-                         float scale = 1.0f) {
+                         float scale = 1.0f, bool leave_tail = false) {
     if (!(scale > 0.0f) || !(scale < INFINITY))
         return agn_fail(ctx, AGN_EINVAL, "softmax_rows: scale %g is not a positive finite number", (double)scale);
     if (n_rows < 0 || row_len < 0 || row_stride < row_len || causal_period < 0 || causal_offset < 0)
@@ -388,7 +394,7 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, in
     a.in = in; a.out = out; a.sums = sums; a.n_valid = n_valid; a.n_rows = n_rows; a.row_len = row_len; a.row_stride = row_stride;
     a.causal_period = causal_period; a.causal_offset = causal_offset;
     a.scale = scale;
-    a.leave_tail = ctx->tune_softmax_leave_tail;
+    a.leave_tail = leave_tail ? 1 : 0;
     a.exp_coef = scale == 1.0f ? 1.4426950408889634f : (float)((double)scale * 1.4426950408889634);
     const bool vec_ok = row_len % 4 == 0 && row_stride % 4 == 0 && agn_aligned16(in) && agn_aligned(out, ActVec<OT>::ALIGN);
     const int64_t n4 = row_len / 4;
@@ -495,4 +501,24 @@ extern "C" int32_t agn_softmax_rows_scaled_f32_out16(agn_ctx *ctx, const float *
         return softmax_dispatch<__nv_bfloat16>(ctx, in, static_cast<__nv_bfloat16 *>(out), sums, n_rows, row_len, row_stride,
                                                n_valid, causal_period, causal_offset, scale);
     return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "softmax_rows_scaled_f32_out16: output type %d is neither f16 nor bf16", out_dtype);
+}
+
+// The reference's CPU loop runs over `scores[..seq_len]` only (src/model/llama/cpu_path.rs:168-183):
+// this form leaves the output entries past a row's valid length untouched instead of writing 0.
+extern "C" int32_t agn_softmax_rows_valid_f32(agn_ctx *ctx, const float *in, void *out, float *sums, int64_t n_rows,
+                                              int64_t row_len, int64_t row_stride, const int32_t *n_valid,
+                                              int32_t causal_period, int32_t causal_offset, float scale, int32_t out_dtype) {
+    AGN_CHECK_CTX(ctx);
+    if (out_dtype == AGN_F32)
+        return softmax_dispatch<float>(ctx, in, static_cast<float *>(out), sums, n_rows, row_len, row_stride, n_valid, causal_period,
+                                       causal_offset, scale, true);
+    if (out == static_cast<const void *>(in) && n_rows > 0)
+        return agn_fail(ctx, AGN_EINVAL, "softmax_rows_valid_f32: a 16-bit output row cannot alias the f32 scores");
+    if (out_dtype == AGN_F16)
+        return softmax_dispatch<__half>(ctx, in, static_cast<__half *>(out), sums, n_rows, row_len, row_stride, n_valid,
+                                        causal_period, causal_offset, scale, true);
+    if (out_dtype == AGN_BF16)
+        return softmax_dispatch<__nv_bfloat16>(ctx, in, static_cast<__nv_bfloat16 *>(out), sums, n_rows, row_len, row_stride,
+                                               n_valid, causal_period, causal_offset, scale, true);
+    return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "softmax_rows_valid_f32: output type %d is not f32, f16 or bf16", out_dtype);
 }

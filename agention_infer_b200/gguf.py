@@ -160,13 +160,19 @@ class GgufFile:
         out = []
         raw = _abi.TensorInfo()
         for i in range(self.tensor_count):
-            if self._lib.agn_gguf_tensor_at(self._g, i, C.byref(raw)) == _abi.AGN_OK:
+            st = self._lib.agn_gguf_tensor_at(self._g, i, C.byref(raw))
+            if st == _abi.AGN_EFORMAT:
+                raise GgufError(st, f"tensor {i}: dimensions or offset overflow 64 bits")
+            if st == _abi.AGN_OK:
                 out.append(TensorInfo(raw))
         return out
 
     def find(self, name: str) -> Optional[TensorInfo]:
         raw = _abi.TensorInfo()
-        if self._lib.agn_gguf_find_tensor(self._g, name.encode(), C.byref(raw)) != _abi.AGN_OK:
+        st = self._lib.agn_gguf_find_tensor(self._g, name.encode(), C.byref(raw))
+        if st == _abi.AGN_EFORMAT:
+            raise GgufError(st, f"tensor '{name}': dimensions or offset overflow 64 bits")
+        if st != _abi.AGN_OK:
             return None
         return TensorInfo(raw)
 

@@ -509,11 +509,10 @@ def run_ours(args, cfg, ops_list, wl):
                                                               causal_period=Ls),
                 4 * (nq * Ls * (Ls + 1) // 2) + 2 * nq * Ls * Ls),
         }
-        def softmax_valid_only(b):  # the reference's form: entries past the valid length are not written
-            be.set_option("softmax_leave_tail", 1)
-            be.launch_softmax_rows(b["sc"], nq * Ls, Ls, out=b["pr"], causal_period=Ls)
-            be.set_option("softmax_leave_tail", 0)
-        extras[f"softmax_causal_leave_tail_{nq}x{Ls}x{Ls}"] = (softmax_valid_only, 8 * (nq * Ls * (Ls + 1) // 2))
+        # the reference's form: entries past the valid length are not written
+        extras[f"softmax_causal_leave_tail_{nq}x{Ls}x{Ls}"] = (
+            lambda b: be.launch_softmax_rows_valid(b["sc"], nq * Ls, Ls, b["pr"], causal_period=Ls),
+            8 * (nq * Ls * (Ls + 1) // 2))
         for name, (fn, nbytes) in extras.items():
             for i in range(4):
                 fn(ex_sets[i % nsets])

@@ -95,10 +95,6 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
 /* Options.  "pdl" (default 1): launch kernels with programmatic stream serialization, so
  * that a kernel's launch latency overlaps the tail of the previous kernel of the stream
  * (every kernel still waits for the previous one to complete before its first access).
- * "softmax_leave_tail" (default 0): 1 makes every softmax entry point leave the output entries past a
- * row's valid length untouched, as the reference's loop over `scores[..seq_len]` does
- * (src/model/llama/cpu_path.rs:168-183), instead of writing them as 0; a causal softmax then writes
- * half as much.
  * Tuning knobs, all with measured defaults: "rms_vpt" (1, 2, 4, 8 vectors per thread; 0 = automatic),
  * "rms_recip" (1: one reciprocal per row, 0: IEEE division per element), "silu_unroll" (2, 4, 8),
  * "silu_threads" (128, 256, 512), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more
@@ -253,6 +249,16 @@ AGN_API int32_t agn_softmax_rows_scaled_f32_out16(agn_ctx *ctx, const float *in,
                                                   int64_t n_rows, int64_t row_len, int64_t row_stride,
                                                   const int32_t *n_valid, int32_t causal_period,
                                                   int32_t causal_offset, float scale, int32_t out_dtype);
+
+/* The softmax exactly as the reference's CPU loop leaves its buffer (src/model/llama/cpu_path.rs:168-183:
+ * it runs over `scores[..seq_len]` and never touches `scores[seq_len..]`): entries nv(r)..row_len-1
+ * of out are NOT written and keep whatever the buffer held, so a causal softmax stores half as much.
+ * Everything else as agn_softmax_rows_scaled_f32 (scale 1 for the plain form, sums optional) and,
+ * with out_dtype = AGN_F16 / AGN_BF16 instead of AGN_F32, as agn_softmax_rows_scaled_f32_out16. */
+AGN_API int32_t agn_softmax_rows_valid_f32(agn_ctx *ctx, const float *in, void *out, float *sums,
+                                           int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                           const int32_t *n_valid, int32_t causal_period,
+                                           int32_t causal_offset, float scale, int32_t out_dtype);
 
 /* Embedding get_rows with inline dequant: `WeightMap::dequant_row`
  * (src/model/mod.rs:343-348) -> `quant::dequant_row` (src/quant/mod.rs:30-47,97-135)
@@ -421,9 +427,15 @@ AGN_API int32_t agn_host_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *t
  * GPU that loads it until the process exits.  It calls no cudaMalloc, cudaFree or allocating
  * library routine.
  *   - Limit: 256 + ceil(2T / 1024) * n_experts * 4 bytes must fit in 256 KiB (8 experts:
- *     T <= 4,189,184); larger problems are rejected with AGN_EINVAL and a message in `err`.
- *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress) and keeps it; make that first call outside any stream capture.
+ *     T <= 4,190,208); larger problems are rejected with AGN_EINVAL and a message in `err`.
+ *   - `cuda_stream` must be a stream of the CURRENT device (the array's address is looked up for
+ *     the current device; with a stream of another device the launches fail with AGN_ECUDA).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress)
+ *     and keeps it.  With CUDA's lazy module loading that first call is also what loads the
+ *     library's device code and gives the array its memory on that device, so make one warm-up
+ *     call per device at start-up, before the host's own arena takes the remaining memory and
+ *     outside any stream capture: T = 0 is enough (the look-up runs before the T == 0 return).
+ *     After it the array stays resident on that device until the process exits.
  *   - All calls share the array and it keeps the previous call's contents; the call itself
  *     clears what has to start at zero.  Two calls whose kernels can overlap on the GPU
  *     (different streams without an event between them) race on it: serialise them.

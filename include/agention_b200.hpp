@@ -196,6 +196,13 @@ class CudaBackend {
         check(agn_softmax_rows_scaled_f32_out16(ctx_, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period,
                                                 causal_offset, scale, out_dtype));
     }
+    // the softmax as the CPU loop leaves its buffer: entries past the valid length are not written
+    void launch_softmax_rows_valid(const float *in, void *out, float *sums, int64_t n_rows, int64_t row_len, int64_t row_stride,
+                                   const int32_t *n_valid, int32_t causal_period, int32_t causal_offset, float scale,
+                                   int32_t out_dtype) {
+        check(agn_softmax_rows_valid_f32(ctx_, in, out, sums, n_rows, row_len, row_stride, n_valid, causal_period, causal_offset,
+                                         scale, out_dtype));
+    }
     void launch_qk_norm_rope_qk_f16(void *q, void *k, const float *wq, const float *wk, int64_t T, int n_q, int n_kv,
                                     int head_dim, float eps, int n_rot, const int32_t *pos, int pos_start, float theta,
                                     float freq_scale = 1.0f, int layout = AGN_ROPE_NEOX) {

@@ -523,7 +523,7 @@ void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out) {
         size_t cnt = n - b * 32 < 32 ? n - b * 32 : 32;
         uint8_t *o = out + b * 34;
         float amax = 0.0f;
-        for (size_t i = 0; i < cnt; i++) amax = fmaxf(amax, fabsf(blk[i]));
+        for (size_t i = 0; i < cnt; i++) amax = fmaxf(amax, fabsf(blk[i])); /* f32::max: a NaN operand is ignored */
         float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
         uint16_t h = f32_to_f16_bits(scale);
         o[0] = (uint8_t)(h & 0xFF);
@@ -531,6 +531,7 @@ void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out) {
         for (size_t i = 0; i < cnt; i++) {
             float q = roundf(blk[i] / scale);
             q = q < -127.0f ? -127.0f : (q > 127.0f ? 127.0f : q);
+            if (q != q) q = 0.0f; /* `NaN as i8` is 0 in Rust (a NaN value, or inf / inf in a block that holds an inf) */
             o[2 + i] = (uint8_t)(int8_t)q;
         }
     }

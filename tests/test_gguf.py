@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 
 from agention_infer_b200 import AGN_Q4_K, AGN_Q8_0, _abi, synth
+from agention_infer_b200.backend import BackendError
 from agention_infer_b200.gguf import GgufError, GgufFile
 from oracle import oracle as orc
 from tests import gguf_writer as gw
@@ -82,6 +83,57 @@ def _model_file(vocab=96, hidden=256):
     tensors = [("token_embd.weight", AGN_Q4_K, [hidden, vocab], table), ("output_norm.weight", 0, [hidden], norm),
                ("blk.0.ffn_gate.weight", 11, [256, 4], bytes(110 * 4))]  # Q3_K: listed, but no codec here
     return gw.build(3, meta, tensors), table, norm
+
+
+def _one_tensor_header(dims, ggml_type, byte_offset):
+    return (gw.header(3, 1, 0) + gw.gstr("t") + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) +
+            struct.pack("<IQ", ggml_type, byte_offset))
+
+
+def test_crafted_sizes_and_offsets_are_format_errors_not_wrapped_numbers():
+    """Sizes and offsets come from the file; the reference rejects them with checked slices
+    (src/quant/mod.rs:124-131).  A product or sum that wraps around 64 bits must not come out as a
+    small, plausible number."""
+    # dims whose product wraps: 2^33 * 2^33 rows
+    g = GgufFile(data=_one_tensor_header([256, 1 << 33, 1 << 33], AGN_Q8_0, 0))
+    with pytest.raises(GgufError) as e:
+        g.tensors()
+    assert e.value.status == _abi.AGN_EFORMAT
+    with pytest.raises(GgufError):
+        g.find("t")
+    # row_bytes * n_rows wraps although the row count itself fits
+    g = GgufFile(data=_one_tensor_header([1 << 40, 1 << 30], AGN_Q8_0, 0))
+    with pytest.raises(GgufError):
+        g.find("t")
+    # a row length that would wrap inside type_size
+    g = GgufFile(data=_one_tensor_header([(1 << 64) - 1], AGN_Q4_K, 0))
+    with pytest.raises(GgufError):
+        g.find("t")
+    # data_offset + byte_offset wraps
+    g = GgufFile(data=_one_tensor_header([32, 2], AGN_Q8_0, (1 << 64) - 8))
+    with pytest.raises(GgufError):
+        g.find("t")
+    # a byte_offset just below the wrap: the directory entry is readable, the bytes are not in the file
+    g = GgufFile(data=_one_tensor_header([32, 2], AGN_Q8_0, (1 << 64) - 4096))
+    t = g.find("t")
+    assert t.n_bytes == 68 and t.file_offset > (1 << 63)
+
+
+@pytest.mark.gpu
+def test_upload_of_a_tensor_outside_the_file_is_rejected(backend):
+    for off in ((1 << 64) - 4096, 1 << 40):
+        g = GgufFile(data=_one_tensor_header([32, 2], AGN_Q8_0, off) + bytes(256))
+        with pytest.raises(BackendError) as e:
+            g.upload(backend, "t")
+        assert e.value.status == _abi.AGN_EFORMAT
+
+
+@pytest.mark.gpu
+def test_get_rows_rejects_a_row_count_whose_byte_size_wraps(backend):
+    t = backend.empty(4096); ids = backend.upload(np.zeros(1, np.uint32)); o = backend.empty(4 * 256)
+    with pytest.raises(BackendError) as e:  # n_rows * 144 wraps to a small number
+        backend.get_rows(AGN_Q4_K, t, 4096, (1 << 63) // 144 * 2 + 1, 256, ids, 1, out=o)
+    assert e.value.status == _abi.AGN_EINVAL
 
 
 def test_file_with_metadata_and_tensors(tmp_path):

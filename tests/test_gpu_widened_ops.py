@@ -225,28 +225,27 @@ def test_silu_mul_f32_to_16bit_output(backend, n, out_dtype):
 
 @pytest.mark.parametrize("R,L", [(6, 8), (5, 30), (7, 100), (4, 516), (6, 4100), (3, 9999), (3, 16388), (2, 152064)])
 def test_softmax_leave_tail_untouched(backend, R, L):
-    """With "softmax_leave_tail" the entries past a row's valid length keep what the buffer held (the
+    """agn_softmax_rows_valid_f32: the entries past a row's valid length keep what the buffer held (the
     reference never touches them, src/model/llama/cpu_path.rs:168-183); the valid entries are the same
-    bits as in the zero-filling mode.  Every kernel family, f32 and 16-bit rows, in place too."""
+    bits as the zero-filling entry points give.  Every kernel family, f32 and 16-bit rows, in place too."""
     s = synth.activations(1, "scores", (R, L), std=2.0)
     nv = np.array([L, 1, L // 2 + 1, L - 1, 0, 3, 2][:R], dtype=np.int32)
     ds, dnv = backend.upload(s), backend.upload(nv)
     zero_filled = backend.read(backend.launch_softmax_rows(ds, R, L, n_valid=dnv), np.float32, (R, L))
     sentinel = np.full((R, L), -7.25, np.float32)
     valid = np.arange(L)[None, :] < nv[:, None]
-    backend.set_option("softmax_leave_tail", 1)
-    try:
-        out = backend.upload(sentinel)
-        backend.launch_softmax_rows(ds, R, L, out=out, n_valid=dnv)
-        got = backend.read(out, np.float32, (R, L))
-        o16 = backend.upload(np.full((R, L), 0x1234, np.uint16))
-        backend.launch_softmax_rows_scaled_out16(ds, R, L, 1.0, AGN_F16, out=o16, n_valid=dnv)
-        got16 = backend.read(o16, np.uint16, (R, L))
-        inplace = backend.upload(s)
-        backend.launch_softmax_rows(inplace, R, L, out=inplace, n_valid=dnv)
-        got_ip = backend.read(inplace, np.float32, (R, L))
-    finally:
-        backend.set_option("softmax_leave_tail", 0)
+    out = backend.upload(sentinel)
+    backend.launch_softmax_rows_valid(ds, R, L, out, n_valid=dnv)
+    got = backend.read(out, np.float32, (R, L))
+    o16 = backend.upload(np.full((R, L), 0x1234, np.uint16))
+    backend.launch_softmax_rows_valid(ds, R, L, o16, out_dtype=AGN_F16, n_valid=dnv)
+    got16 = backend.read(o16, np.uint16, (R, L))
+    inplace = backend.upload(s)
+    backend.launch_softmax_rows_valid(inplace, R, L, inplace, n_valid=dnv)
+    got_ip = backend.read(inplace, np.float32, (R, L))
+    # the zero-filling entry points still zero-fill after a call of the other form (no hidden state)
+    again = backend.read(backend.launch_softmax_rows(ds, R, L, out=backend.upload(sentinel), n_valid=dnv), np.float32, (R, L))
+    assert np.array_equal(again.view(np.uint32), zero_filled.view(np.uint32))
     assert np.array_equal(got[valid].view(np.uint32), zero_filled[valid].view(np.uint32)) and np.all(got[~valid] == -7.25)
     assert np.array_equal(got16[valid], zero_filled.astype(np.float16).view(np.uint16)[valid]) and np.all(got16[~valid] == 0x1234)
     assert np.array_equal(got_ip[valid].view(np.uint32), zero_filled[valid].view(np.uint32))

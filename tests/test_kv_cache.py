@@ -88,6 +88,72 @@ def test_kv_write_and_read_bit_exact(backend, dtype, T, hd, max_seq):
                           orc.kv_read(dtype, ref_v, max_seq, hd).view(np.uint32))
 
 
+def _nonfinite_rows(hd):
+    x = synth.activations(2, "k", (6, hd))
+    x[0, 3] = np.nan                     # a NaN value: ignored by the block maximum, packs as 0
+    x[1, 5] = np.inf                     # an inf in the block: scale inf, every value of that block packs as 0
+    x[2, 1] = -np.inf; x[2, 2] = np.nan
+    x[3, :32] = np.nan                   # a block of NaN only: scale 1, all zeros
+    x[4, 40 % hd] = np.float32(3e38)     # huge but finite
+    return x
+
+
+def test_oracle_q8_0_pack_of_nonfinite_values_follows_rust_casts():
+    """`(v / scale).round().clamp(-127.0, 127.0) as i8` (src/model/mod.rs:580): a NaN casts to 0, and
+    `f32::max` skips a NaN operand in the block maximum (:576)."""
+    hd = 64
+    x = _nonfinite_rows(hd)
+    cache = np.zeros((6, orc.kv_bytes_per_token(orc.Q8_0, hd)), np.uint8)
+    orc.kv_write_rows(orc.Q8_0, x, np.arange(6), cache)
+    blk = cache.reshape(6, 2, 34)
+    q = blk[:, :, 2:].view(np.int8)
+    scale = blk[:, :, :2].copy().view(np.float16)[..., 0]
+    assert q[0, 0, 3] == 0 and np.isfinite(scale[0, 0]) and q[0, 0].any()  # only the NaN entry is 0
+    assert np.isinf(scale[1, 0]) and not q[1, 0].any()                     # inf block: all 0 (finite / inf, inf / inf)
+    assert np.isinf(scale[2, 0]) and not q[2, 0].any()
+    assert scale[3, 0] == 1.0 and not q[3, 0].any()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [AGN_F16, AGN_Q8_0])
+def test_kv_write_of_nonfinite_values_bit_exact(backend, dtype):
+    hd, max_seq = 64, 8
+    k = _nonfinite_rows(hd); v = _nonfinite_rows(hd)[::-1].copy()
+    T = k.shape[0]
+    pos = np.arange(T, dtype=np.int32)
+    bpt = backend.kv_bytes_per_token(dtype, hd)
+    ref_k = np.zeros((max_seq, bpt), np.uint8); ref_v = np.zeros((max_seq, bpt), np.uint8)
+    with np.errstate(all="ignore"):
+        orc.kv_write_rows(dtype, k, pos, ref_k); orc.kv_write_rows(dtype, v, pos, ref_v)
+    dkc, dvc = backend.upload(np.zeros_like(ref_k)), backend.upload(np.zeros_like(ref_v))
+    backend.kv_write(dtype, backend.upload(k), backend.upload(v), dkc, dvc, T, hd, backend.upload(pos), max_seq)
+    got_k, got_v = backend.read(dkc, np.uint8, ref_k.shape), backend.read(dvc, np.uint8, ref_v.shape)
+    if dtype == AGN_F16:  # NaN payloads may differ between converters; compare NaN-ness and everything else exactly
+        gk, rk = got_k.view(np.float16), ref_k.view(np.float16)
+        assert np.array_equal(np.isnan(gk), np.isnan(rk)) and np.array_equal(gk[~np.isnan(rk)], rk[~np.isnan(rk)])
+        gv, rv = got_v.view(np.float16), ref_v.view(np.float16)
+        assert np.array_equal(np.isnan(gv), np.isnan(rv)) and np.array_equal(gv[~np.isnan(rv)], rv[~np.isnan(rv)])
+    else:
+        assert np.array_equal(got_k, ref_k) and np.array_equal(got_v, ref_v)
+
+
+@pytest.mark.gpu
+def test_fused_q8_0_cache_write_of_nonfinite_v_rows(backend):
+    """The fused norm -> rope + cache write packs with the same rule (V rows pass through unrotated)."""
+    T, nq, nkv, hd, max_seq = 600, 28, 4, 128, 1024
+    q = synth.activations(2, "q", (T, nq * hd)); k = synth.activations(2, "k", (T, nkv * hd))
+    v = synth.activations(2, "x", (T, nkv * hd))
+    v[0, 3] = np.nan; v[1, 5] = np.inf; v[2, :32] = np.nan; v[599, 100] = -np.inf
+    bpt = backend.kv_bytes_per_token(AGN_Q8_0, nkv * hd)
+    ref_v = np.zeros((max_seq, bpt), np.uint8)
+    with np.errstate(all="ignore"):
+        orc.kv_write_rows(AGN_Q8_0, v, np.arange(T, dtype=np.int32), ref_v)
+    dkc = backend.upload(np.zeros((max_seq, bpt), np.uint8)); dvc = backend.upload(np.zeros((max_seq, bpt), np.uint8))
+    backend.launch_qk_norm_rope_kv_write(backend.upload(q), backend.upload(k), backend.upload(v), None, None, T, nq, nkv, hd, 0.0, hd,
+                                  None, 1e6, AGN_Q8_0, dkc, dvc, max_seq)
+    assert np.array_equal(backend.read(dvc, np.uint8, ref_v.shape), ref_v)
+
+
 @pytest.mark.gpu
 def test_kv_write_pos_start_and_out_of_range_slot(backend):
     T, hd, max_seq = 8, 64, 10
