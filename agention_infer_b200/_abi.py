@@ -39,6 +39,7 @@ SIGNATURES = {
     "agn_ctx_set_stream": (_i32, [_vp, _vp]),
     "agn_ctx_get_stream": (_i32, [_vp, _pp]),
     "agn_ctx_launch_count": (C.c_uint64, [_vp]),
+    "agn_ctx_last_kernel": (C.c_char_p, [_vp]),
     "agn_launch_noop": (_i32, [_vp]),
     "agn_graph_begin": (_i32, [_vp]),
     "agn_graph_end": (_i32, [_vp, _pp]),

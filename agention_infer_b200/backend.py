@@ -92,6 +92,11 @@ class CudaBackend:
     def launch_count(self) -> int:
         return int(self._lib.agn_ctx_launch_count(self._ctx))
 
+    @property
+    def last_kernel(self) -> str:
+        """Kernel family of the most recent launch (e.g. "rms_norm" or "rms_norm_ring")."""
+        return self._lib.agn_ctx_last_kernel(self._ctx).decode()
+
     def graph_begin(self) -> None:
         """Start recording the ops enqueued on this backend into a CUDA graph."""
         self._check(self._lib.agn_graph_begin(self._ctx))

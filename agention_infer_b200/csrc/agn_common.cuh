@@ -56,24 +56,32 @@ struct agn_ctx {
     int tune_moe_small_sort;    // 1 = up to 4096 (token, slot) pairs are sorted by one CTA in one launch (default)
     int tune_softmax_cluster;   // rows of 16K-128K entries: 1 = one thread-block cluster per row, CTAs of <= 512 threads
                                 // (default); 2 = CTAs of <= 256 threads; 0 = no clusters
+    int tune_softmax_causal_pair; // 1 (default): square causal matrices pair rows i and L-1-i in one CTA
+    int tune_softmax_warp16;    // 1: rows of 1025-2048 entries run one warp per row (16 float4 per lane); 0: one CTA per row
     int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)
     int tune_get_rows_tma;      // stage the quantised row with one bulk asynchronous copy (TMA)
     int tune_silu_unroll;       // float4 pairs in flight per thread in silu_mul: 2, 4 (default) or 8
     int tune_silu_threads;      // 128, 256 (default) or 512
+    int tune_silu_small;        // 1 (default): decode-sized inputs run one float4 pair per thread in 128-thread CTAs
     // Persistent kernels with a shared-memory row ring (rows staged by bulk asynchronous copies
-    // ahead of the row being processed).  *_ring: 0 = never, 1 = automatic (default), >= 2 = that
-    // many slots; *_ring_ctas: resident CTAs per SM (0 = as many as fit).
+    // ahead of the row being processed).  *_ring: 0 = never (default: on B200 the CTA-per-row
+    // kernels measured 5-15 % faster at every batch size), 1 = a ring of the default depth for
+    // batches large enough to keep it busy, >= 2 = that many slots; *_ring_ctas: resident CTAs per
+    // SM (0 = as many as fit).
     int tune_rms_ring, tune_rms_ring_ctas;
     int tune_rope_ring, tune_rope_ring_ctas;
     int tune_get_rows_ring, tune_get_rows_ring_ctas;
+    int tune_host_chunk_bytes;  // host-slice ops: bytes of one staging chunk over all buffers (0 = a whole 24 MiB slot)
     int tune_ring_force;        // 1 = take the persistent form whenever it applies, however few rows (tests)
     int mbar_spin_limit;        // polls before a staging wait gives up
-    int test_mbar_extra_bytes;  // test hook: get_rows arms its staging barrier for this many bytes more than the
-                                // copy delivers, so the bounded wait runs out (0 in normal use)
+    int test_idle_barrier_wait; // test hook (0 in normal use): after its row has arrived, every CTA of get_rows also waits on a
+                                // barrier that nothing ever signals, so that the bounded wait runs out and is reported
     agn_rope_slot rope_slots[AGN_ROPE_CACHE_SLOTS];
     int rope_next;
     bool flags_dirty;           // a kernel that can raise a flag ran since the last sync
     uint64_t launches;
+    bool ring_launched;         // set by a launcher that took the persistent form (read right after the launch)
+    const char *last_kernel;    // name given to AGN_LAUNCHED by the most recent launch (a string literal)
     std::string last_error;
 };
 
@@ -83,6 +91,7 @@ struct agn_event {
 
 int32_t agn_fail(agn_ctx *ctx, int32_t status, const char *fmt, ...);
 void agn_host_pipe_destroy(agn_ctx *ctx);
+int32_t agn_host_pipe_join(agn_ctx *ctx);  // the context's stream waits for the host-slice downloads enqueued so far
 
 // Device pointer to the powf(theta, 2d/n_rot) table, d < n_rot/2 (built on the host
 // with libm the first time a (theta, n_rot) pair is seen).
@@ -105,6 +114,7 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
 #define AGN_LAUNCHED(ctx, name)                                                        \
     do {                                                                               \
         (ctx)->launches++;                                                             \
+        (ctx)->last_kernel = (name);                                                   \
         cudaError_t _e = cudaPeekAtLastError();                                        \
         if (_e != cudaSuccess) {                                                       \
             (void)cudaGetLastError();                                                  \
@@ -210,14 +220,17 @@ inline int agn_ring_ctas_per_sm(agn_ctx *ctx, K kernel, int threads, size_t smem
     auto o = opted.find(std::make_tuple(ctx->device, kp));
     if (o == opted.end()) {
         int lim = 0;
+        cudaFuncAttributes fa;
+        // the opt-in limit covers static + dynamic shared memory: ask for what the kernel's static part leaves
         if (cudaDeviceGetAttribute(&lim, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device) != cudaSuccess ||
+            cudaFuncGetAttributes(&fa, kernel) != cudaSuccess || (lim -= (int)fa.sharedSizeBytes) <= 0 ||
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim) != cudaSuccess) {
             (void)cudaGetLastError();
             lim = 0;
         }
         o = opted.emplace(std::make_tuple(ctx->device, kp), lim).first;
     }
-    if ((size_t)o->second < smem + 1024) return 0;  // (static shared memory of the kernel counts against the limit too)
+    if ((size_t)o->second < smem) return 0;
     const auto key = std::make_tuple(ctx->device, kp, threads, smem);
     auto f = cache.find(key);
     if (f != cache.end()) return f->second;

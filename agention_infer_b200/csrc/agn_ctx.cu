@@ -47,6 +47,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     agn_ctx *ctx = new agn_ctx();
     ctx->device = device;
     ctx->launches = 0;
+    ctx->last_kernel = "";
     ctx->rope_next = 0;
     ctx->flags_dirty = false;
     ctx->d_flags = nullptr;
@@ -65,19 +66,23 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_get_rows_threads = 0;
     ctx->tune_softmax_vpt = 0;
     ctx->tune_softmax_cluster = 1;
+    ctx->tune_softmax_warp16 = 0;
+    ctx->tune_softmax_causal_pair = 1;
     ctx->tune_moe_small_sort = 1;
     ctx->tune_get_rows_tma = 1;
     ctx->tune_silu_unroll = 4;
     ctx->tune_silu_threads = 256;
-    ctx->tune_rms_ring = 1;
+    ctx->tune_silu_small = 1;
+    ctx->tune_rms_ring = 0;
     ctx->tune_rms_ring_ctas = 0;
-    ctx->tune_rope_ring = 1;
+    ctx->tune_rope_ring = 0;
     ctx->tune_rope_ring_ctas = 0;
-    ctx->tune_get_rows_ring = 1;
+    ctx->tune_get_rows_ring = 0;
     ctx->tune_get_rows_ring_ctas = 0;
     ctx->tune_ring_force = 0;
+    ctx->tune_host_chunk_bytes = 0;
     ctx->mbar_spin_limit = AGN_MBAR_SPIN_LIMIT_DEFAULT;
-    ctx->test_mbar_extra_bytes = 0;
+    ctx->test_idle_barrier_wait = 0;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
     const size_t rope_bytes = sizeof(float) * AGN_ROPE_CACHE_SLOTS * AGN_ROPE_MAX_HALF;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -134,6 +139,7 @@ int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream) {
 }
 
 uint64_t agn_ctx_launch_count(agn_ctx *ctx) { return ctx ? ctx->launches : 0; }
+const char *agn_ctx_last_kernel(agn_ctx *ctx) { return ctx ? ctx->last_kernel : ""; }
 
 int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
     AGN_CHECK_CTX(ctx);
@@ -187,8 +193,12 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
             {"get_rows_ring", &ctx->tune_get_rows_ring, 0, 16},
             {"get_rows_ring_ctas", &ctx->tune_get_rows_ring_ctas, 0, 32},
             {"ring_force", &ctx->tune_ring_force, 0, 1},
+            {"softmax_warp16", &ctx->tune_softmax_warp16, 0, 1},
+            {"softmax_causal_pair", &ctx->tune_softmax_causal_pair, 0, 1},
+            {"silu_small", &ctx->tune_silu_small, 0, 1},
+            {"host_chunk_bytes", &ctx->tune_host_chunk_bytes, 0, 24 << 20},
             {"mbar_spin_limit", &ctx->mbar_spin_limit, 1, 1 << 30},
-            {"test_mbar_extra_bytes", &ctx->test_mbar_extra_bytes, 0, 1 << 20},
+            {"test_idle_barrier_wait", &ctx->test_idle_barrier_wait, 0, 1},
         };
         for (auto &o : ints) {
             if (strcmp(name, o.name) != 0) continue;
@@ -281,6 +291,10 @@ int32_t agn_sync(agn_ctx *ctx) {
     AGN_CHECK_CTX(ctx);
     if (ctx->capturing) return agn_fail(ctx, AGN_EINVAL, "agn_sync: not allowed while a graph capture is open");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    {
+        const int32_t jrc = agn_host_pipe_join(ctx);  // the sync covers the downloads of host-slice ops
+        if (jrc != AGN_OK) return jrc;
+    }
     if (ctx->flags_dirty) {
         AGN_CUDA(ctx, cudaMemcpyAsync(ctx->h_flags, ctx->d_flags, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     }
@@ -324,6 +338,10 @@ int32_t agn_event_record(agn_ctx *ctx, agn_event *ev) {
     AGN_CHECK_CTX(ctx);
     if (!ev) return agn_fail(ctx, AGN_EINVAL, "agn_event_record: null event");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
+    {
+        const int32_t jrc = agn_host_pipe_join(ctx);  // an event after a host-slice op covers its downloads
+        if (jrc != AGN_OK) return jrc;
+    }
     AGN_CUDA(ctx, cudaEventRecord(ev->ev, ctx->stream));
     return AGN_OK;
 }

@@ -328,12 +328,14 @@ __device__ __forceinline__ void stage_row_chunks(uint8_t *stage, const uint8_t *
 template <int DTYPE, typename OUT, bool VEC_OUT, bool TMA>
 __global__ void __launch_bounds__(256)
 get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n_rows, int row_len, int row_bytes,
-                const uint32_t *__restrict__ ids, OUT *__restrict__ out, uint32_t *flags, int spin_limit, int test_extra_bytes) {
+                const uint32_t *__restrict__ ids, OUT *__restrict__ out, uint32_t *flags, int spin_limit, int test_idle_wait) {
     extern __shared__ __align__(128) uint8_t stage[];
     __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t idle_bar;  // test hook only: initialised, never signalled
     if (TMA) {
         if (threadIdx.x == 0) {
             agn_mbar_init(&bar, 1);
+            agn_mbar_init(&idle_bar, 1);
             agn_mbar_init_fence();
         }
         __syncthreads();  // barrier initialised before anyone polls it (runs ahead of the dependency wait)
@@ -355,13 +357,15 @@ get_rows_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int64_t n
     const bool bulk = TMA && a0 + 16 * (size_t)n16 <= table_bytes;  // same answer in every thread of the CTA
     if (bulk) {
         if (threadIdx.x == 0) {
-            // test_extra_bytes is 0 outside the test of the bounded wait, which arms the barrier
-            // for more bytes than the copy brings so that the wait below runs out
-            agn_mbar_expect_tx(&bar, 16u * (uint32_t)n16 + (uint32_t)test_extra_bytes);
+            agn_mbar_expect_tx(&bar, 16u * (uint32_t)n16);
             agn_bulk_g2s(stage, table + a0, 16u * (uint32_t)n16, &bar);
         }
-        if (!agn_mbar_wait(&bar, 0, spin_limit)) {
-            // the copy may still be writing shared memory: wait once more, bounded, before leaving
+        // (with the test hook the row itself is awaited with the default limit, so that no copy is in
+        // flight when the wait that is meant to run out, on the idle barrier, gives up)
+        if (!agn_mbar_wait(&bar, 0, test_idle_wait ? AGN_MBAR_SPIN_LIMIT_DEFAULT : spin_limit) ||
+            (test_idle_wait && !agn_mbar_wait(&idle_bar, 0, spin_limit))) {
+            // report it; the copy may still be writing shared memory: wait once more, bounded, before
+            // leaving.  The output row is not written.
             if (threadIdx.x == 0) atomicOr(flags, AGN_FLAG_TIMEOUT);
             (void)agn_mbar_wait(&bar, 0, spin_limit);
             return;
@@ -460,7 +464,7 @@ get_rows_ring_kernel(const uint8_t *__restrict__ table, size_t table_bytes, int6
 template <int DTYPE, typename OUT, bool VEC_OUT>
 bool launch_get_rows_ring(agn_ctx *ctx, int threads, const uint8_t *table, size_t table_bytes, int64_t n_rows, int row_len,
                           int row_bytes, const uint32_t *ids, int64_t T, OUT *out) {
-    if (ctx->tune_get_rows_ring == 0 || !ctx->tune_get_rows_tma || ctx->test_mbar_extra_bytes) return false;
+    if (ctx->tune_get_rows_ring == 0 || !ctx->tune_get_rows_tma || ctx->test_idle_barrier_wait) return false;
     const int slot_bytes = (((row_bytes + 15) / 16 + 2) * 16 + 127) & ~127;
     int slots = ctx->tune_get_rows_ring >= 2 ? ctx->tune_get_rows_ring : 4;
     while (slots > 2 && (size_t)slots * slot_bytes > 48 * 1024) slots--;
@@ -475,6 +479,7 @@ bool launch_get_rows_ring(agn_ctx *ctx, int threads, const uint8_t *table, size_
     if (grid > T) grid = T;
     agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, T,
                slots, slot_bytes, ctx->d_flags, ctx->mbar_spin_limit);
+    ctx->ring_launched = true;
     return true;
 }
 
@@ -494,7 +499,7 @@ cudaError_t launch_get_rows(agn_ctx *ctx, bool vec, int64_t T, int threads, size
         if (e != cudaSuccess) return e;
     }
     const bool tma = ctx->tune_get_rows_tma != 0;
-    const int lim = ctx->mbar_spin_limit, extra = ctx->test_mbar_extra_bytes;
+    const int lim = ctx->mbar_spin_limit, extra = ctx->test_idle_barrier_wait;  // extra: the idle-barrier test hook
     if (vec && tma)
         agn_launch(ctx, get_rows_kernel<DTYPE, OUT, true, true>, dim3(grid), dim3(threads), smem, table, table_bytes, n_rows, row_len, row_bytes, ids, out, ctx->d_flags, lim, extra);
     else if (vec)
@@ -538,6 +543,7 @@ int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t
     const uint8_t *tb = static_cast<const uint8_t *>(table);
     const int rl = (int)row_len, rb = (int)row_bytes;
     cudaError_t e;
+    ctx->ring_launched = false;
     switch (dtype) {
     case AGN_Q8_0: e = launch_get_rows<AGN_Q8_0, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
     case AGN_Q4_K: e = launch_get_rows<AGN_Q4_K, OUT>(ctx, vec, T, threads, smem, tb, table_bytes, n_rows, rl, rb, ids, out); break;
@@ -551,7 +557,8 @@ int32_t get_rows_dispatch(agn_ctx *ctx, int32_t dtype, const void *table, size_t
     }
     AGN_CUDA(ctx, e);
     ctx->flags_dirty = true;
-    AGN_LAUNCHED(ctx, "get_rows");
+    if (ctx->ring_launched) AGN_LAUNCHED(ctx, "get_rows_ring");
+    else AGN_LAUNCHED(ctx, "get_rows");
     return AGN_OK;
 }
 

@@ -35,9 +35,21 @@ struct agn_host_pipe {
     cudaEvent_t h2d_done[PIPE_SLOTS] = {}, k_done[PIPE_SLOTS] = {}, d2h_done[PIPE_SLOTS] = {};
     bool slot_used[PIPE_SLOTS] = {};
     cudaEvent_t op_done = nullptr;  // last device->host copy of the previous host op
+    bool join_pending = false;      // the context's stream has not been made to wait for op_done yet
     bool have_prev = false;
     std::vector<std::pair<uintptr_t, uintptr_t>> prev_out;  // host ranges the previous op writes
 };
+
+// Makes the context's stream wait for the downloads of the host-slice ops enqueued so far.  Done
+// lazily — by agn_sync and agn_event_record, not at the end of every host-slice op — so that the
+// kernels of the next host-slice op do not wait for the previous op's last downloads.
+int32_t agn_host_pipe_join(agn_ctx *ctx) {
+    agn_host_pipe *p = ctx->host_pipe;
+    if (!p || !p->join_pending) return AGN_OK;
+    AGN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, p->op_done, 0));
+    p->join_pending = false;
+    return AGN_OK;
+}
 
 void agn_host_pipe_destroy(agn_ctx *ctx) {
     agn_host_pipe *p = ctx->host_pipe;
@@ -102,7 +114,10 @@ int32_t run_pipelined(agn_ctx *ctx, const char *name, int64_t n_rows, const Host
     for (int b = 0; b < nb; b++) per_row += bufs[b].row_bytes;
     if (per_row + 256 * (size_t)nb > PIPE_SLOT_BYTES)
         return agn_fail(ctx, AGN_EINVAL, "%s: one row (%zu bytes over all buffers) exceeds a staging slot", name, per_row);
-    int64_t chunk = (int64_t)((PIPE_SLOT_BYTES - 256 * (size_t)nb) / per_row);
+    size_t slot_budget = PIPE_SLOT_BYTES;
+    if (ctx->tune_host_chunk_bytes >= (1 << 20) && (size_t)ctx->tune_host_chunk_bytes < slot_budget) slot_budget = (size_t)ctx->tune_host_chunk_bytes;
+    if (slot_budget < per_row + 256 * (size_t)nb) slot_budget = per_row + 256 * (size_t)nb;
+    int64_t chunk = (int64_t)((slot_budget - 256 * (size_t)nb) / per_row);
     // at least ~8 chunks per op so that the ring actually overlaps the three stages
     const int64_t want = (n_rows + 7) / 8;
     if (chunk > want) {
@@ -179,9 +194,9 @@ int32_t run_pipelined(agn_ctx *ctx, const char *name, int64_t n_rows, const Host
         AGN_CUDA(ctx, cudaEventRecord(p->d2h_done[s], p->d2h));
         p->slot_used[s] = true;
     }
-    // agn_sync waits on the context's stream: make it cover the downloads.
+    // agn_sync / agn_event_record make the context's stream wait for this (agn_host_pipe_join)
     AGN_CUDA(ctx, cudaEventRecord(p->op_done, p->d2h));
-    AGN_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, p->op_done, 0));
+    p->join_pending = true;
     p->prev_out.clear();
     for (int b = 0; b < nb; b++)
         if (bufs[b].h_out)

@@ -275,17 +275,19 @@ rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delt
         ActVec<OT>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
 }
 
+// Returns true when the persistent form was launched.
 template <typename T, typename OT, int VPT, bool RESIDUAL>
-void launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, OT *out, int64_t T_rows, int n4,
+bool launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new_x, OT *out, int64_t T_rows, int n4,
                 float eps, int threads) {
     const float4 *w4 = reinterpret_cast<const float4 *>(w);
-    if (ctx->tune_rms_recip && launch_ring<T, OT, VPT, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads)) return;
+    if (ctx->tune_rms_recip && launch_ring<T, OT, VPT, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads)) return true;
     if (ctx->tune_rms_recip)
         agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, true>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
                    new_x, out, n4, (float)(n4 * 4), eps);
     else
         agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, false>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
                    new_x, out, n4, (float)(n4 * 4), eps);
+    return false;
 }
 
 template <typename T, typename OT, bool RESIDUAL>
@@ -312,13 +314,15 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float 
         int threads = (n4 + vpt - 1) / vpt;
         threads = ((threads + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
+        bool ring;
         switch (vpt) {
-        case 1: launch_vec<T, OT, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        case 2: launch_vec<T, OT, 2, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        case 4: launch_vec<T, OT, 4, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
-        default: launch_vec<T, OT, 8, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 1: ring = launch_vec<T, OT, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 2: ring = launch_vec<T, OT, 2, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        case 4: ring = launch_vec<T, OT, 4, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
+        default: ring = launch_vec<T, OT, 8, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;
         }
-        AGN_LAUNCHED(ctx, name);
+        if (ring) AGN_LAUNCHED(ctx, "rms_norm_ring");
+        else AGN_LAUNCHED(ctx, name);
     } else {
         int threads = H >= 1024 ? 256 : (int)(((H + 31) / 32) * 32);
         if (threads > 256) threads = 256;

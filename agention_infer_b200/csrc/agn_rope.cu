@@ -130,7 +130,7 @@ __device__ __forceinline__ void rope_head_math(float4 (&v)[VPL], bool rot, const
         for (int l = 0; l < VPL; l++) {
             const int i = lane + W * l;
             if (rot && i < hd4) {
-                const float4 ww = __ldg(wv + i);
+                const float4 ww = wv[i];  // shared memory (CTA-per-unit kernel) or global memory (persistent kernel)
                 v[l].x = act_round<T>(ww.x * v[l].x * inv);
                 v[l].y = act_round<T>(ww.y * v[l].y * inv);
                 v[l].z = act_round<T>(ww.z * v[l].z * inv);
@@ -210,12 +210,23 @@ rope_heads_kernel(const RopeArgs a) {
     const int half = a.n_rot >> 1;
     const int n_heads = a.n_q + a.n_kv + (KV != KV_NONE ? a.n_kv : 0);  // head rows per token: Q, K and (fused cache write) V
     const int rows = a.tpc * n_heads;  // head rows of this CTA
-    // shared memory: row pointers | row meta (token in CTA, is-K flag) | cos | sin
+    // shared memory: row pointers | row meta (token in CTA, is-K flag) | cos | sin | (NORM) wq | wk
     T **s_ptr = reinterpret_cast<T **>(smem_raw);
     int *s_meta = reinterpret_cast<int *>(smem_raw + (size_t)rows * 8);
     float *s_cos = reinterpret_cast<float *>(smem_raw + (((size_t)rows * 12 + 15) & ~(size_t)15));
     float *s_sin = s_cos + a.tpc * half;
+    float *s_wq = s_sin + a.tpc * half + ((4 - ((2 * a.tpc * half) & 3)) & 3);  // 16-byte aligned
+    float *s_wk = s_wq + a.head_dim;
     const int64_t t0 = (int64_t)blockIdx.x * a.tpc;
+    if (NORM) {
+        // The norm weights are model parameters, not the previous kernel's output: they are staged
+        // ahead of the dependency wait, so their load latency is off the critical path of a
+        // decode-sized launch (a handful of CTAs whose whole life is one dependent chain).
+        for (int d = threadIdx.x; d < a.head_dim; d += blockDim.x) {
+            s_wq[d] = a.n_q > 0 ? a.wq[d] : 0.0f;
+            s_wk[d] = a.n_kv > 0 ? a.wk[d] : 0.0f;
+        }
+    }
 
     // one integer division per head row per CTA, instead of one per lane and slot
     for (int hr = threadIdx.x; hr < rows; hr += blockDim.x) {
@@ -269,7 +280,7 @@ rope_heads_kernel(const RopeArgs a) {
             const float *c_tab = s_cos + (meta[s] & 0xffff) * half;
             const float *s_tab = s_sin + (meta[s] & 0xffff) * half;
             rope_head_math<T, W, VPL, MODE, NORM>(v[s], ptr[s] != nullptr && kind < 2,
-                                                  reinterpret_cast<const float4 *>(kind == 1 ? a.wk : a.wq), c_tab, s_tab, lane, hd4, hq,
+                                                  reinterpret_cast<const float4 *>(kind == 1 ? s_wk : s_wq), c_tab, s_tab, lane, hd4, hq,
                                                   a.head_dim, a.n_rot, a.eps);
 #pragma unroll
             for (int l = 0; l < VPL; l++) {
@@ -522,6 +533,7 @@ bool launch_ring4(agn_ctx *ctx, const RopeArgs &a, int threads) {
     if (grid > n_units) grid = n_units;
     agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, a, slots, slot_bytes, ctx->mbar_spin_limit);
     ctx->flags_dirty = true;
+    ctx->ring_launched = true;
     return true;
 }
 
@@ -651,8 +663,10 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
         threads = ((threads + 31) / 32) * 32;
         if (threads > 256) threads = 256;
         const unsigned grid = (unsigned)((T + tpc - 1) / tpc);
-        const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1);
+        const size_t smem = (((size_t)rows * 12 + 15) & ~(size_t)15) + sizeof(float) * 2 * (size_t)tpc * (half > 0 ? half : 1) + 16 +
+                            (norm ? sizeof(float) * 2 * (size_t)head_dim : 0);
         bool ok = false;
+        ctx->ring_launched = false;
         if (kv_ok) {
             ok = launch_kv(ctx, a, norm, kvf->kv, W, VPL, mode, grid, threads, smem);
             if (ok) {
@@ -667,7 +681,8 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
         else if (W == 32 && VPL == 2) ok = launch_fast<AT, 32, 2>(ctx, a, norm, mode, grid, threads, smem);
         else if (W == 32 && VPL == 1) ok = launch_fast<AT, 32, 1>(ctx, a, norm, mode, grid, threads, smem);
         if (!ok) return agn_fail(ctx, AGN_EINVAL, "%s: internal dispatch error (W=%d VPL=%d mode=%d)", name, W, VPL, mode);
-        AGN_LAUNCHED(ctx, name);
+        if (ctx->ring_launched) AGN_LAUNCHED(ctx, norm ? "qk_norm_rope_ring" : "rope_ring");
+        else AGN_LAUNCHED(ctx, name);
     } else {
         int threads = n_heads >= 8 ? 256 : 32 * n_heads;
         const size_t smem = sizeof(float) * 2 * (size_t)(half > 0 ? half : 1);

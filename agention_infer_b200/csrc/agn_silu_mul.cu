@@ -106,7 +106,16 @@ int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, OT *out, int
     if (n == 0) return AGN_OK;
     if (!gate || !up || !out) return agn_fail(ctx, AGN_EINVAL, "silu_mul: null pointer");
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
-    const int THREADS = ctx->tune_silu_threads, UNROLL = ctx->tune_silu_unroll;
+    int THREADS = ctx->tune_silu_threads, UNROLL = ctx->tune_silu_unroll;
+    // Decode-sized inputs (a few token rows): with the streaming shape a row of 18944 values is five
+    // CTAs whose threads each run sixteen expf + IEEE divisions back to back, which is a microsecond
+    // of dependent arithmetic on five SMs.  One float4 pair per thread in 128-thread CTAs spreads
+    // the same work over 37 CTAs per row; up to about two such CTAs per thread slot of the GPU this
+    // is the faster shape, beyond it the deep-unrolled streaming shape takes over.
+    if (ctx->tune_silu_small && n / 4 <= (int64_t)ctx->sm_count * 2048) {
+        THREADS = 128;
+        UNROLL = 1;
+    }
     constexpr int A = ActVec<T>::ALIGN;
     int64_t done = 0;
     if (agn_aligned(gate, A) && agn_aligned(up, A) && agn_aligned(out, ActVec<OT>::ALIGN)) {
@@ -115,7 +124,8 @@ int32_t silu_mul_dispatch(agn_ctx *ctx, const T *gate, const T *up, OT *out, int
             const int64_t per_cta = (int64_t)THREADS * UNROLL;
             const int64_t blocks = (n4 + per_cta - 1) / per_cta;
             if (blocks > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "silu_mul: n too large");
-            if (UNROLL == 2) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 2>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
+            if (UNROLL == 1) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 1>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
+            else if (UNROLL == 2) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 2>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
             else if (UNROLL == 8) agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 8>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
             else agn_launch(ctx, silu_mul_vec4_kernel<T, OT, 4>, dim3((unsigned)blocks), dim3(THREADS), 0, gate, up, out, n4);
             AGN_LAUNCHED(ctx, "silu_mul_vec4");

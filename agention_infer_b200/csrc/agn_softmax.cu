@@ -150,7 +150,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
 }
 
 template <typename OT, int VPL>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256, VPL >= 16 ? 2 : 4)
 softmax_warp_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
     const int lane = threadIdx.x & 31;
@@ -239,6 +239,102 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
         const int i = threadIdx.x + k * blockDim.x;
         if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
         else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
+    }
+}
+
+// Square causal matrices ([heads, L, L], row i of a head has i + 1 valid entries): rows i and
+// L-1-i of a head are done by ONE CTA, so every CTA loads and stores the same L + 1 valid entries
+// whatever i is.  With a CTA per row, half of the CTAs hold mostly masked rows: their threads keep
+// their registers but have no load in flight, and the kernel ends up bound by latency rather than by
+// HBM once the output shrinks (16-bit probabilities, or the tail left unwritten).  The CTA's
+// threads walk the concatenation [valid part of row A | valid part of row B] in float4 steps;
+// maxima and sums are kept per row (two values through every reduction).
+template <typename OT, int VPT>
+__global__ void __launch_bounds__(1024)
+softmax_causal_pair_kernel(const SoftmaxArgs a) {
+    agn_pdl_prologue();
+    __shared__ float red[2][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int L = (int)a.row_len, n4 = L >> 2;
+    const int half_rows = (L + 1) >> 1;
+    const int64_t head = blockIdx.x / half_rows;
+    const int p = (int)(blockIdx.x - head * half_rows);
+    const int rowA = p, rowB = L - 1 - p;       // rowB == rowA for the middle row of an odd L
+    const bool twoRows = rowB != rowA;
+    const int nvA = rowA + 1, nvB = twoRows ? rowB + 1 : 0;
+    const int vA = (nvA + 3) >> 2, vB = (nvB + 3) >> 2;  // float4 that hold valid entries
+    const int64_t rA = head * L + rowA, rB = head * L + rowB;
+    const float4 *inA = reinterpret_cast<const float4 *>(a.in + rA * a.row_stride);
+    const float4 *inB = reinterpret_cast<const float4 *>(a.in + rB * a.row_stride);
+    OT *outA = static_cast<OT *>(a.out) + rA * a.row_stride, *outB = static_cast<OT *>(a.out) + rB * a.row_stride;
+    // vector j of the concatenation: row A's float4 number j for j < vA, else row B's number j - vA
+    float4 v[VPT];
+    int idx[VPT];  // float4 index inside its row, or -1; bit 30 set = row B
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        const int j = threadIdx.x + k * blockDim.x;
+        const bool isB = j >= vA;
+        const int i = isB ? j - vA : j;
+        const bool on = isB ? i < vB : true;
+        idx[k] = on ? (i | (isB ? (1 << 30) : 0)) : -1;
+        v[k] = on ? agn_ld_stream((isB ? inB : inA) + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float mA = -INFINITY, mB = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        if (idx[k] >= 0) {
+            const bool isB = (idx[k] >> 30) & 1;
+            mask_tail(v[k], idx[k] & 0x3fffffff, isB ? nvB : nvA);
+            const float m = max4(v[k]);
+            if (isB) mB = fmaxf(mB, m);
+            else mA = fmaxf(mA, m);
+        }
+    }
+    mA = agn_warp_max(mA);
+    mB = agn_warp_max(mB);
+    if (lane == 0) { red[0][warp] = mA; red[1][warp] = mB; }
+    __syncthreads();
+    mA = -INFINITY; mB = -INFINITY;
+    for (int w = 0; w < nwarps; w++) { mA = fmaxf(mA, red[0][w]); mB = fmaxf(mB, red[1][w]); }
+    __syncthreads();
+    float sA = 0.0f, sB = 0.0f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        if (idx[k] >= 0) {
+            const bool isB = (idx[k] >> 30) & 1;
+            v[k] = exp4(v[k], isB ? mB : mA, a.exp_coef);
+            const float t = (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            if (isB) sB += t;
+            else sA += t;
+        }
+    }
+    sA = agn_warp_sum(sA);
+    sB = agn_warp_sum(sB);
+    if (lane == 0) { red[0][warp] = sA; red[1][warp] = sB; }
+    __syncthreads();
+    sA = 0.0f; sB = 0.0f;
+    for (int w = 0; w < nwarps; w++) { sA += red[0][w]; sB += red[1][w]; }
+    if (a.sums && threadIdx.x == 0) {
+        a.sums[rA] = sA;
+        if (twoRows) a.sums[rB] = sB;
+    }
+    const float invA = a.sums ? 1.0f : 1.0f / sA, invB = (a.sums || !twoRows) ? 1.0f : 1.0f / sB;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+        if (idx[k] >= 0) {
+            const bool isB = (idx[k] >> 30) & 1;
+            const float inv = isB ? invB : invA;
+            store_probs<OT>(isB ? outB : outA, idx[k] & 0x3fffffff, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv),
+                            isB ? nvB : nvA, n4, a.leave_tail != 0);
+        }
+    }
+    if (!a.leave_tail) {
+        // the float4 wholly past the valid length of either row: n4 - vA of row A, then n4 - vB of row B
+        const int zA = n4 - vA, zB = twoRows ? n4 - vB : 0;
+        for (int z = threadIdx.x; z < zA + zB; z += blockDim.x) {
+            if (z < zA) ActVec<OT>::store(outA, vA + z, make_float4(0.f, 0.f, 0.f, 0.f));
+            else ActVec<OT>::store(outB, vB + (z - zA), make_float4(0.f, 0.f, 0.f, 0.f));
+        }
     }
 }
 
@@ -404,13 +500,17 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, in
         else if (n4 <= 4) agn_launch(ctx, softmax_thread_rows_kernel<OT, 4>, dim3(grid), dim3(256), 0, a);
         else agn_launch(ctx, softmax_thread_rows_kernel<OT, 8>, dim3(grid), dim3(256), 0, a);
         AGN_LAUNCHED(ctx, "softmax_thread_rows");
-    } else if (vec_ok && n4 <= 256) {
+    } else if (vec_ok && (n4 <= 256 || (n4 <= 512 && ctx->tune_softmax_warp16))) {
+        // one warp per row, statistics by shuffles alone; rows of 1025-2048 entries (sixteen float4 per
+        // lane) too: a prefill's causal rows are this long, half of them mostly masked, and a CTA per
+        // row with its two block-wide barriers is then bound by CTA turnover, not by HBM
         const int warps = 8;
         const unsigned grid = (unsigned)((n_rows + warps - 1) / warps);
         if (n4 <= 32) agn_launch(ctx, softmax_warp_rows_kernel<OT, 1>, dim3(grid), dim3(32 * warps), 0, a);
         else if (n4 <= 64) agn_launch(ctx, softmax_warp_rows_kernel<OT, 2>, dim3(grid), dim3(32 * warps), 0, a);
         else if (n4 <= 128) agn_launch(ctx, softmax_warp_rows_kernel<OT, 4>, dim3(grid), dim3(32 * warps), 0, a);
-        else agn_launch(ctx, softmax_warp_rows_kernel<OT, 8>, dim3(grid), dim3(32 * warps), 0, a);
+        else if (n4 <= 256) agn_launch(ctx, softmax_warp_rows_kernel<OT, 8>, dim3(grid), dim3(32 * warps), 0, a);
+        else agn_launch(ctx, softmax_warp_rows_kernel<OT, 16>, dim3(grid), dim3(32 * warps), 0, a);
         AGN_LAUNCHED(ctx, "softmax_warp_rows");
     } else if (vec_ok && n4 > 4096 && ctx->tune_softmax_cluster && n_rows <= 0x7fffffffLL / 8 && n4 <= 8 * 16 * 512) {
         // 2..8 CTAs (the portable cluster limit) of <= 512 threads; 8 float4 per thread, or 16 for rows
@@ -425,6 +525,18 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, in
         else
             agn_launch_cluster(ctx, softmax_cluster_rows_kernel<OT, 16>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
         AGN_LAUNCHED(ctx, "softmax_cluster_rows");
+    } else if (vec_ok && n4 <= 8192 && ctx->tune_softmax_causal_pair && !n_valid && causal_period == row_len && causal_offset == 0 &&
+               n_rows % row_len == 0) {
+        // square causal matrices: rows i and L-1-i share a CTA, L + 1 valid entries per CTA (nine
+        // float4 per thread: eight and the one or two vectors by which the two rounded-up halves exceed a row)
+        constexpr int VPT = 9;
+        int threads = (int)((n4 + 7) / 8);
+        threads = ((threads + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        const int64_t heads = n_rows / row_len;
+        const int64_t grid = heads * ((row_len + 1) / 2);
+        agn_launch(ctx, softmax_causal_pair_kernel<OT, VPT>, dim3((unsigned)grid), dim3(threads), 0, a);
+        AGN_LAUNCHED(ctx, "softmax_causal_pair");
     } else if (vec_ok && n4 <= 8192) {
         // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries
         // (fewer warps in the two block-wide reductions, more loads in flight per thread)

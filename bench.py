@@ -144,6 +144,14 @@ def op_bytes(cfg, T, ops, act_bytes=4):
     return {k: table[k] for k in ops}
 
 
+def workload_config(cfg, tokens_per_gpu, tokens_total, ops, world):
+    """The `config` object of the JSON line: what the workload is, the same keys and values in both arms."""
+    return {"workload": cfg.name, "tokens_per_gpu": tokens_per_gpu, "tokens_total": tokens_total, "hidden": cfg.hidden,
+            "head_dim": cfg.head_dim, "q_heads": cfg.n_q_heads, "kv_heads": cfg.n_kv_heads, "ffn": cfg.ffn,
+            "embedding": f"{DTYPE_NAMES[cfg.embd_dtype]} {cfg.vocab}x{cfg.hidden}", "ops": list(ops),
+            "parallelism": f"token rows sharded over {world} rank(s), no data-path collective"}
+
+
 # ------------------------------------------------------------------- CPU (reference) arm
 
 def host_threads():
@@ -221,11 +229,11 @@ def time_cpu(orc, cfg, data, rows, ops, threads, reps):
 def cpu_sample(cfg, ops):
     """Bounded sample of the workload for the host arm: at most 4096 token rows (the whole batch of
     the headline configuration; all 512 for the causal-softmax configuration, whose scores need
-    whole heads) and a 16384-row table."""
+    whole heads), ids drawn over the configuration's whole embedding table."""
     from oracle import oracle as orc
     rows = cfg.T if "softmax" in ops else min(cfg.T, 4096)
-    data, vocab = host_data(cfg, rows, ops, vocab_rows=min(cfg.vocab, 16384))
-    return orc, rows, data, dataclasses.replace(cfg, vocab=vocab, T=rows), vocab
+    data, vocab = host_data(cfg, rows, ops)
+    return orc, rows, data, dataclasses.replace(cfg, T=rows), vocab
 
 
 def run_reference(args, cfg, ops, wl):
@@ -249,12 +257,15 @@ def run_reference(args, cfg, ops, wl):
     dt = (time.perf_counter() - t0) / args.steps
     value = rows / dt
     sample = f"{rows} of {cfg.T} token rows per step, table of {vocab} rows, OpenMP over rows"
+    world = max(1, args.gpus)
+    scaling = WORKLOADS[wl][2]
+    per_gpu = cfg.T // world if scaling == "strong" else cfg.T
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": WORKLOADS[wl][2], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens_per_step": rows, "hidden": cfg.hidden, "ffn": cfg.ffn,
-                   "embedding": DTYPE_NAMES[cfg.embd_dtype], "ops": ops},
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, per_gpu, cfg.T if scaling == "strong" else world * cfg.T, ops, world),
+        "sample_rows_per_step": rows,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -302,6 +313,9 @@ def setup_cuda(args):
     assert be.stream() == stream.cuda_stream
     if args.no_pdl:
         be.set_option("pdl", 0)
+    for kv in args.set_option or []:  # tuning knobs of agn_ctx_set_option, e.g. --set-option rms_ring=3
+        name, _, val = kv.partition("=")
+        be.set_option(name, int(val))
     return torch, dist, be, dev, stream, sampler, rank, world, local
 
 
@@ -333,22 +347,36 @@ def run_ours(args, cfg, ops_list, wl):
     pos = torch.from_numpy(synth.positions(cfg.index, T, cfg.random_pos)).to(dev)
     gen = torch.Generator(device=dev)
     rn = lambda *shape: torch.randn(*shape, device=dev, generator=gen).to(adt)
+    # Buffer set 0 holds seeded host bytes (the same arrays the CPU arm and the oracle read) and is what the
+    # outputs are checked on after the timed region; the other sets hold device-generated values that differ
+    # per rank.  (The 16 GB configuration generates set 0 on the device too: its host copy would be 17 GB.)
+    host0 = None
+    if step_bytes < 4e9:
+        ci = cfg.index
+        host0 = {"x": synth.activations(ci, "x", (T, H)), "q": synth.activations(ci, "q", (T, nq * hd)),
+                 "k": synth.activations(ci, "k", (T, nkv * hd)), "gate": synth.activations(ci, "gate", (R, I)),
+                 "up": synth.activations(ci, "up", (R, I))}
+        if "softmax" in ops_list:
+            host0["scores"] = synth.causal_scores(ci, nq, T)
+        if E:
+            host0["logits"] = synth.activations(ci, "logits", (T, E))
+    up0 = lambda name: torch.from_numpy(host0[name]).to(dev).to(adt)
     sets = []
     for s in range(nsets):
-        # buffer set 0 holds the same values on every rank (its outputs are compared across ranks
-        # at the end); the other sets differ per rank
         salt = 0 if s == 0 else 1 + rank * NSETS + s
         gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index + 7919 * salt)
         ids = torch.from_numpy(synth.token_ids(cfg.index, T, cfg.vocab, salt=salt).astype(np.int32)).to(dev)
-        b = {"ids": ids, "emb": torch.empty(T, H, device=dev, dtype=adt), "x": rn(T, H),
-             "xn": torch.empty(T, H, device=dev, dtype=adt), "q": rn(T, nq * hd), "k": rn(T, nkv * hd), "gate": rn(R, I),
-             "up": rn(R, I), "act": torch.empty(R, I, device=dev, dtype=adt)}
+        from_host = s == 0 and host0 is not None
+        mk = (lambda name, *shape: up0(name)) if from_host else (lambda name, *shape: rn(*shape))
+        b = {"ids": ids, "emb": torch.empty(T, H, device=dev, dtype=adt), "x": mk("x", T, H),
+             "xn": torch.empty(T, H, device=dev, dtype=adt), "q": mk("q", T, nq * hd), "k": mk("k", T, nkv * hd),
+             "gate": mk("gate", R, I), "up": mk("up", R, I), "act": torch.empty(R, I, device=dev, dtype=adt)}
         if "qk_norm_rope_qk" in ops_list:
-            b.update(q2=rn(T, nq * hd), k2=rn(T, nkv * hd))
+            b.update(q2=mk("q", T, nq * hd), k2=mk("k", T, nkv * hd))
         if "softmax" in ops_list:
-            b.update(scores=rn(nq, T, T) * 2.0, probs=torch.empty(nq, T, T, device=dev))
+            b.update(scores=up0("scores") if from_host else rn(nq, T, T) * 2.0, probs=torch.empty(nq, T, T, device=dev))
         if E:
-            b.update(logits=rn(T, E), ridx=torch.empty(T, 2, dtype=torch.int32, device=dev),
+            b.update(logits=mk("logits", T, E), ridx=torch.empty(T, 2, dtype=torch.int32, device=dev),
                      rw=torch.empty(T, 2, device=dev), gx=torch.empty(2 * T, H, device=dev),
                      goff=torch.empty(E + 1, dtype=torch.int32, device=dev),
                      gtok=torch.empty(2 * T, dtype=torch.int32, device=dev),
@@ -409,7 +437,9 @@ def run_ours(args, cfg, ops_list, wl):
         torch.cuda.synchronize()
     barrier()
 
-    # ---- timed region: exactly K steps, device time, max over ranks
+    # ---- timed regions: exactly K steps each, device time, max over ranks; the K-step region is repeated
+    #      `repeats` times back to back (each bracketed by barrier + synchronize) and the median region is the
+    #      reported one, so that the headline does not rest on a few milliseconds
     use_graph = args.graph == "on" or (args.graph == "auto" and step_bytes < 2e8)  # launch-bound steps: one graph replay each
     silu_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -419,22 +449,27 @@ def run_ours(args, cfg, ops_list, wl):
             be.graph_begin(); step(s_); graphs.append(be.graph_end())
         for s_ in range(nsets):
             be.graph_launch(graphs[s_])
+    region_ms, silu_samples, launches = [], [], 0
+    for rep in range(max(1, args.repeats)):
         barrier()
-    n0 = be.launch_count
-    start.record(stream)
-    if use_graph:
-        for i in range(args.steps):
-            be.graph_launch(graphs[i % nsets])
-    else:
-        for i in range(args.steps):
-            step(i, silu_ev[i])
-    stop.record(stream)
-    barrier()
-    launches = be.launch_count - n0
-    elapsed_ms = sharding.max_over_ranks(start.elapsed_time(stop))
+        n0 = be.launch_count
+        start.record(stream)
+        if use_graph:
+            for i in range(args.steps):
+                be.graph_launch(graphs[i % nsets])
+        else:
+            for i in range(args.steps):
+                step(i, silu_ev[i])
+        stop.record(stream)
+        barrier()
+        launches = be.launch_count - n0
+        region_ms.append(sharding.max_over_ranks(start.elapsed_time(stop)))
+        if not use_graph:
+            silu_samples += [a.elapsed_time(b) for i, (a, b) in enumerate(silu_ev) if i % 4 == 0]
     for g_ in graphs:
         be.graph_destroy(g_)
-    silu_ms = None if use_graph else float(np.mean([a.elapsed_time(b) for i, (a, b) in enumerate(silu_ev) if i % 4 == 0]))
+    silu_ms = float(np.mean(silu_samples)) if silu_samples else None
+    elapsed_ms = float(np.median(region_ms))
     ms_per_step = elapsed_ms / args.steps
     value = T_total / (ms_per_step * 1e-3)
 
@@ -489,7 +524,7 @@ def run_ours(args, cfg, ops_list, wl):
                             "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev),
                             "pb": torch.empty(nq, Ls, Ls, dtype=torch.bfloat16, device=dev),
                             "ab": torch.empty(R, I, dtype=torch.bfloat16, device=dev),
-                            "g": sets[s_]["gate"], "u": sets[s_]["up"]})
+                            "g": sets[s_]["gate"], "u": sets[s_]["up"], "q2": sets[s_].get("q2"), "k2": sets[s_].get("k2")})
         extras = {
             "add_residual_rms_norm": (lambda b: be.launch_add_residual_rms_norm(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], normed=b["nm"]),
                                       16 * T * H + 4 * H),
@@ -509,6 +544,12 @@ def run_ours(args, cfg, ops_list, wl):
                                                               causal_period=Ls),
                 4 * (nq * Ls * (Ls + 1) // 2) + 2 * nq * Ls * Ls),
         }
+        if "qk_norm_rope_qk" in ops_list:
+            # QK-norm -> RoPE of q and k and the f16 cache write of the rotated k and of v, one launch
+            extras["qk_norm_rope_kv_write_f16"] = (
+                lambda b: be.launch_qk_norm_rope_kv_write(b["q2"], b["k2"], b["v"], wq, wk, T, nq, nkv, hd, cfg.eps, cfg.n_rot,
+                                                          pos, cfg.theta, KV_F16, b["kh"], b["vh"], T),
+                ab["qk_norm_rope_qk"] + T * (4 * hd_kv + 2 * 2 * hd_kv))
         # the reference's form: entries past the valid length are not written
         extras[f"softmax_causal_leave_tail_{nq}x{Ls}x{Ls}"] = (
             lambda b: be.launch_softmax_rows_valid(b["sc"], nq * Ls, Ls, b["pr"], causal_period=Ls),
@@ -581,25 +622,95 @@ def run_ours(args, cfg, ops_list, wl):
                "ms_per_step": e2e_ms, "steps": e2e_steps,
                "api": "host-slice entry points (agn_host_*), pinned host arrays, 3-stream staging ring"}
 
-    # ---- verification gather (the only collective): per-rank checksums of one op's output
-    #      recomputed from identical inputs (buffer set 0 is re-seeded, because the timed steps have
-    #      rotated q and k in place), so all ranks must agree bit for bit
+    # ---- the two other configurations a driver run should see: the decode chain (one GPU) and the large batch
+    #      split over the ranks (every N).  The headline buffers make room first.
+    decode_rec = split_rec = None
+    if world == 1 and not args.no_decode and not f16:
+        sw, fl, c3 = decode_sweep(torch, be, dev, stream, 20)
+        decode_rec = {"workload": c3.name, "chain": "28 x (qk_norm_rope_qk + silu_mul), random positions", "sweep": sw,
+                      "launch_floor": fl, "us_graph_T1": sw[0]["us_graph"]}
+    if not args.no_split and not f16 and wl == "c2":
+        for b in sets[1:]:
+            b.clear()
+        torch.cuda.empty_cache()
+        split_rec = strong_split_record(torch, be, dev, stream, rank, world, barrier, sharding.max_over_ranks)
+
+    # ---- verification.  (1) Against the CPU oracle, outside every timed region: the inputs of buffer set 0 are
+    #      restored (the timed steps rotated q and k in place), every op runs once more, and a strided sample of
+    #      rows of every output is compared with the oracle's result for the same input rows, which are read
+    #      back from the device — bit-exact for the embedding rows and the routing, 1e-5 of the row scale for the
+    #      float ops.  (2) Across ranks: per-rank checksums of the same outputs (set 0 is identical on every
+    #      rank), gathered over the process group — the only collective.
     b0 = sets[0]
-    gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index)
-    fresh = {n: rn(*b0[n].shape) for n in ("x", "q", "k", "gate", "up")}
-    for n, t in fresh.items():
-        b0[n].copy_(t)
-    if "qk_norm_rope_qk" in order:
-        b0["q2"].copy_(fresh["q"]); b0["k2"].copy_(fresh["k"])
+    if host0 is not None:
+        for n in ("x", "q", "k", "gate", "up"):
+            b0[n].copy_(up0(n))
+        if "qk_norm_rope_qk" in order:
+            b0["q2"].copy_(up0("q")); b0["k2"].copy_(up0("k"))
+    else:
+        gen.manual_seed(synth.BASE_SEED + 1000 * cfg.index)
+        fresh = {n: rn(*b0[n].shape) for n in ("x", "q", "k", "gate", "up")}
+        for n, t in fresh.items():
+            b0[n].copy_(t)
+        if "qk_norm_rope_qk" in order:
+            b0["q2"].copy_(fresh["q"]); b0["k2"].copy_(fresh["k"])
+        del fresh
+    n_chk = min(T, args.check_rows)
+    rows = np.unique(np.linspace(0, T - 1, n_chk).astype(np.int64))
+    rows_t = torch.from_numpy(rows).to(dev)
+    take = lambda t, idx=None: t.index_select(0, rows_t if idx is None else idx).float().cpu().numpy()
+    ins = {n: take(b0[n]) for n in ("x", "q", "k")}
+    rrows = np.unique(np.linspace(0, R - 1, n_chk).astype(np.int64)); rrows_t = torch.from_numpy(rrows).to(dev)
+    ins["gate"], ins["up"] = take(b0["gate"], rrows_t), take(b0["up"], rrows_t)
     for name in order:
         ops[name](b0)
     be.sync()
     torch.cuda.synchronize()
+    oracle_report = None
+    if not f16 and not args.no_verify:
+        from oracle import oracle as orc
+        pos_h = synth.positions(cfg.index, T, cfg.random_pos)[rows]
+        w_h, wq_h, wk_h = (synth.norm_weight(cfg.index, n, m) for n, m in (("w", H), ("wq", hd), ("wk", hd)))
+        rel = synth.max_rel_to_row_scale
+        err = {}
+        for name in order:
+            if name == "get_rows":
+                ids_h = b0["ids"].cpu().numpy().view(np.uint32)[rows]
+                _, ref = orc.get_rows(cfg.embd_dtype, table_h, cfg.vocab, H, ids_h)
+                err[name] = 0.0 if np.array_equal(take(b0["emb"]).view(np.uint32), ref.view(np.uint32)) else float("inf")
+            elif name == "rms_norm":
+                err[name] = rel(take(b0["xn"]), orc.rms_norm_rows(ins["x"], w_h, cfg.eps))
+            elif name == "rope_qk":
+                err[name] = max(rel(take(b0["q"]), orc.rope_rows(ins["q"], nq, hd, cfg.n_rot, pos_h, cfg.theta)),
+                                rel(take(b0["k"]), orc.rope_rows(ins["k"], nkv, hd, cfg.n_rot, pos_h, cfg.theta)))
+            elif name == "qk_norm_rope_qk":
+                err[name] = max(
+                    rel(take(b0["q2"]), orc.qk_norm_rope_rows(ins["q"], wq_h, nq, hd, cfg.eps, cfg.n_rot, pos_h, cfg.theta)),
+                    rel(take(b0["k2"]), orc.qk_norm_rope_rows(ins["k"], wk_h, nkv, hd, cfg.eps, cfg.n_rot, pos_h, cfg.theta)))
+            elif name == "silu_mul":
+                err[name] = rel(take(b0["act"], rrows_t), orc.silu_mul(ins["gate"], ins["up"]))
+            elif name == "softmax":  # rows `rows` of every head; row i of a head has i + 1 valid entries
+                sc = b0["scores"].index_select(1, rows_t).cpu().numpy().reshape(-1, T)
+                pr = b0["probs"].index_select(1, rows_t).cpu().numpy().reshape(-1, T)
+                err[name] = rel(pr, orc.softmax_rows(sc, np.tile(rows + 1, nq).astype(np.int32)))
+            elif name == "router_top2":
+                ridx_ref, rw_ref = orc.router_top2(take(b0["logits"]))
+                same = np.array_equal(take(b0["ridx"]).astype(np.int32), ridx_ref)
+                err[name] = float(np.max(np.abs(take(b0["rw"]) - rw_ref))) * 10.0 if same else float("inf")  # weights within 1e-6
+            elif name == "gather_rows_by_expert":  # a global sort: the whole batch
+                ref = orc.gather_rows_by_expert(b0["x"].cpu().numpy(), b0["ridx"].cpu().numpy(), E)
+                got = (b0["gx"].cpu().numpy(), b0["goff"].cpu().numpy(), b0["gtok"].cpu().numpy(), b0["gslot"].cpu().numpy())
+                err[name] = 0.0 if all(np.array_equal(g.view(np.uint32), r.view(np.uint32)) for g, r in zip(got, ref)) else float("inf")
+        oracle_report = {"max_rel_err": {k: float(f"{v:.3g}") for k, v in err.items()}, "rows_checked": int(rows.size),
+                         "tolerance": 1e-5, "bit_exact_ops": [o for o in order if o in ("get_rows", "gather_rows_by_expert")],
+                         "ok": all(v <= 1e-5 for v in err.values()),
+                         "how": "rows of buffer set 0 re-run after the timed regions, oracle fed the same input rows"}
     outs = ["emb", "xn", "q", "k", "act"] + (["q2", "k2"] if "qk_norm_rope_qk" in order else []) + \
            (["probs"] if "softmax" in order else []) + (["ridx", "gx"] if E else [])
     mine = [sharding.checksum(b0[n][: min(T, 512)].contiguous().cpu().numpy()) for n in outs]
     chk = sharding.gather_objects(mine)
     agree = all(c == chk[0] for c in chk)
+    verified = agree and (oracle_report is None or oracle_report["ok"])
 
     if rank == 0:
         peak, peak_src = measured_peaks()
@@ -611,14 +722,16 @@ def run_ours(args, cfg, ops_list, wl):
         achieved = ab["silu_mul"] / (silu_ms * 1e-3) / 1e9
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": n_warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "f32" if not f16 else "f16 storage, f32 arithmetic", "data": "synthetic",
-            "config": {"workload": cfg.name, "tokens_per_gpu": T, "tokens_total": T_total, "hidden": H, "head_dim": hd,
-                       "q_heads": nq, "kv_heads": nkv, "ffn": I,
-                       "embedding": f"{DTYPE_NAMES[cfg.embd_dtype]} {cfg.vocab}x{H}", "ops": order,
-                       "parallelism": f"token rows sharded over {world} GPU(s), no data-path collective",
-                       "l2": f"inputs larger than L2: {nsets} rotating buffer sets, {step_bytes / 1e9:.2f} GB per step",
-                       "launch": "one CUDA graph replay per step" if use_graph else "stream launches"},
+            "config": workload_config(cfg, T, T_total, order, world),
+            "timing": {"l2": f"inputs larger than L2: {nsets} rotating buffer sets, {step_bytes / 1e9:.2f} GB per step",
+                       "launch": "one CUDA graph replay per step" if use_graph else "stream launches",
+                       "preheat_steps": n_warm, "repeats": len(region_ms),
+                       "ms_per_step_median": ms_per_step, "ms_per_step_min": min(region_ms) / args.steps,
+                       "ms_per_step_max": max(region_ms) / args.steps,
+                       "what": "K steps per region, regions back to back, each bracketed by barrier + synchronize; "
+                               "value and ms_per_step are the median region"},
             "hbm_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9 * world,
             "hbm_frac_of_measured_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
             "hbm_frac_of_nominal_8tbs": step_bytes / (ms_per_step * 1e-3) / 1e9 / 8000.0,
@@ -629,7 +742,9 @@ def run_ours(args, cfg, ops_list, wl):
                          "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
             "ops": per_op, "extra_ops": extra_ops, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk), "outputs_checked": outs, "identical_across_ranks": agree,
-                             "how": "checksums of every op's output for identical inputs, gathered over the process group"},
+                             "how": "checksums of every op's output for identical inputs, gathered over the process group",
+                             "oracle": oracle_report},
+            "strong_c4": split_rec, "decode_c3": decode_rec,
         }
         if world == 1 and not args.no_cpu and not f16:
             out["cpu_baseline"] = cpu_baseline(cfg, order)
@@ -637,22 +752,21 @@ def run_ours(args, cfg, ops_list, wl):
     if world > 1:
         dist.destroy_process_group()
     be.close()
+    if not verified:
+        raise SystemExit("bench: outputs differ from the CPU oracle (or between ranks); see `verification` in the JSON line")
 
 
-def run_decode_sweep(args):
+def decode_sweep(torch, be, dev, stream, steps, seed_salt=0):
     """Decode-shaped latency sweep (Qwen2.5-7B shapes): for T in {1, 8, 32, 64} tokens per step with
     random positions, the fused norm->rope and SiLU*mul kernels run back to back for 28 layers.
-    Timed as plain stream launches and as one CUDA graph replay."""
+    Timed as plain stream launches and as one CUDA graph replay.  Returns (sweep, launch floor)."""
     from agention_infer_b200 import synth
-    torch, dist, be, dev, stream, sampler, rank, world, local = setup_cuda(args)
     cfg = synth.CONFIGS["c3"]
     H, hd, nq, nkv, I, layers = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn, 28
     wq = torch.from_numpy(synth.norm_weight(cfg.index, "wq", hd)).to(dev)
     wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
-    gen = torch.Generator(device=dev); gen.manual_seed(synth.BASE_SEED + 3000 + rank)
+    gen = torch.Generator(device=dev); gen.manual_seed(synth.BASE_SEED + 3000 + seed_salt)
     sweep = []
-    if sampler:
-        sampler.mark_load(True)
 
     def timed(fn, reps):
         a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -675,6 +789,7 @@ def run_decode_sweep(args):
         be.graph_launch(g0)
     floor_graph = timed(lambda: be.graph_launch(g0), 50)
     be.graph_destroy(g0)
+    reps = max(steps, 20)
     for T in (1, 8, 32, 64):
         pos = torch.from_numpy(synth.positions(cfg.index, T, True)).to(dev)
         # one buffer set per layer: 28 layers of activations are distinct memory, as in the engine
@@ -690,28 +805,29 @@ def run_decode_sweep(args):
         for _ in range(5):
             chain()
         torch.cuda.synchronize()
-        reps = max(args.steps, 20)
-        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for _ in range(reps):
-            chain()
-        b_.record(stream); torch.cuda.synchronize()
-        us_plain = a.elapsed_time(b_) * 1e3 / reps
+        us_plain = timed(chain, reps)
         be.graph_begin(); chain(); g = be.graph_end()  # recorded through the library's own graph entry points
         for _ in range(5):
             be.graph_launch(g)
         torch.cuda.synchronize()
-        a.record(stream)
-        for _ in range(reps):
-            be.graph_launch(g)
-        b_.record(stream); torch.cuda.synchronize()
-        us_graph = a.elapsed_time(b_) * 1e3 / reps
+        us_graph = timed(lambda: be.graph_launch(g), reps)
         be.graph_destroy(g)
         bytes_chain = layers * (8 * T * (nq + nkv) * hd + 12 * T * I)
         sweep.append({"T": T, "layers": layers, "launches": 2 * layers, "us_plain": round(us_plain, 2),
                       "us_graph": round(us_graph, 2), "us_per_layer_graph": round(us_graph / layers, 3),
                       "gbs_graph": round(bytes_chain / (us_graph * 1e-6) / 1e9, 1),
                       "tokens_per_s_graph": round(T / (us_graph * 1e-6), 1)})
+    floor = {"kernels": 2 * layers, "us_plain": round(floor_plain, 2), "us_graph": round(floor_graph, 2),
+             "what": "the same number of empty kernels"}
+    return sweep, floor, cfg
+
+
+def run_decode_sweep(args):
+    """`--workload c3`: the decode sweep as the run's own JSON line."""
+    torch, dist, be, dev, stream, sampler, rank, world, local = setup_cuda(args)
+    if sampler:
+        sampler.mark_load(True)
+    sweep, floor, cfg = decode_sweep(torch, be, dev, stream, args.steps, seed_salt=rank)
     if sampler:
         sampler.mark_load(False)
     clocks = sampler.stop() if sampler else None
@@ -721,14 +837,101 @@ def run_decode_sweep(args):
             "metric": "decode_layer_chain_tokens_per_s", "value": best["tokens_per_s_graph"], "unit": UNIT, "n_gpus": world,
             "steps": max(args.steps, 20), "warmup": 5, "ms_per_step": best["us_graph"] / 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": cfg.name, "chain": "28 x (qk_norm_rope_qk + silu_mul)", "hidden": H, "ffn": I,
+            "config": {"workload": cfg.name, "chain": "28 x (qk_norm_rope_qk + silu_mul)", "hidden": cfg.hidden, "ffn": cfg.ffn,
                        "positions": "random in [0, 32768)", "timing": "CUDA graph replay vs plain launches"},
-            "launch_floor": {"kernels": 2 * layers, "us_plain": round(floor_plain, 2), "us_graph": round(floor_graph, 2),
-                             "what": "the same number of empty kernels"},
-            "sweep": sweep, "clocks": clocks, "gpu_launches": 2 * layers * max(args.steps, 20), "e2e": None}))
+            "launch_floor": floor,
+            "sweep": sweep, "clocks": clocks, "gpu_launches": 2 * 28 * max(args.steps, 20), "e2e": None}))
     if world > 1:
         dist.destroy_process_group()
     be.close()
+
+
+def strong_split_record(torch, be, dev, stream, rank, world, barrier, max_over_ranks, steps=10):
+    """The large prefill batch (Llama-3-8B shapes, T = 65536 token rows, Q6_K embedding 128256 x 4096) with its rows
+    SPLIT over the ranks: T / world rows per GPU, no data-path collective.  Device time of K steps (max over ranks)
+    and of every op alone.  With more than one rank, rank 0 then runs the whole batch by itself, so that the
+    efficiency against one GPU comes from the same invocation."""
+    from agention_infer_b200 import sharding, synth
+    cfg = synth.CONFIGS["c4"]
+    ops_list = WORKLOADS["c4"][1]
+    H, hd, nq, nkv, I = cfg.hidden, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn
+    table_h = synth.quant_table(cfg.embd_dtype, cfg.vocab, H, cfg_index=cfg.index)
+    table = torch.from_numpy(table_h).to(dev)
+    w = torch.from_numpy(synth.norm_weight(cfg.index, "w", H)).to(dev)
+    wq = torch.from_numpy(synth.norm_weight(cfg.index, "wq", hd)).to(dev)
+    wk = torch.from_numpy(synth.norm_weight(cfg.index, "wk", hd)).to(dev)
+    gen = torch.Generator(device=dev)
+
+    def measure(T, row0, collective):
+        nsets = 2 if T > 16384 else 4  # every launch reads inputs that are not in L2 (>= 2 GB per set)
+        pos = torch.arange(row0, row0 + T, dtype=torch.int32, device=dev)
+        sets = []
+        for s_ in range(nsets):
+            gen.manual_seed(synth.BASE_SEED + 4000 + 7919 * (1 + rank * NSETS + s_))
+            rn = lambda *shape: torch.randn(*shape, device=dev, generator=gen)
+            ids = torch.from_numpy(synth.token_ids(cfg.index, T, cfg.vocab, salt=1 + rank * NSETS + s_).astype(np.int32)).to(dev)
+            sets.append({"ids": ids, "emb": torch.empty(T, H, device=dev), "x": rn(T, H), "xn": torch.empty(T, H, device=dev),
+                         "q": rn(T, nq * hd), "k": rn(T, nkv * hd), "q2": rn(T, nq * hd), "k2": rn(T, nkv * hd),
+                         "gate": rn(T, I), "up": rn(T, I), "act": torch.empty(T, I, device=dev)})
+        ops = {
+            "get_rows": lambda b: be.get_rows(cfg.embd_dtype, table, table_h.nbytes, cfg.vocab, H, b["ids"], T, out=b["emb"]),
+            "rms_norm": lambda b: be.launch_rms_norm(b["x"], w, T, H, cfg.eps, out=b["xn"]),
+            "rope_qk": lambda b: be.launch_rope_qk(b["q"], b["k"], T, nq, nkv, hd, cfg.n_rot, pos, cfg.theta),
+            "qk_norm_rope_qk": lambda b: be.launch_qk_norm_rope_qk(b["q2"], b["k2"], wq, wk, T, nq, nkv, hd, cfg.eps, cfg.n_rot,
+                                                                   pos, cfg.theta),
+            "silu_mul": lambda b: be.launch_silu_mul(b["gate"], b["up"], T * I, out=b["act"]),
+        }
+        ab = op_bytes(cfg, T, ops_list)
+
+        def step(i):
+            for name in ops_list:
+                ops[name](sets[i % nsets])
+
+        sync = barrier if collective else torch.cuda.synchronize
+        for i in range(3):
+            step(i)
+        sync()
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(steps):
+            step(i)
+        b_.record(stream)
+        sync()
+        ms = a.elapsed_time(b_)
+        if collective:
+            ms = max_over_ranks(ms)
+        per_op = {}
+        for name in ops_list:
+            for i in range(2):
+                ops[name](sets[i % nsets])
+            torch.cuda.synchronize()
+            a.record(stream)
+            for i in range(steps):
+                ops[name](sets[i % nsets])
+            b_.record(stream)
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b_) * 1e3 / steps
+            per_op[name] = {"us": round(us, 2), "gbs": round(ab[name] / (us * 1e-6) / 1e9, 1)}
+        del sets
+        torch.cuda.empty_cache()
+        return ms / steps, per_op, sum(ab.values())
+
+    r0, r1 = sharding.shard_rows(cfg.T, rank, world)
+    ms_split, per_op, bytes_rank = measure(r1 - r0, r0, world > 1)
+    rec = {"workload": cfg.name, "scaling": "strong", "tokens_total": cfg.T, "tokens_per_gpu": r1 - r0, "n_gpus": world,
+           "steps": steps, "ms_per_step": ms_split, "tokens_per_s": cfg.T / (ms_split * 1e-3),
+           "hbm_gbs_per_gpu": bytes_rank / (ms_split * 1e-3) / 1e9, "ops_rank0": per_op,
+           "embedding": f"{DTYPE_NAMES[cfg.embd_dtype]} {cfg.vocab}x{H}"}
+    if world == 1:
+        rec.update(ms_per_step_n1=ms_split, efficiency_vs_n1=1.0)
+    else:
+        ms_n1 = None
+        if rank == 0:  # the other ranks wait at the barrier below
+            ms_n1, _, _ = measure(cfg.T, 0, False)
+        barrier()
+        rec.update(ms_per_step_n1=ms_n1, efficiency_vs_n1=(ms_n1 / world / ms_split) if ms_n1 else None,
+                   n1_how="rank 0 ran all 65536 rows by itself in the same invocation, the other ranks idle")
+    return rec
 
 
 def main():
@@ -749,6 +952,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the ops measured outside the step")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches (for comparison)")
+    ap.add_argument("--set-option", action="append", metavar="NAME=INT",
+                    help="a tuning knob passed to agn_ctx_set_option before the run (repeatable)")
+    ap.add_argument("--no-verify", action="store_true", help="skip the comparison of the outputs with the CPU oracle")
+    ap.add_argument("--no-split", action="store_true", help="skip the strong_c4 record (the large batch split over the ranks)")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode_c3 record (one GPU)")
+    ap.add_argument("--repeats", type=int, default=25, help="how many times the K-step timed region is repeated (median reported)")
+    ap.add_argument("--check-rows", type=int, default=64, help="rows of every output compared with the oracle")
     ap.add_argument("--warm-seconds", type=float, default=0.6,
                     help="minimum duration of the warm-up (0 for profiling runs)")
     ap.add_argument("--tokens", type=int, default=None,

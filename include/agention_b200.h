@@ -109,6 +109,11 @@ AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value
 AGN_API int32_t agn_launch_noop(agn_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 AGN_API uint64_t agn_ctx_launch_count(agn_ctx *ctx);
+/* Which kernel family the most recent launch of this context took, e.g. "rms_norm" (one CTA per
+ * row) or "rms_norm_ring" (persistent CTAs with a staged row ring): a diagnostic for tests and
+ * profiling, the counterpart of the kernel names the reference's per-kernel
+ * tracing prints (GGUF_TRACE_KERNEL, src/ops/trace.rs).  Never NULL; "" before the first launch. */
+AGN_API const char *agn_ctx_last_kernel(agn_ctx *ctx);
 
 /* `client.empty(bytes)` / `client.create_from_slice` / `read_one_unchecked`
  * (src/ops/wgpu_backend/resident.rs:195,673-700). Copies are stream-ordered;

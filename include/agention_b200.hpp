@@ -71,6 +71,8 @@ class CudaBackend {
     const char *name() const { return agn_backend_name(); }  // Backend::name, src/ops/mod.rs:99
     agn_ctx *ctx() const { return ctx_; }
     uint64_t launch_count() const { return agn_ctx_launch_count(ctx_); }
+    // kernel family of the most recent launch (a diagnostic; see agn_ctx_last_kernel)
+    std::string last_kernel() const { return agn_ctx_last_kernel(ctx_); }
     void sync() { check(agn_sync(ctx_)); }
 
     DeviceBuffer empty(size_t bytes) {  // client.empty, resident.rs:195

@@ -94,3 +94,16 @@ def test_softmax_full_rows_sum_to_one(backend):
     assert synth.max_rel_to_row_scale(got[r], orc.softmax_rows(s[r], nv, THREADS)) <= TOL
     # idempotence of the support: entries past the valid length are exactly zero
     assert not got[0, 1:].any() and not got[L - 2, L - 1:].any()
+
+
+def test_silu_mul_headline_size_against_the_oracle_in_full(backend):
+    """The dominant kernel on the headline shape (Qwen2.5-7B-shaped prefill: 4096 rows x 18944, 77.6 M elements):
+    every element against the oracle, not a sample."""
+    Tq, Iq = 4096, 18944
+    g = synth.activations(2, "gate", (Tq, Iq)); u = synth.activations(2, "up", (Tq, Iq))
+    ref = orc.silu_mul(g, u, THREADS)
+    out = backend.launch_silu_mul(backend.upload(g), backend.upload(u), Tq * Iq)
+    assert backend.last_kernel == "silu_mul_vec4"
+    got = backend.read(out, np.float32, (Tq, Iq))
+    assert synth.max_rel_to_row_scale(got, ref) <= TOL
+    assert np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)) <= TOL

@@ -73,3 +73,48 @@ def test_graph_misuse_is_reported(backend):
     g = backend.graph_end()
     backend.graph_destroy(g)
     backend.sync()
+
+
+def test_rope_with_a_cold_table_cannot_be_recorded(backend):
+    """The (theta, n_rot) table is built on the host and copied from a staging slot: recording that copy would make
+    every replay re-copy whatever the slot holds later.  A rope op whose table does not exist yet is refused inside a
+    capture (the capture survives); after one run outside, the same op records and replays."""
+    be = backend
+    T, nh, hd, theta = 4, 2, 64, 12345.0 + 0.25  # a theta no other test uses: its table is certainly cold
+    x = synth.activations(3, "q", (T, nh * hd)); pos = synth.positions(3, T, True)
+    dx, dp = be.upload(x), be.upload(pos)
+    be.graph_begin()
+    with pytest.raises(BackendError) as e:
+        be.launch_rope(dx, T, nh, hd, hd, dp, theta)
+    assert "before" in str(e.value) and "graph" in str(e.value)
+    g = be.graph_end()  # an empty graph: the refused op recorded nothing
+    be.graph_destroy(g)
+    assert np.array_equal(be.read(dx, np.float32, x.shape), x)
+    be.launch_rope(dx, T, nh, hd, hd, dp, theta); be.sync()  # builds the table
+    be.copy_h2d(dx, x); be.sync()
+    be.graph_begin()
+    be.launch_rope(dx, T, nh, hd, hd, dp, theta)
+    g = be.graph_end()
+    be.graph_launch(g)
+    assert synth.max_rel_to_row_scale(be.read(dx, np.float32, x.shape), orc.rope_rows(x, nh, hd, hd, pos, theta)) <= TOL
+    be.graph_destroy(g)
+
+
+def test_rope_tables_used_by_a_graph_are_not_evicted(backend):
+    """More (theta, n_rot) pairs than the table cache holds: a pair that a recorded graph uses keeps its slot, so the
+    graph still computes with its own theta afterwards."""
+    be = backend
+    T, nh, hd, theta = 3, 2, 64, 777.5
+    x = synth.activations(3, "q", (T, nh * hd)); pos = synth.positions(3, T, True)
+    dx, dp, scratch = be.upload(x), be.upload(pos), be.upload(x)
+    be.launch_rope(dx, T, nh, hd, hd, dp, theta); be.sync()
+    be.copy_h2d(dx, x); be.sync()
+    be.graph_begin()
+    be.launch_rope(dx, T, nh, hd, hd, dp, theta)
+    g = be.graph_end()
+    for k in range(24):  # cycle through more pairs than there are slots
+        be.launch_rope(scratch, T, nh, hd, hd, dp, 1000.0 + 17.0 * k)
+    be.sync()
+    be.graph_launch(g)
+    assert synth.max_rel_to_row_scale(be.read(dx, np.float32, x.shape), orc.rope_rows(x, nh, hd, hd, pos, theta)) <= TOL
+    be.graph_destroy(g)

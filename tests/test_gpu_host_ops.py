@@ -101,3 +101,12 @@ def test_host_ops_chain_output_feeds_next_input(backend):
     backend.sync()
     ref = orc.rms_norm_rows(orc.rms_norm_rows(x, w, 1e-5, THREADS), w, 1e-5, THREADS)
     assert synth.max_rel_to_row_scale(out, ref) <= 2 * TOL
+
+
+def test_hostlink_probe_one_gpu():
+    """The pinned-copy probe that bounds the host-slice path: runs, and reports plausible figures."""
+    from agention_infer_b200 import hostlink
+    r = hostlink.probe(1, mb=32, reps=3)
+    row = r["active_gpus"]["1"]
+    assert set(row) == {"h2d", "d2h", "both_per_direction"}
+    assert all(1.0 < row[c]["mean_gbs_per_gpu"] < 1000.0 for c in row)

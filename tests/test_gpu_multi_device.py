@@ -39,3 +39,29 @@ def test_two_contexts_two_devices_interleaved(backend):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))  # both GPUs agree bit for bit
     finally:
         be1.close()
+
+
+def test_events_and_copies_follow_their_own_context(backend):
+    """Events, copies and syncs of a context act on that context's device whatever the last op left current: time
+    a kernel on device 1 right after work on device 0, and the other way round."""
+    be1 = _second_backend()
+    try:
+        T, H = 512, 2048
+        x = synth.activations(1, "x", (T, H)); w = synth.norm_weight(1, "w", H)
+        ref = orc.rms_norm_rows(x, w, 1e-5)
+        for first, second in ((backend, be1), (be1, backend)):
+            d0x, d0w = first.upload(x), first.upload(w)
+            first.launch_rms_norm(d0x, d0w, T, H, 1e-5)  # leaves `first`'s device current
+            dx, dw = second.upload(x), second.upload(w)
+            first.launch_rms_norm(d0x, d0w, T, H, 1e-5)  # ... again, right before the events of `second`
+            e0, e1 = second.event(), second.event()
+            second.record(e0)
+            out = second.launch_rms_norm(dx, dw, T, H, 1e-5)
+            second.record(e1)
+            second.sync()
+            assert 0.0 < second.elapsed_ms(e0, e1) < 1000.0
+            assert synth.max_rel_to_row_scale(second.read(out, np.float32, (T, H)), ref) <= 1e-5
+            second.destroy_event(e0); second.destroy_event(e1)
+            first.sync()
+    finally:
+        be1.close()

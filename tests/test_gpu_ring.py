@@ -1,8 +1,8 @@
 """The persistent kernels with a staged row ring (rms_norm, add_residual_rms_norm, rope, fused
 norm->rope, get_rows) against the CPU oracle, called through the C ABI.
 
-Large batches take these kernels by themselves; the option "ring_force" makes small and ragged
-batches take them too, so that the partial last unit, rows that wrap the ring several times, one
+They are opt-in (options "rms_ring", "rope_ring", "get_rows_ring"; the CTA-per-row kernels are
+the measured-faster default); the option "ring_force" makes small and ragged batches take them too, so that the partial last unit, rows that wrap the ring several times, one
 row per CTA and the chunked copy of the table's last row are all covered.  get_rows is
 bit-exact; float ops are within 1e-5 of the row scale.  The persistent and the CTA-per-row
 kernels perform the same operations in the same order, so their outputs are also compared bit
@@ -32,11 +32,11 @@ def bits(a):
 @pytest.fixture()
 def ring(backend):
     """Backend with the persistent kernels forced on; options restored afterwards."""
-    backend.set_option("ring_force", 1)
+    for name in ("ring_force", "rms_ring", "rope_ring", "get_rows_ring"):
+        backend.set_option(name, 1)
     yield backend
-    for name, v in (("ring_force", 0), ("rms_ring", 1), ("rms_ring_ctas", 0), ("rope_ring", 1), ("rope_ring_ctas", 0),
-                    ("get_rows_ring", 1), ("get_rows_ring_ctas", 0)):
-        backend.set_option(name, v)
+    for name in ("ring_force", "rms_ring", "rms_ring_ctas", "rope_ring", "rope_ring_ctas", "get_rows_ring", "get_rows_ring_ctas"):
+        backend.set_option(name, 0)
 
 
 @pytest.mark.parametrize("slots,ctas", [(1, 0), (2, 1), (5, 2)])
@@ -47,9 +47,11 @@ def test_rms_norm_ring(ring, T, H, slots, ctas):
     ref = orc.rms_norm_rows(x, w, 1e-6, THREADS)
     dx, dw = ring.upload(x), ring.upload(w)
     got = ring.read(ring.launch_rms_norm(dx, dw, T, H, 1e-6), np.float32, (T, H))
+    assert ring.last_kernel == "rms_norm_ring"
     assert rel(got, ref) <= TOL
     ring.set_option("rms_ring", 0)
     old = ring.read(ring.launch_rms_norm(dx, dw, T, H, 1e-6), np.float32, (T, H))
+    assert ring.last_kernel == "rms_norm"
     assert np.array_equal(bits(got), bits(old))
 
 
@@ -58,6 +60,7 @@ def test_add_residual_rms_norm_ring(ring, T, H):
     x = synth.activations(4, "x", (T, H)); d = synth.activations(4, "delta", (T, H)); w = synth.norm_weight(4, "w", H)
     ref_nx, ref_nm = orc.add_residual_rms_norm_rows(x, d, w, 1e-5)
     nx, nm = ring.launch_add_residual_rms_norm(ring.upload(x), ring.upload(d), ring.upload(w), T, H, 1e-5)
+    assert ring.last_kernel == "rms_norm_ring"
     assert np.array_equal(bits(ring.read(nx, np.float32, (T, H))), bits(ref_nx))
     assert rel(ring.read(nm, np.float32, (T, H)), ref_nm) <= TOL
 
@@ -68,6 +71,7 @@ def test_rms_norm_ring_in_place(ring):
     ref = orc.rms_norm_rows(x, w, 1e-5, THREADS)
     dx = ring.upload(x)
     ring.launch_rms_norm(dx, ring.upload(w), T, H, 1e-5, out=dx)  # a row is staged before it is overwritten
+    assert ring.last_kernel == "rms_norm_ring"
     assert rel(ring.read(dx, np.float32, (T, H)), ref) <= TOL
 
 
@@ -77,18 +81,30 @@ def test_rms_norm_out16_ring(ring, out_dtype):
     x = synth.activations(2, "x", (T, H)); w = synth.norm_weight(2, "w", H)
     dx, dw = ring.upload(x), ring.upload(w)
     got = ring.read(ring.launch_rms_norm_out16(dx, dw, T, H, 1e-6, out_dtype), np.uint16, (T, H))
+    assert ring.last_kernel == "rms_norm_ring"
     ring.set_option("rms_ring", 0)
     old = ring.read(ring.launch_rms_norm_out16(dx, dw, T, H, 1e-6, out_dtype), np.uint16, (T, H))
     assert np.array_equal(got, old)
 
 
 def test_rms_norm_natural_ring_size(backend):
-    """4096 rows engage the persistent kernel without any option."""
+    """With "rms_ring" = 1 (automatic depth) 4096 rows engage the persistent kernel; 64 rows do not."""
     T, H = 4096, 3584
+    backend.set_option("rms_ring", 1)
+    try:
+        _rms_natural(backend, T, H)
+    finally:
+        backend.set_option("rms_ring", 0)
+
+
+def _rms_natural(backend, T, H):
     x = synth.activations(2, "x", (T, H)); w = synth.norm_weight(2, "w", H)
     ref = orc.rms_norm_rows(x, w, 1e-6, THREADS)
     got = backend.read(backend.launch_rms_norm(backend.upload(x), backend.upload(w), T, H, 1e-6), np.float32, (T, H))
+    assert backend.last_kernel == "rms_norm_ring"
     assert rel(got, ref) <= TOL
+    backend.launch_rms_norm(backend.upload(x[:64]), backend.upload(w), 64, H, 1e-6)
+    assert backend.last_kernel == "rms_norm"
 
 
 ROPE_RING_CASES = [  # T, n_q, n_kv, head_dim, n_rot, theta
@@ -120,8 +136,10 @@ def test_rope_ring(ring, norm, layout, T, nq, nkv, hd, n_rot, theta):
                                         1.0, layout)
         else:
             ring.launch_rope_qk(dq, dk if nkv else None, T, nq, nkv, hd, n_rot, dp, theta, 1.0, layout)
+        kernels.append(ring.last_kernel)
         return ring.read(dq, np.float32, q.shape), ring.read(dk, np.float32, k.shape)
 
+    kernels = []
     gq, gk = run()
     assert rel(gq, rq) <= TOL
     if nkv:
@@ -131,6 +149,11 @@ def test_rope_ring(ring, norm, layout, T, nq, nkv, hd, n_rot, theta):
     ring.set_option("rope_ring", 0)
     oq, ok = run()
     assert np.array_equal(bits(gq), bits(oq)) and np.array_equal(bits(gk), bits(ok))
+    # (head_dim 96 with NeoX pairing has no register fast path, persistent or not: it runs the generic kernel)
+    has_fast_path = not (hd == 96 and layout == AGN_ROPE_NEOX)
+    assert kernels[0].endswith("_ring") == has_fast_path and not kernels[1].endswith("_ring")
+    if has_fast_path:
+        assert kernels[0] == ("qk_norm_rope_ring" if norm else "rope_ring")
 
 
 def test_rope_natural_ring_size(backend):
@@ -139,7 +162,12 @@ def test_rope_natural_ring_size(backend):
     pos = synth.positions(2, T, False)
     rq = orc.rope_rows(q, nq, hd, hd, pos, 1e6, 1.0, 0, THREADS); rk = orc.rope_rows(k, nkv, hd, hd, pos, 1e6, 1.0, 0, THREADS)
     dq, dk = backend.upload(q), backend.upload(k)
-    backend.launch_rope_qk(dq, dk, T, nq, nkv, hd, hd, backend.upload(pos), 1e6)
+    backend.set_option("rope_ring", 1)
+    try:
+        backend.launch_rope_qk(dq, dk, T, nq, nkv, hd, hd, backend.upload(pos), 1e6)
+        assert backend.last_kernel == "rope_ring"
+    finally:
+        backend.set_option("rope_ring", 0)
     assert rel(backend.read(dq, np.float32, q.shape), rq) <= TOL
     assert rel(backend.read(dk, np.float32, k.shape), rk) <= TOL
 
@@ -156,6 +184,7 @@ def test_get_rows_ring(ring, dtype, vocab, H, T, slots, ctas):
     st, ref = orc.get_rows(dtype, table, vocab, H, ids)
     assert st == orc.OK
     out = ring.get_rows(dtype, ring.upload(table), table.nbytes, vocab, H, ring.upload(ids), T)
+    assert ring.last_kernel == "get_rows_ring"
     assert np.array_equal(bits(ring.read(out, np.float32, (T, H))), bits(ref))
 
 
@@ -166,6 +195,7 @@ def test_get_rows_ring_out_of_range_id(ring):
     ids[[3, 250, 499]] = [vocab, 2 ** 31, 2 ** 32 - 1]
     _, ref = orc.get_rows(dtype, table, vocab, H, ids)
     out = ring.get_rows(dtype, ring.upload(table), table.nbytes, vocab, H, ring.upload(ids), T)
+    assert ring.last_kernel == "get_rows_ring"
     with pytest.raises(BackendError) as e:
         ring.sync()
     assert e.value.status == _abi.AGN_EOOB_ID
@@ -179,5 +209,10 @@ def test_get_rows_natural_ring_size(backend):
     table = synth.quant_table(dtype, vocab, H, cfg_index=2)
     ids = synth.token_ids(2, T, vocab)
     _, ref = orc.get_rows(dtype, table, vocab, H, ids, THREADS)
-    out = backend.get_rows(dtype, backend.upload(table), table.nbytes, vocab, H, backend.upload(ids), T)
+    backend.set_option("get_rows_ring", 1)
+    try:
+        out = backend.get_rows(dtype, backend.upload(table), table.nbytes, vocab, H, backend.upload(ids), T)
+        assert backend.last_kernel == "get_rows_ring"
+    finally:
+        backend.set_option("get_rows_ring", 0)
     assert np.array_equal(bits(backend.read(out, np.float32, (T, H))), bits(ref))

@@ -250,3 +250,47 @@ def test_softmax_leave_tail_untouched(backend, R, L):
     assert np.array_equal(got16[valid], zero_filled.astype(np.float16).view(np.uint16)[valid]) and np.all(got16[~valid] == 0x1234)
     assert np.array_equal(got_ip[valid].view(np.uint32), zero_filled[valid].view(np.uint32))
     assert np.array_equal(got_ip[~valid].view(np.uint32), s[~valid].view(np.uint32))  # the scores past the valid length survive
+
+
+@pytest.mark.parametrize("heads,L", [(3, 2048), (2, 1028), (1, 4096), (2, 1100)])
+def test_softmax_square_causal_row_pairs(backend, heads, L):
+    """Square causal matrices of more than 1024 columns run rows i and L-1-i in one CTA: every form of the op
+    (zero-filled, valid entries only, 16-bit rows, unnormalised + sums, scaled, in place) against the oracle."""
+    s = synth.causal_scores(1, heads, L)
+    nv = np.tile(np.arange(1, L + 1, dtype=np.int32), heads)
+    ref = orc.softmax_rows(s, nv, max(1, orc.max_threads()))
+    ds = backend.upload(s)
+    got = backend.read(backend.launch_softmax_rows(ds, heads * L, L, causal_period=L), np.float32, s.shape)
+    assert backend.last_kernel == "softmax_causal_pair"
+    assert synth.max_rel_to_row_scale(got, ref) <= 1e-5
+    upper = np.triu(np.ones((L, L), dtype=bool), k=1)
+    assert not got[:, upper].any()
+    # the CTA-per-row kernel gives the same values to within the tolerance (different reduction tree)
+    backend.set_option("softmax_causal_pair", 0)
+    try:
+        per_row = backend.read(backend.launch_softmax_rows(ds, heads * L, L, causal_period=L), np.float32, s.shape)
+        assert backend.last_kernel != "softmax_causal_pair"
+    finally:
+        backend.set_option("softmax_causal_pair", 1)
+    assert synth.max_rel_to_row_scale(per_row, got) <= 2e-6
+    # valid entries only: the tail keeps the sentinel, the valid part is bit-identical to the zero-filled form
+    out = backend.upload(np.full(s.shape, -7.25, np.float32))
+    backend.launch_softmax_rows_valid(ds, heads * L, L, out, causal_period=L)
+    assert backend.last_kernel == "softmax_causal_pair"
+    g2 = backend.read(out, np.float32, s.shape)
+    assert np.array_equal(g2[:, ~upper].view(np.uint32), got[:, ~upper].view(np.uint32)) and np.all(g2[:, upper] == -7.25)
+    # bf16 rows = the f32 result rounded to nearest even
+    o16 = backend.launch_softmax_rows_scaled_out16(ds, heads * L, L, 1.0, AGN_BF16, causal_period=L)
+    g16 = backend.read(o16, np.uint16, s.shape)
+    assert np.array_equal(g16, to_bf16_bits(got).reshape(s.shape))
+    # unnormalised weights and sums with a score scale (the reference kernel's form)
+    sums = backend.empty(4 * heads * L)
+    wts = backend.read(backend.launch_softmax_rows_scaled(ds, heads * L, L, 0.125, sums=sums, causal_period=L), np.float32, s.shape)
+    sm = backend.read(sums, np.float32, (heads, L))
+    ref_scaled = orc.softmax_rows(s * np.float32(0.125), nv, max(1, orc.max_threads()))
+    assert synth.max_rel_to_row_scale(wts / sm[:, :, None], ref_scaled) <= 1e-5
+    assert np.allclose(wts.sum(axis=2, dtype=np.float64), sm, rtol=1e-5)
+    # in place
+    inplace = backend.upload(s)
+    backend.launch_softmax_rows(inplace, heads * L, L, out=inplace, causal_period=L)
+    assert np.array_equal(backend.read(inplace, np.float32, s.shape).view(np.uint32), got.view(np.uint32))
