@@ -71,6 +71,8 @@ struct agn_ctx {
     int tune_rms_ring, tune_rms_ring_ctas;
     int tune_rope_ring, tune_rope_ring_ctas;
     int tune_get_rows_ring, tune_get_rows_ring_ctas;
+    int tune_softmax_ring, tune_softmax_ring_ctas;
+    int tune_host_slots;        // host-slice ops: slots of the staging ring (2..16, read when the ring is created; 0 = 8)
     int tune_host_chunk_bytes;  // host-slice ops: bytes of one staging chunk over all buffers (0 = a whole 24 MiB slot)
     int tune_ring_force;        // 1 = take the persistent form whenever it applies, however few rows (tests)
     int mbar_spin_limit;        // polls before a staging wait gives up

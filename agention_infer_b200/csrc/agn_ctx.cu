@@ -79,8 +79,11 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_rope_ring_ctas = 0;
     ctx->tune_get_rows_ring = 0;
     ctx->tune_get_rows_ring_ctas = 0;
+    ctx->tune_softmax_ring = 0;
+    ctx->tune_softmax_ring_ctas = 0;
     ctx->tune_ring_force = 0;
     ctx->tune_host_chunk_bytes = 0;
+    ctx->tune_host_slots = 0;
     ctx->mbar_spin_limit = AGN_MBAR_SPIN_LIMIT_DEFAULT;
     ctx->test_idle_barrier_wait = 0;
     memset(ctx->rope_slots, 0, sizeof(ctx->rope_slots));
@@ -192,11 +195,14 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
             {"rope_ring_ctas", &ctx->tune_rope_ring_ctas, 0, 32},
             {"get_rows_ring", &ctx->tune_get_rows_ring, 0, 16},
             {"get_rows_ring_ctas", &ctx->tune_get_rows_ring_ctas, 0, 32},
+            {"softmax_ring", &ctx->tune_softmax_ring, 0, 8},
+            {"softmax_ring_ctas", &ctx->tune_softmax_ring_ctas, 0, 32},
             {"ring_force", &ctx->tune_ring_force, 0, 1},
             {"softmax_warp16", &ctx->tune_softmax_warp16, 0, 1},
             {"softmax_causal_pair", &ctx->tune_softmax_causal_pair, 0, 1},
             {"silu_small", &ctx->tune_silu_small, 0, 1},
             {"host_chunk_bytes", &ctx->tune_host_chunk_bytes, 0, 24 << 20},
+            {"host_slots", &ctx->tune_host_slots, 0, 16},
             {"mbar_spin_limit", &ctx->mbar_spin_limit, 1, 1 << 30},
             {"test_idle_barrier_wait", &ctx->test_idle_barrier_wait, 0, 1},
         };

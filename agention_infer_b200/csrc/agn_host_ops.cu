@@ -17,8 +17,8 @@
 
 namespace {
 
-constexpr int PIPE_SLOTS = 4;
-constexpr size_t PIPE_SLOT_BYTES = 24u << 20;
+constexpr int PIPE_MAX_SLOTS = 16;
+constexpr size_t PIPE_SLOT_BYTES = 24u << 20;  // capacity of one slot
 constexpr int MAX_BUFS = 6;
 
 struct HostBuf {
@@ -32,8 +32,10 @@ struct HostBuf {
 struct agn_host_pipe {
     cudaStream_t h2d = nullptr, d2h = nullptr;
     unsigned char *stage = nullptr;
-    cudaEvent_t h2d_done[PIPE_SLOTS] = {}, k_done[PIPE_SLOTS] = {}, d2h_done[PIPE_SLOTS] = {};
-    bool slot_used[PIPE_SLOTS] = {};
+    int slots = 0;                  // slots of the ring (option "host_slots" when the ring is created)
+    uint64_t next_chunk = 0;        // chunks enqueued so far over all ops: chunk c uses slot c % slots
+    cudaEvent_t h2d_done[PIPE_MAX_SLOTS] = {}, k_done[PIPE_MAX_SLOTS] = {}, d2h_done[PIPE_MAX_SLOTS] = {};
+    bool slot_used[PIPE_MAX_SLOTS] = {};
     cudaEvent_t op_done = nullptr;  // last device->host copy of the previous host op
     bool join_pending = false;      // the context's stream has not been made to wait for op_done yet
     bool have_prev = false;
@@ -56,7 +58,7 @@ void agn_host_pipe_destroy(agn_ctx *ctx) {
     if (!p) return;
     if (p->h2d) { cudaStreamSynchronize(p->h2d); cudaStreamDestroy(p->h2d); }
     if (p->d2h) { cudaStreamSynchronize(p->d2h); cudaStreamDestroy(p->d2h); }
-    for (int s = 0; s < PIPE_SLOTS; s++) {
+    for (int s = 0; s < PIPE_MAX_SLOTS; s++) {
         if (p->h2d_done[s]) cudaEventDestroy(p->h2d_done[s]);
         if (p->k_done[s]) cudaEventDestroy(p->k_done[s]);
         if (p->d2h_done[s]) cudaEventDestroy(p->d2h_done[s]);
@@ -70,7 +72,7 @@ void agn_host_pipe_destroy(agn_ctx *ctx) {
 
 namespace {
 
-// The staging ring (96 MiB of device memory, two streams, events) is created by the first
+// The staging ring (8 slots of 24 MiB of device memory, two streams, events) is created by the first
 // host-slice call on a context, not by agn_ctx_create: device-pointer users never pay for it.
 int32_t get_pipe(agn_ctx *ctx, agn_host_pipe **out) {
     if (ctx->host_pipe) {
@@ -79,11 +81,12 @@ int32_t get_pipe(agn_ctx *ctx, agn_host_pipe **out) {
     }
     agn_host_pipe *p = new agn_host_pipe();
     ctx->host_pipe = p;
+    p->slots = ctx->tune_host_slots >= 2 && ctx->tune_host_slots <= PIPE_MAX_SLOTS ? ctx->tune_host_slots : 8;
     bool ok = cudaStreamCreateWithFlags(&p->h2d, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&p->d2h, cudaStreamNonBlocking) == cudaSuccess &&
               cudaEventCreateWithFlags(&p->op_done, cudaEventDisableTiming) == cudaSuccess &&
-              cudaMalloc(&p->stage, PIPE_SLOTS * PIPE_SLOT_BYTES) == cudaSuccess;
-    for (int s = 0; ok && s < PIPE_SLOTS; s++)
+              cudaMalloc(&p->stage, (size_t)p->slots * PIPE_SLOT_BYTES) == cudaSuccess;
+    for (int s = 0; ok && s < p->slots; s++)
         ok = cudaEventCreateWithFlags(&p->h2d_done[s], cudaEventDisableTiming) == cudaSuccess &&
              cudaEventCreateWithFlags(&p->k_done[s], cudaEventDisableTiming) == cudaSuccess &&
              cudaEventCreateWithFlags(&p->d2h_done[s], cudaEventDisableTiming) == cudaSuccess;
@@ -91,7 +94,7 @@ int32_t get_pipe(agn_ctx *ctx, agn_host_pipe **out) {
         (void)cudaGetLastError();
         agn_host_pipe_destroy(ctx);
         return agn_fail(ctx, AGN_ENOMEM, "host-slice ops: cannot create the staging ring (%zu bytes of device memory)",
-                        (size_t)PIPE_SLOTS * PIPE_SLOT_BYTES);
+                        (size_t)p->slots * PIPE_SLOT_BYTES);
     }
     *out = p;
     return AGN_OK;
@@ -167,7 +170,9 @@ int32_t run_pipelined(agn_ctx *ctx, const char *name, int64_t n_rows, const Host
     int c = 0;
     for (int64_t row0 = 0; row0 < n_rows; row0 += chunk, c++) {
         const int64_t rows = n_rows - row0 < chunk ? n_rows - row0 : chunk;
-        const int s = c % PIPE_SLOTS;
+        // the ring position runs on from op to op: the next chunk takes the slot whose previous
+        // contents are the oldest, so an upload runs ahead of the downloads by a whole ring of chunks
+        const int s = (int)(p->next_chunk++ % (uint64_t)p->slots);
         unsigned char *slot = p->stage + (size_t)s * PIPE_SLOT_BYTES;
         void *dptr[MAX_BUFS];
         size_t off = 0;

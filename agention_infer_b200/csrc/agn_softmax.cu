@@ -338,6 +338,113 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
     }
 }
 
+// Persistent form of the CTA-per-row kernel for large batches of rows of 1K-32K entries.  A softmax
+// row goes through two block-wide reductions between its loads and its stores, so a CTA that owns
+// one row has nothing in flight for most of its life; with causal rows, whose valid part is half
+// the row on average, the registers that could hold loads sit idle and the kernel is bound by
+// latency (5.0 TB/s when the tail is not written) although HBM has room.  Here a CTA loops over
+// rows blockIdx.x, blockIdx.x + gridDim.x, ... and the valid prefixes of its next rows are already
+// on their way into a ring of shared-memory slots (one bulk asynchronous copy per row, issued by
+// one thread, completing on the slot's mbarrier with a bounded wait), so loads overlap the
+// reductions and the stores of the rows before them.
+template <typename OT, int VPT>
+__global__ void __launch_bounds__(1024)
+softmax_ring_kernel(const SoftmaxArgs a, int slots, int slot_bytes, int spin_limit, uint32_t *flags) {
+    extern __shared__ __align__(128) unsigned char sm_ring[];
+    __shared__ float red[2][32];
+    uint64_t *full = reinterpret_cast<uint64_t *>(sm_ring + (size_t)slots * slot_bytes);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < slots; s++) agn_mbar_init(&full[s], 1);
+        agn_mbar_init_fence();
+    }
+    __syncthreads();
+    agn_pdl_launch_dependents();
+    agn_pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int n4 = (int)(a.row_len >> 2);
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    const int n_my = first < a.n_rows ? (int)((a.n_rows - first + stride - 1) / stride) : 0;
+    auto issue = [&](int j) {  // thread 0 only; a row without valid entries brings nothing
+        const int64_t r = first + (int64_t)j * stride;
+        const int nv = (int)valid_len(a, r);
+        if (nv <= 0) return;
+        const uint32_t bytes = (uint32_t)((nv + 3) >> 2) * 16u;
+        uint64_t *bar = &full[j % slots];
+        agn_mbar_expect_tx(bar, bytes);
+        agn_bulk_g2s(sm_ring + (size_t)(j % slots) * slot_bytes, a.in + r * a.row_stride, bytes, bar);
+    };
+    if (threadIdx.x == 0)
+        for (int j = 0; j < slots && j < n_my; j++) issue(j);
+    uint32_t phase_bits = 0;  // bit s: parity the next wait on slot s expects (flips only when a copy was issued)
+    for (int it = 0; it < n_my; it++) {
+        const int slot = it % slots;
+        const int64_t r = first + (int64_t)it * stride;
+        const int nv = (int)valid_len(a, r);
+        OT *out = static_cast<OT *>(a.out) + r * a.row_stride;
+        int failed = 0;
+        if (nv > 0) {
+            failed = !agn_mbar_wait(&full[slot], (phase_bits >> slot) & 1u, spin_limit);
+            phase_bits ^= 1u << slot;
+        }
+        const float4 *row = reinterpret_cast<const float4 *>(sm_ring + (size_t)slot * slot_bytes);
+        float4 v[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            v[k] = (4 * i < nv && !failed) ? row[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (4 * i < nv) {
+                mask_tail(v[k], i, nv);
+                m = fmaxf(m, max4(v[k]));
+            }
+        }
+        m = agn_warp_max(m);
+        if (lane == 0) red[0][warp] = m;
+        // maxima visible; every thread has read its part of the slot; one CTA-wide answer to "did
+        // any thread's wait run out", so that all threads leave together
+        if (__syncthreads_or(failed)) {
+            if (threadIdx.x == 0) {
+                atomicOr(flags, AGN_FLAG_TIMEOUT);
+                // copies still in flight target this CTA's shared memory: one more bounded wait each
+                for (int j = it; j < n_my && j < it + slots; j++) {
+                    if ((int)valid_len(a, first + (int64_t)j * stride) <= 0) continue;
+                    const uint32_t par = ((phase_bits >> (j % slots)) & 1u) ^ (j == it ? 1u : 0u);
+                    (void)agn_mbar_wait(&full[j % slots], par, spin_limit);
+                }
+            }
+            return;
+        }
+        if (threadIdx.x == 0 && it + slots < n_my) issue(it + slots);
+        m = -INFINITY;
+        for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[0][w]);
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            if (4 * (threadIdx.x + k * blockDim.x) < nv) {
+                v[k] = exp4(v[k], m, a.exp_coef);
+                sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            }
+        }
+        sum = agn_warp_sum(sum);
+        if (lane == 0) red[1][warp] = sum;
+        __syncthreads();
+        sum = 0.0f;
+        for (int w = 0; w < nwarps; w++) sum += red[1][w];
+        if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
+        const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+            else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
+        }
+    }
+}
+
 // Long rows (8K-64K entries): one thread-block CLUSTER per row.  Each of the C CTAs (256 threads,
 // 8 float4 per thread) owns 8192 consecutive entries in registers; the row maximum and the row
 // sum are combined across the cluster through distributed shared memory (each CTA publishes its
@@ -473,6 +580,31 @@ softmax_generic_rows_kernel(const SoftmaxArgs a) {
 }  // namespace
 
 namespace {
+// Persistent ring form; false = not applicable or switched off.
+template <typename OT>
+bool softmax_try_ring(agn_ctx *ctx, const SoftmaxArgs &a) {
+    if (ctx->tune_softmax_ring == 0 || a.in == static_cast<const float *>(a.out)) return false;  // (in place: a later row's copy could overtake an earlier row's stores only if rows overlapped; rows do not, but keep the simple rule)
+    const int64_t n4 = a.row_len / 4;
+    int threads = (int)((n4 + 7) / 8);
+    threads = ((threads + 31) / 32) * 32;
+    if (threads > 1024) return false;
+    const int slot_bytes = (int)((a.row_len * 4 + 127) & ~(int64_t)127);
+    int slots = ctx->tune_softmax_ring >= 2 ? ctx->tune_softmax_ring : 3;
+    while (slots > 2 && (size_t)slots * slot_bytes > 96 * 1024) slots--;
+    const size_t smem = (size_t)slots * slot_bytes + 8 * (size_t)slots;
+    if (smem > 200 * 1024) return false;
+    auto kernel = softmax_ring_kernel<OT, 8>;
+    int per_sm = agn_ring_ctas_per_sm(ctx, kernel, threads, smem);
+    if (per_sm < 1) return false;
+    if (ctx->tune_softmax_ring_ctas > 0 && ctx->tune_softmax_ring_ctas < per_sm) per_sm = ctx->tune_softmax_ring_ctas;
+    int64_t grid = (int64_t)per_sm * ctx->sm_count;
+    if (a.n_rows < 2 * grid && !ctx->tune_ring_force) return false;
+    if (grid > a.n_rows) grid = a.n_rows;
+    agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, a, slots, slot_bytes, ctx->mbar_spin_limit, ctx->d_flags);
+    ctx->flags_dirty = true;
+    return true;
+}
+
 template <typename OT>
 int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, int64_t n_rows, int64_t row_len,
                          int64_t row_stride, const int32_t *n_valid, int32_t causal_period, int32_t causal_offset,
@@ -525,17 +657,19 @@ int32_t softmax_dispatch(agn_ctx *ctx, const float *in, OT *out, float *sums, in
         else
             agn_launch_cluster(ctx, softmax_cluster_rows_kernel<OT, 16>, dim3((unsigned)(n_rows * cs)), dim3(threads), 0, cs, a, cs);
         AGN_LAUNCHED(ctx, "softmax_cluster_rows");
+    } else if (vec_ok && n4 <= 8192 && softmax_try_ring<OT>(ctx, a)) {
+        AGN_LAUNCHED(ctx, "softmax_ring");
     } else if (vec_ok && n4 <= 8192 && ctx->tune_softmax_causal_pair && !n_valid && causal_period == row_len && causal_offset == 0 &&
                n_rows % row_len == 0) {
         // square causal matrices: rows i and L-1-i share a CTA, L + 1 valid entries per CTA (nine
         // float4 per thread: eight and the one or two vectors by which the two rounded-up halves exceed a row)
-        constexpr int VPT = 9;
+        // (four float4 and a spare per thread with twice the threads measured 124 against 86 us on 28 x 2048^2)
         int threads = (int)((n4 + 7) / 8);
         threads = ((threads + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
         const int64_t heads = n_rows / row_len;
         const int64_t grid = heads * ((row_len + 1) / 2);
-        agn_launch(ctx, softmax_causal_pair_kernel<OT, VPT>, dim3((unsigned)grid), dim3(threads), 0, a);
+        agn_launch(ctx, softmax_causal_pair_kernel<OT, 9>, dim3((unsigned)grid), dim3(threads), 0, a);
         AGN_LAUNCHED(ctx, "softmax_causal_pair");
     } else if (vec_ok && n4 <= 8192) {
         // few, fat threads: 8 float4 per thread keeps the CTA at <= 256 threads up to 8192 entries

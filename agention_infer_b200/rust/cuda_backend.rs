@@ -239,6 +239,23 @@ impl CudaBackend {
         Ok(out)
     }
 
+    /// The causal prefill softmax exactly as the CPU loop leaves its buffer (cpu_path.rs:168-183 runs over
+    /// `scores[..seq_len]` only): entries past a row's valid length keep what `out` held.  `out_dtype` is
+    /// `AGN_F32`, `AGN_F16` or `AGN_BF16`.
+    pub fn launch_softmax_causal_valid(&self, scores: &DevBuf, out: &DevBuf, n_heads: usize, seq: usize, scale: f32,
+                                       out_dtype: i32) -> Result<()> {
+        self.check(unsafe {
+            agn_softmax_rows_valid_f32(self.ctx, scores.ptr as *const f32, out.ptr, std::ptr::null_mut(),
+                                       (n_heads * seq) as i64, seq as i64, seq as i64, std::ptr::null(), seq as i32, 0,
+                                       scale, out_dtype)
+        })
+    }
+
+    /// Kernel family of the most recent launch (the per-kernel name `GGUF_TRACE_KERNEL` would print).
+    pub fn last_kernel(&self) -> String {
+        unsafe { CStr::from_ptr(agn_ctx_last_kernel(self.ctx)) }.to_string_lossy().into_owned()
+    }
+
     /// Embedding rows for a batch of tokens: replaces the per-token CPU `dequant_row` + upload of
     /// `run_gpu_resident` (src/model/llama/gpu_resident.rs:436-437).  `table` holds the tensor's
     /// bytes as they are in the GGUF file, uploaded once.

@@ -610,17 +610,22 @@ def run_ours(args, cfg, ops_list, wl):
         e2e_steps = max(3, min(args.steps, 10))
         for _ in range(2):
             e2e_step()
-        barrier()
+        # the link is shared with the other tenants of the host: the K-step region is repeated and the median taken
+        e2e_regions = []
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for _ in range(e2e_steps):
-            e2e_step()
-        b.record(stream)
-        barrier()
-        e2e_ms = sharding.max_over_ranks(a.elapsed_time(b)) / e2e_steps
+        for _ in range(max(1, min(args.repeats, 5))):
+            barrier()
+            a.record(stream)
+            for _ in range(e2e_steps):
+                e2e_step()
+            b.record(stream)
+            barrier()
+            e2e_regions.append(sharding.max_over_ranks(a.elapsed_time(b)) / e2e_steps)
+        e2e_ms = float(np.median(e2e_regions))
         e2e = {"value": T_total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": e2e_ms, "steps": e2e_steps,
-               "api": "host-slice entry points (agn_host_*), pinned host arrays, 3-stream staging ring"}
+               "ms_per_step": e2e_ms, "ms_per_step_min": min(e2e_regions), "ms_per_step_max": max(e2e_regions),
+               "steps": e2e_steps, "repeats": len(e2e_regions),
+               "api": "host-slice entry points (agn_host_*), pinned host arrays, staging ring over three streams"}
 
     # ---- the two other configurations a driver run should see: the decode chain (one GPU) and the large batch
     #      split over the ranks (every N).  The headline buffers make room first.
@@ -739,6 +744,9 @@ def run_ours(args, cfg, ops_list, wl):
                          "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of measured (copy bandwidth, MEASURED_PEAKS.json)" if peak_src == "measured"
                          else "of fallback", "traffic": silu_traffic_bytes(R * I) if not f16 else None,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel at this "
+                                           "size (profiles/dram_traffic_qwen7b_prefill_rows4096.md), scaled with the element "
+                                           "count; not measured by this run",
                          "algorithmic_bytes_per_launch": ab["silu_mul"], "avg_launch_ms": silu_ms},
             "ops": per_op, "extra_ops": extra_ops, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk), "outputs_checked": outs, "identical_across_ranks": agree,

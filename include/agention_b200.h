@@ -97,11 +97,24 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
  * (every kernel still waits for the previous one to complete before its first access).
  * Tuning knobs, all with measured defaults: "rms_vpt" (1, 2, 4, 8 vectors per thread; 0 = automatic),
  * "rms_recip" (1: one reciprocal per row, 0: IEEE division per element), "silu_unroll" (2, 4, 8),
- * "silu_threads" (128, 256, 512), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more
- * than 16384 entries: 1 = one thread-block cluster per row, 2 = the same with smaller CTAs, 0 = one
- * CTA per row), "get_rows_tma" (1: bulk-copy staging, 0: cp.async), "get_rows_threads" (32..256;
- * 0 = automatic), "moe_small_sort" (1: up to 4096 (token, slot) pairs are sorted by one CTA in one
- * launch, 0: always the three-kernel counting sort).  An unknown name is AGN_EINVAL. */
+ * "silu_threads" (128, 256, 512), "silu_small" (1: decode-sized inputs run one vector pair per thread in
+ * 128-thread CTAs), "softmax_vpt" (2, 4; 0 = 8), "softmax_cluster" (rows of more than 16384 entries:
+ * 1 = one thread-block cluster per row, 2 = the same with smaller CTAs, 0 = one CTA per row),
+ * "softmax_causal_pair" (1: square causal matrices of more than 1024 columns run rows i and L-1-i in one
+ * CTA), "softmax_warp16" (1: rows of 1025-2048 entries run one warp per row; default 0), "get_rows_tma"
+ * (1: bulk-copy staging, 0: cp.async), "get_rows_threads" (32..256; 0 = automatic), "moe_small_sort"
+ * (1: up to 4096 (token, slot) pairs are sorted by one CTA in one launch, 0: always the three-kernel
+ * counting sort), "host_slots" (2..16 staging slots of the host-slice ops, read when their ring is created;
+ * 0 = 8), "host_chunk_bytes" (bytes of one staging chunk; 0 = a whole 24 MiB slot).
+ * Persistent kernels that stage rows through a shared-memory ring with bulk asynchronous copies (off by
+ * default: the CTA-per-row kernels measured faster on B200): "rms_ring", "rope_ring", "get_rows_ring",
+ * "softmax_ring" = 0 (never), 1 (a ring of the default depth for batches large enough to keep it busy) or
+ * 2..8 / 2..16 slots; "<op>_ring_ctas" = resident CTAs per SM (0 = as many as fit); "ring_force" = 1 takes the
+ * persistent form however small the batch (tests).
+ * "mbar_spin_limit" (default 4194304): polls of a staging barrier before a kernel gives up and the next
+ * agn_sync returns AGN_ETIMEOUT; "test_idle_barrier_wait" = 1 is a test hook that makes get_rows wait on a
+ * barrier nothing signals, so that this path can be exercised without a fault.
+ * An unknown name or a value outside the option's range is AGN_EINVAL. */
 AGN_API int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value);
 /* Launches one empty kernel: the per-launch floor for launch-bound (decode-shaped) timings,
  * the counterpart of the reference's "dispatch floor" probe

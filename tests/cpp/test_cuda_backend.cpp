@@ -174,6 +174,29 @@ int main() {
         for (int i = 0; i < 8; i++) same = same && rows[i] == w[16 + i] && rows[8 + i] == w[i];
         expect(same, "GgufFile parse + upload + get_rows");
     }
+    {  // softmax that writes the valid entries only: the tail keeps the sentinel, the valid part matches the oracle
+        const int R = 5, L = 516;
+        std::vector<float> sc(R * L), ref(R * L, 0.f), sentinel(R * L, -7.25f);
+        for (auto &v : sc) v = 2.f * N01(rng);
+        std::vector<int32_t> nv = {L, 1, 300, 0, 515};
+        orc_softmax_rows(sc.data(), ref.data(), R, L, L, nv.data(), 1);
+        auto ds = be.upload(sc);
+        auto dn = be.upload(nv);
+        auto dout = be.upload(sentinel);
+        be.launch_softmax_rows_valid(ds.as<float>(), dout.ptr(), nullptr, R, L, L, dn.as<int32_t>(), 0, 0, 1.0f, AGN_F32);
+        auto got = be.read<float>(dout, R * L);
+        double worst = 0;
+        bool tail_kept = true;
+        for (int r = 0; r < R; r++) {
+            float scale = 1e-30f;
+            for (int i = 0; i < nv[r]; i++) scale = std::fmax(scale, std::fabs(ref[r * L + i]));
+            for (int i = 0; i < L; i++) {
+                if (i < nv[r]) worst = std::fmax(worst, std::fabs((double)got[r * L + i] - ref[r * L + i]) / scale);
+                else tail_kept = tail_kept && got[r * L + i] == -7.25f;
+            }
+        }
+        expect(worst <= 1e-5 && tail_kept && !be.last_kernel().empty(), "softmax_rows_valid", worst);
+    }
     {  // error behaviour: bad argument -> status + message, context still usable
         bool threw = false;
         auto d = be.empty(512);

@@ -32,10 +32,11 @@ def bits(a):
 @pytest.fixture()
 def ring(backend):
     """Backend with the persistent kernels forced on; options restored afterwards."""
-    for name in ("ring_force", "rms_ring", "rope_ring", "get_rows_ring"):
+    for name in ("ring_force", "rms_ring", "rope_ring", "get_rows_ring", "softmax_ring"):
         backend.set_option(name, 1)
     yield backend
-    for name in ("ring_force", "rms_ring", "rms_ring_ctas", "rope_ring", "rope_ring_ctas", "get_rows_ring", "get_rows_ring_ctas"):
+    for name in ("ring_force", "rms_ring", "rms_ring_ctas", "rope_ring", "rope_ring_ctas", "get_rows_ring", "get_rows_ring_ctas",
+                 "softmax_ring", "softmax_ring_ctas"):
         backend.set_option(name, 0)
 
 
@@ -216,3 +217,49 @@ def test_get_rows_natural_ring_size(backend):
     finally:
         backend.set_option("get_rows_ring", 0)
     assert np.array_equal(bits(backend.read(out, np.float32, (T, H))), bits(ref))
+
+
+@pytest.mark.parametrize("slots,ctas", [(1, 0), (2, 1), (6, 2)])
+@pytest.mark.parametrize("R,L", [(300, 2048), (77, 1028), (9, 8192), (5, 16384), (1, 4096)])
+def test_softmax_ring_ragged_rows(ring, R, L, slots, ctas):
+    """Rows of 1K-32K entries with ragged valid lengths (full, one entry, none, everything in between): the
+    persistent kernel against the oracle, and bit for bit against the CTA-per-row kernel (same thread
+    mapping, same reduction order).  Zero-filled and valid-only forms, f32 and bf16 rows, sums."""
+    ring.set_option("softmax_ring", slots); ring.set_option("softmax_ring_ctas", ctas)
+    s = synth.activations(5, "logits", (R, L), std=2.0)
+    nv = synth.rng_for(5, "pos").integers(0, L + 1, size=R, dtype=np.int32)
+    nv[:3] = [L, 1, 0][:min(3, R)]
+    ref = orc.softmax_rows(s, nv, THREADS)
+    ds, dnv = ring.upload(s), ring.upload(nv)
+    got = ring.read(ring.launch_softmax_rows(ds, R, L, n_valid=dnv), np.float32, (R, L))
+    assert ring.last_kernel == "softmax_ring"
+    drift = 0.0
+    assert rel(got, ref) <= TOL + drift
+    valid = np.arange(L)[None, :] < nv[:, None]
+    assert not got[~valid].any()
+    sentinel = ring.upload(np.full((R, L), -7.25, np.float32))
+    ring.launch_softmax_rows_valid(ds, R, L, sentinel, n_valid=dnv)
+    assert ring.last_kernel == "softmax_ring"
+    g2 = ring.read(sentinel, np.float32, (R, L))
+    assert np.array_equal(bits(g2[valid]), bits(got[valid])) and np.all(g2[~valid] == -7.25)
+    sums = ring.empty(4 * R)
+    w16 = ring.read(ring.launch_softmax_rows_scaled_out16(ds, R, L, 0.5, AGN_BF16, sums=sums, n_valid=dnv), np.uint16, (R, L))
+    sm = ring.read(sums, np.float32, (R,))
+    ring.set_option("softmax_ring", 0)
+    old = ring.read(ring.launch_softmax_rows(ds, R, L, n_valid=dnv), np.float32, (R, L))
+    assert not ring.last_kernel.endswith("_ring")
+    assert np.array_equal(bits(got), bits(old))
+    sums2 = ring.empty(4 * R)
+    w16_old = ring.read(ring.launch_softmax_rows_scaled_out16(ds, R, L, 0.5, AGN_BF16, sums=sums2, n_valid=dnv), np.uint16, (R, L))
+    assert np.array_equal(w16, w16_old) and np.array_equal(bits(sm), bits(ring.read(sums2, np.float32, (R,))))
+
+
+def test_softmax_ring_square_causal(ring):
+    heads, L = 3, 2048
+    s = synth.causal_scores(1, heads, L)
+    nv = np.tile(np.arange(1, L + 1, dtype=np.int32), heads)
+    ref = orc.softmax_rows(s, nv, THREADS)
+    got = ring.read(ring.launch_softmax_rows(ring.upload(s), heads * L, L, causal_period=L), np.float32, s.shape)
+    assert ring.last_kernel == "softmax_ring"
+    assert rel(got, ref) <= TOL
+    assert not got[:, np.triu(np.ones((L, L), dtype=bool), k=1)].any()
