@@ -32,7 +32,7 @@ struct agn_rope_slot {
     uint32_t theta_bits;
     int32_t n_rot;
     bool used;
-    bool in_graph;  // handed out while a graph capture was open: a recorded graph points at it, never evicted
+    int graph_refs;  // recorded graphs that point at this table (counted at agn_graph_end, released at agn_graph_destroy): never evicted while > 0
 };
 
 struct agn_ctx {
@@ -50,6 +50,7 @@ struct agn_ctx {
     bool pdl;                   // launch kernels with programmatic stream serialization
     bool capturing;             // between agn_graph_begin and agn_graph_end
     uint64_t capture_launches0;
+    uint32_t capture_rope_slots; // bit s: the open capture recorded a kernel that reads rope table slot s
     int tune_rms_vpt;           // 0 = automatic; 1/2/4/8 float4 per thread in rms_norm
     int tune_rms_recip;         // rms_norm multiplies by 1/rms instead of dividing each element (default 1)
     int tune_get_rows_threads;  // 0 = automatic

@@ -61,6 +61,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->pdl = true;
     ctx->capturing = false;
     ctx->capture_launches0 = 0;
+    ctx->capture_rope_slots = 0;
     ctx->tune_rms_vpt = 0;
     ctx->tune_rms_recip = 1;
     ctx->tune_get_rows_threads = 0;
@@ -412,6 +413,7 @@ struct agn_graph {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     uint64_t kernels = 0;  // kernels recorded, added to the launch count at every replay
+    uint32_t rope_slots = 0;  // rope table slots its kernels read: kept out of eviction until the graph is destroyed
 };
 
 // Records every op enqueued on the context's stream between begin and end into a CUDA graph
@@ -426,6 +428,7 @@ extern "C" int32_t agn_graph_begin(agn_ctx *ctx) {
     AGN_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     ctx->capturing = true;
     ctx->capture_launches0 = ctx->launches;
+    ctx->capture_rope_slots = 0;
     return AGN_OK;
 }
 
@@ -445,6 +448,9 @@ extern "C" int32_t agn_graph_end(agn_ctx *ctx, agn_graph **out) {
         return agn_fail(ctx, AGN_ECUDA, "agn_graph_end: %s", cudaGetErrorString(e));
     }
     g->kernels = ctx->launches - ctx->capture_launches0;
+    g->rope_slots = ctx->capture_rope_slots;
+    for (int sl = 0; sl < AGN_ROPE_CACHE_SLOTS; sl++)
+        if (g->rope_slots & (1u << sl)) ctx->rope_slots[sl].graph_refs++;
     ctx->launches = ctx->capture_launches0;  // nothing ran yet
     *out = g;
     return AGN_OK;
@@ -462,6 +468,8 @@ extern "C" int32_t agn_graph_launch(agn_ctx *ctx, agn_graph *g) {
 extern "C" int32_t agn_graph_destroy(agn_ctx *ctx, agn_graph *g) {
     AGN_CHECK_CTX(ctx);
     if (!g) return AGN_OK;
+    for (int sl = 0; sl < AGN_ROPE_CACHE_SLOTS; sl++)
+        if ((g->rope_slots & (1u << sl)) && ctx->rope_slots[sl].graph_refs > 0) ctx->rope_slots[sl].graph_refs--;
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
     delete g;
@@ -494,7 +502,7 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
     for (int s = 0; s < AGN_ROPE_CACHE_SLOTS; s++) {
         const agn_rope_slot &sl = ctx->rope_slots[s];
         if (sl.used && sl.theta_bits == bits && sl.n_rot == n_rot) {
-            if (ctx->capturing) ctx->rope_slots[s].in_graph = true;
+            if (ctx->capturing) ctx->capture_rope_slots |= 1u << s;
             *d_table = ctx->d_rope_denom + (size_t)s * AGN_ROPE_MAX_HALF;
             return AGN_OK;
         }
@@ -508,7 +516,7 @@ int32_t agn_rope_table(agn_ctx *ctx, float theta, int32_t n_rot, const float **d
     int s = -1;
     for (int k = 0; k < AGN_ROPE_CACHE_SLOTS; k++) {
         const int c = (ctx->rope_next + k) % AGN_ROPE_CACHE_SLOTS;
-        if (!ctx->rope_slots[c].in_graph) { s = c; break; }
+        if (ctx->rope_slots[c].graph_refs == 0) { s = c; break; }
     }
     if (s < 0)
         return agn_fail(ctx, AGN_EINVAL, "rope: all %d (theta, n_rot) table slots are in use by recorded graphs", AGN_ROPE_CACHE_SLOTS);

@@ -28,6 +28,19 @@ __device__ __forceinline__ uint32_t ld_u32_2(const uint8_t *p) {  // 4 bytes fro
     return (uint32_t)ld_u16(p) | ((uint32_t)ld_u16(p + 2) << 16);
 }
 
+// Four small unsigned integers (one per byte of x, each < 256) minus `bias` as floats without a
+// conversion instruction (I2F issues at a quarter of the rate of an FADD): byte k is placed into the
+// mantissa of 2^23 (0x4B000000) by one byte permute, and (2^23 + n) - (2^23 + bias) = n - bias
+// exactly, because every operand and the result are integers below 2^24.
+__device__ __forceinline__ float4 bytes_minus_bias_to_float4(uint32_t x, float two23_plus_bias) {
+    float4 f;
+    f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - two23_plus_bias;
+    f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - two23_plus_bias;
+    f.z = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - two23_plus_bias;
+    f.w = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - two23_plus_bias;
+    return f;
+}
+
 // Four consecutive outputs starting at element e0 (a multiple of 4) of a staged row (the
 // formats whose blocks decode in element order; the K-quants have decode8 below).
 template <int DTYPE>
@@ -38,12 +51,9 @@ __device__ __forceinline__ float4 decode4<AGN_Q8_0>(const uint8_t *row, int e0) 
     const uint8_t *blk = row + (e0 >> 5) * 34;
     const float d = f16_bits_to_f32(ld_u16(blk));
     const uint32_t q = ld_u32_2(blk + 2 + (e0 & 31));
-    float4 o;
-    o.x = __fmul_rn(d, (float)(int8_t)(q & 0xff));
-    o.y = __fmul_rn(d, (float)(int8_t)((q >> 8) & 0xff));
-    o.z = __fmul_rn(d, (float)(int8_t)((q >> 16) & 0xff));
-    o.w = __fmul_rn(d, (float)(int8_t)(q >> 24));
-    return o;
+    // int8 -> float: flip the sign bit (the byte becomes value + 128 in 0..255), then subtract 2^23 + 128
+    const float4 f = bytes_minus_bias_to_float4(q ^ 0x80808080u, 8388736.0f);
+    return make_float4(__fmul_rn(d, f.x), __fmul_rn(d, f.y), __fmul_rn(d, f.z), __fmul_rn(d, f.w));
 }
 
 template <>
@@ -132,17 +142,7 @@ __device__ __forceinline__ void decode8<AGN_Q4_K>(const uint8_t *row, int u, int
     vb.w = __fsub_rn(__fmul_rn(d2, (float)(q >> 28)), mm2);
 }
 
-// Four small unsigned integers (one per byte of x, each < 256) as floats without a conversion
-// instruction: byte k is placed into the mantissa of 2^23 (0x4B000000) by one byte permute,
-// and 2^23 + n - 2^23 = n exactly.
-__device__ __forceinline__ float4 bytes_to_float4(uint32_t x) {
-    float4 f;
-    f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - 8388608.0f;
-    f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - 8388608.0f;
-    f.z = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - 8388608.0f;
-    f.w = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - 8388608.0f;
-    return f;
-}
+__device__ __forceinline__ float4 bytes_to_float4(uint32_t x) { return bytes_minus_bias_to_float4(x, 8388608.0f); }
 __device__ __forceinline__ float4 scale_sub4(float4 q, float d, float m) {  // d * q - m, two roundings each
     return make_float4(__fsub_rn(__fmul_rn(d, q.x), m), __fsub_rn(__fmul_rn(d, q.y), m), __fsub_rn(__fmul_rn(d, q.z), m),
                        __fsub_rn(__fmul_rn(d, q.w), m));
@@ -201,14 +201,9 @@ __device__ __forceinline__ void decode8<AGN_Q5_K>(const uint8_t *row, int u, int
     const float d2 = __fmul_rn(d, (float)s1), mm2 = __fmul_rn(dmin, (float)m1);
     const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 16 + l) >> (2 * g);  // bit 0: low run, bit 1: high run
     const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 48 + 32 * g + l);
-    va.x = __fsub_rn(__fmul_rn(d1, (float)((q & 0xF) + ((qh & 1) << 4))), mm1);
-    va.y = __fsub_rn(__fmul_rn(d1, (float)(((q >> 8) & 0xF) + (((qh >> 8) & 1) << 4))), mm1);
-    va.z = __fsub_rn(__fmul_rn(d1, (float)(((q >> 16) & 0xF) + (((qh >> 16) & 1) << 4))), mm1);
-    va.w = __fsub_rn(__fmul_rn(d1, (float)(((q >> 24) & 0xF) + (((qh >> 24) & 1) << 4))), mm1);
-    vb.x = __fsub_rn(__fmul_rn(d2, (float)(((q >> 4) & 0xF) + (((qh >> 1) & 1) << 4))), mm2);
-    vb.y = __fsub_rn(__fmul_rn(d2, (float)(((q >> 12) & 0xF) + (((qh >> 9) & 1) << 4))), mm2);
-    vb.z = __fsub_rn(__fmul_rn(d2, (float)(((q >> 20) & 0xF) + (((qh >> 17) & 1) << 4))), mm2);
-    vb.w = __fsub_rn(__fmul_rn(d2, (float)((q >> 28) + (((qh >> 25) & 1) << 4))), mm2);
+    // four 5-bit values per word, a byte each: nibble plus the high bit (bit 0 of the qh byte for the low run, bit 1 for the high run)
+    va = scale_sub4(bytes_to_float4((q & 0x0F0F0F0Fu) | ((qh & 0x01010101u) << 4)), d1, mm1);
+    vb = scale_sub4(bytes_to_float4(((q >> 4) & 0x0F0F0F0Fu) | (((qh >> 1) & 0x01010101u) << 4)), d2, mm2);
 }
 
 template <>
@@ -228,14 +223,8 @@ __device__ __forceinline__ void decode8<AGN_Q2_K>(const uint8_t *row, int u, int
     const float d1 = __fmul_rn(d, (float)(sa & 0xF)), mm1 = __fmul_rn(dmin, (float)(sa >> 4));
     const float d2 = __fmul_rn(d, (float)(sb & 0xF)), mm2 = __fmul_rn(dmin, (float)(sb >> 4));
     const uint32_t q = *reinterpret_cast<const uint32_t *>(blk + 16 + 32 * g + l) >> (4 * jp);
-    va.x = __fsub_rn(__fmul_rn(d1, (float)(q & 3)), mm1);
-    va.y = __fsub_rn(__fmul_rn(d1, (float)((q >> 8) & 3)), mm1);
-    va.z = __fsub_rn(__fmul_rn(d1, (float)((q >> 16) & 3)), mm1);
-    va.w = __fsub_rn(__fmul_rn(d1, (float)((q >> 24) & 3)), mm1);
-    vb.x = __fsub_rn(__fmul_rn(d2, (float)((q >> 2) & 3)), mm2);
-    vb.y = __fsub_rn(__fmul_rn(d2, (float)((q >> 10) & 3)), mm2);
-    vb.z = __fsub_rn(__fmul_rn(d2, (float)((q >> 18) & 3)), mm2);
-    vb.w = __fsub_rn(__fmul_rn(d2, (float)((q >> 26) & 3)), mm2);
+    va = scale_sub4(bytes_to_float4(q & 0x03030303u), d1, mm1);
+    vb = scale_sub4(bytes_to_float4((q >> 2) & 0x03030303u), d2, mm2);
 }
 
 template <>
@@ -249,14 +238,12 @@ __device__ __forceinline__ void decode8<AGN_Q6_K>(const uint8_t *row, int u, int
     const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * h + (l >> 4) + 2 * cp);
     const float d = f16_bits_to_f32(ld_u16(blk + 208));
     const float da = __fmul_rn(d, (float)sc[0]), db = __fmul_rn(d, (float)sc[4]);
-    va.x = __fmul_rn(da, (float)((int)((ql & 0xF) | ((qh & 3) << 4)) - 32));
-    va.y = __fmul_rn(da, (float)((int)(((ql >> 8) & 0xF) | (((qh >> 8) & 3) << 4)) - 32));
-    va.z = __fmul_rn(da, (float)((int)(((ql >> 16) & 0xF) | (((qh >> 16) & 3) << 4)) - 32));
-    va.w = __fmul_rn(da, (float)((int)(((ql >> 24) & 0xF) | (((qh >> 24) & 3) << 4)) - 32));
-    vb.x = __fmul_rn(db, (float)((int)(((ql >> 4) & 0xF) | (((qh >> 4) & 3) << 4)) - 32));
-    vb.y = __fmul_rn(db, (float)((int)(((ql >> 12) & 0xF) | (((qh >> 12) & 3) << 4)) - 32));
-    vb.z = __fmul_rn(db, (float)((int)(((ql >> 20) & 0xF) | (((qh >> 20) & 3) << 4)) - 32));
-    vb.w = __fmul_rn(db, (float)((int)((ql >> 28) | (((qh >> 28) & 3) << 4)) - 32));
+    // four 6-bit values per word, a byte each: low (high) nibbles of ql with bits 0-1 (4-5) of the qh bytes on top;
+    // value - 32 comes out of the byte-to-float step (2^23 + 32 is subtracted)
+    const float4 fa = bytes_minus_bias_to_float4((ql & 0x0F0F0F0Fu) | ((qh & 0x03030303u) << 4), 8388640.0f);
+    const float4 fb = bytes_minus_bias_to_float4(((ql >> 4) & 0x0F0F0F0Fu) | (((qh >> 4) & 0x03030303u) << 4), 8388640.0f);
+    va = make_float4(__fmul_rn(da, fa.x), __fmul_rn(da, fa.y), __fmul_rn(da, fa.z), __fmul_rn(da, fa.w));
+    vb = make_float4(__fmul_rn(db, fb.x), __fmul_rn(db, fb.y), __fmul_rn(db, fb.z), __fmul_rn(db, fb.w));
 }
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {

@@ -169,3 +169,69 @@ def test_router_and_gather_stay_inside(backend, T, H, E):
     ref_out, ref_off, ref_tok, _ = orc.gather_rows_by_expert(x, ref_idx, E)
     assert np.array_equal(off.get(np.int32, (E + 1,)), ref_off) and np.array_equal(tok.get(np.int32, (2 * T,)), ref_tok)
     assert np.array_equal(out.get(np.float32, (2 * T, H)).view(np.uint32), ref_out.view(np.uint32))
+
+
+@pytest.mark.parametrize("heads,L", [(1, 1028), (2, 2048)])
+def test_softmax_square_causal_forms_stay_inside(backend, heads, L):
+    """The row-pair kernel of square causal matrices, zero-filled, valid entries only and with 16-bit rows."""
+    s = synth.causal_scores(1, heads, L)
+    nv = np.tile(np.arange(1, L + 1, dtype=np.int32), heads)
+    ref = orc.softmax_rows(s, nv, max(1, orc.max_threads()))
+    gs = guarded_like(backend, s)
+    out, val, o16 = Guarded(backend, s.nbytes), Guarded(backend, s.nbytes).put(np.zeros_like(s)), Guarded(backend, s.nbytes // 2)
+    backend.launch_softmax_rows(gs.ptr, heads * L, L, out=out.ptr, causal_period=L)
+    assert backend.last_kernel == "softmax_causal_pair"
+    backend.launch_softmax_rows_valid(gs.ptr, heads * L, L, val.ptr, causal_period=L)
+    backend.launch_softmax_rows_scaled_out16(gs.ptr, heads * L, L, 1.0, AGN_BF16, out=o16.ptr, causal_period=L)
+    for g, name in ((out, "probs"), (val, "valid-only probs"), (o16, "bf16 probs"), (gs, "scores")):
+        g.check(name)
+    assert synth.max_rel_to_row_scale(out.get(np.float32, s.shape), ref) <= 1e-5
+    assert synth.max_rel_to_row_scale(val.get(np.float32, s.shape), ref) <= 1e-5
+
+
+def test_persistent_ring_kernels_stay_inside(backend):
+    """The opt-in persistent kernels (rows staged through shared memory by bulk copies): every buffer between guard
+    bands, row counts that leave a partial last round and lengths that are not multiples of the copy granularity."""
+    opts = ("ring_force", "rms_ring", "rope_ring", "get_rows_ring", "softmax_ring")
+    for o in opts:
+        backend.set_option(o, 1)
+    try:
+        T, H = 301, 1000
+        x, d, w = synth.activations(2, "x", (T, H)), synth.activations(2, "delta", (T, H)), synth.norm_weight(2, "w", H)
+        gx, gd, gw = guarded_like(backend, x), guarded_like(backend, d), guarded_like(backend, w)
+        out, nx, nm = Guarded(backend, x.nbytes), Guarded(backend, x.nbytes), Guarded(backend, x.nbytes)
+        backend.launch_rms_norm(gx.ptr, gw.ptr, T, H, 1e-6, out=out.ptr)
+        assert backend.last_kernel == "rms_norm_ring"
+        backend.launch_add_residual_rms_norm(gx.ptr, gd.ptr, gw.ptr, T, H, 1e-6, new_x=nx.ptr, normed=nm.ptr)
+        for g, name in ((out, "rms_norm"), (nx, "new_x"), (nm, "normed"), (gx, "x"), (gd, "delta")):
+            g.check("ring " + name)
+        assert synth.max_rel_to_row_scale(out.get(np.float32, x.shape), orc.rms_norm_rows(x, w, 1e-6)) <= 1e-5
+        nq, nkv, hd = 5, 3, 64
+        q, k = synth.activations(3, "q", (T, nq * hd)), synth.activations(3, "k", (T, nkv * hd))
+        pos = synth.positions(3, T, True)
+        gq, gk, gp = guarded_like(backend, q), guarded_like(backend, k), guarded_like(backend, pos)
+        backend.launch_rope_qk(gq.ptr, gk.ptr, T, nq, nkv, hd, hd, gp.ptr, 1e4)
+        assert backend.last_kernel == "rope_ring"
+        gq.check("ring rope q"); gk.check("ring rope k")
+        assert synth.max_rel_to_row_scale(gq.get(np.float32, q.shape), orc.rope_rows(q, nq, hd, hd, pos, 1e4)) <= 1e-5
+        vocab, Hq = 77, 96
+        table = synth.quant_table(AGN_Q8_0, vocab, Hq)
+        ids = synth.token_ids(2, T, vocab); ids[::5] = vocab - 1
+        gt, gi = guarded_like(backend, table), guarded_like(backend, ids)
+        emb = Guarded(backend, 4 * T * Hq)
+        backend.get_rows(AGN_Q8_0, gt.ptr, table.nbytes, vocab, Hq, gi.ptr, T, out=emb.ptr)
+        assert backend.last_kernel == "get_rows_ring"
+        emb.check("ring get_rows")
+        _, ref = orc.get_rows(AGN_Q8_0, table, vocab, Hq, ids)
+        assert np.array_equal(emb.get(np.float32, (T, Hq)).view(np.uint32), ref.view(np.uint32))
+        R, L = 37, 1100
+        s = synth.activations(5, "logits", (R, L), std=2.0)
+        nv = synth.rng_for(5, "pos").integers(0, L + 1, size=R, dtype=np.int32)
+        gs, gn, pr = guarded_like(backend, s), guarded_like(backend, nv), Guarded(backend, s.nbytes)
+        backend.launch_softmax_rows(gs.ptr, R, L, out=pr.ptr, n_valid=gn.ptr)
+        assert backend.last_kernel == "softmax_ring"
+        pr.check("ring softmax")
+        assert synth.max_rel_to_row_scale(pr.get(np.float32, s.shape), orc.softmax_rows(s, nv)) <= 1e-5
+    finally:
+        for o in opts:
+            backend.set_option(o, 0)
