@@ -322,6 +322,21 @@ template <> struct ActVec<__nv_bfloat16> {
     static __device__ __forceinline__ void store1(__nv_bfloat16 *p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 };
 
+// Packed f32x2 arithmetic (Blackwell: add / mul / fma .rn.f32x2, two IEEE round-to-nearest results
+// per instruction, each the same bits as the scalar operation).  The row-wise kernels spend a
+// third to a half of their instructions on element-wise float arithmetic; issuing it two at a
+// time keeps them bound by memory rather than by instruction issue when the SM clock is low.
+__device__ __forceinline__ float4 agn_mul4(float4 a, float4 b) {
+    const float2 lo = __fmul2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y));
+    const float2 hi = __fmul2_rn(make_float2(a.z, a.w), make_float2(b.z, b.w));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float4 agn_scale4(float4 a, float f) { return agn_mul4(a, make_float4(f, f, f, f)); }
+// acc + (x^2, y^2) + (z^2, w^2) as two packed fused multiply-adds; acc holds two partial sums
+__device__ __forceinline__ float2 agn_sum_sq4(float4 v, float2 acc) {
+    return __ffma2_rn(make_float2(v.z, v.w), make_float2(v.z, v.w), __ffma2_rn(make_float2(v.x, v.y), make_float2(v.x, v.y), acc));
+}
+
 // Streaming (read-once / write-once) 128-bit accesses: keep them from displacing
 // reusable lines (weights, tables) in L1/L2.
 __device__ __forceinline__ float4 agn_ld_stream(const float4 *p) { return __ldcs(p); }

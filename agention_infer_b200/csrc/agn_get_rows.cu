@@ -32,13 +32,23 @@ __device__ __forceinline__ uint32_t ld_u32_2(const uint8_t *p) {  // 4 bytes fro
 // conversion instruction (I2F issues at a quarter of the rate of an FADD): byte k is placed into the
 // mantissa of 2^23 (0x4B000000) by one byte permute, and (2^23 + n) - (2^23 + bias) = n - bias
 // exactly, because every operand and the result are integers below 2^24.
+// The arithmetic of the codecs runs on Blackwell's packed f32x2 instructions (add.rn.f32x2 /
+// mul.rn.f32x2: two IEEE round-to-nearest results per instruction, bit-identical to the scalar
+// operations), which halves the floating-point instructions of kernels that are bound by
+// instruction issue rather than by HBM.
 __device__ __forceinline__ float4 bytes_minus_bias_to_float4(uint32_t x, float two23_plus_bias) {
-    float4 f;
-    f.x = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - two23_plus_bias;
-    f.y = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - two23_plus_bias;
-    f.z = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - two23_plus_bias;
-    f.w = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - two23_plus_bias;
-    return f;
+    const float2 nb = make_float2(-two23_plus_bias, -two23_plus_bias);
+    const float2 lo = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)),
+                                             __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541))), nb);
+    const float2 hi = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)),
+                                             __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543))), nb);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+// d * q, one rounding each
+__device__ __forceinline__ float4 scale4(float4 q, float d) {
+    const float2 dd = make_float2(d, d);
+    const float2 lo = __fmul2_rn(make_float2(q.x, q.y), dd), hi = __fmul2_rn(make_float2(q.z, q.w), dd);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // Four consecutive outputs starting at element e0 (a multiple of 4) of a staged row (the
@@ -52,8 +62,7 @@ __device__ __forceinline__ float4 decode4<AGN_Q8_0>(const uint8_t *row, int e0) 
     const float d = f16_bits_to_f32(ld_u16(blk));
     const uint32_t q = ld_u32_2(blk + 2 + (e0 & 31));
     // int8 -> float: flip the sign bit (the byte becomes value + 128 in 0..255), then subtract 2^23 + 128
-    const float4 f = bytes_minus_bias_to_float4(q ^ 0x80808080u, 8388736.0f);
-    return make_float4(__fmul_rn(d, f.x), __fmul_rn(d, f.y), __fmul_rn(d, f.z), __fmul_rn(d, f.w));
+    return scale4(bytes_minus_bias_to_float4(q ^ 0x80808080u, 8388736.0f), d);
 }
 
 template <>
@@ -143,9 +152,11 @@ __device__ __forceinline__ void decode8<AGN_Q4_K>(const uint8_t *row, int u, int
 }
 
 __device__ __forceinline__ float4 bytes_to_float4(uint32_t x) { return bytes_minus_bias_to_float4(x, 8388608.0f); }
-__device__ __forceinline__ float4 scale_sub4(float4 q, float d, float m) {  // d * q - m, two roundings each
-    return make_float4(__fsub_rn(__fmul_rn(d, q.x), m), __fsub_rn(__fmul_rn(d, q.y), m), __fsub_rn(__fmul_rn(d, q.z), m),
-                       __fsub_rn(__fmul_rn(d, q.w), m));
+__device__ __forceinline__ float4 scale_sub4(float4 q, float d, float m) {  // d * q - m, two roundings each (x - m is x + (-m))
+    const float2 dd = make_float2(d, d), nm = make_float2(-m, -m);
+    const float2 lo = __fadd2_rn(__fmul2_rn(make_float2(q.x, q.y), dd), nm);
+    const float2 hi = __fadd2_rn(__fmul2_rn(make_float2(q.z, q.w), dd), nm);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // Q4_K, sixteen outputs per call: two 4-byte words of one 64-value group, 16 bytes apart, give
@@ -242,8 +253,8 @@ __device__ __forceinline__ void decode8<AGN_Q6_K>(const uint8_t *row, int u, int
     // value - 32 comes out of the byte-to-float step (2^23 + 32 is subtracted)
     const float4 fa = bytes_minus_bias_to_float4((ql & 0x0F0F0F0Fu) | ((qh & 0x03030303u) << 4), 8388640.0f);
     const float4 fb = bytes_minus_bias_to_float4(((ql >> 4) & 0x0F0F0F0Fu) | (((qh >> 4) & 0x03030303u) << 4), 8388640.0f);
-    va = make_float4(__fmul_rn(da, fa.x), __fmul_rn(da, fa.y), __fmul_rn(da, fa.z), __fmul_rn(da, fa.w));
-    vb = make_float4(__fmul_rn(db, fb.x), __fmul_rn(db, fb.y), __fmul_rn(db, fb.z), __fmul_rn(db, fb.w));
+    va = scale4(fa, da);
+    vb = scale4(fb, db);
 }
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {

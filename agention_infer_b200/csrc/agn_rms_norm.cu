@@ -35,12 +35,24 @@ __device__ __forceinline__ float block_sum(float v, float *smem) {
     return total;
 }
 
+// (The sum of squares runs on fused multiply-adds, two per instruction (agn_sum_sq4): one rounding
+// each; the reference's separate multiply and add differ from it by less than the reordering of
+// the sum already does.)
+
+// 1 / sqrt(ss / n + eps), the factor every element of the row is multiplied by.  Evaluated as
+// rsqrt(ss * (1/n) + eps) with the hardware reciprocal square root (2 ulp): three instructions
+// instead of the ~45 of two IEEE divisions and a square root, which every thread of the CTA would
+// run while the row's stores wait.  Together with the multiplication by 1/n this moves a result
+// by a few 1e-7 relative, inside the 1e-5 tolerance; infinities, zeros and NaN come out as they
+// do from the exact sequence (rsqrt(inf) = 0, rsqrt(0) = inf).
+__device__ __forceinline__ float inv_rms(float ss, float inv_n, float eps) { return rsqrtf(__fmaf_rn(ss, inv_n, eps)); }
+
 // T: storage type of x, delta and new_x; OT: storage type of the normed output (T, or a 16-bit
 // type for a row that feeds a matmul with half-precision operands).
 template <typename T, typename OT, int VPT, bool RESIDUAL, bool RECIP>
 __global__ void __launch_bounds__(1024)
 rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float4 *__restrict__ w,
-                     T *__restrict__ new_x, OT *__restrict__ out, int n4, float n_f, float eps) {
+                     T *__restrict__ new_x, OT *__restrict__ out, int n4, float n_f, float inv_n, float eps) {
     agn_pdl_prologue();
     __shared__ float red[32];
     const int64_t row = (int64_t)blockIdx.x * n4;  // in vectors of four activations
@@ -68,12 +80,12 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
             }
         }
     }
-    float ss = 0.0f;
+    float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-    for (int k = 0; k < VPT; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
-    ss = block_sum(ss, red);
-    const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps
-    const float inv = 1.0f / rms;
+    for (int k = 0; k < VPT; k++) ss2 = agn_sum_sq4(v[k], ss2);
+    float ss = block_sum(ss2.x + ss2.y, red);
+    const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps (used by the dividing arm)
+    const float inv = inv_rms(ss, inv_n, eps);
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
@@ -81,10 +93,7 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
             const float4 ww = __ldg(w + i);
             float4 o;
             if (RECIP) {
-                o.x = ww.x * v[k].x * inv;
-                o.y = ww.y * v[k].y * inv;
-                o.z = ww.z * v[k].z * inv;
-                o.w = ww.w * v[k].w * inv;
+                o = agn_scale4(agn_mul4(ww, v[k]), inv);  // (w * x) * inv, two roundings, as the scalar form
             } else {
                 o.x = ww.x * v[k].x / rms;
                 o.y = ww.y * v[k].y / rms;
@@ -102,7 +111,7 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
 template <typename T, typename OT, int VPT, bool RESIDUAL>
 __global__ void __launch_bounds__(1024)
 rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float4 *__restrict__ w,
-                     T *__restrict__ new_x, OT *__restrict__ out, int64_t T_rows, int n4, float n_f, float eps, int slots,
+                     T *__restrict__ new_x, OT *__restrict__ out, int64_t T_rows, int n4, float inv_n, float eps, int slots,
                      int spin_limit, uint32_t *flags) {
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ float red[2][32];
@@ -167,7 +176,7 @@ rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
                 }
             }
         }
-        float ss = 0.0f;
+        float2 ss2 = make_float2(0.0f, 0.0f);
         if (RESIDUAL && sizeof(T) == 2) {
             // the f16 residual form normalises the STORED new_x (see rms_norm_rows_kernel)
 #pragma unroll
@@ -175,13 +184,13 @@ rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
                 float4 r;
                 r.x = __half2float(__float2half_rn(v[k].x)); r.y = __half2float(__float2half_rn(v[k].y));
                 r.z = __half2float(__float2half_rn(v[k].z)); r.w = __half2float(__float2half_rn(v[k].w));
-                ss += r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
+                ss2 = agn_sum_sq4(r, ss2);
             }
         } else {
 #pragma unroll
-            for (int k = 0; k < VPT; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+            for (int k = 0; k < VPT; k++) ss2 = agn_sum_sq4(v[k], ss2);
         }
-        ss = agn_warp_sum(ss);
+        float ss = agn_warp_sum(ss2.x + ss2.y);
         float *r2 = red[it & 1];  // two sets: a warp may already write the next row's partial while another still sums this one's
         if (lane == 0) r2[warp] = ss;
         // partial sums visible; every thread has read its part of the slot; and one CTA-wide answer
@@ -198,7 +207,7 @@ rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
         if (threadIdx.x == 0 && it + slots < n_my) issue(it + slots);
         float total = 0.0f;
         for (int wi = 0; wi < nwarps; wi++) total += r2[wi];
-        const float inv = 1.0f / sqrtf(total / n_f + eps);
+        const float inv = inv_rms(total, inv_n, eps);
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             const int i = threadIdx.x + k * blockDim.x;
@@ -212,12 +221,7 @@ rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
                     }
                 }
                 const float4 wk = VPT <= 4 ? ww[k < WREG ? k : 0] : __ldg(w + i);
-                float4 o;
-                o.x = wk.x * xv.x * inv;
-                o.y = wk.y * xv.y * inv;
-                o.z = wk.z * xv.z * inv;
-                o.w = wk.w * xv.w * inv;
-                ActVec<OT>::store(out, row + i, o);
+                ActVec<OT>::store(out, row + i, agn_scale4(agn_mul4(wk, xv), inv));
             }
         }
     }
@@ -244,7 +248,7 @@ bool launch_ring(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *ne
     if (T_rows < 2 * grid && !ctx->tune_ring_force) return false;  // too few rows to keep a ring busy: one CTA per row is faster
     if (grid > T_rows) grid = T_rows;
     agn_launch(ctx, kernel, dim3((unsigned)grid), dim3(threads), smem, x, delta, reinterpret_cast<const float4 *>(w), new_x, out,
-               T_rows, n4, (float)(n4 * 4), eps, slots, ctx->mbar_spin_limit, ctx->d_flags);
+               T_rows, n4, 1.0f / (float)(n4 * 4), eps, slots, ctx->mbar_spin_limit, ctx->d_flags);
     ctx->flags_dirty = true;
     return true;
 }
@@ -269,7 +273,7 @@ rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delt
         ss += v * v;
     }
     ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    const float inv = inv_rms(ss, 1.0f / (float)H, eps);
     const T *src = RESIDUAL ? new_x : x;
     for (int64_t i = threadIdx.x; i < H; i += blockDim.x)
         ActVec<OT>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
@@ -283,10 +287,10 @@ bool launch_vec(agn_ctx *ctx, const T *x, const T *delta, const float *w, T *new
     if (ctx->tune_rms_recip && launch_ring<T, OT, VPT, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads)) return true;
     if (ctx->tune_rms_recip)
         agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, true>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
-                   new_x, out, n4, (float)(n4 * 4), eps);
+                   new_x, out, n4, (float)(n4 * 4), 1.0f / (float)(n4 * 4), eps);
     else
         agn_launch(ctx, rms_norm_rows_kernel<T, OT, VPT, RESIDUAL, false>, dim3((unsigned)T_rows), dim3(threads), 0, x, delta, w4,
-                   new_x, out, n4, (float)(n4 * 4), eps);
+                   new_x, out, n4, (float)(n4 * 4), 1.0f / (float)(n4 * 4), eps);
     return false;
 }
 

@@ -38,6 +38,7 @@ struct RopeArgs {
     int pos_start;
     int tpc;  // tokens per CTA
     float freq_scale, eps;
+    float inv_head_dim;  // 1 / head_dim, for the per-head mean square
     // fused KV-cache write (template parameter KV != 0): the rotated K heads and the V heads of the
     // token are packed into one layer's cache at slot pos (`KvCache::write`, src/model/mod.rs:648-672)
     const float *v;
@@ -116,25 +117,28 @@ enum { MODE_NORMAL = 0,   // pairs (2p, 2p+1): both members inside one float4
 // cache write and idle slots pass false; they still take part in the shuffles).
 template <typename T, int W, int VPL, int MODE, bool NORM>
 __device__ __forceinline__ void rope_head_math(float4 (&v)[VPL], bool rot, const float4 *wv, const float *c_tab,
-                                               const float *s_tab, int lane, int hd4, int hq, int head_dim, int n_rot, float eps) {
+                                               const float *s_tab, int lane, int hd4, int hq, float inv_head_dim, int n_rot, float eps) {
     if (NORM) {
-        float ss = 0.0f;
+        float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int l = 0; l < VPL; l++) ss += v[l].x * v[l].x + v[l].y * v[l].y + v[l].z * v[l].z + v[l].w * v[l].w;
+        for (int l = 0; l < VPL; l++) ss2 = agn_sum_sq4(v[l], ss2);
+        float ss = ss2.x + ss2.y;
 #pragma unroll
         for (int o = W / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        // (w*x)/rms of the CPU path, evaluated as (w*x)*(1/rms): one IEEE division per
-        // head instead of one per element; differs from the CPU order by <= 1 ulp
-        const float inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+        // (w*x)/rms of the CPU path, evaluated as (w*x) * rsqrt(ss/hd + eps): the hardware reciprocal
+        // square root (2 ulp) instead of two IEEE divisions and a square root per head row and lane;
+        // a few 1e-7 relative from the CPU order, inside the 1e-5 tolerance
+        const float inv = rsqrtf(__fmaf_rn(ss, inv_head_dim, eps));
 #pragma unroll
         for (int l = 0; l < VPL; l++) {
             const int i = lane + W * l;
             if (rot && i < hd4) {
                 const float4 ww = wv[i];  // shared memory (CTA-per-unit kernel) or global memory (persistent kernel)
-                v[l].x = act_round<T>(ww.x * v[l].x * inv);
-                v[l].y = act_round<T>(ww.y * v[l].y * inv);
-                v[l].z = act_round<T>(ww.z * v[l].z * inv);
-                v[l].w = act_round<T>(ww.w * v[l].w * inv);
+                const float4 nx = agn_scale4(agn_mul4(ww, v[l]), inv);  // (w * x) * inv
+                v[l].x = act_round<T>(nx.x);
+                v[l].y = act_round<T>(nx.y);
+                v[l].z = act_round<T>(nx.z);
+                v[l].w = act_round<T>(nx.w);
             }
         }
     }
@@ -281,7 +285,7 @@ rope_heads_kernel(const RopeArgs a) {
             const float *s_tab = s_sin + (meta[s] & 0xffff) * half;
             rope_head_math<T, W, VPL, MODE, NORM>(v[s], ptr[s] != nullptr && kind < 2,
                                                   reinterpret_cast<const float4 *>(kind == 1 ? s_wk : s_wq), c_tab, s_tab, lane, hd4, hq,
-                                                  a.head_dim, a.n_rot, a.eps);
+                                                  a.inv_head_dim, a.n_rot, a.eps);
 #pragma unroll
             for (int l = 0; l < VPL; l++) {
                 const int i = lane + W * l;
@@ -417,7 +421,7 @@ rope_heads_ring_kernel(const RopeArgs a, int slots, int slot_bytes, int spin_lim
                 const float *c_tab = s_cos + (meta[s] & 0xffff) * half;
                 const float *sn_tab = s_sin + (meta[s] & 0xffff) * half;
                 rope_head_math<T, W, VPL, MODE, NORM>(v[s], live[s], reinterpret_cast<const float4 *>(is_k ? a.wk : a.wq), c_tab, sn_tab,
-                                                      lane, hd4, hq, a.head_dim, a.n_rot, a.eps);
+                                                      lane, hd4, hq, a.inv_head_dim, a.n_rot, a.eps);
                 // the head's place in q / k: the slot holds the pieces in the same order as global memory
                 T *dst = is_k ? reinterpret_cast<T *>(kb + t0 * k_tok_bytes + (off[s] - (int)k_off))
                               : reinterpret_cast<T *>(qb + t0 * q_tok_bytes + off[s]);
@@ -597,6 +601,7 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
     a.q = q; a.k = k; a.wq = wq; a.wk = wk; a.pos = pos; a.T = T;
     a.n_q = n_q; a.n_kv = n_kv; a.head_dim = head_dim; a.n_rot = n_rot;
     a.pos_start = pos_start; a.freq_scale = freq_scale; a.eps = eps; a.tpc = 1;
+    a.inv_head_dim = 1.0f / (float)head_dim;
     a.denom = nullptr;
     a.v = nullptr; a.k_cache = nullptr; a.v_cache = nullptr; a.max_seq = 0; a.bytes_per_token = 0; a.flags = ctx->d_flags;
     if (n_rot >= 2) {

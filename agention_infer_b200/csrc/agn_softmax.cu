@@ -107,8 +107,29 @@ __device__ __forceinline__ float exp_shifted(float v, float m, float coef) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
     return r;
 }
+__device__ __forceinline__ float ex2_approx(float t) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    return r;
+}
+// Four at a time.  The subtraction, the multiplication, the row sum and the final scaling run on
+// Blackwell's packed f32x2 instructions (two IEEE round-to-nearest results per instruction, the
+// same bits as the scalar operations): these kernels are bound by instruction issue once the
+// output shrinks, and this takes a third of the floating-point instructions out.
 __device__ __forceinline__ float4 exp4(float4 v, float m, float coef) {
-    return make_float4(exp_shifted(v.x, m, coef), exp_shifted(v.y, m, coef), exp_shifted(v.z, m, coef), exp_shifted(v.w, m, coef));
+    const float2 nm = make_float2(-m, -m), cc = make_float2(coef, coef);
+    const float2 lo = __fmul2_rn(__fadd2_rn(make_float2(v.x, v.y), nm), cc);
+    const float2 hi = __fmul2_rn(__fadd2_rn(make_float2(v.z, v.w), nm), cc);
+    return make_float4(ex2_approx(lo.x), ex2_approx(lo.y), ex2_approx(hi.x), ex2_approx(hi.y));
+}
+__device__ __forceinline__ float hsum4(float4 v) {  // (x + y) + (z + w)
+    const float2 p = __fadd2_rn(make_float2(v.x, v.z), make_float2(v.y, v.w));
+    return p.x + p.y;
+}
+__device__ __forceinline__ float4 scale4(float4 v, float f) {
+    const float2 ff = make_float2(f, f);
+    const float2 lo = __fmul2_rn(make_float2(v.x, v.y), ff), hi = __fmul2_rn(make_float2(v.z, v.w), ff);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // Very short rows (router logits, <= 32 entries): one thread per row, everything in registers.
@@ -135,7 +156,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             v[k] = exp4(v[k], m, a.exp_coef);
-            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            sum += hsum4(v[k]);
         }
     }
     if (a.sums) a.sums[r] = sum;
@@ -144,7 +165,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPT; k++)
         {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * k < nv) o = make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv);
+            if (4 * k < nv) o = scale4(v[k], inv);
             store_probs<OT>(out, k, o, nv, n4, a.leave_tail != 0);
         }
 }
@@ -177,7 +198,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPL; k++) {
         if (4 * (lane + 32 * k) < nv) {
             v[k] = exp4(v[k], m, a.exp_coef);
-            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            sum += hsum4(v[k]);
         }
     }
     sum = agn_warp_sum(sum);
@@ -186,7 +207,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
 #pragma unroll
     for (int k = 0; k < VPL; k++) {
         const int i = lane + 32 * k;
-        if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+        if (4 * i < nv) store_probs<OT>(out, i, scale4(v[k], inv), nv, n4, a.leave_tail != 0);
         else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
     }
 }
@@ -224,7 +245,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPT; k++) {
         if (4 * (threadIdx.x + k * blockDim.x) < nv) {
             v[k] = exp4(v[k], m, a.exp_coef);
-            sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            sum += hsum4(v[k]);
         }
     }
     sum = agn_warp_sum(sum);
@@ -237,7 +258,7 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
-        if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+        if (4 * i < nv) store_probs<OT>(out, i, scale4(v[k], inv), nv, n4, a.leave_tail != 0);
         else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
     }
 }
@@ -303,7 +324,7 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
         if (idx[k] >= 0) {
             const bool isB = (idx[k] >> 30) & 1;
             v[k] = exp4(v[k], isB ? mB : mA, a.exp_coef);
-            const float t = (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            const float t = hsum4(v[k]);
             if (isB) sB += t;
             else sA += t;
         }
@@ -324,7 +345,7 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
         if (idx[k] >= 0) {
             const bool isB = (idx[k] >> 30) & 1;
             const float inv = isB ? invB : invA;
-            store_probs<OT>(isB ? outB : outA, idx[k] & 0x3fffffff, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv),
+            store_probs<OT>(isB ? outB : outA, idx[k] & 0x3fffffff, scale4(v[k], inv),
                             isB ? nvB : nvA, n4, a.leave_tail != 0);
         }
     }
@@ -426,7 +447,7 @@ softmax_ring_kernel(const SoftmaxArgs a, int slots, int slot_bytes, int spin_lim
         for (int k = 0; k < VPT; k++) {
             if (4 * (threadIdx.x + k * blockDim.x) < nv) {
                 v[k] = exp4(v[k], m, a.exp_coef);
-                sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+                sum += hsum4(v[k]);
             }
         }
         sum = agn_warp_sum(sum);
@@ -439,7 +460,7 @@ softmax_ring_kernel(const SoftmaxArgs a, int slots, int slot_bytes, int spin_lim
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             const int i = threadIdx.x + k * blockDim.x;
-            if (4 * i < nv) store_probs<OT>(out, i, make_float4(v[k].x * inv, v[k].y * inv, v[k].z * inv, v[k].w * inv), nv, n4, a.leave_tail != 0);
+            if (4 * i < nv) store_probs<OT>(out, i, scale4(v[k], inv), nv, n4, a.leave_tail != 0);
             else store_past_valid<OT>(out, i, n4, a.leave_tail != 0);
         }
     }
@@ -492,7 +513,7 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         v[k] = exp4(v[k], m_c, a.exp_coef);
-        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        sum += hsum4(v[k]);
     }
     sum = agn_warp_sum(sum);
     if (lane == 0) red[warp] = sum;
@@ -527,7 +548,7 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
         const int i = base + k * step;
         {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (4 * i < nv) o = make_float4(v[k].x * f, v[k].y * f, v[k].z * f, v[k].w * f);
+            if (4 * i < nv) o = scale4(v[k], f);
             store_probs<OT>(out, i, o, nv, n4, a.leave_tail != 0);
         }
     }
