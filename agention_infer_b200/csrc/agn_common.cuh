@@ -63,6 +63,7 @@ struct agn_ctx {
     int tune_get_rows_tma;      // stage the quantised row with one bulk asynchronous copy (TMA)
     int tune_silu_unroll;       // float4 pairs in flight per thread in silu_mul: 2, 4 (default) or 8
     int tune_silu_threads;      // 128, 256 (default) or 512
+    int tune_kv_multi;          // 1 (default): kv_write packs four tokens per CTA for batches that fill the GPU that way
     int tune_silu_small;        // 1 (default): decode-sized inputs run one float4 pair per thread in 128-thread CTAs
     // Persistent kernels with a shared-memory row ring (rows staged by bulk asynchronous copies
     // ahead of the row being processed).  *_ring: 0 = never (default: on B200 the CTA-per-row

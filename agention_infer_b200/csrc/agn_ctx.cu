@@ -74,6 +74,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_silu_unroll = 4;
     ctx->tune_silu_threads = 256;
     ctx->tune_silu_small = 1;
+    ctx->tune_kv_multi = 1;
     ctx->tune_rms_ring = 0;
     ctx->tune_rms_ring_ctas = 0;
     ctx->tune_rope_ring = 0;
@@ -202,6 +203,7 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
             {"softmax_warp16", &ctx->tune_softmax_warp16, 0, 1},
             {"softmax_causal_pair", &ctx->tune_softmax_causal_pair, 0, 1},
             {"silu_small", &ctx->tune_silu_small, 0, 1},
+            {"kv_multi", &ctx->tune_kv_multi, 0, 1},
             {"host_chunk_bytes", &ctx->tune_host_chunk_bytes, 0, 24 << 20},
             {"host_slots", &ctx->tune_host_slots, 0, 16},
             {"mbar_spin_limit", &ctx->mbar_spin_limit, 1, 1 << 30},

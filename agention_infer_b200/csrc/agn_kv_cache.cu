@@ -46,30 +46,41 @@ kv_write_q8_0_kernel(const KvArgs a) {
     const int lane8 = threadIdx.x & 7;
     const int nblk = (int)((a.hd + 31) >> 5);
     const float *src_row = (blockIdx.y ? a.v : a.k) + t * a.hd;
+    const bool vec = (a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src_row) & 15) == 0);
+    const int bpp = (int)(blockDim.x >> 3);  // blocks per pass
+    const int e0 = lane8 * 4;
+    // values of pass p, block b = p * bpp + (thread / 8): issued before the slot is known (below)
+    auto load_pass = [&](int p, float (&x)[4]) {
+        const int b = p * bpp + (int)(threadIdx.x >> 3);
+        const int left = b < nblk ? (int)(a.hd - (int64_t)b * 32) : 0;  // elements of this (possibly partial) block
+        const float *src = src_row + (int64_t)b * 32;
+        x[0] = x[1] = x[2] = x[3] = 0.f;
+        if (left > 0 && vec && e0 + 3 < left) {
+            const float4 q = __ldcs(reinterpret_cast<const float4 *>(src + e0));
+            x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
+        } else if (left > 0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (e0 + i < left) x[i] = src[e0 + i];
+        }
+    };
+    // The token's values do not depend on its position: their loads go out before the position load
+    // returns, so the two memory latencies of this short kernel overlap instead of adding up.
+    float x[4];
+    load_pass(0, x);
     const int64_t slot = kv_slot(a, t);
     if (slot < 0) {  // same answer for the whole CTA
         if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
         return;
     }
     unsigned char *tok = (blockIdx.y ? a.v_cache : a.k_cache) + slot * a.bytes_per_token;
-    const bool vec = (a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src_row) & 15) == 0);
     // all lanes of a warp run the same number of passes (the shuffles below need them)
-    const int passes = (nblk + (int)(blockDim.x >> 3) - 1) / (int)(blockDim.x >> 3);
+    const int passes = (nblk + bpp - 1) / bpp;
     for (int p = 0; p < passes; p++) {
-        const int b = p * (int)(blockDim.x >> 3) + (int)(threadIdx.x >> 3);
+        if (p > 0) load_pass(p, x);
+        const int b = p * bpp + (int)(threadIdx.x >> 3);
         const bool on = b < nblk;
-        const int e0 = lane8 * 4;
-        const int left = on ? (int)(a.hd - (int64_t)b * 32) : 0;  // elements of this (possibly partial) block
-        const float *src = src_row + (int64_t)b * 32;
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-        if (on && vec && e0 + 3 < left) {
-            const float4 q = __ldcs(reinterpret_cast<const float4 *>(src + e0));
-            x[0] = q.x; x[1] = q.y; x[2] = q.z; x[3] = q.w;
-        } else if (on) {
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                if (e0 + i < left) x[i] = src[e0 + i];
-        }
+        const int left = on ? (int)(a.hd - (int64_t)b * 32) : 0;
         float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
 #pragma unroll
         for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -99,18 +110,87 @@ __global__ void __launch_bounds__(256)
 kv_write_f16_kernel(const KvArgs a) {
     agn_pdl_prologue();
     const int64_t t = blockIdx.x;
+    const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd;
+    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
+    // (a slot starts at a multiple of bytes_per_token from the cache base, so the alignment of the
+    // destination is known before the position is)
+    const bool vec = (a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(cache) & 7) == 0) && (a.bytes_per_token & 7) == 0;
+    const int n4 = (int)(a.hd >> 2);
+    // The token's values do not depend on its position: the first load goes out before the position
+    // load returns, so the two memory latencies of this short kernel overlap instead of adding up.
+    float4 first = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec && (int)threadIdx.x < n4) first = __ldcs(reinterpret_cast<const float4 *>(src) + threadIdx.x);
     const int64_t slot = kv_slot(a, t);
     if (slot < 0) {
         if (threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
         return;
     }
-    const float *src = (blockIdx.y ? a.v : a.k) + t * a.hd;
-    __half *dst = reinterpret_cast<__half *>((blockIdx.y ? a.v_cache : a.k_cache) + slot * a.bytes_per_token);
-    if ((a.hd & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-        for (int i = threadIdx.x; i < (int)(a.hd >> 2); i += blockDim.x)
+    __half *dst = reinterpret_cast<__half *>(cache + slot * a.bytes_per_token);
+    if (vec) {
+        if ((int)threadIdx.x < n4) ActVec<__half>::store(dst, threadIdx.x, first);
+        for (int i = threadIdx.x + blockDim.x; i < n4; i += blockDim.x)
             ActVec<__half>::store(dst, i, __ldcs(reinterpret_cast<const float4 *>(src) + i));
     } else {
         for (int i = threadIdx.x; i < (int)a.hd; i += blockDim.x) dst[i] = __float2half_rn(src[i]);
+    }
+}
+
+// Batches of more than a few tokens: one CTA packs TPC consecutive tokens of K or of V.  Every
+// thread owns float4 number threadIdx.x of each of them and issues all its loads (values and
+// positions) before the first use, so a thread has TPC independent chains in flight instead of
+// one and the launch has TPC times fewer CTAs: with a CTA per token this kernel moves 20 MB in
+// about three rounds of short-lived CTAs whose whole life is one dependent chain of two memory
+// latencies.  Needs whole 32-value blocks (hd % 32 == 0), hd / 4 <= 256 threads and 16-byte
+// aligned rows (checked by the host).
+template <bool Q8, int TPC>
+__global__ void __launch_bounds__(256)
+kv_write_multi_kernel(const KvArgs a) {
+    agn_pdl_prologue();
+    const int64_t t0 = (int64_t)blockIdx.x * TPC;
+    const float *src = blockIdx.y ? a.v : a.k;
+    unsigned char *cache = blockIdx.y ? a.v_cache : a.k_cache;
+    const int n4 = (int)(a.hd >> 2);
+    const bool lane_on = (int)threadIdx.x < n4;
+    float4 x[TPC];
+    int64_t p[TPC];
+#pragma unroll
+    for (int j = 0; j < TPC; j++) {
+        const int64_t t = t0 + j;
+        const bool on = t < a.T;
+        x[j] = (on && lane_on) ? __ldcs(reinterpret_cast<const float4 *>(src + t * a.hd) + threadIdx.x) : make_float4(0.f, 0.f, 0.f, 0.f);
+        p[j] = !on ? -2 : (a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t);
+    }
+#pragma unroll
+    for (int j = 0; j < TPC; j++) {
+        if (p[j] == -2) continue;  // past the last token: the same answer in every thread of the CTA
+        const bool in_range = p[j] >= 0 && p[j] < a.max_seq;
+        if (!in_range && threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
+        unsigned char *tok = cache + (in_range ? p[j] : 0) * a.bytes_per_token;
+        if (!Q8) {
+            if (in_range && lane_on) ActVec<__half>::store(reinterpret_cast<__half *>(tok), threadIdx.x, x[j]);
+        } else {
+            // eight lanes hold one 32-value block; every lane of the warp takes part in the shuffles
+            float amax = fmaxf(fmaxf(fabsf(x[j].x), fabsf(x[j].y)), fmaxf(fabsf(x[j].z), fabsf(x[j].w)));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (in_range && lane_on) {
+                const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+                const int lane8 = threadIdx.x & 7;
+                unsigned char *blk = tok + (size_t)(threadIdx.x >> 3) * 34;
+                if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+                const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+                uint32_t q[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float r = roundf(__fdiv_rn(xs[i], scale));
+                    r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0
+                    q[i] = (uint32_t)(unsigned char)(signed char)(int)r;
+                }
+                *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
+                *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+            }
+        }
     }
 }
 
@@ -188,6 +268,21 @@ extern "C" int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float 
     a.k = k; a.v = v; a.k_cache = static_cast<unsigned char *>(k_cache); a.v_cache = static_cast<unsigned char *>(v_cache);
     a.pos = pos; a.T = T; a.hd = head_dim_kv; a.max_seq = max_seq_len; a.pos_start = pos_start; a.bytes_per_token = bpt;
     a.flags = ctx->d_flags;
+    // several tokens per CTA once there are enough tokens to fill the GPU that way
+    constexpr int TPC = 4;
+    const bool multi = ctx->tune_kv_multi && T >= 4 * TPC * (int64_t)ctx->sm_count && head_dim_kv % 32 == 0 && head_dim_kv <= 1024 &&
+                       agn_aligned16(k) && agn_aligned16(v) &&
+                       (kv_dtype == AGN_Q8_0 || (agn_aligned(k_cache, 8) && agn_aligned(v_cache, 8)));
+    if (multi) {
+        if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
+        const int threads = (int)(((head_dim_kv / 4) + 31) / 32 * 32);
+        const dim3 grid((unsigned)((T + TPC - 1) / TPC), 2);
+        if (kv_dtype == AGN_Q8_0) agn_launch(ctx, kv_write_multi_kernel<true, TPC>, grid, dim3(threads), 0, a);
+        else agn_launch(ctx, kv_write_multi_kernel<false, TPC>, grid, dim3(threads), 0, a);
+        ctx->flags_dirty = true;
+        AGN_LAUNCHED(ctx, "kv_write_multi");
+        return AGN_OK;
+    }
     if (kv_dtype == AGN_Q8_0) {
         if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
         int threads = (int)(((head_dim_kv + 31) / 32) * 8);  // eight lanes per 32-value block

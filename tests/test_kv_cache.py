@@ -155,6 +155,40 @@ def test_fused_q8_0_cache_write_of_nonfinite_v_rows(backend):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [AGN_F16, AGN_Q8_0])
+@pytest.mark.parametrize("T,hd", [(2501, 256), (4096, 1024), (3000, 32)])
+def test_kv_write_four_tokens_per_cta(backend, dtype, T, hd):
+    """Large batches pack four tokens per CTA: a token count that is not a multiple of four, positions out of
+    range in the middle of a group (skipped and reported), bytes identical to the CTA-per-token kernel and the oracle."""
+    max_seq = T + 7
+    k = synth.activations(2, "k", (T, hd)); v = synth.activations(2, "q", (T, hd)) * np.float32(3.0)
+    k[5, :32] = 0.0
+    pos = synth.rng_for(2, "pos").permutation(max_seq)[:T].astype(np.int32)
+    bad = [1, 1234, T - 1]
+    pos_bad = pos.copy(); pos_bad[bad] = [-3, max_seq, 2 ** 30]
+    bpt = backend.kv_bytes_per_token(dtype, hd)
+    ref_k = np.zeros((max_seq, bpt), np.uint8); ref_v = np.zeros((max_seq, bpt), np.uint8)
+    keep = np.ones(T, bool); keep[bad] = False
+    orc.kv_write_rows(dtype, k[keep], pos[keep], ref_k); orc.kv_write_rows(dtype, v[keep], pos[keep], ref_v)
+    dk, dv, dp = backend.upload(k), backend.upload(v), backend.upload(pos_bad)
+    got = {}
+    for multi in (1, 0):
+        backend.set_option("kv_multi", multi)
+        try:
+            dkc, dvc = backend.upload(np.zeros_like(ref_k)), backend.upload(np.zeros_like(ref_v))
+            backend.kv_write(dtype, dk, dv, dkc, dvc, T, hd, dp, max_seq)
+            assert backend.last_kernel == ("kv_write_multi" if multi else "kv_write")
+            with pytest.raises(BackendError) as e:
+                backend.sync()
+            assert e.value.status == 4 and "kv_write" in str(e.value)
+            got[multi] = (backend.read(dkc, np.uint8, ref_k.shape), backend.read(dvc, np.uint8, ref_v.shape))
+        finally:
+            backend.set_option("kv_multi", 1)
+    assert np.array_equal(got[1][0], ref_k) and np.array_equal(got[1][1], ref_v)
+    assert np.array_equal(got[1][0], got[0][0]) and np.array_equal(got[1][1], got[0][1])
+
+
+@pytest.mark.gpu
 def test_kv_write_pos_start_and_out_of_range_slot(backend):
     T, hd, max_seq = 8, 64, 10
     k = synth.activations(2, "k", (T, hd))
