@@ -49,8 +49,10 @@ __device__ __forceinline__ float inv_rms(float ss, float inv_n, float eps) { ret
 
 // T: storage type of x, delta and new_x; OT: storage type of the normed output (T, or a 16-bit
 // type for a row that feeds a matmul with half-precision operands).
+// (Two CTAs of 1024 threads per SM as the launch bound caps the kernel at 32 registers for up to
+// four float4 per thread, which is what keeps nine 224-thread CTAs — nine rows — resident per SM.)
 template <typename T, typename OT, int VPT, bool RESIDUAL, bool RECIP>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(1024, VPT <= 4 ? 2 : 1)
 rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const float4 *__restrict__ w,
                      T *__restrict__ new_x, OT *__restrict__ out, int n4, float n_f, float inv_n, float eps) {
     agn_pdl_prologue();
