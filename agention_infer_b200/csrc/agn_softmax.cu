@@ -36,7 +36,9 @@ struct SoftmaxArgs {
 __device__ __forceinline__ int64_t valid_len(const SoftmaxArgs &a, int64_t r) {
     int64_t nv;
     if (a.n_valid) nv = a.n_valid[r];
-    else if (a.causal_period > 0) nv = (int64_t)a.causal_offset + (r % a.causal_period) + 1;
+    // (row numbers fit 31 bits — the host checks — so the remainder is a 32-bit one: a 64-bit
+    // remainder is ~100 instructions in every thread of kernels that run ~600 per thread)
+    else if (a.causal_period > 0) nv = (int64_t)a.causal_offset + (int64_t)((uint32_t)r % (uint32_t)a.causal_period) + 1;
     else nv = a.row_len;
     if (nv > a.row_len) nv = a.row_len;
     if (nv < 0) nv = 0;
@@ -79,10 +81,12 @@ template <typename OT>
 __device__ __forceinline__ void store_probs(OT *out, int i, float4 o, int nv, int n4, bool leave_tail) {
     if (i >= n4) return;
     const int e = 4 * i;
-    if (!leave_tail || e + 3 < nv) {
+    if (e + 3 < nv) {  // wholly valid: the common case, nothing to mask
+        ActVec<OT>::store(out, i, o);
+    } else if (!leave_tail) {  // straddles the valid length (or lies past it, with o = 0): zeros behind it
         zero_tail(o, i, nv);
         ActVec<OT>::store(out, i, o);
-    } else if (e < nv) {  // e + 3 >= nv: one to three valid entries
+    } else if (e < nv) {  // one to three valid entries, the rest left untouched
         ActVec<OT>::store1(out, e, o.x);
         if (e + 1 < nv) ActVec<OT>::store1(out, e + 1, o.y);
         if (e + 2 < nv) ActVec<OT>::store1(out, e + 2, o.z);
@@ -278,8 +282,9 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int L = (int)a.row_len, n4 = L >> 2;
     const int half_rows = (L + 1) >> 1;
-    const int64_t head = blockIdx.x / half_rows;
-    const int p = (int)(blockIdx.x - head * half_rows);
+    const uint32_t head_u = blockIdx.x / (uint32_t)half_rows;  // 32-bit division: the grid fits 31 bits
+    const int64_t head = head_u;
+    const int p = (int)(blockIdx.x - head_u * (uint32_t)half_rows);
     const int rowA = p, rowB = L - 1 - p;       // rowB == rowA for the middle row of an odd L
     const bool twoRows = rowB != rowA;
     const int nvA = rowA + 1, nvB = twoRows ? rowB + 1 : 0;
