@@ -159,11 +159,11 @@ kv_write_multi_kernel(const KvArgs a) {
         const int64_t t = t0 + j;
         const bool on = t < a.T;
         x[j] = (on && lane_on) ? __ldcs(reinterpret_cast<const float4 *>(src + t * a.hd) + threadIdx.x) : make_float4(0.f, 0.f, 0.f, 0.f);
-        p[j] = !on ? -2 : (a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t);
+        p[j] = !on ? 0 : (a.pos ? (int64_t)a.pos[t] : (int64_t)a.pos_start + t);
     }
 #pragma unroll
     for (int j = 0; j < TPC; j++) {
-        if (p[j] == -2) continue;  // past the last token: the same answer in every thread of the CTA
+        if (t0 + j >= a.T) continue;  // past the last token: the same answer in every thread of the CTA
         const bool in_range = p[j] >= 0 && p[j] < a.max_seq;
         if (!in_range && threadIdx.x == 0) atomicOr(a.flags, AGN_FLAG_OOB_SLOT);
         unsigned char *tok = cache + (in_range ? p[j] : 0) * a.bytes_per_token;

@@ -165,7 +165,7 @@ def test_kv_write_four_tokens_per_cta(backend, dtype, T, hd):
     k[5, :32] = 0.0
     pos = synth.rng_for(2, "pos").permutation(max_seq)[:T].astype(np.int32)
     bad = [1, 1234, T - 1]
-    pos_bad = pos.copy(); pos_bad[bad] = [-3, max_seq, 2 ** 30]
+    pos_bad = pos.copy(); pos_bad[bad] = [-2, max_seq, 2 ** 30]  # (-2 of all values: no sentinel may swallow it)
     bpt = backend.kv_bytes_per_token(dtype, hd)
     ref_k = np.zeros((max_seq, bpt), np.uint8); ref_v = np.zeros((max_seq, bpt), np.uint8)
     keep = np.ones(T, bool); keep[bad] = False
@@ -186,6 +186,14 @@ def test_kv_write_four_tokens_per_cta(backend, dtype, T, hd):
             backend.set_option("kv_multi", 1)
     assert np.array_equal(got[1][0], ref_k) and np.array_equal(got[1][1], ref_v)
     assert np.array_equal(got[1][0], got[0][0]) and np.array_equal(got[1][1], got[0][1])
+    # a single bad position, and that one is -2: still reported
+    one_bad = pos.copy(); one_bad[T // 2] = -2
+    backend.kv_write(dtype, dk, dv, backend.upload(np.zeros_like(ref_k)), backend.upload(np.zeros_like(ref_v)), T, hd,
+                     backend.upload(one_bad), max_seq)
+    assert backend.last_kernel == "kv_write_multi"
+    with pytest.raises(BackendError) as e:
+        backend.sync()
+    assert e.value.status == 4
 
 
 @pytest.mark.gpu
