@@ -603,6 +603,59 @@ void orc_gather_rows_by_expert(const float *x, size_t T, size_t H, const int32_t
     }
 }
 
+/* ------------------------------------------------ Q8_K activation rows -- */
+
+/* Rust's `f32 as i32`: saturating, NaN -> 0 */
+static int32_t f32_as_i32(float v) {
+    if (v != v) return 0;
+    if (v >= 2147483648.0f) return INT32_MAX;
+    if (v <= -2147483648.0f) return INT32_MIN;
+    return (int32_t)v;
+}
+
+/* src/quant/q8_k.rs:49-92 */
+void orc_quantize_row_q8_k(const float *x, size_t n, float *d, int8_t *qs, int16_t *bsums) {
+    size_t n_blocks = (n + 255) / 256;
+    for (size_t block = 0; block < n_blocks; block++) {
+        size_t start = block * 256;
+        size_t end = start + 256 < n ? start + 256 : n;
+        float amax = 0.0f, max = 0.0f;
+        for (size_t i = start; i < end; i++) {
+            float av = fabsf(x[i]);
+            if (av > amax) {
+                amax = av;
+                max = x[i];
+            }
+        }
+        int8_t *q = qs + block * 256;
+        memset(q, 0, 256);
+        d[block] = 0.0f;
+        if (amax > 0.0f) {
+            float iscale = -127.0f / max;
+            for (size_t i = start; i < end; i++) {
+                int32_t rounded = f32_as_i32(roundf(iscale * x[i])); /* f32::round: half away from zero */
+                if (rounded > 127) rounded = 127;
+                q[i - start] = (int8_t)(uint8_t)((uint32_t)rounded & 0xffu); /* `as i8` truncates */
+            }
+            d[block] = 1.0f / iscale;
+        }
+        for (size_t g = 0; g < 16; g++) {
+            int16_t s = 0;
+            for (size_t j = 0; j < 16; j++) s = (int16_t)(s + q[g * 16 + j]);
+            bsums[block * 16 + g] = s;
+        }
+    }
+}
+
+void orc_quantize_rows_q8_k(const float *x, size_t T, size_t n, float *d, int8_t *qs, int16_t *bsums,
+                            int threads) {
+    size_t nb = (n + 255) / 256;
+#pragma omp parallel for schedule(static) num_threads(threads) if (threads > 1)
+    for (long t = 0; t < (long)T; t++)
+        orc_quantize_row_q8_k(x + (size_t)t * n, n, d + (size_t)t * nb, qs + (size_t)t * nb * 256,
+                              bsums + (size_t)t * nb * 16);
+}
+
 int orc_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

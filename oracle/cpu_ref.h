@@ -162,6 +162,19 @@ void orc_gather_rows_by_expert(const float *x, size_t T, size_t H, const int32_t
                                size_t n_experts, float *out, int32_t *offsets,
                                int32_t *src_token, int32_t *src_slot);
 
+/* Q8_K activation quantisation, quantize_row_q8_k (src/quant/q8_k.rs:49-92): what the matmul of a
+ * Q5_K tensor turns its activation vector into before the int8 dot products
+ * (WeightMap::matmul_into, src/model/mod.rs:381-386).  Per block of 256 values (the last one
+ * zero-padded): the signed value of largest magnitude (first one on ties) -> iscale = -127 / max;
+ * q = min(round_half_away(iscale * v) as i32 (saturating, NaN -> 0), 127) as i8 (wrapping);
+ * d = 1 / iscale (0 for an all-zero block); bsums[g] = sum of q over group g of 16.
+ * Outputs as the parallel arrays of `Q8KRow` (:27-37): d [nb], qs [nb * 256], bsums [nb * 16],
+ * nb = ceil(n / 256).  Pinned by the reference's four unit tests (:97-139). */
+void orc_quantize_row_q8_k(const float *x, size_t n, float *d, int8_t *qs, int16_t *bsums);
+/* rows of length n, row r at x + r * n; outputs row after row */
+void orc_quantize_rows_q8_k(const float *x, size_t T, size_t n, float *d, int8_t *qs, int16_t *bsums,
+                            int threads);
+
 int orc_max_threads(void);
 
 #ifdef __cplusplus

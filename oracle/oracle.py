@@ -61,6 +61,7 @@ def lib() -> C.CDLL:
             "orc_kv_read": (None, [_i, _vp, _sz, _sz, _vp]),
             "orc_router_top2": (None, [_vp, _sz, _sz, _vp, _vp]),
             "orc_gather_rows_by_expert": (None, [_vp, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _vp]),
+            "orc_quantize_rows_q8_k": (None, [_vp, _sz, _sz, _vp, _vp, _vp, _i]),
             "orc_max_threads": (_i, []),
         }
         for name, (res, args) in sig.items():
@@ -153,6 +154,17 @@ def silu_mul(gate, up, threads: int = 1) -> np.ndarray:
     out = np.empty_like(g)
     lib().orc_silu_mul(_p(g), _p(u), _p(out), g.size, threads)
     return out
+
+
+def quantize_rows_q8_k(x, threads: int = 1):
+    """Rows of `x` [..., n] -> (d [T, nb] f32, qs [T, nb*256] i8, bsums [T, nb*16] i16), nb = ceil(n / 256)."""
+    a = _f32(x)
+    rows = a.reshape(-1, a.shape[-1])
+    T, n = rows.shape
+    nb = (n + 255) // 256
+    d = np.empty((T, nb), np.float32); qs = np.empty((T, nb * 256), np.int8); bs = np.empty((T, nb * 16), np.int16)
+    lib().orc_quantize_rows_q8_k(_p(rows), T, n, _p(d), _p(qs), _p(bs), threads)
+    return d, qs, bs
 
 
 def get_scale_min_k4(j: int, scales) -> tuple:

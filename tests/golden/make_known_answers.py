@@ -121,6 +121,22 @@ cases["f16_row"] = {"cite": "src/quant/mod.rs:187-196",
 cases["bf16_row"] = {"cite": "src/quant/mod.rs:198-205", "data": [0x80, 0x3F, 0x00, 0xC0], "n": 2,
                      "expected": [1.0, -2.0], "tol": 1e-3}
 
+# src/quant/q8_k.rs:97-139  quantize_row_q8_k: the four test inputs (as f32 bit patterns) and what each test asserts
+def f32_bits(a) -> list:
+    return [int(v) for v in np.asarray(a, dtype=np.float32).view(np.uint32)]
+
+
+cases["q8_k_roundtrip_error"] = {
+    "cite": "src/quant/q8_k.rs:97-109", "x_bits": f32_bits((np.arange(256, dtype=np.float32) - np.float32(128.0)) * np.float32(0.1)),
+    "n_blocks": 1, "dequant_abs_err_below": 0.15}
+cases["q8_k_bsums"] = {
+    "cite": "src/quant/q8_k.rs:111-119", "x_bits": f32_bits(((np.arange(256) % 7).astype(np.float32) - np.float32(3.0)) * np.float32(0.3)),
+    "bsums_are_group_sums": True}
+cases["q8_k_all_zero"] = {"cite": "src/quant/q8_k.rs:121-127", "x_bits": f32_bits(np.zeros(256)), "d": [0.0], "qs_all": 0}
+cases["q8_k_partial_block"] = {
+    "cite": "src/quant/q8_k.rs:129-139", "x_bits": f32_bits(np.arange(100, dtype=np.float32) * np.float32(0.01)),
+    "n": 100, "n_blocks": 1, "qs_len": 256, "bsums_len": 16}
+
 # src/model/llama/cpu_path.rs:1034-1060  compute_rope_freq_scale
 cases["rope_freq_scale"] = {
     "cite": "src/model/llama/cpu_path.rs:1034-1060",

@@ -114,6 +114,32 @@ def dequant_q6_k(data: np.ndarray, n: int) -> np.ndarray:
     return (ds * q.astype(np.float32)).astype(np.float32).reshape(-1)[:n]
 
 
+def quantize_rows_q8_k(x: np.ndarray):
+    """Second statement of quantize_row_q8_k (src/quant/q8_k.rs:49-92), vectorised over rows and blocks:
+    x [T, n] f32 -> (d [T, nb], qs [T, nb*256] i8, bsums [T, nb*16] i16)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    T, n = x.shape
+    nb = (n + 255) // 256
+    xp = np.zeros((T, nb * 256), np.float32); xp[:, :n] = x
+    valid = np.zeros((T, nb * 256), bool); valid[:, :n] = True
+    xb, vb = xp.reshape(T, nb, 256), valid.reshape(T, nb, 256)
+    av = np.where(vb & ~np.isnan(xb), np.abs(xb), np.float32(0.0))  # NaN never passes `av > amax`
+    first = np.argmax(av, axis=2)  # first index of the largest magnitude, like the strict `>` scan
+    amax = np.take_along_axis(av, first[..., None], 2)[..., 0]
+    mx = np.take_along_axis(xb, first[..., None], 2)[..., 0]
+    with np.errstate(all="ignore"):
+        iscale = np.where(amax > 0, np.float32(-127.0) / np.where(amax > 0, mx, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+        prod = (iscale[..., None] * xb).astype(np.float32)
+        r = np.where(prod >= 0, np.floor(prod + np.float32(0.5)), np.ceil(prod - np.float32(0.5)))  # f64 intermediate is exact here
+        # exact round-half-away on the f32 value: |prod| < 2^23 has an exact f64 sum with 0.5
+        r = np.where(np.isnan(prod), 0.0, np.clip(r, -2147483648.0, 2147483647.0)).astype(np.int64)
+        d = np.where(amax > 0, np.float32(1.0) / np.where(amax > 0, iscale, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+    q = (np.minimum(r, 127) & 0xFF).astype(np.uint8).view(np.int8)
+    q = np.where((amax > 0)[..., None] & vb, q, np.int8(0)).astype(np.int8)
+    bs = q.reshape(T, nb, 16, 16).astype(np.int16).sum(axis=3, dtype=np.int16)
+    return d, q.reshape(T, nb * 256), bs.reshape(T, nb * 16)
+
+
 def rms_norm64(x, w, eps):
     x64 = x.astype(np.float64)
     rms = np.sqrt((x64 * x64).mean(axis=-1, keepdims=True) + eps)

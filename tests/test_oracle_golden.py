@@ -148,6 +148,63 @@ def test_random_blocks_match_numpy_statement_bitwise(dtype, fn, blk):
     assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
 
 
+def _bits_f32(bits):
+    return np.array(bits, dtype=np.uint32).view(np.float32)
+
+
+def test_q8_k_reference_tests():  # src/quant/q8_k.rs:97-139
+    c = KA["q8_k_roundtrip_error"]
+    x = _bits_f32(c["x_bits"])
+    d, qs, bs = orc.quantize_rows_q8_k(x[None])
+    assert d.shape == (1, c["n_blocks"])
+    assert np.abs(d[0, 0] * qs[0].astype(np.float32) - x).max() < c["dequant_abs_err_below"]
+    x = _bits_f32(KA["q8_k_bsums"]["x_bits"])
+    d, qs, bs = orc.quantize_rows_q8_k(x[None])
+    assert np.array_equal(bs[0], qs[0].reshape(16, 16).astype(np.int16).sum(axis=1))
+    c = KA["q8_k_all_zero"]
+    d, qs, bs = orc.quantize_rows_q8_k(_bits_f32(c["x_bits"])[None])
+    assert d[0, 0] == c["d"][0] and np.all(qs == c["qs_all"])
+    c = KA["q8_k_partial_block"]
+    x = _bits_f32(c["x_bits"])
+    assert x.size == c["n"]
+    d, qs, bs = orc.quantize_rows_q8_k(x[None])
+    assert d.shape[1] == c["n_blocks"] and qs.shape[1] == c["qs_len"] and bs.shape[1] == c["bsums_len"]
+    assert np.all(qs[0, c["n"]:] == 0)  # "padded block should still be safe to read": zero past n
+
+
+def test_q8_k_hand_values():
+    """One block worked by hand: max magnitude is the NEGATIVE value -4 at index 2 (first of the ties with +4 at
+    index 9) -> iscale = -127 / -4 = 31.75, d = 1 / 31.75; 1.0 -> 31.75 -> 32; 0.5 -> 15.875 -> 16; -4 -> -127;
+    +4 -> 127; -1 -> -32.  Then the same with the positive 4 first, and exact .5 products."""
+    x = np.zeros(256, np.float32)
+    x[0], x[1], x[2], x[9], x[17] = 1.0, 0.5, -4.0, 4.0, -1.0
+    d, qs, bs = orc.quantize_rows_q8_k(x[None])
+    assert d[0, 0] == np.float32(1.0) / np.float32(31.75)
+    assert list(qs[0, [0, 1, 2, 9, 17]]) == [32, 16, -127, 127, -32]
+    assert list(bs[0, :2]) == [32 + 16 - 127 + 127, -32]
+    y = x.copy(); y[2], y[9] = 4.0, -4.0  # the positive one first: signs flip, d is negative
+    d2, q2, _ = orc.quantize_rows_q8_k(y[None])
+    assert d2[0, 0] == -d[0, 0] and list(q2[0, [0, 1, 2, 9, 17]]) == [-32, -16, -127, 127, 32]
+    # round half away from zero: iscale = -127 / -127 = 1 -> values k + 0.5 round outwards
+    z = np.zeros(256, np.float32); z[0], z[1], z[2], z[3], z[4] = -127.0, 0.5, 1.5, -0.5, -2.5
+    _, q3, _ = orc.quantize_rows_q8_k(z[None])
+    assert list(q3[0, :5]) == [-127, 1, 2, -1, -3]
+
+
+def test_q8_k_matches_numpy_statement_bitwise():
+    rng = np.random.default_rng(815)
+    for n in (256, 100, 1000, 3584, 257):
+        x = (rng.standard_normal((9, n)) * rng.choice([1e-3, 1.0, 50.0], size=(9, 1))).astype(np.float32)
+        x[1, : min(n, 256)] = 0.0  # an all-zero block
+        x[2, 3] = np.nan; x[3, 5] = np.inf; x[4, 7] = 1e-41  # NaN skipped by the scan; inf and a subnormal maximum
+        x[5, :] = 0.0; x[5, 7] = 1e-41  # subnormal maximum alone: iscale overflows to -inf
+        got = orc.quantize_rows_q8_k(x)
+        want = rn.quantize_rows_q8_k(x)
+        assert np.array_equal(got[0].view(np.uint32), want[0].view(np.uint32)), n
+        assert np.array_equal(got[1], want[1]), n
+        assert np.array_equal(got[2], want[2]), n
+
+
 def test_type_sizes():  # src/types.rs:88-168
     assert orc.type_size(orc.Q8_0, 2048) == 2176
     assert orc.type_size(orc.Q4_K, 3584) == 2016
