@@ -83,6 +83,11 @@ SIGNATURES = {
     "agn_silu_mul_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32]),
     "agn_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
     "agn_add_residual_rms_norm_f32_out16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
+    "agn_q8_k_blocks": (_i64, [_i64]),
+    "agn_quantize_rows_q8_k_f32": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "agn_rms_norm_q8_k_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "agn_add_residual_rms_norm_q8_k_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "agn_silu_mul_q8_k_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "agn_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_add_residual_rms_norm_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "agn_rope_qk_f16": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _i32, _f32, _f32, _i32]),

@@ -416,6 +416,38 @@ class CudaBackend:
                                                                   _ptr(normed), T, H, eps, out_dtype))
         return new_x, normed
 
+    # -- Q8_K activation rows (quantize_row_q8_k, src/quant/q8_k.rs:49-92): (d, qs, bsums) device buffers -----
+    def _q8k_outputs(self, T: int, n: int, out):
+        nb = int(self._lib.agn_q8_k_blocks(n))
+        return out if out is not None else (self.empty(4 * T * nb), self.empty(256 * T * nb), self.empty(32 * T * nb))
+
+    def launch_quantize_rows_q8_k(self, x, T: int, n: int, out=None):
+        """T rows of n f32 values -> d [T, nb] f32, qs [T, nb*256] i8, bsums [T, nb*16] i16, nb = ceil(n / 256)."""
+        d, qs, bs = self._q8k_outputs(T, n, out)
+        self._check(self._lib.agn_quantize_rows_q8_k_f32(self._ctx, _ptr(x), T, n, _ptr(d), _ptr(qs), _ptr(bs)))
+        return d, qs, bs
+
+    def launch_rms_norm_q8_k(self, x, w, T: int, H: int, eps: float, out=None):
+        """RMSNorm with the Q8_K quantiser fused on: the normed f32 row is never written."""
+        d, qs, bs = self._q8k_outputs(T, H, out)
+        self._check(self._lib.agn_rms_norm_q8_k_f32(self._ctx, _ptr(x), _ptr(w), T, H, eps, _ptr(d), _ptr(qs), _ptr(bs)))
+        return d, qs, bs
+
+    def launch_add_residual_rms_norm_q8_k(self, x, delta, w, T: int, H: int, eps: float, new_x=None, out=None):
+        """new_x = x + delta stays f32; the normed row leaves as Q8_K blocks."""
+        if new_x is None:
+            new_x = self.empty(4 * T * H)
+        d, qs, bs = self._q8k_outputs(T, H, out)
+        self._check(self._lib.agn_add_residual_rms_norm_q8_k_f32(self._ctx, _ptr(x), _ptr(delta), _ptr(w), _ptr(new_x), T, H,
+                                                                 eps, _ptr(d), _ptr(qs), _ptr(bs)))
+        return new_x, (d, qs, bs)
+
+    def launch_silu_mul_q8_k(self, gate, up, T: int, I: int, out=None):
+        """silu(gate) * up over [T, I] rows, stored as Q8_K blocks (the input of a Q5_K down projection)."""
+        d, qs, bs = self._q8k_outputs(T, I, out)
+        self._check(self._lib.agn_silu_mul_q8_k_f32(self._ctx, _ptr(gate), _ptr(up), T, I, _ptr(d), _ptr(qs), _ptr(bs)))
+        return d, qs, bs
+
     def launch_add_residual_rms_norm_f16(self, x, delta, w, T: int, H: int, eps: float, new_x=None, normed=None):
         if new_x is None:
             new_x = self.empty(2 * T * H)

@@ -19,33 +19,13 @@
 // current one, every SM gets the same number of rows to within one, and the per-CTA set-up
 // (weight vector, barriers) is paid once per CTA instead of once per row.
 #include "agn_common.cuh"
+#include "agn_row_math.cuh"
 
 namespace {
-
-// Sum over the CTA; every thread returns the same value.
-__device__ __forceinline__ float block_sum(float v, float *smem) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nwarps = (blockDim.x + 31) >> 5;
-    v = agn_warp_sum(v);
-    if (lane == 0) smem[warp] = v;
-    __syncthreads();
-    float total = 0.0f;
-    for (int w = 0; w < nwarps; w++) total += smem[w];
-    __syncthreads();  // smem is reused by the next call
-    return total;
-}
 
 // (The sum of squares runs on fused multiply-adds, two per instruction (agn_sum_sq4): one rounding
 // each; the reference's separate multiply and add differ from it by less than the reordering of
 // the sum already does.)
-
-// 1 / sqrt(ss / n + eps), the factor every element of the row is multiplied by.  Evaluated as
-// rsqrt(ss * (1/n) + eps) with the hardware reciprocal square root (2 ulp): three instructions
-// instead of the ~45 of two IEEE divisions and a square root, which every thread of the CTA would
-// run while the row's stores wait.  Together with the multiplication by 1/n this moves a result
-// by a few 1e-7 relative, inside the 1e-5 tolerance; infinities, zeros and NaN come out as they
-// do from the exact sequence (rsqrt(inf) = 0, rsqrt(0) = inf).
-__device__ __forceinline__ float inv_rms(float ss, float inv_n, float eps) { return rsqrtf(__fmaf_rn(ss, inv_n, eps)); }
 
 // T: storage type of x, delta and new_x; OT: storage type of the normed output (T, or a 16-bit
 // type for a row that feeds a matmul with half-precision operands).
@@ -85,9 +65,9 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
     float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int k = 0; k < VPT; k++) ss2 = agn_sum_sq4(v[k], ss2);
-    float ss = block_sum(ss2.x + ss2.y, red);
+    float ss = agn_block_sum(ss2.x + ss2.y, red);
     const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps (used by the dividing arm)
-    const float inv = inv_rms(ss, inv_n, eps);
+    const float inv = agn_inv_rms(ss, inv_n, eps);
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
         const int i = threadIdx.x + k * blockDim.x;
@@ -209,7 +189,7 @@ rms_norm_ring_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
         if (threadIdx.x == 0 && it + slots < n_my) issue(it + slots);
         float total = 0.0f;
         for (int wi = 0; wi < nwarps; wi++) total += r2[wi];
-        const float inv = inv_rms(total, inv_n, eps);
+        const float inv = agn_inv_rms(total, inv_n, eps);
 #pragma unroll
         for (int k = 0; k < VPT; k++) {
             const int i = threadIdx.x + k * blockDim.x;
@@ -274,8 +254,8 @@ rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delt
         }
         ss += v * v;
     }
-    ss = block_sum(ss, red);
-    const float inv = inv_rms(ss, 1.0f / (float)H, eps);
+    ss = agn_block_sum(ss, red);
+    const float inv = agn_inv_rms(ss, 1.0f / (float)H, eps);
     const T *src = RESIDUAL ? new_x : x;
     for (int64_t i = threadIdx.x; i < H; i += blockDim.x)
         ActVec<OT>::store1(out, row + i, w[i] * ActVec<T>::load1(src, row + i) * inv);
@@ -309,17 +289,8 @@ int32_t rms_norm_dispatch(agn_ctx *ctx, const T *x, const T *delta, const float 
                         (!RESIDUAL || (agn_aligned(delta, A) && agn_aligned(new_x, A))) && H <= 32768;
     if (vec_ok) {
         const int n4 = (int)(H / 4);
-        // Pick the smallest VPT in {1,2,4,8} that keeps the CTA at <= 256 threads when
-        // possible: more rows resident per SM and more loads in flight per thread.
-        int vpt = 1;
-        while (vpt < 8 && (n4 + vpt - 1) / vpt > 256) vpt *= 2;
-        if (ctx->tune_rms_vpt == 1 || ctx->tune_rms_vpt == 2 || ctx->tune_rms_vpt == 4 || ctx->tune_rms_vpt == 8) {
-            vpt = ctx->tune_rms_vpt;
-            while (vpt < 8 && (n4 + vpt - 1) / vpt > 1024) vpt *= 2;
-        }
-        int threads = (n4 + vpt - 1) / vpt;
-        threads = ((threads + 31) / 32) * 32;
-        if (threads > 1024) threads = 1024;
+        int vpt, threads;
+        agn_rms_shape(ctx, n4, &vpt, &threads);
         bool ring;
         switch (vpt) {
         case 1: ring = launch_vec<T, OT, 1, RESIDUAL>(ctx, x, delta, w, new_x, out, T_rows, n4, eps, threads); break;

@@ -5,23 +5,9 @@
 // instructions: bound by HBM, so the kernel is nothing but 128-bit streaming loads with
 // several of them in flight per thread, and 128-bit streaming stores.
 #include "agn_common.cuh"
+#include "agn_row_math.cuh"
 
 namespace {
-
-__device__ __forceinline__ float silu_mul1(float g, float u) {
-    // IEEE division (-prec-div=true is nvcc's default; no fast-math anywhere).
-    const float silu = g / (1.0f + expf(-g));
-    return silu * u;
-}
-
-__device__ __forceinline__ float4 silu_mul4(float4 g, float4 u) {
-    float4 o;
-    o.x = silu_mul1(g.x, u.x);
-    o.y = silu_mul1(g.y, u.y);
-    o.z = silu_mul1(g.z, u.z);
-    o.w = silu_mul1(g.w, u.w);
-    return o;
-}
 
 // Each CTA owns a contiguous tile of UNROLL * blockDim vectors of four activations; a thread
 // issues all of its 2*UNROLL loads before the first use so that UNROLL*32 B (f32) per thread
@@ -45,7 +31,7 @@ silu_mul_vec4_kernel(const T *__restrict__ gate, const T *__restrict__ up, OT *_
 #pragma unroll
     for (int k = 0; k < UNROLL; k++) {
         const int64_t i = tile + k * blockDim.x + threadIdx.x;
-        if (i < n4) ActVec<OT>::store(out, i, silu_mul4(g[k], u[k]));
+        if (i < n4) ActVec<OT>::store(out, i, agn_silu_mul4(g[k], u[k]));
     }
 }
 
@@ -97,7 +83,7 @@ __global__ void silu_mul_scalar_kernel(const T *__restrict__ gate, const T *__re
                                        int64_t begin, int64_t n) {
     agn_pdl_prologue();
     const int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) ActVec<OT>::store1(out, i, silu_mul1(ActVec<T>::load1(gate, i), ActVec<T>::load1(up, i)));
+    if (i < n) ActVec<OT>::store1(out, i, agn_silu_mul1(ActVec<T>::load1(gate, i), ActVec<T>::load1(up, i)));
 }
 
 template <typename T, typename OT>

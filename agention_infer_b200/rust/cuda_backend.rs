@@ -29,6 +29,15 @@ impl Drop for DevBuf {
     }
 }
 
+/// Device-resident `Q8KRow`s (src/quant/q8_k.rs:27-37) of `t` rows: per row `ceil(n / 256)` scales, 256 times as
+/// many quantised values (zero past `n`) and 16 times as many group sums.
+pub struct Q8KRows {
+    pub d: DevBuf,
+    pub qs: DevBuf,
+    pub bsums: DevBuf,
+    pub n: usize,
+}
+
 /// A recorded chain of ops (`agn_graph_begin` .. `agn_graph_end`), replayed with one launch.
 pub struct OpGraph {
     ctx: *mut AgnCtx,
@@ -169,6 +178,56 @@ impl CudaBackend {
                                                 h as i64, eps, out_dtype)
         })?;
         Ok((new_x, normed))
+    }
+
+    /// `quantize_row_q8_k` (src/quant/q8_k.rs:49-92) over `t` rows of `n` values already on the device:
+    /// the `Q8KRow` arrays (`d` f32, `qs` i8, `bsums` i16) for `ceil(n / 256)` blocks per row.
+    pub fn launch_quantize_rows_q8_k(&self, x: &DevBuf, t: usize, n: usize) -> Result<Q8KRows> {
+        let out = self.q8k_rows(t, n)?;
+        self.check(unsafe {
+            agn_quantize_rows_q8_k_f32(self.ctx, x.ptr as *const f32, t as i64, n as i64, out.d.ptr as *mut f32,
+                                       out.qs.ptr as *mut i8, out.bsums.ptr as *mut i16)
+        })?;
+        Ok(out)
+    }
+
+    /// `launch_rms_norm` with the quantiser of `matmul_into` (src/model/mod.rs:381-386) fused on: the input of a
+    /// Q5_K projection without the f32 row in between.
+    pub fn launch_rms_norm_q8_k(&self, x: &DevBuf, w: &DevBuf, t: usize, h: usize, eps: f32) -> Result<Q8KRows> {
+        let out = self.q8k_rows(t, h)?;
+        self.check(unsafe {
+            agn_rms_norm_q8_k_f32(self.ctx, x.ptr as *const f32, w.ptr as *const f32, t as i64, h as i64, eps,
+                                  out.d.ptr as *mut f32, out.qs.ptr as *mut i8, out.bsums.ptr as *mut i16)
+        })?;
+        Ok(out)
+    }
+
+    /// `launch_add_residual_rms_norm` whose normed row leaves as Q8_K blocks; `new_x` stays f32.
+    pub fn launch_add_residual_rms_norm_q8_k(&self, x: &DevBuf, delta: &DevBuf, w: &DevBuf, t: usize, h: usize,
+                                             eps: f32) -> Result<(DevBuf, Q8KRows)> {
+        let new_x = self.empty(4 * t * h)?;
+        let out = self.q8k_rows(t, h)?;
+        self.check(unsafe {
+            agn_add_residual_rms_norm_q8_k_f32(self.ctx, x.ptr as *const f32, delta.ptr as *const f32, w.ptr as *const f32,
+                                               new_x.ptr as *mut f32, t as i64, h as i64, eps, out.d.ptr as *mut f32,
+                                               out.qs.ptr as *mut i8, out.bsums.ptr as *mut i16)
+        })?;
+        Ok((new_x, out))
+    }
+
+    /// `launch_silu_mul` over `[t, i]` rows whose product leaves as Q8_K blocks (input of a Q5_K down projection).
+    pub fn launch_silu_mul_q8_k(&self, gate: &DevBuf, up: &DevBuf, t: usize, i: usize) -> Result<Q8KRows> {
+        let out = self.q8k_rows(t, i)?;
+        self.check(unsafe {
+            agn_silu_mul_q8_k_f32(self.ctx, gate.ptr as *const f32, up.ptr as *const f32, t as i64, i as i64,
+                                  out.d.ptr as *mut f32, out.qs.ptr as *mut i8, out.bsums.ptr as *mut i16)
+        })?;
+        Ok(out)
+    }
+
+    fn q8k_rows(&self, t: usize, n: usize) -> Result<Q8KRows> {
+        let nb = unsafe { agn_q8_k_blocks(n as i64) } as usize;
+        Ok(Q8KRows { d: self.empty(4 * t * nb)?, qs: self.empty(256 * t * nb)?, bsums: self.empty(32 * t * nb)?, n })
     }
 
     /// `launch_rope(handle, n_heads, head_dim, n_rot, pos, theta)` in place (resident.rs:326-353)

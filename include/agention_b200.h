@@ -380,6 +380,36 @@ AGN_API int32_t agn_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float
 AGN_API int32_t agn_add_residual_rms_norm_f32_out16(agn_ctx *ctx, const float *x, const float *delta,
                                                     const float *w, float *new_x, void *normed,
                                                     int64_t T, int64_t H, float eps, int32_t out_dtype);
+
+/* ---- Q8_K activation rows: the input of the int8 dot products -------------------------------
+ * quantize_row_q8_k (src/quant/q8_k.rs:49-92), which WeightMap::matmul_into applies to the
+ * activation vector in front of a Q5_K tensor (src/model/mod.rs:381-386), over T rows of n values.
+ * Per block of 256 values (the last block of a row zero-padded): max = the value of largest
+ * magnitude (the first one on ties, NaN never), iscale = -127 / max, d = 1 / iscale,
+ * q = min(round_half_away(iscale * v) as i32, 127) as i8, bsums[g] = the sum of q over group g of
+ * 16; a block without a magnitude above 0 is d = 0, q = 0.  Outputs are the parallel arrays of
+ * `Q8KRow` (:27-37), row after row, with nb = agn_q8_k_blocks(n) = ceil(n / 256):
+ *   d [T, nb] f32 ; qs [T, nb * 256] int8 ; bsums [T, nb * 16] int16
+ * (d and qs 4-byte aligned, bsums 2-byte aligned, else AGN_EINVAL).  Bit-exact against the
+ * reference's arithmetic for every input, NaN and infinities included. */
+AGN_API int64_t agn_q8_k_blocks(int64_t n);
+AGN_API int32_t agn_quantize_rows_q8_k_f32(agn_ctx *ctx, const float *x, int64_t T, int64_t n, float *d,
+                                           int8_t *qs, int16_t *bsums);
+/* The producers of a matmul's input with the quantiser fused on, so that the f32 row is never
+ * written: RMSNorm (agn_rms_norm_f32's arguments), residual add + RMSNorm (new_x, the residual
+ * stream, is still written as f32) and SiLU·mul over [T, I] rows.  Every output byte equals
+ * agn_quantize_rows_q8_k_f32 applied to the f32 result of the unfused entry point (with the
+ * context's default options).  H and I must be multiples of 256 — a Q5_K weight row is a whole
+ * number of 256-value blocks — and H <= 32768; x, delta, new_x, w, gate, up 16-byte aligned;
+ * otherwise AGN_EINVAL.  No counterpart in the reference, which normalises into an f32 vector
+ * and quantises it inside matmul_into. */
+AGN_API int32_t agn_rms_norm_q8_k_f32(agn_ctx *ctx, const float *x, const float *w, int64_t T, int64_t H,
+                                      float eps, float *d, int8_t *qs, int16_t *bsums);
+AGN_API int32_t agn_add_residual_rms_norm_q8_k_f32(agn_ctx *ctx, const float *x, const float *delta,
+                                                   const float *w, float *new_x, int64_t T, int64_t H,
+                                                   float eps, float *d, int8_t *qs, int16_t *bsums);
+AGN_API int32_t agn_silu_mul_q8_k_f32(agn_ctx *ctx, const float *gate, const float *up, int64_t T,
+                                      int64_t I, float *d, int8_t *qs, int16_t *bsums);
 AGN_API int32_t agn_rope_qk_f16(agn_ctx *ctx, void *q, void *k, int64_t T, int32_t n_q_heads,
                                 int32_t n_kv_heads, int32_t head_dim, int32_t n_rot,
                                 const int32_t *pos, int32_t pos_start, float theta, float freq_scale,

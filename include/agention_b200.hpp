@@ -186,6 +186,38 @@ class CudaBackend {
                                                   out_dtype));
         return {std::move(new_x), std::move(normed)};
     }
+    // ---- Q8_K activation rows (quantize_row_q8_k, src/quant/q8_k.rs:49-92): d f32, qs i8, bsums i16 per row
+    struct Q8KRows {
+        DeviceBuffer d, qs, bsums;
+    };
+    Q8KRows launch_quantize_rows_q8_k(const float *x, int64_t T, int64_t n) {
+        Q8KRows r = q8k_rows(T, n);
+        check(agn_quantize_rows_q8_k_f32(ctx_, x, T, n, static_cast<float *>(r.d.ptr()), static_cast<int8_t *>(r.qs.ptr()),
+                                         static_cast<int16_t *>(r.bsums.ptr())));
+        return r;
+    }
+    // the producers of a Q5_K matmul's input with the quantiser fused on (no f32 row in between)
+    Q8KRows launch_rms_norm_q8_k(const float *x, const float *w, int64_t T, int64_t H, float eps) {
+        Q8KRows r = q8k_rows(T, H);
+        check(agn_rms_norm_q8_k_f32(ctx_, x, w, T, H, eps, static_cast<float *>(r.d.ptr()), static_cast<int8_t *>(r.qs.ptr()),
+                                    static_cast<int16_t *>(r.bsums.ptr())));
+        return r;
+    }
+    std::pair<DeviceBuffer, Q8KRows> launch_add_residual_rms_norm_q8_k(const float *x, const float *delta, const float *w,
+                                                                       int64_t T, int64_t H, float eps) {
+        DeviceBuffer new_x = empty(4 * (size_t)(T * H));
+        Q8KRows r = q8k_rows(T, H);
+        check(agn_add_residual_rms_norm_q8_k_f32(ctx_, x, delta, w, static_cast<float *>(new_x.ptr()), T, H, eps,
+                                                 static_cast<float *>(r.d.ptr()), static_cast<int8_t *>(r.qs.ptr()),
+                                                 static_cast<int16_t *>(r.bsums.ptr())));
+        return {std::move(new_x), std::move(r)};
+    }
+    Q8KRows launch_silu_mul_q8_k(const float *gate, const float *up, int64_t T, int64_t I) {
+        Q8KRows r = q8k_rows(T, I);
+        check(agn_silu_mul_q8_k_f32(ctx_, gate, up, T, I, static_cast<float *>(r.d.ptr()), static_cast<int8_t *>(r.qs.ptr()),
+                                    static_cast<int16_t *>(r.bsums.ptr())));
+        return r;
+    }
     // softmax of scale * scores; sums != nullptr: unnormalised weights + row sums
     void launch_softmax_rows_scaled(const float *in, float *out, float *sums, int64_t n_rows, int64_t row_len, int64_t row_stride,
                                     const int32_t *n_valid, int causal_period, int causal_offset, float scale) {
@@ -257,6 +289,10 @@ class CudaBackend {
     }
 
   private:
+    Q8KRows q8k_rows(int64_t T, int64_t n) {
+        const size_t nb = (size_t)agn_q8_k_blocks(n) * (size_t)T;
+        return Q8KRows{empty(4 * nb), empty(256 * nb), empty(32 * nb)};
+    }
     agn_ctx *ctx_ = nullptr;
 };
 

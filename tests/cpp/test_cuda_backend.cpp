@@ -197,6 +197,27 @@ int main() {
         }
         expect(worst <= 1e-5 && tail_kept && !be.last_kernel().empty(), "softmax_rows_valid", worst);
     }
+    {  // Q8_K activation rows: the standalone quantiser is the oracle's bytes; the fused norm equals the two launches
+        const int T = 9, H = 1024, nb = H / 256;
+        auto x = randn((size_t)T * H), w = weight(H);
+        x[5] = 3.0f; x[9] = -3.0f;  // a tie in magnitude inside the first block
+        std::vector<float> rd((size_t)T * nb);
+        std::vector<int8_t> rq((size_t)T * H);
+        std::vector<int16_t> rb((size_t)T * nb * 16);
+        orc_quantize_rows_q8_k(x.data(), T, H, rd.data(), rq.data(), rb.data(), 1);
+        auto dx = be.upload(x), dw = be.upload(w);
+        auto q = be.launch_quantize_rows_q8_k(dx.as<float>(), T, H);
+        bool same = be.read<float>(q.d, rd.size()) == rd && be.read<int8_t>(q.qs, rq.size()) == rq &&
+                    be.read<int16_t>(q.bsums, rb.size()) == rb;
+        expect(same, "launch_quantize_rows_q8_k bit-exact");
+        auto normed = be.launch_rms_norm(dx.as<float>(), dw.as<float>(), T, H, 1e-6f);
+        auto two = be.launch_quantize_rows_q8_k(normed.as<float>(), T, H);
+        auto fused = be.launch_rms_norm_q8_k(dx.as<float>(), dw.as<float>(), T, H, 1e-6f);
+        same = be.read<float>(two.d, rd.size()) == be.read<float>(fused.d, rd.size()) &&
+               be.read<int8_t>(two.qs, rq.size()) == be.read<int8_t>(fused.qs, rq.size()) &&
+               be.read<int16_t>(two.bsums, rb.size()) == be.read<int16_t>(fused.bsums, rb.size());
+        expect(same, "launch_rms_norm_q8_k equals rms_norm then quantize");
+    }
     {  // error behaviour: bad argument -> status + message, context still usable
         bool threw = false;
         auto d = be.empty(512);
