@@ -57,6 +57,7 @@ struct agn_ctx {
     int tune_moe_small_sort;    // 1 = up to 4096 (token, slot) pairs are sorted by one CTA in one launch (default)
     int tune_softmax_cluster;   // rows of 16K-128K entries: 1 = one thread-block cluster per row, CTAs of <= 512 threads
                                 // (default); 2 = CTAs of <= 256 threads; 0 = no clusters
+    int tune_rms_q8k_bpw;         // RMSNorm -> Q8_K: blocks of 256 values per warp (1, 2, 4); 0 = by row length
     int tune_softmax_causal_pair; // 1 (default): square causal matrices pair rows i and L-1-i in one CTA
     int tune_softmax_warp16;    // 1: rows of 1025-2048 entries run one warp per row (16 float4 per lane); 0: one CTA per row
     int tune_softmax_vpt;       // 0 = automatic (8 float4 per thread in the CTA-per-row kernel)

@@ -69,6 +69,7 @@ int32_t agn_ctx_create(int32_t device, agn_ctx **out) {
     ctx->tune_softmax_cluster = 1;
     ctx->tune_softmax_warp16 = 0;
     ctx->tune_softmax_causal_pair = 1;
+    ctx->tune_rms_q8k_bpw = 0;
     ctx->tune_moe_small_sort = 1;
     ctx->tune_get_rows_tma = 1;
     ctx->tune_silu_unroll = 4;
@@ -202,6 +203,7 @@ int32_t agn_ctx_set_option(agn_ctx *ctx, const char *name, int64_t value) {
             {"ring_force", &ctx->tune_ring_force, 0, 1},
             {"softmax_warp16", &ctx->tune_softmax_warp16, 0, 1},
             {"softmax_causal_pair", &ctx->tune_softmax_causal_pair, 0, 1},
+            {"rms_q8k_bpw", &ctx->tune_rms_q8k_bpw, 0, 4},
             {"silu_small", &ctx->tune_silu_small, 0, 1},
             {"kv_multi", &ctx->tune_kv_multi, 0, 1},
             {"host_chunk_bytes", &ctx->tune_host_chunk_bytes, 0, 24 << 20},

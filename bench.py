@@ -554,6 +554,20 @@ def run_ours(args, cfg, ops_list, wl):
         extras[f"softmax_causal_leave_tail_{nq}x{Ls}x{Ls}"] = (
             lambda b: be.launch_softmax_rows_valid(b["sc"], nq * Ls, Ls, b["pr"], causal_period=Ls),
             8 * (nq * Ls * (Ls + 1) // 2))
+        if H % 256 == 0 and I % 256 == 0:
+            # Q8_K activation rows (the input of a Q5_K matmul): 4 B read, 1 B + 36 B / 256 written per value
+            nq8 = max(T * H, R * I)
+            for b_ in ex_sets:
+                b_["q8"] = (torch.empty(nq8 // 256, device=dev), torch.empty(nq8, dtype=torch.int8, device=dev),
+                            torch.empty(nq8 // 16, dtype=torch.int16, device=dev))
+            q8_out = lambda n: n + 36 * (n // 256)
+            extras["quantize_rows_q8_k"] = (lambda b: be.launch_quantize_rows_q8_k(b["x"], T, H, out=b["q8"]), 4 * T * H + q8_out(T * H))
+            extras["rms_norm_q8_k"] = (lambda b: be.launch_rms_norm_q8_k(b["x"], w, T, H, cfg.eps, out=b["q8"]),
+                                       4 * T * H + 4 * H + q8_out(T * H))
+            extras["add_residual_rms_norm_q8_k"] = (
+                lambda b: be.launch_add_residual_rms_norm_q8_k(b["x"], b["d"], w, T, H, cfg.eps, new_x=b["nx"], out=b["q8"]),
+                12 * T * H + 4 * H + q8_out(T * H))
+            extras["silu_mul_q8_k"] = (lambda b: be.launch_silu_mul_q8_k(b["g"], b["u"], R, I, out=b["q8"]), 8 * R * I + q8_out(R * I))
         for name, (fn, nbytes) in extras.items():
             for i in range(4):
                 fn(ex_sets[i % nsets])

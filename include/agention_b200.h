@@ -105,7 +105,8 @@ AGN_API int32_t agn_ctx_get_stream(agn_ctx *ctx, void **cuda_stream);
  * (1: bulk-copy staging, 0: cp.async), "get_rows_threads" (32..256; 0 = automatic), "moe_small_sort"
  * (1: up to 4096 (token, slot) pairs are sorted by one CTA in one launch, 0: always the three-kernel
  * counting sort), "host_slots" (2..16 staging slots of the host-slice ops, read when their ring is created;
- * 0 = 8), "host_chunk_bytes" (bytes of one staging chunk; 0 = a whole 24 MiB slot).
+ * 0 = 8), "host_chunk_bytes" (bytes of one staging chunk; 0 = a whole 24 MiB slot), "rms_q8k_bpw" (blocks
+ * of 256 values a warp owns in the fused norm -> Q8_K kernels: 1, 2, 4; 0 = by row length).
  * Persistent kernels that stage rows through a shared-memory ring with bulk asynchronous copies (off by
  * default: the CTA-per-row kernels measured faster on B200): "rms_ring", "rope_ring", "get_rows_ring",
  * "softmax_ring" = 0 (never), 1 (a ring of the default depth for batches large enough to keep it busy) or
@@ -397,9 +398,11 @@ AGN_API int32_t agn_quantize_rows_q8_k_f32(agn_ctx *ctx, const float *x, int64_t
                                            int8_t *qs, int16_t *bsums);
 /* The producers of a matmul's input with the quantiser fused on, so that the f32 row is never
  * written: RMSNorm (agn_rms_norm_f32's arguments), residual add + RMSNorm (new_x, the residual
- * stream, is still written as f32) and SiLU·mul over [T, I] rows.  Every output byte equals
- * agn_quantize_rows_q8_k_f32 applied to the f32 result of the unfused entry point (with the
- * context's default options).  H and I must be multiples of 256 — a Q5_K weight row is a whole
+ * stream, is still written as f32) and SiLU·mul over [T, I] rows.  agn_silu_mul_q8_k_f32 equals
+ * agn_quantize_rows_q8_k_f32 applied to agn_silu_mul_f32's result byte for byte; the two norms sum
+ * the squares in another order than agn_rms_norm_f32, so their scale factor can differ from its
+ * in the last bit, d by as much, and a q by one step in about one position in a thousand.  H and I
+ * must be multiples of 256 — a Q5_K weight row is a whole
  * number of 256-value blocks — and H <= 32768; x, delta, new_x, w, gate, up 16-byte aligned;
  * otherwise AGN_EINVAL.  No counterpart in the reference, which normalises into an f32 vector
  * and quantises it inside matmul_into. */

@@ -5,11 +5,13 @@ bar is the oracle's bytes exactly: d as bit patterns, qs and bsums as integers, 
 ragged rows (zero-padded last block), unaligned rows, and the values where implementations differ
 (ties between +a and -a, products that end in .5, NaN, infinities, a subnormal maximum).
 
-The fused forms (RMSNorm / residual add + RMSNorm / SiLU·mul with the quantiser on the end) compute
-their f32 value with the same instructions as the unfused kernel, so they must equal
-`quantize(unfused f32 output)` byte for byte; against the oracle's own chain (whose f32 values
-differ from the GPU's by up to 1e-5 of the row scale) d agrees to 1e-5 relative, and a q differs by
-at most one step, in a small fraction of the positions."""
+SiLU·mul with the quantiser on the end computes its f32 value with the same function as the unfused
+kernel, so it must equal `quantize(unfused f32 output)` byte for byte.  The fused norms hold a row
+in another thread mapping than the f32 norm kernel (a warp owns whole blocks), so the sum of
+squares is added in another order: against `quantize(GPU f32 norm)` and against the oracle's own
+chain (whose f32 values differ from the GPU's by up to 1e-5 of the row scale) d agrees to 1e-5
+relative, a q differs by at most one step in a small fraction of the positions, and bsums are
+exactly the group sums of the qs that were written."""
 import json
 from pathlib import Path
 
@@ -130,26 +132,31 @@ def q8k_close_to_chain(got, want, what):
     assert np.array_equal(bs, qs.reshape(qs.shape[0], -1, 16).astype(np.int16).sum(axis=2)), what
 
 
+@pytest.mark.parametrize("bpw", [0, 1, 4])
 @pytest.mark.parametrize("T,H", [(512, 2048), (300, 3584), (64, 4096), (9, 256), (5, 8192), (3, 12288), (2, 32768), (1, 3584)])
-def test_rms_norm_q8_k_equals_the_two_launches(backend, T, H):
+def test_rms_norm_q8_k(backend, T, H, bpw):
     x, w = synth.activations(2, "x", (T, H)), synth.norm_weight(2, "w", H)
     dx, dw = backend.upload(x), backend.upload(w)
     normed = backend.launch_rms_norm(dx, dw, T, H, 1e-6)
     two = read_q8k(backend, backend.launch_quantize_rows_q8_k(normed, T, H), T, H)
-    fused = read_q8k(backend, backend.launch_rms_norm_q8_k(dx, dw, T, H, 1e-6), T, H)
+    backend.set_option("rms_q8k_bpw", bpw)  # blocks per warp: by row length (0), or forced
+    try:
+        fused = read_q8k(backend, backend.launch_rms_norm_q8_k(dx, dw, T, H, 1e-6), T, H)
+    finally:
+        backend.set_option("rms_q8k_bpw", 0)
     assert backend.last_kernel == "rms_norm_q8_k"
-    assert_same(fused, two, f"rms_norm_q8_k T={T} H={H}")
+    q8k_close_to_chain(fused, two, f"rms_norm_q8_k T={T} H={H} vs the two launches")
     q8k_close_to_chain(fused, orc.quantize_rows_q8_k(orc.rms_norm_rows(x, w, 1e-6, THREADS), THREADS), "vs oracle chain")
 
 
 @pytest.mark.parametrize("T,H", [(512, 2048), (300, 3584), (7, 4096), (3, 16384)])
-def test_add_residual_rms_norm_q8_k_equals_the_two_launches(backend, T, H):
+def test_add_residual_rms_norm_q8_k(backend, T, H):
     x, dl, w = synth.activations(2, "x", (T, H)), synth.activations(2, "delta", (T, H)), synth.norm_weight(2, "w", H)
     dx, dd, dw = backend.upload(x), backend.upload(dl), backend.upload(w)
     new_x, normed = backend.launch_add_residual_rms_norm(dx, dd, dw, T, H, 1e-5)
     two = read_q8k(backend, backend.launch_quantize_rows_q8_k(normed, T, H), T, H)
     new_x2, bufs = backend.launch_add_residual_rms_norm_q8_k(dx, dd, dw, T, H, 1e-5)
-    assert_same(read_q8k(backend, bufs, T, H), two, f"add_residual_rms_norm_q8_k T={T} H={H}")
+    q8k_close_to_chain(read_q8k(backend, bufs, T, H), two, f"add_residual_rms_norm_q8_k T={T} H={H} vs the two launches")
     a, b = backend.read(new_x, np.float32, (T, H)), backend.read(new_x2, np.float32, (T, H))
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
     assert np.array_equal(a.view(np.uint32), (x + dl).view(np.uint32))  # one f32 addition: exact against numpy
@@ -177,7 +184,10 @@ def test_fused_forms_with_special_values(backend):
     w = synth.norm_weight(2, "w", H)
     dx, dw = backend.upload(x), backend.upload(w)
     two = read_q8k(backend, backend.launch_quantize_rows_q8_k(backend.launch_rms_norm(dx, dw, T, H, 1e-6), T, H), T, H)
-    assert_same(read_q8k(backend, backend.launch_rms_norm_q8_k(dx, dw, T, H, 1e-6), T, H), two, "rms_norm_q8_k special")
+    fused = read_q8k(backend, backend.launch_rms_norm_q8_k(dx, dw, T, H, 1e-6), T, H)
+    finite = [0, 1, 4, 5]  # rows 2 (a NaN) and 3 (an infinity) have a NaN or zero scale factor: every value NaN or 0
+    q8k_close_to_chain(tuple(a[finite] for a in fused), tuple(a[finite] for a in two), "rms_norm_q8_k special")
+    assert_same(tuple(a[[2, 3]] for a in fused), tuple(a[[2, 3]] for a in two), "rms_norm_q8_k NaN / inf rows")
     two = read_q8k(backend, backend.launch_quantize_rows_q8_k(backend.launch_silu_mul(dx, dx, T * H), T, H), T, H)
     assert_same(read_q8k(backend, backend.launch_silu_mul_q8_k(dx, dx, T, H), T, H), two, "silu_mul_q8_k special")
 
