@@ -254,10 +254,19 @@ __device__ __forceinline__ float agn_warp_sum(float v) {
     return v;
 }
 
+// Warp-wide maximum in one instruction (redux.sync.max.f32, sm_100a); a NaN operand is ignored, as
+// fmaxf ignores it.  Every lane of the warp must take part.
 __device__ __forceinline__ float agn_warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+// max(m, x, y, z, w) as two three-input maxima (sm_100); NaN operands are ignored.
+__device__ __forceinline__ float agn_max_acc4(float m, float4 v) {
+    float t;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(t) : "f"(m), "f"(v.x), "f"(v.y));
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(t), "f"(v.z), "f"(v.w));
+    return m;
 }
 
 // Activation storage.  The kernels compute in f32; activations are stored as f32 or, like the

@@ -65,7 +65,7 @@ rms_norm_rows_kernel(const T *__restrict__ x, const T *__restrict__ delta, const
     float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int k = 0; k < VPT; k++) ss2 = agn_sum_sq4(v[k], ss2);
-    float ss = agn_block_sum(ss2.x + ss2.y, red);
+    float ss = agn_block_sum_once(ss2.x + ss2.y, red);
     const float rms = sqrtf(ss / n_f + eps);  // same operations as the reference: sum/n + eps (used by the dividing arm)
     const float inv = agn_inv_rms(ss, inv_n, eps);
 #pragma unroll
@@ -254,7 +254,7 @@ rms_norm_rows_generic_kernel(const T *__restrict__ x, const T *__restrict__ delt
         }
         ss += v * v;
     }
-    ss = agn_block_sum(ss, red);
+    ss = agn_block_sum_once(ss, red);
     const float inv = agn_inv_rms(ss, 1.0f / (float)H, eps);
     const T *src = RESIDUAL ? new_x : x;
     for (int64_t i = threadIdx.x; i < H; i += blockDim.x)

@@ -7,8 +7,9 @@
 #ifdef __CUDACC__
 
 // Sum over the CTA; every thread returns the same value.  Warp shuffles, then across warps
-// through shared memory in a fixed order: the result does not depend on scheduling.
-__device__ __forceinline__ float agn_block_sum(float v, float *smem) {
+// through shared memory in a fixed order: the result does not depend on scheduling.  For a kernel
+// that sums once per CTA: nothing writes smem again, so there is no barrier after the reads.
+__device__ __forceinline__ float agn_block_sum_once(float v, float *smem) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = (blockDim.x + 31) >> 5;
     v = agn_warp_sum(v);
@@ -16,7 +17,6 @@ __device__ __forceinline__ float agn_block_sum(float v, float *smem) {
     __syncthreads();
     float total = 0.0f;
     for (int w = 0; w < nwarps; w++) total += smem[w];
-    __syncthreads();  // smem is reused by the next call
     return total;
 }
 

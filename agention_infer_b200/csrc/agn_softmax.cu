@@ -45,7 +45,6 @@ __device__ __forceinline__ int64_t valid_len(const SoftmaxArgs &a, int64_t r) {
     return nv;
 }
 
-__device__ __forceinline__ float max4(float4 v) { return fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)); }
 
 // Float4 number i of a row whose first nv entries are valid.  The load is one predicated
 // instruction (so that a thread's loads are all issued back to back); mask_tail then sets
@@ -154,7 +153,7 @@ softmax_thread_rows_kernel(const SoftmaxArgs a) {
     for (int k = 0; k < VPT; k++) mask_tail(v[k], k, nv);
     float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    for (int k = 0; k < VPT; k++) m = agn_max_acc4(m, v[k]);
     float sum = 0.0f;
     if (nv > 0) {
 #pragma unroll
@@ -195,7 +194,7 @@ softmax_warp_rows_kernel(const SoftmaxArgs a) {
     float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < VPL; k++)
-        if (4 * (lane + 32 * k) < nv) m = fmaxf(m, max4(v[k]));
+        if (4 * (lane + 32 * k) < nv) m = agn_max_acc4(m, v[k]);
     m = agn_warp_max(m);
     float sum = 0.0f;
 #pragma unroll
@@ -220,7 +219,7 @@ template <typename OT, int VPT>
 __global__ void __launch_bounds__(1024)
 softmax_block_rows_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
-    __shared__ float red[32];
+    __shared__ float red[32], red_sum[32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int64_t r = blockIdx.x;
     const int nv = (int)valid_len(a, r);
@@ -237,13 +236,12 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
     float m = -INFINITY;
 #pragma unroll
     for (int k = 0; k < VPT; k++)
-        if (4 * (threadIdx.x + k * blockDim.x) < nv) m = fmaxf(m, max4(v[k]));
+        if (4 * (threadIdx.x + k * blockDim.x) < nv) m = agn_max_acc4(m, v[k]);
     m = agn_warp_max(m);
     if (lane == 0) red[warp] = m;
     __syncthreads();
     m = -INFINITY;
     for (int w = 0; w < nwarps; w++) m = fmaxf(m, red[w]);
-    __syncthreads();
     float sum = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
@@ -253,10 +251,10 @@ softmax_block_rows_kernel(const SoftmaxArgs a) {
         }
     }
     sum = agn_warp_sum(sum);
-    if (lane == 0) red[warp] = sum;
+    if (lane == 0) red_sum[warp] = sum;  // (its own array: no barrier between reading the maxima and writing the sums)
     __syncthreads();
     sum = 0.0f;
-    for (int w = 0; w < nwarps; w++) sum += red[w];
+    for (int w = 0; w < nwarps; w++) sum += red_sum[w];
     if (a.sums && threadIdx.x == 0) a.sums[r] = sum;
     const float inv = (a.sums || nv <= 0) ? 1.0f : 1.0f / sum;
 #pragma unroll
@@ -278,7 +276,7 @@ template <typename OT, int VPT>
 __global__ void __launch_bounds__(1024)
 softmax_causal_pair_kernel(const SoftmaxArgs a) {
     agn_pdl_prologue();
-    __shared__ float red[2][32];
+    __shared__ float red[2][32], red_sum[2][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int L = (int)a.row_len, n4 = L >> 2;
     const int half_rows = (L + 1) >> 1;
@@ -311,9 +309,8 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
         if (idx[k] >= 0) {
             const bool isB = (idx[k] >> 30) & 1;
             mask_tail(v[k], idx[k] & 0x3fffffff, isB ? nvB : nvA);
-            const float m = max4(v[k]);
-            if (isB) mB = fmaxf(mB, m);
-            else mA = fmaxf(mA, m);
+            if (isB) mB = agn_max_acc4(mB, v[k]);
+            else mA = agn_max_acc4(mA, v[k]);
         }
     }
     mA = agn_warp_max(mA);
@@ -322,7 +319,6 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
     __syncthreads();
     mA = -INFINITY; mB = -INFINITY;
     for (int w = 0; w < nwarps; w++) { mA = fmaxf(mA, red[0][w]); mB = fmaxf(mB, red[1][w]); }
-    __syncthreads();
     float sA = 0.0f, sB = 0.0f;
 #pragma unroll
     for (int k = 0; k < VPT; k++) {
@@ -336,10 +332,10 @@ softmax_causal_pair_kernel(const SoftmaxArgs a) {
     }
     sA = agn_warp_sum(sA);
     sB = agn_warp_sum(sB);
-    if (lane == 0) { red[0][warp] = sA; red[1][warp] = sB; }
+    if (lane == 0) { red_sum[0][warp] = sA; red_sum[1][warp] = sB; }  // (own arrays: no barrier between maxima and sums)
     __syncthreads();
     sA = 0.0f; sB = 0.0f;
-    for (int w = 0; w < nwarps; w++) { sA += red[0][w]; sB += red[1][w]; }
+    for (int w = 0; w < nwarps; w++) { sA += red_sum[0][w]; sB += red_sum[1][w]; }
     if (a.sums && threadIdx.x == 0) {
         a.sums[rA] = sA;
         if (twoRows) a.sums[rB] = sB;
@@ -425,7 +421,7 @@ softmax_ring_kernel(const SoftmaxArgs a, int slots, int slot_bytes, int spin_lim
             const int i = threadIdx.x + k * blockDim.x;
             if (4 * i < nv) {
                 mask_tail(v[k], i, nv);
-                m = fmaxf(m, max4(v[k]));
+                m = agn_max_acc4(m, v[k]);
             }
         }
         m = agn_warp_max(m);
@@ -506,7 +502,7 @@ softmax_cluster_rows_kernel(const SoftmaxArgs a, int cluster_size) {
     // this CTA's part on its own: maximum m_c, then e = exp(v - m_c) and their sum s_c
     float m = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < VPT; k++) m = fmaxf(m, max4(v[k]));
+    for (int k = 0; k < VPT; k++) m = agn_max_acc4(m, v[k]);
     m = agn_warp_max(m);
     if (lane == 0) red[warp] = m;
     __syncthreads();
