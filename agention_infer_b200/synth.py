@@ -138,8 +138,19 @@ def scale_of_rows(ref: np.ndarray) -> np.ndarray:
     return np.maximum(s, np.float32(1e-30))
 
 
+def rel_to_row_scale(got: np.ndarray, ref: np.ndarray) -> np.ndarray:
+    """|got - ref| / scale(row), element by element."""
+    got = got.reshape(ref.shape)
+    return np.abs(got.astype(np.float64) - ref.astype(np.float64)) / scale_of_rows(ref)
+
+
 def max_rel_to_row_scale(got: np.ndarray, ref: np.ndarray) -> float:
     """max_i |got - ref| / scale(row) — the parity figure for the float ops."""
-    got = got.reshape(ref.shape)
-    err = np.abs(got.astype(np.float64) - ref.astype(np.float64)) / scale_of_rows(ref)
+    err = rel_to_row_scale(got, ref)
     return float(err.max()) if err.size else 0.0
+
+
+def p999_rel_to_row_scale(got: np.ndarray, ref: np.ndarray) -> float:
+    """The 99.9th percentile of the same figure (how far the bulk of the elements sits below the maximum)."""
+    err = rel_to_row_scale(got, ref)
+    return float(np.quantile(err, 0.999)) if err.size else 0.0

@@ -226,3 +226,66 @@ def test_q8_k_argument_errors(backend):
         backend.launch_quantize_rows_q8_k(x, 2, 0, out=out)
     backend.launch_quantize_rows_q8_k(x, 0, 512, out=out)  # T = 0: nothing to do
     backend.sync()
+
+
+def test_fuzz_quantize_rows(backend):
+    """Seeded random shapes: ragged lengths, rows off a 16-byte boundary, magnitudes over twelve decades, and a
+    sprinkling of exact zeros, ties and non-finite values."""
+    r = np.random.default_rng(815)
+    for it in range(60):
+        T = int(r.integers(1, 9))
+        n = int(r.choice([1, 3, 4, 15, 16, 17, 100, 255, 256, 257, 511, 512, 640, 1000, 1024, 1028, 3584, 4100]))
+        x = (r.standard_normal((T, n)) * 10.0 ** r.integers(-6, 6, size=(T, 1))).astype(np.float32)
+        x[r.random((T, n)) < 0.05] = 0.0
+        if n > 8:
+            j = r.integers(0, n, size=4)
+            x[0, j[0]], x[0, j[1]] = np.abs(x[0]).max() + 1, -(np.abs(x[0]).max() + 1)  # a +a / -a tie for the block maximum
+            if it % 5 == 0:
+                x[T - 1, j[2]] = np.nan
+            if it % 7 == 0:
+                x[T - 1, j[3]] = np.inf
+        off = int(r.integers(0, 4))
+        g = Guarded(backend, x.nbytes, skew=4 * off).put(x)
+        with np.errstate(all="ignore"):
+            want = orc.quantize_rows_q8_k(x)
+        got = read_q8k(backend, backend.launch_quantize_rows_q8_k(g.ptr, T, n), T, n)
+        assert_same(got, want, f"fuzz it={it} T={T} n={n} off={off}")
+
+
+def test_q8_k_ops_in_a_recorded_graph(backend):
+    """The fused producers recorded once and replayed on new inputs: the replay's bytes are the eager call's."""
+    be = backend
+    T, H, I = 8, 3584, 18944
+    w = synth.norm_weight(3, "w", H)
+    dx, dd, dnx, dg, du, dw = be.empty(4 * T * H), be.empty(4 * T * H), be.empty(4 * T * H), be.empty(4 * T * I), be.empty(4 * T * I), be.upload(w)
+    qa = (be.empty(4 * T * H // 256), be.empty(T * H), be.empty(2 * T * H // 16))
+    qb = (be.empty(4 * T * I // 256), be.empty(T * I), be.empty(2 * T * I // 16))
+
+    def chain():
+        be.launch_add_residual_rms_norm_q8_k(dx, dd, dw, T, H, 1e-6, new_x=dnx, out=qa)
+        be.launch_silu_mul_q8_k(dg, du, T, I, out=qb)
+
+    def load(salt):
+        a = {n: synth.activations(3, n, s, salt=salt) for n, s in (("x", (T, H)), ("delta", (T, H)), ("gate", (T, I)), ("up", (T, I)))}
+        for buf, n in ((dx, "x"), (dd, "delta"), (dg, "gate"), (du, "up")):
+            be.copy_h2d(buf, a[n])
+        be.sync()
+        return a
+
+    load(0)
+    be.graph_begin()
+    chain()
+    g = be.graph_end()
+    try:
+        for salt in (1, 2):
+            a = load(salt)
+            be.graph_launch(g)
+            rep_a, rep_b = read_q8k(be, qa, T, H), read_q8k(be, qb, T, I)
+            nx = be.read(dnx, np.float32, (T, H))
+            chain()
+            assert_same(read_q8k(be, qa, T, H), rep_a, "replayed add_residual_rms_norm_q8_k")
+            assert_same(read_q8k(be, qb, T, I), rep_b, "replayed silu_mul_q8_k")
+            assert np.array_equal(nx.view(np.uint32), (a["x"] + a["delta"]).view(np.uint32))
+            q8k_close_to_chain(rep_b, orc.quantize_rows_q8_k(orc.silu_mul(a["gate"], a["up"], THREADS), THREADS), "replay vs oracle chain")
+    finally:
+        be.graph_destroy(g)
