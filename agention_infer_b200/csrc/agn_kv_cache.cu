@@ -11,14 +11,16 @@
 //          store f16(scale) ; q = clamp(round(v / scale), -127, 127)   (round half away,
 //          dividing by the f32 scale, not by the stored f16 one)
 //
-// Integer / byte outputs: bit-exact with the CPU code (IEEE division and f16 conversion
-// spelled with __fdiv_rn / __float2half_rn).  Bound by HBM: 4 B read + 2 or 1.06 B written
+// Integer / byte outputs: bit-exact with the CPU code (f16 conversion by __float2half_rn; the
+// division of every value by the scale through agn_q8_0_quant4, which takes the reference's IEEE
+// division only where an approximate quotient could round differently).  Bound by HBM: 4 B read + 2 or 1.06 B written
 // per element; eight lanes own one 32-value block (coalesced 128-bit loads, amax by three
 // shuffles).
 #include <cuda_fp16.h>
 #include <math.h>
 
 #include "agn_common.cuh"
+#include "agn_row_math.cuh"
 
 namespace {
 
@@ -88,13 +90,8 @@ kv_write_q8_0_kernel(const KvArgs a) {
         const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
         unsigned char *blk = tok + b * 34;
         if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
-        unsigned char q[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float r = roundf(__fdiv_rn(x[i], scale));
-            r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0 (a NaN value, or inf / inf)
-            q[i] = (unsigned char)(signed char)(int)r;
-        }
+        uint32_t q[4];
+        agn_q8_0_quant4(x, scale, q);
         if (e0 + 3 < left) {  // blocks are 2-byte aligned: two 16-bit stores
             *reinterpret_cast<uint16_t *>(blk + 2 + e0) = (uint16_t)(q[0] | (q[1] << 8));
             *reinterpret_cast<uint16_t *>(blk + 4 + e0) = (uint16_t)(q[2] | (q[3] << 8));
@@ -181,12 +178,7 @@ kv_write_multi_kernel(const KvArgs a) {
                 if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
                 const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
                 uint32_t q[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float r = roundf(__fdiv_rn(xs[i], scale));
-                    r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0
-                    q[i] = (uint32_t)(unsigned char)(signed char)(int)r;
-                }
+                agn_q8_0_quant4(xs, scale, q);
                 *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
                 *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
             }

@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include "agn_common.cuh"
+#include "agn_row_math.cuh"
 
 namespace {
 
@@ -70,12 +71,7 @@ __device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_h
             if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
             const float xs[4] = {x.x, x.y, x.z, x.w};
             uint32_t q[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float r = roundf(__fdiv_rn(xs[j], scale));
-                r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0
-                q[j] = (uint32_t)(unsigned char)(signed char)(int)r;
-            }
+            agn_q8_0_quant4(xs, scale, q);
             *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
             *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
         }

@@ -44,6 +44,39 @@ __device__ __forceinline__ float4 agn_silu_mul4(float4 g, float4 u) {
     return o;
 }
 
+// Q8_0 cache packing of four values of a block with the given scale (`KvDtype::pack`,
+// src/model/mod.rs:574-583): q = (v / scale).round().clamp(-127, 127) as i8, NaN -> 0, as bytes.
+// The reference divides every value by the scale (IEEE) and rounds half away from zero: ~25
+// instructions per value.  Here the quotient is first approximated as v * rcp.approx(scale): within
+// 1.5 * 2^-23 relative of the true quotient t, so within 3.1e-5 of fl(t) for |t| < 128.  If that
+// approximation lies more than 1e-4 away from every k + 0.5, fl(t) rounds to the same integer, which
+// is read off the mantissa of |qa| + 2^23 (round to nearest; exact ties never get here).  A lane with a
+// value too close to a boundary, beyond +-127.25, or not finite (NaN value, infinite or subnormal
+// scale) recomputes its four values the reference's way.  Same bytes for every input.
+__device__ __forceinline__ void agn_q8_0_quant4(const float (&x)[4], float scale, uint32_t (&q)[4]) {
+    float inv;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(scale));
+    bool sure = true;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float qa = __fmul_rn(x[i], inv);
+        const float a = fabsf(qa);
+        const float m = __fadd_rn(a, 8388608.0f);              // 2^23 + round_to_nearest(a) for a < 2^22
+        const float g = __fsub_rn(a, __fsub_rn(m, 8388608.0f));  // a - round_to_nearest(a), in [-0.5, 0.5]
+        sure = sure && (fabsf(g) <= 0.4999f) && (a < 127.25f);  // false for NaN
+        const int mag = __float_as_int(m) & 0xff;
+        q[i] = (uint32_t)(qa < 0.0f ? -mag : mag) & 0xffu;
+    }
+    if (!sure) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float r = roundf(__fdiv_rn(x[i], scale));
+            r = (r != r) ? 0.0f : fminf(fmaxf(r, -127.0f), 127.0f);  // Rust's `NaN as i8` is 0 (a NaN value, or inf / inf)
+            q[i] = (uint32_t)(unsigned char)(signed char)(int)r;
+        }
+    }
+}
+
 #endif  // __CUDACC__
 
 // CTA shape of the register-resident RMSNorm kernels for a row of n4 vectors of four values:

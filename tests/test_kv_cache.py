@@ -287,3 +287,52 @@ def test_fused_rope_kv_write_reports_a_slot_out_of_range(backend):
     assert e.value.status == 4
     got = backend.read(vc, np.uint8, (max_seq, bpt))
     assert np.all(got[[1, 2, 4, 5, 6, 7]] == 0) and np.any(got[0] != 0) and np.any(got[3] != 0)  # only slots 0 and 3 were written
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("amax", [127.0, 100.0, 1.0, 3.3e-3, 6.02e4, 1e-30, 1e-39])
+def test_q8_0_quotients_at_the_rounding_boundaries_bit_exact(backend, amax):
+    """Values whose quotient by the block scale falls on k + 0.5, or within a few ulps of it, for every k: the
+    cases where an approximate quotient and the reference's IEEE division could round to different integers.
+    Each block holds `amax` (which fixes the scale), and 31 such values; through the stand-alone kernels (a CTA
+    per token, four tokens per CTA) and through the write fused into the norm -> RoPE launch."""
+    amax = np.float32(amax)
+    scale = amax / np.float32(127.0) if amax > 0 else np.float32(1.0)
+    k = np.arange(-127, 127, dtype=np.float32) + np.float32(0.5)
+    with np.errstate(all="ignore"):
+        base = (k * scale).astype(np.float32)
+    vals = [base]
+    for steps in (1, 2, 3, 6):
+        up, dn = base.copy(), base.copy()
+        for _ in range(steps):
+            up, dn = np.nextafter(up, np.float32(np.inf)), np.nextafter(dn, np.float32(-np.inf))
+        vals += [up, dn]
+    vals = np.concatenate(vals)
+    vals = vals[np.abs(vals) <= amax]
+    n_blocks = -(-vals.size // 31)
+    body = np.zeros(n_blocks * 31, np.float32); body[: vals.size] = vals
+    x = np.empty((n_blocks, 32), np.float32)
+    x[:, 0] = amax
+    x[:, 1:] = body.reshape(n_blocks, 31)
+    hd = 128
+    T = -(-n_blocks // (hd // 32))
+    rows = np.zeros((T, hd), np.float32); rows.reshape(-1, 32)[:n_blocks] = x
+    rows.reshape(-1, 32)[n_blocks:, 0] = amax
+    pos = np.arange(T, dtype=np.int32)
+    bpt = backend.kv_bytes_per_token(AGN_Q8_0, hd)
+    ref = np.zeros((T, bpt), np.uint8)
+    orc.kv_write_rows(AGN_Q8_0, rows, pos, ref)
+    for reps in (1, 40):  # 40 copies of the rows: enough tokens for the four-tokens-per-CTA kernel (T >= 16 * SMs)
+        big = np.tile(rows, (reps, 1)); Tb = big.shape[0]
+        dk, dv = backend.upload(np.zeros((Tb, bpt), np.uint8)), backend.upload(np.zeros((Tb, bpt), np.uint8))
+        backend.kv_write(AGN_Q8_0, backend.upload(big), backend.upload(big), dk, dv, Tb, hd, backend.upload(np.arange(Tb, dtype=np.int32)), Tb)
+        for buf in (dk, dv):
+            got = backend.read(buf, np.uint8, (Tb, bpt))
+            assert np.array_equal(got, np.tile(ref, (reps, 1))), (float(amax), reps, backend.last_kernel)
+    # fused: V rides along unrotated, so its cache bytes are the pack of the input rows
+    nq = nkv = 1
+    q = synth.activations(2, "q", (T, nq * hd)); kk = synth.activations(2, "k", (T, nkv * hd))
+    dk, dv = backend.upload(np.zeros((T, bpt), np.uint8)), backend.upload(np.zeros((T, bpt), np.uint8))
+    backend.launch_qk_norm_rope_kv_write(backend.upload(q), backend.upload(kk), backend.upload(rows), None, None, T, nq, nkv, hd, 1e-6,
+                                         hd, backend.upload(pos), 1e6, AGN_Q8_0, dk, dv, T)
+    assert np.array_equal(backend.read(dv, np.uint8, (T, bpt)), ref), float(amax)
