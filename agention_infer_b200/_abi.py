@@ -121,6 +121,10 @@ SIGNATURES = {
     "agn_gguf_tensor_at": (_i32, [_vp, C.c_uint64, _pti]),
     "agn_gguf_find_tensor": (_i32, [_vp, C.c_char_p, _pti]),
     "agn_gguf_upload_tensor": (_i32, [_vp, _vp, C.c_char_p, _pp, _pti]),
+    "agn_gguf_upload_tensors": (_i32, [_vp, _vp, C.POINTER(C.c_char_p), C.c_uint64, C.POINTER(C.c_void_p), _pti, _i32,
+                                       C.POINTER(C.c_uint64)]),
+    "agn_gguf_tensor_data": (_i32, [_vp, C.c_char_p, _pp, C.POINTER(C.c_uint64)]),
+    "agn_gguf_release_pages": (_i32, [_vp, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
     "agn_type_size": (_sz, [_i32, _sz]),
 }
 

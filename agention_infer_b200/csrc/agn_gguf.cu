@@ -447,4 +447,101 @@ int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name
     return AGN_OK;
 }
 
+// The tensor's bytes where they lie in the mapping (or in the caller's buffer): the slice
+// `&raw_data[byte_offset .. byte_offset + byte_size]` the reference hands to its codecs
+// (src/quant/mod.rs:97-135).  Valid until agn_gguf_close.
+int32_t agn_gguf_tensor_data(const agn_gguf *g, const char *name, const void **data, uint64_t *n_bytes) {
+    if (!g || !name || !data) return AGN_EINVAL;
+    *data = nullptr;
+    agn_tensor_info ti;
+    const int32_t rc = agn_gguf_find_tensor(g, name, &ti);
+    if (rc != AGN_OK) return rc;
+    if (ti.row_bytes == 0) return AGN_EUNSUPPORTED_DTYPE;
+    const uint8_t *src = g->slice(ti.file_offset, ti.n_bytes);
+    if (!src) return AGN_EFORMAT;  // beyond the file, or astride two files of a split model
+    *data = src;
+    if (n_bytes) *n_bytes = ti.n_bytes;
+    return AGN_OK;
+}
+
+// `release_mmap_prefix` (src/model/llama/gpu_resident.rs:29-49): drop the page-cache pages that lie
+// wholly inside the file bytes [from, to) (start rounded up, end rounded down to page boundaries)
+// with madvise(MADV_DONTNEED).  The mappings are read-only and file-backed, so a later access
+// re-faults the page from disk: slower, never wrong.  *mark (may be null) receives the offset up to
+// which pages are gone — the rounded-down end, what the reference returns for its next call — or
+// `from` when no whole page lay inside the range.
+static uint64_t release_range(const agn_gguf *g, uint64_t from, uint64_t to, uint64_t *mark) {
+    if (mark) *mark = from;
+    if (to <= from) return 0;
+    long ps = sysconf(_SC_PAGESIZE);
+    const uint64_t page = ps > 0 ? (uint64_t)ps : 4096u;
+    uint64_t total = 0;
+    auto release_in = [&](void *mapping, size_t len, uint64_t start) {  // one mapped file covering [start, start + len)
+        if (!mapping) return;
+        const uint64_t lo = from > start ? from : start, hi = to < start + len ? to : start + len;
+        if (hi <= lo) return;
+        // mmap returns page-aligned addresses: round the offsets inside the file
+        const uint64_t o0 = (lo - start + page - 1) / page * page, o1 = (hi - start) / page * page;
+        if (o1 > o0 && madvise(static_cast<uint8_t *>(mapping) + o0, (size_t)(o1 - o0), MADV_DONTNEED) == 0) {
+            total += o1 - o0;
+            if (mark && start + o1 > *mark) *mark = start + o1;
+        }
+    };
+    release_in(g->mapping, g->map_len, 0);
+    for (const agn_gguf::Part &p : g->parts) release_in(p.mapping, p.len, p.start);
+    return total;
+}
+
+int32_t agn_gguf_release_pages(const agn_gguf *g, uint64_t from, uint64_t to, uint64_t *released_bytes) {
+    if (released_bytes) *released_bytes = 0;
+    if (!g) return AGN_EINVAL;
+    const uint64_t got = release_range(g, from, to, nullptr);
+    if (released_bytes) *released_bytes = got;
+    return AGN_OK;
+}
+
+// The upload loop of `pre_upload_gpu` (src/model/llama/gpu_resident.rs:112-152): the named tensors
+// are copied in ascending file-offset order, not in the order given, and — with release_pages — the
+// part of the mapping that lies below the tensor just uploaded is dropped from the page cache, so
+// that a file of about the size of host memory does not sit in the page cache next to its growing
+// copy on the device.  Results are returned in the caller's order.
+int32_t agn_gguf_upload_tensors(agn_ctx *ctx, const agn_gguf *g, const char *const *names, uint64_t n, void **dptrs,
+                                agn_tensor_info *infos, int32_t release_pages, uint64_t *released_bytes) {
+    AGN_CHECK_CTX(ctx);
+    if (released_bytes) *released_bytes = 0;
+    if (!g || (n && (!names || !dptrs))) return agn_fail(ctx, AGN_EINVAL, "agn_gguf_upload_tensors: null argument");
+    std::vector<agn_tensor_info> ti(n);
+    std::vector<uint64_t> order(n);
+    for (uint64_t i = 0; i < n; i++) {
+        dptrs[i] = nullptr;
+        order[i] = i;
+    }
+    for (uint64_t i = 0; i < n; i++) {
+        if (!names[i]) return agn_fail(ctx, AGN_EINVAL, "agn_gguf_upload_tensors: names[%llu] is null", (unsigned long long)i);
+        const int32_t frc = agn_gguf_find_tensor(g, names[i], &ti[i]);
+        if (frc == AGN_EFORMAT) return agn_fail(ctx, AGN_EFORMAT, "tensor '%s': dimensions or offset overflow 64 bits", names[i]);
+        if (frc != AGN_OK) return agn_fail(ctx, AGN_ENOTFOUND, "tensor '%s' not found", names[i]);
+    }
+    for (uint64_t i = 1; i < n; i++)  // insertion sort by file offset (a few hundred names at most)
+        for (uint64_t j = i; j > 0 && ti[order[j]].file_offset < ti[order[j - 1]].file_offset; j--) std::swap(order[j], order[j - 1]);
+    uint64_t released_up_to = g->data_offset, total = 0;  // the header pages stay
+    for (uint64_t k = 0; k < n; k++) {
+        const uint64_t i = order[k];
+        const int32_t rc = agn_gguf_upload_tensor(ctx, g, names[i], &dptrs[i], nullptr);
+        if (rc != AGN_OK) {
+            for (uint64_t j = 0; j < n; j++) {
+                if (dptrs[j]) agn_free(ctx, dptrs[j]);
+                dptrs[j] = nullptr;
+            }
+            return rc;
+        }
+        const uint64_t end = ti[i].file_offset + ti[i].n_bytes;
+        if (release_pages && end > released_up_to) total += release_range(g, released_up_to, end, &released_up_to);
+    }
+    if (infos)
+        for (uint64_t i = 0; i < n; i++) infos[i] = ti[i];
+    if (released_bytes) *released_bytes = total;
+    return AGN_OK;
+}
+
 }  // extern "C"

@@ -220,6 +220,42 @@ class GgufFile:
         info = TensorInfo(raw)
         return DeviceBuffer(backend, p.value, info.n_bytes), info
 
+    def tensor_bytes(self, name: str) -> bytes:
+        """A copy of the tensor's bytes as the file holds them (`&raw_data[byte_offset ..]`, src/quant/mod.rs:97-135)."""
+        p, n = C.c_void_p(), C.c_uint64(0)
+        st = self._lib.agn_gguf_tensor_data(self._g, name.encode(), C.byref(p), C.byref(n))
+        if st != _abi.AGN_OK:
+            raise GgufError(st, f"tensor {name!r}")
+        return C.string_at(p.value, n.value)
+
+    def upload_tensors(self, backend: CudaBackend, names, release_pages: bool = True):
+        """`pre_upload_gpu` (src/model/llama/gpu_resident.rs:112-152): uploads the named tensors in ascending file-offset
+        order and (release_pages) drops the consumed part of the mapping from the page cache as it goes.
+        Returns ({name: (DeviceBuffer, TensorInfo)}, bytes of page cache released)."""
+        names = list(names)
+        n = len(names)
+        c_names = (C.c_char_p * n)(*[s.encode() for s in names])
+        ptrs = (C.c_void_p * n)()
+        infos = (_abi.TensorInfo * n)()
+        released = C.c_uint64(0)
+        st = self._lib.agn_gguf_upload_tensors(backend._ctx, self._g, c_names, n, ptrs, infos, 1 if release_pages else 0,
+                                               C.byref(released))
+        if st != _abi.AGN_OK:
+            raise BackendError(st, self._lib.agn_last_error(backend._ctx).decode())
+        out = {}
+        for i, name in enumerate(names):
+            info = TensorInfo(infos[i])
+            out[name] = (DeviceBuffer(backend, ptrs[i], info.n_bytes), info)
+        return out, int(released.value)
+
+    def release_pages(self, start: int, end: int) -> int:
+        """Drops the whole pages inside file bytes [start, end) from the page cache; returns the bytes released."""
+        released = C.c_uint64(0)
+        st = self._lib.agn_gguf_release_pages(self._g, start, end, C.byref(released))
+        if st != _abi.AGN_OK:
+            raise GgufError(st, "release_pages")
+        return int(released.value)
+
     def dequant_tensor(self, backend: CudaBackend, name: str):
         """`WeightMap::dequant_tensor` (src/model/mod.rs:318-345): the whole tensor as f32 [n_rows, row_len] on the device
         (every row through the get_rows kernel).  Returns (DeviceBuffer, TensorInfo)."""

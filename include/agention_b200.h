@@ -549,6 +549,25 @@ AGN_API int32_t agn_gguf_find_tensor(const agn_gguf *g, const char *name, agn_te
  * return.  The result is what agn_get_rows_* takes as `table` (n_rows, row_len from info). */
 AGN_API int32_t agn_gguf_upload_tensor(agn_ctx *ctx, const agn_gguf *g, const char *name, void **dptr,
                                        agn_tensor_info *info);
+/* The tensor's bytes in host memory, where the mapping (or the caller's buffer) holds them: the slice
+ * the reference passes to its codecs (src/quant/mod.rs:97-135).  Valid until agn_gguf_close.
+ * AGN_ENOTFOUND, AGN_EUNSUPPORTED_DTYPE (no codec here, size unknown), AGN_EFORMAT (outside the file). */
+AGN_API int32_t agn_gguf_tensor_data(const agn_gguf *g, const char *name, const void **data, uint64_t *n_bytes);
+/* The upload loop of `pre_upload_gpu` (src/model/llama/gpu_resident.rs:112-152): the n named tensors
+ * are copied in ascending file-offset order, whatever order they are named in, and with
+ * release_pages != 0 the part of the memory mapping below each uploaded tensor is dropped from
+ * the page cache as the loop goes (`release_mmap_prefix`, gpu_resident.rs:29-49: whole pages only,
+ * madvise(MADV_DONTNEED); a later access re-reads the page from the file), so a file of about the
+ * size of host memory never sits in the page cache next to its copy on the device.  dptrs[i] /
+ * infos[i] (infos may be NULL) belong to names[i]; on an error nothing stays allocated.
+ * *released_bytes (may be NULL): bytes of page cache given back (0 for an agn_gguf_parse object,
+ * whose memory belongs to the caller). */
+AGN_API int32_t agn_gguf_upload_tensors(agn_ctx *ctx, const agn_gguf *g, const char *const *names, uint64_t n,
+                                        void **dptrs, agn_tensor_info *infos, int32_t release_pages,
+                                        uint64_t *released_bytes);
+/* The release step alone, for a caller with its own upload loop: whole pages inside the file bytes
+ * [from, to) of a mapped file (or of the files of a split model, in their concatenated offsets). */
+AGN_API int32_t agn_gguf_release_pages(const agn_gguf *g, uint64_t from, uint64_t to, uint64_t *released_bytes);
 
 /* `GgmlType::type_size` (src/types.rs:164-168); 0 for a dtype without a kernel. */
 AGN_API size_t agn_type_size(int32_t dtype, size_t n);

@@ -331,6 +331,20 @@ class GgufFile {
         if (info) *info = ti;
         return DeviceBuffer(be.ctx(), d, (size_t)ti.n_bytes);
     }
+    // `pre_upload_gpu` (src/model/llama/gpu_resident.rs:112-152): all named tensors, uploaded in ascending
+    // file-offset order, the consumed part of the mapping dropped from the page cache on the way
+    std::vector<DeviceBuffer> upload_all(CudaBackend &be, const std::vector<const char *> &names, bool release_pages = true,
+                                         std::vector<agn_tensor_info> *infos = nullptr, uint64_t *released_bytes = nullptr) const {
+        std::vector<void *> d(names.size(), nullptr);
+        std::vector<agn_tensor_info> ti(names.size());
+        be.check(agn_gguf_upload_tensors(be.ctx(), g_, names.data(), names.size(), d.data(), ti.data(), release_pages ? 1 : 0,
+                                         released_bytes));
+        std::vector<DeviceBuffer> out;
+        out.reserve(names.size());
+        for (size_t i = 0; i < names.size(); i++) out.emplace_back(be.ctx(), d[i], (size_t)ti[i].n_bytes);
+        if (infos) *infos = ti;
+        return out;
+    }
 
   private:
     agn_gguf *g_ = nullptr;

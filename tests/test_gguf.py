@@ -1,6 +1,7 @@
 """GGUF container glue through the C ABI: the reference parser's own unit-test vectors
 (src/parser.rs:209-303), a file with metadata and tensors, and (GPU) get_rows from a tensor
 uploaded out of a GGUF file."""
+import os
 import struct
 
 import numpy as np
@@ -282,3 +283,64 @@ def test_get_rows_from_a_tensor_uploaded_out_of_a_gguf_file(backend, tmp_path):
     with pytest.raises(BackendError) as e:
         g.upload(backend, "nope")
     assert e.value.status == _abi.AGN_ENOTFOUND
+
+
+def _many_tensor_file(n_tensors=6, rows=64, hidden=4096):
+    """A file with several Q8_0 tensors of 136 KiB each (33 pages), so that page release has whole pages to drop."""
+    rng = np.random.default_rng(77)
+    tensors, raw = [], {}
+    for i in range(n_tensors):
+        t = synth.quant_table(orc.Q8_0, rows, hidden, cfg_index=0)
+        t = (t.astype(np.int32) + i).astype(np.uint8)  # distinct bytes per tensor
+        raw[f"blk.{i}.attn_q.weight"] = t
+        tensors.append((f"blk.{i}.attn_q.weight", orc.Q8_0, [hidden, rows], t))
+    blob = gw.build(3, [("general.architecture", "str", "llama")], tensors)
+    return bytes(blob), raw
+
+
+def test_release_pages_drops_whole_pages_and_data_stays_readable(tmp_path):  # release_mmap_prefix, gpu_resident.rs:29-49
+    blob, raw = _many_tensor_file()
+    path = tmp_path / "many.gguf"
+    path.write_bytes(blob)
+    g = GgufFile(str(path))
+    page = os.sysconf("SC_PAGESIZE")
+    infos = [g.find(n) for n in raw]
+    lo, hi = infos[1].file_offset + 5, infos[3].file_offset + infos[3].n_bytes - 7  # deliberately unaligned
+    want = hi // page * page - -(-lo // page) * page
+    assert want > 0
+    assert g.release_pages(lo, hi) == want
+    assert g.release_pages(hi, lo) == 0 and g.release_pages(lo, lo + 10) == 0  # empty range, no whole page inside
+    assert g.release_pages(0, 1 << 62) == len(blob) // page * page  # clipped to the file
+    for n, info in zip(raw, infos):  # every tensor still reads back from the mapping (pages re-fault from the file)
+        assert g.tensor_bytes(n) == raw[n].tobytes()
+    g2 = GgufFile(data=blob)  # memory of the caller: nothing to release
+    assert g2.release_pages(lo, hi) == 0
+    g.close(); g2.close()
+
+
+@pytest.mark.gpu
+def test_upload_tensors_in_file_order_with_page_release(backend, tmp_path):  # pre_upload_gpu, gpu_resident.rs:112-152
+    blob, raw = _many_tensor_file()
+    path = tmp_path / "many.gguf"
+    path.write_bytes(blob)
+    g = GgufFile(str(path))
+    names = list(raw)
+    shuffled = [names[i] for i in (4, 0, 5, 2, 1, 3)]
+    got, released = g.upload_tensors(backend, shuffled)
+    page = os.sysconf("SC_PAGESIZE")
+    first, last = g.find(names[0]), g.find(names[-1])
+    span_end = (last.file_offset + last.n_bytes) // page * page
+    span_start = -(-g.data_offset // page) * page
+    assert released == span_end - span_start  # everything below the last tensor's end, down to the data section
+    for n in shuffled:
+        buf, info = got[n]
+        assert info.name == n and info.n_bytes == raw[n].nbytes
+        assert backend.read(buf, np.uint8, (info.n_bytes,)).tobytes() == raw[n].tobytes()
+    again, released2 = g.upload_tensors(backend, names[:2], release_pages=False)  # the released pages re-fault
+    assert released2 == 0
+    assert backend.read(again[names[1]][0], np.uint8, (raw[names[1]].nbytes,)).tobytes() == raw[names[1]].tobytes()
+    from agention_infer_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        g.upload_tensors(backend, [names[0], "nope"])
+    assert e.value.status == _abi.AGN_ENOTFOUND
+    g.close()
