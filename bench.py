@@ -777,12 +777,45 @@ def run_ours(args, cfg, ops_list, wl):
         }
         if world == 1 and not args.no_cpu and not f16:
             out["cpu_baseline"] = cpu_baseline(cfg, order)
+        if world == 1 and args.workload == "c2" and not args.no_others and not f16:
+            out["other_workloads"] = other_workloads()
+            if any(r.get("oracle_ok") is False for r in out["other_workloads"].values()):
+                verified = False
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
     be.close()
     if not verified:
         raise SystemExit("bench: outputs differ from the CPU oracle (or between ranks); see `verification` in the JSON line")
+
+
+def other_workloads():
+    """The two configurations the default line does not otherwise touch, each as a short run of this
+    file in a child process on the same GPU (one GPU only): c1 (Llama-3.2-1B shapes with the causal
+    softmax, launch-bound, one graph replay per step) and c5 (Mixtral-shaped MoE routing: router top-2, gather
+    by expert, SiLU over the routed rows).  Device time per step, every op alone, and the comparison of the
+    outputs with the CPU oracle."""
+    recs = {}
+    for w in ("c1", "c5"):
+        cmd = [sys.executable, os.path.abspath(__file__), "--workload", w, "--no-e2e", "--no-cpu", "--no-split", "--no-decode",
+               "--no-extras", "--no-others", "--repeats", "5", "--warm-seconds", "0.2"]
+        try:
+            p = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+            lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+            if not lines:
+                recs[w] = {"unavailable": f"child exited {p.returncode}: {p.stderr.strip()[-200:]}"}
+                continue
+            d = json.loads(lines[-1])
+            orc_rep = (d.get("verification") or {}).get("oracle") or {}
+            recs[w] = {"workload": d["config"]["workload"], "tokens": d["config"].get("tokens_per_gpu"), "steps": d["steps"],
+                       "ms_per_step": d["ms_per_step"], "tokens_per_s": d["value"], "launch": d["timing"]["launch"],
+                       "hbm_gbs": d["hbm_gbs"], "hbm_frac_of_measured_peak": d["hbm_frac_of_measured_peak"],
+                       "ops": {k: {"us": v["us"], "gbs": v["gbs"]} for k, v in d["ops"].items()},
+                       "oracle_ok": orc_rep.get("ok"), "oracle_max_rel_err": orc_rep.get("max_rel_err"),
+                       "gpu_launches": d.get("gpu_launches")}
+        except Exception as e:  # a child that hangs or prints something else: say so, keep the headline
+            recs[w] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return recs
 
 
 def decode_sweep(torch, be, dev, stream, steps, seed_salt=0):
@@ -986,6 +1019,8 @@ def main():
     ap.add_argument("--no-verify", action="store_true", help="skip the comparison of the outputs with the CPU oracle")
     ap.add_argument("--no-split", action="store_true", help="skip the strong_c4 record (the large batch split over the ranks)")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode_c3 record (one GPU)")
+    ap.add_argument("--no-others", action="store_true", help="skip the other_workloads record (c1 and c5 as child runs, one GPU); implied by --no-split with --no-decode "
+                         "(the headline workload alone)")
     ap.add_argument("--repeats", type=int, default=25, help="how many times the K-step timed region is repeated (median reported)")
     ap.add_argument("--check-rows", type=int, default=64, help="rows of every output compared with the oracle")
     ap.add_argument("--warm-seconds", type=float, default=0.6,
@@ -994,6 +1029,8 @@ def main():
                     help="token rows (default: the configuration's); smaller values are for profiling")
     args = ap.parse_args()
     from agention_infer_b200 import synth
+    if args.no_split and args.no_decode:
+        args.no_others = True
     if args.steps is None:
         args.steps = 5 if args.impl == "reference" else (200 if args.workload in ("c1", "c2", "c3") else 20)
     world = int(os.environ.get("WORLD_SIZE", "1"))
