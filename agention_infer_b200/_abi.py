@@ -101,6 +101,7 @@ SIGNATURES = {
     "agn_host_qk_norm_rope_qk_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _i32,
                                             _f32, _f32, _i32]),
     "agn_host_softmax_rows_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _i32, _i32]),
+    "agn_host_quantize_rows_q8_k_f32": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "agn_host_get_rows_f32": (_i32, [_vp, _i32, _vp, _sz, _i64, _i64, _vp, _i64, _vp]),
     "agn_gather_rows_by_expert_noalloc_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp, _vp, C.c_char_p,
                                                      _sz]),

@@ -528,6 +528,13 @@ class CudaBackend:
         self._check(self._lib.agn_host_get_rows_f32(self._ctx, dtype, _ptr(table_dev), table_bytes, n_rows, row_len,
                                                     self._h(ids, np.uint32), ids.size, self._h(out, np.float32)))
 
+    def quantize_rows_q8_k_into(self, x: np.ndarray, d: np.ndarray, qs: np.ndarray, bsums: np.ndarray) -> None:
+        """`quantize_row_q8_k` (src/quant/q8_k.rs:49-92) on host rows x [T, n] -> d [T, nb] f32, qs [T, nb*256] i8,
+        bsums [T, nb*16] i16."""
+        rows = x.reshape(-1, x.shape[-1])
+        self._check(self._lib.agn_host_quantize_rows_q8_k_f32(self._ctx, self._h(x, np.float32), rows.shape[0], rows.shape[1],
+                                                              self._h(d, np.float32), self._h(qs, np.int8), self._h(bsums, np.int16)))
+
     @staticmethod
     def type_size(dtype: int, n: int) -> int:
         """`GgmlType::type_size` (src/types.rs:164-168)."""

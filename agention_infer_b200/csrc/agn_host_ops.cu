@@ -329,4 +329,20 @@ int32_t agn_host_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table_dev
     });
 }
 
+// `quantize_row_q8_k(x)` at the top of `WeightMap::matmul_into` (src/model/mod.rs:381-386) for a
+// caller whose activations live in host memory: T host rows of n values in, the three `Q8KRow`
+// arrays (src/quant/q8_k.rs:27-37) out, row after row.
+int32_t agn_host_quantize_rows_q8_k_f32(agn_ctx *ctx, const float *x_host, int64_t T, int64_t n, float *d_host, int8_t *qs_host,
+                                        int16_t *bsums_host) {
+    AGN_CHECK_CTX(ctx);
+    if (T < 0 || n <= 0) return agn_fail(ctx, AGN_EINVAL, "host_quantize_rows_q8_k: T=%lld n=%lld", (long long)T, (long long)n);
+    if (T > 0 && (!x_host || !d_host || !qs_host || !bsums_host)) return agn_fail(ctx, AGN_EINVAL, "host_quantize_rows_q8_k: null pointer");
+    const size_t nb = (size_t)agn_q8_k_blocks(n);
+    const HostBuf bufs[4] = {{x_host, nullptr, sizeof(float) * (size_t)n}, {nullptr, d_host, sizeof(float) * nb},
+                             {nullptr, qs_host, 256 * nb}, {nullptr, bsums_host, sizeof(int16_t) * 16 * nb}};
+    return run_pipelined(ctx, "host_quantize_rows_q8_k", T, bufs, 4, [&](int64_t rows, void **d, int64_t) {
+        return agn_quantize_rows_q8_k_f32(ctx, (const float *)d[0], rows, n, (float *)d[1], (int8_t *)d[2], (int16_t *)d[3]);
+    });
+}
+
 }  // extern "C"

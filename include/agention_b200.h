@@ -467,6 +467,10 @@ AGN_API int32_t agn_host_softmax_rows_f32(agn_ctx *ctx, const float *in_host, fl
 AGN_API int32_t agn_host_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table_dev,
                                       size_t table_bytes, int64_t n_rows, int64_t row_len,
                                       const uint32_t *ids_host, int64_t T, float *out_host);
+/* `quantize_row_q8_k` (src/quant/q8_k.rs:49-92) on host rows: T rows of n values in, the `Q8KRow` arrays
+ * out (see agn_quantize_rows_q8_k_f32), bit-exact. */
+AGN_API int32_t agn_host_quantize_rows_q8_k_f32(agn_ctx *ctx, const float *x_host, int64_t T, int64_t n,
+                                                float *d_host, int8_t *qs_host, int16_t *bsums_host);
 
 /* Allocation-free variant of agn_gather_rows_by_expert_f32.  It has no counterpart in the
  * reference.  It exists for hosts that cannot allocate device memory: one that has given the

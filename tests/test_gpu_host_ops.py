@@ -110,3 +110,15 @@ def test_hostlink_probe_one_gpu():
     row = r["active_gpus"]["1"]
     assert set(row) == {"h2d", "d2h", "both_per_direction"}
     assert all(1.0 < row[c]["mean_gbs_per_gpu"] < 1000.0 for c in row)
+
+
+def test_host_quantize_rows_q8_k_bit_exact(backend):
+    """Host rows in, the three Q8KRow arrays out, through the staging ring (several chunks), ragged rows included."""
+    for T, n in ((6000, 3584), (300, 1000), (3, 100)):
+        x = synth.activations(3, "x", (T, n)) * np.float32(2.5)
+        x[0, : min(n, 256)] = 0.0
+        nb = (n + 255) // 256
+        d, qs, bs = np.empty((T, nb), np.float32), np.empty((T, nb * 256), np.int8), np.empty((T, nb * 16), np.int16)
+        backend.quantize_rows_q8_k_into(x, d, qs, bs); backend.sync()
+        rd, rq, rb = orc.quantize_rows_q8_k(x, THREADS)
+        assert np.array_equal(d.view(np.uint32), rd.view(np.uint32)) and np.array_equal(qs, rq) and np.array_equal(bs, rb), (T, n)
