@@ -508,7 +508,7 @@ def run_ours(args, cfg, ops_list, wl):
     # ---- ops of the path that are not part of this configuration's step, each alone (f32 only):
     #      fused residual-add + norm, KV-cache packing, and a causal softmax at prefill size
     extra_ops = {}
-    if not f16 and not args.no_extras and step_bytes < 4e9:
+    if not f16 and not args.no_extras and step_bytes < 8e9:
         from agention_infer_b200 import AGN_BF16, AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
         hd_kv = nkv * hd
         Ls = min(T, 2048)
