@@ -1,5 +1,5 @@
-"""Writes tests/golden/oracle_small.npz: small seeded inputs and the CPU oracle's outputs for
-every op of the hot path.  The fixtures pin the oracle itself (a rebuilt oracle, another
+"""Writes tests/golden/oracle_small.npz (and q8k_small.npz, the Q8_K activation quantiser): small seeded
+inputs and the CPU oracle's outputs for every op of the hot path.  The fixtures pin the oracle itself (a rebuilt oracle, another
 libm or another compiler must reproduce them) and give the GPU tests a committed target
 that does not depend on the oracle being rebuilt on the GPU box.
 Run from the repository root: python tests/golden/make_oracle_fixtures.py
@@ -57,3 +57,17 @@ out.update(router_logits=logits, router_idx=idx, router_w=wts, gather_x=xg, gath
 path = Path(__file__).with_name("oracle_small.npz")
 np.savez_compressed(path, **out)
 print("wrote", path, path.stat().st_size, "bytes")
+
+# Q8_K activation rows (quantize_row_q8_k, src/quant/q8_k.rs:49-92): ragged rows with a tie of +a / -a, an all-zero
+# block, exact .5 products, a NaN and an infinity; integer outputs, so the fixture is exact
+xq = (synth.activations(1, "x", (8, 600)) * np.float32(3.0)).astype(np.float32)
+xq[1, :256] = 0.0
+xq[2, 7], xq[2, 300] = 9.5, -9.5
+xq[3, :6] = [-127.0, 0.5, 1.5, -2.5, 126.5, -0.5]; xq[3, 6:256] = 0.25
+xq[4, 11] = np.nan
+xq[5, 13] = np.inf
+with np.errstate(all="ignore"):
+    qd, qq, qb = orc.quantize_rows_q8_k(xq)
+qpath = Path(__file__).with_name("q8k_small.npz")
+np.savez_compressed(qpath, x=xq, d=qd, qs=qq, bsums=qb)
+print("wrote", qpath, qpath.stat().st_size, "bytes")

@@ -84,3 +84,26 @@ def test_gpu_matches_committed_fixtures(backend):
     assert np.array_equal(be.read(go, np.float32, (32, 64)), G["gather_out"])
     assert np.array_equal(be.read(goff, np.int32, (9,)), G["gather_offsets"])
     assert np.array_equal(be.read(gtok, np.int32, (32,)), G["gather_token"])
+
+
+Q8K = np.load(Path(__file__).parent / "golden" / "q8k_small.npz")
+
+
+def _same_q8k(got, what):
+    assert np.array_equal(got[0].view(np.uint32), Q8K["d"].view(np.uint32)), f"{what}: d"
+    assert np.array_equal(got[1], Q8K["qs"]) and np.array_equal(got[2], Q8K["bsums"]), f"{what}: qs / bsums"
+
+
+def test_oracle_reproduces_q8_k_fixture_bitwise():
+    with np.errstate(all="ignore"):
+        _same_q8k(orc.quantize_rows_q8_k(Q8K["x"]), "oracle")
+
+
+@pytest.mark.gpu
+def test_gpu_matches_committed_q8_k_fixture(backend):
+    x = np.ascontiguousarray(Q8K["x"])
+    T, n = x.shape
+    nb = (n + 255) // 256
+    d, qs, bs = backend.launch_quantize_rows_q8_k(backend.upload(x), T, n)
+    _same_q8k((backend.read(d, np.float32, (T, nb)), backend.read(qs, np.int8, (T, nb * 256)),
+               backend.read(bs, np.int16, (T, nb * 16))), "gpu")
