@@ -336,3 +336,31 @@ def test_q8_0_quotients_at_the_rounding_boundaries_bit_exact(backend, amax):
     backend.launch_qk_norm_rope_kv_write(backend.upload(q), backend.upload(kk), backend.upload(rows), None, None, T, nq, nkv, hd, 1e-6,
                                          hd, backend.upload(pos), 1e6, AGN_Q8_0, dk, dv, T)
     assert np.array_equal(backend.read(dv, np.uint8, (T, bpt)), ref), float(amax)
+
+
+@pytest.mark.gpu
+def test_q8_0_pack_random_blocks_over_the_whole_exponent_range_bit_exact(backend):
+    """262,144 blocks whose magnitudes span 1e-44 .. 3e38 (subnormal scales, scales near f16 overflow, blocks made of
+    small integers times the scale, i.e. quotients on or next to k and k + 0.5): the bytes of the reference's division."""
+    r = np.random.default_rng(2611)
+    T, hd = 8192, 1024
+    mag = (10.0 ** r.uniform(-44, 38.5, size=(T, hd // 32, 1))).astype(np.float32)
+    base = r.standard_normal((T, hd // 32, 32)).astype(np.float32)
+    half_steps = r.integers(-254, 255, size=(T, hd // 32, 32)).astype(np.float32) * np.float32(0.5)
+    pick = r.random((T, hd // 32, 1)) < 0.5  # half of the blocks: values k/2 * scale with max 127 * scale
+    with np.errstate(all="ignore"):
+        vals = np.where(pick, half_steps / np.float32(127.0), base / np.float32(4.5))
+        vals[..., 0] = np.where(pick[..., 0], 1.0, vals[..., 0])
+        x = (vals * mag).astype(np.float32).reshape(T, hd)
+    x[~np.isfinite(x)] = 0.0
+    pos = np.arange(T, dtype=np.int32)
+    bpt = backend.kv_bytes_per_token(AGN_Q8_0, hd)
+    ref = np.zeros((T, bpt), np.uint8)
+    orc.kv_write_rows(AGN_Q8_0, x, pos, ref)
+    dk, dv = backend.upload(np.zeros((T, bpt), np.uint8)), backend.upload(np.zeros((T, bpt), np.uint8))
+    dx = backend.upload(x)
+    backend.kv_write(AGN_Q8_0, dx, dx, dk, dv, T, hd, backend.upload(pos), T)
+    got = backend.read(dk, np.uint8, (T, bpt))
+    bad = np.argwhere(got != ref)
+    assert bad.size == 0, f"{len(bad)} bytes differ, first at token {bad[0][0]} byte {bad[0][1]}: {got[tuple(bad[0])]} vs {ref[tuple(bad[0])]}"
+    assert np.array_equal(backend.read(dv, np.uint8, (T, bpt)), ref)
