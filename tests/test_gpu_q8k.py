@@ -289,3 +289,24 @@ def test_q8_k_ops_in_a_recorded_graph(backend):
             q8k_close_to_chain(rep_b, orc.quantize_rows_q8_k(orc.silu_mul(a["gate"], a["up"], THREADS), THREADS), "replay vs oracle chain")
     finally:
         be.graph_destroy(g)
+
+
+def test_quantize_random_blocks_over_the_whole_exponent_range_bit_exact(backend):
+    """131,072 blocks with magnitudes from 1e-44 to 3e38 (subnormal maxima, whose iscale overflows, up to maxima whose
+    iscale is almost subnormal); half of them hold multiples of max / 254, so that iscale * v lands on or next to k and
+    k + 0.5."""
+    r = np.random.default_rng(2612)
+    T, nb = 2048, 64
+    mag = (10.0 ** r.uniform(-44, 38.5, size=(T, nb, 1))).astype(np.float32)
+    base = r.standard_normal((T, nb, 256)).astype(np.float32)
+    half_steps = r.integers(-254, 255, size=(T, nb, 256)).astype(np.float32) * np.float32(0.5)
+    pick = r.random((T, nb, 1)) < 0.5
+    sign = np.where(r.random((T, nb)) < 0.5, np.float32(-1.0), np.float32(1.0))
+    with np.errstate(all="ignore"):
+        vals = np.where(pick, half_steps / np.float32(127.0), base / np.float32(5.0))
+        vals[..., 0] = np.where(pick[..., 0], sign, vals[..., 0])  # the block maximum of the structured blocks, either sign
+        x = (vals * mag).astype(np.float32).reshape(T, nb * 256)
+    x[~np.isfinite(x)] = 0.0
+    with np.errstate(all="ignore"):
+        want = orc.quantize_rows_q8_k(x, THREADS)
+    assert_same(gpu_quantize(backend, x), want, "random blocks, whole exponent range")
