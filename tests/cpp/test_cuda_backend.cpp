@@ -173,6 +173,12 @@ int main() {
         bool same = g.get_u64("llama.embedding_length", &h) && h == 8 && g.version() == 3 && ti.n_rows == 3 && ti.row_len == 8;
         for (int i = 0; i < 8; i++) same = same && rows[i] == w[16 + i] && rows[8 + i] == w[i];
         expect(same, "GgufFile parse + upload + get_rows");
+        // the pre-upload loop on the same container (memory of the caller: no pages to release)
+        std::vector<agn_tensor_info> infos;
+        uint64_t released = 1;
+        auto all = g.upload_all(be, {"w"}, true, &infos, &released);
+        auto back = be.read<float>(all[0], w.size());
+        expect(all.size() == 1 && infos[0].n_bytes == w.size() * 4 && released == 0 && back == w, "GgufFile upload_all");
     }
     {  // softmax that writes the valid entries only: the tail keeps the sentinel, the valid part matches the oracle
         const int R = 5, L = 516;
