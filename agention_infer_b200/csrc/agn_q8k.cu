@@ -17,7 +17,7 @@
 // cvt.rzi.s32.f32 does, NaN -> 0) and the wrapping i32 -> i8 one.
 //
 // 4 bytes read and 1.14 written per value: bound by HBM, provided the instruction count stays
-// near 100 per block and warp.  One warp owns one block of 256 values, lane l holding values
+// near 120 per block and warp (it is 122).  One warp owns one block of 256 values, lane l holding values
 // 4l..4l+3 and 128+4l..128+4l+3 (two coalesced 128-bit loads); the maximum is two warp-wide redux
 // instructions, a group of 16 values is four neighbouring lanes, the quantised values leave as one
 // 32-bit store per lane and half-block.  The fused kernels compute their f32 values with the
@@ -29,13 +29,8 @@ namespace {
 
 constexpr int QK_K = 256;
 
-// Warp-wide maximum / minimum of f32 values in one instruction (sm_100a); NaN operands are ignored
-// (the result is NaN only when every lane holds one).
-__device__ __forceinline__ float warp_max_f32(float v) {
-    float r;
-    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
-    return r;
-}
+// Warp-wide minimum of f32 values in one instruction (sm_100a), the counterpart of agn_warp_max; NaN
+// operands are ignored (the result is NaN only when every lane holds one).
 __device__ __forceinline__ float warp_min_f32(float v) {
     float r;
     asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
@@ -68,7 +63,7 @@ __device__ __forceinline__ float q8k_first_max(const float4 (&v)[N], int lane) {
         mx = max3_f32(max3_f32(mx, v[k].x, v[k].y), v[k].z, v[k].w);
         mn = min3_f32(min3_f32(mn, v[k].x, v[k].y), v[k].z, v[k].w);
     }
-    mx = warp_max_f32(mx);
+    mx = agn_warp_max(mx);
     mn = warp_min_f32(mn);
     if (mx != -mn) return mx > -mn ? mx : mn;  // one sign holds the largest magnitude alone
     // +a and -a both present, nothing but zeros, or nothing but NaN (mx = -inf, mn = +inf)
