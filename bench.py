@@ -508,6 +508,7 @@ def run_ours(args, cfg, ops_list, wl):
     # ---- ops of the path that are not part of this configuration's step, each alone (f32 only):
     #      fused residual-add + norm, KV-cache packing, and a causal softmax at prefill size
     extra_ops = {}
+    q8k_report = None
     if not f16 and not args.no_extras and step_bytes < 8e9:
         from agention_infer_b200 import AGN_BF16, AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
         hd_kv = nkv * hd
@@ -580,6 +581,38 @@ def run_ours(args, cfg, ops_list, wl):
             torch.cuda.synchronize()
             us = a.elapsed_time(b) * 1e3 / reps
             extra_ops[name] = {"us": round(us, 2), "gbs": round(nbytes / (us * 1e-6) / 1e9, 1), "bytes": nbytes}
+        if "quantize_rows_q8_k" in extras and not args.no_verify:
+            # The Q8_K rows against the oracle, on 64 strided rows of buffer set 0: the quantiser alone must give the
+            # oracle's bytes for the same f32 rows; the fused norm is held to the oracle's norm -> quantise chain
+            # (scales to 1e-5 relative, a quantised value at most one step off, group sums exact).
+            from oracle import oracle as orc
+            b_ = ex_sets[0]
+            rows = torch.from_numpy(np.unique(np.linspace(0, T - 1, min(T, args.check_rows)).astype(np.int64))).to(dev)
+            nbk = H // 256
+            xs = b_["x"].index_select(0, rows).contiguous()
+            sub = (torch.empty(rows.numel() * nbk, device=dev), torch.empty(rows.numel() * H, dtype=torch.int8, device=dev),
+                   torch.empty(rows.numel() * nbk * 16, dtype=torch.int16, device=dev))
+            host = lambda t3: (t3[0].cpu().numpy().reshape(-1, nbk), t3[1].cpu().numpy().reshape(-1, H),
+                               t3[2].cpu().numpy().reshape(-1, nbk * 16))
+            be.launch_quantize_rows_q8_k(xs, rows.numel(), H, out=sub)
+            be.sync(); torch.cuda.synchronize()
+            got = host(sub)
+            x_h = xs.cpu().numpy()
+            ref = orc.quantize_rows_q8_k(x_h)
+            exact = bool(np.array_equal(got[0].view(np.uint32), ref[0].view(np.uint32)) and np.array_equal(got[1], ref[1])
+                         and np.array_equal(got[2], ref[2]))
+            be.launch_rms_norm_q8_k(xs, w, rows.numel(), H, cfg.eps, out=sub)
+            be.sync(); torch.cuda.synchronize()
+            got = host(sub)
+            ref = orc.quantize_rows_q8_k(orc.rms_norm_rows(x_h, synth.norm_weight(cfg.index, "w", H), cfg.eps))
+            dq = np.abs(got[1].astype(np.int32) - ref[1].astype(np.int32))
+            d_rel = float(np.max(np.abs(got[0] - ref[0]) / np.maximum(np.abs(ref[0]), 1e-30)))
+            sums_ok = bool(np.array_equal(got[2], got[1].reshape(got[1].shape[0], -1, 16).astype(np.int16).sum(axis=2)))
+            q8k_report = {"rows_checked": int(rows.numel()), "quantize_rows_bit_exact": exact,
+                          "rms_norm_q8_k": {"max_rel_err_d": float(f"{d_rel:.3g}"), "max_step_err_q": int(dq.max()),
+                                            "fraction_of_q_off_by_one": float(f"{float((dq != 0).mean()):.3g}"),
+                                            "bsums_are_group_sums": sums_ok},
+                          "ok": exact and d_rel <= 1e-5 and int(dq.max()) <= 1 and float((dq != 0).mean()) < 2e-3 and sums_ok}
         del ex_sets
     if sampler:
         sampler.mark_load(False)
@@ -736,7 +769,7 @@ def run_ours(args, cfg, ops_list, wl):
     mine = [sharding.checksum(b0[n][: min(T, 512)].contiguous().cpu().numpy()) for n in outs]
     chk = sharding.gather_objects(mine)
     agree = all(c == chk[0] for c in chk)
-    verified = agree and (oracle_report is None or oracle_report["ok"])
+    verified = agree and (oracle_report is None or oracle_report["ok"]) and (q8k_report is None or q8k_report["ok"])
 
     if rank == 0:
         peak, peak_src = measured_peaks()
@@ -772,7 +805,7 @@ def run_ours(args, cfg, ops_list, wl):
             "ops": per_op, "extra_ops": extra_ops, "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
             "verification": {"ranks": len(chk), "outputs_checked": outs, "identical_across_ranks": agree,
                              "how": "checksums of every op's output for identical inputs, gathered over the process group",
-                             "oracle": oracle_report},
+                             "oracle": oracle_report, "q8_k_rows": q8k_report},
             "strong_c4": split_rec, "decode_c3": decode_rec,
         }
         if world == 1 and not args.no_cpu and not f16:
