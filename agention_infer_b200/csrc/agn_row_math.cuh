@@ -50,7 +50,7 @@ __device__ __forceinline__ float4 agn_silu_mul4(float4 g, float4 u) {
 // instructions per value.  Here the quotient is first approximated as v * rcp.approx(scale): within
 // 1.5 * 2^-23 relative of the true quotient t, so within 3.1e-5 of fl(t) for |t| < 128.  If that
 // approximation lies more than 1e-4 away from every k + 0.5, fl(t) rounds to the same integer, which
-// is read off the mantissa of |qa| + 2^23 (round to nearest; exact ties never get here).  A lane with a
+// is read off the mantissa of qa + 1.5 * 2^23 (round to nearest; exact ties never get here).  A lane with a
 // value too close to a boundary, beyond +-127.25, or not finite (NaN value, infinite or subnormal
 // scale) recomputes its four values the reference's way.  Same bytes for every input.
 __device__ __forceinline__ void agn_q8_0_quant4(const float (&x)[4], float scale, uint32_t (&q)[4]) {
@@ -60,12 +60,11 @@ __device__ __forceinline__ void agn_q8_0_quant4(const float (&x)[4], float scale
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const float qa = __fmul_rn(x[i], inv);
-        const float a = fabsf(qa);
-        const float m = __fadd_rn(a, 8388608.0f);              // 2^23 + round_to_nearest(a) for a < 2^22
-        const float g = __fsub_rn(a, __fsub_rn(m, 8388608.0f));  // a - round_to_nearest(a), in [-0.5, 0.5]
-        sure = sure && (fabsf(g) <= 0.4999f) && (a < 127.25f);  // false for NaN
-        const int mag = __float_as_int(m) & 0xff;
-        q[i] = (uint32_t)(qa < 0.0f ? -mag : mag) & 0xffu;
+        // 1.5 * 2^23 + round_to_nearest(qa) for |qa| < 2^22: the low mantissa bits are the integer in two's complement
+        const float m = __fadd_rn(qa, 12582912.0f);
+        const float g = __fsub_rn(qa, __fsub_rn(m, 12582912.0f));  // qa - round_to_nearest(qa), in [-0.5, 0.5]
+        sure = sure && (fabsf(g) <= 0.4999f) && (fabsf(qa) < 127.25f);  // false for NaN
+        q[i] = (uint32_t)__float_as_int(m) & 0xffu;
     }
     if (!sure) {
 #pragma unroll
