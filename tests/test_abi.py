@@ -60,6 +60,15 @@ def test_null_context_is_rejected(lib):
     assert lib.agn_sync(None) == _abi.AGN_EINVAL
     assert lib.agn_silu_mul_f32(None, None, None, None, 4) == _abi.AGN_EINVAL
     assert lib.agn_ctx_create(0, None) == _abi.AGN_EINVAL
+    assert lib.agn_quantize_rows_q8_k_f32(None, None, 1, 256, None, None, None) == _abi.AGN_EINVAL
+    assert lib.agn_rms_norm_q8_k_f32(None, None, None, 1, 256, 1e-6, None, None, None) == _abi.AGN_EINVAL
+    assert lib.agn_host_quantize_rows_q8_k_f32(None, None, 1, 256, None, None, None) == _abi.AGN_EINVAL
+
+
+def test_host_side_helpers_need_no_gpu(lib):
+    assert [lib.agn_q8_k_blocks(n) for n in (-5, 0, 1, 255, 256, 257, 3584)] == [0, 0, 1, 1, 1, 2, 14]
+    released = C.c_uint64(7)
+    assert lib.agn_gguf_release_pages(None, 0, 10, C.byref(released)) == _abi.AGN_EINVAL and released.value == 0
 
 
 def test_context_creation_fails_loudly_without_a_gpu(lib):
