@@ -13,6 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libagention_b200.so"
 AGN_OK, AGN_EINVAL, AGN_EUNSUPPORTED_DTYPE, AGN_ECUDA, AGN_EOOB_ID, AGN_ENOMEM, AGN_ETIMEOUT = range(7)
 AGN_EFORMAT, AGN_ENOTFOUND, AGN_EIO = 7, 8, 9
 AGN_F32, AGN_F16, AGN_Q8_0, AGN_Q4_K, AGN_Q6_K, AGN_BF16 = 0, 1, 8, 12, 14, 30
+AGN_KV_Q8_0_WORDS = 1008  # a KV-cache layout (the GPU path's 36-byte Q8_0 blocks), not a GgmlType
 AGN_Q5_0, AGN_Q5_K, AGN_Q2_K = 6, 13, 10
 AGN_ROPE_NEOX, AGN_ROPE_NORMAL = 0, 1
 

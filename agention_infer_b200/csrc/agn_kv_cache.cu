@@ -31,6 +31,7 @@ struct KvArgs {
     int64_t T, hd, max_seq;
     int pos_start;
     int bytes_per_token;
+    int words;  // Q8_0 in the GPU path's blocks of nine 32-bit words (f32 scale, offset-binary bytes)
     uint32_t *flags;
 };
 
@@ -88,10 +89,16 @@ kv_write_q8_0_kernel(const KvArgs a) {
         for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         if (!on) continue;
         const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-        unsigned char *blk = tok + b * 34;
-        if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
         uint32_t q[4];
         agn_q8_0_quant4(x, scale, q);
+        if (a.words) {  // nine aligned words per block; values past the row's end are 0, stored as byte 128
+            uint32_t *blk32 = reinterpret_cast<uint32_t *>(tok + b * 36);
+            if (lane8 == 0) blk32[0] = __float_as_uint(scale);
+            blk32[1 + lane8] = (q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24)) ^ 0x80808080u;
+            continue;
+        }
+        unsigned char *blk = tok + b * 34;
+        if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
         if (e0 + 3 < left) {  // blocks are 2-byte aligned: two 16-bit stores
             *reinterpret_cast<uint16_t *>(blk + 2 + e0) = (uint16_t)(q[0] | (q[1] << 8));
             *reinterpret_cast<uint16_t *>(blk + 4 + e0) = (uint16_t)(q[2] | (q[3] << 8));
@@ -174,13 +181,19 @@ kv_write_multi_kernel(const KvArgs a) {
             if (in_range && lane_on) {
                 const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
                 const int lane8 = threadIdx.x & 7;
-                unsigned char *blk = tok + (size_t)(threadIdx.x >> 3) * 34;
-                if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
                 const float xs[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
                 uint32_t q[4];
                 agn_q8_0_quant4(xs, scale, q);
-                *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
-                *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+                if (a.words) {
+                    uint32_t *blk32 = reinterpret_cast<uint32_t *>(tok + (size_t)(threadIdx.x >> 3) * 36);
+                    if (lane8 == 0) blk32[0] = __float_as_uint(scale);
+                    blk32[1 + lane8] = (q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24)) ^ 0x80808080u;
+                } else {
+                    unsigned char *blk = tok + (size_t)(threadIdx.x >> 3) * 34;
+                    if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+                    *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
+                    *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+                }
             }
         }
     }
@@ -199,7 +212,16 @@ kv_read_kernel(const unsigned char *__restrict__ k_cache, const unsigned char *_
     if (vec) {
         for (int i = threadIdx.x; i < (int)(hd >> 2); i += blockDim.x) {
             float4 o;
-            if (q8) {
+            if (q8 == 2) {  // nine words per block: f32 scale, then offset-binary bytes (dequant_kv_q8_0, kernels_wgpu.rs:705-718)
+                const int d = 4 * i;
+                const uint32_t *blk = reinterpret_cast<const uint32_t *>(tok + (d >> 5) * 36);
+                const float scale = __uint_as_float(blk[0]);
+                const uint32_t wq = blk[1 + ((d & 31) >> 2)];
+                o.x = __fmul_rn((float)(int)(wq & 0xff) - 128.0f, scale);
+                o.y = __fmul_rn((float)(int)((wq >> 8) & 0xff) - 128.0f, scale);
+                o.z = __fmul_rn((float)(int)((wq >> 16) & 0xff) - 128.0f, scale);
+                o.w = __fmul_rn((float)(int)(wq >> 24) - 128.0f, scale);
+            } else if (q8) {
                 const int d = 4 * i;
                 const unsigned char *blk = tok + (d >> 5) * 34;
                 const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
@@ -217,7 +239,10 @@ kv_read_kernel(const unsigned char *__restrict__ k_cache, const unsigned char *_
     } else {
         for (int d = threadIdx.x; d < (int)hd; d += blockDim.x) {
             float val;
-            if (q8) {
+            if (q8 == 2) {
+                const unsigned char *blk = tok + (d >> 5) * 36;
+                val = __fmul_rn((float)(int)blk[4 + (d & 31)] - 128.0f, __uint_as_float(*reinterpret_cast<const uint32_t *>(blk)));
+            } else if (q8) {
                 const unsigned char *blk = tok + (d >> 5) * 34;
                 const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk)));
                 val = __fmul_rn((float)(signed char)blk[2 + (d & 31)], scale);
@@ -232,6 +257,7 @@ kv_read_kernel(const unsigned char *__restrict__ k_cache, const unsigned char *_
 int kv_bytes_per_token(int32_t dtype, int64_t hd) {
     if (dtype == AGN_F16) return (int)(hd * 2);
     if (dtype == AGN_Q8_0) return (int)(((hd + 31) / 32) * 34);
+    if (dtype == AGN_KV_Q8_0_WORDS) return (int)(((hd + 31) / 32) * 36);  // `words_per_token * 4`, gpu_resident.rs:276-277
     return 0;
 }
 
@@ -246,36 +272,37 @@ extern "C" int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float 
                                     int64_t max_seq_len) {
     AGN_CHECK_CTX(ctx);
     const int bpt = head_dim_kv > 0 ? kv_bytes_per_token(kv_dtype, head_dim_kv) : 0;
-    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
-        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_write: KV dtype %d is neither f16 (1) nor q8_0 (8)", kv_dtype);
+    const bool words = kv_dtype == AGN_KV_Q8_0_WORDS;
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0 && !words)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_write: KV dtype %d is neither f16 (1), q8_0 (8) nor q8_0 in words (1008)", kv_dtype);
     if (T < 0 || head_dim_kv <= 0 || max_seq_len <= 0)
         return agn_fail(ctx, AGN_EINVAL, "kv_write: T=%lld head_dim_kv=%lld max_seq_len=%lld", (long long)T,
                         (long long)head_dim_kv, (long long)max_seq_len);
     if (T == 0) return AGN_OK;
     if (!k || !v || !k_cache || !v_cache) return agn_fail(ctx, AGN_EINVAL, "kv_write: null pointer");
-    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 1)
-        return agn_fail(ctx, AGN_EINVAL, "kv_write: caches must be 2-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & (words ? 3 : 1))
+        return agn_fail(ctx, AGN_EINVAL, "kv_write: caches must be %d-byte aligned", words ? 4 : 2);
     AGN_CUDA(ctx, cudaSetDevice(ctx->device));
     KvArgs a;
     a.k = k; a.v = v; a.k_cache = static_cast<unsigned char *>(k_cache); a.v_cache = static_cast<unsigned char *>(v_cache);
-    a.pos = pos; a.T = T; a.hd = head_dim_kv; a.max_seq = max_seq_len; a.pos_start = pos_start; a.bytes_per_token = bpt;
+    a.pos = pos; a.T = T; a.hd = head_dim_kv; a.max_seq = max_seq_len; a.pos_start = pos_start; a.bytes_per_token = bpt; a.words = words ? 1 : 0;
     a.flags = ctx->d_flags;
     // several tokens per CTA once there are enough tokens to fill the GPU that way
     constexpr int TPC = 4;
     const bool multi = ctx->tune_kv_multi && T >= 4 * TPC * (int64_t)ctx->sm_count && head_dim_kv % 32 == 0 && head_dim_kv <= 1024 &&
                        agn_aligned16(k) && agn_aligned16(v) &&
-                       (kv_dtype == AGN_Q8_0 || (agn_aligned(k_cache, 8) && agn_aligned(v_cache, 8)));
+                       (kv_dtype != AGN_F16 || (agn_aligned(k_cache, 8) && agn_aligned(v_cache, 8)));
     if (multi) {
         if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
         const int threads = (int)(((head_dim_kv / 4) + 31) / 32 * 32);
         const dim3 grid((unsigned)((T + TPC - 1) / TPC), 2);
-        if (kv_dtype == AGN_Q8_0) agn_launch(ctx, kv_write_multi_kernel<true, TPC>, grid, dim3(threads), 0, a);
+        if (kv_dtype != AGN_F16) agn_launch(ctx, kv_write_multi_kernel<true, TPC>, grid, dim3(threads), 0, a);
         else agn_launch(ctx, kv_write_multi_kernel<false, TPC>, grid, dim3(threads), 0, a);
         ctx->flags_dirty = true;
         AGN_LAUNCHED(ctx, "kv_write_multi");
         return AGN_OK;
     }
-    if (kv_dtype == AGN_Q8_0) {
+    if (kv_dtype != AGN_F16) {
         if (T > 0x7fffffffLL) return agn_fail(ctx, AGN_EINVAL, "kv_write: too many rows");
         int threads = (int)(((head_dim_kv + 31) / 32) * 8);  // eight lanes per 32-value block
         threads = ((threads + 31) / 32) * 32;
@@ -295,8 +322,10 @@ extern "C" int32_t agn_kv_write_f32(agn_ctx *ctx, int32_t kv_dtype, const float 
 extern "C" int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k_cache, const void *v_cache, int64_t n_pos,
                                    int64_t head_dim_kv, float *k_out, float *v_out) {
     AGN_CHECK_CTX(ctx);
-    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
-        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_read: KV dtype %d is neither f16 (1) nor q8_0 (8)", kv_dtype);
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0 && kv_dtype != AGN_KV_Q8_0_WORDS)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "kv_read: KV dtype %d is neither f16 (1), q8_0 (8) nor q8_0 in words (1008)", kv_dtype);
+    if (kv_dtype == AGN_KV_Q8_0_WORDS && ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 3))
+        return agn_fail(ctx, AGN_EINVAL, "kv_read: caches must be 4-byte aligned");
     if (n_pos < 0 || head_dim_kv <= 0)
         return agn_fail(ctx, AGN_EINVAL, "kv_read: n_pos=%lld head_dim_kv=%lld", (long long)n_pos, (long long)head_dim_kv);
     if (n_pos == 0) return AGN_OK;
@@ -307,7 +336,7 @@ extern "C" int32_t agn_kv_read_f32(agn_ctx *ctx, int32_t kv_dtype, const void *k
     if (threads > 256) threads = 256;
     agn_launch(ctx, kv_read_kernel, dim3((unsigned)n_pos, 2), dim3(threads), 0, static_cast<const unsigned char *>(k_cache),
                static_cast<const unsigned char *>(v_cache), n_pos, head_dim_kv, kv_bytes_per_token(kv_dtype, head_dim_kv),
-               kv_dtype == AGN_Q8_0 ? 1 : 0, k_out, v_out);
+               kv_dtype == AGN_Q8_0 ? 1 : kv_dtype == AGN_KV_Q8_0_WORDS ? 2 : 0, k_out, v_out);
     AGN_LAUNCHED(ctx, "kv_read");
     return AGN_OK;
 }

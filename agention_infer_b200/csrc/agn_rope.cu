@@ -46,6 +46,7 @@ struct RopeArgs {
     unsigned char *k_cache, *v_cache;
     int64_t max_seq;
     int bytes_per_token;
+    int kv_words;  // Q8_0 cache blocks are the GPU path's nine 32-bit words instead of 34 bytes
     uint32_t *flags;
 };
 
@@ -56,8 +57,10 @@ enum { KV_NONE = 0, KV_F16 = 1, KV_Q8_0 = 2 };
 // eight lanes that hold one 32-value block (float4 numbers 8b .. 8b+7) share amax through three
 // shuffles; scale = amax / 127 (1 if amax is 0), q = clamp(round(v / scale)).  Must be called by
 // every lane of the warp (`on` = this lane holds data of a K / V row with a valid slot).
+// words: the GPU path's block of nine 32-bit words (f32 scale, then offset-binary bytes, kernels_wgpu.rs:583-698)
+// instead of the 34-byte block.
 template <int KV>
-__device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_head, int i, int blocks_before) {
+__device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_head, int i, int blocks_before, bool words) {
     if (KV == KV_F16) {
         if (on) ActVec<__half>::store(reinterpret_cast<__half *>(tok_head), i, x);
     } else if (KV == KV_Q8_0) {
@@ -66,14 +69,20 @@ __device__ __forceinline__ void kv_pack4(float4 x, bool on, unsigned char *tok_h
         for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         if (on) {
             const float scale = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-            unsigned char *blk = tok_head + (size_t)(blocks_before + (i >> 3)) * 34;
             const int lane8 = i & 7;
-            if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
             const float xs[4] = {x.x, x.y, x.z, x.w};
             uint32_t q[4];
             agn_q8_0_quant4(xs, scale, q);
-            *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
-            *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+            if (words) {
+                uint32_t *blk = reinterpret_cast<uint32_t *>(tok_head + (size_t)(blocks_before + (i >> 3)) * 36);
+                if (lane8 == 0) blk[0] = __float_as_uint(scale);
+                blk[1 + lane8] = (q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24)) ^ 0x80808080u;  // byte = q + 128
+            } else {
+                unsigned char *blk = tok_head + (size_t)(blocks_before + (i >> 3)) * 34;
+                if (lane8 == 0) *reinterpret_cast<uint16_t *>(blk) = __half_as_ushort(__float2half_rn(scale));
+                *reinterpret_cast<uint16_t *>(blk + 2 + 4 * lane8) = (uint16_t)(q[0] | (q[1] << 8));
+                *reinterpret_cast<uint16_t *>(blk + 4 + 4 * lane8) = (uint16_t)(q[2] | (q[3] << 8));
+            }
         }
     }
 }
@@ -308,7 +317,7 @@ rope_heads_kernel(const RopeArgs a) {
 #pragma unroll
                 for (int l = 0; l < VPL; l++) {
                     const int i = lane + W * l;
-                    kv_pack4<KV>(v[s][l], slot >= 0 && i < hd4, tok_head, i, blocks_before);
+                    kv_pack4<KV>(v[s][l], slot >= 0 && i < hd4, tok_head, i, blocks_before, a.kv_words != 0);
                 }
             }
         }
@@ -566,6 +575,7 @@ bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 // What the fused cache write needs besides the rope arguments.
 struct KvFuse {
     int kv;  // KV_F16 or KV_Q8_0
+    int words;  // Q8_0 in the GPU path's 36-byte blocks
     const float *v;
     unsigned char *k_cache, *v_cache;
     int64_t max_seq;
@@ -599,7 +609,7 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
     a.pos_start = pos_start; a.freq_scale = freq_scale; a.eps = eps; a.tpc = 1;
     a.inv_head_dim = 1.0f / (float)head_dim;
     a.denom = nullptr;
-    a.v = nullptr; a.k_cache = nullptr; a.v_cache = nullptr; a.max_seq = 0; a.bytes_per_token = 0; a.flags = ctx->d_flags;
+    a.v = nullptr; a.k_cache = nullptr; a.v_cache = nullptr; a.max_seq = 0; a.bytes_per_token = 0; a.kv_words = 0; a.flags = ctx->d_flags;
     if (n_rot >= 2) {
         int32_t rc = agn_rope_table(ctx, theta, n_rot, &a.denom);
         if (rc != AGN_OK) return rc;
@@ -644,10 +654,12 @@ int32_t rope_dispatch(agn_ctx *ctx, const char *name, AT *q, AT *k, const float 
     if (kvf && fast && sizeof(AT) == 4 && n_kv > 0 && W == 8 && (VPL == 4 || VPL == 2) && (kvf->kv == KV_F16 || T >= 512) &&
         (mode == MODE_NORMAL || mode == (VPL == 4 ? MODE_NEOX_K2 : MODE_NEOX_K1)) && agn_aligned16(kvf->v) &&
         (kvf->kv == KV_F16 ? (agn_aligned(kvf->k_cache, 8) && agn_aligned(kvf->v_cache, 8) && kvf->bytes_per_token % 8 == 0)
-                           : (head_dim % 32 == 0 && agn_aligned(kvf->k_cache, 2) && agn_aligned(kvf->v_cache, 2)))) {
+                           : (head_dim % 32 == 0 && agn_aligned(kvf->k_cache, kvf->words ? 4 : 2) &&
+                              agn_aligned(kvf->v_cache, kvf->words ? 4 : 2)))) {
         kv_ok = true;
         a.v = kvf->v; a.k_cache = kvf->k_cache; a.v_cache = kvf->v_cache; a.max_seq = kvf->max_seq;
         a.bytes_per_token = kvf->bytes_per_token;
+        a.kv_words = kvf->words;
     }
     if (fast) {
         // tokens per CTA: aim at 32 head rows per CTA, keep the sin/cos table small
@@ -746,8 +758,8 @@ extern "C" int32_t agn_qk_norm_rope_kv_write_f32(agn_ctx *ctx, float *q, float *
                                                  int32_t pos_start, float theta, float freq_scale, int32_t layout,
                                                  int32_t kv_dtype, void *k_cache, void *v_cache, int64_t max_seq_len) {
     AGN_CHECK_CTX(ctx);
-    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0)
-        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "qk_norm_rope_kv_write: cache type %d is neither f16 nor q8_0", kv_dtype);
+    if (kv_dtype != AGN_F16 && kv_dtype != AGN_Q8_0 && kv_dtype != AGN_KV_Q8_0_WORDS)
+        return agn_fail(ctx, AGN_EUNSUPPORTED_DTYPE, "qk_norm_rope_kv_write: cache type %d is neither f16, q8_0 nor q8_0 in words", kv_dtype);
     if (n_kv_heads <= 0 || head_dim <= 0 || max_seq_len <= 0)
         return agn_fail(ctx, AGN_EINVAL, "qk_norm_rope_kv_write: n_kv_heads=%d head_dim=%d max_seq_len=%lld", n_kv_heads, head_dim,
                         (long long)max_seq_len);
@@ -756,6 +768,7 @@ extern "C" int32_t agn_qk_norm_rope_kv_write_f32(agn_ctx *ctx, float *q, float *
     const int64_t hd_kv = (int64_t)n_kv_heads * head_dim;
     KvFuse f;
     f.kv = kv_dtype == AGN_F16 ? KV_F16 : KV_Q8_0;
+    f.words = kv_dtype == AGN_KV_Q8_0_WORDS ? 1 : 0;
     f.v = v;
     f.k_cache = static_cast<unsigned char *>(k_cache);
     f.v_cache = static_cast<unsigned char *>(v_cache);

@@ -63,7 +63,10 @@ typedef enum agn_dtype {
     AGN_Q4_K = 12,
     AGN_Q5_K = 13,
     AGN_Q6_K = 14,
-    AGN_BF16 = 30
+    AGN_BF16 = 30,
+    /* not a GgmlType: a KV-cache layout, Q8_0 values in the GPU path's blocks of nine 32-bit words
+     * (see agn_kv_write_f32) */
+    AGN_KV_Q8_0_WORDS = 1008
 } agn_dtype;
 
 /* Pairing of rotated dims: NeoX (d, d + n_rot/2) is what the reference does
@@ -297,7 +300,13 @@ AGN_API int32_t agn_get_rows_f32(agn_ctx *ctx, int32_t dtype, const void *table,
 
 /* KV-cache write: `KvCache::write` / `write_range` (src/model/mod.rs:648-672) with
  * `KvDtype::pack` (:567-585); GPU twins `kv_cache_write` / `kv_cache_write_q8_0`
- * (src/ops/kernels_wgpu.rs:566-698).  kv_dtype is AGN_F16 or AGN_Q8_0 (`KvDtype`, :536-539).
+ * (src/ops/kernels_wgpu.rs:566-698).  kv_dtype is AGN_F16 or AGN_Q8_0 (`KvDtype`, :536-539: the
+ * CPU path's tight 34-byte blocks, f16 scale + 32 int8), or AGN_KV_Q8_0_WORDS for the block the
+ * reference's GPU path stores (`kv_cache_write_q8_0`, kernels_wgpu.rs:583-698; `words_per_token`,
+ * src/model/llama/gpu_resident.rs:276): nine 32-bit words per 32 values — the scale as f32 bits,
+ * then four bytes per word, offset-binary (byte = q + 128) — with the same amax, scale and q as
+ * the 34-byte form, values past head_dim_kv in the last block stored as 0 (byte 128), caches
+ * 4-byte aligned.
  * k, v: [T, head_dim_kv] f32 (head_dim_kv = n_kv_heads * head_dim); k_cache, v_cache: one
  * layer's [max_seq_len, agn_kv_bytes_per_token] bytes.  Token t goes to slot pos[t] (device
  * int32) or pos_start + t.  Bit-exact with the CPU pack.  A slot outside [0, max_seq_len)

@@ -505,7 +505,33 @@ static uint16_t f32_to_f16_bits(float f) { /* half::f16::from_f32: round to near
 size_t orc_kv_bytes_per_token(int dtype, size_t hd) { /* src/model/mod.rs:550-556 */
     if (dtype == ORC_F16) return hd * 2;
     if (dtype == ORC_Q8_0) return ((hd + 31) / 32) * 34;
+    if (dtype == ORC_KV_Q8_0_WORDS) return ((hd + 31) / 32) * 36; /* words_per_token * 4, gpu_resident.rs:276-277 */
     return 0;
+}
+
+/* The GPU path's Q8_0 cache block (kv_cache_write_q8_0, src/ops/kernels_wgpu.rs:583-698): nine 32-bit words per
+ * 32 values — word 0 the scale as f32 bits, words 1..8 four bytes each, offset-binary (byte = q + 128), the low
+ * byte first.  Values past n in the last block are 0 (byte 128) and are written.  amax, scale and q as in the
+ * CPU packing; the kernel's `round` is taken as f32::round (half away from zero) and a NaN quotient as q = 0,
+ * like KvDtype::pack: the two layouts hold the same numbers. */
+static void kv_pack_q8_0_words(const float *x, size_t n, uint8_t *out) {
+    for (size_t b = 0; b * 32 < n; b++) {
+        const float *blk = x + b * 32;
+        size_t cnt = n - b * 32 < 32 ? n - b * 32 : 32;
+        uint8_t *o = out + b * 36;
+        float amax = 0.0f;
+        for (size_t i = 0; i < cnt; i++) amax = fmaxf(amax, fabsf(blk[i]));
+        float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        uint32_t sb;
+        memcpy(&sb, &scale, 4);
+        o[0] = (uint8_t)sb; o[1] = (uint8_t)(sb >> 8); o[2] = (uint8_t)(sb >> 16); o[3] = (uint8_t)(sb >> 24);
+        for (size_t i = 0; i < 32; i++) {
+            float q = i < cnt ? roundf(blk[i] / scale) : 0.0f;
+            q = q < -127.0f ? -127.0f : (q > 127.0f ? 127.0f : q);
+            if (q != q) q = 0.0f;
+            o[4 + i] = (uint8_t)((int)q + 128);
+        }
+    }
 }
 
 /* KvDtype::pack, src/model/mod.rs:567-585 */
@@ -516,6 +542,10 @@ void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out) {
             out[2 * i] = (uint8_t)(h & 0xFF);
             out[2 * i + 1] = (uint8_t)(h >> 8);
         }
+        return;
+    }
+    if (dtype == ORC_KV_Q8_0_WORDS) {
+        kv_pack_q8_0_words(x, n, out);
         return;
     }
     for (size_t b = 0; b * 32 < n; b++) {
@@ -541,6 +571,15 @@ void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out) {
 void orc_kv_unpack(int dtype, const uint8_t *bytes, size_t n, float *out) {
     if (dtype == ORC_F16) {
         for (size_t i = 0; i < n; i++) out[i] = orc_f16_to_f32(rd_u16(bytes + 2 * i));
+        return;
+    }
+    if (dtype == ORC_KV_Q8_0_WORDS) { /* dequant_kv_q8_0, src/ops/kernels_wgpu.rs:705-718 */
+        for (size_t i = 0; i < n; i++) {
+            const uint8_t *blk = bytes + (i / 32) * 36;
+            float scale;
+            memcpy(&scale, blk, 4);
+            out[i] = ((float)blk[4 + i % 32] - 128.0f) * scale;
+        }
         return;
     }
     for (size_t i = 0; i < n; i++) {

@@ -49,7 +49,10 @@ enum {
     ORC_Q4_K = 12,
     ORC_Q5_K = 13,
     ORC_Q6_K = 14,
-    ORC_BF16 = 30
+    ORC_BF16 = 30,
+    /* not a GgmlType: the GPU path's Q8_0 cache layout, 36-byte blocks of nine 32-bit words
+     * (src/ops/kernels_wgpu.rs:583-698) */
+    ORC_KV_Q8_0_WORDS = 1008
 };
 
 enum { ORC_OK = 0, ORC_ESHORT = 1, ORC_EROW = 2, ORC_EDTYPE = 3, ORC_ELEN = 4 };
@@ -141,7 +144,9 @@ int orc_get_rows(int dtype, const uint8_t *table, size_t table_len, size_t n_voc
                  size_t row_len, const uint32_t *ids, size_t T, float *out, int threads);
 
 /* KV cache: KvDtype::bytes_per_token / pack / unpack (src/model/mod.rs:550-604),
- * KvCache::write_range (:660-672), read_up_to (:678-697); dtype ORC_F16 or ORC_Q8_0.
+ * KvCache::write_range (:660-672), read_up_to (:678-697); dtype ORC_F16 or ORC_Q8_0, or
+ * ORC_KV_Q8_0_WORDS for the GPU path's 36-byte blocks (kv_cache_write_q8_0 / dequant_kv_q8_0,
+ * src/ops/kernels_wgpu.rs:583-718).
  * Parity unpinned: the reference has no test for them. */
 size_t orc_kv_bytes_per_token(int dtype, size_t hd);
 void orc_kv_pack(int dtype, const float *x, size_t n, uint8_t *out);

@@ -15,6 +15,7 @@ HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
 
 F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
+KV_Q8_0_WORDS = 1008  # the GPU path's Q8_0 cache layout (36-byte blocks), not a GgmlType
 Q5_0, Q5_K, Q2_K = 6, 13, 10
 NEOX, NORMAL = 0, 1
 OK, ESHORT, EROW, EDTYPE, ELEN = 0, 1, 2, 3, 4

@@ -134,7 +134,7 @@ def test_get_rows_stays_inside(backend, dtype, row_len, T):
         assert st == orc.OK and np.array_equal(out.get(np.float32, (T, rl)).view(np.uint32), ref.view(np.uint32))
 
 
-@pytest.mark.parametrize("kv_dtype", [AGN_F16, AGN_Q8_0])
+@pytest.mark.parametrize("kv_dtype", [AGN_F16, AGN_Q8_0, 1008])
 @pytest.mark.parametrize("T,hd", [(1, 512), (5, 100), (3, 33), (4, 1024)])
 def test_kv_write_and_read_stay_inside(backend, kv_dtype, T, hd):
     max_seq = 16

@@ -364,3 +364,76 @@ def test_q8_0_pack_random_blocks_over_the_whole_exponent_range_bit_exact(backend
     bad = np.argwhere(got != ref)
     assert bad.size == 0, f"{len(bad)} bytes differ, first at token {bad[0][0]} byte {bad[0][1]}: {got[tuple(bad[0])]} vs {ref[tuple(bad[0])]}"
     assert np.array_equal(backend.read(dv, np.uint8, (T, bpt)), ref)
+
+
+def test_oracle_q8_0_words_layout_by_hand():
+    """kv_cache_write_q8_0 / dequant_kv_q8_0 (src/ops/kernels_wgpu.rs:583-718): nine words per 32 values, the f32 scale
+    first, then offset-binary bytes; a ragged last block is padded with zeros (byte 128)."""
+    W = orc.KV_Q8_0_WORDS
+    x = np.zeros((1, 40), np.float32); x[0, :5] = [1.0, -2.0, 0.5, 127.0, -127.0]; x[0, 33] = 3.0
+    assert orc.kv_bytes_per_token(W, 40) == 72 and orc.kv_bytes_per_token(W, 512) == 576
+    c = np.zeros((1, 72), np.uint8)
+    orc.kv_write_rows(W, x, np.array([0], np.int32), c)
+    assert c[0, :4].view(np.float32)[0] == 1.0                       # amax 127 -> scale 1
+    assert list(c[0, 4:10]) == [129, 126, 129, 255, 1, 128]           # q + 128, round half away (0.5 -> 1)
+    assert c[0, 36:40].view(np.float32)[0] == np.float32(3.0) / np.float32(127.0)
+    assert list(c[0, 40:44]) == [128, 255, 128, 128] and np.all(c[0, 48:72] == 128)  # padding is written as q = 0
+    back = orc.kv_read(W, c, 1, 40)
+    assert list(back[0, :5]) == [1.0, -2.0, 1.0, 127.0, -127.0] and back[0, 33] == np.float32(127.0) * (np.float32(3.0) / np.float32(127.0))
+    # the same numbers as the 34-byte form: q equal, scale equal before its rounding to f16
+    c34 = np.zeros((1, orc.kv_bytes_per_token(orc.Q8_0, 40)), np.uint8)
+    orc.kv_write_rows(orc.Q8_0, x, np.array([0], np.int32), c34)
+    assert np.array_equal(c34[0, 2:34].view(np.int8).astype(np.int16) + 128, c[0, 4:36].astype(np.int16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,hd,max_seq", [(4096, 512, 4096), (300, 1024, 512), (1, 512, 64), (33, 100, 50), (17, 33, 40), (2500, 256, 2500)])
+def test_kv_write_and_read_q8_0_words_bit_exact(backend, T, hd, max_seq):
+    from agention_infer_b200 import AGN_KV_Q8_0_WORDS as W
+    k = synth.activations(2, "k", (T, hd)); v = synth.activations(2, "q", (T, hd)) * np.float32(3.0)
+    k[0, :min(hd, 32)] = 0.0
+    if hd >= 64:
+        v[0, 40] = np.nan; v[0, 3] = np.inf
+    pos = synth.rng_for(2, "pos").permutation(max_seq)[:T].astype(np.int32)
+    bpt = backend.kv_bytes_per_token(W, hd)
+    assert bpt == orc.kv_bytes_per_token(orc.KV_Q8_0_WORDS, hd) == ((hd + 31) // 32) * 36
+    ref_k = np.zeros((max_seq, bpt), np.uint8); ref_v = np.zeros((max_seq, bpt), np.uint8)
+    with np.errstate(all="ignore"):
+        orc.kv_write_rows(orc.KV_Q8_0_WORDS, k, pos, ref_k); orc.kv_write_rows(orc.KV_Q8_0_WORDS, v, pos, ref_v)
+    dkc, dvc = backend.upload(np.zeros_like(ref_k)), backend.upload(np.zeros_like(ref_v))
+    backend.kv_write(W, backend.upload(k), backend.upload(v), dkc, dvc, T, hd, backend.upload(pos), max_seq)
+    assert np.array_equal(backend.read(dkc, np.uint8, ref_k.shape), ref_k)
+    assert np.array_equal(backend.read(dvc, np.uint8, ref_v.shape), ref_v)
+    clean = np.ascontiguousarray(ref_k)
+    ko, vo = backend.kv_read(W, backend.upload(clean), backend.upload(clean), max_seq, hd)
+    want = orc.kv_read(orc.KV_Q8_0_WORDS, clean, max_seq, hd)
+    assert np.array_equal(backend.read(ko, np.float32, (max_seq, hd)).view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(backend.read(vo, np.float32, (max_seq, hd)).view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("norm", [True, False])
+def test_fused_rope_kv_write_q8_0_words_equals_the_two_ops(backend, norm):
+    from agention_infer_b200 import AGN_KV_Q8_0_WORDS as W
+    T, nq, nkv, hd = 600, 8, 2, 128
+    q = synth.activations(2, "q", (T, nq * hd)); k = synth.activations(2, "k", (T, nkv * hd)); v = synth.activations(2, "x", (T, nkv * hd))
+    wq, wk = synth.norm_weight(2, "wq", hd), synth.norm_weight(2, "wk", hd)
+    pos = synth.positions(2, T, False)
+    dpos = backend.upload(pos)
+    dwq, dwk = (backend.upload(wq), backend.upload(wk)) if norm else (None, None)
+    bpt = backend.kv_bytes_per_token(W, nkv * hd)
+    # the two launches
+    dq, dk, dv = backend.upload(q), backend.upload(k), backend.upload(v)
+    if norm:
+        backend.launch_qk_norm_rope_qk(dq, dk, dwq, dwk, T, nq, nkv, hd, 1e-6, hd, dpos, 1e6)
+    else:
+        backend.launch_rope_qk(dq, dk, T, nq, nkv, hd, hd, dpos, 1e6)
+    k1, v1 = backend.upload(np.zeros((T, bpt), np.uint8)), backend.upload(np.zeros((T, bpt), np.uint8))
+    backend.kv_write(W, dk, dv, k1, v1, T, nkv * hd, dpos, T)
+    # one launch
+    dq2, dk2 = backend.upload(q), backend.upload(k)
+    k2, v2 = backend.upload(np.zeros((T, bpt), np.uint8)), backend.upload(np.zeros((T, bpt), np.uint8))
+    backend.launch_qk_norm_rope_kv_write(dq2, dk2, dv, dwq, dwk, T, nq, nkv, hd, 1e-6, hd, dpos, 1e6, W, k2, v2, T)
+    for a_, b_ in ((k1, k2), (v1, v2)):
+        assert np.array_equal(backend.read(a_, np.uint8, (T, bpt)), backend.read(b_, np.uint8, (T, bpt)))
+    assert np.array_equal(backend.read(dq, np.float32, q.shape).view(np.uint32), backend.read(dq2, np.float32, q.shape).view(np.uint32))
