@@ -510,7 +510,7 @@ def run_ours(args, cfg, ops_list, wl):
     extra_ops = {}
     q8k_report = None
     if not f16 and not args.no_extras and step_bytes < 8e9:
-        from agention_infer_b200 import AGN_BF16, AGN_F16 as KV_F16, AGN_Q8_0 as KV_Q8_0
+        from agention_infer_b200 import AGN_BF16, AGN_F16 as KV_F16, AGN_KV_Q8_0_WORDS as KV_Q8_0_WORDS, AGN_Q8_0 as KV_Q8_0
         hd_kv = nkv * hd
         Ls = min(T, 2048)
         ex_sets = []
@@ -520,6 +520,8 @@ def run_ours(args, cfg, ops_list, wl):
                             "k": rn(T, hd_kv), "v": rn(T, hd_kv),
                             "kc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
                             "vc": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0, hd_kv), dtype=torch.uint8, device=dev),
+                            "kw": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0_WORDS, hd_kv), dtype=torch.uint8, device=dev),
+                            "vw": torch.empty(T * be.kv_bytes_per_token(KV_Q8_0_WORDS, hd_kv), dtype=torch.uint8, device=dev),
                             "kh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
                             "vh": torch.empty(T * hd_kv, dtype=torch.float16, device=dev),
                             "sc": rn(nq, Ls, Ls) * 2.0, "pr": torch.empty(nq, Ls, Ls, device=dev),
@@ -536,6 +538,8 @@ def run_ours(args, cfg, ops_list, wl):
                                                14 * T * H + 4 * H),
             "kv_write_q8_0": (lambda b: be.kv_write(KV_Q8_0, b["k"], b["v"], b["kc"], b["vc"], T, hd_kv, None, T),
                               2 * T * (4 * hd_kv + be.kv_bytes_per_token(KV_Q8_0, hd_kv))),
+            "kv_write_q8_0_words": (lambda b: be.kv_write(KV_Q8_0_WORDS, b["k"], b["v"], b["kw"], b["vw"], T, hd_kv, None, T),
+                                    2 * T * (4 * hd_kv + be.kv_bytes_per_token(KV_Q8_0_WORDS, hd_kv))),
             "kv_write_f16": (lambda b: be.kv_write(KV_F16, b["k"], b["v"], b["kh"], b["vh"], T, hd_kv, None, T),
                              2 * T * (4 * hd_kv + 2 * hd_kv)),
             f"softmax_causal_{nq}x{Ls}x{Ls}": (lambda b: be.launch_softmax_rows(b["sc"], nq * Ls, Ls, out=b["pr"], causal_period=Ls),
