@@ -225,6 +225,19 @@ impl CudaBackend {
         Ok(out)
     }
 
+    /// `quantize_row_q8_k(x)` at the top of `WeightMap::matmul_into` (src/model/mod.rs:386) for a host vector: the
+    /// reference's own `Q8KRow`, filled by the GPU through the host-slice staging ring.
+    pub fn quantize_row_q8_k(&self, x: &[f32]) -> Result<crate::quant::q8_k::Q8KRow> {
+        let n = x.len();
+        let nb = unsafe { agn_q8_k_blocks(n as i64) } as usize;
+        let (mut d, mut qs, mut bsums) = (vec![0f32; nb], vec![0i8; nb * 256], vec![0i16; nb * 16]);
+        self.check(unsafe {
+            agn_host_quantize_rows_q8_k_f32(self.ctx, x.as_ptr(), 1, n as i64, d.as_mut_ptr(), qs.as_mut_ptr(), bsums.as_mut_ptr())
+        })?;
+        self.sync()?;
+        Ok(crate::quant::q8_k::Q8KRow { d, qs, bsums, n })
+    }
+
     fn q8k_rows(&self, t: usize, n: usize) -> Result<Q8KRows> {
         let nb = unsafe { agn_q8_k_blocks(n as i64) } as usize;
         Ok(Q8KRows { d: self.empty(4 * t * nb)?, qs: self.empty(256 * t * nb)?, bsums: self.empty(32 * t * nb)?, n })
